@@ -1,0 +1,352 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path on B200.
+
+Workload (BASELINE config 2): MXFP4 weight-only linears of the Llama-3-8B MLP shape,
+W_gate/W_up [14336, 4096] and W_down [4096, 14336], bf16 activations X [M, 4096] for
+M in {1, 8, 64, 512, 4096}. One *step* is one pass of the sweep: for every M, the fused
+gate/up pair with the SiLU*mul epilogue, then the down projection.
+
+Headline `value`: quantized-GEMM HBM GB/s over the decode-shaped part of the sweep (M <= 64):
+algorithmic bytes (packed codes + scales + activations in + out) / device time. The prefill part
+(M >= 512) is reported as TFLOP/s under `prefill`. Weights rotate over several distinct packed
+copies (together larger than L2) so that no launch finds its weights in L2.
+
+`python bench.py --impl reference` times the CPU restatement of the reference's path (the
+reference's own libxsmm build is not possible here) on the host cores.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+D_MODEL, D_FF = 4096, 14336
+SWEEP = [1, 8, 64, 512, 4096]
+DECODE_MAX_M = 64
+N_COPIES = 6  # distinct packed weight sets: 6 x 93.6 MB = 561 MB >> 126 MB of L2
+
+
+def packed_bytes(N, K):
+    return N * K // 2 + N * K // 32
+
+
+def op_bytes(M, pair):
+    """Algorithmic bytes of one launch (weights once, activations in, result out)."""
+    if pair:  # gate/up: two weights, X in, H out
+        return 2 * packed_bytes(D_FF, D_MODEL) + M * D_MODEL * 2 + M * D_FF * 2
+    return packed_bytes(D_MODEL, D_FF) + M * D_FF * 2 + M * D_MODEL * 2
+
+
+def op_flops(M, pair):
+    return (4 if pair else 2) * M * D_FF * D_MODEL
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "src": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_arm(seconds_target=12.0):
+    """Times the CPU restatement on a bounded sample: the gate/up pair at M = 1 and M = 8 over a slice
+    of 1024 output features (of 14336), all host threads. Returns GB/s of algorithmic bytes."""
+    import numpy as np
+    from oracle import oracle as O
+    rng = np.random.default_rng(0)
+    Ns = 1024
+    wg = O.randn_bf16(rng, (Ns, D_MODEL), 0.02)
+    wu = O.randn_bf16(rng, (Ns, D_MODEL), 0.02)
+    cg, sg = O.remap_and_quantize_mxfp4(wg)
+    cu, su = O.remap_and_quantize_mxfp4(wu)
+    threads = O.lib().orc_num_threads()
+    total_b, total_t = 0.0, 0.0
+    per_m = {}
+    for M in (1, 8):
+        x = O.randn_bf16(rng, (M, D_MODEL))
+        O.qlinear_mxfp4_packed(x, cg, sg, cu, su, act=O.ACT_SILU)  # warm-up
+        reps, t0 = 0, time.perf_counter()
+        while True:
+            O.qlinear_mxfp4_packed(x, cg, sg, cu, su, act=O.ACT_SILU)
+            reps += 1
+            dt = time.perf_counter() - t0
+            if dt > seconds_target / 2 or reps >= 200:
+                break
+        b = reps * (2 * packed_bytes(Ns, D_MODEL) + M * D_MODEL * 2 + M * Ns * 2)
+        per_m[M] = b / dt / 1e9
+        total_b += b
+        total_t += dt
+    return {"value": total_b / total_t / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"gate/up pair, M in (1, 8), {Ns} of {D_FF} output features, K = {D_MODEL}; "
+                      f"per-M GB/s {', '.join(f'M={m}: {v:.2f}' for m, v in per_m.items())}"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t0 = time.perf_counter()
+    vals = []
+    for _ in range(max(1, args.warmup) - 1 + 1):
+        pass
+    per_step = max(2.0, min(20.0, 60.0 / max(1, args.steps)))
+    for _ in range(args.steps):
+        vals.append(cpu_arm(per_step))
+    dt = time.perf_counter() - t0
+    v = sum(x["value"] for x in vals) / len(vals)
+    cb = dict(vals[-1])
+    cb["value"] = v
+    line = {"impl": "reference", "metric": "qgemm_hbm_gbs", "value": v, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x mxfp4 -> fp32 acc",
+            "data": "synthetic", "config": workload_config(), "cpu_baseline": cb,
+            "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "CPU restatement of the reference path (oracle/tpx_oracle.c): the reference's libxsmm build is not available"}
+    print(json.dumps(line))
+
+
+def workload_config():
+    return {"workload": "config 2: MXFP4 weight-only linear sweep, Llama-3-8B MLP shape "
+                        "(gate/up [14336x4096] pair with SiLU*mul, down [4096x14336]), M in {1,8,64,512,4096}",
+            "metric_scope": f"HBM GB/s over M <= {DECODE_MAX_M}; prefill TFLOP/s over M >= 512 reported under 'prefill'",
+            "l2": f"weights rotate over {N_COPIES} distinct packed copies (561 MB > 126 MB L2)",
+            "parallelism": "replicas (one independent sweep per GPU)"}
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from tpp_pytorch_extension_b200 import _lib
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    from tpp_pytorch_extension_b200._C import _qtype
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()  # fails loudly when the CUDA library is missing
+
+    def block(w):  # BlockedParameter.block() with bk=16, bc=64, VNNI2
+        N, K = w.shape
+        return w.view(N // 16, 16, K // 64, 32, 2).permute(0, 2, 3, 1, 4).contiguous()
+
+    g = torch.Generator(device="cpu").manual_seed(0)
+    sets = []
+    for c in range(N_COPIES):
+        ws = []
+        for (N, K) in ((D_FF, D_MODEL), (D_FF, D_MODEL), (D_MODEL, D_FF)):
+            if c == 0:  # seed-0 CPU weights for the first set, device RNG for the L2-rotation copies
+                w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+            else:
+                w = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
+            q = _qtype.remap_and_quantize_mxfp4(block(w))
+            q.packed(drop_interchange=True)
+            ws.append(q)
+            del w
+        sets.append(ws)
+    xs_host = {M: torch.randn(M, D_MODEL, generator=g).to(torch.bfloat16).pin_memory() for M in SWEEP}
+    xs = {M: xs_host[M].to(dev) for M in SWEEP}
+    ys_host = {M: torch.empty(M, D_MODEL, dtype=torch.bfloat16).pin_memory() for M in SWEEP}
+    torch.cuda.synchronize()
+
+    def launches_for(M):
+        return 2 * ((M + 31) // 32)  # the streaming kernel re-launches per 32 tokens
+
+    counter = [0]
+
+    def sweep(events=None, host=False):
+        for mi, M in enumerate(SWEEP):
+            wg, wu, wd = sets[counter[0] % N_COPIES]
+            counter[0] += 1
+            x = xs_host[M].to(dev, non_blocking=True) if host else xs[M]
+            if events is not None:
+                events[mi][0].record()
+            h = F.fc_gate_up(x, wg, wu)
+            if events is not None:
+                events[mi][1].record()
+            y = F.fc_plain(h, wd)
+            if events is not None:
+                events[mi][2].record()
+            if host:
+                ys_host[M].copy_(y, non_blocking=True)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        sweep()
+    # ---- device-resident timing with per-launch events
+    evs = [[[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in SWEEP] for _ in range(args.steps)]
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for s in range(args.steps):
+        sweep(evs[s])
+    t_end.record()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = t_start.elapsed_time(t_end)
+    seg = np.zeros((len(SWEEP), 2))
+    for s in range(args.steps):
+        for mi in range(len(SWEEP)):
+            seg[mi, 0] += evs[s][mi][0].elapsed_time(evs[s][mi][1])
+            seg[mi, 1] += evs[s][mi][1].elapsed_time(evs[s][mi][2])
+    seg /= args.steps  # ms per launch group
+    # ---- end to end: host buffers in, host buffers out, through the public ops
+    for _ in range(2):
+        sweep(host=True)
+    barrier()
+    e_evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in SWEEP] for _ in range(args.steps)]
+    e2e_ms = np.zeros(len(SWEEP))
+    for s in range(args.steps):
+        for mi, M in enumerate(SWEEP):
+            wg, wu, wd = sets[counter[0] % N_COPIES]
+            counter[0] += 1
+            a, b = e_evs[s][mi]
+            a.record()
+            x = xs_host[M].to(dev, non_blocking=True)
+            y = F.fc_plain(F.fc_gate_up(x, wg, wu), wd)
+            ys_host[M].copy_(y, non_blocking=True)
+            b.record()
+    barrier()
+    for s in range(args.steps):
+        for mi in range(len(SWEEP)):
+            e2e_ms[mi] += e_evs[s][mi][0].elapsed_time(e_evs[s][mi][1])
+    e2e_ms /= args.steps
+
+    dec = [i for i, M in enumerate(SWEEP) if M <= DECODE_MAX_M]
+    pre = [i for i, M in enumerate(SWEEP) if M > DECODE_MAX_M]
+    dec_bytes = sum(op_bytes(SWEEP[i], True) + op_bytes(SWEEP[i], False) for i in dec)
+    dec_ms = float(sum(seg[i].sum() for i in dec))
+    pre_flops = sum(op_flops(SWEEP[i], True) + op_flops(SWEEP[i], False) for i in pre)
+    pre_ms = float(sum(seg[i].sum() for i in pre))
+    stats = torch.tensor([total_ms, dec_ms, pre_ms, float(sum(e2e_ms[i] for i in dec))], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    total_ms, dec_ms, pre_ms, e2e_dec_ms = [float(v) for v in stats.cpu()]
+    pk = peaks()
+    value = world * dec_bytes / (dec_ms * 1e-3) / 1e9
+    e2e_value = world * dec_bytes / (e2e_dec_ms * 1e-3) / 1e9
+    # dominant decode kernel: the gate/up pair launch with the largest time share among M <= 64
+    dom = max(dec, key=lambda i: seg[i, 0])
+    dom_gbs = op_bytes(SWEEP[dom], True) / (seg[dom, 0] * 1e-3) / 1e9
+    kernels = []
+    for i, M in enumerate(SWEEP):
+        for j, pair in enumerate((True, False)):
+            ms = float(seg[i, j])
+            kernels.append({"M": M, "op": "gate_up" if pair else "down", "ms": round(ms, 5),
+                            "gbs": round(op_bytes(M, pair) / (ms * 1e-3) / 1e9, 1),
+                            "tflops": round(op_flops(M, pair) / (ms * 1e-3) / 1e12, 2),
+                            "launches": launches_for(M) // 2})
+    if rank == 0:
+        line = {
+            "metric": "qgemm_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x mxfp4 -> fp32 acc", "data": "synthetic",
+            "config": workload_config(),
+            "prefill": {"tflops": world * pre_flops / (pre_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                        "frac_of_bf16_peak": pre_flops / (pre_ms * 1e-3) / 1e12 / pk["bf16_tflops"], "peak_src": pk["src"]},
+            "roofline": {"bound": "hbm", "kernel": f"qlinear_stream_mxfp4 gate/up pair, M={SWEEP[dom]}",
+                         "achieved": dom_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": dom_gbs / pk["hbm_gbs"],
+                         "peak_src": pk["src"], "traffic": None},
+            "kernels": kernels,
+            "e2e": {"value": e2e_value, "unit": "GB/s",
+                    "h2d_bytes_per_step": sum(M * D_MODEL * 2 for M in SWEEP),
+                    "d2h_bytes_per_step": sum(M * D_MODEL * 2 for M in SWEEP),
+                    "scope": "same decode-shaped launches, pinned host X in and host Y out inside the timed region"},
+            "gpu_launches": args.steps * sum(launches_for(M) for M in SWEEP),
+            "clocks": clocks,
+        }
+        if world == 1:
+            line["cpu_baseline"] = cpu_arm()
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

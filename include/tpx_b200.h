@@ -1,0 +1,111 @@
+/*
+ * tpx_b200 — C ABI of the B200 (sm_100a) implementation of the LLM-inference hot path of
+ * libxsmm/tpp-pytorch-extension: weight-only quantized linear (MXFP4 / int8 weights, bf16
+ * activations, fused bias / GeLU / SiLU / mul / residual epilogues), RMSNorm, RoPE + KV-cache
+ * write and attention over the blocked KV cache.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its name ends in _host;
+ *   - bf16 tensors are passed as uint16_t bit patterns, row-major, contiguous;
+ *   - every call enqueues work on `stream` (a cudaStream_t passed as void*) and returns without
+ *     synchronising; nothing allocates device memory: scratch is passed in by the caller;
+ *   - return value 0 = success; otherwise a TPX_ERR_* code, with text from tpx_last_error().
+ *     The reference aborts the process on its own argument checks (TPP_ASSERT -> exit(1),
+ *     src/csrc/utils.h:34-41); this library reports instead.
+ *
+ * Each declaration cites the reference interface it replaces (paths relative to the reference
+ * repository root).
+ */
+#ifndef TPX_B200_H
+#define TPX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  TPX_OK = 0,
+  TPX_ERR_ARG = 1,      /* bad shape / pointer / alignment                         */
+  TPX_ERR_UNSUPPORTED = 2,
+  TPX_ERR_CUDA = 3,     /* a CUDA runtime call failed; see tpx_last_error()        */
+  TPX_ERR_SCRATCH = 4   /* scratch buffer too small                                */
+};
+
+/* activation selector of the fused epilogue (post-ops of src/csrc/fused_gemm.h:1343-1410) */
+enum { TPX_ACT_NONE = 0, TPX_ACT_GELU = 1, TPX_ACT_SILU = 2, TPX_ACT_RELU = 3 };
+
+/* weight kinds (dispatch of src/csrc/fused_gemm.h:1509-1597) */
+enum { TPX_W_MXFP4 = 1, TPX_W_INT8 = 2 };
+
+int tpx_version(void);
+const char* tpx_last_error(void);
+/* number of SMs of the current device (used by callers to size scratch) */
+int tpx_sm_count(void);
+
+/* ---------------------------------------------------------------- quantize / remap
+ * Replaces _C._qtype.remap_and_quantize_mxfp4 (src/csrc/qtypes.cpp:783-864, pybind :1086).
+ * in:  blocked bf16 weight [K1][C1][C2][K2][C3] as BlockedParameter.block() lays it out
+ *      (src/tpp_pytorch_extension/utils/blocked_layout.py:268-292), C3 = 2.
+ * out: codes  uint8 [K1*K2/32][C1][C2][32]   (two E2M1 codes per byte, low nibble = even lane)
+ *      scales uint8 [K1*K2/32][C1][C2*2/32][32]  (UE8M0)
+ * i.e. the storage of the reference's quantized tensor, bit for bit.                       */
+int tpx_remap_and_quantize_mxfp4(const uint16_t* blocked, int64_t K1, int64_t C1, int64_t C2, int64_t K2,
+                                 int64_t C3, uint8_t* codes, uint8_t* scales, void* stream);
+
+/* Replaces _C._qtype.remap_and_quantize_qint8 (src/csrc/qtypes.cpp:866-932, pybind :1087).
+ * block_size plays the role of the QINT8_BLOCK_SIZE environment variable (:28), and is
+ * adjusted downwards as the reference does when it does not divide K (:878-889); the block
+ * size actually used is returned through *block_size_used.
+ * out: q int8 [K1][C/B][B/4][K2][4], scales fp32 [K1][C/B][1][K2].                         */
+int tpx_remap_and_quantize_qint8(const uint16_t* blocked, int64_t K1, int64_t C1, int64_t C2, int64_t K2,
+                                 int64_t C3, int64_t block_size, int8_t* q, float* scales,
+                                 int64_t* block_size_used, void* stream);
+
+/* Replaces Tensor.dequantize() on the two quantized carriers
+ * (PerBlockMxFPQuantizer::dequantize src/csrc/qtypes.cpp:438-445, PerBlockAffineQuantizer
+ * :521-560): fp32 output in the same blocked 5-D shape as the quantizer input.            */
+int tpx_dequantize_mxfp4(const uint8_t* codes, const uint8_t* scales, int64_t K1, int64_t C1, int64_t C2,
+                         int64_t K2, float* out, void* stream);
+int tpx_dequantize_qint8(const int8_t* q, const float* scales, int64_t K1, int64_t C1, int64_t C2,
+                         int64_t K2, float* out, void* stream);
+
+/* ---------------------------------------------------------------- device repack
+ * The reference keeps one blocked layout and, for prefill, a second copy with merged blocks
+ * (wt_tensor_for_first_token, src/csrc/llm/fused_llm_infer.cpp:365-420). Here the interchange
+ * tensors above are re-laid once into the streaming layout the kernels read:
+ *   MXFP4 codes  [N/16][Kp/128][2][32 lanes][16 B], scales [N/16][Kp/128][16 rows][4]
+ *   int8  values [N/16][K/64][2][32 lanes][16 B],  scales fp32 [N][K/B]
+ * (Kp = K rounded up to 128; the padding holds zero codes).
+ * tpx_packed_bytes returns the byte sizes of the two outputs.                              */
+int tpx_packed_bytes(int kind, int64_t N, int64_t K, int64_t block_size, size_t* codes_bytes,
+                     size_t* scales_bytes);
+int tpx_repack_mxfp4(const uint8_t* codes, const uint8_t* scales, int64_t N, int64_t K, uint8_t* pk_codes,
+                     uint8_t* pk_scales, void* stream);
+int tpx_repack_qint8(const int8_t* q, const float* scales, int64_t N, int64_t K, int64_t block_size,
+                     uint8_t* pk_codes, float* pk_scales, void* stream);
+
+/* ---------------------------------------------------------------- quantized linear
+ * Replaces GemmCaller / fc_plain with a post-op (src/csrc/fused_gemm.h:1509-1650) and
+ * torch.ops.tpp_llm.fc_plain (src/csrc/llm/fused_llm_infer.cpp:1514-1566):
+ *     y[M][N] = epilogue( x[M][K] . dequant(W)[N][K]^T + bias[N] )
+ *     epilogue(v) = act(v) * mul_in[M][N] (MulPostOp) + res[M][N] * res_scale (AddScalePostOp)
+ * With pk_codes2 != NULL the call computes the gate/up pair of the SwiGLU MLP in one pass
+ * (the reference issues SiluPostOp then MulPostOp, fused_llm_infer.cpp:1271-1272):
+ *     y = act(x.W^T) * (x.W2^T)
+ * NULL for bias / mul_in / res / pk_codes2 means "absent" (the reference's empty tensor).
+ * fp32 accumulation, one bf16 rounding at the store.
+ * scratch: tpx_qlinear_scratch_bytes(...) bytes, 256-byte aligned, zero-filled once by the
+ * caller before first use (the kernels leave it zeroed where it must be).                  */
+size_t tpx_qlinear_scratch_bytes(int kind, int64_t M, int64_t N, int64_t K, int dual);
+int tpx_qlinear(int kind, const uint8_t* pk_codes, const void* pk_scales, const uint8_t* pk_codes2,
+                const void* pk_scales2, int64_t block_size, const uint16_t* x, int64_t M, int64_t N,
+                int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
+                float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TPX_B200_H */

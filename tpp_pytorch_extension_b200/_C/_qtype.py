@@ -1,0 +1,176 @@
+"""Mirror of the reference's `_C._qtype` submodule (src/csrc/qtypes.cpp:1075-1093) on CUDA.
+
+The reference returns torch quantized tensors carried by a custom `at::Quantizer`
+(src/csrc/qtypes.h:30-410). Those carriers cannot live on a CUDA device without the reference's
+C++ classes, so the same information travels in a small Python object, `QTensor`: the code bytes
+and the per-block scales in exactly the reference's storage layout, plus the quantizer's
+attributes (`qscheme`, `block_size`, `axis`, `pack_size`). `QTensor.packed()` lazily re-lays the
+weight into the streaming layout the kernels read."""
+import ctypes
+
+import torch
+
+from .. import _lib
+
+W_MXFP4, W_INT8 = 1, 2
+kPerBlockMxFP = "per_block_mxfp"      # at::kPerBlockMxFP, src/csrc/qtypes.h:12
+kPerBlockAffine = "per_block_affine"  # at::kPerBlockAffine, src/csrc/qtypes.h:11
+
+
+class QTensor:
+    is_quantized = True
+
+    def __init__(self, codes, scales, shape, qscheme, block_size, axis=2, is_vnni=True):
+        self.codes = codes      # uint8 [K1,C1,C2,K2] (mxfp4, two codes per byte) or int8 [K1,C1,C2,K2,4]
+        self.scales = scales    # uint8 [K1,C1,C2/16,K2] or fp32 [K1,C1,1,K2]
+        self.shape = tuple(shape)  # logical 5-D shape, as Tensor.sizes() of the reference tensor
+        self._qscheme = qscheme
+        self.block_size = int(block_size)
+        self.axis = axis
+        self.is_vnni = is_vnni
+        self._packed = None
+
+    # --- the attributes the reference's dispatch reads (src/csrc/fused_gemm.h:1517-1540)
+    def qscheme(self):
+        return self._qscheme
+
+    @property
+    def dtype(self):
+        return torch.quint4x2 if self._qscheme == kPerBlockMxFP else torch.qint8
+
+    @property
+    def device(self):
+        return self.codes.device
+
+    def size(self, dim=None):
+        return self.shape if dim is None else self.shape[dim]
+
+    def dim(self):
+        return len(self.shape)
+
+    def numel(self):
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+    @property
+    def kind(self):
+        return W_MXFP4 if self._qscheme == kPerBlockMxFP else W_INT8
+
+    @property
+    def out_features(self):
+        return self.shape[0] * self.shape[3]
+
+    @property
+    def in_features(self):
+        return self.shape[1] * self.shape[2] * self.shape[4]
+
+    def dequantize(self):
+        """fp32 tensor of the same 5-D shape (Tensor.dequantize(), src/csrc/qtypes.cpp:438-445, :521-529)."""
+        K1, C1, C2, K2, _ = self.shape
+        out = torch.empty(self.shape, dtype=torch.float32, device=self.codes.device)
+        L = _lib.lib()
+        with torch.cuda.device(self.codes.device):
+            if self.kind == W_MXFP4:
+                _lib.check(L.tpx_dequantize_mxfp4(self.codes.data_ptr(), self.scales.data_ptr(), K1, C1, C2, K2,
+                                                  out.data_ptr(), _lib.stream()))
+            else:
+                _lib.check(L.tpx_dequantize_qint8(self.codes.data_ptr(), self.scales.data_ptr(), K1, C1, C2, K2,
+                                                  out.data_ptr(), _lib.stream()))
+        return out
+
+    def packed(self, drop_interchange=False):
+        """(codes, scales) in the streaming layout; built once and cached."""
+        if self._packed is None:
+            L = _lib.lib()
+            N, K = self.out_features, self.in_features
+            cb, sb = ctypes.c_size_t(), ctypes.c_size_t()
+            _lib.check(L.tpx_packed_bytes(self.kind, N, K, self.block_size, ctypes.byref(cb), ctypes.byref(sb)))
+            dev = self.codes.device
+            pc = torch.empty(cb.value, dtype=torch.uint8, device=dev)
+            with torch.cuda.device(dev):
+                if self.kind == W_MXFP4:
+                    if self.shape[2] * self.shape[4] != 64 or self.shape[3] != 32:
+                        raise _lib.TpxError("MXFP4 repack expects the [N/32, K/64, 32, 32, 2] layout of remap_and_quantize_mxfp4")
+                    ps = torch.empty(sb.value, dtype=torch.uint8, device=dev)
+                    _lib.check(L.tpx_repack_mxfp4(self.codes.data_ptr(), self.scales.data_ptr(), N, K, pc.data_ptr(),
+                                                  ps.data_ptr(), _lib.stream()))
+                else:
+                    if self.shape[3] != 16:
+                        raise _lib.TpxError("int8 repack expects K2 == 16")
+                    ps = torch.empty(sb.value // 4, dtype=torch.float32, device=dev)
+                    _lib.check(L.tpx_repack_qint8(self.codes.data_ptr(), self.scales.data_ptr(), N, K, self.block_size,
+                                                  pc.data_ptr(), ps.data_ptr(), _lib.stream()))
+            self._packed = (pc, ps)
+        if drop_interchange:
+            self.codes = self.codes.new_empty(0)
+        return self._packed
+
+
+def _as_blocked_bf16(t):
+    _lib.require_cuda(t, "weight")
+    if t.dim() != 5:
+        raise _lib.TpxError("expected a 5-D blocked weight [K1, C1, C2, K2, C3] (BlockedParameter.block())")
+    if t.dtype != torch.bfloat16:
+        raise _lib.TpxError("Unsupported input type for quantization: expected bfloat16")
+    return t
+
+
+def remap_and_quantize_mxfp4(t):
+    """src/csrc/qtypes.cpp:783-864. `t`: blocked bf16 weight [K1, C1, C2, K2, 2] on a CUDA device."""
+    t = _as_blocked_bf16(t)
+    K1, C1, C2, K2, C3 = t.shape
+    if not ((K2 <= 32 and 32 % K2 == 0 and K1 % (32 // K2) == 0) or (K2 > 32 and K2 % 32 == 0)):
+        raise _lib.TpxError("Shape not compatible for MXFP4")
+    K1o = K1 * K2 // 32
+    codes = torch.empty((K1o, C1, C2, 32), dtype=torch.uint8, device=t.device)
+    scales = torch.empty((K1o, C1, C2 * C3 // 32, 32), dtype=torch.uint8, device=t.device)
+    with torch.cuda.device(t.device):
+        _lib.check(_lib.lib().tpx_remap_and_quantize_mxfp4(t.data_ptr(), K1, C1, C2, K2, C3, codes.data_ptr(),
+                                                           scales.data_ptr(), _lib.stream()))
+    return QTensor(codes, scales, (K1o, C1, C2, 32, C3), kPerBlockMxFP, 32)
+
+
+def remap_and_quantize_qint8(t, block_size=None):
+    """src/csrc/qtypes.cpp:866-932. `block_size` defaults to the QINT8_BLOCK_SIZE environment
+    variable (256 if unset), as in the reference (:28)."""
+    import os
+    t = _as_blocked_bf16(t)
+    if block_size is None:
+        block_size = int(os.environ.get("QINT8_BLOCK_SIZE", "256"))
+    K1, C1, C2, K2, C3 = t.shape
+    C = C1 * C2 * C3
+    used = ctypes.c_int64(0)
+    q = torch.empty(K1 * C * K2, dtype=torch.int8, device=t.device)
+    # scale count depends on the block size actually used; allocate for the smallest (64)
+    scales = torch.empty(K1 * (C // 64) * K2, dtype=torch.float32, device=t.device)
+    with torch.cuda.device(t.device):
+        _lib.check(_lib.lib().tpx_remap_and_quantize_qint8(t.data_ptr(), K1, C1, C2, K2, C3, block_size, q.data_ptr(),
+                                                           scales.data_ptr(), ctypes.byref(used), _lib.stream()))
+    B = used.value
+    q = q.view(K1, C // B, B // 4, K2, 4)
+    scales = scales[: K1 * (C // B) * K2].view(K1, C // B, 1, K2)
+    return QTensor(q, scales, (K1, C // B, B // 4, K2, 4), kPerBlockAffine, B)
+
+
+def q_per_block_scales(q):
+    return q.scales
+
+
+def q_per_block_block_size(q):
+    return q.block_size
+
+
+def q_per_block_axis(q):
+    return q.axis
+
+
+def q_per_block_pack_size(q):
+    return 2 if q.kind == W_MXFP4 else 1
+
+
+def remap_and_quantize_qint4(t):
+    """Imported by the reference's qtypes.py:19 although its C++ no longer registers it
+    (src/csrc/qtypes.cpp:1090 is commented out); kept as an explicit refusal so imports succeed."""
+    raise _lib.TpxError("remap_and_quantize_qint4 is not provided by the reference at this revision")

@@ -1,0 +1,88 @@
+"""ctypes binding of the C ABI declared in include/tpx_b200.h.
+
+There is no fallback: if the CUDA library has not been built, importing a compute entry point
+raises. Device pointers are taken from torch tensors (`data_ptr()`), the stream is torch's
+current CUDA stream."""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libtpx_b200.so")
+_lib = None
+
+c_i64, c_int, c_f32, c_vp, c_sz = ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
+
+_SIGS = {
+    "tpx_version": (c_int, []),
+    "tpx_last_error": (ctypes.c_char_p, []),
+    "tpx_sm_count": (c_int, []),
+    "tpx_debug_cvt_e2m1": (c_int, [c_vp, c_vp]),
+    "tpx_remap_and_quantize_mxfp4": (c_int, [c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "tpx_remap_and_quantize_qint8": (c_int, [c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, ctypes.POINTER(c_i64), c_vp]),
+    "tpx_dequantize_mxfp4": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp]),
+    "tpx_dequantize_qint8": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp]),
+    "tpx_packed_bytes": (c_int, [c_int, c_i64, c_i64, c_i64, ctypes.POINTER(c_sz), ctypes.POINTER(c_sz)]),
+    "tpx_repack_mxfp4": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "tpx_repack_qint8": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "tpx_qlinear_scratch_bytes": (c_sz, [c_int, c_i64, c_i64, c_i64, c_int]),
+    "tpx_qlinear": (c_int, [c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp,
+                            c_f32, c_vp, c_vp, c_sz, c_vp]),
+}
+
+
+class TpxError(RuntimeError):
+    pass
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_SO):
+            raise TpxError(
+                f"{_SO} is missing: build it with `python -m tpp_pytorch_extension_b200._build` "
+                "(there is no CPU or eager fallback)")
+        L = ctypes.CDLL(_SO)
+        for name, (res, args) in _SIGS.items():
+            if hasattr(L, name):
+                fn = getattr(L, name)
+                fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        raise TpxError(f"tpx error {rc}: {lib().tpx_last_error().decode()}")
+
+
+def ptr(t):
+    """Device pointer of a tensor, or NULL for None / empty (the reference's 'absent' tensor)."""
+    if t is None or t.numel() == 0:
+        return None
+    return t.data_ptr()
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def require_cuda(t, name):
+    if not t.is_cuda:
+        raise TpxError(f"{name} must be a CUDA tensor (this library has no CPU path)")
+    if not t.is_contiguous():
+        raise TpxError(f"{name} must be contiguous")
+
+
+_scratch = {}
+
+
+def scratch(nbytes, device):
+    """Per-device, per-stream zero-initialised scratch for split-K partial sums, grown on demand."""
+    key = (device.index, stream())
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf

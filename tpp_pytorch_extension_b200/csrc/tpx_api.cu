@@ -1,0 +1,78 @@
+// C-ABI entry points that are not tied to one kernel file: error text, device info, and the
+// dispatch of tpx_qlinear onto the kernel families.
+#include "tpx_common.cuh"
+#include <string.h>
+
+namespace tpx {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+int qlinear_stream(int kind, const uint8_t* pk_codes, const void* pk_scales, const uint8_t* pk_codes2,
+                   const void* pk_scales2, int64_t block_size, const uint16_t* x, int64_t M, int64_t N, int64_t K,
+                   const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res, float res_scale,
+                   uint16_t* y, void* scratch, size_t scratch_bytes, cudaStream_t st);
+
+__global__ void debug_cvt_e2m1_kernel(uint32_t* out) {
+  uint32_t b = threadIdx.x;
+  uint32_t r;
+  asm("{ .reg .b8 t; cvt.u8.u32 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(r) : "r"(b));
+  out[b] = r;
+}
+
+}  // namespace tpx
+
+using namespace tpx;
+
+extern "C" int tpx_version(void) { return 100; }
+extern "C" const char* tpx_last_error(void) { return g_err; }
+extern "C" int tpx_sm_count(void) { return sm_count(); }
+
+extern "C" int tpx_debug_cvt_e2m1(uint32_t* out256, void* stream) {
+  TPX_REQUIRE(out256, TPX_ERR_ARG, "debug_cvt_e2m1: null pointer");
+  debug_cvt_e2m1_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(out256);
+  TPX_LAUNCH_OK();
+  return TPX_OK;
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+extern "C" int tpx_qlinear(int kind, const uint8_t* pk_codes, const void* pk_scales, const uint8_t* pk_codes2,
+                           const void* pk_scales2, int64_t block_size, const uint16_t* x, int64_t M, int64_t N,
+                           int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
+                           float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream) {
+  TPX_REQUIRE(kind == TPX_W_MXFP4 || kind == TPX_W_INT8, TPX_ERR_ARG, "qlinear: unknown weight kind %d", kind);
+  TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear: bad shape M=%ld N=%ld K=%ld", (long)M, (long)N, (long)K);
+  if (M == 0) return TPX_OK;  // empty batch: nothing to do, as a zero-row GEMM in the reference
+  TPX_REQUIRE(pk_codes && pk_scales && x && y, TPX_ERR_ARG, "qlinear: null pointer");
+  TPX_REQUIRE((pk_codes2 == nullptr) == (pk_scales2 == nullptr), TPX_ERR_ARG, "qlinear: second weight needs both codes and scales");
+  TPX_REQUIRE(!(pk_codes2 && mul_in), TPX_ERR_ARG, "qlinear: gate/up pair and mul_in are exclusive");
+  TPX_REQUIRE(N % 16 == 0 && K % 64 == 0, TPX_ERR_ARG, "qlinear: needs N %% 16 == 0 and K %% 64 == 0 (N=%ld K=%ld)", (long)N, (long)K);
+  TPX_REQUIRE(act >= TPX_ACT_NONE && act <= TPX_ACT_RELU, TPX_ERR_ARG, "qlinear: unknown activation %d", act);
+  TPX_REQUIRE(aligned16(pk_codes) && aligned16(pk_scales) && aligned16(x) && aligned16(pk_codes2) && aligned16(pk_scales2),
+              TPX_ERR_ARG, "qlinear: weights and activations must be 16-byte aligned");
+  TPX_REQUIRE(M <= INT32_MAX / 2 && N <= INT32_MAX / 2 && K <= INT32_MAX / 2 && M * N < ((int64_t)1 << 40), TPX_ERR_ARG, "qlinear: shape too large");
+  if (kind == TPX_W_INT8)
+    TPX_REQUIRE(block_size >= 64 && block_size % 64 == 0 && K % block_size == 0, TPX_ERR_ARG,
+                "qlinear: int8 block size %ld must be a multiple of 64 dividing K=%ld", (long)block_size, (long)K);
+  return qlinear_stream(kind, pk_codes, pk_scales, pk_codes2, pk_scales2, block_size, x, M, N, K, bias, act, mul_in,
+                        res, res_scale, y, scratch, scratch_bytes, (cudaStream_t)stream);
+}

@@ -1,0 +1,64 @@
+// Shared helpers of the tpx_b200 CUDA library (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#include "../../include/tpx_b200.h"
+
+namespace tpx {
+
+// Thread-local error text behind tpx_last_error().
+void set_error(const char* fmt, ...);
+
+#define TPX_REQUIRE(cond, code, ...)      \
+  do {                                    \
+    if (!(cond)) {                        \
+      ::tpx::set_error(__VA_ARGS__);      \
+      return (code);                      \
+    }                                     \
+  } while (0)
+
+#define TPX_CUDA_OK(call)                                                                  \
+  do {                                                                                     \
+    cudaError_t e__ = (call);                                                              \
+    if (e__ != cudaSuccess) {                                                              \
+      ::tpx::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__), __FILE__, __LINE__); \
+      return TPX_ERR_CUDA;                                                                 \
+    }                                                                                      \
+  } while (0)
+
+#define TPX_LAUNCH_OK()                                                                    \
+  do {                                                                                     \
+    cudaError_t e__ = cudaGetLastError();                                                  \
+    if (e__ != cudaSuccess) {                                                              \
+      ::tpx::set_error("kernel launch failed: %s (%s:%d)", cudaGetErrorString(e__), __FILE__, __LINE__); \
+      return TPX_ERR_CUDA;                                                                 \
+    }                                                                                      \
+  } while (0)
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint16_t h) { return __uint_as_float(((uint32_t)h) << 16); }
+
+// fp32 -> bf16 bits, round to nearest even (matches at::BFloat16 and the CPU oracle)
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
+  uint32_t u = __float_as_uint(f);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  switch (act) {
+    case TPX_ACT_GELU: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    case TPX_ACT_SILU: return v / (1.0f + __expf(-v));
+    case TPX_ACT_RELU: return fmaxf(v, 0.0f);
+    default: return v;
+  }
+}
+
+int sm_count();
+
+}  // namespace tpx
