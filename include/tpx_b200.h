@@ -76,8 +76,9 @@ int tpx_dequantize_qint8(const int8_t* q, const float* scales, int64_t K1, int64
  * The reference keeps one blocked layout and, for prefill, a second copy with merged blocks
  * (wt_tensor_for_first_token, src/csrc/llm/fused_llm_infer.cpp:365-420). Here the interchange
  * tensors above are re-laid once into the streaming layout the kernels read:
- *   MXFP4 codes  [N/16][Kp/128][2][32 lanes][16 B], scales [N/16][Kp/128][16 rows][4]
- *   int8  values [N/16][K/64][2][32 lanes][16 B],  scales fp32 [N][K/B]
+ *   MXFP4 tiles  [N/16][Kp/128] of 1088 bytes: codes [2][32 lanes][16 B], then scales [16 rows][4]
+ *                (scales_bytes is 0: they ride inside the tiles; pk_scales may be NULL)
+ *   int8  values [N/16][K/64][2][32 lanes][16 B],  scales fp32 [N/16][K/B][16 rows]
  * (Kp = K rounded up to 128; the padding holds zero codes).
  * tpx_packed_bytes returns the byte sizes of the two outputs.                              */
 int tpx_packed_bytes(int kind, int64_t N, int64_t K, int64_t block_size, size_t* codes_bytes,
@@ -97,13 +98,34 @@ int tpx_repack_qint8(const int8_t* q, const float* scales, int64_t N, int64_t K,
  *     y = act(x.W^T) * (x.W2^T)
  * NULL for bias / mul_in / res / pk_codes2 means "absent" (the reference's empty tensor).
  * fp32 accumulation, one bf16 rounding at the store.
- * scratch: tpx_qlinear_scratch_bytes(...) bytes, 256-byte aligned, zero-filled once by the
- * caller before first use (the kernels leave it zeroed where it must be).                  */
-size_t tpx_qlinear_scratch_bytes(int kind, int64_t M, int64_t N, int64_t K, int dual);
+ * scratch: tpx_qlinear_scratch_bytes(...) bytes, 256-byte aligned. Its first 64 KiB (arrival counters,
+ * and an error word at byte 65532 that a kernel sets if a bounded wait inside it gave up) must be
+ * zero-filled once by the caller before first use; the kernels leave the counters zeroed. Calls that
+ * share a scratch buffer must not overlap on the device.                                    */
+size_t tpx_qlinear_scratch_bytes(int kind, int64_t M, int64_t N, int64_t K, int64_t block_size, int dual);
 int tpx_qlinear(int kind, const uint8_t* pk_codes, const void* pk_scales, const uint8_t* pk_codes2,
                 const void* pk_scales2, int64_t block_size, const uint16_t* x, int64_t M, int64_t N,
                 int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
                 float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream);
+
+/* ---------------------------------------------------------------- MXFP4 linear on the tcgen05 tensor cores
+ * Same contract as tpx_qlinear for MXFP4 weights (it replaces the same reference interfaces), with the
+ * weight in the layout the tensor-core path reads:
+ *   wq  [N][K/2]  row-major packed E2M1 codes, low nibble = even k (unpacked by TMA)
+ *   sfa [ceil(N/128)][ceil(K/128)][512]  UE8M0 scale-factor blocks: byte (r%32)*16 + (r/32)*4 + j holds the
+ *       scale of row r of the 128-row tile for the j-th 32-wide block of the 128-wide k step
+ * built by tpx_repack_mxfp4_tc from the interchange tensors of tpx_remap_and_quantize_mxfp4.
+ * Activations are split on the device into two E4M3 terms with a shared power-of-two block scale
+ * (exact for bf16 inputs within 2^-10 of their block maximum). The scratch buffer holds those terms and the
+ * partial tiles; its first 64 KiB must be zero before first use, as for tpx_qlinear.                       */
+int tpx_tc_packed_bytes(int64_t N, int64_t K, size_t* wq_bytes, size_t* sfa_bytes);
+int tpx_repack_mxfp4_tc(const uint8_t* codes, const uint8_t* scales, int64_t N, int64_t K, uint8_t* wq, uint8_t* sfa,
+                        void* stream);
+size_t tpx_qlinear_mxfp4_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int dual);
+int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, const uint8_t* wq2, const uint8_t* sfa2,
+                         const uint16_t* x, int64_t M, int64_t N, int64_t K, const uint16_t* bias, int act,
+                         const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y, void* scratch,
+                         size_t scratch_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -25,3 +25,11 @@ def make_qweight(rng, N, K, kind, dev, block=64, std=0.02):
     q = _qtype.remap_and_quantize_qint8(wb, block)
     qq, ss, bs = O.remap_and_quantize_qint8(w, block)
     return q, O.int8_dequant_plain(qq, ss, bs), (qq, ss, bs)
+
+
+def assert_no_kernel_error():
+    """The bounded waits inside the kernels report through a word in the scratch buffer."""
+    from tpp_pytorch_extension_b200 import _lib
+    torch.cuda.synchronize()
+    for buf in _lib._scratch.values():
+        assert int(buf[65532:65536].view(torch.int32).item()) == 0, "a kernel gave up on a bounded wait"

@@ -38,4 +38,4 @@ def test_argument_errors_are_reported_not_fatal():
     rc = L.tpx_qlinear(7, None, None, None, None, 32, None, 1, 16, 64, None, 0, None, None, 1.0, None, None, 0, None)
     assert rc == 1 and b"unknown weight kind" in L.tpx_last_error()
     rc = L.tpx_qlinear(1, None, None, None, None, 32, None, 0, 16, 64, None, 0, None, None, 1.0, None, None, 0, None)
-    assert rc == 0  # an empty batch is a no-op
+    assert rc == 0, L.tpx_last_error()  # an empty batch is a no-op

@@ -6,17 +6,24 @@ import pytest
 import torch
 
 from oracle import oracle as O
-from tests.gpu_util import make_qweight, to_dev_bf16, to_host_bits
+from tests.gpu_util import assert_no_kernel_error, make_qweight, to_dev_bf16, to_host_bits
 
 pytestmark = pytest.mark.gpu
 TOL = 2e-2
+
+
+@pytest.fixture(autouse=True, params=["tc", "stream"])
+def mxfp4_path(request, monkeypatch):
+    """Every case runs on both MXFP4 kernel families: the tcgen05 tensor-core kernel and the mma.sync streaming kernel."""
+    monkeypatch.setenv("TPX_MXFP4_PATH", request.param)
+    return request.param
 
 
 def run_fc(x_bits, q, dev, **kw):
     from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
     x = to_dev_bf16(x_bits, dev)
     y = F.fc_plain_act(x, q, **kw)
-    torch.cuda.synchronize()
+    assert_no_kernel_error()
     return to_host_bits(y)
 
 

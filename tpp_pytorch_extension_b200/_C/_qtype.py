@@ -29,6 +29,7 @@ class QTensor:
         self.axis = axis
         self.is_vnni = is_vnni
         self._packed = None
+        self._packed_tc = None
 
     # --- the attributes the reference's dispatch reads (src/csrc/fused_gemm.h:1517-1540)
     def qscheme(self):
@@ -93,9 +94,9 @@ class QTensor:
                 if self.kind == W_MXFP4:
                     if self.shape[2] * self.shape[4] != 64 or self.shape[3] != 32:
                         raise _lib.TpxError("MXFP4 repack expects the [N/32, K/64, 32, 32, 2] layout of remap_and_quantize_mxfp4")
-                    ps = torch.empty(sb.value, dtype=torch.uint8, device=dev)
+                    ps = torch.empty(0, dtype=torch.uint8, device=dev)  # the scales ride inside the tiles
                     _lib.check(L.tpx_repack_mxfp4(self.codes.data_ptr(), self.scales.data_ptr(), N, K, pc.data_ptr(),
-                                                  ps.data_ptr(), _lib.stream()))
+                                                  None, _lib.stream()))
                 else:
                     if self.shape[3] != 16:
                         raise _lib.TpxError("int8 repack expects K2 == 16")
@@ -106,6 +107,28 @@ class QTensor:
         if drop_interchange:
             self.codes = self.codes.new_empty(0)
         return self._packed
+
+
+def _packed_tc(self):
+    """(wq, sfa) in the tensor-core layout (MXFP4 only); built once and cached."""
+    if self._packed_tc is None:
+        if self.kind != W_MXFP4 or self.shape[2] * self.shape[4] != 64 or self.shape[3] != 32:
+            raise _lib.TpxError("the tensor-core path takes MXFP4 weights in the [N/32, K/64, 32, 32, 2] layout")
+        L = _lib.lib()
+        N, K = self.out_features, self.in_features
+        wb, sb = ctypes.c_size_t(), ctypes.c_size_t()
+        _lib.check(L.tpx_tc_packed_bytes(N, K, ctypes.byref(wb), ctypes.byref(sb)))
+        dev = self.codes.device
+        wq = torch.empty(wb.value, dtype=torch.uint8, device=dev)
+        sfa = torch.empty(sb.value, dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(L.tpx_repack_mxfp4_tc(self.codes.data_ptr(), self.scales.data_ptr(), N, K, wq.data_ptr(),
+                                             sfa.data_ptr(), _lib.stream()))
+        self._packed_tc = (wq, sfa)
+    return self._packed_tc
+
+
+QTensor.packed_tc = _packed_tc
 
 
 def _as_blocked_bf16(t):

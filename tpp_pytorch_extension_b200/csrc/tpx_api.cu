@@ -26,10 +26,11 @@ int sm_count() {
   return cached[dev];
 }
 
-int qlinear_stream(int kind, const uint8_t* pk_codes, const void* pk_scales, const uint8_t* pk_codes2,
-                   const void* pk_scales2, int64_t block_size, const uint16_t* x, int64_t M, int64_t N, int64_t K,
-                   const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res, float res_scale,
-                   uint16_t* y, void* scratch, size_t scratch_bytes, cudaStream_t st);
+size_t qlinear_stream_scratch_bytes(int kind, int64_t M, int64_t N, int64_t K, int64_t block_size, bool dual);
+int qlinear_stream_launch(int kind, const uint8_t* pk_codes, const void* pk_scales, const uint8_t* pk_codes2,
+                          const void* pk_scales2, int64_t block_size, const uint16_t* x, int64_t M, int64_t N, int64_t K,
+                          const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res, float res_scale,
+                          uint16_t* y, void* scratch, size_t scratch_bytes, cudaStream_t st);
 
 __global__ void debug_cvt_e2m1_kernel(uint32_t* out) {
   uint32_t b = threadIdx.x;
@@ -55,24 +56,39 @@ extern "C" int tpx_debug_cvt_e2m1(uint32_t* out256, void* stream) {
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-extern "C" int tpx_qlinear(int kind, const uint8_t* pk_codes, const void* pk_scales, const uint8_t* pk_codes2,
-                           const void* pk_scales2, int64_t block_size, const uint16_t* x, int64_t M, int64_t N,
-                           int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
-                           float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream) {
+static int check_qlinear_shape(int kind, int64_t M, int64_t N, int64_t K, int64_t block_size) {
   TPX_REQUIRE(kind == TPX_W_MXFP4 || kind == TPX_W_INT8, TPX_ERR_ARG, "qlinear: unknown weight kind %d", kind);
   TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear: bad shape M=%ld N=%ld K=%ld", (long)M, (long)N, (long)K);
-  if (M == 0) return TPX_OK;  // empty batch: nothing to do, as a zero-row GEMM in the reference
-  TPX_REQUIRE(pk_codes && pk_scales && x && y, TPX_ERR_ARG, "qlinear: null pointer");
-  TPX_REQUIRE((pk_codes2 == nullptr) == (pk_scales2 == nullptr), TPX_ERR_ARG, "qlinear: second weight needs both codes and scales");
-  TPX_REQUIRE(!(pk_codes2 && mul_in), TPX_ERR_ARG, "qlinear: gate/up pair and mul_in are exclusive");
   TPX_REQUIRE(N % 16 == 0 && K % 64 == 0, TPX_ERR_ARG, "qlinear: needs N %% 16 == 0 and K %% 64 == 0 (N=%ld K=%ld)", (long)N, (long)K);
-  TPX_REQUIRE(act >= TPX_ACT_NONE && act <= TPX_ACT_RELU, TPX_ERR_ARG, "qlinear: unknown activation %d", act);
-  TPX_REQUIRE(aligned16(pk_codes) && aligned16(pk_scales) && aligned16(x) && aligned16(pk_codes2) && aligned16(pk_scales2),
-              TPX_ERR_ARG, "qlinear: weights and activations must be 16-byte aligned");
   TPX_REQUIRE(M <= INT32_MAX / 2 && N <= INT32_MAX / 2 && K <= INT32_MAX / 2 && M * N < ((int64_t)1 << 40), TPX_ERR_ARG, "qlinear: shape too large");
   if (kind == TPX_W_INT8)
     TPX_REQUIRE(block_size >= 64 && block_size % 64 == 0 && K % block_size == 0, TPX_ERR_ARG,
                 "qlinear: int8 block size %ld must be a multiple of 64 dividing K=%ld", (long)block_size, (long)K);
-  return qlinear_stream(kind, pk_codes, pk_scales, pk_codes2, pk_scales2, block_size, x, M, N, K, bias, act, mul_in,
+  return TPX_OK;
+}
+
+extern "C" size_t tpx_qlinear_scratch_bytes(int kind, int64_t M, int64_t N, int64_t K, int64_t block_size, int dual) {
+  if (check_qlinear_shape(kind, M, N, K, block_size) != TPX_OK) return 0;
+  if (M == 0) return 0;
+  return qlinear_stream_scratch_bytes(kind, M, N, K, block_size, dual != 0);
+}
+
+extern "C" int tpx_qlinear(int kind, const uint8_t* pk_codes, const void* pk_scales, const uint8_t* pk_codes2,
+                           const void* pk_scales2, int64_t block_size, const uint16_t* x, int64_t M, int64_t N,
+                           int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
+                           float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream) {
+  int rc = check_qlinear_shape(kind, M, N, K, block_size);
+  if (rc != TPX_OK) return rc;
+  if (M == 0) return TPX_OK;  // empty batch: nothing to do, as a zero-row GEMM in the reference
+  TPX_REQUIRE(pk_codes && x && y, TPX_ERR_ARG, "qlinear: null pointer");
+  if (kind == TPX_W_INT8) {  // MXFP4 tiles carry their scales; int8 scales are a separate array
+    TPX_REQUIRE(pk_scales, TPX_ERR_ARG, "qlinear: int8 needs the scale array");
+    TPX_REQUIRE((pk_codes2 == nullptr) == (pk_scales2 == nullptr), TPX_ERR_ARG, "qlinear: second weight needs both codes and scales");
+  }
+  TPX_REQUIRE(!(pk_codes2 && mul_in), TPX_ERR_ARG, "qlinear: gate/up pair and mul_in are exclusive");
+  TPX_REQUIRE(act >= TPX_ACT_NONE && act <= TPX_ACT_RELU, TPX_ERR_ARG, "qlinear: unknown activation %d", act);
+  TPX_REQUIRE(aligned16(pk_codes) && aligned16(pk_scales) && aligned16(x) && aligned16(pk_codes2) && aligned16(pk_scales2),
+              TPX_ERR_ARG, "qlinear: weights and activations must be 16-byte aligned");
+  return qlinear_stream_launch(kind, pk_codes, pk_scales, pk_codes2, pk_scales2, block_size, x, M, N, K, bias, act, mul_in,
                         res, res_scale, y, scratch, scratch_bytes, (cudaStream_t)stream);
 }

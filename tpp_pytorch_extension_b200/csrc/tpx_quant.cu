@@ -168,11 +168,11 @@ __global__ void dequantize_qint8_kernel(const int8_t* __restrict__ q, const floa
 
 // ---------------------------------------------------------------- repack into the streaming layout
 // MXFP4: one thread builds one 32-bit word = 8 codes of one row for one 32-wide scale block.
+// Tile (nt, kt) occupies 1088 bytes at (nt*KT + kt)*1088: codes [h][lane][16 B], then scales [16 rows][4].
 //   word (nt, kt, h, lane=4g+t, b): row n = 16nt + g + 8h; nibble j holds k = 128kt + 32b + 16(j/4) + 4t + (j%4)
 // Source byte (k1,c1,r,k2) of the reference tensor holds W[32k1+k2][64c1+2r+{0,1}], low nibble first.
 __global__ void repack_mxfp4_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
-                                    int64_t N, int64_t K, int64_t KT, uint32_t* __restrict__ pk,
-                                    uint8_t* __restrict__ pks) {
+                                    int64_t N, int64_t K, int64_t KT, uint32_t* __restrict__ pk) {
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t total = (N / 16) * KT * 256;
   if (idx >= total) return;
@@ -195,13 +195,13 @@ __global__ void repack_mxfp4_kernel(const uint8_t* __restrict__ codes, const uin
     }
     word |= c << (4 * j);
   }
-  pk[idx] = word;
-  // scales: [nt][kt][row 0..15][b]; threads with h==0 and t==0 write rows g and g+8
+  // a tile is 1088 bytes: 1024 of codes, then the 64 scale bytes [row 0..15][b]
+  pk[tile * 272 + (idx & 255)] = word;
   if (t == 0) {
     int64_t kb = kt * 4 + b;  // 32-wide block index along K
     uint8_t s = 0;
     if (kb * 32 < K) s = scales[(((n / 32) * C1 + kb / 2) * 2 + (kb & 1)) * 32 + (n % 32)];
-    pks[(tile * 16 + g + 8 * h) * 4 + b] = s;
+    reinterpret_cast<uint8_t*>(pk)[tile * 1088 + 1024 + (g + 8 * h) * 4 + b] = s;
   }
 }
 
@@ -300,8 +300,8 @@ extern "C" int tpx_packed_bytes(int kind, int64_t N, int64_t K, int64_t block_si
   if (kind == TPX_W_MXFP4) {
     TPX_REQUIRE(K % 64 == 0, TPX_ERR_ARG, "packed_bytes: MXFP4 needs K %% 64 == 0");
     int64_t KT = (K + 127) / 128;
-    if (codes_bytes) *codes_bytes = (size_t)(N / 16) * KT * 1024;
-    if (scales_bytes) *scales_bytes = (size_t)(N / 16) * KT * 64;
+    if (codes_bytes) *codes_bytes = (size_t)(N / 16) * KT * 1088;  // the scales ride inside the tiles
+    if (scales_bytes) *scales_bytes = 0;
     return TPX_OK;
   }
   if (kind == TPX_W_INT8) {
@@ -317,12 +317,13 @@ extern "C" int tpx_packed_bytes(int kind, int64_t N, int64_t K, int64_t block_si
 
 extern "C" int tpx_repack_mxfp4(const uint8_t* codes, const uint8_t* scales, int64_t N, int64_t K, uint8_t* pk_codes,
                                 uint8_t* pk_scales, void* stream) {
-  TPX_REQUIRE(codes && scales && pk_codes && pk_scales, TPX_ERR_ARG, "repack_mxfp4: null pointer");
+  (void)pk_scales;
+  TPX_REQUIRE(codes && scales && pk_codes, TPX_ERR_ARG, "repack_mxfp4: null pointer");
   TPX_REQUIRE(N % 32 == 0 && K % 64 == 0, TPX_ERR_ARG, "repack_mxfp4: needs N %% 32 == 0 and K %% 64 == 0 (N=%ld K=%ld)", (long)N, (long)K);
   int64_t KT = (K + 127) / 128;
   int64_t total = (N / 16) * KT * 256;
   repack_mxfp4_kernel<<<blocks_for(total, 256), 256, 0, (cudaStream_t)stream>>>(
-      codes, scales, N, K, KT, reinterpret_cast<uint32_t*>(pk_codes), pk_scales);
+      codes, scales, N, K, KT, reinterpret_cast<uint32_t*>(pk_codes));
   TPX_LAUNCH_OK();
   return TPX_OK;
 }
