@@ -205,10 +205,10 @@ def run_ours(args):
                 w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16).to(dev)
             else:
                 w = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
-            q = _qtype.remap_and_quantize_mxfp4(block(w))
-            q.packed(drop_interchange=True)
-            ws.append(q)
+            ws.append(_qtype.remap_and_quantize_mxfp4(block(w)))
             del w
+        ws[0].prepare(drop_interchange=True, pair_with=ws[1])
+        ws[2].prepare(drop_interchange=True)
         sets.append(ws)
     xs_host = {M: torch.randn(M, D_MODEL, generator=g).to(torch.bfloat16).pin_memory() for M in SWEEP}
     xs = {M: xs_host[M].to(dev) for M in SWEEP}

@@ -110,22 +110,24 @@ int tpx_qlinear(int kind, const uint8_t* pk_codes, const void* pk_scales, const 
 
 /* ---------------------------------------------------------------- MXFP4 linear on the tcgen05 tensor cores
  * Same contract as tpx_qlinear for MXFP4 weights (it replaces the same reference interfaces), with the
- * weight in the layout the tensor-core path reads:
- *   wq  [N][K/2]  row-major packed E2M1 codes, low nibble = even k (unpacked by TMA)
- *   sfa [ceil(N/128)][ceil(K/128)][512]  UE8M0 scale-factor blocks: byte (r%32)*16 + (r/32)*4 + j holds the
- *       scale of row r of the 128-row tile for the j-th 32-wide block of the 128-wide k step
- * built by tpx_repack_mxfp4_tc from the interchange tensors of tpx_remap_and_quantize_mxfp4.
+ * weight in the layout the tensor-core path reads (TN = ceil(N/128); KS = ceil(K/128) rounded up to a
+ * multiple of 4 for one weight, of 2 for a gate/up pair; padding holds zero codes):
+ *   one weight : wq [TN][KS][128 rows][64 bytes]      sfa [TN][KS][512]
+ *   gate/up    : wq [TN][KS][2][128 rows][64 bytes]   sfa [TN][KS][2][512]
+ * wq holds packed E2M1 codes, low nibble = even k, unpacked by TMA; byte (r%32)*16 + (r/32)*4 + j of a
+ * 512-byte scale block is the UE8M0 scale of row r of the tile for the j-th 32-wide block of the k step.
+ * Both are built by tpx_repack_mxfp4_tc from the interchange tensors of tpx_remap_and_quantize_mxfp4
+ * (codes2/scales2 NULL = one weight). With pair != 0 the linear computes y = act(x.Wg^T) * (x.Wu^T).
  * Activations are split on the device into two E4M3 terms with a shared power-of-two block scale
  * (exact for bf16 inputs within 2^-10 of their block maximum). The scratch buffer holds those terms and the
  * partial tiles; its first 64 KiB must be zero before first use, as for tpx_qlinear.                       */
-int tpx_tc_packed_bytes(int64_t N, int64_t K, size_t* wq_bytes, size_t* sfa_bytes);
-int tpx_repack_mxfp4_tc(const uint8_t* codes, const uint8_t* scales, int64_t N, int64_t K, uint8_t* wq, uint8_t* sfa,
-                        void* stream);
-size_t tpx_qlinear_mxfp4_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int dual);
-int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, const uint8_t* wq2, const uint8_t* sfa2,
-                         const uint16_t* x, int64_t M, int64_t N, int64_t K, const uint16_t* bias, int act,
-                         const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y, void* scratch,
-                         size_t scratch_bytes, void* stream);
+int tpx_tc_packed_bytes(int64_t N, int64_t K, int pair, size_t* wq_bytes, size_t* sfa_bytes);
+int tpx_repack_mxfp4_tc(const uint8_t* codes, const uint8_t* scales, const uint8_t* codes2, const uint8_t* scales2,
+                        int64_t N, int64_t K, uint8_t* wq, uint8_t* sfa, void* stream);
+size_t tpx_qlinear_mxfp4_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int pair);
+int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M, int64_t N,
+                         int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
+                         float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream);
 
 #ifdef __cplusplus
 }

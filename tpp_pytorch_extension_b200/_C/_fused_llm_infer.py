@@ -38,14 +38,13 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale):
     if w.kind == 1 and mxfp4_path() == "tc":
         if w2 is not None and (w2.out_features, w2.in_features, w2.kind) != (N, K, w.kind):
             raise _lib.TpxError("gate/up weights must have the same shape and quantization")
-        wq, sfa = w.packed_tc()
-        wq2, sfa2 = w2.packed_tc() if w2 is not None else (None, None)
-        key = ("tc", min(M, 4096), M, N, K, w2 is not None)
+        wq, sfa = w.packed_tc(w2)
+        key = ("tc", M, N, K, w2 is not None)
         nb = _SCRATCH_BYTES.get(key)
         if nb is None:
             nb = _SCRATCH_BYTES[key] = L.tpx_qlinear_mxfp4_tc_scratch_bytes(M, N, K, int(w2 is not None))
         sc = _lib.scratch(nb, x.device)
-        rc = L.tpx_qlinear_mxfp4_tc(wq.data_ptr(), sfa.data_ptr(), _lib.ptr(wq2), _lib.ptr(sfa2), x.data_ptr(), M, N, K,
+        rc = L.tpx_qlinear_mxfp4_tc(wq.data_ptr(), sfa.data_ptr(), int(w2 is not None), x.data_ptr(), M, N, K,
                                     _lib.ptr(bias), ACT[act], _lib.ptr(mul_in), _lib.ptr(res), float(res_scale),
                                     y.data_ptr(), sc.data_ptr(), sc.numel(), _lib.stream())
         if rc:

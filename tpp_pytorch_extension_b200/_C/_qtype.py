@@ -109,26 +109,62 @@ class QTensor:
         return self._packed
 
 
-def _packed_tc(self):
-    """(wq, sfa) in the tensor-core layout (MXFP4 only); built once and cached."""
-    if self._packed_tc is None:
-        if self.kind != W_MXFP4 or self.shape[2] * self.shape[4] != 64 or self.shape[3] != 32:
-            raise _lib.TpxError("the tensor-core path takes MXFP4 weights in the [N/32, K/64, 32, 32, 2] layout")
-        L = _lib.lib()
-        N, K = self.out_features, self.in_features
-        wb, sb = ctypes.c_size_t(), ctypes.c_size_t()
-        _lib.check(L.tpx_tc_packed_bytes(N, K, ctypes.byref(wb), ctypes.byref(sb)))
-        dev = self.codes.device
-        wq = torch.empty(wb.value, dtype=torch.uint8, device=dev)
-        sfa = torch.empty(sb.value, dtype=torch.uint8, device=dev)
-        with torch.cuda.device(dev):
-            _lib.check(L.tpx_repack_mxfp4_tc(self.codes.data_ptr(), self.scales.data_ptr(), N, K, wq.data_ptr(),
-                                             sfa.data_ptr(), _lib.stream()))
+def _packed_tc(self, other=None):
+    """(wq, sfa) in the tensor-core layout (MXFP4 only), built once and cached. With `other` (the up
+    projection of a SwiGLU pair, `self` being the gate) the two weights are packed tile by tile side by
+    side, which lets the kernel fetch a gate/up pair of tiles with one copy request."""
+    if self.kind != W_MXFP4 or self.shape[2] * self.shape[4] != 64 or self.shape[3] != 32:
+        raise _lib.TpxError("the tensor-core path takes MXFP4 weights in the [N/32, K/64, 32, 32, 2] layout")
+    if other is None:
+        if self._packed_tc is not None:
+            return self._packed_tc
+    else:
+        hit = getattr(self, "_pair_tc", None)
+        if hit is not None and hit[0] is other:
+            return hit[1]
+    if self.codes.numel() == 0 or (other is not None and other.codes.numel() == 0):
+        raise _lib.TpxError("the interchange tensors of this weight were dropped before it was packed for this use")
+    L = _lib.lib()
+    N, K = self.out_features, self.in_features
+    wb, sb = ctypes.c_size_t(), ctypes.c_size_t()
+    _lib.check(L.tpx_tc_packed_bytes(N, K, int(other is not None), ctypes.byref(wb), ctypes.byref(sb)))
+    dev = self.codes.device
+    wq = torch.empty(wb.value, dtype=torch.uint8, device=dev)
+    sfa = torch.empty(sb.value, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(L.tpx_repack_mxfp4_tc(self.codes.data_ptr(), self.scales.data_ptr(),
+                                         other.codes.data_ptr() if other is not None else None,
+                                         other.scales.data_ptr() if other is not None else None,
+                                         N, K, wq.data_ptr(), sfa.data_ptr(), _lib.stream()))
+    if other is None:
         self._packed_tc = (wq, sfa)
-    return self._packed_tc
+    else:
+        self._pair_tc = (other, (wq, sfa))
+    return (wq, sfa)
 
 
 QTensor.packed_tc = _packed_tc
+
+
+def _prepare(self, drop_interchange=False, pair_with=None):
+    """Build the device layout of the kernel family in use now (`pair_with`: this weight is the gate of a
+    gate/up pair and is only used that way); optionally free the interchange copy (dequantize() and the
+    other layouts are then no longer available)."""
+    from ._fused_llm_infer import mxfp4_path
+    if self.kind == W_MXFP4 and mxfp4_path() == "tc":
+        self.packed_tc(pair_with)
+    else:
+        self.packed()
+        if pair_with is not None:
+            pair_with.packed()
+    if drop_interchange:
+        self.codes = self.codes.new_empty(0)
+        if pair_with is not None:
+            pair_with.codes = pair_with.codes.new_empty(0)
+    return self
+
+
+QTensor.prepare = _prepare
 
 
 def _as_blocked_bf16(t):

@@ -27,11 +27,12 @@ _SIGS = {
     "tpx_repack_mxfp4": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "tpx_repack_qint8": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "tpx_qlinear_scratch_bytes": (c_sz, [c_int, c_i64, c_i64, c_i64, c_i64, c_int]),
-    "tpx_tc_packed_bytes": (c_int, [c_i64, c_i64, ctypes.POINTER(c_sz), ctypes.POINTER(c_sz)]),
-    "tpx_repack_mxfp4_tc": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "tpx_tc_packed_bytes": (c_int, [c_i64, c_i64, c_int, ctypes.POINTER(c_sz), ctypes.POINTER(c_sz)]),
+    "tpx_repack_mxfp4_tc": (c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "tpx_qlinear_mxfp4_tc_scratch_bytes": (c_sz, [c_i64, c_i64, c_i64, c_int]),
-    "tpx_qlinear_mxfp4_tc": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp, c_f32, c_vp,
+    "tpx_qlinear_mxfp4_tc": (c_int, [c_vp, c_vp, c_int, c_vp, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp, c_f32, c_vp,
                                      c_vp, c_sz, c_vp]),
+    "tpx_debug_tc_timeline": (None, [c_vp]),
     "tpx_qlinear": (c_int, [c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp,
                             c_f32, c_vp, c_vp, c_sz, c_vp]),
 }

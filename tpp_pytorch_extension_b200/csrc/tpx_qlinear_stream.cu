@@ -211,25 +211,40 @@ __device__ __forceinline__ void flush_rowtile(const StreamParams& p, int nt, int
   prev = __shfl_sync(0xffffffffu, prev, 0);
   if (prev != expected - 1) return;
   __threadfence();
+  float v[NT][4], v2[NT][4];
 #pragma unroll
   for (int j = 0; j < NT; j++)
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-      int tok = 8 * j + 2 * t + (i & 1), row = nt * 16 + g + 8 * (i >> 1);
-      if (tok >= p.mcount) continue;
-      float v = 0.0f, v2 = 0.0f;
-      for (int s = 0; s < p.ksplit; s++) {  // fixed order: slices, then contributors within a slice
-        int Ls = min(p.kt_per_split, p.KT - s * p.kt_per_split);
-        long long Us = (long long)(p.N / 16) * Ls;
-        int cnt = (int)(owner_of((long long)(nt + 1) * Ls - 1, Us, W) - owner_of((long long)nt * Ls, Us, W) + 1);
-        for (int c = 0; c < cnt; c++) {
-          size_t base = ((size_t)((s * p.max_slots + c) * 2)) * plane + (size_t)tok * p.N + row;
-          v += __ldcg(p.partial + base);
-          if (DUAL) v2 += __ldcg(p.partial + base + plane);
+    for (int i = 0; i < 4; i++) v[j][i] = v2[j][i] = 0.0f;
+  for (int s = 0; s < p.ksplit; s++) {  // fixed order: slices, then contributors within a slice
+    int Ls = min(p.kt_per_split, p.KT - s * p.kt_per_split);
+    long long Us = (long long)(p.N / 16) * Ls;
+    int cnt = (int)(owner_of((long long)(nt + 1) * Ls - 1, Us, W) - owner_of((long long)nt * Ls, Us, W) + 1);
+    for (int c = 0; c < cnt; c++) {
+      const float* base = p.partial + ((size_t)((s * p.max_slots + c) * 2)) * plane;
+      float a[NT][4], b[NT][4];
+#pragma unroll
+      for (int j = 0; j < NT; j++)  // all of this contributor's loads are issued before any is used
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          int tok = 8 * j + 2 * t + (i & 1), row = nt * 16 + g + 8 * (i >> 1);
+          a[j][i] = tok < p.mcount ? __ldcg(base + (size_t)tok * p.N + row) : 0.0f;
+          b[j][i] = (DUAL && tok < p.mcount) ? __ldcg(base + plane + (size_t)tok * p.N + row) : 0.0f;
         }
-      }
-      finish(p, tok, row, v, v2, DUAL);
+#pragma unroll
+      for (int j = 0; j < NT; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          v[j][i] += a[j][i];
+          v2[j][i] += b[j][i];
+        }
     }
+  }
+#pragma unroll
+  for (int j = 0; j < NT; j++)
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+      finish(p, 8 * j + 2 * t + (i & 1), nt * 16 + g + 8 * (i >> 1), v[j][i], v2[j][i], DUAL);
   if (lane == 0) p.counters[nt] = 0;  // leave the counter ready for the next launch
 }
 

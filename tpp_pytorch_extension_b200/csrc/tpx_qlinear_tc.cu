@@ -9,17 +9,26 @@
 // so each activation is split beforehand into two E4M3 terms that share one power-of-two scale per
 // 32-wide block: x = (hi + lo) * 2^e. A bf16 value has 8 significant bits, hi and lo carry 4 each, so the
 // split is exact for every element within 2^-10 of its block maximum (smaller ones keep an absolute error
-// below 2^-18 of the block maximum). Two MMAs (hi, lo) accumulate into the same fp32 tile in tensor memory.
+// below 2^-18 of the block maximum). The two terms sit side by side as 2*TOK columns of one MMA, so the
+// weight tile is read from shared memory once; the epilogue adds the two halves of the fp32 tile.
 //
 //   rows of W (output features) = M of the MMA (128 per tile), tokens = N (TOK per tile), K step 128
 //   warp 0   : TMA producer (W tiles, activation terms, scale-factor blocks) into a ring of stages
-//   warp 1   : allocates tensor memory, issues the MMAs, commits stages back to the producer
-//   warps 2-5: copy the scale factors of each stage into tensor memory, then run the epilogue
+//   warp 1   : allocates tensor memory; per stage copies the scale-factor blocks from shared to tensor
+//              memory (tcgen05.cp, which runs in order with the MMAs of the same thread), issues the
+//              MMAs and commits the stage back to the producer
+//   warps 2-5: epilogue (tensor memory -> registers -> bias / activation / gate / residual -> y)
 //
-// Work is the flat list of (output tile, k step) units cut into equal contiguous ranges, one CTA per SM:
+// The TMA unit of an SM retires roughly one copy request per 0.12 us whatever its size, so a stage is
+// fetched with few, large requests: 16 KiB of packed weight per request (a gate/up pair of tiles, or two
+// k steps of one weight), both activation terms of all k steps of the unit in one request, and one request
+// each for the weight and activation scale-factor blocks.
+//
+// Work is the flat list of (output tile, k unit) units cut into equal contiguous ranges, one CTA per SM:
 // every SM streams the same number of weight bytes. A tile cut between CTAs is completed through fp32
 // partial tiles in scratch (one slot per contributor, summed in a fixed order by the last to arrive).
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "tpx_common.cuh"
 #include <cuda_fp8.h>
@@ -43,10 +52,20 @@ struct TcParams {
   unsigned* counters;
   unsigned* err;
   int M, N, K;
-  int KS;               // k steps of 128
+  int KS;               // k units (of UKS k steps of 128) per tile
   int TN, TM;           // output tiles along features / tokens
   int act;
+  unsigned long long* tl;  // optional per-CTA timeline (8 globaltimer stamps each), null in normal use
+  int dbg;              // debug knobs for timing experiments: 1 = skip MMAs, 2 = skip weight copies
 };
+
+__device__ __forceinline__ void tc_stamp(const TcParams& p, int slot) {
+  if (p.tl) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.tl[(size_t)blockIdx.x * 8 + slot] = t;
+  }
+}
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -98,6 +117,14 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
       : "memory");
 }
+// 32 rows x 16 bytes, rows 16 bytes apart, no swizzle: 8-row core matrices 128 bytes apart.
+__device__ __forceinline__ uint64_t tc_sf_desc(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(128 >> 4) << 32) | (1ull << 46);
+}
+// shared -> tensor memory: 32 lanes x 128 bits, replicated to the four 32-lane quarters
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
 __device__ __forceinline__ void tc_st_x4(uint32_t taddr, uint4 v) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v.x), "r"(v.y), "r"(v.z),
                "r"(v.w)
@@ -118,12 +145,15 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
 }
 
 // ---------------------------------------------------------------- activation split
-// x[M][K] bf16 -> hi, lo [Mpad][Kp] E4M3 and the UE8M0 scale blocks, one thread per (token, 32-wide block).
-// Scale-factor block of (token tile tm, k step ks): byte (r%32)*16 + (r/32)*4 + j for row r of the tile and
-// the j-th 32-wide block of the step. Padding rows and padding columns get zeros with scale 2^0.
-__global__ void split_activations_kernel(const uint16_t* __restrict__ x, int M, int K, int Mpad, int Kp, int TOK,
-                                         uint8_t* __restrict__ hi, uint8_t* __restrict__ lo, uint8_t* __restrict__ sfb) {
-  const int nb = Kp / 32;
+// x[M][K] bf16 -> two E4M3 terms and the UE8M0 scale blocks, one thread per (token, 32-wide block), written
+// in the order the GEMM fetches them:
+//   terms [TM][KU][UKS][2 terms][TOK rows][128 bytes]     (one k step of one term = a TOK x 128 operand tile)
+//   sfb   [TM][KU][UKS][ceil(2*TOK/128)][512]   scale blocks over the 2*TOK MMA columns (hi columns, then lo
+//         columns with the same scales): byte (c%32)*16 + ((c%128)/32)*4 + j of block c/128 for column c
+// Padding rows and padding columns get zeros with scale 2^0.
+__global__ void split_activations_kernel(const uint16_t* __restrict__ x, int M, int K, int Mpad, int KS, int TOK, int UKS,
+                                         uint8_t* __restrict__ terms, uint8_t* __restrict__ sfb) {
+  const int nb = KS * 4;
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)Mpad * nb) return;
   const int kb = (int)(idx % nb);
@@ -171,59 +201,88 @@ __global__ void split_activations_kernel(const uint16_t* __restrict__ x, int M, 
     ph[i] = h4;
     pl[i] = l4;
   }
-  uint4* dh = reinterpret_cast<uint4*>(hi + (size_t)tok * Kp + kb * 32);
-  uint4* dl = reinterpret_cast<uint4*>(lo + (size_t)tok * Kp + kb * 32);
+  const int tm = tok / TOK, r = tok % TOK, ks = kb / 4, j = kb % 4;
+  const int KU = KS / UKS, ku = ks / UKS, kk = ks % UKS;
+  const size_t step = ((size_t)tm * KU + ku) * UKS + kk;  // k step in fetch order
+  uint4* dh = reinterpret_cast<uint4*>(terms + ((step * 2 + 0) * TOK + r) * 128 + j * 32);
+  uint4* dl = reinterpret_cast<uint4*>(terms + ((step * 2 + 1) * TOK + r) * 128 + j * 32);
   dh[0] = make_uint4(ph[0], ph[1], ph[2], ph[3]);
   dh[1] = make_uint4(ph[4], ph[5], ph[6], ph[7]);
   dl[0] = make_uint4(pl[0], pl[1], pl[2], pl[3]);
   dl[1] = make_uint4(pl[4], pl[5], pl[6], pl[7]);
-  const int tm = tok / TOK, r = tok % TOK, ks = kb / 4, j = kb % 4;
-  sfb[((size_t)tm * (Kp / 128) + ks) * 512 + (r % 32) * 16 + (r / 32) * 4 + j] = (uint8_t)(e + 127);
+  // the hi columns are MMA columns r, the lo columns TOK + r: both carry this scale
+  const int per = (2 * TOK + 127) / 128;
+  uint8_t* blk = sfb + step * per * 512;
+  const int r2 = TOK + r;
+  blk[(r / 128) * 512 + (r % 32) * 16 + ((r % 128) / 32) * 4 + j] = (uint8_t)(e + 127);
+  blk[(r2 / 128) * 512 + (r2 % 32) * 16 + ((r2 % 128) / 32) * 4 + j] = (uint8_t)(e + 127);
 }
 
 // ---------------------------------------------------------------- repack for the tensor-core path
-// Interchange tensors of remap_and_quantize_mxfp4 -> row-major packed codes wq[N][K/2] (low nibble = even k)
-// and scale-factor blocks sfa[ceil(N/128)][KS][512]. One thread per output byte of wq.
-__global__ void repack_mxfp4_tc_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales, int64_t N,
-                                       int64_t K, uint8_t* __restrict__ wq, uint8_t* __restrict__ sfa) {
+// Interchange tensors of remap_and_quantize_mxfp4 -> tiled packed codes and scale-factor blocks.
+//   one weight : wq [TN][KS][128 rows][64 bytes]          sfa [TN][KS][512]          KS padded to a multiple of 4
+//   gate/up    : wq [TN][KS][2][128 rows][64 bytes]       sfa [TN][KS][2][512]       KS padded to a multiple of 2
+// (low nibble = even k; rows beyond N and columns beyond K hold zero codes and zero scale bytes). A copy
+// request of 256 such 64-byte rows is 16 KiB of consecutive addresses. One thread per output byte of wq.
+__global__ void repack_mxfp4_tc_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
+                                       const uint8_t* __restrict__ codes2, const uint8_t* __restrict__ scales2, int64_t N,
+                                       int64_t K, int64_t KS, uint8_t* __restrict__ wq, uint8_t* __restrict__ sfa) {
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t C1 = K / 64;
-  if (idx < N * (K / 2)) {
-    int64_t n = idx / (K / 2), k = (idx % (K / 2)) * 2;
-    // source byte (k1,c1,r,k2) = W[32k1+k2][64c1+2r+{0,1}]: already the (k, k+1) pair
-    wq[idx] = codes[(((n / 32) * C1 + k / 64) * 32 + (k % 64) / 2) * 32 + (n % 32)];
-  }
-  const int64_t KS = (K + 127) / 128;
   const int64_t TN = (N + 127) / 128;
-  if (idx < TN * KS * 512) {
-    int64_t blk = idx / 512;
+  const int NW = codes2 ? 2 : 1;
+  if (idx < TN * KS * NW * 8192) {
+    int64_t tile = idx / 8192;  // (tn*KS + ks)*NW + d
+    int d = (int)(tile % NW);
+    int64_t tk = tile / NW;
+    int r = (int)((idx % 8192) / 64), kb = (int)(idx % 64);
+    int64_t n = (tk / KS) * 128 + r, k = (tk % KS) * 128 + 2 * kb;
+    const uint8_t* src = d ? codes2 : codes;
+    // source byte (k1,c1,r,k2) = W[32k1+k2][64c1+2r+{0,1}]: already the (k, k+1) pair
+    wq[idx] = (n < N && k < K) ? src[(((n / 32) * C1 + k / 64) * 32 + (k % 64) / 2) * 32 + (n % 32)] : (uint8_t)0;
+  }
+  if (idx < TN * KS * NW * 512) {
+    int64_t blk = idx / 512;  // (tn*KS + ks)*NW + d
+    int d = (int)(blk % NW);
+    int64_t tk = blk / NW;
     int b = (int)(idx % 512);
     int r = (b / 16) + 32 * ((b % 16) / 4), j = b % 4;
-    int64_t n = (blk / KS) * 128 + r, kb = (blk % KS) * 4 + j;
-    uint8_t s = 0;
-    if (n < N && kb * 32 < K) s = scales[(((n / 32) * C1 + kb / 2) * 2 + (kb & 1)) * 32 + (n % 32)];
-    sfa[idx] = s;
+    int64_t n = (tk / KS) * 128 + r, kbk = (tk % KS) * 4 + j;
+    const uint8_t* src = d ? scales2 : scales;
+    uint8_t sv = 0;
+    if (n < N && kbk * 32 < K) sv = src[(((n / 32) * C1 + kbk / 2) * 2 + (kbk & 1)) * 32 + (n % 32)];
+    sfa[idx] = sv;
   }
 }
 
 // ---------------------------------------------------------------- the GEMM kernel
-template <int TOK, bool DUAL>
+// TOK tokens per tile, DUAL = gate/up pair, UKS = k steps (of 128) per pipeline unit.
+template <int TOK, bool DUAL, int UKS>
 struct TcCfg {
   static constexpr int NW = DUAL ? 2 : 1;
-  static constexpr int A_BYTES = 128 * 128;  // shared-memory footprint of an unpacked 128 x 128 fp4 tile
-  static constexpr int A_TX = 128 * 64;      // bytes the copy accounts for (the packed data)
-  static constexpr int B_BYTES = TOK * 128;
-  static constexpr int SF_BYTES = 512;
-  static constexpr int RAW = NW * A_BYTES + 2 * B_BYTES + (NW + 1) * SF_BYTES;
+  static constexpr int A_BYTES = 128 * 128;            // shared-memory footprint of an unpacked 128 x 128 fp4 tile
+  static constexpr int A_TX = 128 * 64;                // bytes the copy accounts for (the packed data)
+  static constexpr int A_TILES = UKS * NW;             // tiles per unit, fetched 2 at a time (256 rows, 16 KiB)
+  static constexpr int B_BYTES = TOK * 128;            // one term of one k step
+  static constexpr int X_ROWS = UKS * 2 * TOK;         // rows of 128 bytes of both terms of the unit
+  static constexpr int X_BOX = X_ROWS > 256 ? 256 : X_ROWS;
+  static constexpr int NCOL = 2 * TOK;                 // MMA N: hi columns then lo columns
+  static constexpr int SFB_PER = (NCOL + 127) / 128;   // activation scale blocks per k step
+  static constexpr int SF_BLOCKS = UKS * (NW + SFB_PER);  // weight blocks first, then activation blocks
+  static constexpr int RAW = A_TILES * A_BYTES + X_ROWS * 128 + SF_BLOCKS * 512;
   static constexpr int STAGE_BYTES = (RAW + 1023) / 1024 * 1024;
-  static constexpr int TX = NW * A_TX + 2 * B_BYTES + (NW + 1) * SF_BYTES;
-  static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int SF_COLS = (NW + 1) * 4;  // tensor-memory columns of one stage's scale factors
-  static constexpr int D_COLS = NW * TOK;
+  static constexpr int TX = A_TILES * A_TX + X_ROWS * 128 + SF_BLOCKS * 512;
+  static constexpr int BUDGET = 227 * 1024 - 2048;
+  static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
+  static constexpr int SF_COLS = SF_BLOCKS * 4;        // tensor-memory columns of one stage's scale factors
+  static constexpr int D_COLS = NW * NCOL;
   static constexpr int COLS_RAW = D_COLS + STAGES * SF_COLS;
   static constexpr int TMEM_COLS = COLS_RAW <= 32 ? 32 : COLS_RAW <= 64 ? 64 : COLS_RAW <= 128 ? 128 : COLS_RAW <= 256 ? 256 : 512;
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;  // + alignment slack
+  static_assert(A_TILES % 2 == 0, "weight tiles are fetched in pairs");
+  static_assert(STAGES >= 2, "at least two stages");
+  static_assert(COLS_RAW <= 512, "tensor memory");
 };
 
 __device__ __forceinline__ void tc_finish(const TcParams& p, int tok, int n, float v, float v2, bool dual) {
@@ -236,33 +295,31 @@ __device__ __forceinline__ void tc_finish(const TcParams& p, int tok, int n, flo
   p.y[o] = f32_to_bf16_bits(v);
 }
 
-template <int TOK, bool DUAL>
+template <int TOK, bool DUAL, int UKS>
 __global__ void __launch_bounds__(kTcThreads, 1)
-qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2,
-                  const __grid_constant__ CUtensorMap tmXh, const __grid_constant__ CUtensorMap tmXl, TcParams p) {
-  using C = TcCfg<TOK, DUAL>;
+qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, TcParams p) {
+  using C = TcCfg<TOK, DUAL, UKS>;
   extern __shared__ unsigned char tc_smem_raw[];
-  __shared__ __align__(8) unsigned long long bar_full[C::STAGES], bar_empty[C::STAGES], bar_sf[C::STAGES];
+  __shared__ __align__(8) unsigned long long bar_full[C::STAGES], bar_empty[C::STAGES];
   __shared__ __align__(8) unsigned long long bar_acc_full, bar_acc_empty;
   __shared__ uint32_t tmem_holder;
   __shared__ unsigned last_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem_base = (tc_smem_u32(tc_smem_raw) + 1023u) & ~1023u;
-  unsigned char* smem_gen = tc_smem_raw + (smem_base - tc_smem_u32(tc_smem_raw));
 
-  // this CTA's contiguous range of (tile, k step) units
+  // this CTA's contiguous range of (tile, k unit) units; p.KS counts k units here
   const long long U = (long long)p.TN * p.TM * p.KS;
   const long long G = gridDim.x;
   const long long u0 = (long long)blockIdx.x * U / G, u1 = ((long long)blockIdx.x + 1) * U / G;
   const int nunits = (int)(u1 - u0);
   const int tile0 = (int)(u0 / p.KS), ks0 = (int)(u0 % p.KS);
 
+  if (threadIdx.x == 0) tc_stamp(p, 0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; s++) {
       tc_mbar_init(tc_smem_u32(&bar_full[s]), 1);
       tc_mbar_init(tc_smem_u32(&bar_empty[s]), 1);
-      tc_mbar_init(tc_smem_u32(&bar_sf[s]), 4);
     }
     tc_mbar_init(tc_smem_u32(&bar_acc_full), 1);
     tc_mbar_init(tc_smem_u32(&bar_acc_empty), 4);
@@ -280,6 +337,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   tc_fence_after();
   const uint32_t tmem = tmem_holder;
   const uint32_t sf_col0 = C::D_COLS;
+  if (threadIdx.x == 0) tc_stamp(p, 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -294,24 +352,28 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const int tn = tile / p.TM, tm = tile % p.TM;
         const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
         const uint32_t bar = tc_smem_u32(&bar_full[s]);
-        tc_mbar_expect_tx(bar, C::TX);
-        tc_tma_2d(st, &tmW, ks * 128, tn * 128, bar);
-        if (DUAL) tc_tma_2d(st + C::A_BYTES, &tmW2, ks * 128, tn * 128, bar);
-        const uint32_t sb = st + C::NW * C::A_BYTES;
-        tc_tma_2d(sb, &tmXh, ks * 128, tm * TOK, bar);
-        tc_tma_2d(sb + C::B_BYTES, &tmXl, ks * 128, tm * TOK, bar);
-        const uint32_t ssf = sb + 2 * C::B_BYTES;
-        tc_bulk_g2s(ssf, p.sfa + ((size_t)tn * p.KS + ks) * 512, 512, bar);
-        if (DUAL) tc_bulk_g2s(ssf + 512, p.sfa2 + ((size_t)tn * p.KS + ks) * 512, 512, bar);
-        tc_bulk_g2s(ssf + C::NW * 512, p.sfb + ((size_t)tm * p.KS + ks) * 512, 512, bar);
+        tc_mbar_expect_tx(bar, (p.dbg & 2) ? C::TX - C::A_TILES * C::A_TX : C::TX);
+        const int wtile = (tn * p.KS + ks) * C::A_TILES;  // first weight tile of the unit
+        if (!(p.dbg & 2)) {
+#pragma unroll
+          for (int r = 0; r < C::A_TILES / 2; r++) tc_tma_2d(st + r * 2 * C::A_BYTES, &tmW, 0, (wtile + 2 * r) * 128, bar);
+        }
+        const uint32_t sb = st + C::A_TILES * C::A_BYTES;
+        const int xrow = (tm * p.KS + ks) * C::X_ROWS;
+#pragma unroll
+        for (int r = 0; r < C::X_ROWS / C::X_BOX; r++) tc_tma_2d(sb + r * C::X_BOX * 128, &tmX, 0, xrow + r * C::X_BOX, bar);
+        const uint32_t ssf = sb + C::X_ROWS * 128;
+        tc_bulk_g2s(ssf, p.sfa + (size_t)wtile * 512, C::A_TILES * 512, bar);
+        tc_bulk_g2s(ssf + C::A_TILES * 512, p.sfb + ((size_t)tm * p.KS + ks) * UKS * C::SFB_PER * 512, UKS * C::SFB_PER * 512, bar);
         if (++ks == p.KS) { ks = 0; tile++; }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       // instruction descriptor: A = E2M1 (5), B = E4M3 (0), both K-major, N = TOK, UE8M0 scales, M = 128
-      const uint32_t idesc0 = (5u << 7) | (0u << 10) | ((uint32_t)(TOK >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
+      const uint32_t idesc0 = (5u << 7) | (0u << 10) | ((uint32_t)(C::NCOL >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
       int ks = ks0;
       uint32_t acc_phase = 0;
       bool fresh = true;  // next MMA starts a new accumulation
@@ -322,39 +384,49 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           if (!tc_wait(tc_smem_u32(&bar_acc_empty), acc_phase)) { atomicExch(p.err, 3u); break; }
           acc_phase ^= 1;
         }
-        if (!tc_wait(tc_smem_u32(&bar_full[s]), ph) || !tc_wait(tc_smem_u32(&bar_sf[s]), ph)) {
+        if (!tc_wait(tc_smem_u32(&bar_full[s]), ph)) {
           atomicExch(p.err, 4u);
           break;
         }
+        if (it == 0) tc_stamp(p, 2);
+        if (it == nunits - 1) tc_stamp(p, 3);
         tc_fence_after();
         const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
         const uint32_t sf_t = tmem + sf_col0 + (uint32_t)s * C::SF_COLS;
+        const uint32_t sb = st + C::A_TILES * C::A_BYTES;
+        const uint32_t ssf = sb + C::X_ROWS * 128;
+        const bool part_end = (ks == p.KS - 1) || (it == nunits - 1);
+        if (p.dbg & 1) {
+          tc_mbar_arrive(tc_smem_u32(&bar_empty[s]));
+          if (part_end) tc_mbar_arrive(tc_smem_u32(&bar_acc_full));
+        } else {
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-          const uint32_t idesc = idesc0 | ((uint32_t)j << 29) | ((uint32_t)j << 4);
+          for (int q = 0; q < C::SF_BLOCKS; q++) tc_cp_sf(sf_t + q * 4, tc_sf_desc(ssf + q * 512));
 #pragma unroll
-          for (int term = 0; term < 2; term++) {
-            const uint64_t bdesc = tc_smem_desc(st + C::NW * C::A_BYTES + term * C::B_BYTES) + (uint64_t)(2 * j);
+          for (int kk = 0; kk < UKS; kk++) {
 #pragma unroll
-            for (int d = 0; d < C::NW; d++) {
-              const uint64_t adesc = tc_smem_desc(st + d * C::A_BYTES) + (uint64_t)(2 * j);
-              const uint32_t acc = (fresh && j == 0 && term == 0) ? 0u : 1u;
-              tc_mma(tmem + d * TOK, adesc, bdesc, idesc, (sf_t + d * 4) | ((uint32_t)j << 30),
-                     (sf_t + C::NW * 4) | ((uint32_t)j << 30), acc);
+            for (int j = 0; j < 4; j++) {
+              const uint32_t idesc = idesc0 | ((uint32_t)j << 29) | ((uint32_t)j << 4);
+              const uint64_t bdesc = tc_smem_desc(sb + kk * 2 * C::B_BYTES) + (uint64_t)(2 * j);
+#pragma unroll
+              for (int d = 0; d < C::NW; d++) {
+                const uint64_t adesc = tc_smem_desc(st + (kk * C::NW + d) * C::A_BYTES) + (uint64_t)(2 * j);
+                const uint32_t acc = (fresh && kk == 0 && j == 0) ? 0u : 1u;
+                tc_mma(tmem + d * C::NCOL, adesc, bdesc, idesc, (sf_t + (kk * C::NW + d) * 4) | ((uint32_t)j << 30),
+                       (sf_t + (C::A_TILES + kk * C::SFB_PER) * 4) | ((uint32_t)j << 30), acc);
+              }
             }
           }
+          tc_commit(tc_smem_u32(&bar_empty[s]));
+          if (part_end) tc_commit(tc_smem_u32(&bar_acc_full));
         }
-        fresh = false;
-        tc_commit(tc_smem_u32(&bar_empty[s]));
-        if (++ks == p.KS || it == nunits - 1) {
-          tc_commit(tc_smem_u32(&bar_acc_full));
-          ks = (ks == p.KS) ? 0 : ks;
-          fresh = true;
-        }
+        fresh = part_end;
+        if (++ks == p.KS) ks = 0;
       }
     }
+    __syncwarp();
   } else {
-    // ------------------------------------------------------------ scale factors + epilogue (warps 2..5)
+    // ------------------------------------------------------------ epilogue (warps 2..5)
     const int sub = warp & 3;  // tensor-memory lanes 32*sub .. 32*sub+31 belong to this warp
     const uint32_t lane_base = ((uint32_t)(sub * 32)) << 16;
     int tile = tile0, ks = ks0;
@@ -362,22 +434,6 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     uint32_t acc_phase = 0;
     bool dead = false;
     for (int it = 0; it < nunits && !dead; it++) {
-      const int s = it % C::STAGES;
-      const uint32_t ph = (uint32_t)((it / C::STAGES) & 1);
-      if (!tc_wait(tc_smem_u32(&bar_full[s]), ph)) {
-        if (lane == 0) atomicExch(p.err, 5u);
-        dead = true;
-        break;
-      }
-      const unsigned char* ssf = smem_gen + (size_t)s * C::STAGE_BYTES + C::NW * C::A_BYTES + 2 * C::B_BYTES;
-      const uint32_t sf_t = tmem + lane_base + sf_col0 + (uint32_t)s * C::SF_COLS;
-#pragma unroll
-      for (int q = 0; q < C::NW + 1; q++) tc_st_x4(sf_t + q * 4, reinterpret_cast<const uint4*>(ssf + q * 512)[lane]);
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) tc_mbar_arrive(tc_smem_u32(&bar_sf[s]));
-
       const bool part_end = (ks == p.KS - 1) || (it == nunits - 1);
       if (part_end) {
         if (!tc_wait(tc_smem_u32(&bar_acc_full), acc_phase)) {
@@ -387,18 +443,32 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         }
         acc_phase ^= 1;
         tc_fence_after();
+        if (threadIdx.x == 64) tc_stamp(p, it == nunits - 1 ? 5 : 4);
         const int tn = tile / p.TM, tm = tile % p.TM;
         const int row = sub * 32 + lane;
         const int n = tn * 128 + row;
         const int tok0 = tm * TOK;
         const bool whole = (part_first_ks == 0) && (ks == p.KS - 1);
-        float* myslot = p.partial + (((size_t)blockIdx.x * 2 + (tile == tile0 ? 0 : 1)) * C::NW) * TOK * 128;
+        // partial tiles live as [slot][weight][128 rows][TOK] fp32: a thread owns one row, TOK consecutive floats
+        float* myslot = p.partial + (((size_t)blockIdx.x * 2 + (tile == tile0 ? 0 : 1)) * C::NW) * TOK * 128 + (size_t)row * TOK;
 #pragma unroll 1
         for (int c0 = 0; c0 < TOK; c0 += 16) {
           uint32_t r0[16], r1[16];
-          tc_ld_x16(tmem + lane_base + c0, r0);
-          if (DUAL) tc_ld_x16(tmem + lane_base + TOK + c0, r1);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          {  // hi columns + lo columns
+            uint32_t t0[16], t1[16];
+            tc_ld_x16(tmem + lane_base + c0, r0);
+            tc_ld_x16(tmem + lane_base + TOK + c0, t0);
+            if (DUAL) {
+              tc_ld_x16(tmem + lane_base + C::NCOL + c0, r1);
+              tc_ld_x16(tmem + lane_base + C::NCOL + TOK + c0, t1);
+            }
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+              r0[j] = __float_as_uint(__uint_as_float(r0[j]) + __uint_as_float(t0[j]));
+              if (DUAL) r1[j] = __float_as_uint(__uint_as_float(r1[j]) + __uint_as_float(t1[j]));
+            }
+          }
           if (whole) {
             if (n < p.N) {
 #pragma unroll
@@ -408,9 +478,11 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-              __stcg(myslot + (size_t)(c0 + j) * 128 + row, __uint_as_float(r0[j]));
-              if (DUAL) __stcg(myslot + (size_t)(TOK + c0 + j) * 128 + row, __uint_as_float(r1[j]));
+            for (int q = 0; q < 4; q++) {
+              __stcg(reinterpret_cast<uint4*>(myslot + c0) + q, make_uint4(r0[4 * q], r0[4 * q + 1], r0[4 * q + 2], r0[4 * q + 3]));
+              if (DUAL)
+                __stcg(reinterpret_cast<uint4*>(myslot + (size_t)TOK * 128 + c0) + q,
+                       make_uint4(r1[4 * q], r1[4 * q + 1], r1[4 * q + 2], r1[4 * q + 3]));
             }
           }
         }
@@ -433,16 +505,44 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             __threadfence();
             if (n < p.N) {
 #pragma unroll 1
-              for (int j = 0; j < TOK; j++) {
-                if (tok0 + j >= p.M) break;
-                float v = 0.0f, v2 = 0.0f;
-                for (int c = cfirst; c <= clast; c++) {
-                  const int ctile0 = (int)(((long long)c * U / G) / p.KS);
-                  const float* slot = p.partial + (((size_t)c * 2 + (tile == ctile0 ? 0 : 1)) * C::NW) * TOK * 128;
-                  v += __ldcg(slot + (size_t)j * 128 + row);
-                  if (DUAL) v2 += __ldcg(slot + (size_t)(TOK + j) * 128 + row);
+              for (int c0 = 0; c0 < TOK; c0 += 16) {
+                float v[16], v2[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) v[j] = v2[j] = 0.0f;
+#pragma unroll 1
+                for (int cb = cfirst; cb <= clast; cb += 4) {  // four contributors' loads in flight at a time
+                  uint4 t[4][DUAL ? 2 : 1][4];
+#pragma unroll
+                  for (int cc = 0; cc < 4; cc++) {
+                    const int c = cb + cc;
+                    if (c <= clast) {
+                      const int ctile0 = (int)(((long long)c * U / G) / p.KS);
+                      const float* slot = p.partial + (((size_t)c * 2 + (tile == ctile0 ? 0 : 1)) * C::NW) * TOK * 128 + (size_t)row * TOK + c0;
+#pragma unroll
+                      for (int q = 0; q < 4; q++) {
+                        t[cc][0][q] = __ldcg(reinterpret_cast<const uint4*>(slot) + q);
+                        if (DUAL) t[cc][DUAL ? 1 : 0][q] = __ldcg(reinterpret_cast<const uint4*>(slot + (size_t)TOK * 128) + q);
+                      }
+                    }
+                  }
+#pragma unroll
+                  for (int cc = 0; cc < 4; cc++) {
+                    if (cb + cc <= clast) {
+#pragma unroll
+                      for (int q = 0; q < 4; q++) {
+                        v[4 * q] += __uint_as_float(t[cc][0][q].x); v[4 * q + 1] += __uint_as_float(t[cc][0][q].y);
+                        v[4 * q + 2] += __uint_as_float(t[cc][0][q].z); v[4 * q + 3] += __uint_as_float(t[cc][0][q].w);
+                        if (DUAL) {
+                          v2[4 * q] += __uint_as_float(t[cc][DUAL ? 1 : 0][q].x); v2[4 * q + 1] += __uint_as_float(t[cc][DUAL ? 1 : 0][q].y);
+                          v2[4 * q + 2] += __uint_as_float(t[cc][DUAL ? 1 : 0][q].z); v2[4 * q + 3] += __uint_as_float(t[cc][DUAL ? 1 : 0][q].w);
+                        }
+                      }
+                    }
+                  }
                 }
-                tc_finish(p, tok0 + j, n, v, v2, DUAL);
+#pragma unroll
+                for (int j = 0; j < 16; j++)
+                  if (tok0 + c0 + j < p.M) tc_finish(p, tok0 + c0 + j, n, v[j], v2[j], DUAL);
               }
             }
           }
@@ -456,8 +556,10 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       }
     }
   }
+  if (threadIdx.x == 64) tc_stamp(p, 6);
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) tc_stamp(p, 7);
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)C::TMEM_COLS) : "memory");
@@ -481,61 +583,67 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D row-major tensor [rows][cols elements], box = 128 elements x box_rows, 128-byte swizzle.
-static int make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t cols, uint64_t rows,
-                    uint64_t row_stride_bytes, uint32_t box_rows) {
+// 2-D tensor of `rows` rows of 128 elements (row_bytes apart), box = 128 elements x box_rows, 128-byte swizzle.
+static int make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
   TPX_REQUIRE(fn, TPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t gdim[2] = {cols, rows};
-  cuuint64_t gstr[1] = {row_stride_bytes};
+  cuuint64_t gdim[2] = {128, rows};
+  cuuint64_t gstr[1] = {row_bytes};
   cuuint32_t box[2] = {128, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(m, dt, 2, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  TPX_REQUIRE(r == CUDA_SUCCESS, TPX_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (cols=%llu rows=%llu stride=%llu)", (int)r,
-              (unsigned long long)cols, (unsigned long long)rows, (unsigned long long)row_stride_bytes);
+  TPX_REQUIRE(r == CUDA_SUCCESS, TPX_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (rows=%llu row_bytes=%llu box_rows=%u)", (int)r,
+              (unsigned long long)rows, (unsigned long long)row_bytes, box_rows);
   return TPX_OK;
 }
 
+static inline int tc_padded_ks(int64_t K, bool pair) {
+  int ks = (int)((K + 127) / 128);
+  int m = pair ? 2 : 4;
+  return (ks + m - 1) / m * m;
+}
+
 struct TcPlan {
-  int tok;      // tokens per tile
-  int TN, TM, KS, Kp, Mpad, grid;
-  size_t off_hi, off_lo, off_sfb, off_partial, total;
+  int tok, uks;     // tokens per tile, k steps per unit
+  int TN, TM, KS, KU, Mpad, grid, xbox;
+  size_t off_terms, off_sfb, off_partial, total;
 };
 
-static TcPlan tc_plan(int64_t M, int64_t N, int64_t K, bool dual) {
+static TcPlan tc_plan(int64_t M, int64_t N, int64_t K, bool pair) {
   TcPlan pl;
-  pl.tok = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
-  pl.KS = (int)((K + 127) / 128);
-  pl.Kp = pl.KS * 128;
+  pl.tok = M <= 16 ? 16 : M <= 32 ? 32 : (M <= 64 || pair) ? 64 : 128;  // a pair needs 4*tok columns of tensor memory
+  pl.uks = pair ? 2 : (pl.tok <= 32 ? 4 : 2);
+  pl.KS = tc_padded_ks(K, pair);
+  pl.KU = pl.KS / pl.uks;
   pl.TN = (int)((N + 127) / 128);
   pl.TM = (int)((M + pl.tok - 1) / pl.tok);
   pl.Mpad = pl.TM * pl.tok;
-  long long U = (long long)pl.TN * pl.TM * pl.KS;
+  int xrows = pl.uks * 2 * pl.tok;
+  pl.xbox = xrows > 256 ? 256 : xrows;
+  long long U = (long long)pl.TN * pl.TM * pl.KU;
   int sms = sm_count();
   pl.grid = (int)(U < sms ? U : sms);
   size_t o = kTcCounterBytes;
-  auto bump = [&](size_t bytes) { size_t r = o; o += (bytes + 255) & ~(size_t)255; return r; };
-  pl.off_hi = bump((size_t)pl.Mpad * pl.Kp);
-  pl.off_lo = bump((size_t)pl.Mpad * pl.Kp);
-  pl.off_sfb = bump((size_t)pl.TM * pl.KS * 512);
-  pl.off_partial = bump((size_t)pl.grid * 2 * (dual ? 2 : 1) * pl.tok * 128 * sizeof(float));
+  auto bump = [&](size_t bytes) { size_t r = o; o += (bytes + 1023) & ~(size_t)1023; return r; };
+  pl.off_terms = bump((size_t)pl.Mpad * pl.KS * 128 * 2);
+  pl.off_sfb = bump((size_t)pl.TM * pl.KS * ((2 * pl.tok + 127) / 128) * 512);
+  pl.off_partial = bump((size_t)pl.grid * 2 * (pair ? 2 : 1) * pl.tok * 128 * sizeof(float));
   pl.total = o;
   return pl;
 }
 
-template <int TOK, bool DUAL>
-static int tc_launch(const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& xh, const CUtensorMap& xl,
-                     const TcParams& p, int grid, cudaStream_t st) {
-  using C = TcCfg<TOK, DUAL>;
+template <int TOK, bool DUAL, int UKS>
+static int tc_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams& p, int grid, cudaStream_t st) {
+  using C = TcCfg<TOK, DUAL, UKS>;
   static bool opted[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 16 || !opted[dev]) {
-    TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_tc_kernel<TOK, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+    TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_tc_kernel<TOK, DUAL, UKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     if (dev >= 0 && dev < 16) opted[dev] = true;
   }
-  qlinear_tc_kernel<TOK, DUAL><<<grid, kTcThreads, C::SMEM, st>>>(w, w2, xh, xl, p);
+  qlinear_tc_kernel<TOK, DUAL, UKS><<<grid, kTcThreads, C::SMEM, st>>>(w, x, p);
   TPX_LAUNCH_OK();
   return TPX_OK;
 }
@@ -544,44 +652,48 @@ static int tc_launch(const CUtensorMap& w, const CUtensorMap& w2, const CUtensor
 
 using namespace tpx;
 
-extern "C" int tpx_tc_packed_bytes(int64_t N, int64_t K, size_t* wq_bytes, size_t* sfa_bytes) {
+static unsigned long long* g_tc_timeline = nullptr;
+// Debug aid: when set, every CTA of the next tensor-core GEMMs writes 8 globaltimer stamps to `buf`.
+extern "C" void tpx_debug_tc_timeline(void* buf) { g_tc_timeline = reinterpret_cast<unsigned long long*>(buf); }
+
+extern "C" int tpx_tc_packed_bytes(int64_t N, int64_t K, int pair, size_t* wq_bytes, size_t* sfa_bytes) {
   TPX_REQUIRE(N > 0 && K > 0 && N % 32 == 0 && K % 64 == 0, TPX_ERR_ARG, "tc_packed_bytes: needs N %% 32 == 0 and K %% 64 == 0");
-  if (wq_bytes) *wq_bytes = (size_t)N * (K / 2);
-  if (sfa_bytes) *sfa_bytes = (size_t)((N + 127) / 128) * ((K + 127) / 128) * 512;
+  size_t tiles = (size_t)((N + 127) / 128) * tc_padded_ks(K, pair != 0) * (pair ? 2 : 1);
+  if (wq_bytes) *wq_bytes = tiles * 8192;
+  if (sfa_bytes) *sfa_bytes = tiles * 512;
   return TPX_OK;
 }
 
-extern "C" int tpx_repack_mxfp4_tc(const uint8_t* codes, const uint8_t* scales, int64_t N, int64_t K, uint8_t* wq,
-                                   uint8_t* sfa, void* stream) {
+extern "C" int tpx_repack_mxfp4_tc(const uint8_t* codes, const uint8_t* scales, const uint8_t* codes2, const uint8_t* scales2,
+                                   int64_t N, int64_t K, uint8_t* wq, uint8_t* sfa, void* stream) {
   TPX_REQUIRE(codes && scales && wq && sfa, TPX_ERR_ARG, "repack_mxfp4_tc: null pointer");
+  TPX_REQUIRE((codes2 == nullptr) == (scales2 == nullptr), TPX_ERR_ARG, "repack_mxfp4_tc: the second weight needs codes and scales");
   TPX_REQUIRE(N % 32 == 0 && K % 64 == 0, TPX_ERR_ARG, "repack_mxfp4_tc: needs N %% 32 == 0 and K %% 64 == 0");
-  int64_t a = N * (K / 2), b = ((N + 127) / 128) * ((K + 127) / 128) * 512;
-  int64_t total = a > b ? a : b;
-  repack_mxfp4_tc_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(codes, scales, N, K, wq, sfa);
+  const bool pair = codes2 != nullptr;
+  int64_t KS = tc_padded_ks(K, pair);
+  int64_t total = ((N + 127) / 128) * KS * (pair ? 2 : 1) * 8192;
+  repack_mxfp4_tc_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(codes, scales, codes2, scales2, N, K, KS, wq, sfa);
   TPX_LAUNCH_OK();
   return TPX_OK;
 }
 
-extern "C" size_t tpx_qlinear_mxfp4_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int dual) {
+extern "C" size_t tpx_qlinear_mxfp4_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int pair) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  return tc_plan(M, N, K, dual != 0).total;
+  return tc_plan(M, N, K, pair != 0).total;
 }
 
-extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, const uint8_t* wq2, const uint8_t* sfa2,
-                                    const uint16_t* x, int64_t M, int64_t N, int64_t K, const uint16_t* bias, int act,
-                                    const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y,
-                                    void* scratch, size_t scratch_bytes, void* stream) {
+extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M, int64_t N,
+                                    int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
+                                    float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream) {
   TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear_mxfp4_tc: bad shape");
   if (M == 0) return TPX_OK;
   TPX_REQUIRE(wq && sfa && x && y, TPX_ERR_ARG, "qlinear_mxfp4_tc: null pointer");
-  TPX_REQUIRE((wq2 == nullptr) == (sfa2 == nullptr), TPX_ERR_ARG, "qlinear_mxfp4_tc: second weight needs codes and scales");
-  TPX_REQUIRE(!(wq2 && mul_in), TPX_ERR_ARG, "qlinear_mxfp4_tc: gate/up pair and mul_in are exclusive");
+  TPX_REQUIRE(!(pair && mul_in), TPX_ERR_ARG, "qlinear_mxfp4_tc: gate/up pair and mul_in are exclusive");
   TPX_REQUIRE(N % 32 == 0 && K % 64 == 0, TPX_ERR_ARG, "qlinear_mxfp4_tc: needs N %% 32 == 0 and K %% 64 == 0");
   TPX_REQUIRE(act >= TPX_ACT_NONE && act <= TPX_ACT_RELU, TPX_ERR_ARG, "qlinear_mxfp4_tc: unknown activation %d", act);
-  TPX_REQUIRE(((uintptr_t)wq & 31) == 0 && ((uintptr_t)wq2 & 31) == 0 && ((uintptr_t)sfa & 15) == 0 && ((uintptr_t)sfa2 & 15) == 0 &&
-                  ((uintptr_t)x & 15) == 0 && ((uintptr_t)scratch & 255) == 0,
+  TPX_REQUIRE(((uintptr_t)wq & 31) == 0 && ((uintptr_t)sfa & 15) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)scratch & 255) == 0,
               TPX_ERR_ARG, "qlinear_mxfp4_tc: misaligned pointer");
-  const bool dual = wq2 != nullptr;
+  const bool dual = pair != 0;
   TcPlan pl = tc_plan(M, N, K, dual);
   TPX_REQUIRE((size_t)pl.TN * pl.TM * sizeof(unsigned) <= kTcCounterBytes - 16, TPX_ERR_UNSUPPORTED,
               "qlinear_mxfp4_tc: %d x %d output tiles exceed the counter region; split the batch", pl.TN, pl.TM);
@@ -589,31 +701,48 @@ extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, const
               pl.total, scratch_bytes);
   cudaStream_t st = (cudaStream_t)stream;
   unsigned char* sc = reinterpret_cast<unsigned char*>(scratch);
-  uint8_t *hi = sc + pl.off_hi, *lo = sc + pl.off_lo, *sfb = sc + pl.off_sfb;
+  uint8_t *terms = sc + pl.off_terms, *sfb = sc + pl.off_sfb;
   {
-    long long threads = (long long)pl.Mpad * (pl.Kp / 32);
-    split_activations_kernel<<<(unsigned)((threads + 127) / 128), 128, 0, st>>>(x, (int)M, (int)K, pl.Mpad, pl.Kp, pl.tok, hi, lo, sfb);
+    long long threads = (long long)pl.Mpad * pl.KS * 4;
+    split_activations_kernel<<<(unsigned)((threads + 127) / 128), 128, 0, st>>>(x, (int)M, (int)K, pl.Mpad, pl.KS, pl.tok, pl.uks, terms, sfb);
     TPX_LAUNCH_OK();
   }
-  CUtensorMap mw, mw2, mxh, mxl;
-  int rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, (uint64_t)K, (uint64_t)N, (uint64_t)K / 2, 128);
+  CUtensorMap mw, mx;
+  // weight: 64-byte rows of 128 codes, 256 rows (two tiles) per request; activation terms: 128-byte rows
+  int rc;
+  { const char* e = getenv("TPX_TC_DBG"); if (e && (atoi(e) & 4)) {  // timing experiment: raw byte copy instead of the unpacking copy
+      EncodeTiledFn fn = encode_fn();
+      cuuint64_t gdim[2] = {64, (uint64_t)pl.TN * pl.KS * (dual ? 2 : 1) * 128};
+      cuuint64_t gstr[1] = {64};
+      cuuint32_t box[2] = {64, 256};
+      cuuint32_t estr[2] = {1, 1};
+      CUresult r = fn(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(wq), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      rc = r == CUDA_SUCCESS ? TPX_OK : TPX_ERR_CUDA;
+    } else
+      rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, (uint64_t)pl.TN * pl.KS * (dual ? 2 : 1) * 128, 64, 256);
+  }
   if (rc) return rc;
-  rc = make_map(&mw2, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, dual ? wq2 : wq, (uint64_t)K, (uint64_t)N, (uint64_t)K / 2, 128);
-  if (rc) return rc;
-  rc = make_map(&mxh, CU_TENSOR_MAP_DATA_TYPE_UINT8, hi, (uint64_t)pl.Kp, (uint64_t)pl.Mpad, (uint64_t)pl.Kp, (uint32_t)pl.tok);
-  if (rc) return rc;
-  rc = make_map(&mxl, CU_TENSOR_MAP_DATA_TYPE_UINT8, lo, (uint64_t)pl.Kp, (uint64_t)pl.Mpad, (uint64_t)pl.Kp, (uint32_t)pl.tok);
+  rc = make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, terms, (uint64_t)pl.Mpad * pl.KS * 2, 128, (uint32_t)pl.xbox);
   if (rc) return rc;
   TcParams p;
-  p.sfa = sfa; p.sfa2 = sfa2; p.sfb = sfb; p.bias = bias; p.mul_in = mul_in; p.res = res; p.res_scale = res_scale; p.y = y;
+  p.sfa = sfa; p.sfa2 = nullptr; p.sfb = sfb; p.bias = bias; p.mul_in = mul_in; p.res = res; p.res_scale = res_scale; p.y = y;
   p.partial = reinterpret_cast<float*>(sc + pl.off_partial);
   p.counters = reinterpret_cast<unsigned*>(sc);
   p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
-  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KS; p.TN = pl.TN; p.TM = pl.TM; p.act = act;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = pl.TM; p.act = act; p.tl = g_tc_timeline;
+  { const char* e = getenv("TPX_TC_DBG"); p.dbg = e ? atoi(e) : 0; }
+  if (dual) {
+    switch (pl.tok) {
+      case 16: return tc_launch<16, true, 2>(mw, mx, p, pl.grid, st);
+      case 32: return tc_launch<32, true, 2>(mw, mx, p, pl.grid, st);
+      default: return tc_launch<64, true, 2>(mw, mx, p, pl.grid, st);
+    }
+  }
   switch (pl.tok) {
-    case 16: return dual ? tc_launch<16, true>(mw, mw2, mxh, mxl, p, pl.grid, st) : tc_launch<16, false>(mw, mw2, mxh, mxl, p, pl.grid, st);
-    case 32: return dual ? tc_launch<32, true>(mw, mw2, mxh, mxl, p, pl.grid, st) : tc_launch<32, false>(mw, mw2, mxh, mxl, p, pl.grid, st);
-    case 64: return dual ? tc_launch<64, true>(mw, mw2, mxh, mxl, p, pl.grid, st) : tc_launch<64, false>(mw, mw2, mxh, mxl, p, pl.grid, st);
-    default: return dual ? tc_launch<128, true>(mw, mw2, mxh, mxl, p, pl.grid, st) : tc_launch<128, false>(mw, mw2, mxh, mxl, p, pl.grid, st);
+    case 16: return tc_launch<16, false, 4>(mw, mx, p, pl.grid, st);
+    case 32: return tc_launch<32, false, 4>(mw, mx, p, pl.grid, st);
+    case 64: return tc_launch<64, false, 2>(mw, mx, p, pl.grid, st);
+    default: return tc_launch<128, false, 2>(mw, mx, p, pl.grid, st);
   }
 }
