@@ -55,6 +55,7 @@ struct TcParams {
   int KS;               // k units (of UKS k steps of 128) per tile
   int TN, TM;           // output tiles along features / tokens
   int act;
+  int whole_tiles;      // 1: every CTA owns whole output tiles (no partial tiles, no fix-up)
   unsigned long long* tl;  // optional per-CTA timeline (8 globaltimer stamps each), null in normal use
   int dbg;              // debug knobs for timing experiments: 1 = skip MMAs, 2 = skip weight copies
 };
@@ -153,6 +154,9 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
 // Padding rows and padding columns get zeros with scale 2^0.
 __global__ void split_activations_kernel(const uint16_t* __restrict__ x, int M, int K, int Mpad, int KS, int TOK, int UKS,
                                          uint8_t* __restrict__ terms, uint8_t* __restrict__ sfb) {
+  // let the GEMM that consumes these terms start its prologue and weight prefetch now; it waits for this
+  // grid to finish (griddepcontrol.wait) before it touches the terms
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int nb = KS * 4;
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)Mpad * nb) return;
@@ -311,7 +315,9 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   // this CTA's contiguous range of (tile, k unit) units; p.KS counts k units here
   const long long U = (long long)p.TN * p.TM * p.KS;
   const long long G = gridDim.x;
-  const long long u0 = (long long)blockIdx.x * U / G, u1 = ((long long)blockIdx.x + 1) * U / G;
+  const long long T = (long long)p.TN * p.TM;
+  const long long u0 = p.whole_tiles ? ((long long)blockIdx.x * T / G) * p.KS : (long long)blockIdx.x * U / G;
+  const long long u1 = p.whole_tiles ? (((long long)blockIdx.x + 1) * T / G) * p.KS : ((long long)blockIdx.x + 1) * U / G;
   const int nunits = (int)(u1 - u0);
   const int tile0 = (int)(u0 / p.KS), ks0 = (int)(u0 % p.KS);
 
@@ -342,14 +348,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      int tile = tile0, ks = ks0;
-      for (int it = 0; it < nunits; it++) {
-        const int s = it % C::STAGES;
-        if (it >= C::STAGES && !tc_wait(tc_smem_u32(&bar_empty[s]), (uint32_t)((it / C::STAGES - 1) & 1))) {
-          atomicExch(p.err, 2u);
-          break;
-        }
-        const int tn = tile / p.TM, tm = tile % p.TM;
+      auto fetch_w = [&](int s, int tn, int ks) {  // weight tiles and their scale blocks: independent of the split kernel
         const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
         const uint32_t bar = tc_smem_u32(&bar_full[s]);
         tc_mbar_expect_tx(bar, (p.dbg & 2) ? C::TX - C::A_TILES * C::A_TX : C::TX);
@@ -358,13 +357,40 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 #pragma unroll
           for (int r = 0; r < C::A_TILES / 2; r++) tc_tma_2d(st + r * 2 * C::A_BYTES, &tmW, 0, (wtile + 2 * r) * 128, bar);
         }
+        tc_bulk_g2s(st + C::A_TILES * C::A_BYTES + C::X_ROWS * 128, p.sfa + (size_t)wtile * 512, C::A_TILES * 512, bar);
+      };
+      auto fetch_x = [&](int s, int tm, int ks) {  // activation terms and their scale blocks
+        const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
+        const uint32_t bar = tc_smem_u32(&bar_full[s]);
         const uint32_t sb = st + C::A_TILES * C::A_BYTES;
         const int xrow = (tm * p.KS + ks) * C::X_ROWS;
 #pragma unroll
         for (int r = 0; r < C::X_ROWS / C::X_BOX; r++) tc_tma_2d(sb + r * C::X_BOX * 128, &tmX, 0, xrow + r * C::X_BOX, bar);
-        const uint32_t ssf = sb + C::X_ROWS * 128;
-        tc_bulk_g2s(ssf, p.sfa + (size_t)wtile * 512, C::A_TILES * 512, bar);
-        tc_bulk_g2s(ssf + C::A_TILES * 512, p.sfb + ((size_t)tm * p.KS + ks) * UKS * C::SFB_PER * 512, UKS * C::SFB_PER * 512, bar);
+        tc_bulk_g2s(sb + C::X_ROWS * 128 + C::A_TILES * 512, p.sfb + ((size_t)tm * p.KS + ks) * UKS * C::SFB_PER * 512,
+                    UKS * C::SFB_PER * 512, bar);
+      };
+      // the first stages' weights go out before this grid is allowed to see the split kernel's output
+      const int early = nunits < C::STAGES ? nunits : C::STAGES;
+      {
+        int tile = tile0, ks = ks0;
+        for (int it = 0; it < early; it++) {
+          fetch_w(it, tile / p.TM, ks);
+          if (++ks == p.KS) { ks = 0; tile++; }
+        }
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      int tile = tile0, ks = ks0;
+      for (int it = 0; it < nunits; it++) {
+        const int s = it % C::STAGES;
+        const int tn = tile / p.TM, tm = tile % p.TM;
+        if (it >= C::STAGES) {
+          if (!tc_wait(tc_smem_u32(&bar_empty[s]), (uint32_t)((it / C::STAGES - 1) & 1))) {
+            atomicExch(p.err, 2u);
+            break;
+          }
+          fetch_w(s, tn, ks);
+        }
+        fetch_x(s, tm, ks);
         if (++ks == p.KS) { ks = 0; tile++; }
       }
     }
@@ -433,6 +459,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     int part_first_ks = ks0;
     uint32_t acc_phase = 0;
     bool dead = false;
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // scratch, residual and gate inputs belong to earlier grids
     for (int it = 0; it < nunits && !dead; it++) {
       const bool part_end = (ks == p.KS - 1) || (it == nunits - 1);
       if (part_end) {
@@ -443,7 +470,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         }
         acc_phase ^= 1;
         tc_fence_after();
-        if (threadIdx.x == 64) tc_stamp(p, it == nunits - 1 ? 5 : 4);
+        if (threadIdx.x == 64 && it == nunits - 1) tc_stamp(p, 5);
         const int tn = tile / p.TM, tm = tile % p.TM;
         const int row = sub * 32 + lane;
         const int n = tn * 128 + row;
@@ -490,19 +517,20 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         __syncwarp();
         if (lane == 0) tc_mbar_arrive(tc_smem_u32(&bar_acc_empty));  // tensor memory may be overwritten
         if (!whole) {
-          // hand the partial tile in; the last contributor adds all of them in CTA order
-          __threadfence();
+          // hand the partial tile in; the last contributor adds all of them in CTA order. The CTA barrier orders
+          // every thread's stores before thread 64's release, and its acquire before every thread's loads.
           asm volatile("bar.sync 1, 128;" ::: "memory");
           const long long ta = (long long)tile * p.KS, tb = ta + p.KS - 1;
           const int cfirst = (int)(((ta + 1) * G - 1) / U), clast = (int)(((tb + 1) * G - 1) / U);
           if (threadIdx.x == 64) {
-            unsigned prev = atomicAdd(p.counters + tile, 1u);
+            unsigned prev;
+            asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prev) : "l"(p.counters + tile) : "memory");
             last_flag = (prev == (unsigned)(clast - cfirst)) ? 1u : 0u;
             if (last_flag) p.counters[tile] = 0;
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 64 && it == nunits - 1) tc_stamp(p, 4);
           if (last_flag) {
-            __threadfence();
             if (n < p.N) {
 #pragma unroll 1
               for (int c0 = 0; c0 < TOK; c0 += 16) {
@@ -540,6 +568,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                     }
                   }
                 }
+                if (threadIdx.x == 64 && it == nunits - 1 && c0 == 0) tc_stamp(p, 7);
 #pragma unroll
                 for (int j = 0; j < 16; j++)
                   if (tok0 + c0 + j < p.M) tc_finish(p, tok0 + c0 + j, n, v[j], v2[j], DUAL);
@@ -559,7 +588,6 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   if (threadIdx.x == 64) tc_stamp(p, 6);
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) tc_stamp(p, 7);
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)C::TMEM_COLS) : "memory");
@@ -606,7 +634,7 @@ static inline int tc_padded_ks(int64_t K, bool pair) {
 
 struct TcPlan {
   int tok, uks;     // tokens per tile, k steps per unit
-  int TN, TM, KS, KU, Mpad, grid, xbox;
+  int TN, TM, KS, KU, Mpad, grid, xbox, whole_tiles;
   size_t off_terms, off_sfb, off_partial, total;
 };
 
@@ -622,8 +650,12 @@ static TcPlan tc_plan(int64_t M, int64_t N, int64_t K, bool pair) {
   int xrows = pl.uks * 2 * pl.tok;
   pl.xbox = xrows > 256 ? 256 : xrows;
   long long U = (long long)pl.TN * pl.TM * pl.KU;
+  long long T = (long long)pl.TN * pl.TM;
   int sms = sm_count();
-  pl.grid = (int)(U < sms ? U : sms);
+  // Cutting tiles between CTAs balances the weight stream exactly but costs a fix-up pass through scratch at
+  // loaded-memory latency; with nearly as many tiles as SMs, or many tiles per SM, whole tiles are cheaper.
+  pl.whole_tiles = (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
+  pl.grid = pl.whole_tiles ? (int)(T < sms ? T : sms) : (int)(U < sms ? U : sms);
   size_t o = kTcCounterBytes;
   auto bump = [&](size_t bytes) { size_t r = o; o += (bytes + 1023) & ~(size_t)1023; return r; };
   pl.off_terms = bump((size_t)pl.Mpad * pl.KS * 128 * 2);
@@ -643,8 +675,18 @@ static int tc_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams&
     TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_tc_kernel<TOK, DUAL, UKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     if (dev >= 0 && dev < 16) opted[dev] = true;
   }
-  qlinear_tc_kernel<TOK, DUAL, UKS><<<grid, kTcThreads, C::SMEM, st>>>(w, x, p);
-  TPX_LAUNCH_OK();
+  // programmatic dependent launch: the prologue and the first weight fetches overlap the split kernel
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = C::SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tc_kernel<TOK, DUAL, UKS>, w, x, p));
   return TPX_OK;
 }
 
@@ -730,7 +772,7 @@ extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int p
   p.partial = reinterpret_cast<float*>(sc + pl.off_partial);
   p.counters = reinterpret_cast<unsigned*>(sc);
   p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
-  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = pl.TM; p.act = act; p.tl = g_tc_timeline;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = pl.TM; p.act = act; p.whole_tiles = pl.whole_tiles; p.tl = g_tc_timeline;
   { const char* e = getenv("TPX_TC_DBG"); p.dbg = e ? atoi(e) : 0; }
   if (dual) {
     switch (pl.tok) {
