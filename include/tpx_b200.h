@@ -129,6 +129,44 @@ int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const 
                          int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
                          float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream);
 
+/* ---------------------------------------------------------------- decoder-layer pieces
+ * RMSNorm: y = x * rsqrt(mean(x^2) + eps) * gamma, fp32 statistics. Replaces llama_rms_norm
+ * (src/csrc/llm/fused_llm_infer.cpp:336-363; RMSNormFwdTPP::ref src/csrc/xsmm_functors.h:4628-4654).
+ * gamma is bf16 or, with gamma_is_f32 != 0, fp32 (the reference accepts either, :346-357).             */
+int tpx_rmsnorm(const uint16_t* x, const void* gamma, int gamma_is_f32, float eps, int64_t rows, int64_t D,
+                uint16_t* y, void* stream);
+
+/* RoPE + KV-cache append in one pass. Replaces apply_rotary_pos_emb_llama on q and k
+ * (src/csrc/llm/fused_llm_infer.cpp:206-253), the q/k/v views and the q permute of self_mha (:563-584) and
+ * TppCache::update -> LayerCache::update (src/csrc/llm/attn.h:197-221, KVLayout_BNSH src/csrc/llm/attn.cpp:389-463).
+ *   qkv   [B*S][(Nq + 2*Nkv)*H] bf16: output of the fused q/k/v linear (q heads, k heads, v heads)
+ *   ep    [2][MP][HR] fp32 (0 = cos, 1 = sin), pos int64 [Bpos][S] with Bpos 1 or B
+ *   q_out [B][Nkv][S][Nq/Nkv][H] rotated queries
+ *   kc,vc [capacity/32][B][Nkv][32][H] cache tensors; the S new tokens land at offset .. offset+S-1
+ * The caller owns the cache tensors and their growth (the reference grows by offset + S + KV_CACHE_INC_SIZE,
+ * attn.h:171-177); this call refuses a write beyond `capacity` tokens.                                      */
+int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const int64_t* pos, int64_t B, int64_t S, int64_t Nq,
+                       int64_t Nkv, int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset, int64_t capacity,
+                       uint16_t* q_out, uint16_t* kc, uint16_t* vc, void* stream);
+
+/* Attention over the blocked cache. Replaces attn<T> (src/csrc/llm/attn.cpp:780-955):
+ *   out = softmax(q.k^T / sqrt(H) + am[b][key], causal: key <= key_len - Sq + query) . v
+ * q/out [B][Nkv][Sq][R][H] (GQA group folded into the row dimension, attn.cpp:793-795), am additive bf16 mask
+ * [B][Spad] or NULL (0 keep, finfo.min drop; attn.h:310-322). fp32 scores, softmax and accumulation, one bf16
+ * rounding of the output. With a long cache and few (batch, head) pairs the key range is split over CTAs and
+ * merged by a second kernel (flash-decoding); the scratch holds the un-normalised partials. out_bsnrh != 0
+ * writes out as [B][Sq][Nkv][R][H], i.e. already as the [B*Sq][Nq*H] rows of the output projection (the
+ * reference permutes and copies, src/csrc/llm/fused_llm_infer.cpp:581).                                     */
+size_t tpx_attention_scratch_bytes(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len);
+int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, const uint16_t* am, int64_t B, int64_t Nkv,
+                  int64_t Sq, int64_t R, int64_t H, int64_t key_len, int64_t Spad, int causal, int out_bsnrh,
+                  uint16_t* out, void* scratch, size_t scratch_bytes, void* stream);
+
+/* TppCache::align_and_invert_mask (src/csrc/llm/attn.h:310-322): [B][S] bf16 0/1 mask -> [B][Spad] additive
+ * mask (1 -> 0, 0 -> min_bits, padding -> min_bits), Spad a multiple of 32.                                  */
+int tpx_align_and_invert_mask(const uint16_t* mask, int64_t B, int64_t S, int64_t Spad, uint16_t min_bits,
+                              uint16_t* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

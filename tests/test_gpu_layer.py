@@ -1,0 +1,156 @@
+"""GPU parity: RMSNorm, RoPE + KV-cache write, attention and the whole Llama decoder layer against the oracle.
+Tolerance: max |y - ref| / max |ref| <= 2e-2 (bf16 outputs, fp32-accumulated oracle)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests.gpu_util import assert_no_kernel_error, make_qweight, to_dev_bf16, to_host_bits
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+def test_rmsnorm(cuda):
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    rng = np.random.default_rng(1)
+    for rows, D in [(1, 4096), (7, 256), (33, 8192)]:
+        x, g = O.randn_bf16(rng, (rows, D)), O.randn_bf16(rng, (D,))
+        y = to_host_bits(F.rms_norm(to_dev_bf16(x, cuda), to_dev_bf16(g, cuda), 1e-5))
+        assert O.rel_err(y, O.rmsnorm(x, g, 1e-5)) <= 1e-2
+        y32 = to_host_bits(F.rms_norm(to_dev_bf16(x, cuda), torch.from_numpy(O.bf16_to_f32(g)).to(cuda), 1e-5))
+        assert np.array_equal(y32, y)
+
+
+def _rope_case(cuda, B, S, Nq, Nkv, H, offset, pos):
+    from tpp_pytorch_extension_b200 import _lib
+    rng = np.random.default_rng(B * 100 + S)
+    MP = 64
+    ep = O.rope_table(MP, H, 1e4)
+    qkv = O.randn_bf16(rng, (B, S, (Nq + 2 * Nkv) * H))
+    cap = (offset + S + 31) // 32 * 32 + 32
+    kc = torch.zeros((cap // 32, B, Nkv, 32, H), dtype=torch.bfloat16, device=cuda)
+    vc = torch.zeros_like(kc)
+    R = Nq // Nkv
+    q = torch.empty((B, Nkv, S, R, H), dtype=torch.bfloat16, device=cuda)
+    pos_t = torch.from_numpy(pos).to(cuda)
+    qkv_t, ep_t = to_dev_bf16(qkv, cuda), torch.from_numpy(ep).to(cuda)  # keep the device copies alive across the launch
+    _lib.check(_lib.lib().tpx_rope_kv_update(qkv_t.data_ptr(), ep_t.data_ptr(),
+                                             pos_t.data_ptr(), B, S, Nq, Nkv, H, MP, H, pos.shape[0], offset, cap,
+                                             q.data_ptr(), kc.data_ptr(), vc.data_ptr(), _lib.stream()))
+    torch.cuda.synchronize()
+    qr = qkv[..., : Nq * H]
+    kr = qkv[..., Nq * H: (Nq + Nkv) * H]
+    vr = qkv[..., (Nq + Nkv) * H:]
+    q_ref = O.rope_llama(qr, ep, pos, Nq, H).reshape(B, S, Nkv, R, H).transpose(0, 2, 1, 3, 4)
+    k_ref = O.rope_llama(kr, ep, pos, Nkv, H).reshape(B, S, Nkv, H)
+    v_ref = vr.reshape(B, S, Nkv, H)
+    assert np.array_equal(to_host_bits(q), np.ascontiguousarray(q_ref))
+    kh, vh = to_host_bits(kc), to_host_bits(vc)
+    for s in range(S):
+        t = offset + s
+        assert np.array_equal(kh[t // 32, :, :, t % 32], k_ref[:, s])
+        assert np.array_equal(vh[t // 32, :, :, t % 32], v_ref[:, s])
+    assert not kh[(offset + S + 31) // 32:].any()  # nothing beyond the written tokens
+
+
+def test_rope_kv_update_bit_exact(cuda):
+    _rope_case(cuda, 2, 5, 8, 2, 128, 0, np.arange(5, dtype=np.int64)[None])
+    _rope_case(cuda, 3, 1, 4, 4, 64, 37, np.array([[37], [12], [63]], dtype=np.int64))
+    # positions at and beyond the table leave the row untouched
+    _rope_case(cuda, 1, 3, 2, 1, 128, 30, np.array([[62, 64, 100]], dtype=np.int64))
+
+
+def test_rope_rejects_overflow(cuda):
+    from tpp_pytorch_extension_b200 import _lib
+    z = torch.zeros(4096, dtype=torch.bfloat16, device=cuda)
+    f = torch.zeros(4096, dtype=torch.float32, device=cuda)
+    p = torch.zeros(8, dtype=torch.int64, device=cuda)
+    rc = _lib.lib().tpx_rope_kv_update(z.data_ptr(), f.data_ptr(), p.data_ptr(), 1, 4, 2, 1, 64, 8, 64, 1, 30, 32,
+                                       z.data_ptr(), z.data_ptr(), z.data_ptr(), _lib.stream())
+    assert rc == 1 and b"capacity" in _lib.lib().tpx_last_error()
+
+
+@pytest.mark.parametrize("B,Nkv,R,H,ctx,Sq", [(1, 2, 4, 128, 100, 1), (2, 1, 8, 128, 1500, 1), (1, 8, 1, 64, 64, 64),
+                                              (2, 2, 4, 128, 300, 37), (16, 8, 4, 128, 2048, 1), (1, 1, 2, 128, 4100, 3)])
+def test_attention_matches_oracle(cuda, B, Nkv, R, H, ctx, Sq):
+    from tpp_pytorch_extension_b200._C._tpp_attn import TppCache, attention
+    rng = np.random.default_rng(ctx + Sq)
+    key_len = ctx
+    S1 = (key_len + 128 + 31) // 32
+    kc = np.zeros((S1, B, Nkv, 32, H), np.uint16)
+    vc = np.zeros_like(kc)
+    k = O.randn_bf16(rng, (key_len, B, Nkv, H))
+    v = O.randn_bf16(rng, (key_len, B, Nkv, H))
+    for t in range(key_len):
+        kc[t // 32, :, :, t % 32] = k[t]
+        vc[t // 32, :, :, t % 32] = v[t]
+    q = O.randn_bf16(rng, (B, Nkv, Sq, R, H))
+    m01 = np.ones((B, key_len))
+    if B > 1:
+        m01[1, :5] = 0  # left padding on one sequence
+    cache = TppCache()
+    am = cache.align_and_invert_mask(torch.from_numpy(m01).to(cuda))
+    am_ref = O.align_and_invert_mask(m01)
+    assert np.array_equal(to_host_bits(am), am_ref)
+    out = attention(to_dev_bf16(q, cuda), to_dev_bf16(kc, cuda), to_dev_bf16(vc, cuda), am, key_len)
+    ref = O.attention(q, kc, vc, am_ref, key_len)
+    assert O.rel_err(to_host_bits(out), ref) <= TOL
+    out2 = attention(to_dev_bf16(q, cuda), to_dev_bf16(kc, cuda), to_dev_bf16(vc, cuda), am, key_len, out_bsnrh=True)
+    want = np.ascontiguousarray(ref.transpose(0, 2, 1, 3, 4)).reshape(B, Sq, -1)
+    assert O.rel_err(to_host_bits(out2), want) <= TOL
+
+
+def test_cache_growth_and_crop(cuda):
+    from tpp_pytorch_extension_b200._C._tpp_attn import TppCache
+    c = TppCache()
+    k = torch.randn(2, 3, 40, 64, device=cuda).bfloat16()
+    kc, vc = c.update(k, k, 0)
+    assert c.get_seq_length() == 40 and c.get_capacity() == (40 + 128 + 31) // 32 * 32 and c.size() == 1
+    assert torch.equal(kc[1, :, :, 7], k[:, :, 39])
+    k2 = torch.randn(2, 3, 200, 64, device=cuda).bfloat16()
+    kc, _ = c.update(k2, k2, 0)
+    assert c.get_seq_length() == 240 and c.get_capacity() >= 240 + 128
+    assert torch.equal(kc[1, :, :, 7], k[:, :, 39]) and torch.equal(kc[7, :, :, 15], k2[:, :, 199])
+    c.crop(100)
+    assert c.get_seq_length() == 100
+    c.crop(500)
+    assert c.get_seq_length() == 100
+    with pytest.raises(NotImplementedError):
+        c.reorder_cache(torch.zeros(2, dtype=torch.long))
+
+
+@pytest.mark.parametrize("kind", ["mxfp4", "int8"])
+def test_llama_layer_prefill_then_decode(cuda, kind):
+    """One decoder layer (GQA, 2 kv heads x 2) through prefill of 37 tokens and three decode steps."""
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    from tpp_pytorch_extension_b200._C._tpp_attn import TppCache
+    rng = np.random.default_rng(5)
+    D, Nq, Nkv, H, FF, B, MP = 256, 4, 2, 64, 512, 2, 128
+    eps = 1e-5
+    names = {"q": (Nq * H, D), "k": (Nkv * H, D), "v": (Nkv * H, D), "o": (D, Nq * H), "gate": (FF, D), "up": (FF, D), "down": (D, FF)}
+    qt, W = {}, {}
+    for nm, (n, k) in names.items():
+        qt[nm], W[nm], _ = make_qweight(rng, n, k, kind, cuda, std=0.05)
+    W["ln1"], W["ln2"] = O.f32_to_bf16(1 + 0.1 * rng.standard_normal(D).astype(np.float32)), O.f32_to_bf16(1 + 0.1 * rng.standard_normal(D).astype(np.float32))
+    ep = O.rope_table(MP, H, 1e4)
+    layer = F.LlamaDecoderLayer([to_dev_bf16(W["ln1"], cuda), qt["q"], qt["k"], qt["v"], qt["o"], to_dev_bf16(W["ln2"], cuda),
+                                 qt["gate"], qt["up"], qt["down"], torch.from_numpy(ep).to(cuda)], 0, eps, H, MP, H)
+    cache, ocache = TppCache(), O.KVCache()
+    total = 0
+    for S in (37, 1, 1, 1):
+        hs = O.randn_bf16(rng, (B, S, D))
+        pos = np.arange(total, total + S, dtype=np.int64)[None]
+        total += S
+        m01 = np.ones((B, total))
+        m01[1, :3] = 0
+        am = cache.align_and_invert_mask(torch.from_numpy(m01).to(cuda))
+        out = layer.forward([to_dev_bf16(hs, cuda), am, torch.from_numpy(pos).to(cuda)], cache, True)
+        ref = O.llama_layer(hs, O.align_and_invert_mask(m01), pos, W, ocache, 0, Nq, Nkv, H, eps, ep)
+        assert_no_kernel_error()
+        assert O.rel_err(to_host_bits(out[0]), ref) <= TOL, S
+        assert cache.get_seq_length(0) == total
+        kc_ref, _ = ocache.layers[0]["k"], ocache.layers[0]["v"]
+        got = to_host_bits(out[1])
+        n = min(got.shape[0], kc_ref.shape[0])
+        assert O.rel_err(got[:n], kc_ref[:n]) <= TOL

@@ -87,3 +87,126 @@ def fc_plain_act(input, weight, bias=None, act=None, mul_in=None, res=None, res_
 def fc_gate_up(input, w_gate, w_up, act="silu"):
     """act(x.Wg^T) * (x.Wu^T) in one pass over both weights (src/csrc/llm/fused_llm_infer.cpp:1271-1272)."""
     return _qlinear(input, w_gate, w_up, None, act, None, None, 1.0)
+
+
+# --------------------------------------------------------------------------- decoder-layer pieces
+def rms_norm(x, gamma, eps):
+    """llama_rms_norm (src/csrc/llm/fused_llm_infer.cpp:336-363)."""
+    _lib.require_cuda(x, "input")
+    y = torch.empty_like(x)
+    D = x.shape[-1]
+    if gamma.dtype not in (torch.bfloat16, torch.float32):
+        raise _lib.TpxError("llama_rms_norm: unsupported gamma dtype")
+    _lib.check(_lib.lib().tpx_rmsnorm(x.data_ptr(), gamma.data_ptr(), int(gamma.dtype == torch.float32), float(eps),
+                                      x.numel() // D, D, y.data_ptr(), _lib.stream()))
+    return y
+
+
+_pg = None
+
+
+def set_pg(pg):
+    """tpp_llm.set_pg (src/csrc/llm/fused_llm_infer.cpp:66-99): the process group of the tensor-parallel ranks."""
+    global _pg
+    _pg = pg
+
+
+def get_pg_size():
+    import torch.distributed as dist
+    return dist.get_world_size(_pg) if (_pg is not None and dist.is_initialized()) else 1
+
+
+def allreduce(t):
+    """tpp_llm.allreduce (src/csrc/llm/fused_llm_infer.cpp:101-119): in-place SUM over the tensor-parallel ranks
+    (NCCL over NVLink here; the reference uses its shared-memory all-reduce or the c10d backend)."""
+    import torch.distributed as dist
+    if _pg is None or not dist.is_initialized():
+        raise _lib.TpxError("Missing process group when using model parallel, use set_pg()")
+    dist.all_reduce(t, group=_pg)
+    return t
+
+
+def _cat_q(ws):
+    """Concatenate quantized weights along the output features (the fused q/k/v loop nest of the reference,
+    src/csrc/llm/fused_llm_infer.cpp:422-505): blocks are per output row, so stacking the storage is exact."""
+    from ._qtype import QTensor
+    w0 = ws[0]
+    for w in ws[1:]:
+        if (w.kind, w.block_size, w.shape[1:]) != (w0.kind, w0.block_size, w0.shape[1:]):
+            raise _lib.TpxError("fused q/k/v: weights must share quantization and in-features")
+    codes = torch.cat([w.codes for w in ws], 0)
+    scales = torch.cat([w.scales for w in ws], 0)
+    return QTensor(codes, scales, (codes.shape[0],) + tuple(w0.shape[1:]), w0.qscheme(), w0.block_size)
+
+
+class LlamaDecoderLayer:
+    """torch.classes.tpp_llm.LlamaDecoderLayer (src/csrc/llm/fused_llm_infer.cpp:1071-1287).
+
+    params: [input_ln_gamma, q, k, v, o, post_attention_ln_gamma, gate, up, down, embed_positions] in the
+    reference's order (:1096-1110). The linear weights are quantized tensors from remap_and_quantize_*; blocked
+    bf16 weights are quantized here when USE_MXFP4 / USE_QINT8 is set, as the reference's constructor does
+    (:1122-1161)."""
+
+    def __init__(self, params, layer_idx, eps, H, max_positions, rotary_dim):
+        import os
+        from . import _qtype
+        if len(params) != 10:
+            raise _lib.TpxError("LlamaDecoderLayer expects 10 parameters")
+        self.Gi, Wq, Wk, Wv, Wp, self.Gpa, Wg, Wu, Wd, self.EP = params
+        ws = [Wq, Wk, Wv, Wp, Wg, Wu, Wd]
+        if not all(isinstance(w, _qtype.QTensor) for w in ws):
+            if os.environ.get("USE_MXFP4", "0") == "1":
+                ws = [w if isinstance(w, _qtype.QTensor) else _qtype.remap_and_quantize_mxfp4(w) for w in ws]
+            elif os.environ.get("USE_QINT8", "0") == "1":
+                ws = [w if isinstance(w, _qtype.QTensor) else _qtype.remap_and_quantize_qint8(w) for w in ws]
+            else:
+                raise _lib.TpxError("LlamaDecoderLayer: unquantized weights are not built on this path; pass "
+                                    "weight_dtype='mxfp4' or 'qint8' (or set USE_MXFP4=1 / USE_QINT8=1)")
+        Wq, Wk, Wv, self.Wp, self.Wg, self.Wu, self.Wd = ws
+        self.layer_idx, self.eps, self.H = int(layer_idx), float(eps), int(H)
+        self.max_positions, self.rotary_dim = int(max_positions), int(rotary_dim)
+        self.Nq = Wq.out_features // self.H
+        self.Nkv = Wk.out_features // self.H
+        self.Wqkv = _cat_q([Wq, Wk, Wv])
+        if self.EP.dtype != torch.float32 or tuple(self.EP.shape[:1]) != (2,):
+            raise _lib.TpxError("embed_positions must be fp32 [2, max_positions, rotary_dim]")
+        self.EP = self.EP.contiguous()
+        for w in (self.Wqkv, self.Wp, self.Wd):
+            w.prepare()
+        self.Wg.prepare(pair_with=self.Wu)
+
+    def forward(self, inp, cache, use_cache=True):
+        """inp = [hidden_states [B,S,D] bf16, additive mask [B,Spad], position_ids int64 [1 or B, S]]
+        (LLMBlock::forward_common / _forward, :531-561, :1195-1286)."""
+        from ._tpp_attn import attention
+        hs, am, pos = inp[0], inp[1], inp[2]
+        _lib.require_cuda(hs, "hidden_states")
+        B, S, D = hs.shape
+        ws = get_pg_size()
+        scale = 1.0 / ws
+        L = _lib.lib()
+        res = hs.reshape(B * S, D)
+        x = rms_norm(res, self.Gi, self.eps)
+        qkv = fc_plain(x, self.Wqkv)
+        lc = cache.layer(self.layer_idx)
+        lc.ensure(B, self.Nkv, self.H, S, hs.dtype, hs.device)
+        R = self.Nq // self.Nkv
+        q = torch.empty((B, self.Nkv, S, R, self.H), dtype=hs.dtype, device=hs.device)
+        pos = pos.to(torch.int64).contiguous()
+        _lib.check(L.tpx_rope_kv_update(qkv.data_ptr(), self.EP.data_ptr(), pos.data_ptr(), B, S, self.Nq, self.Nkv, self.H,
+                                        self.EP.shape[1], self.EP.shape[2], pos.shape[0], lc.offset, lc.capacity(),
+                                        q.data_ptr(), lc.k.data_ptr(), lc.v.data_ptr(), _lib.stream()))
+        lc.offset += S
+        ctx = attention(q, lc.k, lc.v, am, lc.offset, causal=True, out_bsnrh=True).view(B * S, self.Nq * self.H)
+        so = fc_plain_act(ctx, self.Wp, res=res, res_scale=scale)
+        if ws > 1:
+            allreduce(so)
+        x2 = rms_norm(so, self.Gpa, self.eps)
+        inter = fc_gate_up(x2, self.Wg, self.Wu, "silu")
+        out = fc_plain_act(inter, self.Wd, res=so, res_scale=scale)
+        if ws > 1:
+            allreduce(out)
+        out = out.view(B, S, D)
+        if use_cache:
+            return [out, lc.k, lc.v]
+        return [out]

@@ -33,6 +33,11 @@ _SIGS = {
     "tpx_qlinear_mxfp4_tc": (c_int, [c_vp, c_vp, c_int, c_vp, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp, c_f32, c_vp,
                                      c_vp, c_sz, c_vp]),
     "tpx_debug_tc_timeline": (None, [c_vp]),
+    "tpx_rmsnorm": (c_int, [c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_vp, c_vp]),
+    "tpx_rope_kv_update": (c_int, [c_vp, c_vp, c_vp] + [c_i64] * 10 + [c_vp, c_vp, c_vp, c_vp]),
+    "tpx_attention_scratch_bytes": (c_sz, [c_i64] * 6),
+    "tpx_attention": (c_int, [c_vp, c_vp, c_vp, c_vp] + [c_i64] * 7 + [c_int, c_int, c_vp, c_vp, c_sz, c_vp]),
+    "tpx_align_and_invert_mask": (c_int, [c_vp, c_i64, c_i64, c_i64, ctypes.c_uint16, c_vp, c_vp]),
     "tpx_qlinear": (c_int, [c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp,
                             c_f32, c_vp, c_vp, c_sz, c_vp]),
 }
@@ -91,4 +96,17 @@ def scratch(nbytes, device):
     if buf is None or buf.numel() < nbytes:
         buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _scratch[key] = buf
+    return buf
+
+
+_aux = {}
+
+
+def aux_scratch(nbytes, device):
+    """Scratch with no zero-initialisation contract (attention partials), separate from the linear's."""
+    key = (device.index, stream())
+    buf = _aux.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _aux[key] = buf
     return buf

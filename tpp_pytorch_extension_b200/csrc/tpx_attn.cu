@@ -1,0 +1,410 @@
+// RMSNorm, RoPE + KV-cache write, and attention over the blocked KV cache.
+//
+// Replaces, on the decoder-layer path of the reference:
+//   llama_rms_norm / RMSNormFwdTPP           src/csrc/llm/fused_llm_infer.cpp:336-363, src/csrc/xsmm_functors.h:4628-4654
+//   apply_rotary_pos_emb_llama               src/csrc/llm/fused_llm_infer.cpp:206-253
+//   LayerCache::update / KVLayout_BNSH       src/csrc/llm/attn.h:197-221, src/csrc/llm/attn.cpp:389-463
+//   attn<T>                                  src/csrc/llm/attn.cpp:780-955
+//
+// The KV cache keeps the reference's layout [S1][B][Nkv][32][H] (token t at block t/32, slot t%32): a block of
+// 32 tokens of one (batch, kv head) is 32*H contiguous elements, which is what the attention kernel streams.
+#include "tpx_common.cuh"
+
+namespace tpx {
+
+// ---------------------------------------------------------------- RMSNorm: one warp per row
+__global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const void* __restrict__ gamma, int gamma_f32, float eps,
+                               int64_t rows, int D, uint16_t* __restrict__ y) {
+  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+  float ss = 0.0f;
+  for (int i = lane; i < D / 8; i += 32) {
+    uint4 v = xr[i];
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      float a = bf16_bits_to_f32((uint16_t)(w[j] & 0xffff)), b = bf16_bits_to_f32((uint16_t)(w[j] >> 16));
+      ss += a * a + b * b;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float inv = rsqrtf(ss / (float)D + eps);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * D);
+  for (int i = lane; i < D / 8; i += 32) {
+    uint4 v = xr[i];
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      float g0, g1;
+      if (gamma_f32) {
+        g0 = reinterpret_cast<const float*>(gamma)[i * 8 + 2 * j];
+        g1 = reinterpret_cast<const float*>(gamma)[i * 8 + 2 * j + 1];
+      } else {
+        g0 = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(gamma)[i * 8 + 2 * j]);
+        g1 = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(gamma)[i * 8 + 2 * j + 1]);
+      }
+      float a = bf16_bits_to_f32((uint16_t)(w[j] & 0xffff)) * inv * g0;
+      float b = bf16_bits_to_f32((uint16_t)(w[j] >> 16)) * inv * g1;
+      o[j] = (uint32_t)f32_to_bf16_bits(a) | ((uint32_t)f32_to_bf16_bits(b) << 16);
+    }
+    yr[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ---------------------------------------------------------------- RoPE + KV-cache write
+// qkv: [B*S][(Nq + 2*Nkv)*H] bf16, the output of the fused q/k/v linear (q heads, then k heads, then v heads).
+// q is rotated and written as q_out[B][Nkv][S][R][H] (R = Nq/Nkv, the layout the reference hands to attention,
+// src/csrc/llm/fused_llm_infer.cpp:563-584); k is rotated and stored, v stored, at cache tokens offset .. offset+S-1.
+// One thread per (token, head, pair of rotary lanes).
+__global__ void rope_kv_kernel(const uint16_t* __restrict__ qkv, const float* __restrict__ ep, const int64_t* __restrict__ pos,
+                               int B, int S, int Nq, int Nkv, int H, int MP, int HR, int Bpos, int64_t offset,
+                               uint16_t* __restrict__ q_out, uint16_t* __restrict__ kc, uint16_t* __restrict__ vc) {
+  const int heads = Nq + 2 * Nkv;
+  const int half = H / 2;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)B * S * heads * half) return;
+  const int h2 = (int)(idx % half);
+  const int hd = (int)((idx / half) % heads);
+  const int s = (int)((idx / ((int64_t)half * heads)) % S);
+  const int b = (int)(idx / ((int64_t)half * heads * S));
+  const uint16_t* src = qkv + ((int64_t)(b * S + s) * heads + hd) * H;
+  uint16_t o0 = src[h2], o1 = src[h2 + half];
+  if (hd < Nq + Nkv) {  // q and k heads rotate: pair (h2, h2 + H/2)
+    const int64_t p = pos[(int64_t)(Bpos == 1 ? 0 : b) * S + s];
+    if (p < MP) {  // positions beyond the table are left untouched, as in the reference
+      const float x0 = bf16_bits_to_f32(o0), x1 = bf16_bits_to_f32(o1);
+      const float c = ep[(0 * (int64_t)MP + p) * HR + h2], sn = ep[(1 * (int64_t)MP + p) * HR + h2];
+      o0 = f32_to_bf16_bits(x0 * c - x1 * sn);
+      o1 = f32_to_bf16_bits(x1 * c + x0 * sn);
+    }
+  }
+  uint16_t* dst;
+  if (hd < Nq) {
+    const int R = Nq / Nkv, n = hd / R, r = hd % R;
+    dst = q_out + ((((int64_t)b * Nkv + n) * S + s) * R + r) * H;
+  } else {
+    const bool is_k = hd < Nq + Nkv;
+    const int n = is_k ? hd - Nq : hd - Nq - Nkv;
+    const int64_t t = offset + s;
+    dst = (is_k ? kc : vc) + ((((t / 32) * B + b) * Nkv + n) * 32 + (t % 32)) * H;
+  }
+  dst[h2] = o0;
+  dst[h2 + half] = o1;
+}
+
+// ---------------------------------------------------------------- attention
+// Up to 16 query rows (consecutive (query position, group member) pairs of one (batch, kv head)) per CTA against
+// a range of KV blocks. 4 warps split the blocks of the range; each keeps a running (max, sum, fp32 output) per
+// row, merged through shared memory at the end. With more than one KV split the CTA writes an un-normalised
+// partial (max, sum, output) and a second kernel merges the splits (flash-decoding).
+constexpr int kAttnWarps = 4;
+constexpr int kAttnRows = 16;
+
+struct AttnParams {
+  const uint16_t* q;    // [B][Nkv][Sq][R][H]
+  const uint16_t* kc;   // [S1][B][Nkv][32][H]
+  const uint16_t* vc;
+  const uint16_t* am;   // [B][Spad] additive mask or null
+  uint16_t* out;        // same shape as q
+  float* part;          // [B*Nkv][chunks][splits][16][H + 2]
+  int B, Nkv, Sq, R, H;
+  int key_len, Spad, causal;
+  int chunks, splits;
+  int out_bsnrh;        // 0: out laid out like q; 1: out[B][Sq][Nkv][R][H] (rows of the following linear)
+  float scale;
+};
+
+__device__ __forceinline__ int64_t attn_out_index(const AttnParams& p, int bn, int row, int H) {
+  if (!p.out_bsnrh) return ((int64_t)bn * p.Sq * p.R + row) * H;
+  const int b = bn / p.Nkv, n = bn % p.Nkv, sq = row / p.R, r = row % p.R;
+  return ((((int64_t)b * p.Sq + sq) * p.Nkv + n) * p.R + r) * H;
+}
+
+template <int H>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(AttnParams p) {
+  constexpr int HV = H / 32;  // output dims per lane
+  __shared__ float qs[kAttnRows][H];
+  __shared__ float ps[kAttnWarps][kAttnRows][32];
+  __shared__ float red_m[kAttnWarps][kAttnRows], red_l[kAttnWarps][kAttnRows];
+  __shared__ float red_o[kAttnWarps][kAttnRows / 2][H];
+
+  const int bn = blockIdx.x, chunk = blockIdx.y, split = blockIdx.z;
+  const int b = bn / p.Nkv, n = bn % p.Nkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows_total = p.Sq * p.R;
+  const int row0 = chunk * kAttnRows;
+  const int rows = min(kAttnRows, rows_total - row0);
+  const int offset = p.key_len - p.Sq;
+
+  // queries of this chunk to shared memory as fp32, pre-multiplied by 1/sqrt(H)
+  const uint16_t* qbase = p.q + ((int64_t)bn * rows_total + row0) * H;
+  for (int i = threadIdx.x; i < kAttnRows * H; i += blockDim.x) {
+    int r = i / H;
+    qs[r][i % H] = r < rows ? bf16_bits_to_f32(qbase[i]) * p.scale : 0.0f;
+  }
+  __syncthreads();
+
+  // keys this chunk can see at all: up to the last row's causal limit
+  const int last_sq = (row0 + rows - 1) / p.R;
+  const int kmax = p.causal ? min(p.key_len, offset + last_sq + 1) : p.key_len;
+  const int nblocks = (kmax + 31) / 32;
+  const int per_split = (nblocks + p.splits - 1) / p.splits;
+  const int blk0 = split * per_split, blk1 = min(nblocks, blk0 + per_split);
+
+  float m[kAttnRows], l[kAttnRows], acc[kAttnRows][HV];
+#pragma unroll
+  for (int r = 0; r < kAttnRows; r++) {
+    m[r] = -INFINITY;
+    l[r] = 0.0f;
+#pragma unroll
+    for (int j = 0; j < HV; j++) acc[r][j] = 0.0f;
+  }
+
+  for (int blk = blk0 + warp; blk < blk1; blk += kAttnWarps) {
+    const int tok = blk * 32 + lane;
+    const int64_t boff = ((((int64_t)blk * p.B + b) * p.Nkv + n) * 32) * H;
+    // phase A: lane = token; scores of all rows against this lane's key
+    float kreg[H];
+    {
+      const uint4* kr = reinterpret_cast<const uint4*>(p.kc + boff + (int64_t)lane * H);
+#pragma unroll
+      for (int i = 0; i < H / 8; i++) {
+        uint4 v = kr[i];
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          kreg[i * 8 + 2 * j] = bf16_bits_to_f32((uint16_t)(w[j] & 0xffff));
+          kreg[i * 8 + 2 * j + 1] = bf16_bits_to_f32((uint16_t)(w[j] >> 16));
+        }
+      }
+    }
+    const float madd = (p.am && tok < p.Spad) ? bf16_bits_to_f32(p.am[(int64_t)b * p.Spad + tok]) : 0.0f;
+    float alpha[kAttnRows];
+#pragma unroll
+    for (int r = 0; r < kAttnRows; r++) {
+      alpha[r] = 1.0f;
+      if (r < rows) {
+        float s = 0.0f;
+        const float4* qr = reinterpret_cast<const float4*>(qs[r]);
+#pragma unroll
+        for (int i = 0; i < H / 4; i++) {
+          float4 qv = qr[i];
+          s += qv.x * kreg[4 * i] + qv.y * kreg[4 * i + 1] + qv.z * kreg[4 * i + 2] + qv.w * kreg[4 * i + 3];
+        }
+        s += madd;
+        const int sq = (row0 + r) / p.R;
+        const bool visible = tok < p.key_len && (!p.causal || tok <= offset + sq);
+        if (!visible) s = -INFINITY;
+        float bm = s;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+        const float mn = fmaxf(m[r], bm);
+        const float pe = (mn == -INFINITY) ? 0.0f : __expf(s - mn);
+        float bs = pe;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o);
+        alpha[r] = (mn == -INFINITY) ? 1.0f : __expf(m[r] - mn);
+        l[r] = l[r] * alpha[r] + bs;
+        m[r] = mn;
+        ps[warp][r][lane] = pe;
+      }
+    }
+    __syncwarp();
+    // phase B: lane = output dims; out[r] = out[r]*alpha + sum_tok p[r][tok] * V[tok]
+#pragma unroll
+    for (int r = 0; r < kAttnRows; r++)
+#pragma unroll
+      for (int j = 0; j < HV; j++) acc[r][j] *= alpha[r];
+    const int ntok = min(32, p.key_len - blk * 32);
+    for (int t = 0; t < ntok; t++) {
+      float vv[HV];
+      const uint16_t* vr = p.vc + boff + (int64_t)t * H + lane * HV;
+      if (HV == 4) {
+        uint2 v = *reinterpret_cast<const uint2*>(vr);
+        vv[0] = bf16_bits_to_f32((uint16_t)(v.x & 0xffff));
+        vv[1] = bf16_bits_to_f32((uint16_t)(v.x >> 16));
+        vv[2] = bf16_bits_to_f32((uint16_t)(v.y & 0xffff));
+        vv[3] = bf16_bits_to_f32((uint16_t)(v.y >> 16));
+      } else {
+#pragma unroll
+        for (int j = 0; j < HV; j++) vv[j] = bf16_bits_to_f32(vr[j]);
+      }
+#pragma unroll
+      for (int r = 0; r < kAttnRows; r++) {
+        if (r < rows) {
+          const float pr = ps[warp][r][t];
+#pragma unroll
+          for (int j = 0; j < HV; j++) acc[r][j] = fmaf(pr, vv[j], acc[r][j]);
+        }
+      }
+    }
+    __syncwarp();
+  }
+
+  // merge the warps of this CTA, eight rows at a time (shared-memory budget)
+  for (int r = 0; r < kAttnRows; r++)
+    if (lane == 0) { red_m[warp][r] = m[r]; red_l[warp][r] = l[r]; }
+#pragma unroll
+  for (int half = 0; half < 2; half++) {
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < kAttnRows / 2; r++)
+#pragma unroll
+      for (int j = 0; j < HV; j++) red_o[warp][r][lane * HV + j] = acc[half * (kAttnRows / 2) + r][j];
+    __syncthreads();
+    for (int i = threadIdx.x; i < (kAttnRows / 2) * H; i += blockDim.x) {
+      const int rr = i / H, h = i % H, r = half * (kAttnRows / 2) + rr;
+      if (r >= rows) continue;
+      float mm = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kAttnWarps; w++) mm = fmaxf(mm, red_m[w][r]);
+      float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kAttnWarps; w++) {
+        const float f = (red_m[w][r] == -INFINITY) ? 0.0f : __expf(red_m[w][r] - mm);
+        ll += red_l[w][r] * f;
+        oo += red_o[w][rr][h] * f;
+      }
+      if (p.splits == 1) {
+        p.out[attn_out_index(p, bn, row0 + r, H) + h] = f32_to_bf16_bits(oo / ll);
+      } else {
+        float* dst = p.part + ((((int64_t)bn * p.chunks + chunk) * p.splits + split) * kAttnRows + r) * (H + 2);
+        dst[h] = oo;
+        if (h == 0) { dst[H] = mm; dst[H + 1] = ll; }
+      }
+    }
+  }
+}
+
+template <int H>
+__global__ void attn_merge_kernel(AttnParams p) {
+  const int bn = blockIdx.x, chunk = blockIdx.y;
+  const int rows_total = p.Sq * p.R;
+  const int row0 = chunk * kAttnRows;
+  const int rows = min(kAttnRows, rows_total - row0);
+  for (int i = threadIdx.x; i < rows * H; i += blockDim.x) {
+    const int r = i / H, h = i % H;
+    const float* base = p.part + (((int64_t)bn * p.chunks + chunk) * p.splits * kAttnRows + r) * (H + 2);
+    float mm = -INFINITY;
+    for (int s = 0; s < p.splits; s++) mm = fmaxf(mm, base[(int64_t)s * kAttnRows * (H + 2) + H]);
+    float ll = 0.0f, oo = 0.0f;
+    for (int s = 0; s < p.splits; s++) {
+      const float* ps = base + (int64_t)s * kAttnRows * (H + 2);
+      const float f = (ps[H] == -INFINITY) ? 0.0f : __expf(ps[H] - mm);
+      ll += ps[H + 1] * f;
+      oo += ps[h] * f;
+    }
+    p.out[attn_out_index(p, bn, row0 + r, H) + h] = f32_to_bf16_bits(oo / ll);
+  }
+}
+
+// ---------------------------------------------------------------- mask helper
+// TppCache::align_and_invert_mask (src/csrc/llm/attn.h:310-322): [B][S] of 0/1 -> [B][Spad] additive, padding masked.
+__global__ void invert_mask_kernel(const uint16_t* __restrict__ mask, int B, int S, int Spad, uint16_t minval,
+                                   uint16_t* __restrict__ out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)B * Spad) return;
+  int s = (int)(idx % Spad), b = (int)(idx / Spad);
+  uint16_t v = minval;
+  if (s < S && bf16_bits_to_f32(mask[(int64_t)b * S + s]) > 0.0f) v = 0;
+  out[idx] = v;
+}
+
+}  // namespace tpx
+
+using namespace tpx;
+
+extern "C" int tpx_rmsnorm(const uint16_t* x, const void* gamma, int gamma_is_f32, float eps, int64_t rows, int64_t D,
+                           uint16_t* y, void* stream) {
+  TPX_REQUIRE(x && gamma && y, TPX_ERR_ARG, "rmsnorm: null pointer");
+  TPX_REQUIRE(rows >= 0 && D > 0 && D % 8 == 0, TPX_ERR_ARG, "rmsnorm: D must be a positive multiple of 8 (D=%ld)", (long)D);
+  if (rows == 0) return TPX_OK;
+  rmsnorm_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, (cudaStream_t)stream>>>(x, gamma, gamma_is_f32, eps, rows, (int)D, y);
+  TPX_LAUNCH_OK();
+  return TPX_OK;
+}
+
+extern "C" int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const int64_t* pos, int64_t B, int64_t S, int64_t Nq,
+                                  int64_t Nkv, int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset,
+                                  int64_t capacity, uint16_t* q_out, uint16_t* kc, uint16_t* vc, void* stream) {
+  TPX_REQUIRE(qkv && ep && pos && q_out && kc && vc, TPX_ERR_ARG, "rope_kv_update: null pointer");
+  TPX_REQUIRE(B > 0 && S >= 0 && Nq > 0 && Nkv > 0 && Nq % Nkv == 0 && H % 2 == 0, TPX_ERR_ARG,
+              "rope_kv_update: bad shape");
+  TPX_REQUIRE(HR == H, TPX_ERR_UNSUPPORTED, "rope_kv_update: rotary width %ld != head dim %ld (partial rotary is not built)", (long)HR, (long)H);
+  TPX_REQUIRE(Bpos == 1 || Bpos == B, TPX_ERR_ARG, "position_ids shape not compatible");
+  TPX_REQUIRE(offset >= 0 && offset + S <= capacity, TPX_ERR_ARG, "rope_kv_update: cache capacity %ld is short of %ld tokens",
+              (long)capacity, (long)(offset + S));
+  if (S == 0) return TPX_OK;
+  int64_t total = B * S * (Nq + 2 * Nkv) * (H / 2);
+  rope_kv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(qkv, ep, pos, (int)B, (int)S, (int)Nq, (int)Nkv,
+                                                                                  (int)H, (int)MP, (int)HR, (int)Bpos, offset, q_out, kc, vc);
+  TPX_LAUNCH_OK();
+  return TPX_OK;
+}
+
+static int attn_plan(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t key_len, int* chunks, int* splits) {
+  *chunks = (int)((Sq * R + kAttnRows - 1) / kAttnRows);
+  int64_t ctas = B * Nkv * *chunks;
+  int nblocks = (int)((key_len + 31) / 32);
+  int s = 1;
+  int sms = sm_count();
+  // split the KV range while the grid is short of two CTAs per SM and every split keeps >= 8 blocks per warp round
+  while (ctas * s < 2 * sms && nblocks / (s * 2) >= kAttnWarps * 2 && s < 64) s *= 2;
+  *splits = s;
+  return 0;
+}
+
+extern "C" size_t tpx_attention_scratch_bytes(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len) {
+  int chunks, splits;
+  attn_plan(B, Nkv, Sq, R, key_len, &chunks, &splits);
+  if (splits == 1) return 0;
+  return (size_t)B * Nkv * chunks * splits * kAttnRows * (H + 2) * sizeof(float);
+}
+
+extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, const uint16_t* am, int64_t B,
+                             int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len, int64_t Spad, int causal,
+                             int out_bsnrh, uint16_t* out, void* scratch, size_t scratch_bytes, void* stream) {
+  TPX_REQUIRE(q && kc && vc && out, TPX_ERR_ARG, "attention: null pointer");
+  TPX_REQUIRE(B > 0 && Nkv > 0 && Sq >= 0 && R > 0 && key_len >= Sq, TPX_ERR_ARG, "attention: bad shape");
+  TPX_REQUIRE(H == 64 || H == 128, TPX_ERR_UNSUPPORTED, "attention: head dim %ld not supported (64 or 128)", (long)H);
+  TPX_REQUIRE(!am || Spad >= key_len, TPX_ERR_ARG, "attention: mask of %ld keys is shorter than the cache (%ld)", (long)Spad, (long)key_len);
+  if (Sq == 0) return TPX_OK;
+  AttnParams p;
+  p.q = q; p.kc = kc; p.vc = vc; p.am = am; p.out = out; p.part = reinterpret_cast<float*>(scratch);
+  p.B = (int)B; p.Nkv = (int)Nkv; p.Sq = (int)Sq; p.R = (int)R; p.H = (int)H;
+  p.key_len = (int)key_len; p.Spad = (int)Spad; p.causal = causal; p.out_bsnrh = out_bsnrh;
+  attn_plan(B, Nkv, Sq, R, key_len, &p.chunks, &p.splits);
+  p.scale = 1.0f / sqrtf((float)H);
+  if (p.splits > 1) {
+    size_t need = tpx_attention_scratch_bytes(B, Nkv, Sq, R, H, key_len);
+    TPX_REQUIRE(scratch && scratch_bytes >= need, TPX_ERR_SCRATCH, "attention: scratch of %zu bytes needed, %zu given", need, scratch_bytes);
+  }
+  dim3 grid((unsigned)(B * Nkv), (unsigned)p.chunks, (unsigned)p.splits);
+  TPX_REQUIRE(p.chunks <= 65535, TPX_ERR_UNSUPPORTED, "attention: too many query rows in one call");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (H == 128) attn_kernel<128><<<grid, kAttnWarps * 32, 0, st>>>(p);
+  else attn_kernel<64><<<grid, kAttnWarps * 32, 0, st>>>(p);
+  TPX_LAUNCH_OK();
+  if (p.splits > 1) {
+    dim3 g2((unsigned)(B * Nkv), (unsigned)p.chunks);
+    if (H == 128) attn_merge_kernel<128><<<g2, 256, 0, st>>>(p);
+    else attn_merge_kernel<64><<<g2, 256, 0, st>>>(p);
+    TPX_LAUNCH_OK();
+  }
+  return TPX_OK;
+}
+
+extern "C" int tpx_align_and_invert_mask(const uint16_t* mask, int64_t B, int64_t S, int64_t Spad, uint16_t min_bits,
+                                         uint16_t* out, void* stream) {
+  TPX_REQUIRE(mask && out, TPX_ERR_ARG, "align_and_invert_mask: null pointer");
+  TPX_REQUIRE(Spad >= S && Spad % 32 == 0, TPX_ERR_ARG, "align_and_invert_mask: padded length must be a multiple of 32 >= S");
+  int64_t total = B * Spad;
+  if (total == 0) return TPX_OK;
+  invert_mask_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(mask, (int)B, (int)S, (int)Spad, min_bits, out);
+  TPX_LAUNCH_OK();
+  return TPX_OK;
+}

@@ -1,0 +1,190 @@
+"""Llama on the fused decoder layers, mirroring src/tpp_pytorch_extension/llm/fused_llama_infer.py.
+
+`OptimizeModelForLlama(model, dtype, device, weight_dtype)` keeps the reference's entry point: it takes a
+Hugging Face LlamaForCausalLM, shards (tensor parallel), blocks and quantizes its linears exactly as
+FixLlamaDecoderLayer does (fused_llama_infer.py:104-172), and returns a runner whose forward walks the fused
+layers (the patched LlamaModel.forward of the reference, :236-335). `build_random_llama` builds the same runner
+from a config alone, layer by layer on the GPU, for the random-weight benchmark configurations."""
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .._C import _fused_llm_infer as fused_llm_cpp
+from . import llm_common
+from .llm_common import TppCache, get_rank, get_size, quantize_weight, shard_offsets
+
+
+@dataclass
+class LlamaShape:
+    num_hidden_layers: int
+    hidden_size: int
+    num_attention_heads: int
+    num_key_value_heads: int
+    intermediate_size: int
+    vocab_size: int
+    head_dim: int = 0
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 1e4
+    max_position_embeddings: int = 4096
+
+    def __post_init__(self):
+        if not self.head_dim:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+
+
+def rope_table(max_pos, head_dim, theta, device):
+    """cat(cos, sin).view(2, MP, head_dim) in fp32, from HF's default rotary embedding
+    (fused_llama_infer.py:186-204): inv_freq = theta^(-2i/d), emb = cat(freqs, freqs)."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    fr = torch.outer(torch.arange(max_pos, dtype=torch.float32), inv)
+    emb = torch.cat([fr, fr], dim=-1)
+    return torch.stack([emb.cos(), emb.sin()]).to(device).contiguous()
+
+
+def _shard(w, dim, block):
+    """This rank's slice of a weight (ShardLinear, llm_common.py:517-546)."""
+    size, rank = get_size(), get_rank()
+    if size == 1:
+        return w
+    offs = shard_offsets(w.shape[dim], size, block)
+    return (w[offs[rank]:offs[rank + 1], :] if dim == 0 else w[:, offs[rank]:offs[rank + 1]]).contiguous()
+
+
+def make_layer(shape, weights, layer_idx, ep, weight_dtype, device):
+    """weights: dict of plain [N, K] tensors q,k,v,o,gate,up,down and norm vectors ln1, ln2.
+    Sharding units follow FixLlamaDecoderLayer (fused_llama_infer.py:119-129): q and o by head_dim * kv groups,
+    k and v by head_dim, the MLP by 64."""
+    H = shape.head_dim
+    grp = H * (shape.num_attention_heads // shape.num_key_value_heads)
+    plan = {"q": (0, grp), "k": (0, H), "v": (0, H), "o": (1, grp), "gate": (0, 64), "up": (0, 64), "down": (1, 64)}
+    qs = {}
+    for name, (dim, blk) in plan.items():
+        w = _shard(weights[name].to(device), dim, blk)
+        qs[name] = quantize_weight(w, weight_dtype)
+    params = [weights["ln1"].to(device, torch.bfloat16), qs["q"], qs["k"], qs["v"], qs["o"],
+              weights["ln2"].to(device, torch.bfloat16), qs["gate"], qs["up"], qs["down"], ep]
+    layer = fused_llm_cpp.LlamaDecoderLayer(params, layer_idx, shape.rms_norm_eps, H, ep.shape[1], H)
+    # the interchange tensors are no longer needed once the streaming layouts exist
+    for w in (layer.Wqkv, layer.Wp, layer.Wd, layer.Wg, layer.Wu):
+        w.codes = w.codes.new_empty(0)
+    return layer
+
+
+class LlamaRunner(torch.nn.Module):
+    def __init__(self, shape, embed, layers, norm_w, lm_head_w, ep):
+        super().__init__()
+        self.shape, self.embed, self.layers, self.norm_w, self.ep = shape, embed, layers, norm_w, ep
+        # lm_head stays bf16 as in the reference unless it is quantized separately; with tensor parallelism it is
+        # row-parallel followed by an all-reduce (fused_llama_infer.py:218-224)
+        self.lm_head_w = lm_head_w
+        self.lm_split = [lm_head_w.shape[1]] if get_size() == 1 else None
+        self.only_last_logit = True
+
+    @torch.no_grad()
+    def forward(self, input_ids, attention_mask=None, position_ids=None, cache=None):
+        """Patched LlamaModel.forward + LlamaForCausalLM.forward of the reference (fused_llama_infer.py:236-408)."""
+        if cache is None:
+            cache = TppCache()
+        B, S = input_ids.shape
+        hs = torch.nn.functional.embedding(input_ids, self.embed)
+        past = cache.get_seq_length()
+        if position_ids is None:
+            position_ids = torch.arange(past, past + S, device=input_ids.device).unsqueeze(0)
+        if attention_mask is None:
+            attention_mask = torch.ones((B, past + S), device=input_ids.device, dtype=hs.dtype)
+        am = cache.align_and_invert_mask(attention_mask, hs)
+        cpp = cache.get_cpp()
+        for layer in self.layers:
+            hs = layer.forward([hs, am, position_ids], cpp, True)[0]
+        if self.only_last_logit:
+            hs = hs[:, -1:, :]
+        hs = fused_llm_cpp.rms_norm(hs.contiguous(), self.norm_w, self.shape.rms_norm_eps)
+        if get_size() > 1:
+            offs = shard_offsets(self.shape.hidden_size, get_size(), 64)
+            r = get_rank()
+            logits = torch.nn.functional.linear(hs[..., offs[r]:offs[r + 1]], self.lm_head_w)
+            fused_llm_cpp.allreduce(logits)
+        else:
+            logits = torch.nn.functional.linear(hs, self.lm_head_w)
+        return logits, cache
+
+    @torch.no_grad()
+    def generate(self, input_ids, max_new_tokens, attention_mask=None):
+        """Greedy decoding (the reference drives HF generate with --greedy, examples/llm/run_generation.py:337-339)."""
+        cache = TppCache()
+        B = input_ids.shape[0]
+        mask = attention_mask if attention_mask is not None else torch.ones_like(input_ids)
+        logits, cache = self.forward(input_ids, mask, None, cache)
+        out = [input_ids]
+        nxt = logits[:, -1].argmax(-1, keepdim=True)
+        for _ in range(max_new_tokens - 1):
+            out.append(nxt)
+            mask = torch.cat([mask, mask.new_ones((B, 1))], dim=1)
+            pos = (mask.sum(-1, keepdim=True) - 1) if attention_mask is not None else None
+            logits, cache = self.forward(nxt, mask, pos, cache)
+            nxt = logits[:, -1].argmax(-1, keepdim=True)
+        out.append(nxt)
+        return torch.cat(out, dim=1)
+
+
+def _lm_head_shard(w):
+    if get_size() == 1:
+        return w
+    offs = shard_offsets(w.shape[1], get_size(), 64)
+    r = get_rank()
+    return w[:, offs[r]:offs[r + 1]].contiguous()
+
+
+def build_random_llama(shape, weight_dtype="mxfp4", device="cuda", seed=0, std=0.02, max_positions=None):
+    """Random N(0, std) linears and embeddings, unit norm weights, quantized layer by layer on the device.
+    Every tensor-parallel rank draws the same full weights (same seed) and keeps its shard."""
+    llm_common.set_pg()
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    MP = max_positions or shape.max_position_embeddings
+    ep = rope_table(MP, shape.head_dim, shape.rope_theta, dev)
+    D, H = shape.hidden_size, shape.head_dim
+    Nq, Nkv, FF = shape.num_attention_heads, shape.num_key_value_heads, shape.intermediate_size
+
+    def rnd(n, k):
+        return (torch.randn(n, k, generator=g, device=dev) * std).to(torch.bfloat16)
+
+    embed = rnd(shape.vocab_size, D)
+    layers = []
+    for i in range(shape.num_hidden_layers):
+        w = {"q": rnd(Nq * H, D), "k": rnd(Nkv * H, D), "v": rnd(Nkv * H, D), "o": rnd(D, Nq * H), "gate": rnd(FF, D),
+             "up": rnd(FF, D), "down": rnd(D, FF), "ln1": torch.ones(D), "ln2": torch.ones(D)}
+        layers.append(make_layer(shape, w, i, ep, weight_dtype, dev))
+        del w
+    lm = _lm_head_shard(rnd(shape.vocab_size, D))
+    return LlamaRunner(shape, embed, layers, torch.ones(D, device=dev, dtype=torch.bfloat16), lm, ep)
+
+
+def OptimizeModelForLlama(model, dtype=torch.bfloat16, device="cuda", weight_dtype="mxfp4"):
+    """Reference entry point (fused_llama_infer.py:176-233) for a Hugging Face LlamaForCausalLM."""
+    if dtype != torch.bfloat16:
+        raise ValueError("the CUDA path computes in bfloat16")
+    llm_common.set_pg()
+    cfg = model.config
+    shape = LlamaShape(cfg.num_hidden_layers, cfg.hidden_size, cfg.num_attention_heads,
+                       getattr(cfg, "num_key_value_heads", cfg.num_attention_heads), cfg.intermediate_size, cfg.vocab_size,
+                       getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads, cfg.rms_norm_eps,
+                       getattr(cfg, "rope_theta", None) or (getattr(cfg, "rope_parameters", None) or {}).get("rope_theta", 1e4),
+                       cfg.max_position_embeddings)
+    dev = torch.device(device)
+    ep = rope_table(shape.max_position_embeddings, shape.head_dim, shape.rope_theta, dev)
+    layers = []
+    for i, l in enumerate(model.model.layers):
+        w = {"q": l.self_attn.q_proj.weight.data, "k": l.self_attn.k_proj.weight.data, "v": l.self_attn.v_proj.weight.data,
+             "o": l.self_attn.o_proj.weight.data, "gate": l.mlp.gate_proj.weight.data, "up": l.mlp.up_proj.weight.data,
+             "down": l.mlp.down_proj.weight.data, "ln1": l.input_layernorm.weight.data, "ln2": l.post_attention_layernorm.weight.data}
+        layers.append(make_layer(shape, w, i, ep, weight_dtype, dev))
+    embed = model.model.embed_tokens.weight.data.to(dev, torch.bfloat16)
+    lm = _lm_head_shard(model.lm_head.weight.data.to(dev, torch.bfloat16))
+    return LlamaRunner(shape, embed, layers, model.model.norm.weight.data.to(dev, torch.bfloat16), lm, ep)
+
+
+LLAMA2_7B = LlamaShape(32, 4096, 32, 32, 11008, 32000, rms_norm_eps=1e-5, rope_theta=1e4)
+LLAMA3_8B = LlamaShape(32, 4096, 32, 8, 14336, 128256, rms_norm_eps=1e-5, rope_theta=5e5, max_position_embeddings=8192)
+LLAMA2_70B = LlamaShape(80, 8192, 64, 8, 28672, 32000, rms_norm_eps=1e-5, rope_theta=1e4, max_position_embeddings=8192)

@@ -1,0 +1,161 @@
+"""Host-side common pieces of the LLM path, mirroring src/tpp_pytorch_extension/llm/llm_common.py:
+the cache wrapper, the blocked/quantized linear, tensor-parallel sharding and the process-group plumbing."""
+import torch
+
+from .._C import _fused_llm_infer as fused_llm_cpp
+from .._C import _qtype as qtype
+from .._C._tpp_attn import TppCache as _CppCache
+from ..utils.blocked_layout import block_weight
+
+tensor_parallel_enabled = True
+
+
+class TppCache:
+    """llm_common.TppCache (llm_common.py:80-181): the object the model forward carries."""
+
+    def __init__(self, **kwargs):
+        self.tpp_cache = _CppCache()
+
+    def __len__(self):
+        return self.tpp_cache.size()
+
+    def update(self, key_states, value_states, layer_idx, cache_kwargs=None):
+        return self.tpp_cache.update(key_states, value_states, layer_idx)
+
+    def get_seq_length(self, layer_idx=0):
+        return self.tpp_cache.get_seq_length(layer_idx)
+
+    def get_max_length(self):
+        return None
+
+    def crop(self, max_length):
+        seq_len = self.get_seq_length()
+        if max_length < 0:
+            max_length = seq_len - abs(max_length)
+        if seq_len <= max_length:
+            return
+        self.tpp_cache.crop(max_length)
+
+    def align_and_invert_mask(self, mask, inputs_embeds):
+        if mask is None:
+            mask = torch.ones((inputs_embeds.shape[0], inputs_embeds.shape[1]), device=inputs_embeds.device, dtype=inputs_embeds.dtype)
+        return self.tpp_cache.align_and_invert_mask(mask.to(inputs_embeds.dtype), torch.finfo(inputs_embeds.dtype).min)
+
+    def reorder_cache(self, beam_idx):
+        self.tpp_cache.reorder_cache(beam_idx.to(torch.long))
+
+    def get_cpp(self):
+        return self.tpp_cache
+
+
+def get_rank():
+    if not tensor_parallel_enabled:
+        return 0
+    if torch.distributed.is_available() and torch.distributed.is_initialized():
+        return torch.distributed.get_rank()
+    return 0
+
+
+def get_size():
+    if not tensor_parallel_enabled:
+        return 1
+    if torch.distributed.is_available() and torch.distributed.is_initialized():
+        return torch.distributed.get_world_size()
+    return 1
+
+
+def set_pg():
+    """llm_common.set_pg (llm_common.py:574-578)."""
+    if not tensor_parallel_enabled:
+        return
+    if torch.distributed.is_available() and torch.distributed.is_initialized():
+        fused_llm_cpp.set_pg(torch.distributed.distributed_c10d._get_default_group())
+
+
+def shard_offsets(dim_size, size, block_size=1):
+    """Split points of ShardLinear (llm_common.py:517-531): contiguous slices in units of block_size,
+    boundary i at ((num_blocks * i) // size) * block_size, so uneven splits are allowed."""
+    assert dim_size % block_size == 0, f"dim_size ({dim_size}) is not multiple of block_size ({block_size})"
+    nb = dim_size // block_size
+    return [0] + [((nb * (i + 1)) // size) * block_size for i in range(size)]
+
+
+def ShardLinear(m, dim, rank, size, block_size=1):
+    """dim 0 shards output features, dim 1 input features; a row-parallel bias is divided by size
+    (llm_common.py:517-546)."""
+    offs = shard_offsets(m.weight.shape[dim], size, block_size)
+    start, end = offs[rank], offs[rank + 1]
+    m.split_sizes = [offs[i + 1] - offs[i] for i in range(size)]
+    if dim == 0:
+        m.weight.data = m.weight.data[start:end, :].contiguous()
+    else:
+        m.weight.data = m.weight.data[:, start:end].contiguous()
+    if m.bias is not None:
+        if dim == 0:
+            m.bias.data = m.bias.data[start:end].contiguous()
+        else:
+            m.bias.data = m.bias.data / size
+
+
+def quantize_weight(w, weight_dtype, bk=16, bc=64):
+    """What FixLinear does to one nn.Linear weight (llm_common.py:437-510): block as [N/bk, K/bc, bc/2, bk, 2]
+    in bf16, then remap_and_quantize_* by weight_dtype ("mxfp4" | "qint8")."""
+    wb = block_weight(w.to(torch.bfloat16), bk, bc)
+    if weight_dtype == "mxfp4":
+        return qtype.remap_and_quantize_mxfp4(wb)
+    if weight_dtype == "qint8":
+        return qtype.remap_and_quantize_qint8(wb)
+    raise ValueError(f"Unknown weight_dtype {weight_dtype}")
+
+
+class BlockedLinear(torch.nn.Module):
+    """llm_common.BlockedLinear (llm_common.py:383-426) for quantized weights on CUDA."""
+
+    def __init__(self, qweight, bias=None, parallel_dim=-1, split_sizes=()):
+        super().__init__()
+        self.weight = qweight
+        self.bias = bias
+        self.parallel_dim = parallel_dim
+        self.split_sizes = list(split_sizes)
+
+    def forward(self, input):
+        return fc_plain(input.to(torch.bfloat16), self.weight, self.bias, self.parallel_dim, self.split_sizes)
+
+
+def FixLinear(m, bk=None, bc=None, layer_dtype=torch.bfloat16, parallel_dim=None, block_size=1, weight_dtype=None):
+    """llm_common.FixLinear (llm_common.py:437-510): shard (optionally), block and quantize an nn.Linear;
+    returns the BlockedLinear that replaces it."""
+    if not isinstance(m, torch.nn.Linear):
+        return m
+    pd = -1
+    if parallel_dim is not None and get_size() > 1:
+        ShardLinear(m, parallel_dim, get_rank(), get_size(), block_size)
+        pd = parallel_dim
+    if weight_dtype not in ("mxfp4", "qint8"):
+        raise ValueError("this build carries quantized weights only: weight_dtype must be 'mxfp4' or 'qint8'")
+    q = quantize_weight(m.weight.data, weight_dtype, bk or 16, bc or 64)
+    bias = m.bias.data.to(torch.bfloat16) if m.bias is not None else None
+    return BlockedLinear(q, bias, pd, getattr(m, "split_sizes", ()))
+
+
+def fc_plain(input, weight, bias=None, parallel_dim=-1, split_sizes=()):
+    """torch.ops.tpp_llm.fc_plain (llm_common.py:379-380 -> fc_plain_wrap, src/csrc/llm/fused_llm_infer.cpp:1514-1566)."""
+    if parallel_dim == -1 or get_size() == 1:
+        return fused_llm_cpp.fc_plain(input, weight, bias)
+    return fc_plain_parallel(input, weight, bias, parallel_dim, list(split_sizes))
+
+
+def fc_plain_parallel(input, weight, bias, parallel_dim, split_sizes):
+    """Tensor-parallel linear: row-parallel (parallel_dim 1) takes this rank's slice of the input features and
+    all-reduces; column-parallel (0) all-gathers the uneven output slices (fused_llm_infer.cpp:1521-1564)."""
+    import torch.distributed as dist
+    rank = get_rank()
+    if parallel_dim == 1:
+        x = input.split(split_sizes, dim=-1)[rank].contiguous()
+        y = fused_llm_cpp.fc_plain(x, weight, bias)
+        fused_llm_cpp.allreduce(y)
+        return y
+    y = fused_llm_cpp.fc_plain(input, weight, bias)
+    outs = [y.new_empty(y.shape[:-1] + (s,)) for s in split_sizes]
+    dist.all_gather(outs, y)
+    return torch.cat(outs, dim=-1)
