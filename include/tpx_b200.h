@@ -129,6 +129,18 @@ int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const 
                          int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
                          float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream);
 
+/* The same linear for callers that cannot allocate device memory where they call it (all free memory already
+ * handed to a cache pool, a fixed budget inside another framework, a thread that must stay off the allocator's
+ * locks). It has no counterpart in the reference. Its scratch is an 8 MiB array built into the library
+ * (tpx_qlinear_mxfp4_tc_static_max_bytes); shapes whose scratch need (tpx_qlinear_mxfp4_tc_scratch_bytes) exceeds
+ * that are refused with TPX_ERR_SCRATCH. The call allocates nothing. The first call on each device looks up the
+ * array's device address and should therefore come before any stream capture. All calls on one GPU share the
+ * array: two of them in flight at once (different streams) corrupt each other; serialise them.                */
+size_t tpx_qlinear_mxfp4_tc_static_max_bytes(void);
+int tpx_qlinear_mxfp4_tc_static(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M,
+                                int64_t N, int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in,
+                                const uint16_t* res, float res_scale, uint16_t* y, void* stream);
+
 /* ---------------------------------------------------------------- decoder-layer pieces
  * RMSNorm: y = x * rsqrt(mean(x^2) + eps) * gamma, fp32 statistics. Replaces llama_rms_norm
  * (src/csrc/llm/fused_llm_infer.cpp:336-363; RMSNormFwdTPP::ref src/csrc/xsmm_functors.h:4628-4654).

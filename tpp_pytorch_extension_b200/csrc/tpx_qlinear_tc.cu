@@ -788,3 +788,48 @@ extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int p
     default: return tc_launch<128, false, 2>(mw, mx, p, pl.grid, st);
   }
 }
+
+// ---------------------------------------------------------------- variant that allocates nothing
+// Some callers may not allocate device memory at the point where they run a linear: a serving loop that has
+// handed all free memory to its KV-cache pool, a plugin running inside another framework's memory budget, or a
+// host thread that must not take the allocator's locks. For them the scratch of the tensor-core linear lives in
+// this file-scope device array instead of a caller-provided buffer. Every GPU that loads the library holds these
+// 8 MiB until the process exits.
+static constexpr size_t kStaticScratchBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_tc_static_scratch[kStaticScratchBytes];
+
+// In host code the array's name is only a handle: the device address comes from cudaGetSymbolAddress, once per
+// device, with that device current.
+static int static_scratch_ptr(void** out) {
+  static void* ptrs[64] = {};
+  int dev = 0;
+  TPX_CUDA_OK(cudaGetDevice(&dev));
+  TPX_REQUIRE(dev >= 0 && dev < 64, TPX_ERR_UNSUPPORTED, "qlinear_mxfp4_tc_static: device index %d out of range", dev);
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    TPX_CUDA_OK(cudaGetSymbolAddress(&p, g_tc_static_scratch));
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return TPX_OK;
+}
+
+extern "C" size_t tpx_qlinear_mxfp4_tc_static_max_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int tpx_qlinear_mxfp4_tc_static(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M,
+                                           int64_t N, int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in,
+                                           const uint16_t* res, float res_scale, uint16_t* y, void* stream) {
+  TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear_mxfp4_tc_static: bad shape");
+  if (M == 0) return TPX_OK;
+  const size_t need = tpx_qlinear_mxfp4_tc_scratch_bytes(M, N, K, pair);
+  TPX_REQUIRE(need <= kStaticScratchBytes, TPX_ERR_SCRATCH,
+              "qlinear_mxfp4_tc_static: M=%ld N=%ld K=%ld needs %zu bytes of scratch, the built-in array holds %zu; "
+              "use tpx_qlinear_mxfp4_tc with a caller-provided buffer",
+              (long)M, (long)N, (long)K, need, kStaticScratchBytes);
+  void* sc = nullptr;
+  int rc = static_scratch_ptr(&sc);
+  if (rc) return rc;
+  // the array keeps whatever the previous call left: the arrival counters and the error word must start at zero
+  TPX_CUDA_OK(cudaMemsetAsync(sc, 0, kTcCounterBytes, (cudaStream_t)stream));
+  return tpx_qlinear_mxfp4_tc(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, sc, kStaticScratchBytes, stream);
+}
