@@ -29,6 +29,9 @@ if ROOT not in sys.path:
 D_MODEL, D_FF = 4096, 14336
 SWEEP = [1, 8, 64, 512, 4096]
 DECODE_MAX_M = 64
+# dram__bytes_read.sum + dram__bytes_write.sum of one qlinear_tc_kernel gate/up launch, from the ncu captures
+# summarised under profiles/ (bytes); None where no capture exists
+NCU_TRAFFIC = {}
 N_COPIES = 6  # distinct packed weight sets: 6 x 93.6 MB = 561 MB >> 126 MB of L2
 
 
@@ -216,7 +219,9 @@ def run_ours(args):
     torch.cuda.synchronize()
 
     def launches_for(M):
-        return 2 * ((M + 31) // 32)  # the streaming kernel re-launches per 32 tokens
+        # per (gate/up, down) pair of ops: the tensor-core path launches the activation split and the GEMM;
+        # the streaming path launches once per 32 tokens
+        return 4 if F.mxfp4_path() == "tc" else 2 * ((M + 31) // 32)
 
     counter = [0]
 
@@ -312,6 +317,7 @@ def run_ours(args):
                             "gbs": round(op_bytes(M, pair) / (ms * 1e-3) / 1e9, 1),
                             "tflops": round(op_flops(M, pair) / (ms * 1e-3) / 1e12, 2),
                             "launches": launches_for(M) // 2})
+    dom_share = float(seg[dom, 0] / max(1e-9, sum(seg[i].sum() for i in dec)))
     if rank == 0:
         line = {
             "metric": "qgemm_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -321,9 +327,12 @@ def run_ours(args):
             "prefill": {"tflops": world * pre_flops / (pre_ms * 1e-3) / 1e12 if pre_ms > 0 else None, "unit": "TFLOP/s",
                         "frac_of_bf16_peak": pre_flops / (pre_ms * 1e-3) / 1e12 / pk["bf16_tflops"] if pre_ms > 0 else None,
                         "peak_src": pk["src"]},
-            "roofline": {"bound": "hbm", "kernel": f"qlinear_stream_mxfp4 gate/up pair, M={SWEEP[dom]}",
+            "roofline": {"bound": "hbm",
+                         "kernel": f"qlinear_tc_kernel (tcgen05 mxf8f6f4) gate/up pair, M={SWEEP[dom]}"
+                                   if F.mxfp4_path() == "tc" else f"qlinear_stream gate/up pair, M={SWEEP[dom]}",
                          "achieved": dom_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": dom_gbs / pk["hbm_gbs"],
-                         "peak_src": pk["src"], "traffic": None},
+                         "peak_src": pk["src"], "traffic": NCU_TRAFFIC.get(SWEEP[dom]),
+                         "duration": "CUDA events around the op (activation-split kernel + GEMM kernel)"},
             "kernels": kernels,
             "e2e": {"value": e2e_value, "unit": "GB/s",
                     "h2d_bytes_per_step": sum(M * D_MODEL * 2 for M in SWEEP),

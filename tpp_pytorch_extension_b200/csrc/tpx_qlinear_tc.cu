@@ -25,8 +25,10 @@
 // each for the weight and activation scale-factor blocks.
 //
 // Work is the flat list of (output tile, k unit) units cut into equal contiguous ranges, one CTA per SM:
-// every SM streams the same number of weight bytes. A tile cut between CTAs is completed through fp32
-// partial tiles in scratch (one slot per contributor, summed in a fixed order by the last to arrive).
+// every SM streams the same number of weight bytes. A tile cut between CTAs leaves fp32 partial tiles in scratch
+// (one slot per contributor); a small second kernel, launched as a programmatic dependent so that its launch
+// latency hides behind the GEMM, adds them in CTA order and runs the epilogue. Doing this inside the GEMM (last
+// arriver per tile) cost a store -> atomic -> load chain at loaded-memory latency (~2 us per hop).
 #include <cuda.h>
 #include <stdlib.h>
 
@@ -307,7 +309,6 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   __shared__ __align__(8) unsigned long long bar_full[C::STAGES], bar_empty[C::STAGES];
   __shared__ __align__(8) unsigned long long bar_acc_full, bar_acc_empty;
   __shared__ uint32_t tmem_holder;
-  __shared__ unsigned last_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem_base = (tc_smem_u32(tc_smem_raw) + 1023u) & ~1023u;
@@ -344,6 +345,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   const uint32_t tmem = tmem_holder;
   const uint32_t sf_col0 = C::D_COLS;
   if (threadIdx.x == 0) tc_stamp(p, 1);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the fix-up kernel may get its CTAs ready
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -516,67 +518,6 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         tc_fence_before();
         __syncwarp();
         if (lane == 0) tc_mbar_arrive(tc_smem_u32(&bar_acc_empty));  // tensor memory may be overwritten
-        if (!whole) {
-          // hand the partial tile in; the last contributor adds all of them in CTA order. The CTA barrier orders
-          // every thread's stores before thread 64's release, and its acquire before every thread's loads.
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          const long long ta = (long long)tile * p.KS, tb = ta + p.KS - 1;
-          const int cfirst = (int)(((ta + 1) * G - 1) / U), clast = (int)(((tb + 1) * G - 1) / U);
-          if (threadIdx.x == 64) {
-            unsigned prev;
-            asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prev) : "l"(p.counters + tile) : "memory");
-            last_flag = (prev == (unsigned)(clast - cfirst)) ? 1u : 0u;
-            if (last_flag) p.counters[tile] = 0;
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (threadIdx.x == 64 && it == nunits - 1) tc_stamp(p, 4);
-          if (last_flag) {
-            if (n < p.N) {
-#pragma unroll 1
-              for (int c0 = 0; c0 < TOK; c0 += 16) {
-                float v[16], v2[16];
-#pragma unroll
-                for (int j = 0; j < 16; j++) v[j] = v2[j] = 0.0f;
-#pragma unroll 1
-                for (int cb = cfirst; cb <= clast; cb += 4) {  // four contributors' loads in flight at a time
-                  uint4 t[4][DUAL ? 2 : 1][4];
-#pragma unroll
-                  for (int cc = 0; cc < 4; cc++) {
-                    const int c = cb + cc;
-                    if (c <= clast) {
-                      const int ctile0 = (int)(((long long)c * U / G) / p.KS);
-                      const float* slot = p.partial + (((size_t)c * 2 + (tile == ctile0 ? 0 : 1)) * C::NW) * TOK * 128 + (size_t)row * TOK + c0;
-#pragma unroll
-                      for (int q = 0; q < 4; q++) {
-                        t[cc][0][q] = __ldcg(reinterpret_cast<const uint4*>(slot) + q);
-                        if (DUAL) t[cc][DUAL ? 1 : 0][q] = __ldcg(reinterpret_cast<const uint4*>(slot + (size_t)TOK * 128) + q);
-                      }
-                    }
-                  }
-#pragma unroll
-                  for (int cc = 0; cc < 4; cc++) {
-                    if (cb + cc <= clast) {
-#pragma unroll
-                      for (int q = 0; q < 4; q++) {
-                        v[4 * q] += __uint_as_float(t[cc][0][q].x); v[4 * q + 1] += __uint_as_float(t[cc][0][q].y);
-                        v[4 * q + 2] += __uint_as_float(t[cc][0][q].z); v[4 * q + 3] += __uint_as_float(t[cc][0][q].w);
-                        if (DUAL) {
-                          v2[4 * q] += __uint_as_float(t[cc][DUAL ? 1 : 0][q].x); v2[4 * q + 1] += __uint_as_float(t[cc][DUAL ? 1 : 0][q].y);
-                          v2[4 * q + 2] += __uint_as_float(t[cc][DUAL ? 1 : 0][q].z); v2[4 * q + 3] += __uint_as_float(t[cc][DUAL ? 1 : 0][q].w);
-                        }
-                      }
-                    }
-                  }
-                }
-                if (threadIdx.x == 64 && it == nunits - 1 && c0 == 0) tc_stamp(p, 7);
-#pragma unroll
-                for (int j = 0; j < 16; j++)
-                  if (tok0 + c0 + j < p.M) tc_finish(p, tok0 + c0 + j, n, v[j], v2[j], DUAL);
-              }
-            }
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag is reused by the next tile
-        }
       }
       if (++ks == p.KS) {
         ks = 0;
@@ -592,6 +533,61 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)C::TMEM_COLS) : "memory");
   }
+}
+
+// ---------------------------------------------------------------- fix-up of tiles cut between CTAs
+// One CTA of 128 threads (= the 128 rows of a tile) per (tile, 16-token chunk). Contributors of a tile are the
+// consecutive GEMM CTAs cfirst..clast; CTA c keeps its part of the tile in slot 0 if the tile is the first it
+// touched, else in slot 1. Summation order is fixed (CTA order), so results do not depend on timing.
+template <bool DUAL>
+__global__ void __launch_bounds__(128) tc_fixup_kernel(TcParams p, int TOK, int G) {
+  constexpr int NW = DUAL ? 2 : 1;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int tile = blockIdx.x, c0 = blockIdx.y * 16, row = threadIdx.x;
+  const long long U = (long long)p.TN * p.TM * p.KS;
+  const long long ta = (long long)tile * p.KS, tb = ta + p.KS - 1;
+  const int cfirst = (int)(((ta + 1) * G - 1) / U), clast = (int)(((tb + 1) * G - 1) / U);
+  if (cfirst == clast) return;  // one CTA had the whole tile and finished it itself
+  const int tn = tile / p.TM, tm = tile % p.TM;
+  const int n = tn * 128 + row, tok0 = tm * TOK;
+  if (n >= p.N || tok0 + c0 >= p.M) return;
+  float v[16], v2[16];
+#pragma unroll
+  for (int j = 0; j < 16; j++) v[j] = v2[j] = 0.0f;
+#pragma unroll 1
+  for (int cb = cfirst; cb <= clast; cb += 4) {  // four contributors' loads in flight at a time
+    uint4 t[4][NW][4];
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+      const int c = cb + cc;
+      if (c <= clast) {
+        const int ctile0 = (int)(((long long)c * U / G) / p.KS);
+        const float* slot = p.partial + (((size_t)c * 2 + (tile == ctile0 ? 0 : 1)) * NW) * TOK * 128 + (size_t)row * TOK + c0;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          t[cc][0][q] = __ldcg(reinterpret_cast<const uint4*>(slot) + q);
+          if (DUAL) t[cc][NW - 1][q] = __ldcg(reinterpret_cast<const uint4*>(slot + (size_t)TOK * 128) + q);
+        }
+      }
+    }
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+      if (cb + cc <= clast) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          v[4 * q] += __uint_as_float(t[cc][0][q].x); v[4 * q + 1] += __uint_as_float(t[cc][0][q].y);
+          v[4 * q + 2] += __uint_as_float(t[cc][0][q].z); v[4 * q + 3] += __uint_as_float(t[cc][0][q].w);
+          if (DUAL) {
+            v2[4 * q] += __uint_as_float(t[cc][NW - 1][q].x); v2[4 * q + 1] += __uint_as_float(t[cc][NW - 1][q].y);
+            v2[4 * q + 2] += __uint_as_float(t[cc][NW - 1][q].z); v2[4 * q + 3] += __uint_as_float(t[cc][NW - 1][q].w);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 16; j++)
+    if (tok0 + c0 + j < p.M) tc_finish(p, tok0 + c0 + j, n, v[j], v2[j], DUAL);
 }
 
 // ---------------------------------------------------------------- host side
@@ -687,6 +683,15 @@ static int tc_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams&
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tc_kernel<TOK, DUAL, UKS>, w, x, p));
+  if (!p.whole_tiles && grid > 1) {  // tiles cut between CTAs are completed by the fix-up kernel
+    cudaLaunchConfig_t c2 = {};
+    c2.gridDim = dim3((unsigned)(p.TN * p.TM), (unsigned)(TOK / 16));
+    c2.blockDim = dim3(128);
+    c2.stream = st;
+    c2.attrs = attr;
+    c2.numAttrs = 1;
+    TPX_CUDA_OK(cudaLaunchKernelEx(&c2, tc_fixup_kernel<DUAL>, p, (int)TOK, grid));
+  }
   return TPX_OK;
 }
 
