@@ -348,6 +348,31 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def read_calibration():
+    """How fast can a plain streaming read of one launch's worth of weight bytes go on this GPU? Times a library
+    reduction (torch.sum over an int32 view) over rotating buffers of the gate/up pair's packed size and of
+    1 GiB, with the same enqueue-ahead event timing as the benchmark. Prints one JSON line."""
+    import torch
+    dev = torch.device("cuda", 0)
+    out = {}
+    for label, nbytes in (("pair_62MB", 2 * packed_bytes(D_FF, D_MODEL)), ("down_31MB", packed_bytes(D_MODEL, D_FF)), ("1GiB", 1 << 30)):
+        n = nbytes // 4
+        bufs = [torch.randint(0, 1 << 30, (n,), dtype=torch.int32, device=dev) for _ in range(10 if nbytes < (1 << 28) else 3)]
+        for b in bufs:
+            b.sum()
+        torch.cuda.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(20)]
+        torch.cuda._sleep(int(5e6))
+        for i, (a, b) in enumerate(evs):
+            a.record()
+            bufs[i % len(bufs)].sum()
+            b.record()
+        torch.cuda.synchronize()
+        ts = sorted(a.elapsed_time(b) for a, b in evs)
+        out[label] = {"us": round(ts[len(ts) // 2] * 1e3, 2), "gbs": round(nbytes / ts[len(ts) // 2] / 1e6, 1)}
+    print(json.dumps({"read_calibration": out, "peak_hbm_gbs": peaks()["hbm_gbs"]}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -355,7 +380,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ms", default="", help="comma-separated subset of the token counts to run (for profiler captures)")
+    ap.add_argument("--read-calibration", action="store_true", help="time a plain library read of the same byte counts and exit")
     args = ap.parse_args()
+    if args.read_calibration:
+        return read_calibration()
     if args.ms:
         global SWEEP
         SWEEP = [int(v) for v in args.ms.split(",")]

@@ -156,10 +156,12 @@ int tpx_rmsnorm(const uint16_t* x, const void* gamma, int gamma_is_f32, float ep
  *   q_out [B][Nkv][S][Nq/Nkv][H] rotated queries
  *   kc,vc [capacity/32][B][Nkv][32][H] cache tensors; the S new tokens land at offset .. offset+S-1
  * The caller owns the cache tensors and their growth (the reference grows by offset + S + KV_CACHE_INC_SIZE,
- * attn.h:171-177); this call refuses a write beyond `capacity` tokens.                                      */
+ * attn.h:171-177); this call refuses a write beyond `capacity` tokens. With dev_len != NULL the offset is read
+ * on the device from *dev_len instead of the `offset` argument (a decode step recorded once in a CUDA graph and
+ * replayed keeps its lengths in device memory); writes beyond `capacity` are then dropped by the kernel.     */
 int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const int64_t* pos, int64_t B, int64_t S, int64_t Nq,
                        int64_t Nkv, int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset, int64_t capacity,
-                       uint16_t* q_out, uint16_t* kc, uint16_t* vc, void* stream);
+                       const int32_t* dev_len, uint16_t* q_out, uint16_t* kc, uint16_t* vc, void* stream);
 
 /* Attention over the blocked cache. Replaces attn<T> (src/csrc/llm/attn.cpp:780-955):
  *   out = softmax(q.k^T / sqrt(H) + am[b][key], causal: key <= key_len - Sq + query) . v
@@ -168,11 +170,12 @@ int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const int64_t* pos,
  * rounding of the output. With a long cache and few (batch, head) pairs the key range is split over CTAs and
  * merged by a second kernel (flash-decoding); the scratch holds the un-normalised partials. out_bsnrh != 0
  * writes out as [B][Sq][Nkv][R][H], i.e. already as the [B*Sq][Nq*H] rows of the output projection (the
- * reference permutes and copies, src/csrc/llm/fused_llm_infer.cpp:581).                                     */
+ * reference permutes and copies, src/csrc/llm/fused_llm_infer.cpp:581). With dev_len != NULL the number of keys
+ * is *dev_len + Sq, read on the device; `key_len` is then only the planning maximum (cache capacity).         */
 size_t tpx_attention_scratch_bytes(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len);
 int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, const uint16_t* am, int64_t B, int64_t Nkv,
                   int64_t Sq, int64_t R, int64_t H, int64_t key_len, int64_t Spad, int causal, int out_bsnrh,
-                  uint16_t* out, void* scratch, size_t scratch_bytes, void* stream);
+                  const int32_t* dev_len, uint16_t* out, void* scratch, size_t scratch_bytes, void* stream);
 
 /* TppCache::align_and_invert_mask (src/csrc/llm/attn.h:310-322): [B][S] bf16 0/1 mask -> [B][Spad] additive
  * mask (1 -> 0, 0 -> min_bits, padding -> min_bits), Spad a multiple of 32.                                  */

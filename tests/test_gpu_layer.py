@@ -37,7 +37,7 @@ def _rope_case(cuda, B, S, Nq, Nkv, H, offset, pos):
     qkv_t, ep_t = to_dev_bf16(qkv, cuda), torch.from_numpy(ep).to(cuda)  # keep the device copies alive across the launch
     _lib.check(_lib.lib().tpx_rope_kv_update(qkv_t.data_ptr(), ep_t.data_ptr(),
                                              pos_t.data_ptr(), B, S, Nq, Nkv, H, MP, H, pos.shape[0], offset, cap,
-                                             q.data_ptr(), kc.data_ptr(), vc.data_ptr(), _lib.stream()))
+                                             None, q.data_ptr(), kc.data_ptr(), vc.data_ptr(), _lib.stream()))
     torch.cuda.synchronize()
     qr = qkv[..., : Nq * H]
     kr = qkv[..., Nq * H: (Nq + Nkv) * H]
@@ -67,7 +67,7 @@ def test_rope_rejects_overflow(cuda):
     f = torch.zeros(4096, dtype=torch.float32, device=cuda)
     p = torch.zeros(8, dtype=torch.int64, device=cuda)
     rc = _lib.lib().tpx_rope_kv_update(z.data_ptr(), f.data_ptr(), p.data_ptr(), 1, 4, 2, 1, 64, 8, 64, 1, 30, 32,
-                                       z.data_ptr(), z.data_ptr(), z.data_ptr(), _lib.stream())
+                                       None, z.data_ptr(), z.data_ptr(), z.data_ptr(), _lib.stream())
     assert rc == 1 and b"capacity" in _lib.lib().tpx_last_error()
 
 

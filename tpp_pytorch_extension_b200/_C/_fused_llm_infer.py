@@ -175,9 +175,11 @@ class LlamaDecoderLayer:
             w.prepare()
         self.Wg.prepare(pair_with=self.Wu)
 
-    def forward(self, inp, cache, use_cache=True):
+    def forward(self, inp, cache, use_cache=True, dev_len=None):
         """inp = [hidden_states [B,S,D] bf16, additive mask [B,Spad], position_ids int64 [1 or B, S]]
-        (LLMBlock::forward_common / _forward, :531-561, :1195-1286)."""
+        (LLMBlock::forward_common / _forward, :531-561, :1195-1286). dev_len: int32 device scalar holding the number
+        of cached tokens; when given, kernels read lengths from it (nothing in the call depends on host-side
+        lengths, so the step can be recorded in a CUDA graph) and the cache must already have room."""
         from ._tpp_attn import attention
         hs, am, pos = inp[0], inp[1], inp[2]
         _lib.require_cuda(hs, "hidden_states")
@@ -189,15 +191,21 @@ class LlamaDecoderLayer:
         x = rms_norm(res, self.Gi, self.eps)
         qkv = fc_plain(x, self.Wqkv)
         lc = cache.layer(self.layer_idx)
-        lc.ensure(B, self.Nkv, self.H, S, hs.dtype, hs.device)
+        if dev_len is None:
+            lc.ensure(B, self.Nkv, self.H, S, hs.dtype, hs.device)
         R = self.Nq // self.Nkv
         q = torch.empty((B, self.Nkv, S, R, self.H), dtype=hs.dtype, device=hs.device)
-        pos = pos.to(torch.int64).contiguous()
+        if pos.dtype != torch.int64 or not pos.is_contiguous():
+            pos = pos.to(torch.int64).contiguous()
         _lib.check(L.tpx_rope_kv_update(qkv.data_ptr(), self.EP.data_ptr(), pos.data_ptr(), B, S, self.Nq, self.Nkv, self.H,
                                         self.EP.shape[1], self.EP.shape[2], pos.shape[0], lc.offset, lc.capacity(),
-                                        q.data_ptr(), lc.k.data_ptr(), lc.v.data_ptr(), _lib.stream()))
-        lc.offset += S
-        ctx = attention(q, lc.k, lc.v, am, lc.offset, causal=True, out_bsnrh=True).view(B * S, self.Nq * self.H)
+                                        _lib.ptr(dev_len), q.data_ptr(), lc.k.data_ptr(), lc.v.data_ptr(), _lib.stream()))
+        if dev_len is None:
+            lc.offset += S
+            key_len = lc.offset
+        else:
+            key_len = lc.capacity()  # planning maximum; the kernels read the real length from dev_len
+        ctx = attention(q, lc.k, lc.v, am, key_len, causal=True, out_bsnrh=True, dev_len=dev_len).view(B * S, self.Nq * self.H)
         so = fc_plain_act(ctx, self.Wp, res=res, res_scale=scale)
         if ws > 1:
             allreduce(so)

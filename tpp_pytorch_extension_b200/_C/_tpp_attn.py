@@ -95,9 +95,10 @@ class TppCache:
         raise NotImplementedError("beam-search cache reordering (src/csrc/llm/attn.h:327-403) is not built yet")
 
 
-def attention(q, kc, vc, mask, key_len, causal=True, out_bsnrh=False):
+def attention(q, kc, vc, mask, key_len, causal=True, out_bsnrh=False, dev_len=None):
     """attn<T> (src/csrc/llm/attn.cpp:780-955). q [B, Nkv, Sq, R, H] bf16; kc/vc cache tensors; mask additive
-    [B, Spad] or None. Returns [B, Nkv, Sq, R, H], or [B, Sq, Nkv*R*H] with out_bsnrh."""
+    [B, Spad] or None. Returns [B, Nkv, Sq, R, H], or [B, Sq, Nkv*R*H] with out_bsnrh. With dev_len (int32
+    device scalar) the key count is read on the device as dev_len + Sq and key_len is the planning maximum."""
     _lib.require_cuda(q, "q")
     B, Nkv, Sq, R, H = q.shape
     L = _lib.lib()
@@ -106,7 +107,7 @@ def attention(q, kc, vc, mask, key_len, causal=True, out_bsnrh=False):
     sc = _lib.aux_scratch(nb, q.device) if nb else None
     Spad = mask.shape[1] if mask is not None else 0
     _lib.check(L.tpx_attention(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), _lib.ptr(mask), B, Nkv, Sq, R, H, key_len, Spad,
-                               int(causal), int(out_bsnrh), out.data_ptr(), _lib.ptr(sc), nb, _lib.stream()))
+                               int(causal), int(out_bsnrh), _lib.ptr(dev_len), out.data_ptr(), _lib.ptr(sc), nb, _lib.stream()))
     return out
 
 

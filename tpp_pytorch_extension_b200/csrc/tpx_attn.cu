@@ -61,10 +61,11 @@ __global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const void* __res
 // src/csrc/llm/fused_llm_infer.cpp:563-584); k is rotated and stored, v stored, at cache tokens offset .. offset+S-1.
 // One thread per (token, head, pair of rotary lanes).
 __global__ void rope_kv_kernel(const uint16_t* __restrict__ qkv, const float* __restrict__ ep, const int64_t* __restrict__ pos,
-                               int B, int S, int Nq, int Nkv, int H, int MP, int HR, int Bpos, int64_t offset,
-                               uint16_t* __restrict__ q_out, uint16_t* __restrict__ kc, uint16_t* __restrict__ vc) {
+                               int B, int S, int Nq, int Nkv, int H, int MP, int HR, int Bpos, int64_t offset_arg,
+                               const int* __restrict__ dev_len, int64_t capacity, uint16_t* __restrict__ q_out, uint16_t* __restrict__ kc, uint16_t* __restrict__ vc) {
   const int heads = Nq + 2 * Nkv;
   const int half = H / 2;
+  const int64_t offset = dev_len ? (int64_t)*dev_len : offset_arg;  // tokens already cached
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)B * S * heads * half) return;
   const int h2 = (int)(idx % half);
@@ -90,6 +91,7 @@ __global__ void rope_kv_kernel(const uint16_t* __restrict__ qkv, const float* __
     const bool is_k = hd < Nq + Nkv;
     const int n = is_k ? hd - Nq : hd - Nq - Nkv;
     const int64_t t = offset + s;
+    if (t >= capacity) return;  // never write beyond the cache (the host checks this when it knows the offset)
     dst = (is_k ? kc : vc) + ((((t / 32) * B + b) * Nkv + n) * 32 + (t % 32)) * H;
   }
   dst[h2] = o0;
@@ -114,6 +116,7 @@ struct AttnParams {
   int B, Nkv, Sq, R, H;
   int key_len, Spad, causal;
   int chunks, splits;
+  const int* dev_len;   // when set: keys cached before this call; key_len = *dev_len + Sq (key_len above is then the planning maximum)
   int out_bsnrh;        // 0: out laid out like q; 1: out[B][Sq][Nkv][R][H] (rows of the following linear)
   float scale;
 };
@@ -138,7 +141,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(AttnParams p) {
   const int rows_total = p.Sq * p.R;
   const int row0 = chunk * kAttnRows;
   const int rows = min(kAttnRows, rows_total - row0);
-  const int offset = p.key_len - p.Sq;
+  const int key_len = p.dev_len ? *p.dev_len + p.Sq : p.key_len;
+  const int offset = key_len - p.Sq;
 
   // queries of this chunk to shared memory as fp32, pre-multiplied by 1/sqrt(H)
   const uint16_t* qbase = p.q + ((int64_t)bn * rows_total + row0) * H;
@@ -150,7 +154,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(AttnParams p) {
 
   // keys this chunk can see at all: up to the last row's causal limit
   const int last_sq = (row0 + rows - 1) / p.R;
-  const int kmax = p.causal ? min(p.key_len, offset + last_sq + 1) : p.key_len;
+  const int kmax = p.causal ? min(key_len, offset + last_sq + 1) : key_len;
   const int nblocks = (kmax + 31) / 32;
   const int per_split = (nblocks + p.splits - 1) / p.splits;
   const int blk0 = split * per_split, blk1 = min(nblocks, blk0 + per_split);
@@ -197,7 +201,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(AttnParams p) {
         }
         s += madd;
         const int sq = (row0 + r) / p.R;
-        const bool visible = tok < p.key_len && (!p.causal || tok <= offset + sq);
+        const bool visible = tok < key_len && (!p.causal || tok <= offset + sq);
         if (!visible) s = -INFINITY;
         float bm = s;
 #pragma unroll
@@ -219,7 +223,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(AttnParams p) {
     for (int r = 0; r < kAttnRows; r++)
 #pragma unroll
       for (int j = 0; j < HV; j++) acc[r][j] *= alpha[r];
-    const int ntok = min(32, p.key_len - blk * 32);
+    const int ntok = min(32, key_len - blk * 32);
     for (int t = 0; t < ntok; t++) {
       float vv[HV];
       const uint16_t* vr = p.vc + boff + (int64_t)t * H + lane * HV;
@@ -330,18 +334,19 @@ extern "C" int tpx_rmsnorm(const uint16_t* x, const void* gamma, int gamma_is_f3
 
 extern "C" int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const int64_t* pos, int64_t B, int64_t S, int64_t Nq,
                                   int64_t Nkv, int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset,
-                                  int64_t capacity, uint16_t* q_out, uint16_t* kc, uint16_t* vc, void* stream) {
+                                  int64_t capacity, const int32_t* dev_len, uint16_t* q_out, uint16_t* kc, uint16_t* vc, void* stream) {
   TPX_REQUIRE(qkv && ep && pos && q_out && kc && vc, TPX_ERR_ARG, "rope_kv_update: null pointer");
   TPX_REQUIRE(B > 0 && S >= 0 && Nq > 0 && Nkv > 0 && Nq % Nkv == 0 && H % 2 == 0, TPX_ERR_ARG,
               "rope_kv_update: bad shape");
   TPX_REQUIRE(HR == H, TPX_ERR_UNSUPPORTED, "rope_kv_update: rotary width %ld != head dim %ld (partial rotary is not built)", (long)HR, (long)H);
   TPX_REQUIRE(Bpos == 1 || Bpos == B, TPX_ERR_ARG, "position_ids shape not compatible");
-  TPX_REQUIRE(offset >= 0 && offset + S <= capacity, TPX_ERR_ARG, "rope_kv_update: cache capacity %ld is short of %ld tokens",
-              (long)capacity, (long)(offset + S));
+  if (!dev_len)
+    TPX_REQUIRE(offset >= 0 && offset + S <= capacity, TPX_ERR_ARG, "rope_kv_update: cache capacity %ld is short of %ld tokens",
+                (long)capacity, (long)(offset + S));
   if (S == 0) return TPX_OK;
   int64_t total = B * S * (Nq + 2 * Nkv) * (H / 2);
   rope_kv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(qkv, ep, pos, (int)B, (int)S, (int)Nq, (int)Nkv,
-                                                                                  (int)H, (int)MP, (int)HR, (int)Bpos, offset, q_out, kc, vc);
+                                                                                  (int)H, (int)MP, (int)HR, (int)Bpos, offset, dev_len, capacity, q_out, kc, vc);
   TPX_LAUNCH_OK();
   return TPX_OK;
 }
@@ -367,7 +372,7 @@ extern "C" size_t tpx_attention_scratch_bytes(int64_t B, int64_t Nkv, int64_t Sq
 
 extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, const uint16_t* am, int64_t B,
                              int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len, int64_t Spad, int causal,
-                             int out_bsnrh, uint16_t* out, void* scratch, size_t scratch_bytes, void* stream) {
+                             int out_bsnrh, const int32_t* dev_len, uint16_t* out, void* scratch, size_t scratch_bytes, void* stream) {
   TPX_REQUIRE(q && kc && vc && out, TPX_ERR_ARG, "attention: null pointer");
   TPX_REQUIRE(B > 0 && Nkv > 0 && Sq >= 0 && R > 0 && key_len >= Sq, TPX_ERR_ARG, "attention: bad shape");
   TPX_REQUIRE(H == 64 || H == 128, TPX_ERR_UNSUPPORTED, "attention: head dim %ld not supported (64 or 128)", (long)H);
@@ -376,7 +381,7 @@ extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16
   AttnParams p;
   p.q = q; p.kc = kc; p.vc = vc; p.am = am; p.out = out; p.part = reinterpret_cast<float*>(scratch);
   p.B = (int)B; p.Nkv = (int)Nkv; p.Sq = (int)Sq; p.R = (int)R; p.H = (int)H;
-  p.key_len = (int)key_len; p.Spad = (int)Spad; p.causal = causal; p.out_bsnrh = out_bsnrh;
+  p.key_len = (int)key_len; p.Spad = (int)Spad; p.causal = causal; p.out_bsnrh = out_bsnrh; p.dev_len = dev_len;
   attn_plan(B, Nkv, Sq, R, key_len, &p.chunks, &p.splits);
   p.scale = 1.0f / sqrtf((float)H);
   if (p.splits > 1) {

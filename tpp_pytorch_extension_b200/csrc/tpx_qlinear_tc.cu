@@ -651,6 +651,7 @@ static TcPlan tc_plan(int64_t M, int64_t N, int64_t K, bool pair) {
   // Cutting tiles between CTAs balances the weight stream exactly but costs a fix-up pass through scratch at
   // loaded-memory latency; with nearly as many tiles as SMs, or many tiles per SM, whole tiles are cheaper.
   pl.whole_tiles = (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
+  { const char* e = getenv("TPX_TC_WHOLE"); if (e) pl.whole_tiles = atoi(e); }
   pl.grid = pl.whole_tiles ? (int)(T < sms ? T : sms) : (int)(U < sms ? U : sms);
   size_t o = kTcCounterBytes;
   auto bump = [&](size_t bytes) { size_t r = o; o += (bytes + 1023) & ~(size_t)1023; return r; };
@@ -742,8 +743,6 @@ extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int p
               TPX_ERR_ARG, "qlinear_mxfp4_tc: misaligned pointer");
   const bool dual = pair != 0;
   TcPlan pl = tc_plan(M, N, K, dual);
-  TPX_REQUIRE((size_t)pl.TN * pl.TM * sizeof(unsigned) <= kTcCounterBytes - 16, TPX_ERR_UNSUPPORTED,
-              "qlinear_mxfp4_tc: %d x %d output tiles exceed the counter region; split the batch", pl.TN, pl.TM);
   TPX_REQUIRE(scratch && scratch_bytes >= pl.total, TPX_ERR_SCRATCH, "qlinear_mxfp4_tc: scratch of %zu bytes needed, %zu given",
               pl.total, scratch_bytes);
   cudaStream_t st = (cudaStream_t)stream;

@@ -81,6 +81,19 @@ class LlamaRunner(torch.nn.Module):
         self.lm_split = [lm_head_w.shape[1]] if get_size() == 1 else None
         self.only_last_logit = True
 
+    def _head(self, hs):
+        """Final norm + lm_head on the last position (logits slicing of the reference, fused_llama_infer.py:385-390)."""
+        if self.only_last_logit:
+            hs = hs[:, -1:, :]
+        hs = fused_llm_cpp.rms_norm(hs.contiguous(), self.norm_w, self.shape.rms_norm_eps)
+        if get_size() > 1:
+            offs = shard_offsets(self.shape.hidden_size, get_size(), 64)
+            r = get_rank()
+            logits = torch.nn.functional.linear(hs[..., offs[r]:offs[r + 1]], self.lm_head_w)
+            fused_llm_cpp.allreduce(logits)
+            return logits
+        return torch.nn.functional.linear(hs, self.lm_head_w)
+
     @torch.no_grad()
     def forward(self, input_ids, attention_mask=None, position_ids=None, cache=None):
         """Patched LlamaModel.forward + LlamaForCausalLM.forward of the reference (fused_llama_infer.py:236-408)."""
@@ -97,35 +110,70 @@ class LlamaRunner(torch.nn.Module):
         cpp = cache.get_cpp()
         for layer in self.layers:
             hs = layer.forward([hs, am, position_ids], cpp, True)[0]
-        if self.only_last_logit:
-            hs = hs[:, -1:, :]
-        hs = fused_llm_cpp.rms_norm(hs.contiguous(), self.norm_w, self.shape.rms_norm_eps)
-        if get_size() > 1:
-            offs = shard_offsets(self.shape.hidden_size, get_size(), 64)
-            r = get_rank()
-            logits = torch.nn.functional.linear(hs[..., offs[r]:offs[r + 1]], self.lm_head_w)
-            fused_llm_cpp.allreduce(logits)
-        else:
-            logits = torch.nn.functional.linear(hs, self.lm_head_w)
-        return logits, cache
+        return self._head(hs), cache
 
     @torch.no_grad()
-    def generate(self, input_ids, max_new_tokens, attention_mask=None):
-        """Greedy decoding (the reference drives HF generate with --greedy, examples/llm/run_generation.py:337-339)."""
+    def generate(self, input_ids, max_new_tokens, attention_mask=None, use_graph=True):
+        """Greedy decoding (the reference drives HF generate with --greedy, examples/llm/run_generation.py:337-339).
+
+        With use_graph the decode step (embedding, all layers, head, argmax, length bump) is recorded once in a CUDA
+        graph and replayed: the lengths the kernels need live in device memory, the cache is sized up front, and the
+        host only replays. Returns [B, prompt + max_new_tokens] token ids."""
         cache = TppCache()
-        B = input_ids.shape[0]
+        cpp = cache.get_cpp()
+        B, P = input_ids.shape
+        dev = input_ids.device
         mask = attention_mask if attention_mask is not None else torch.ones_like(input_ids)
         logits, cache = self.forward(input_ids, mask, None, cache)
-        out = [input_ids]
-        nxt = logits[:, -1].argmax(-1, keepdim=True)
-        for _ in range(max_new_tokens - 1):
-            out.append(nxt)
-            mask = torch.cat([mask, mask.new_ones((B, 1))], dim=1)
-            pos = (mask.sum(-1, keepdim=True) - 1) if attention_mask is not None else None
-            logits, cache = self.forward(nxt, mask, pos, cache)
-            nxt = logits[:, -1].argmax(-1, keepdim=True)
-        out.append(nxt)
-        return torch.cat(out, dim=1)
+        tok = logits[:, -1].argmax(-1, keepdim=True)
+        outs = [input_ids, tok.clone()]
+        steps = max_new_tokens - 1
+        if steps <= 0:
+            return torch.cat(outs, dim=1)
+        # room for every token to come, so that no cache tensor moves during decoding
+        for lc in cpp.layers:
+            lc.ensure(B, lc.k.shape[2], lc.k.shape[4], steps, lc.k.dtype, dev)
+        cap = cpp.layers[0].capacity()
+        keep = torch.cat([mask.to(torch.bfloat16), torch.ones((B, cap - P), dtype=torch.bfloat16, device=dev)], dim=1)
+        am = cpp.align_and_invert_mask(keep)  # positions not yet written are excluded by the length, not by the mask
+        dev_len = torch.full((1,), P, dtype=torch.int32, device=dev)
+        pos = mask.sum(-1, keepdim=True).to(torch.int64).contiguous()  # next position per sequence (left padding aware)
+
+        def step():
+            hs = torch.nn.functional.embedding(tok, self.embed)
+            for layer in self.layers:
+                hs = layer.forward([hs, am, pos], cpp, True, dev_len=dev_len)[0]
+            lg = self._head(hs)
+            tok.copy_(lg[:, -1].argmax(-1, keepdim=True))
+            pos.add_(1)
+            dev_len.add_(1)
+
+        done = 0
+        graph = None
+        if use_graph and steps >= 3:
+            step()  # eager once: sizes scratch buffers and opts kernels in to their shared-memory sizes
+            outs.append(tok.clone())
+            done = 1
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    step()
+            except Exception as e:  # capture unsupported here: decode eagerly
+                import warnings
+                warnings.warn(f"CUDA graph capture of the decode step failed ({e!r}); decoding eagerly")
+                graph = None
+                torch.cuda.synchronize()
+        while done < steps:
+            if graph is not None:
+                graph.replay()
+            else:
+                step()
+            outs.append(tok.clone())
+            done += 1
+        for lc in cpp.layers:
+            lc.offset += steps
+        self.last_graph = graph
+        return torch.cat(outs, dim=1)
 
 
 def _lm_head_shard(w):
