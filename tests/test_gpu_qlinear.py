@@ -12,10 +12,12 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-2
 
 
-@pytest.fixture(autouse=True, params=["tc", "stream"])
+@pytest.fixture(autouse=True, params=["tc", "tc_wide", "stream"])
 def mxfp4_path(request, monkeypatch):
-    """Every case runs on both MXFP4 kernel families: the tcgen05 tensor-core kernel and the mma.sync streaming kernel."""
-    monkeypatch.setenv("TPX_MXFP4_PATH", request.param)
+    """Every case runs on each MXFP4 kernel family: the tcgen05 kernel with the weights on the 128-row side of the MMA,
+    the tcgen05 kernel with the weights on the wide side (up to 64 tokens), and the mma.sync streaming kernel."""
+    monkeypatch.setenv("TPX_MXFP4_PATH", "stream" if request.param == "stream" else "tc")
+    monkeypatch.setenv("TPX_TC_WIDE", "1" if request.param == "tc_wide" else "0")
     return request.param
 
 

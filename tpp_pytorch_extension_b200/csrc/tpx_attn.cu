@@ -15,6 +15,8 @@ namespace tpx {
 // ---------------------------------------------------------------- RMSNorm: one warp per row
 __global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const void* __restrict__ gamma, int gamma_f32, float eps,
                                int64_t rows, int D, uint16_t* __restrict__ y) {
+  pdl_trigger();
+  pdl_wait();
   int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -55,6 +57,71 @@ __global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const void* __res
   }
 }
 
+// Few rows (decoding): one CTA of 256 threads per row, the row kept in registers between the two passes.
+constexpr int kNormThreads = 256;
+constexpr int kNormVecs = 4;  // uint4 vectors per thread held in registers: rows up to 256 * 4 * 8 = 8192 elements
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_row_kernel(const uint16_t* __restrict__ x, const void* __restrict__ gamma,
+                                                                   int gamma_f32, float eps, int D, uint16_t* __restrict__ y) {
+  __shared__ float red[kNormThreads / 32];
+  pdl_trigger();
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  const int nv = D / 8;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+  uint4 v[kNormVecs];
+  float ss = 0.0f;
+#pragma unroll
+  for (int q = 0; q < kNormVecs; q++) {
+    const int i = threadIdx.x + q * kNormThreads;
+    v[q] = i < nv ? xr[i] : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int q = 0; q < kNormVecs; q++) {
+    const uint32_t w[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      float a = bf16_bits_to_f32((uint16_t)(w[j] & 0xffff)), b = bf16_bits_to_f32((uint16_t)(w[j] >> 16));
+      ss += a * a + b * b;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.0f;
+#pragma unroll
+  for (int w = 0; w < kNormThreads / 32; w++) tot += red[w];
+  const float inv = rsqrtf(tot / (float)D + eps);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * D);
+#pragma unroll
+  for (int q = 0; q < kNormVecs; q++) {
+    const int i = threadIdx.x + q * kNormThreads;
+    if (i >= nv) continue;
+    const uint32_t w[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+    float g[8];
+    if (gamma_f32) {
+      const float4 g0 = reinterpret_cast<const float4*>(gamma)[2 * i], g1 = reinterpret_cast<const float4*>(gamma)[2 * i + 1];
+      g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+    } else {
+      const uint4 gv = reinterpret_cast<const uint4*>(gamma)[i];
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        g[2 * j] = bf16_bits_to_f32((uint16_t)(gw[j] & 0xffff));
+        g[2 * j + 1] = bf16_bits_to_f32((uint16_t)(gw[j] >> 16));
+      }
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      float a = bf16_bits_to_f32((uint16_t)(w[j] & 0xffff)) * inv * g[2 * j];
+      float b = bf16_bits_to_f32((uint16_t)(w[j] >> 16)) * inv * g[2 * j + 1];
+      o[j] = (uint32_t)f32_to_bf16_bits(a) | ((uint32_t)f32_to_bf16_bits(b) << 16);
+    }
+    yr[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 // ---------------------------------------------------------------- RoPE + KV-cache write
 // qkv: [B*S][(Nq + 2*Nkv)*H] bf16, the output of the fused q/k/v linear (q heads, then k heads, then v heads).
 // q is rotated and written as q_out[B][Nkv][S][R][H] (R = Nq/Nkv, the layout the reference hands to attention,
@@ -63,6 +130,8 @@ __global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const void* __res
 __global__ void rope_kv_kernel(const uint16_t* __restrict__ qkv, const float* __restrict__ ep, const int64_t* __restrict__ pos,
                                int B, int S, int Nq, int Nkv, int H, int MP, int HR, int Bpos, int64_t offset_arg,
                                const int* __restrict__ dev_len, int64_t capacity, uint16_t* __restrict__ q_out, uint16_t* __restrict__ kc, uint16_t* __restrict__ vc) {
+  pdl_trigger();
+  pdl_wait();
   const int heads = Nq + 2 * Nkv;
   const int half = H / 2;
   const int64_t offset = dev_len ? (int64_t)*dev_len : offset_arg;  // tokens already cached
@@ -135,6 +204,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(AttnParams p) {
   __shared__ float red_m[kAttnWarps][kAttnRows], red_l[kAttnWarps][kAttnRows];
   __shared__ float red_o[kAttnWarps][kAttnRows / 2][H];
 
+  pdl_trigger();
+  pdl_wait();
   const int bn = blockIdx.x, chunk = blockIdx.y, split = blockIdx.z;
   const int b = bn / p.Nkv, n = bn % p.Nkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -224,25 +295,36 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(AttnParams p) {
 #pragma unroll
       for (int j = 0; j < HV; j++) acc[r][j] *= alpha[r];
     const int ntok = min(32, key_len - blk * 32);
-    for (int t = 0; t < ntok; t++) {
-      float vv[HV];
-      const uint16_t* vr = p.vc + boff + (int64_t)t * H + lane * HV;
-      if (HV == 4) {
-        uint2 v = *reinterpret_cast<const uint2*>(vr);
-        vv[0] = bf16_bits_to_f32((uint16_t)(v.x & 0xffff));
-        vv[1] = bf16_bits_to_f32((uint16_t)(v.x >> 16));
-        vv[2] = bf16_bits_to_f32((uint16_t)(v.y & 0xffff));
-        vv[3] = bf16_bits_to_f32((uint16_t)(v.y >> 16));
-      } else {
+    for (int t0 = 0; t0 < ntok; t0 += 8) {  // eight value rows in flight at a time
+      float vv[8][HV];
 #pragma unroll
-        for (int j = 0; j < HV; j++) vv[j] = bf16_bits_to_f32(vr[j]);
+      for (int u = 0; u < 8; u++) {
+        const uint16_t* vr = p.vc + boff + (int64_t)(t0 + u) * H + lane * HV;
+        if (t0 + u < ntok) {  // slots past the cached length may hold anything
+          if (HV == 4) {
+            uint2 v = *reinterpret_cast<const uint2*>(vr);
+            vv[u][0] = bf16_bits_to_f32((uint16_t)(v.x & 0xffff));
+            vv[u][1] = bf16_bits_to_f32((uint16_t)(v.x >> 16));
+            vv[u][2] = bf16_bits_to_f32((uint16_t)(v.y & 0xffff));
+            vv[u][3] = bf16_bits_to_f32((uint16_t)(v.y >> 16));
+          } else {
+#pragma unroll
+            for (int j = 0; j < HV; j++) vv[u][j] = bf16_bits_to_f32(vr[j]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < HV; j++) vv[u][j] = 0.0f;
+        }
       }
 #pragma unroll
-      for (int r = 0; r < kAttnRows; r++) {
-        if (r < rows) {
-          const float pr = ps[warp][r][t];
+      for (int u = 0; u < 8; u++) {
 #pragma unroll
-          for (int j = 0; j < HV; j++) acc[r][j] = fmaf(pr, vv[j], acc[r][j]);
+        for (int r = 0; r < kAttnRows; r++) {
+          if (r < rows) {
+            const float pr = ps[warp][r][t0 + u];
+#pragma unroll
+            for (int j = 0; j < HV; j++) acc[r][j] = fmaf(pr, vv[u][j], acc[r][j]);
+          }
         }
       }
     }
@@ -286,6 +368,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(AttnParams p) {
 
 template <int H>
 __global__ void attn_merge_kernel(AttnParams p) {
+  pdl_trigger();
+  pdl_wait();
   const int bn = blockIdx.x, chunk = blockIdx.y;
   const int rows_total = p.Sq * p.R;
   const int row0 = chunk * kAttnRows;
@@ -327,8 +411,13 @@ extern "C" int tpx_rmsnorm(const uint16_t* x, const void* gamma, int gamma_is_f3
   TPX_REQUIRE(x && gamma && y, TPX_ERR_ARG, "rmsnorm: null pointer");
   TPX_REQUIRE(rows >= 0 && D > 0 && D % 8 == 0, TPX_ERR_ARG, "rmsnorm: D must be a positive multiple of 8 (D=%ld)", (long)D);
   if (rows == 0) return TPX_OK;
-  rmsnorm_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, (cudaStream_t)stream>>>(x, gamma, gamma_is_f32, eps, rows, (int)D, y);
-  TPX_LAUNCH_OK();
+  const bool aligned = (((uintptr_t)x | (uintptr_t)y | (uintptr_t)gamma) & 15) == 0;
+  if (rows <= 2048 && D <= kNormThreads * kNormVecs * 8 && aligned)
+    TPX_CUDA_OK(launch_pdl(rmsnorm_row_kernel, dim3((unsigned)rows), dim3(kNormThreads), 0, (cudaStream_t)stream, x, gamma, gamma_is_f32,
+                           eps, (int)D, y));
+  else
+    TPX_CUDA_OK(launch_pdl(rmsnorm_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, (cudaStream_t)stream, x, gamma, gamma_is_f32, eps,
+                           rows, (int)D, y));
   return TPX_OK;
 }
 
@@ -345,9 +434,8 @@ extern "C" int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const in
                 (long)capacity, (long)(offset + S));
   if (S == 0) return TPX_OK;
   int64_t total = B * S * (Nq + 2 * Nkv) * (H / 2);
-  rope_kv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(qkv, ep, pos, (int)B, (int)S, (int)Nq, (int)Nkv,
-                                                                                  (int)H, (int)MP, (int)HR, (int)Bpos, offset, dev_len, capacity, q_out, kc, vc);
-  TPX_LAUNCH_OK();
+  TPX_CUDA_OK(launch_pdl(rope_kv_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, qkv, ep, pos, (int)B,
+                         (int)S, (int)Nq, (int)Nkv, (int)H, (int)MP, (int)HR, (int)Bpos, offset, dev_len, capacity, q_out, kc, vc));
   return TPX_OK;
 }
 
@@ -357,8 +445,8 @@ static int attn_plan(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t key_
   int nblocks = (int)((key_len + 31) / 32);
   int s = 1;
   int sms = sm_count();
-  // split the KV range while the grid is short of two CTAs per SM and every split keeps >= 8 blocks per warp round
-  while (ctas * s < 2 * sms && nblocks / (s * 2) >= kAttnWarps * 2 && s < 64) s *= 2;
+  // split the KV range while the grid is short of two CTAs per SM and every split keeps a block for each warp
+  while (ctas * s < 2 * sms && nblocks / (s * 2) >= kAttnWarps && s < 64) s *= 2;
   *splits = s;
   return 0;
 }
@@ -391,14 +479,12 @@ extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16
   dim3 grid((unsigned)(B * Nkv), (unsigned)p.chunks, (unsigned)p.splits);
   TPX_REQUIRE(p.chunks <= 65535, TPX_ERR_UNSUPPORTED, "attention: too many query rows in one call");
   cudaStream_t st = (cudaStream_t)stream;
-  if (H == 128) attn_kernel<128><<<grid, kAttnWarps * 32, 0, st>>>(p);
-  else attn_kernel<64><<<grid, kAttnWarps * 32, 0, st>>>(p);
-  TPX_LAUNCH_OK();
+  if (H == 128) TPX_CUDA_OK(launch_pdl(attn_kernel<128>, grid, dim3(kAttnWarps * 32), 0, st, p));
+  else TPX_CUDA_OK(launch_pdl(attn_kernel<64>, grid, dim3(kAttnWarps * 32), 0, st, p));
   if (p.splits > 1) {
     dim3 g2((unsigned)(B * Nkv), (unsigned)p.chunks);
-    if (H == 128) attn_merge_kernel<128><<<g2, 256, 0, st>>>(p);
-    else attn_merge_kernel<64><<<g2, 256, 0, st>>>(p);
-    TPX_LAUNCH_OK();
+    if (H == 128) TPX_CUDA_OK(launch_pdl(attn_merge_kernel<128>, g2, dim3(256), 0, st, p));
+    else TPX_CUDA_OK(launch_pdl(attn_merge_kernel<64>, g2, dim3(256), 0, st, p));
   }
   return TPX_OK;
 }

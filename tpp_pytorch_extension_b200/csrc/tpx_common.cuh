@@ -61,4 +61,27 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 
 int sm_count();
 
+// Programmatic dependent launch. Every kernel of the decoder-layer path starts with pdl_trigger() (the next
+// kernel in the stream may be scheduled and run its prologue while this one works) and calls pdl_wait() before
+// it touches global memory that an earlier kernel may have written or may still read: the wait returns once
+// every earlier grid has completed and its writes are visible, so the memory order is that of plain stream
+// launches and only launch latency and prologues overlap.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace tpx

@@ -29,123 +29,10 @@
 // (one slot per contributor); a small second kernel, launched as a programmatic dependent so that its launch
 // latency hides behind the GEMM, adds them in CTA order and runs the epilogue. Doing this inside the GEMM (last
 // arriver per tile) cost a store -> atomic -> load chain at loaded-memory latency (~2 us per hop).
-#include <cuda.h>
-#include <stdlib.h>
-
-#include "tpx_common.cuh"
+#include "tpx_tc_ptx.cuh"
 #include <cuda_fp8.h>
 
 namespace tpx {
-
-constexpr unsigned kTcSpinLimit = 1u << 22;
-constexpr int kTcThreads = 192;
-constexpr size_t kTcCounterBytes = 64 * 1024;  // arrival counters (one per output tile) + error word at the end
-
-struct TcParams {
-  const uint8_t* sfa;   // [ceil(N/128)][KS][512] scale-factor blocks of W
-  const uint8_t* sfa2;
-  const uint8_t* sfb;   // [TM][KS][512] scale-factor blocks of the activation terms
-  const uint16_t* bias;
-  const uint16_t* mul_in;
-  const uint16_t* res;
-  float res_scale;
-  uint16_t* y;
-  float* partial;       // [grid][2 slots][NW][TOK][128]
-  unsigned* counters;
-  unsigned* err;
-  int M, N, K;
-  int KS;               // k units (of UKS k steps of 128) per tile
-  int TN, TM;           // output tiles along features / tokens
-  int act;
-  int whole_tiles;      // 1: every CTA owns whole output tiles (no partial tiles, no fix-up)
-  unsigned long long* tl;  // optional per-CTA timeline (8 globaltimer stamps each), null in normal use
-  int dbg;              // debug knobs for timing experiments: 1 = skip MMAs, 2 = skip weight copies
-};
-
-__device__ __forceinline__ void tc_stamp(const TcParams& p, int slot) {
-  if (p.tl) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    p.tl[(size_t)blockIdx.x * 8 + slot] = t;
-  }
-}
-
-// ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void tc_mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void tc_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void tc_mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool tc_mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-               : "=r"(ok)
-               : "r"(bar), "r"(parity)
-               : "memory");
-  return ok != 0;
-}
-// Bounded wait: false when the barrier never flipped (the caller reports and leaves).
-__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity) {
-  for (unsigned spins = 0; spins < kTcSpinLimit; spins++)
-    if (tc_mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-__device__ __forceinline__ void tc_tma_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(c0), "r"(c1), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tc_bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
-                                       uint32_t sfb, uint32_t accumulate) {
-  asm volatile(
-      "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
-      "  tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p; }" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
-      : "memory");
-}
-// 32 rows x 16 bytes, rows 16 bytes apart, no swizzle: 8-row core matrices 128 bytes apart.
-__device__ __forceinline__ uint64_t tc_sf_desc(uint32_t saddr) {
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(128 >> 4) << 32) | (1ull << 46);
-}
-// shared -> tensor memory: 32 lanes x 128 bits, replicated to the four 32-lane quarters
-__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-__device__ __forceinline__ void tc_st_x4(uint32_t taddr, uint4 v) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w)
-               : "memory");
-}
-__device__ __forceinline__ void tc_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-
-// K-major operand tile, 128-byte rows, 128-byte swizzle: 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
 
 // ---------------------------------------------------------------- activation split
 // x[M][K] bf16 -> two E4M3 terms and the UE8M0 scale blocks, one thread per (token, 32-wide block), written
@@ -154,11 +41,15 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
 //   sfb   [TM][KU][UKS][ceil(2*TOK/128)][512]   scale blocks over the 2*TOK MMA columns (hi columns, then lo
 //         columns with the same scales): byte (c%32)*16 + ((c%128)/32)*4 + j of block c/128 for column c
 // Padding rows and padding columns get zeros with scale 2^0.
+// rowmap 1 (tokens on the M side of the MMA, one token tile): a k step holds 2*TOK rows with the hi row of token r
+// at 32*(r/16) + r%16 and its lo row 16 further, so that both terms of a token sit in the same 32-lane quarter of
+// tensor memory; one scale block of 128 rows per k step.
 __global__ void split_activations_kernel(const uint16_t* __restrict__ x, int M, int K, int Mpad, int KS, int TOK, int UKS,
-                                         uint8_t* __restrict__ terms, uint8_t* __restrict__ sfb) {
+                                         int rowmap, uint8_t* __restrict__ terms, uint8_t* __restrict__ sfb) {
   // let the GEMM that consumes these terms start its prologue and weight prefetch now; it waits for this
   // grid to finish (griddepcontrol.wait) before it touches the terms
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  pdl_trigger();
+  pdl_wait();  // x and the scratch belong to earlier grids until they have completed
   const int nb = KS * 4;
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)Mpad * nb) return;
@@ -210,6 +101,19 @@ __global__ void split_activations_kernel(const uint16_t* __restrict__ x, int M, 
   const int tm = tok / TOK, r = tok % TOK, ks = kb / 4, j = kb % 4;
   const int KU = KS / UKS, ku = ks / UKS, kk = ks % UKS;
   const size_t step = ((size_t)tm * KU + ku) * UKS + kk;  // k step in fetch order
+  if (rowmap == 1) {
+    const int rh = 32 * (r / 16) + (r % 16), rl = rh + 16;
+    uint4* dh = reinterpret_cast<uint4*>(terms + (step * 2 * TOK + rh) * 128 + j * 32);
+    uint4* dl = reinterpret_cast<uint4*>(terms + (step * 2 * TOK + rl) * 128 + j * 32);
+    dh[0] = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+    dh[1] = make_uint4(ph[4], ph[5], ph[6], ph[7]);
+    dl[0] = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+    dl[1] = make_uint4(pl[4], pl[5], pl[6], pl[7]);
+    uint8_t* blk = sfb + step * 512;
+    blk[(rh % 32) * 16 + (rh / 32) * 4 + j] = (uint8_t)(e + 127);
+    blk[(rl % 32) * 16 + (rl / 32) * 4 + j] = (uint8_t)(e + 127);
+    return;
+  }
   uint4* dh = reinterpret_cast<uint4*>(terms + ((step * 2 + 0) * TOK + r) * 128 + j * 32);
   uint4* dl = reinterpret_cast<uint4*>(terms + ((step * 2 + 1) * TOK + r) * 128 + j * 32);
   dh[0] = make_uint4(ph[0], ph[1], ph[2], ph[3]);
@@ -291,14 +195,53 @@ struct TcCfg {
   static_assert(COLS_RAW <= 512, "tensor memory");
 };
 
-__device__ __forceinline__ void tc_finish(const TcParams& p, int tok, int n, float v, float v2, bool dual) {
-  size_t o = (size_t)tok * p.N + n;
-  if (p.bias) v += bf16_bits_to_f32(p.bias[n]);
-  v = apply_act(v, p.act);
-  if (dual) v *= v2;
-  if (p.mul_in) v *= bf16_bits_to_f32(p.mul_in[o]);
-  if (p.res) v += bf16_bits_to_f32(p.res[o]) * p.res_scale;
-  p.y[o] = f32_to_bf16_bits(v);
+// Epilogue of 16 consecutive tokens of one output feature n: bias, activation, gate multiply, residual, bf16 store.
+// Straight-line code over the 16 tokens (loads first, then arithmetic, then stores) so that the tokens' dependent
+// chains overlap; only the loads and stores are predicated on the token being inside M.
+template <bool DUAL>
+__device__ __forceinline__ void tc_finish16(const TcParams& p, int tok0, int n, const float (&v)[16], const float (&v2)[16]) {
+  const int live = p.M - tok0;  // tokens tok0 .. tok0+live-1 exist
+  const size_t o0 = (size_t)tok0 * p.N + n;
+  const float b = p.bias ? bf16_bits_to_f32(p.bias[n]) : 0.0f;
+  float x[16];
+#pragma unroll
+  for (int j = 0; j < 16; j++) x[j] = v[j] + b;
+  switch (p.act) {
+    case TPX_ACT_GELU:
+#pragma unroll
+      for (int j = 0; j < 16; j++) x[j] = 0.5f * x[j] * (1.0f + erff(x[j] * 0.70710678118654752f));
+      break;
+    case TPX_ACT_SILU:
+#pragma unroll
+      for (int j = 0; j < 16; j++) x[j] = __fdividef(x[j], 1.0f + __expf(-x[j]));
+      break;
+    case TPX_ACT_RELU:
+#pragma unroll
+      for (int j = 0; j < 16; j++) x[j] = fmaxf(x[j], 0.0f);
+      break;
+    default: break;
+  }
+  if (DUAL) {
+#pragma unroll
+    for (int j = 0; j < 16; j++) x[j] *= v2[j];
+  }
+  if (p.mul_in) {
+    uint16_t t[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) t[j] = j < live ? p.mul_in[o0 + (size_t)j * p.N] : (uint16_t)0;
+#pragma unroll
+    for (int j = 0; j < 16; j++) x[j] *= bf16_bits_to_f32(t[j]);
+  }
+  if (p.res) {
+    uint16_t t[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) t[j] = j < live ? p.res[o0 + (size_t)j * p.N] : (uint16_t)0;
+#pragma unroll
+    for (int j = 0; j < 16; j++) x[j] += bf16_bits_to_f32(t[j]) * p.res_scale;
+  }
+#pragma unroll
+  for (int j = 0; j < 16; j++)
+    if (j < live) p.y[o0 + (size_t)j * p.N] = f32_to_bf16_bits(x[j]);
 }
 
 template <int TOK, bool DUAL, int UKS>
@@ -371,20 +314,35 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         tc_bulk_g2s(sb + C::X_ROWS * 128 + C::A_TILES * 512, p.sfb + ((size_t)tm * p.KS + ks) * UKS * C::SFB_PER * 512,
                     UKS * C::SFB_PER * 512, bar);
       };
+      // Units further ahead than the shared-memory stages reach are prefetched into L2: the bytes in flight from
+      // HBM are then not limited by shared memory, and the stage copies find their data at L2 latency.
+      auto prefetch_w = [&](int tn, int ks) {
+        const int wtile = (tn * p.KS + ks) * C::A_TILES;
+#pragma unroll
+        for (int r = 0; r < C::A_TILES / 2; r++) tc_prefetch_2d(&tmW, 0, (wtile + 2 * r) * 128);
+        tc_prefetch_bulk(p.sfa + (size_t)wtile * 512, C::A_TILES * 512);
+      };
       // the first stages' weights go out before this grid is allowed to see the split kernel's output
       const int early = nunits < C::STAGES ? nunits : C::STAGES;
-      {
-        int tile = tile0, ks = ks0;
-        for (int it = 0; it < early; it++) {
-          fetch_w(it, tile / p.TM, ks);
-          if (++ks == p.KS) { ks = 0; tile++; }
-        }
+      int ptile = tile0, pks = ks0, pit = 0;  // prefetch cursor
+      for (; pit < early; pit++) {
+        fetch_w(pit, ptile / p.TM, pks);
+        if (++pks == p.KS) { pks = 0; ptile++; }
+      }
+      for (; pit < nunits && pit < early + p.pf; pit++) {
+        prefetch_w(ptile / p.TM, pks);
+        if (++pks == p.KS) { pks = 0; ptile++; }
       }
       asm volatile("griddepcontrol.wait;" ::: "memory");
       int tile = tile0, ks = ks0;
       for (int it = 0; it < nunits; it++) {
         const int s = it % C::STAGES;
         const int tn = tile / p.TM, tm = tile % p.TM;
+        if (pit < nunits && pit < it + C::STAGES + p.pf) {
+          prefetch_w(ptile / p.TM, pks);
+          pit++;
+          if (++pks == p.KS) { pks = 0; ptile++; }
+        }
         if (it >= C::STAGES) {
           if (!tc_wait(tc_smem_u32(&bar_empty[s]), (uint32_t)((it / C::STAGES - 1) & 1))) {
             atomicExch(p.err, 2u);
@@ -482,36 +440,31 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         float* myslot = p.partial + (((size_t)blockIdx.x * 2 + (tile == tile0 ? 0 : 1)) * C::NW) * TOK * 128 + (size_t)row * TOK;
 #pragma unroll 1
         for (int c0 = 0; c0 < TOK; c0 += 16) {
-          uint32_t r0[16], r1[16];
+          float r0[16], r1[16];
           {  // hi columns + lo columns
-            uint32_t t0[16], t1[16];
-            tc_ld_x16(tmem + lane_base + c0, r0);
+            uint32_t a0[16], t0[16], a1[16], t1[16];
+            tc_ld_x16(tmem + lane_base + c0, a0);
             tc_ld_x16(tmem + lane_base + TOK + c0, t0);
             if (DUAL) {
-              tc_ld_x16(tmem + lane_base + C::NCOL + c0, r1);
+              tc_ld_x16(tmem + lane_base + C::NCOL + c0, a1);
               tc_ld_x16(tmem + lane_base + C::NCOL + TOK + c0, t1);
             }
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
             for (int j = 0; j < 16; j++) {
-              r0[j] = __float_as_uint(__uint_as_float(r0[j]) + __uint_as_float(t0[j]));
-              if (DUAL) r1[j] = __float_as_uint(__uint_as_float(r1[j]) + __uint_as_float(t1[j]));
+              r0[j] = __uint_as_float(a0[j]) + __uint_as_float(t0[j]);
+              r1[j] = DUAL ? __uint_as_float(a1[j]) + __uint_as_float(t1[j]) : 0.0f;
             }
           }
           if (whole) {
-            if (n < p.N) {
-#pragma unroll
-              for (int j = 0; j < 16; j++)
-                if (tok0 + c0 + j < p.M)
-                  tc_finish(p, tok0 + c0 + j, n, __uint_as_float(r0[j]), DUAL ? __uint_as_float(r1[j]) : 0.0f, DUAL);
-            }
+            if (n < p.N && tok0 + c0 < p.M) tc_finish16<DUAL>(p, tok0 + c0, n, r0, r1);
           } else {
 #pragma unroll
             for (int q = 0; q < 4; q++) {
-              __stcg(reinterpret_cast<uint4*>(myslot + c0) + q, make_uint4(r0[4 * q], r0[4 * q + 1], r0[4 * q + 2], r0[4 * q + 3]));
+              __stcg(reinterpret_cast<float4*>(myslot + c0) + q, make_float4(r0[4 * q], r0[4 * q + 1], r0[4 * q + 2], r0[4 * q + 3]));
               if (DUAL)
-                __stcg(reinterpret_cast<uint4*>(myslot + (size_t)TOK * 128 + c0) + q,
-                       make_uint4(r1[4 * q], r1[4 * q + 1], r1[4 * q + 2], r1[4 * q + 3]));
+                __stcg(reinterpret_cast<float4*>(myslot + (size_t)TOK * 128 + c0) + q,
+                       make_float4(r1[4 * q], r1[4 * q + 1], r1[4 * q + 2], r1[4 * q + 3]));
             }
           }
         }
@@ -542,6 +495,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 template <bool DUAL>
 __global__ void __launch_bounds__(128) tc_fixup_kernel(TcParams p, int TOK, int G) {
   constexpr int NW = DUAL ? 2 : 1;
+  pdl_trigger();
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int tile = blockIdx.x, c0 = blockIdx.y * 16, row = threadIdx.x;
   const long long U = (long long)p.TN * p.TM * p.KS;
@@ -585,9 +539,7 @@ __global__ void __launch_bounds__(128) tc_fixup_kernel(TcParams p, int TOK, int 
       }
     }
   }
-#pragma unroll
-  for (int j = 0; j < 16; j++)
-    if (tok0 + c0 + j < p.M) tc_finish(p, tok0 + c0 + j, n, v[j], v2[j], DUAL);
+  tc_finish16<DUAL>(p, tok0 + c0, n, v, v2);
 }
 
 // ---------------------------------------------------------------- host side
@@ -608,7 +560,7 @@ static EncodeTiledFn encode_fn() {
 }
 
 // 2-D tensor of `rows` rows of 128 elements (row_bytes apart), box = 128 elements x box_rows, 128-byte swizzle.
-static int make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+int tc_make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
   TPX_REQUIRE(fn, TPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t gdim[2] = {128, rows};
@@ -622,10 +574,18 @@ static int make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, ui
   return TPX_OK;
 }
 
-static inline int tc_padded_ks(int64_t K, bool pair) {
+int tc_padded_ks(int64_t K, bool pair) {
   int ks = (int)((K + 127) / 128);
   int m = pair ? 2 : 4;
   return (ks + m - 1) / m * m;
+}
+
+int tc_launch_split(const uint16_t* x, int M, int K, int Mpad, int KS, int TOK, int UKS, int rowmap, uint8_t* terms, uint8_t* sfb,
+                    cudaStream_t st) {
+  long long threads = (long long)Mpad * KS * 4;
+  TPX_CUDA_OK(launch_pdl(split_activations_kernel, dim3((unsigned)((threads + 127) / 128)), dim3(128), 0, st, x, M, K, Mpad, KS, TOK, UKS,
+                         rowmap, terms, sfb));
+  return TPX_OK;
 }
 
 struct TcPlan {
@@ -701,6 +661,7 @@ static int tc_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams&
 using namespace tpx;
 
 static unsigned long long* g_tc_timeline = nullptr;
+
 // Debug aid: when set, every CTA of the next tensor-core GEMMs writes 8 globaltimer stamps to `buf`.
 extern "C" void tpx_debug_tc_timeline(void* buf) { g_tc_timeline = reinterpret_cast<unsigned long long*>(buf); }
 
@@ -725,14 +686,26 @@ extern "C" int tpx_repack_mxfp4_tc(const uint8_t* codes, const uint8_t* scales, 
   return TPX_OK;
 }
 
-extern "C" size_t tpx_qlinear_mxfp4_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int pair) {
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
-  return tc_plan(M, N, K, pair != 0).total;
+// With TPX_TC_WIDE=1 up to 64 tokens go to the kernel that puts the weights on the wide (N) side of the MMA. Both
+// kernels stream weights at about the same pace (shared-memory bandwidth: the unpacking copy writes 2 bytes per
+// packed byte and the MMA reads them back), so the default stays with the one kernel that serves every M.
+static bool tc_wide(int64_t M) {
+  const char* e = getenv("TPX_TC_WIDE");
+  return e && atoi(e) != 0 && M <= 64;
 }
 
-extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M, int64_t N,
-                                    int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
-                                    float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream) {
+static size_t tc_scratch_need(int64_t M, int64_t N, int64_t K, bool pair, bool wide) {
+  return wide ? tcw_scratch_bytes(M, N, K, pair) : tc_plan(M, N, K, pair).total;
+}
+
+extern "C" size_t tpx_qlinear_mxfp4_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int pair) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  return tc_scratch_need(M, N, K, pair != 0, tc_wide(M));
+}
+
+static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M, int64_t N, int64_t K,
+                  const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y,
+                  void* scratch, size_t scratch_bytes, void* stream, bool wide) {
   TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear_mxfp4_tc: bad shape");
   if (M == 0) return TPX_OK;
   TPX_REQUIRE(wq && sfa && x && y, TPX_ERR_ARG, "qlinear_mxfp4_tc: null pointer");
@@ -742,6 +715,13 @@ extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int p
   TPX_REQUIRE(((uintptr_t)wq & 31) == 0 && ((uintptr_t)sfa & 15) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)scratch & 255) == 0,
               TPX_ERR_ARG, "qlinear_mxfp4_tc: misaligned pointer");
   const bool dual = pair != 0;
+  if (wide) {
+    TcParams b = {};
+    b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act; b.tl = g_tc_timeline;
+    { const char* e = getenv("TPX_TC_DBG"); b.dbg = e ? atoi(e) : 0; }
+    { const char* e = getenv("TPX_TC_PF"); b.pf = e ? atoi(e) : 8; }
+    return tcw_run(wq, sfa, dual, x, M, N, K, b, scratch, scratch_bytes, (cudaStream_t)stream);
+  }
   TcPlan pl = tc_plan(M, N, K, dual);
   TPX_REQUIRE(scratch && scratch_bytes >= pl.total, TPX_ERR_SCRATCH, "qlinear_mxfp4_tc: scratch of %zu bytes needed, %zu given",
               pl.total, scratch_bytes);
@@ -749,27 +729,27 @@ extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int p
   unsigned char* sc = reinterpret_cast<unsigned char*>(scratch);
   uint8_t *terms = sc + pl.off_terms, *sfb = sc + pl.off_sfb;
   {
-    long long threads = (long long)pl.Mpad * pl.KS * 4;
-    split_activations_kernel<<<(unsigned)((threads + 127) / 128), 128, 0, st>>>(x, (int)M, (int)K, pl.Mpad, pl.KS, pl.tok, pl.uks, terms, sfb);
-    TPX_LAUNCH_OK();
+    int rc0 = tc_launch_split(x, (int)M, (int)K, pl.Mpad, pl.KS, pl.tok, pl.uks, 0, terms, sfb, st);
+    if (rc0) return rc0;
   }
   CUtensorMap mw, mx;
   // weight: 64-byte rows of 128 codes, 256 rows (two tiles) per request; activation terms: 128-byte rows
   int rc;
   { const char* e = getenv("TPX_TC_DBG"); if (e && (atoi(e) & 4)) {  // timing experiment: raw byte copy instead of the unpacking copy
       EncodeTiledFn fn = encode_fn();
-      cuuint64_t gdim[2] = {64, (uint64_t)pl.TN * pl.KS * (dual ? 2 : 1) * 128};
-      cuuint64_t gstr[1] = {64};
-      cuuint32_t box[2] = {64, 256};
+      const bool wide_rows = (atoi(e) & 8) != 0;  // 128-byte rows instead of 64-byte rows, same bytes per request
+      cuuint64_t gdim[2] = {wide_rows ? 128u : 64u, (uint64_t)pl.TN * pl.KS * (dual ? 2 : 1) * (wide_rows ? 64 : 128)};
+      cuuint64_t gstr[1] = {wide_rows ? 128u : 64u};
+      cuuint32_t box[2] = {wide_rows ? 128u : 64u, wide_rows ? 128u : 256u};
       cuuint32_t estr[2] = {1, 1};
       CUresult r = fn(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(wq), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       rc = r == CUDA_SUCCESS ? TPX_OK : TPX_ERR_CUDA;
     } else
-      rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, (uint64_t)pl.TN * pl.KS * (dual ? 2 : 1) * 128, 64, 256);
+      rc = tc_make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, (uint64_t)pl.TN * pl.KS * (dual ? 2 : 1) * 128, 64, 256);
   }
   if (rc) return rc;
-  rc = make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, terms, (uint64_t)pl.Mpad * pl.KS * 2, 128, (uint32_t)pl.xbox);
+  rc = tc_make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, terms, (uint64_t)pl.Mpad * pl.KS * 2, 128, (uint32_t)pl.xbox);
   if (rc) return rc;
   TcParams p;
   p.sfa = sfa; p.sfa2 = nullptr; p.sfb = sfb; p.bias = bias; p.mul_in = mul_in; p.res = res; p.res_scale = res_scale; p.y = y;
@@ -778,6 +758,7 @@ extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int p
   p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = pl.TM; p.act = act; p.whole_tiles = pl.whole_tiles; p.tl = g_tc_timeline;
   { const char* e = getenv("TPX_TC_DBG"); p.dbg = e ? atoi(e) : 0; }
+  { const char* e = getenv("TPX_TC_PF"); p.pf = e ? atoi(e) : 6; }
   if (dual) {
     switch (pl.tok) {
       case 16: return tc_launch<16, true, 2>(mw, mx, p, pl.grid, st);
@@ -791,6 +772,12 @@ extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int p
     case 64: return tc_launch<64, false, 2>(mw, mx, p, pl.grid, st);
     default: return tc_launch<128, false, 2>(mw, mx, p, pl.grid, st);
   }
+}
+
+extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M, int64_t N,
+                                    int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
+                                    float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream) {
+  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, tc_wide(M));
 }
 
 // ---------------------------------------------------------------- variant that allocates nothing
@@ -825,7 +812,10 @@ extern "C" int tpx_qlinear_mxfp4_tc_static(const uint8_t* wq, const uint8_t* sfa
                                            const uint16_t* res, float res_scale, uint16_t* y, void* stream) {
   TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear_mxfp4_tc_static: bad shape");
   if (M == 0) return TPX_OK;
-  const size_t need = tpx_qlinear_mxfp4_tc_scratch_bytes(M, N, K, pair);
+  // the kernel whose scratch fits the array: the wide one's partial slots grow with the token count
+  bool wide = tc_wide(M);
+  if (wide && tc_scratch_need(M, N, K, pair != 0, true) > kStaticScratchBytes) wide = false;
+  const size_t need = tc_scratch_need(M, N, K, pair != 0, wide);
   TPX_REQUIRE(need <= kStaticScratchBytes, TPX_ERR_SCRATCH,
               "qlinear_mxfp4_tc_static: M=%ld N=%ld K=%ld needs %zu bytes of scratch, the built-in array holds %zu; "
               "use tpx_qlinear_mxfp4_tc with a caller-provided buffer",
@@ -835,5 +825,5 @@ extern "C" int tpx_qlinear_mxfp4_tc_static(const uint8_t* wq, const uint8_t* sfa
   if (rc) return rc;
   // the array keeps whatever the previous call left: the arrival counters and the error word must start at zero
   TPX_CUDA_OK(cudaMemsetAsync(sc, 0, kTcCounterBytes, (cudaStream_t)stream));
-  return tpx_qlinear_mxfp4_tc(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, sc, kStaticScratchBytes, stream);
+  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, sc, kStaticScratchBytes, stream, wide);
 }

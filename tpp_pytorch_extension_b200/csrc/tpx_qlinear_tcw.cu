@@ -1,0 +1,495 @@
+// MXFP4 weight-only linear for few tokens (M <= 64: decoding), tensor-core path with the WEIGHTS on the wide side.
+//
+// A tcgen05.mma of shape 128 x N x 32 reads its 128-row A slab from shared memory at a fixed pace whatever N is, so
+// a kernel that puts 128 weight rows on the A side consumes at most one 2 KiB slab of packed weights per ~110
+// cycles: about 30 bytes/ns per SM, well below an SM's share of HBM bandwidth. Here the roles are swapped:
+//   A (128 rows)  = the activation terms of up to 64 tokens (hi and lo E4M3 terms are separate rows),
+//   B (256 rows)  = 256 output features of packed E2M1 weights (a gate tile and its up tile, or two adjacent tiles),
+//   D             = [token term][feature] in tensor memory, 256 fp32 columns.
+// Every MMA then consumes 4 KiB of packed weights in the same time, and the weight stream is bounded by memory.
+//
+// Replaces the same reference functions as tpx_qlinear_tc.cu (fc_plain / fc_gate_up of
+// src/csrc/llm/fused_llm_infer.cpp on MXFP4 weights) for M <= 64; layouts of the packed weights are shared.
+//
+// Work split: stream-K over (feature tile, k step) with whole tiles when the tile count suits the SM count;
+// partial tiles go to per-CTA slots and a second, programmatically launched kernel sums them in CTA order.
+#include "tpx_tc_ptx.cuh"
+
+namespace tpx {
+
+template <int TOKP>
+struct TcwCfg {
+  static constexpr int X_BYTES = 2 * TOKP * 128;        // both terms of one k step (128 k values of TOKP tokens)
+  static constexpr int B_BYTES = 256 * 128;             // 256 features x 128 k values, unpacked to 16-byte-aligned groups
+  static constexpr int B_TX = 256 * 64;                 // what the copy accounts for (packed bytes)
+  static constexpr int SF_BYTES = 512 + 2 * 512;        // activation scale block, two weight scale blocks
+  static constexpr int RAW = X_BYTES + B_BYTES + SF_BYTES;
+  static constexpr int STAGE_BYTES = (RAW + 1023) / 1024 * 1024;
+  static constexpr int BUDGET = 227 * 1024 - 2048;
+  static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
+  static constexpr int SF_COLS = 12;                    // 4 (activations) + 8 (weights) columns per stage
+  static constexpr int D_COLS = 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int EPI_WARPS = TOKP / 16;           // 32-lane quarters of tensor memory that hold tokens
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
+  static_assert(D_COLS + STAGES * SF_COLS <= 512, "tensor memory");
+  static_assert(X_BYTES + B_BYTES >= 128 * 128, "the A descriptor spans 128 rows inside the stage");
+};
+
+// Eight consecutive output features of one token: bias, activation, gate multiply, residual, one 16-byte store.
+template <bool DUAL>
+__device__ __forceinline__ void tcw_finish8(const TcParams& p, int tok, int n, const float (&v)[8], const float (&u)[8]) {
+  const size_t o = (size_t)tok * p.N + n;
+  float x[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) x[i] = v[i];
+  auto unpack = [](const uint4& q, float (&f)[8]) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      f[2 * i] = bf16_bits_to_f32((uint16_t)(w[i] & 0xffff));
+      f[2 * i + 1] = bf16_bits_to_f32((uint16_t)(w[i] >> 16));
+    }
+  };
+  uint4 qb = make_uint4(0, 0, 0, 0), qm = qb, qr = qb;
+  if (p.bias) qb = *reinterpret_cast<const uint4*>(p.bias + n);
+  if (p.mul_in) qm = *reinterpret_cast<const uint4*>(p.mul_in + o);
+  if (p.res) qr = *reinterpret_cast<const uint4*>(p.res + o);
+  if (p.bias) {
+    float f[8];
+    unpack(qb, f);
+#pragma unroll
+    for (int i = 0; i < 8; i++) x[i] += f[i];
+  }
+  switch (p.act) {
+    case TPX_ACT_GELU:
+#pragma unroll
+      for (int i = 0; i < 8; i++) x[i] = 0.5f * x[i] * (1.0f + erff(x[i] * 0.70710678118654752f));
+      break;
+    case TPX_ACT_SILU:
+#pragma unroll
+      for (int i = 0; i < 8; i++) x[i] = __fdividef(x[i], 1.0f + __expf(-x[i]));
+      break;
+    case TPX_ACT_RELU:
+#pragma unroll
+      for (int i = 0; i < 8; i++) x[i] = fmaxf(x[i], 0.0f);
+      break;
+    default: break;
+  }
+  if (DUAL) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) x[i] *= u[i];
+  }
+  if (p.mul_in) {
+    float f[8];
+    unpack(qm, f);
+#pragma unroll
+    for (int i = 0; i < 8; i++) x[i] *= f[i];
+  }
+  if (p.res) {
+    float f[8];
+    unpack(qr, f);
+#pragma unroll
+    for (int i = 0; i < 8; i++) x[i] += f[i] * p.res_scale;
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) w[i] = (uint32_t)f32_to_bf16_bits(x[2 * i]) | ((uint32_t)f32_to_bf16_bits(x[2 * i + 1]) << 16);
+  *reinterpret_cast<uint4*>(p.y + o) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// p.TN counts the 256-feature tiles here (a gate/up pair: 128 + 128), p.TM is 1, p.KS the k steps of 128.
+template <int TOKP, bool DUAL>
+__global__ void __launch_bounds__(kTcThreads, 1)
+qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, TcParams p, const uint8_t* wq,
+                   int tiles128) {
+  using C = TcwCfg<TOKP>;
+  extern __shared__ unsigned char tcw_smem_raw[];
+  __shared__ __align__(8) unsigned long long bar_full[C::STAGES], bar_empty[C::STAGES];
+  __shared__ __align__(8) unsigned long long bar_acc_full, bar_acc_empty;
+  __shared__ uint32_t tmem_holder;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = (tc_smem_u32(tcw_smem_raw) + 1023u) & ~1023u;
+
+  const long long U = (long long)p.TN * p.KS;
+  const long long G = gridDim.x;
+  const long long T = p.TN;
+  const long long u0 = p.whole_tiles ? ((long long)blockIdx.x * T / G) * p.KS : (long long)blockIdx.x * U / G;
+  const long long u1 = p.whole_tiles ? (((long long)blockIdx.x + 1) * T / G) * p.KS : ((long long)blockIdx.x + 1) * U / G;
+  const int nunits = (int)(u1 - u0);
+  const int tile0 = (int)(u0 / p.KS), ks0 = (int)(u0 % p.KS);
+
+  if (threadIdx.x == 0) tc_stamp(p, 0);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; s++) {
+      tc_mbar_init(tc_smem_u32(&bar_full[s]), 1);
+      tc_mbar_init(tc_smem_u32(&bar_empty[s]), 1);
+    }
+    tc_mbar_init(tc_smem_u32(&bar_acc_full), 1);
+    tc_mbar_init(tc_smem_u32(&bar_acc_empty), C::EPI_WARPS);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(&tmem_holder)),
+                 "r"((uint32_t)C::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_holder;
+  if (threadIdx.x == 0) tc_stamp(p, 1);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the fix-up kernel may get its CTAs ready
+
+  // weight tiles (of 128 features) of feature tile t at k step ks: a pair is stored as [t][ks][gate, up], single
+  // weights as [tile128][ks], so the two halves of a 256-feature tile are p.KS tiles apart
+  auto wtile_a = [&](int t, int ks) { return DUAL ? (t * p.KS + ks) * 2 : (2 * t * p.KS + ks); };
+  auto wtile_b = [&](int t, int ks) { return DUAL ? (t * p.KS + ks) * 2 + 1 : ((2 * t + 1) * p.KS + ks); };
+  auto has_b = [&](int t) { return DUAL || 2 * t + 1 < tiles128; };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      auto fetch_w = [&](int s, int t, int ks) {
+        const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
+        const uint32_t bar = tc_smem_u32(&bar_full[s]);
+        const uint32_t sb = st + C::X_BYTES, ssf = sb + C::B_BYTES + 512;
+        const bool second = has_b(t);
+        tc_mbar_expect_tx(bar, C::X_BYTES + 512 + (second ? C::B_TX + 1024 : C::B_TX / 2 + 512));
+        const int ta = wtile_a(t, ks), tb = wtile_b(t, ks);
+        if (DUAL) {
+          tc_tma_2d(sb, &tmW, 0, ta * 128, bar);  // 256 rows: gate tile and up tile are adjacent
+          tc_bulk_g2s(ssf, p.sfa + (size_t)ta * 512, 1024, bar);
+        } else {
+          tc_tma_2d(sb, &tmW, 0, ta * 128, bar);
+          tc_bulk_g2s(ssf, p.sfa + (size_t)ta * 512, 512, bar);
+          if (second) {
+            tc_tma_2d(sb + C::B_BYTES / 2, &tmW, 0, tb * 128, bar);
+            tc_bulk_g2s(ssf + 512, p.sfa + (size_t)tb * 512, 512, bar);
+          }
+        }
+      };
+      auto fetch_x = [&](int s, int ks) {
+        const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
+        const uint32_t bar = tc_smem_u32(&bar_full[s]);
+        tc_tma_2d(st, &tmX, 0, ks * 2 * TOKP, bar);
+        tc_bulk_g2s(st + C::X_BYTES + C::B_BYTES, p.sfb + (size_t)ks * 512, 512, bar);
+      };
+      // Packed weights further ahead than the stages reach are prefetched into L2 with one request per 8 KiB or
+      // 16 KiB run, so that the bytes in flight from HBM are not limited by shared memory.
+      auto prefetch_w = [&](int t, int ks) {
+        if (DUAL) {
+          tc_prefetch_bulk(wq + (size_t)wtile_a(t, ks) * 8192, 16384);
+        } else {
+          tc_prefetch_bulk(wq + (size_t)wtile_a(t, ks) * 8192, 8192);
+          if (has_b(t)) tc_prefetch_bulk(wq + (size_t)wtile_b(t, ks) * 8192, 8192);
+        }
+      };
+      const int early = nunits < C::STAGES ? nunits : C::STAGES;
+      int ptile = tile0, pks = ks0, pit = 0;
+      for (; pit < early; pit++) {  // weights do not depend on the split kernel: out before the grid dependency wait
+        fetch_w(pit, ptile, pks);
+        if (++pks == p.KS) { pks = 0; ptile++; }
+      }
+      for (; pit < nunits && pit < early + p.pf; pit++) {
+        prefetch_w(ptile, pks);
+        if (++pks == p.KS) { pks = 0; ptile++; }
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      int tile = tile0, ks = ks0;
+      for (int it = 0; it < nunits; it++) {
+        const int s = it % C::STAGES;
+        if (pit < nunits && pit < it + C::STAGES + p.pf) {
+          prefetch_w(ptile, pks);
+          pit++;
+          if (++pks == p.KS) { pks = 0; ptile++; }
+        }
+        if (it >= C::STAGES) {
+          if (!tc_wait(tc_smem_u32(&bar_empty[s]), (uint32_t)((it / C::STAGES - 1) & 1))) {
+            atomicExch(p.err, 2u);
+            break;
+          }
+          fetch_w(s, tile, ks);
+        }
+        fetch_x(s, ks);
+        if (++ks == p.KS) { ks = 0; tile++; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // A = E4M3 (0), B = E2M1 (5), both K-major, N = 256, UE8M0 scales, M = 128
+      const uint32_t idesc0 = (0u << 7) | (5u << 10) | ((256u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
+      int ks = ks0;
+      uint32_t acc_phase = 0;
+      bool fresh = true;
+      for (int it = 0; it < nunits; it++) {
+        const int s = it % C::STAGES;
+        const uint32_t ph = (uint32_t)((it / C::STAGES) & 1);
+        if (fresh && it > 0) {
+          if (!tc_wait(tc_smem_u32(&bar_acc_empty), acc_phase)) { atomicExch(p.err, 3u); break; }
+          acc_phase ^= 1;
+        }
+        if (!tc_wait(tc_smem_u32(&bar_full[s]), ph)) { atomicExch(p.err, 4u); break; }
+        if (it == 0) tc_stamp(p, 2);
+        if (it == nunits - 1) tc_stamp(p, 3);
+        tc_fence_after();
+        const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
+        const uint32_t sb = st + C::X_BYTES;
+        const uint32_t ssf = sb + C::B_BYTES;
+        const uint32_t sf_t = tmem + C::D_COLS + (uint32_t)s * C::SF_COLS;
+        const bool part_end = (ks == p.KS - 1) || (it == nunits - 1);
+        if (!(p.dbg & 16)) {
+#pragma unroll
+          for (int q = 0; q < 3; q++) tc_cp_sf(sf_t + q * 4, tc_sf_desc(ssf + q * 512));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          if (p.dbg & 32) break;
+          const uint32_t idesc = idesc0 | ((uint32_t)j << 29) | ((uint32_t)j << 4);
+          const uint64_t adesc = tc_smem_desc(st) + (uint64_t)(2 * j);   // rows past 2*TOKP read the weight area: unused lanes
+          const uint64_t bdesc = tc_smem_desc(sb) + (uint64_t)(2 * j);
+          tc_mma(tmem, adesc, bdesc, idesc, sf_t | ((uint32_t)j << 30), (sf_t + 4) | ((uint32_t)j << 30), (fresh && j == 0) ? 0u : 1u);
+        }
+        tc_commit(tc_smem_u32(&bar_empty[s]));
+        if (part_end) tc_commit(tc_smem_u32(&bar_acc_full));
+        fresh = part_end;
+        if (++ks == p.KS) ks = 0;
+      }
+    }
+    __syncwarp();
+  } else if ((warp & 3) < C::EPI_WARPS) {
+    // ------------------------------------------------------------ epilogue: quarter `sub` of tensor memory holds
+    // tokens 16*sub .. 16*sub+15: hi terms in lanes 0-15, lo terms in lanes 16-31
+    const int sub = warp & 3;
+    const uint32_t lane_base = ((uint32_t)(sub * 32)) << 16;
+    const int tok = sub * 16 + (lane & 15);
+    const int half = lane >> 4;  // after the hi+lo sum both halves hold the same values: each finishes 8 of 16 features
+    int tile = tile0, ks = ks0;
+    int part_first_ks = ks0;
+    uint32_t acc_phase = 0;
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // scratch, residual and gate inputs belong to earlier grids
+    for (int it = 0; it < nunits; it++) {
+      const bool part_end = (ks == p.KS - 1) || (it == nunits - 1);
+      if (part_end) {
+        if (!tc_wait(tc_smem_u32(&bar_acc_full), acc_phase)) {
+          if (lane == 0) atomicExch(p.err, 6u);
+          break;
+        }
+        acc_phase ^= 1;
+        tc_fence_after();
+        if (threadIdx.x == 128 && it == nunits - 1) tc_stamp(p, 5);
+        const bool whole = (part_first_ks == 0) && (ks == p.KS - 1);
+        float* myslot = p.partial + (((size_t)blockIdx.x * 2 + (tile == tile0 ? 0 : 1)) * TOKP + tok) * 256;
+        constexpr int CHUNKS = DUAL ? 8 : 16;
+#pragma unroll 2
+        for (int c = 0; c < CHUNKS; c++) {
+          uint32_t a[16], b[16];
+          tc_ld_x16(tmem + lane_base + c * 16, a);
+          if (DUAL) tc_ld_x16(tmem + lane_base + 128 + c * 16, b);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          float v[8], u[8];
+#pragma unroll
+          for (int i = 0; i < 16; i++) {
+            const float sa = __uint_as_float(a[i]) + __shfl_xor_sync(0xffffffffu, __uint_as_float(a[i]), 16);
+            if ((i >> 3) == 0) { if (!half) v[i & 7] = sa; } else { if (half) v[i & 7] = sa; }
+            if (DUAL) {
+              const float sb2 = __uint_as_float(b[i]) + __shfl_xor_sync(0xffffffffu, __uint_as_float(b[i]), 16);
+              if ((i >> 3) == 0) { if (!half) u[i & 7] = sb2; } else { if (half) u[i & 7] = sb2; }
+            } else {
+              u[i & 7] = 0.0f;
+            }
+          }
+          const int col = c * 16 + half * 8;  // first of this thread's 8 accumulator columns
+          if (whole) {
+            const int n = DUAL ? tile * 128 + col : tile * 256 + col;
+            if (tok < p.M && n < p.N) tcw_finish8<DUAL>(p, tok, n, v, u);
+          } else {
+            __stcg(reinterpret_cast<float4*>(myslot + col), make_float4(v[0], v[1], v[2], v[3]));
+            __stcg(reinterpret_cast<float4*>(myslot + col) + 1, make_float4(v[4], v[5], v[6], v[7]));
+            if (DUAL) {
+              __stcg(reinterpret_cast<float4*>(myslot + 128 + col), make_float4(u[0], u[1], u[2], u[3]));
+              __stcg(reinterpret_cast<float4*>(myslot + 128 + col) + 1, make_float4(u[4], u[5], u[6], u[7]));
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc_mbar_arrive(tc_smem_u32(&bar_acc_empty));
+      }
+      if (++ks == p.KS) {
+        ks = 0;
+        tile++;
+        part_first_ks = 0;
+      }
+    }
+  }
+  if (threadIdx.x == 128) tc_stamp(p, 6);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)C::TMEM_COLS) : "memory");
+  }
+}
+
+
+// ---------------------------------------------------------------- fix-up of tiles cut between CTAs
+// One thread per (token, 8 output features) of a tile; contributors are the consecutive CTAs cfirst..clast, CTA c
+// keeps its part in slot 0 if the tile is the first it touched, else in slot 1. Fixed summation order.
+template <bool DUAL>
+__global__ void __launch_bounds__(128) tcw_fixup_kernel(TcParams p, int TOKP, int G) {
+  constexpr int GROUPS = DUAL ? 16 : 32;
+  pdl_trigger();
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int tile = blockIdx.x;
+  const int idx = blockIdx.y * 128 + threadIdx.x;
+  const int tok = idx / GROUPS, col = (idx % GROUPS) * 8;
+  const long long U = (long long)p.TN * p.KS;
+  const long long ta = (long long)tile * p.KS, tb = ta + p.KS - 1;
+  const int cfirst = (int)(((ta + 1) * G - 1) / U), clast = (int)(((tb + 1) * G - 1) / U);
+  if (cfirst == clast) return;  // one CTA had the whole tile and finished it itself
+  const int n = DUAL ? tile * 128 + col : tile * 256 + col;
+  if (tok >= p.M || tok >= TOKP || n >= p.N) return;
+  float v[8], u[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) v[i] = u[i] = 0.0f;
+#pragma unroll 1
+  for (int cb = cfirst; cb <= clast; cb += 4) {  // four contributors' loads in flight at a time
+    float4 t[4][DUAL ? 4 : 2];
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+      const int c = cb + cc;
+      if (c <= clast) {
+        const int ctile0 = (int)(((long long)c * U / G) / p.KS);
+        const float* slot = p.partial + (((size_t)c * 2 + (tile == ctile0 ? 0 : 1)) * TOKP + tok) * 256 + col;
+        t[cc][0] = __ldcg(reinterpret_cast<const float4*>(slot));
+        t[cc][1] = __ldcg(reinterpret_cast<const float4*>(slot) + 1);
+        if (DUAL) {
+          t[cc][DUAL ? 2 : 0] = __ldcg(reinterpret_cast<const float4*>(slot + 128));
+          t[cc][DUAL ? 3 : 1] = __ldcg(reinterpret_cast<const float4*>(slot + 128) + 1);
+        }
+      }
+    }
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+      if (cb + cc <= clast) {
+        v[0] += t[cc][0].x; v[1] += t[cc][0].y; v[2] += t[cc][0].z; v[3] += t[cc][0].w;
+        v[4] += t[cc][1].x; v[5] += t[cc][1].y; v[6] += t[cc][1].z; v[7] += t[cc][1].w;
+        if (DUAL) {
+          u[0] += t[cc][DUAL ? 2 : 0].x; u[1] += t[cc][DUAL ? 2 : 0].y; u[2] += t[cc][DUAL ? 2 : 0].z; u[3] += t[cc][DUAL ? 2 : 0].w;
+          u[4] += t[cc][DUAL ? 3 : 1].x; u[5] += t[cc][DUAL ? 3 : 1].y; u[6] += t[cc][DUAL ? 3 : 1].z; u[7] += t[cc][DUAL ? 3 : 1].w;
+        }
+      }
+    }
+  }
+  tcw_finish8<DUAL>(p, tok, n, v, u);
+}
+
+// ---------------------------------------------------------------- host side
+struct TcwPlan {
+  int tokp, KS, tiles128, TN, grid, whole;
+  size_t off_terms, off_sfb, off_partial, total;
+};
+
+static TcwPlan tcw_plan(int64_t M, int64_t N, int64_t K, bool pair) {
+  TcwPlan pl;
+  pl.tokp = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+  pl.KS = tc_padded_ks(K, pair);
+  pl.tiles128 = (int)((N + 127) / 128);
+  pl.TN = pair ? pl.tiles128 : (pl.tiles128 + 1) / 2;
+  const long long U = (long long)pl.TN * pl.KS, T = pl.TN;
+  const int sms = sm_count();
+  // whole tiles when their count suits the SM count (no fix-up pass), else the (tile, k step) units are cut evenly
+  pl.whole = (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
+  { const char* e = getenv("TPX_TC_WHOLE"); if (e) pl.whole = atoi(e); }
+  pl.grid = pl.whole ? (int)(T < sms ? T : sms) : (int)(U < sms ? U : sms);
+  size_t o = kTcCounterBytes;
+  auto bump = [&](size_t bytes) { size_t r = o; o += (bytes + 1023) & ~(size_t)1023; return r; };
+  pl.off_terms = bump((size_t)pl.KS * 2 * pl.tokp * 128);
+  pl.off_sfb = bump((size_t)pl.KS * 512);
+  pl.off_partial = bump((size_t)pl.grid * 2 * pl.tokp * 256 * sizeof(float));
+  pl.total = o;
+  return pl;
+}
+
+size_t tcw_scratch_bytes(int64_t M, int64_t N, int64_t K, bool pair) { return tcw_plan(M, N, K, pair).total; }
+
+template <int TOKP, bool DUAL>
+static int tcw_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams& p, const uint8_t* wq, int tiles128, int grid,
+                      cudaStream_t st) {
+  using C = TcwCfg<TOKP>;
+  static bool opted[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16 || !opted[dev]) {
+    TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_tcw_kernel<TOKP, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+    if (dev >= 0 && dev < 16) opted[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = C::SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tcw_kernel<TOKP, DUAL>, w, x, p, wq, tiles128));
+  if (!p.whole_tiles && grid > 1) {
+    constexpr int GROUPS = DUAL ? 16 : 32;
+    cudaLaunchConfig_t c2 = {};
+    c2.gridDim = dim3((unsigned)p.TN, (unsigned)(TOKP * GROUPS / 128));
+    c2.blockDim = dim3(128);
+    c2.stream = st;
+    c2.attrs = attr;
+    c2.numAttrs = 1;
+    TPX_CUDA_OK(cudaLaunchKernelEx(&c2, tcw_fixup_kernel<DUAL>, p, (int)TOKP, grid));
+  }
+  return TPX_OK;
+}
+
+int tcw_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x, int64_t M, int64_t N, int64_t K, const TcParams& base,
+            void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  TcwPlan pl = tcw_plan(M, N, K, pair);
+  TPX_REQUIRE(scratch && scratch_bytes >= pl.total, TPX_ERR_SCRATCH, "qlinear_mxfp4_tc: scratch of %zu bytes needed, %zu given", pl.total,
+              scratch_bytes);
+  TPX_REQUIRE((((uintptr_t)base.y | (uintptr_t)base.bias | (uintptr_t)base.mul_in | (uintptr_t)base.res) & 15) == 0, TPX_ERR_ARG,
+              "qlinear_mxfp4_tc: y, bias, mul_in and res must be 16-byte aligned");
+  unsigned char* sc = reinterpret_cast<unsigned char*>(scratch);
+  uint8_t *terms = sc + pl.off_terms, *sfb = sc + pl.off_sfb;
+  int rc = tc_launch_split(x, (int)M, (int)K, pl.tokp, pl.KS, pl.tokp, 1, 1, terms, sfb, st);
+  if (rc) return rc;
+  CUtensorMap mw, mx;
+  const uint64_t wrows = (uint64_t)(pair ? pl.TN * 2 : pl.tiles128) * pl.KS * 128;
+  rc = tc_make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, wrows, 64, pair ? 256 : 128);
+  if (rc) return rc;
+  rc = tc_make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, terms, (uint64_t)pl.KS * 2 * pl.tokp, 128, (uint32_t)(2 * pl.tokp));
+  if (rc) return rc;
+  TcParams p = base;
+  p.sfa = sfa; p.sfa2 = nullptr; p.sfb = sfb;
+  p.partial = reinterpret_cast<float*>(sc + pl.off_partial);
+  p.counters = reinterpret_cast<unsigned*>(sc);
+  p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KS; p.TN = pl.TN; p.TM = 1; p.whole_tiles = pl.whole;
+  if (pair) {
+    switch (pl.tokp) {
+      case 16: return tcw_launch<16, true>(mw, mx, p, wq, pl.tiles128, pl.grid, st);
+      case 32: return tcw_launch<32, true>(mw, mx, p, wq, pl.tiles128, pl.grid, st);
+      default: return tcw_launch<64, true>(mw, mx, p, wq, pl.tiles128, pl.grid, st);
+    }
+  }
+  switch (pl.tokp) {
+    case 16: return tcw_launch<16, false>(mw, mx, p, wq, pl.tiles128, pl.grid, st);
+    case 32: return tcw_launch<32, false>(mw, mx, p, wq, pl.tiles128, pl.grid, st);
+    default: return tcw_launch<64, false>(mw, mx, p, wq, pl.tiles128, pl.grid, st);
+  }
+}
+
+}  // namespace tpx
