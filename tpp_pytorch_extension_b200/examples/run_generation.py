@@ -78,7 +78,12 @@ def main(argv=None):
             "decode_tokens_per_s": round(a.batch_size / per_tok, 1),
             "prefill_tokens_per_s": round(a.batch_size * a.input_tokens / t1, 1), "data": "synthetic"}))
     if world > 1:
+        import gc
         import torch.distributed as dist
+        # a CUDA graph that recorded NCCL collectives must be gone before its communicator is destroyed
+        model.last_graph = None
+        gc.collect()
+        torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
 
