@@ -168,10 +168,9 @@ __global__ void rope_kv_kernel(const uint16_t* __restrict__ qkv, const float* __
 }
 
 // ---------------------------------------------------------------- attention
-// Up to 16 query rows (consecutive (query position, group member) pairs of one (batch, kv head)) per CTA against
-// a range of KV blocks. 4 warps split the blocks of the range; each keeps a running (max, sum, fp32 output) per
-// row, merged through shared memory at the end. With more than one KV split the CTA writes an un-normalised
-// partial (max, sum, output) and a second kernel merges the splits (flash-decoding).
+// Query rows are consecutive (query position, group member) pairs of one (batch, kv head). Each warp keeps a
+// running (max, sum, fp32 output) for 16 rows over the KV blocks it visits. With more than one KV split a CTA
+// writes an un-normalised partial (max, sum, output) and a second kernel merges the splits (flash-decoding).
 constexpr int kAttnWarps = 4;
 constexpr int kAttnRows = 16;
 
@@ -196,172 +195,249 @@ __device__ __forceinline__ int64_t attn_out_index(const AttnParams& p, int bn, i
   return ((((int64_t)b * p.Sq + sq) * p.Nkv + n) * p.R + r) * H;
 }
 
-template <int H>
-__global__ void __launch_bounds__(kAttnWarps * 32) attn_kernel(AttnParams p) {
-  constexpr int HV = H / 32;  // output dims per lane
-  __shared__ float qs[kAttnRows][H];
-  __shared__ float ps[kAttnWarps][kAttnRows][32];
+// ---- tensor-core attention (mma.sync m16n8k16, bf16 in, fp32 accumulate), flash-attention style
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;  // size 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// MODE 0 (prefill): a CTA owns 64 consecutive query rows (16 per warp) of one (batch, kv head); its four warps
+//   share every KV block, copied once into shared memory (two stages, cp.async).
+// MODE 1 (decoding, at most 16 query rows): all warps work on the same 16 rows and take every fourth KV block of
+//   the CTA's split, each with its own two stages; the warps' (max, sum, output) are merged through shared memory,
+//   and with more than one KV split the CTA writes an un-normalised partial for attn_merge_kernel.
+// Rows of a KV block are kept 16 bytes apart from a power-of-two pitch so that ldmatrix is conflict-free.
+template <int H, int MODE>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_mma_kernel(AttnParams p) {
+  constexpr int PB = H * 2 + 16;        // bytes per key row in shared memory
+  constexpr int TILE = 32 * PB;         // one block of keys or of values
+  constexpr int STAGE = 2 * TILE;       // keys, then values
+  constexpr int NT = H / 8;             // output n-tiles
+  constexpr int KK = H / 16;            // k steps of Q.K^T
+  constexpr int GROUP = MODE == 0 ? kAttnWarps * 32 : 32;  // threads that share a KV stream
+  extern __shared__ __align__(16) unsigned char attn_smem[];
   __shared__ float red_m[kAttnWarps][kAttnRows], red_l[kAttnWarps][kAttnRows];
-  __shared__ float red_o[kAttnWarps][kAttnRows / 2][H];
 
   pdl_trigger();
   pdl_wait();
   const int bn = blockIdx.x, chunk = blockIdx.y, split = blockIdx.z;
   const int b = bn / p.Nkv, n = bn % p.Nkv;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int rows_total = p.Sq * p.R;
-  const int row0 = chunk * kAttnRows;
-  const int rows = min(kAttnRows, rows_total - row0);
+  const int cta_row0 = chunk * (MODE == 0 ? 64 : 16);
+  const int row0 = cta_row0 + (MODE == 0 ? warp * 16 : 0);  // first of this warp's 16 rows
   const int key_len = p.dev_len ? *p.dev_len + p.Sq : p.key_len;
   const int offset = key_len - p.Sq;
 
-  // queries of this chunk to shared memory as fp32, pre-multiplied by 1/sqrt(H)
-  const uint16_t* qbase = p.q + ((int64_t)bn * rows_total + row0) * H;
-  for (int i = threadIdx.x; i < kAttnRows * H; i += blockDim.x) {
-    int r = i / H;
-    qs[r][i % H] = r < rows ? bf16_bits_to_f32(qbase[i]) * p.scale : 0.0f;
-  }
-  __syncthreads();
-
-  // keys this chunk can see at all: up to the last row's causal limit
-  const int last_sq = (row0 + rows - 1) / p.R;
-  const int kmax = p.causal ? min(key_len, offset + last_sq + 1) : key_len;
+  // keys this CTA can see at all (last row's causal limit), cut into the CTA's KV split
+  const int cta_last_row = min(rows_total, cta_row0 + (MODE == 0 ? 64 : 16)) - 1;
+  const int kmax = p.causal ? min(key_len, offset + cta_last_row / p.R + 1) : key_len;
   const int nblocks = (kmax + 31) / 32;
   const int per_split = (nblocks + p.splits - 1) / p.splits;
   const int blk0 = split * per_split, blk1 = min(nblocks, blk0 + per_split);
+  // keys this warp's rows can see
+  const int warp_last_row = min(rows_total - 1, row0 + 15);
+  const int warp_kmax = (row0 < rows_total) ? (p.causal ? min(key_len, offset + warp_last_row / p.R + 1) : key_len) : 0;
 
-  float m[kAttnRows], l[kAttnRows], acc[kAttnRows][HV];
+  // query fragments (A operand), straight from global memory
+  uint32_t qf[KK][4];
+  {
+    const uint16_t* qbase = p.q + (int64_t)bn * rows_total * H;
+    const int ra = row0 + g, rb = row0 + g + 8;
 #pragma unroll
-  for (int r = 0; r < kAttnRows; r++) {
-    m[r] = -INFINITY;
-    l[r] = 0.0f;
-#pragma unroll
-    for (int j = 0; j < HV; j++) acc[r][j] = 0.0f;
+    for (int kk = 0; kk < KK; kk++) {
+      const int c = kk * 16 + 2 * t;
+      qf[kk][0] = ra < rows_total ? *reinterpret_cast<const uint32_t*>(qbase + (int64_t)ra * H + c) : 0u;
+      qf[kk][1] = rb < rows_total ? *reinterpret_cast<const uint32_t*>(qbase + (int64_t)rb * H + c) : 0u;
+      qf[kk][2] = ra < rows_total ? *reinterpret_cast<const uint32_t*>(qbase + (int64_t)ra * H + c + 8) : 0u;
+      qf[kk][3] = rb < rows_total ? *reinterpret_cast<const uint32_t*>(qbase + (int64_t)rb * H + c + 8) : 0u;
+    }
   }
+  float o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};  // rows g and g + 8; l is this thread's share
 
-  for (int blk = blk0 + warp; blk < blk1; blk += kAttnWarps) {
-    const int tok = blk * 32 + lane;
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(attn_smem) + (MODE == 0 ? 0u : (uint32_t)warp * 2u * STAGE);
+  const int gtid = MODE == 0 ? threadIdx.x : lane;
+  auto load_block = [&](int blk, int stage) {
+    const uint32_t dst = sbase + (uint32_t)stage * STAGE;
     const int64_t boff = ((((int64_t)blk * p.B + b) * p.Nkv + n) * 32) * H;
-    // phase A: lane = token; scores of all rows against this lane's key
-    float kreg[H];
-    {
-      const uint4* kr = reinterpret_cast<const uint4*>(p.kc + boff + (int64_t)lane * H);
+    constexpr int CPR = H / 8;  // 16-byte chunks per row
+    for (int i = gtid; i < 32 * CPR; i += GROUP) {
+      const int r = i / CPR, c = i % CPR;
+      const bool valid = blk * 32 + r < key_len;  // slots past the cached length may hold anything
+      cp_async_16(dst + r * PB + c * 16, p.kc + boff + r * H + c * 8, valid);
+      cp_async_16(dst + TILE + r * PB + c * 16, p.vc + boff + r * H + c * 8, valid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  auto group_sync = [&]() {
+    if (MODE == 0) __syncthreads(); else __syncwarp();
+  };
+
+  const int first = MODE == 0 ? blk0 : blk0 + warp, step = MODE == 0 ? 1 : kAttnWarps;
+  if (first < blk1) load_block(first, 0);
+  int it = 0;
+  for (int blk = first; blk < blk1; blk += step, it++) {
+    const int stage = it & 1;
+    if (blk + step < blk1) {
+      load_block(blk + step, stage ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    group_sync();
+    if (blk * 32 < warp_kmax) {
+      const uint32_t sk = sbase + (uint32_t)stage * STAGE, sv = sk + TILE;
+      // ---- S = Q.K^T for 32 keys: four n-tiles of 8 keys
+      float sc[4][4];
 #pragma unroll
-      for (int i = 0; i < H / 8; i++) {
-        uint4 v = kr[i];
-        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      for (int i = 0; i < 4; i++) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-          kreg[i * 8 + 2 * j] = bf16_bits_to_f32((uint16_t)(w[j] & 0xffff));
-          kreg[i * 8 + 2 * j + 1] = bf16_bits_to_f32((uint16_t)(w[j] >> 16));
+      for (int kk = 0; kk < KK; kk += 2) {
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+          uint32_t kf[4];  // keys nt*8..+7: h [kk*16, +8), [kk*16+8, +16), [(kk+1)*16, +8), [(kk+1)*16+8, +16)
+          ldmatrix_x4(kf, sk + (nt * 8 + (lane & 7)) * PB + (kk * 16 + (lane >> 3) * 8) * 2);
+          mma_bf16_16816(sc[nt], qf[kk], kf[0], kf[1]);
+          mma_bf16_16816(sc[nt], qf[kk + 1], kf[2], kf[3]);
+        }
+      }
+      // ---- scale, masks, running max
+      float bm[2] = {-INFINITY, -INFINITY};
+      const int sq_a = (row0 + g) / p.R, sq_b = (row0 + g + 8) / p.R;
+#pragma unroll
+      for (int nt = 0; nt < 4; nt++) {
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          const int key = blk * 32 + nt * 8 + 2 * t + e;
+          const float madd = (p.am && key < p.Spad) ? bf16_bits_to_f32(p.am[(int64_t)b * p.Spad + key]) : 0.0f;
+          const bool in = key < key_len;
+          const bool va = in && (!p.causal || key <= offset + sq_a);
+          const bool vb = in && (!p.causal || key <= offset + sq_b);
+          sc[nt][e] = va ? sc[nt][e] * p.scale + madd : -INFINITY;
+          sc[nt][2 + e] = vb ? sc[nt][2 + e] * p.scale + madd : -INFINITY;
+          bm[0] = fmaxf(bm[0], sc[nt][e]);
+          bm[1] = fmaxf(bm[1], sc[nt][2 + e]);
+        }
+      }
+      float alpha[2];
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        bm[h] = fmaxf(bm[h], __shfl_xor_sync(0xffffffffu, bm[h], 1));
+        bm[h] = fmaxf(bm[h], __shfl_xor_sync(0xffffffffu, bm[h], 2));
+        const float mn = fmaxf(m_run[h], bm[h]);
+        alpha[h] = (mn == -INFINITY) ? 1.0f : __expf(m_run[h] - mn);
+        m_run[h] = mn;
+        l_run[h] *= alpha[h];
+      }
+      // ---- P = exp(S - max), packed to bf16 A fragments; row sums
+      uint32_t pf[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 4; nt++) {
+        float e0 = (m_run[0] == -INFINITY) ? 0.0f : __expf(sc[nt][0] - m_run[0]);
+        float e1 = (m_run[0] == -INFINITY) ? 0.0f : __expf(sc[nt][1] - m_run[0]);
+        float e2 = (m_run[1] == -INFINITY) ? 0.0f : __expf(sc[nt][2] - m_run[1]);
+        float e3 = (m_run[1] == -INFINITY) ? 0.0f : __expf(sc[nt][3] - m_run[1]);
+        l_run[0] += e0 + e1;
+        l_run[1] += e2 + e3;
+        pf[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16x2(e0, e1);
+        pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16x2(e2, e3);
+      }
+      // ---- O = O * alpha + P.V
+#pragma unroll
+      for (int i = 0; i < NT; i++) {
+        o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+        o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+      }
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+#pragma unroll
+        for (int nt = 0; nt < NT; nt += 2) {
+          uint32_t vf[4];  // keys j*16..+7 and +8..+15 for h tiles nt and nt+1
+          ldmatrix_x4_trans(vf, sv + (j * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * PB + ((nt + (lane >> 4)) * 8) * 2);
+          mma_bf16_16816(o[nt], pf[j], vf[0], vf[1]);
+          mma_bf16_16816(o[nt + 1], pf[j], vf[2], vf[3]);
         }
       }
     }
-    const float madd = (p.am && tok < p.Spad) ? bf16_bits_to_f32(p.am[(int64_t)b * p.Spad + tok]) : 0.0f;
-    float alpha[kAttnRows];
-#pragma unroll
-    for (int r = 0; r < kAttnRows; r++) {
-      alpha[r] = 1.0f;
-      if (r < rows) {
-        float s = 0.0f;
-        const float4* qr = reinterpret_cast<const float4*>(qs[r]);
-#pragma unroll
-        for (int i = 0; i < H / 4; i++) {
-          float4 qv = qr[i];
-          s += qv.x * kreg[4 * i] + qv.y * kreg[4 * i + 1] + qv.z * kreg[4 * i + 2] + qv.w * kreg[4 * i + 3];
-        }
-        s += madd;
-        const int sq = (row0 + r) / p.R;
-        const bool visible = tok < key_len && (!p.causal || tok <= offset + sq);
-        if (!visible) s = -INFINITY;
-        float bm = s;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
-        const float mn = fmaxf(m[r], bm);
-        const float pe = (mn == -INFINITY) ? 0.0f : __expf(s - mn);
-        float bs = pe;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o);
-        alpha[r] = (mn == -INFINITY) ? 1.0f : __expf(m[r] - mn);
-        l[r] = l[r] * alpha[r] + bs;
-        m[r] = mn;
-        ps[warp][r][lane] = pe;
-      }
-    }
-    __syncwarp();
-    // phase B: lane = output dims; out[r] = out[r]*alpha + sum_tok p[r][tok] * V[tok]
-#pragma unroll
-    for (int r = 0; r < kAttnRows; r++)
-#pragma unroll
-      for (int j = 0; j < HV; j++) acc[r][j] *= alpha[r];
-    const int ntok = min(32, key_len - blk * 32);
-    for (int t0 = 0; t0 < ntok; t0 += 8) {  // eight value rows in flight at a time
-      float vv[8][HV];
-#pragma unroll
-      for (int u = 0; u < 8; u++) {
-        const uint16_t* vr = p.vc + boff + (int64_t)(t0 + u) * H + lane * HV;
-        if (t0 + u < ntok) {  // slots past the cached length may hold anything
-          if (HV == 4) {
-            uint2 v = *reinterpret_cast<const uint2*>(vr);
-            vv[u][0] = bf16_bits_to_f32((uint16_t)(v.x & 0xffff));
-            vv[u][1] = bf16_bits_to_f32((uint16_t)(v.x >> 16));
-            vv[u][2] = bf16_bits_to_f32((uint16_t)(v.y & 0xffff));
-            vv[u][3] = bf16_bits_to_f32((uint16_t)(v.y >> 16));
-          } else {
-#pragma unroll
-            for (int j = 0; j < HV; j++) vv[u][j] = bf16_bits_to_f32(vr[j]);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < HV; j++) vv[u][j] = 0.0f;
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 8; u++) {
-#pragma unroll
-        for (int r = 0; r < kAttnRows; r++) {
-          if (r < rows) {
-            const float pr = ps[warp][r][t0 + u];
-#pragma unroll
-            for (int j = 0; j < HV; j++) acc[r][j] = fmaf(pr, vv[u][j], acc[r][j]);
-          }
-        }
-      }
-    }
-    __syncwarp();
+    group_sync();  // the stage is rewritten by the copy issued at the top of the next round
   }
 
-  // merge the warps of this CTA, eight rows at a time (shared-memory budget)
-  for (int r = 0; r < kAttnRows; r++)
-    if (lane == 0) { red_m[warp][r] = m[r]; red_l[warp][r] = l[r]; }
+  // row sums over the four threads of a row
 #pragma unroll
-  for (int half = 0; half < 2; half++) {
-    __syncthreads();
+  for (int h = 0; h < 2; h++) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+
+  if (MODE == 0) {
+    // every warp finishes its own rows (no KV split in this mode)
 #pragma unroll
-    for (int r = 0; r < kAttnRows / 2; r++)
+    for (int h = 0; h < 2; h++) {
+      const int row = row0 + g + 8 * h;
+      if (row >= rows_total) continue;
+      const float inv = 1.0f / l_run[h];
+      uint16_t* dst = p.out + attn_out_index(p, bn, row, H);
 #pragma unroll
-      for (int j = 0; j < HV; j++) red_o[warp][r][lane * HV + j] = acc[half * (kAttnRows / 2) + r][j];
-    __syncthreads();
-    for (int i = threadIdx.x; i < (kAttnRows / 2) * H; i += blockDim.x) {
-      const int rr = i / H, h = i % H, r = half * (kAttnRows / 2) + rr;
-      if (r >= rows) continue;
-      float mm = -INFINITY;
+      for (int i = 0; i < NT; i++)
+        *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t) = pack_bf16x2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+    }
+    return;
+  }
+
+  // MODE 1: merge the four warps through shared memory (the KV stages are free now)
+  __syncthreads();
+  float* red_o = reinterpret_cast<float*>(attn_smem);  // [warp][16][H]
+  if (t == 0) {
+    red_m[warp][g] = m_run[0]; red_m[warp][g + 8] = m_run[1];
+    red_l[warp][g] = l_run[0]; red_l[warp][g + 8] = l_run[1];
+  }
 #pragma unroll
-      for (int w = 0; w < kAttnWarps; w++) mm = fmaxf(mm, red_m[w][r]);
-      float ll = 0.0f, oo = 0.0f;
+  for (int i = 0; i < NT; i++) {
+    float* ra = red_o + ((size_t)warp * kAttnRows + g) * H + i * 8 + 2 * t;
+    float* rb = red_o + ((size_t)warp * kAttnRows + g + 8) * H + i * 8 + 2 * t;
+    ra[0] = o[i][0]; ra[1] = o[i][1];
+    rb[0] = o[i][2]; rb[1] = o[i][3];
+  }
+  __syncthreads();
+  const int rows = min(kAttnRows, rows_total - cta_row0);
+  for (int i = threadIdx.x; i < rows * H; i += blockDim.x) {
+    const int r = i / H, h = i % H;
+    float mm = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < kAttnWarps; w++) {
-        const float f = (red_m[w][r] == -INFINITY) ? 0.0f : __expf(red_m[w][r] - mm);
-        ll += red_l[w][r] * f;
-        oo += red_o[w][rr][h] * f;
-      }
-      if (p.splits == 1) {
-        p.out[attn_out_index(p, bn, row0 + r, H) + h] = f32_to_bf16_bits(oo / ll);
-      } else {
-        float* dst = p.part + ((((int64_t)bn * p.chunks + chunk) * p.splits + split) * kAttnRows + r) * (H + 2);
-        dst[h] = oo;
-        if (h == 0) { dst[H] = mm; dst[H + 1] = ll; }
-      }
+    for (int w = 0; w < kAttnWarps; w++) mm = fmaxf(mm, red_m[w][r]);
+    float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; w++) {
+      const float f = (red_m[w][r] == -INFINITY) ? 0.0f : __expf(red_m[w][r] - mm);
+      ll += red_l[w][r] * f;
+      oo += red_o[((size_t)w * kAttnRows + r) * H + h] * f;
+    }
+    if (p.splits == 1) {
+      p.out[attn_out_index(p, bn, cta_row0 + r, H) + h] = f32_to_bf16_bits(oo / ll);
+    } else {
+      float* dst = p.part + ((((int64_t)bn * p.chunks + chunk) * p.splits + split) * kAttnRows + r) * (H + 2);
+      dst[h] = oo;
+      if (h == 0) { dst[H] = mm; dst[H + 1] = ll; }
     }
   }
 }
@@ -439,16 +515,39 @@ extern "C" int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const in
   return TPX_OK;
 }
 
+// More than 16 query rows: 64 rows per CTA, no KV split. Up to 16 rows (decoding): one CTA row tile, the KV range
+// split while the grid is short of two CTAs per SM and every split keeps a block for each warp.
 static int attn_plan(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t key_len, int* chunks, int* splits) {
-  *chunks = (int)((Sq * R + kAttnRows - 1) / kAttnRows);
-  int64_t ctas = B * Nkv * *chunks;
+  const int64_t rows = Sq * R;
+  if (rows > kAttnRows) {
+    *chunks = (int)((rows + 63) / 64);
+    *splits = 1;
+    return 0;
+  }
+  *chunks = 1;
+  int64_t ctas = B * Nkv;
   int nblocks = (int)((key_len + 31) / 32);
   int s = 1;
   int sms = sm_count();
-  // split the KV range while the grid is short of two CTAs per SM and every split keeps a block for each warp
   while (ctas * s < 2 * sms && nblocks / (s * 2) >= kAttnWarps && s < 64) s *= 2;
   *splits = s;
   return 0;
+}
+
+template <int H, int MODE>
+static int attn_launch(const AttnParams& p, dim3 grid, cudaStream_t st) {
+  constexpr int STAGE = 2 * 32 * (H * 2 + 16);
+  constexpr size_t smem = MODE == 0 ? 2 * STAGE : (size_t)kAttnWarps * 2 * STAGE;
+  static_assert(MODE == 0 || smem >= (size_t)kAttnWarps * kAttnRows * H * sizeof(float), "merge area");
+  static bool opted[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16 || !opted[dev]) {
+    TPX_CUDA_OK(cudaFuncSetAttribute(attn_mma_kernel<H, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev >= 0 && dev < 16) opted[dev] = true;
+  }
+  TPX_CUDA_OK(launch_pdl(attn_mma_kernel<H, MODE>, grid, dim3(kAttnWarps * 32), smem, st, p));
+  return TPX_OK;
 }
 
 extern "C" size_t tpx_attention_scratch_bytes(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len) {
@@ -479,8 +578,11 @@ extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16
   dim3 grid((unsigned)(B * Nkv), (unsigned)p.chunks, (unsigned)p.splits);
   TPX_REQUIRE(p.chunks <= 65535, TPX_ERR_UNSUPPORTED, "attention: too many query rows in one call");
   cudaStream_t st = (cudaStream_t)stream;
-  if (H == 128) TPX_CUDA_OK(launch_pdl(attn_kernel<128>, grid, dim3(kAttnWarps * 32), 0, st, p));
-  else TPX_CUDA_OK(launch_pdl(attn_kernel<64>, grid, dim3(kAttnWarps * 32), 0, st, p));
+  const bool decode = Sq * R <= kAttnRows;
+  int rc;
+  if (H == 128) rc = decode ? attn_launch<128, 1>(p, grid, st) : attn_launch<128, 0>(p, grid, st);
+  else rc = decode ? attn_launch<64, 1>(p, grid, st) : attn_launch<64, 0>(p, grid, st);
+  if (rc) return rc;
   if (p.splits > 1) {
     dim3 g2((unsigned)(B * Nkv), (unsigned)p.chunks);
     if (H == 128) TPX_CUDA_OK(launch_pdl(attn_merge_kernel<128>, g2, dim3(256), 0, st, p));
