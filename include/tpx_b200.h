@@ -129,6 +129,15 @@ int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const 
                          int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
                          float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream);
 
+/* RMSNorm followed by the linear, the pair the reference's decoder block runs before q/k/v and before gate/up
+ * (llama_rms_norm then the fused loop nests, src/csrc/llm/fused_llm_infer.cpp:1204-1272): x is normalised
+ * (y = bf16(x * rsqrt(mean(x^2) + eps) * gamma), gamma bf16 or fp32) on its way into the activation split, so the
+ * normalised tensor never goes to memory. Rows of up to 8192 elements; otherwise as tpx_qlinear_mxfp4_tc.     */
+int tpx_rmsnorm_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, const void* gamma,
+                                 int gamma_is_f32, float eps, int64_t M, int64_t N, int64_t K, const uint16_t* bias, int act,
+                                 const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y, void* scratch,
+                                 size_t scratch_bytes, void* stream);
+
 /* The same linear for callers that cannot allocate device memory where they call it (all free memory already
  * handed to a cache pool, a fixed budget inside another framework, a thread that must stay off the allocator's
  * locks). It has no counterpart in the reference. Its scratch is an 8 MiB array built into the library

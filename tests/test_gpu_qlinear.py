@@ -85,6 +85,31 @@ def test_gate_up_pair(cuda, kind, M):
     assert O.rel_err(y, O.gate_up(x, wg, wu, ref_rounding=True)) <= TOL
 
 
+@pytest.mark.parametrize("M", [1, 5, 40, 200])
+def test_rmsnorm_fused_into_linear(cuda, M):
+    """RMSNorm fused into the activation split of the tensor-core linear (and the separate-kernel fallback of the other
+    families) against the oracle's rmsnorm -> bf16 -> linear, single weight and gate/up pair, K not a multiple of 128."""
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    rng = np.random.default_rng(90 + M)
+    N, K = 256, 1088
+    q, wd, _ = make_qweight(rng, N, K, "mxfp4", cuda)
+    qu, wu, _ = make_qweight(rng, N, K, "mxfp4", cuda)
+    x = O.randn_bf16(rng, (M, K), 3.0)
+    gamma = O.f32_to_bf16(1 + 0.2 * rng.standard_normal(K).astype(np.float32))
+    xn = O.rmsnorm(x, gamma, 1e-5)
+    xd, gd = to_dev_bf16(x, cuda), to_dev_bf16(gamma, cuda)
+    y = to_host_bits(F.fc_plain_norm(xd, gd, 1e-5, q))
+    assert_no_kernel_error()
+    assert O.rel_err(y, O.qlinear(xn, wd)) <= TOL
+    y2 = to_host_bits(F.fc_gate_up(xd, q, qu, "silu", norm=(gd, 1e-5)))
+    assert_no_kernel_error()
+    assert O.rel_err(y2, O.gate_up(xn, wd, wu)) <= TOL
+    # fp32 gamma, as the reference also accepts
+    g32 = torch.from_numpy(O.bf16_to_f32(gamma).copy()).to(cuda)
+    y3 = to_host_bits(F.fc_plain_norm(xd, g32, 1e-5, q))
+    assert np.array_equal(y3, y)
+
+
 def test_int8_reference_arithmetic_is_within_tolerance(cuda):
     """The reference's int8 path quantises activations on the fly; ours is weight-only. Both sit within the
     tolerance of the fp32 oracle, and of each other."""

@@ -16,7 +16,7 @@ def mxfp4_path():
     return os.environ.get("TPX_MXFP4_PATH", "tc")
 
 
-def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale):
+def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
     if not isinstance(w, QTensor):
         raise _lib.TpxError("fc_plain: weight must be a quantized tensor from remap_and_quantize_*")
     _lib.require_cuda(x, "input")
@@ -45,12 +45,25 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale):
         if nb is None:
             nb = _SCRATCH_BYTES[key] = L.tpx_qlinear_mxfp4_tc_scratch_bytes(M, N, K, int(w2 is not None))
         sc = _lib.scratch(nb, x.device)
+        if norm is not None and K <= 8192 and os.environ.get("TPX_FUSED_NORM", "1") != "0":
+            gamma, eps = norm
+            rc = L.tpx_rmsnorm_qlinear_mxfp4_tc(wq.data_ptr(), sfa.data_ptr(), int(w2 is not None), x.data_ptr(), gamma.data_ptr(),
+                                                int(gamma.dtype == torch.float32), float(eps), M, N, K, _lib.ptr(bias), ACT[act],
+                                                _lib.ptr(mul_in), _lib.ptr(res), float(res_scale), y.data_ptr(), sc.data_ptr(),
+                                                sc.numel(), _lib.stream())
+            if rc:
+                _lib.check(rc)
+            return y
+        if norm is not None:
+            x = rms_norm(x, norm[0], norm[1])
         rc = L.tpx_qlinear_mxfp4_tc(wq.data_ptr(), sfa.data_ptr(), int(w2 is not None), x.data_ptr(), M, N, K,
                                     _lib.ptr(bias), ACT[act], _lib.ptr(mul_in), _lib.ptr(res), float(res_scale),
                                     y.data_ptr(), sc.data_ptr(), sc.numel(), _lib.stream())
         if rc:
             _lib.check(rc)
         return y
+    if norm is not None:
+        x = rms_norm(x, norm[0], norm[1])
     pc, ps = w.packed()
     pc2 = ps2 = None
     if w2 is not None:
@@ -85,9 +98,17 @@ def fc_plain_act(input, weight, bias=None, act=None, mul_in=None, res=None, res_
     return _qlinear(input, weight, None, bias, act, mul_in, res, res_scale)
 
 
-def fc_gate_up(input, w_gate, w_up, act="silu"):
-    """act(x.Wg^T) * (x.Wu^T) in one pass over both weights (src/csrc/llm/fused_llm_infer.cpp:1271-1272)."""
-    return _qlinear(input, w_gate, w_up, None, act, None, None, 1.0)
+def fc_gate_up(input, w_gate, w_up, act="silu", norm=None):
+    """act(x.Wg^T) * (x.Wu^T) in one pass over both weights (src/csrc/llm/fused_llm_infer.cpp:1271-1272).
+    norm = (gamma, eps): RMSNorm of the input first, fused into the linear where the kernel family supports it."""
+    return _qlinear(input, w_gate, w_up, None, act, None, None, 1.0, norm)
+
+
+def fc_plain_norm(input, gamma, eps, weight, bias=None):
+    """llama_rms_norm followed by fc_plain (src/csrc/llm/fused_llm_infer.cpp:1204-1215) as one call."""
+    if gamma.dtype not in (torch.bfloat16, torch.float32):
+        raise _lib.TpxError("llama_rms_norm: unsupported gamma dtype")
+    return _qlinear(input, weight, None, bias, None, None, None, 1.0, (gamma, eps))
 
 
 # --------------------------------------------------------------------------- decoder-layer pieces
@@ -189,8 +210,7 @@ class LlamaDecoderLayer:
         scale = 1.0 / ws
         L = _lib.lib()
         res = hs.reshape(B * S, D)
-        x = rms_norm(res, self.Gi, self.eps)
-        qkv = fc_plain(x, self.Wqkv)
+        qkv = fc_plain_norm(res, self.Gi, self.eps, self.Wqkv)
         lc = cache.layer(self.layer_idx)
         if dev_len is None:
             lc.ensure(B, self.Nkv, self.H, S, hs.dtype, hs.device)
@@ -210,8 +230,7 @@ class LlamaDecoderLayer:
         so = fc_plain_act(ctx, self.Wp, res=res, res_scale=scale)
         if ws > 1:
             allreduce(so)
-        x2 = rms_norm(so, self.Gpa, self.eps)
-        inter = fc_gate_up(x2, self.Wg, self.Wu, "silu")
+        inter = fc_gate_up(so, self.Wg, self.Wu, "silu", norm=(self.Gpa, self.eps))
         out = fc_plain_act(inter, self.Wd, res=so, res_scale=scale)
         if ws > 1:
             allreduce(out)

@@ -128,6 +128,128 @@ __global__ void split_activations_kernel(const uint16_t* __restrict__ x, int M, 
   blk[(r2 / 128) * 512 + (r2 % 32) * 16 + ((r2 % 128) / 32) * 4 + j] = (uint8_t)(e + 127);
 }
 
+// RMSNorm fused into the split: one CTA per token row (rows up to 8192 elements), the row kept in registers.
+// y = bf16(x * rsqrt(mean(x^2) + eps) * gamma) is what llama_rms_norm (src/csrc/llm/fused_llm_infer.cpp:336-363)
+// hands to the next linear; it is split here without a trip through memory. Same output layouts as above.
+constexpr int kNsThreads = 256;
+constexpr int kNsVecs = 4;
+__global__ void __launch_bounds__(kNsThreads) rmsnorm_split_kernel(const uint16_t* __restrict__ x, const void* __restrict__ gamma,
+                                                                   int gamma_f32, float eps, int M, int K, int KS, int TOK, int UKS,
+                                                                   int rowmap, uint8_t* __restrict__ terms, uint8_t* __restrict__ sfb) {
+  __shared__ float red[kNsThreads / 32];
+  pdl_trigger();
+  pdl_wait();
+  const int tok = blockIdx.x;
+  const bool live_row = tok < M;
+  const int nv = K / 8, nvp = KS * 16;  // 8-element vectors of the row, and of the row padded to whole k steps
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)tok * K);
+  uint4 v[kNsVecs];
+  float ss = 0.0f;
+#pragma unroll
+  for (int q = 0; q < kNsVecs; q++) {
+    const int i = threadIdx.x + q * kNsThreads;
+    v[q] = (live_row && i < nv) ? xr[i] : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int q = 0; q < kNsVecs; q++) {
+    const uint32_t w[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      float a = bf16_bits_to_f32((uint16_t)(w[j] & 0xffff)), b = bf16_bits_to_f32((uint16_t)(w[j] >> 16));
+      ss += a * a + b * b;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.0f;
+#pragma unroll
+  for (int w = 0; w < kNsThreads / 32; w++) tot += red[w];
+  const float inv = rsqrtf(tot / (float)K + eps);
+
+  const int tm = tok / TOK, r = tok % TOK, KU = KS / UKS;
+#pragma unroll
+  for (int q = 0; q < kNsVecs; q++) {
+    const int i = threadIdx.x + q * kNsThreads;  // vector index: four consecutive threads hold one block of 32
+    const bool in = i < nvp;
+    float f[8];
+    {
+      const uint32_t w[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+      float gm[8];
+      if (live_row && i < nv) {
+        if (gamma_f32) {
+          const float4 g0 = reinterpret_cast<const float4*>(gamma)[2 * i], g1 = reinterpret_cast<const float4*>(gamma)[2 * i + 1];
+          gm[0] = g0.x; gm[1] = g0.y; gm[2] = g0.z; gm[3] = g0.w; gm[4] = g1.x; gm[5] = g1.y; gm[6] = g1.z; gm[7] = g1.w;
+        } else {
+          const uint4 gv = reinterpret_cast<const uint4*>(gamma)[i];
+          const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            gm[2 * j] = bf16_bits_to_f32((uint16_t)(gw[j] & 0xffff));
+            gm[2 * j + 1] = bf16_bits_to_f32((uint16_t)(gw[j] >> 16));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) gm[j] = 0.0f;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; j++) {  // the normalised value rounded to bf16, as the separate kernel stores it
+        f[2 * j] = bf16_bits_to_f32(f32_to_bf16_bits(bf16_bits_to_f32((uint16_t)(w[j] & 0xffff)) * inv * gm[2 * j]));
+        f[2 * j + 1] = bf16_bits_to_f32(f32_to_bf16_bits(bf16_bits_to_f32((uint16_t)(w[j] >> 16)) * inv * gm[2 * j + 1]));
+      }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(f[j]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    int e = 0;
+    if (amax > 0.0f && amax < INFINITY) e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 - 7;
+    e = max(-127, min(127, e));
+    const float down = __uint_as_float((uint32_t)(127 - e) << 23);
+    uint32_t ph[2], pl[2];
+#pragma unroll
+    for (int h2 = 0; h2 < 2; h2++) {
+      uint32_t h4 = 0, l4 = 0;
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        float a = f[4 * h2 + 2 * j] * down, b = f[4 * h2 + 2 * j + 1] * down;
+        __nv_fp8x2_storage_t hs = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+        __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(hs, __NV_E4M3);
+        float ra = a - __half2float(__ushort_as_half(hr.x)), rb = b - __half2float(__ushort_as_half(hr.y));
+        __nv_fp8x2_storage_t ls = __nv_cvt_float2_to_fp8x2(make_float2(ra, rb), __NV_SATFINITE, __NV_E4M3);
+        h4 |= (uint32_t)hs << (16 * j);
+        l4 |= (uint32_t)ls << (16 * j);
+      }
+      ph[h2] = h4;
+      pl[h2] = l4;
+    }
+    if (!in) continue;
+    const int kb = i >> 2, part = i & 3, ks = kb >> 2, j = kb & 3;
+    const size_t step = ((size_t)tm * KU + ks / UKS) * UKS + ks % UKS;
+    int rh, rl;  // rows of the hi and lo term inside the k step, and the scale block they belong to
+    size_t blk_off;
+    if (rowmap == 1) {
+      rh = 32 * (r / 16) + (r % 16);
+      rl = rh + 16;
+      blk_off = step * 512;
+    } else {
+      rh = r;
+      rl = TOK + r;
+      blk_off = step * (size_t)((2 * TOK + 127) / 128) * 512;
+    }
+    *reinterpret_cast<uint2*>(terms + (step * 2 * TOK + rh) * 128 + j * 32 + part * 8) = make_uint2(ph[0], ph[1]);
+    *reinterpret_cast<uint2*>(terms + (step * 2 * TOK + rl) * 128 + j * 32 + part * 8) = make_uint2(pl[0], pl[1]);
+    if (part == 0) {
+      uint8_t* blk = sfb + blk_off;
+      blk[(rh / 128) * 512 + (rh % 32) * 16 + ((rh % 128) / 32) * 4 + j] = (uint8_t)(e + 127);
+      blk[(rl / 128) * 512 + (rl % 32) * 16 + ((rl % 128) / 32) * 4 + j] = (uint8_t)(e + 127);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- repack for the tensor-core path
 // Interchange tensors of remap_and_quantize_mxfp4 -> tiled packed codes and scale-factor blocks.
 //   one weight : wq [TN][KS][128 rows][64 bytes]          sfa [TN][KS][512]          KS padded to a multiple of 4
@@ -581,7 +703,15 @@ int tc_padded_ks(int64_t K, bool pair) {
 }
 
 int tc_launch_split(const uint16_t* x, int M, int K, int Mpad, int KS, int TOK, int UKS, int rowmap, uint8_t* terms, uint8_t* sfb,
-                    cudaStream_t st) {
+                    cudaStream_t st, const TcNorm* norm) {
+  if (norm && norm->gamma) {
+    TPX_REQUIRE(KS * 16 <= kNsThreads * kNsVecs, TPX_ERR_UNSUPPORTED, "fused RMSNorm: rows of more than %d elements are not supported (K=%d)",
+                kNsThreads * kNsVecs * 8, K);
+    TPX_REQUIRE((((uintptr_t)x | (uintptr_t)norm->gamma) & 15) == 0, TPX_ERR_ARG, "fused RMSNorm: x and gamma must be 16-byte aligned");
+    TPX_CUDA_OK(launch_pdl(rmsnorm_split_kernel, dim3((unsigned)Mpad), dim3(kNsThreads), 0, st, x, norm->gamma, norm->gamma_f32, norm->eps, M, K,
+                           KS, TOK, UKS, rowmap, terms, sfb));
+    return TPX_OK;
+  }
   long long threads = (long long)Mpad * KS * 4;
   TPX_CUDA_OK(launch_pdl(split_activations_kernel, dim3((unsigned)((threads + 127) / 128)), dim3(128), 0, st, x, M, K, Mpad, KS, TOK, UKS,
                          rowmap, terms, sfb));
@@ -705,7 +835,7 @@ extern "C" size_t tpx_qlinear_mxfp4_tc_scratch_bytes(int64_t M, int64_t N, int64
 
 static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M, int64_t N, int64_t K,
                   const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y,
-                  void* scratch, size_t scratch_bytes, void* stream, bool wide) {
+                  void* scratch, size_t scratch_bytes, void* stream, bool wide, const TcNorm* norm = nullptr) {
   TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear_mxfp4_tc: bad shape");
   if (M == 0) return TPX_OK;
   TPX_REQUIRE(wq && sfa && x && y, TPX_ERR_ARG, "qlinear_mxfp4_tc: null pointer");
@@ -720,7 +850,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
     b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act; b.tl = g_tc_timeline;
     { const char* e = getenv("TPX_TC_DBG"); b.dbg = e ? atoi(e) : 0; }
     { const char* e = getenv("TPX_TC_PF"); b.pf = e ? atoi(e) : 8; }
-    return tcw_run(wq, sfa, dual, x, M, N, K, b, scratch, scratch_bytes, (cudaStream_t)stream);
+    return tcw_run(wq, sfa, dual, x, M, N, K, b, scratch, scratch_bytes, (cudaStream_t)stream, norm);
   }
   TcPlan pl = tc_plan(M, N, K, dual);
   TPX_REQUIRE(scratch && scratch_bytes >= pl.total, TPX_ERR_SCRATCH, "qlinear_mxfp4_tc: scratch of %zu bytes needed, %zu given",
@@ -729,7 +859,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   unsigned char* sc = reinterpret_cast<unsigned char*>(scratch);
   uint8_t *terms = sc + pl.off_terms, *sfb = sc + pl.off_sfb;
   {
-    int rc0 = tc_launch_split(x, (int)M, (int)K, pl.Mpad, pl.KS, pl.tok, pl.uks, 0, terms, sfb, st);
+    int rc0 = tc_launch_split(x, (int)M, (int)K, pl.Mpad, pl.KS, pl.tok, pl.uks, 0, terms, sfb, st, norm);
     if (rc0) return rc0;
   }
   CUtensorMap mw, mx;
@@ -778,6 +908,15 @@ extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int p
                                     int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
                                     float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream) {
   return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, tc_wide(M));
+}
+
+extern "C" int tpx_rmsnorm_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, const void* gamma,
+                                            int gamma_is_f32, float eps, int64_t M, int64_t N, int64_t K, const uint16_t* bias, int act,
+                                            const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y, void* scratch,
+                                            size_t scratch_bytes, void* stream) {
+  TPX_REQUIRE(gamma, TPX_ERR_ARG, "rmsnorm_qlinear_mxfp4_tc: null gamma");
+  TcNorm nm = {gamma, gamma_is_f32, eps};
+  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, tc_wide(M), &nm);
 }
 
 // ---------------------------------------------------------------- variant that allocates nothing

@@ -456,7 +456,7 @@ static int tcw_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams
 }
 
 int tcw_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x, int64_t M, int64_t N, int64_t K, const TcParams& base,
-            void* scratch, size_t scratch_bytes, cudaStream_t st) {
+            void* scratch, size_t scratch_bytes, cudaStream_t st, const TcNorm* norm) {
   TcwPlan pl = tcw_plan(M, N, K, pair);
   TPX_REQUIRE(scratch && scratch_bytes >= pl.total, TPX_ERR_SCRATCH, "qlinear_mxfp4_tc: scratch of %zu bytes needed, %zu given", pl.total,
               scratch_bytes);
@@ -464,7 +464,7 @@ int tcw_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x,
               "qlinear_mxfp4_tc: y, bias, mul_in and res must be 16-byte aligned");
   unsigned char* sc = reinterpret_cast<unsigned char*>(scratch);
   uint8_t *terms = sc + pl.off_terms, *sfb = sc + pl.off_sfb;
-  int rc = tc_launch_split(x, (int)M, (int)K, pl.tokp, pl.KS, pl.tokp, 1, 1, terms, sfb, st);
+  int rc = tc_launch_split(x, (int)M, (int)K, pl.tokp, pl.KS, pl.tokp, 1, 1, terms, sfb, st, norm);
   if (rc) return rc;
   CUtensorMap mw, mx;
   const uint64_t wrows = (uint64_t)(pair ? pl.TN * 2 : pl.tiles128) * pl.KS * 128;

@@ -128,10 +128,15 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
 // host helpers shared by the tensor-core linears
 int tc_make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows);
 int tc_padded_ks(int64_t K, bool pair);
+struct TcNorm {  // optional RMSNorm applied to x on its way into the split (null gamma: none)
+  const void* gamma;
+  int gamma_f32;
+  float eps;
+};
 int tc_launch_split(const uint16_t* x, int M, int K, int Mpad, int KS, int TOK, int UKS, int rowmap, uint8_t* terms, uint8_t* sfb,
-                    cudaStream_t st);
+                    cudaStream_t st, const TcNorm* norm = nullptr);
 // decode-shaped variant (tokens on the M side of the MMA): tpx_qlinear_tcw.cu
 size_t tcw_scratch_bytes(int64_t M, int64_t N, int64_t K, bool pair);
 int tcw_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x, int64_t M, int64_t N, int64_t K, const TcParams& base,
-            void* scratch, size_t scratch_bytes, cudaStream_t st);
+            void* scratch, size_t scratch_bytes, cudaStream_t st, const TcNorm* norm = nullptr);
 }  // namespace tpx
