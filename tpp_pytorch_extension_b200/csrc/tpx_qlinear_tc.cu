@@ -144,11 +144,29 @@ __global__ void __launch_bounds__(kNsThreads) rmsnorm_split_kernel(const uint16_
   const int nv = K / 8, nvp = KS * 16;  // 8-element vectors of the row, and of the row padded to whole k steps
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)tok * K);
   uint4 v[kNsVecs];
+  float gm[kNsVecs][8];  // gamma is fetched together with the row, not after the reduction
   float ss = 0.0f;
 #pragma unroll
   for (int q = 0; q < kNsVecs; q++) {
     const int i = threadIdx.x + q * kNsThreads;
-    v[q] = (live_row && i < nv) ? xr[i] : make_uint4(0, 0, 0, 0);
+    const bool have = live_row && i < nv;
+    v[q] = have ? xr[i] : make_uint4(0, 0, 0, 0);
+    if (have && gamma_f32) {
+      const float4 g0 = reinterpret_cast<const float4*>(gamma)[2 * i], g1 = reinterpret_cast<const float4*>(gamma)[2 * i + 1];
+      gm[q][0] = g0.x; gm[q][1] = g0.y; gm[q][2] = g0.z; gm[q][3] = g0.w;
+      gm[q][4] = g1.x; gm[q][5] = g1.y; gm[q][6] = g1.z; gm[q][7] = g1.w;
+    } else if (have) {
+      const uint4 gv = reinterpret_cast<const uint4*>(gamma)[i];
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        gm[q][2 * j] = bf16_bits_to_f32((uint16_t)(gw[j] & 0xffff));
+        gm[q][2 * j + 1] = bf16_bits_to_f32((uint16_t)(gw[j] >> 16));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; j++) gm[q][j] = 0.0f;
+    }
   }
 #pragma unroll
   for (int q = 0; q < kNsVecs; q++) {
@@ -176,28 +194,10 @@ __global__ void __launch_bounds__(kNsThreads) rmsnorm_split_kernel(const uint16_
     float f[8];
     {
       const uint32_t w[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
-      float gm[8];
-      if (live_row && i < nv) {
-        if (gamma_f32) {
-          const float4 g0 = reinterpret_cast<const float4*>(gamma)[2 * i], g1 = reinterpret_cast<const float4*>(gamma)[2 * i + 1];
-          gm[0] = g0.x; gm[1] = g0.y; gm[2] = g0.z; gm[3] = g0.w; gm[4] = g1.x; gm[5] = g1.y; gm[6] = g1.z; gm[7] = g1.w;
-        } else {
-          const uint4 gv = reinterpret_cast<const uint4*>(gamma)[i];
-          const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
-#pragma unroll
-          for (int j = 0; j < 4; j++) {
-            gm[2 * j] = bf16_bits_to_f32((uint16_t)(gw[j] & 0xffff));
-            gm[2 * j + 1] = bf16_bits_to_f32((uint16_t)(gw[j] >> 16));
-          }
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; j++) gm[j] = 0.0f;
-      }
 #pragma unroll
       for (int j = 0; j < 4; j++) {  // the normalised value rounded to bf16, as the separate kernel stores it
-        f[2 * j] = bf16_bits_to_f32(f32_to_bf16_bits(bf16_bits_to_f32((uint16_t)(w[j] & 0xffff)) * inv * gm[2 * j]));
-        f[2 * j + 1] = bf16_bits_to_f32(f32_to_bf16_bits(bf16_bits_to_f32((uint16_t)(w[j] >> 16)) * inv * gm[2 * j + 1]));
+        f[2 * j] = bf16_bits_to_f32(f32_to_bf16_bits(bf16_bits_to_f32((uint16_t)(w[j] & 0xffff)) * inv * gm[q][2 * j]));
+        f[2 * j + 1] = bf16_bits_to_f32(f32_to_bf16_bits(bf16_bits_to_f32((uint16_t)(w[j] >> 16)) * inv * gm[q][2 * j + 1]));
       }
     }
     float amax = 0.0f;
@@ -382,8 +382,13 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   const long long U = (long long)p.TN * p.TM * p.KS;
   const long long G = gridDim.x;
   const long long T = (long long)p.TN * p.TM;
-  const long long u0 = p.whole_tiles ? ((long long)blockIdx.x * T / G) * p.KS : (long long)blockIdx.x * U / G;
-  const long long u1 = p.whole_tiles ? (((long long)blockIdx.x + 1) * T / G) * p.KS : ((long long)blockIdx.x + 1) * U / G;
+  // p.cluster > 1: the CTAs of a cluster share one tile and cut its k units evenly between them
+  const int crank = p.cluster > 1 ? (int)tc_cluster_rank() : 0;
+  const long long ctile = blockIdx.x / p.cluster;
+  const long long u0 = p.cluster > 1 ? ctile * p.KS + (long long)crank * p.KS / p.cluster
+                     : p.whole_tiles ? ((long long)blockIdx.x * T / G) * p.KS : (long long)blockIdx.x * U / G;
+  const long long u1 = p.cluster > 1 ? ctile * p.KS + ((long long)crank + 1) * p.KS / p.cluster
+                     : p.whole_tiles ? (((long long)blockIdx.x + 1) * T / G) * p.KS : ((long long)blockIdx.x + 1) * U / G;
   const int nunits = (int)(u1 - u0);
   const int tile0 = (int)(u0 / p.KS), ks0 = (int)(u0 % p.KS);
 
@@ -580,6 +585,14 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           }
           if (whole) {
             if (n < p.N && tok0 + c0 < p.M) tc_finish16<DUAL>(p, tok0 + c0, n, r0, r1);
+          } else if (p.cluster > 1) {  // partial of a cluster member: [weight][128 rows][TOK] fp32 at the start of its stages
+            const uint32_t sp = smem_base + (uint32_t)((row * TOK + c0) * 4);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+              tc_st_shared_f4(sp + q * 16, make_float4(r0[4 * q], r0[4 * q + 1], r0[4 * q + 2], r0[4 * q + 3]));
+              if (DUAL)
+                tc_st_shared_f4(sp + 128 * TOK * 4 + q * 16, make_float4(r1[4 * q], r1[4 * q + 1], r1[4 * q + 2], r1[4 * q + 3]));
+            }
           } else {
 #pragma unroll
             for (int q = 0; q < 4; q++) {
@@ -604,6 +617,41 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   if (threadIdx.x == 64) tc_stamp(p, 6);
   tc_fence_before();
   __syncthreads();
+  if (p.cluster > 1) {
+    // every member's partial is in its own shared memory; each member takes some 16-token chunks of the tile, adds
+    // the members' parts in rank order (distributed shared memory reads) and runs the epilogue on them. Nobody
+    // leaves before all have finished reading.
+    tc_cluster_sync();
+    if (warp >= 2) {  // 16-token chunks of the tile go round the members
+      const int sub = warp & 3;
+      const int row = sub * 32 + lane;
+      const int tn = (int)(ctile / p.TM), tm = (int)(ctile % p.TM);
+      const int n = tn * 128 + row, tok0 = tm * TOK;
+#pragma unroll 1
+      for (int c0 = crank * 16; c0 < TOK; c0 += 16 * p.cluster) {
+        float v[16], v2[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) v[j] = v2[j] = 0.0f;
+        const uint32_t sp = smem_base + (uint32_t)((row * TOK + c0) * 4);
+        for (int m = 0; m < p.cluster; m++) {
+          const uint32_t rp = tc_mapa(sp, (uint32_t)m);
+          float4 t[4], t2[4];
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            t[q] = tc_ld_cluster_f4(rp + q * 16);
+            if (DUAL) t2[q] = tc_ld_cluster_f4(rp + 128 * TOK * 4 + q * 16);
+          }
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            v[4 * q] += t[q].x; v[4 * q + 1] += t[q].y; v[4 * q + 2] += t[q].z; v[4 * q + 3] += t[q].w;
+            if (DUAL) { v2[4 * q] += t2[q].x; v2[4 * q + 1] += t2[q].y; v2[4 * q + 2] += t2[q].z; v2[4 * q + 3] += t2[q].w; }
+          }
+        }
+        if (n < p.N && tok0 + c0 < p.M) tc_finish16<DUAL>(p, tok0 + c0, n, v, v2);
+      }
+    }
+    tc_cluster_sync();
+  }
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)C::TMEM_COLS) : "memory");
@@ -720,11 +768,11 @@ int tc_launch_split(const uint16_t* x, int M, int K, int Mpad, int KS, int TOK, 
 
 struct TcPlan {
   int tok, uks;     // tokens per tile, k steps per unit
-  int TN, TM, KS, KU, Mpad, grid, xbox, whole_tiles;
+  int TN, TM, KS, KU, Mpad, grid, xbox, whole_tiles, cluster;
   size_t off_terms, off_sfb, off_partial, total;
 };
 
-static TcPlan tc_plan(int64_t M, int64_t N, int64_t K, bool pair) {
+static TcPlan tc_plan(int64_t M, int64_t N, int64_t K, bool pair, bool allow_cluster = true) {
   TcPlan pl;
   pl.tok = M <= 16 ? 16 : M <= 32 ? 32 : (M <= 64 || pair) ? 64 : 128;  // a pair needs 4*tok columns of tensor memory
   pl.uks = pair ? 2 : (pl.tok <= 32 ? 4 : 2);
@@ -743,6 +791,15 @@ static TcPlan tc_plan(int64_t M, int64_t N, int64_t K, bool pair) {
   pl.whole_tiles = (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
   { const char* e = getenv("TPX_TC_WHOLE"); if (e) pl.whole_tiles = atoi(e); }
   pl.grid = pl.whole_tiles ? (int)(T < sms ? T : sms) : (int)(U < sms ? U : sms);
+  // Few tiles: a cluster of c CTAs per tile cuts K between them and reduces through distributed shared memory,
+  // which takes the fix-up pass (a second kernel behind a round trip through L2) off the critical path.
+  pl.cluster = 1;
+  if (allow_cluster && !pl.whole_tiles && T * 2 <= sms && pl.tok <= 32) {
+    int c = (int)(sms / T);
+    if (c > 8) c = 8;
+    if (c > pl.KU) c = pl.KU;
+    if (c > 1) pl.cluster = c;
+  }
   size_t o = kTcCounterBytes;
   auto bump = [&](size_t bytes) { size_t r = o; o += (bytes + 1023) & ~(size_t)1023; return r; };
   pl.off_terms = bump((size_t)pl.Mpad * pl.KS * 128 * 2);
@@ -773,6 +830,35 @@ static int tc_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams&
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (p.cluster > 1) {
+    // one cluster per tile, all of them resident at once, or not at all (then the tiles are cut stream-K fashion)
+    const int tiles = p.TN * p.TM;
+    cudaLaunchConfig_t cc = cfg;
+    cc.gridDim = dim3((unsigned)(tiles * p.cluster));
+    cudaLaunchAttribute a2[2];
+    a2[0] = attr[0];
+    a2[1].id = cudaLaunchAttributeClusterDimension;
+    a2[1].val.clusterDim.x = (unsigned)p.cluster;
+    a2[1].val.clusterDim.y = 1;
+    a2[1].val.clusterDim.z = 1;
+    cc.attrs = a2;
+    cc.numAttrs = 2;
+    static int fits[16][9] = {};  // 0 unknown, else 1 + the number of clusters of this size that can be resident
+    int& f = fits[(dev >= 0 && dev < 16) ? dev : 0][p.cluster];
+    if (f == 0) {
+      int n = 0;
+      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, qlinear_tc_kernel<TOK, DUAL, UKS>, &cc);
+      if (e != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
+      f = 1 + n;
+    }
+    if (f - 1 >= tiles) {
+      TPX_CUDA_OK(cudaLaunchKernelEx(&cc, qlinear_tc_kernel<TOK, DUAL, UKS>, w, x, p));
+      return TPX_OK;
+    }
+    TcParams q = p;
+    q.cluster = 1;
+    return tc_launch<TOK, DUAL, UKS>(w, x, q, grid, st);
+  }
   TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tc_kernel<TOK, DUAL, UKS>, w, x, p));
   if (!p.whole_tiles && grid > 1) {  // tiles cut between CTAs are completed by the fix-up kernel
     cudaLaunchConfig_t c2 = {};
@@ -886,9 +972,10 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   p.partial = reinterpret_cast<float*>(sc + pl.off_partial);
   p.counters = reinterpret_cast<unsigned*>(sc);
   p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
-  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = pl.TM; p.act = act; p.whole_tiles = pl.whole_tiles; p.tl = g_tc_timeline;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = pl.TM; p.act = act; p.whole_tiles = pl.whole_tiles; p.cluster = pl.cluster; p.tl = g_tc_timeline;
   { const char* e = getenv("TPX_TC_DBG"); p.dbg = e ? atoi(e) : 0; }
   { const char* e = getenv("TPX_TC_PF"); p.pf = e ? atoi(e) : 6; }
+  { const char* e = getenv("TPX_TC_CLUSTER"); if (e && atoi(e) == 0) p.cluster = 1; }
   if (dual) {
     switch (pl.tok) {
       case 16: return tc_launch<16, true, 2>(mw, mx, p, pl.grid, st);

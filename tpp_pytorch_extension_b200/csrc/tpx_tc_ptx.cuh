@@ -29,6 +29,7 @@ struct TcParams {
   int act;
   int whole_tiles;      // 1: every CTA owns whole output tiles (no partial tiles, no fix-up)
   unsigned long long* tl;  // optional per-CTA timeline (8 globaltimer stamps each), null in normal use
+  int cluster;          // CTAs per thread-block cluster that share one output tile along K (1: none)
   int pf;               // units prefetched into L2 ahead of the shared-memory stages
   int dbg;              // debug knobs for timing experiments: 1 = skip MMAs, 2 = skip weight copies
 };
@@ -77,6 +78,29 @@ __device__ __forceinline__ void tc_bulk_g2s(uint32_t dst, const void* src, uint3
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
+}
+// thread-block cluster helpers (split-K partners reduce through distributed shared memory)
+__device__ __forceinline__ uint32_t tc_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void tc_cluster_sync() {  // every thread of every CTA of the cluster
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t tc_mapa(uint32_t saddr, uint32_t rank) {  // the same offset in CTA `rank` of the cluster
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float4 tc_ld_cluster_f4(uint32_t caddr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(caddr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void tc_st_shared_f4(uint32_t saddr, float4 v) {
+  asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(saddr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 // L2 prefetches: no shared memory is tied up while the data travels from HBM
 __device__ __forceinline__ void tc_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
