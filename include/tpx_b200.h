@@ -175,9 +175,12 @@ int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const int64_t* pos,
 /* Attention over the blocked cache. Replaces attn<T> (src/csrc/llm/attn.cpp:780-955):
  *   out = softmax(q.k^T / sqrt(H) + am[b][key], causal: key <= key_len - Sq + query) . v
  * q/out [B][Nkv][Sq][R][H] (GQA group folded into the row dimension, attn.cpp:793-795), am additive bf16 mask
- * [B][Spad] or NULL (0 keep, finfo.min drop; attn.h:310-322). fp32 scores, softmax and accumulation, one bf16
- * rounding of the output. With a long cache and few (batch, head) pairs the key range is split over CTAs and
- * merged by a second kernel (flash-decoding); the scratch holds the un-normalised partials. out_bsnrh != 0
+ * [B][Spad] or NULL (0 keep, finfo.min drop; attn.h:310-322). Scores and the output are accumulated in fp32 on
+ * the tensor cores (bf16 operands: the probabilities are rounded to bf16 before they meet the values, as a bf16
+ * batch-reduce GEMM would), softmax in fp32, one bf16 rounding of the output. With a long cache and few (batch,
+ * head) pairs the key range is split over CTAs (flash-decoding); the split that finishes last merges them. The
+ * scratch holds arrival counters and the un-normalised partials: it must be 16-byte aligned and zero-filled once
+ * before first use (the kernel leaves the counters zero); calls sharing it must not overlap. out_bsnrh != 0
  * writes out as [B][Sq][Nkv][R][H], i.e. already as the [B*Sq][Nq*H] rows of the output projection (the
  * reference permutes and copies, src/csrc/llm/fused_llm_infer.cpp:581). With dev_len != NULL the number of keys
  * is *dev_len + Sq, read on the device; `key_len` is then only the planning maximum (cache capacity).         */

@@ -107,10 +107,11 @@ _aux = {}
 
 
 def aux_scratch(nbytes, device):
-    """Scratch with no zero-initialisation contract (attention partials), separate from the linear's."""
+    """Attention scratch (arrival counters of the KV splits, zero before first use and left zero by the kernel, then
+    the splits' partials), separate from the linear's."""
     key = (device.index, stream())
     buf = _aux.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _aux[key] = buf
     return buf

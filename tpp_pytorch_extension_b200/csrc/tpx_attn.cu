@@ -181,6 +181,7 @@ struct AttnParams {
   const uint16_t* am;   // [B][Spad] additive mask or null
   uint16_t* out;        // same shape as q
   float* part;          // [B*Nkv][chunks][splits][16][H + 2]
+  unsigned* counters;   // [B*Nkv][chunks] arrivals of the KV splits; zero between calls
   int B, Nkv, Sq, R, H;
   int key_len, Spad, causal;
   int chunks, splits;
@@ -436,33 +437,37 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_mma_kernel(AttnParams p)
       p.out[attn_out_index(p, bn, cta_row0 + r, H) + h] = f32_to_bf16_bits(oo / ll);
     } else {
       float* dst = p.part + ((((int64_t)bn * p.chunks + chunk) * p.splits + split) * kAttnRows + r) * (H + 2);
-      dst[h] = oo;
-      if (h == 0) { dst[H] = mm; dst[H + 1] = ll; }
+      __stcg(dst + h, oo);
+      if (h == 0) { __stcg(dst + H, mm); __stcg(dst + H + 1, ll); }
     }
   }
-}
-
-template <int H>
-__global__ void attn_merge_kernel(AttnParams p) {
-  pdl_trigger();
-  pdl_wait();
-  const int bn = blockIdx.x, chunk = blockIdx.y;
-  const int rows_total = p.Sq * p.R;
-  const int row0 = chunk * kAttnRows;
-  const int rows = min(kAttnRows, rows_total - row0);
+  if (p.splits == 1) return;
+  // The split that arrives last merges all of them (no second kernel behind a grid boundary).
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(&p.counters[bn * p.chunks + chunk], 1u);
+    is_last = prev == (unsigned)p.splits - 1;
+    if (is_last) p.counters[bn * p.chunks + chunk] = 0;  // ready for the next call
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
   for (int i = threadIdx.x; i < rows * H; i += blockDim.x) {
     const int r = i / H, h = i % H;
     const float* base = p.part + (((int64_t)bn * p.chunks + chunk) * p.splits * kAttnRows + r) * (H + 2);
     float mm = -INFINITY;
-    for (int s = 0; s < p.splits; s++) mm = fmaxf(mm, base[(int64_t)s * kAttnRows * (H + 2) + H]);
+    for (int s2 = 0; s2 < p.splits; s2++) mm = fmaxf(mm, __ldcg(base + (int64_t)s2 * kAttnRows * (H + 2) + H));
     float ll = 0.0f, oo = 0.0f;
-    for (int s = 0; s < p.splits; s++) {
-      const float* ps = base + (int64_t)s * kAttnRows * (H + 2);
-      const float f = (ps[H] == -INFINITY) ? 0.0f : __expf(ps[H] - mm);
-      ll += ps[H + 1] * f;
-      oo += ps[h] * f;
+    for (int s2 = 0; s2 < p.splits; s2++) {
+      const float* ps = base + (int64_t)s2 * kAttnRows * (H + 2);
+      const float pm = __ldcg(ps + H);
+      const float f = (pm == -INFINITY) ? 0.0f : __expf(pm - mm);
+      ll += __ldcg(ps + H + 1) * f;
+      oo += __ldcg(ps + h) * f;
     }
-    p.out[attn_out_index(p, bn, row0 + r, H) + h] = f32_to_bf16_bits(oo / ll);
+    p.out[attn_out_index(p, bn, cta_row0 + r, H) + h] = f32_to_bf16_bits(oo / ll);
   }
 }
 
@@ -550,11 +555,15 @@ static int attn_launch(const AttnParams& p, dim3 grid, cudaStream_t st) {
   return TPX_OK;
 }
 
+static size_t attn_counter_bytes(int64_t B, int64_t Nkv, int chunks) {
+  return ((size_t)B * Nkv * chunks * sizeof(unsigned) + 255) & ~(size_t)255;
+}
+
 extern "C" size_t tpx_attention_scratch_bytes(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len) {
   int chunks, splits;
   attn_plan(B, Nkv, Sq, R, key_len, &chunks, &splits);
   if (splits == 1) return 0;
-  return (size_t)B * Nkv * chunks * splits * kAttnRows * (H + 2) * sizeof(float);
+  return attn_counter_bytes(B, Nkv, chunks) + (size_t)B * Nkv * chunks * splits * kAttnRows * (H + 2) * sizeof(float);
 }
 
 extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, const uint16_t* am, int64_t B,
@@ -566,7 +575,7 @@ extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16
   TPX_REQUIRE(!am || Spad >= key_len, TPX_ERR_ARG, "attention: mask of %ld keys is shorter than the cache (%ld)", (long)Spad, (long)key_len);
   if (Sq == 0) return TPX_OK;
   AttnParams p;
-  p.q = q; p.kc = kc; p.vc = vc; p.am = am; p.out = out; p.part = reinterpret_cast<float*>(scratch);
+  p.q = q; p.kc = kc; p.vc = vc; p.am = am; p.out = out; p.part = nullptr; p.counters = nullptr;
   p.B = (int)B; p.Nkv = (int)Nkv; p.Sq = (int)Sq; p.R = (int)R; p.H = (int)H;
   p.key_len = (int)key_len; p.Spad = (int)Spad; p.causal = causal; p.out_bsnrh = out_bsnrh; p.dev_len = dev_len;
   attn_plan(B, Nkv, Sq, R, key_len, &p.chunks, &p.splits);
@@ -574,6 +583,9 @@ extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16
   if (p.splits > 1) {
     size_t need = tpx_attention_scratch_bytes(B, Nkv, Sq, R, H, key_len);
     TPX_REQUIRE(scratch && scratch_bytes >= need, TPX_ERR_SCRATCH, "attention: scratch of %zu bytes needed, %zu given", need, scratch_bytes);
+    TPX_REQUIRE(((uintptr_t)scratch & 15) == 0, TPX_ERR_ARG, "attention: scratch must be 16-byte aligned");
+    p.counters = reinterpret_cast<unsigned*>(scratch);
+    p.part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(scratch) + attn_counter_bytes(B, Nkv, p.chunks));
   }
   dim3 grid((unsigned)(B * Nkv), (unsigned)p.chunks, (unsigned)p.splits);
   TPX_REQUIRE(p.chunks <= 65535, TPX_ERR_UNSUPPORTED, "attention: too many query rows in one call");
@@ -583,11 +595,6 @@ extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16
   if (H == 128) rc = decode ? attn_launch<128, 1>(p, grid, st) : attn_launch<128, 0>(p, grid, st);
   else rc = decode ? attn_launch<64, 1>(p, grid, st) : attn_launch<64, 0>(p, grid, st);
   if (rc) return rc;
-  if (p.splits > 1) {
-    dim3 g2((unsigned)(B * Nkv), (unsigned)p.chunks);
-    if (H == 128) TPX_CUDA_OK(launch_pdl(attn_merge_kernel<128>, g2, dim3(256), 0, st, p));
-    else TPX_CUDA_OK(launch_pdl(attn_merge_kernel<64>, g2, dim3(256), 0, st, p));
-  }
   return TPX_OK;
 }
 
