@@ -35,6 +35,13 @@ NCU_TRAFFIC = {1: 63.06e6, 8: 63.06e6, 64: 63.60e6}  # M=1 runs the M=8 kernel i
 N_COPIES = 6  # distinct packed weight sets: 6 x 93.6 MB = 561 MB >> 126 MB of L2
 
 
+def _lib_launch_count():
+    """The library's own tally of the kernels it has launched (tpx_launch_count)."""
+    from tpp_pytorch_extension_b200 import _lib
+    fn = _lib.lib().tpx_launch_count
+    return lambda: int(fn())
+
+
 def packed_bytes(N, K):
     return N * K // 2 + N * K // 32
 
@@ -218,10 +225,8 @@ def run_ours(args):
     ys_host = {M: torch.empty(M, D_MODEL, dtype=torch.bfloat16).pin_memory() for M in SWEEP}
     torch.cuda.synchronize()
 
-    def launches_for(M):
-        # per (gate/up, down) pair of ops: the tensor-core path launches the activation split and the GEMM;
-        # the streaming path launches once per 32 tokens
-        return 4 if F.mxfp4_path() == "tc" else 2 * ((M + 31) // 32)
+    launch_count = _lib_launch_count()
+    per_op_launches = {}  # (M, op) -> kernels the library launched for one call
 
     counter = [0]
 
@@ -232,10 +237,13 @@ def run_ours(args):
             x = xs_host[M].to(dev, non_blocking=True) if host else xs[M]
             if events is not None:
                 events[mi][0].record()
+            c0 = launch_count()
             h = F.fc_gate_up(x, wg, wu)
+            c1 = launch_count()
             if events is not None:
                 events[mi][1].record()
             y = F.fc_plain(h, wd)
+            per_op_launches[(M, "gate_up")], per_op_launches[(M, "down")] = c1 - c0, launch_count() - c1
             if events is not None:
                 events[mi][2].record()
             if host:
@@ -258,10 +266,12 @@ def run_ours(args):
     # Hold the stream busy while the host enqueues the timed steps, so that the events measure device
     # time of back-to-back launches and not the host's launch rate (the end-to-end figure below keeps it).
     torch.cuda._sleep(int(args.steps * len(SWEEP) * 2 * 60e-6 * 1.9e9) + int(5e6))
+    launches_before = launch_count()
     t_start.record()
     for s in range(args.steps):
         sweep(evs[s])
     t_end.record()
+    timed_launches = launch_count() - launches_before
     barrier()
     clocks = sampler.stop()
     total_ms = t_start.elapsed_time(t_end)
@@ -316,7 +326,7 @@ def run_ours(args):
             kernels.append({"M": M, "op": "gate_up" if pair else "down", "ms": round(ms, 5),
                             "gbs": round(op_bytes(M, pair) / (ms * 1e-3) / 1e9, 1),
                             "tflops": round(op_flops(M, pair) / (ms * 1e-3) / 1e12, 2),
-                            "launches": launches_for(M) // 2})
+                            "launches": per_op_launches.get((M, "gate_up" if pair else "down"))})
     dom_share = float(seg[dom, 0] / max(1e-9, sum(seg[i].sum() for i in dec)))
     if rank == 0:
         line = {
@@ -338,7 +348,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": sum(M * D_MODEL * 2 for M in SWEEP),
                     "d2h_bytes_per_step": sum(M * D_MODEL * 2 for M in SWEEP),
                     "scope": "same decode-shaped launches, pinned host X in and host Y out inside the timed region"},
-            "gpu_launches": args.steps * sum(launches_for(M) for M in SWEEP),
+            "gpu_launches": int(timed_launches),
             "clocks": clocks,
         }
         if world == 1:

@@ -44,6 +44,9 @@ int tpx_version(void);
 const char* tpx_last_error(void);
 /* number of SMs of the current device (used by callers to size scratch) */
 int tpx_sm_count(void);
+/* Number of kernels of the linear / norm / rope / attention path this library has launched so far in this process
+ * (host-side tally, for benchmarks that report their launch count). No counterpart in the reference.          */
+unsigned long long tpx_launch_count(void);
 
 /* ---------------------------------------------------------------- quantize / remap
  * Replaces _C._qtype.remap_and_quantize_mxfp4 (src/csrc/qtypes.cpp:783-864, pybind :1086).

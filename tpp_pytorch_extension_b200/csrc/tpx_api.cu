@@ -14,6 +14,9 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+static unsigned long long g_launches = 0;  // relaxed tally; exact when one host thread launches
+void count_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -92,3 +95,5 @@ extern "C" int tpx_qlinear(int kind, const uint8_t* pk_codes, const void* pk_sca
   return qlinear_stream_launch(kind, pk_codes, pk_scales, pk_codes2, pk_scales2, block_size, x, M, N, K, bias, act, mul_in,
                         res, res_scale, y, scratch, scratch_bytes, (cudaStream_t)stream);
 }
+
+extern "C" unsigned long long tpx_launch_count(void) { return __atomic_load_n(&tpx::g_launches, __ATOMIC_RELAXED); }

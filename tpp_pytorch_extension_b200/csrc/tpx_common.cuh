@@ -60,6 +60,7 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 }
 
 int sm_count();
+void count_launch();  // host-side tally behind tpx_launch_count()
 
 // Programmatic dependent launch. Every kernel of the decoder-layer path starts with pdl_trigger() (the next
 // kernel in the stream may be scheduled and run its prologue while this one works) and calls pdl_wait() before
@@ -81,6 +82,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  count_launch();
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

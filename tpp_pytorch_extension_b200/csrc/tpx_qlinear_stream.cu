@@ -527,6 +527,7 @@ static int launch_one(const StreamParams& p, const Plan& pl, cudaStream_t st) {
     TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_stream<KIND, NT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
     if (dev >= 0 && dev < 16) opted[dev] = true;
   }
+  count_launch();
   qlinear_stream<KIND, NT, DUAL><<<dim3(pl.grid_x, pl.ksplit), kThreads, pl.smem, st>>>(p);
   TPX_LAUNCH_OK();
   return TPX_OK;

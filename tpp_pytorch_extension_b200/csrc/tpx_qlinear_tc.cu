@@ -852,13 +852,15 @@ static int tc_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams&
       f = 1 + n;
     }
     if (f - 1 >= tiles) {
-      TPX_CUDA_OK(cudaLaunchKernelEx(&cc, qlinear_tc_kernel<TOK, DUAL, UKS>, w, x, p));
+      count_launch();
+  TPX_CUDA_OK(cudaLaunchKernelEx(&cc, qlinear_tc_kernel<TOK, DUAL, UKS>, w, x, p));
       return TPX_OK;
     }
     TcParams q = p;
     q.cluster = 1;
     return tc_launch<TOK, DUAL, UKS>(w, x, q, grid, st);
   }
+  count_launch();
   TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tc_kernel<TOK, DUAL, UKS>, w, x, p));
   if (!p.whole_tiles && grid > 1) {  // tiles cut between CTAs are completed by the fix-up kernel
     cudaLaunchConfig_t c2 = {};
@@ -867,7 +869,8 @@ static int tc_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams&
     c2.stream = st;
     c2.attrs = attr;
     c2.numAttrs = 1;
-    TPX_CUDA_OK(cudaLaunchKernelEx(&c2, tc_fixup_kernel<DUAL>, p, (int)TOK, grid));
+    count_launch();
+  TPX_CUDA_OK(cudaLaunchKernelEx(&c2, tc_fixup_kernel<DUAL>, p, (int)TOK, grid));
   }
   return TPX_OK;
 }

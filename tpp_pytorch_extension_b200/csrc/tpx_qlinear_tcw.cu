@@ -441,6 +441,7 @@ static int tcw_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  count_launch();
   TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tcw_kernel<TOKP, DUAL>, w, x, p, wq, tiles128));
   if (!p.whole_tiles && grid > 1) {
     constexpr int GROUPS = DUAL ? 16 : 32;
@@ -450,7 +451,8 @@ static int tcw_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams
     c2.stream = st;
     c2.attrs = attr;
     c2.numAttrs = 1;
-    TPX_CUDA_OK(cudaLaunchKernelEx(&c2, tcw_fixup_kernel<DUAL>, p, (int)TOKP, grid));
+    count_launch();
+  TPX_CUDA_OK(cudaLaunchKernelEx(&c2, tcw_fixup_kernel<DUAL>, p, (int)TOKP, grid));
   }
   return TPX_OK;
 }
