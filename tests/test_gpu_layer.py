@@ -116,8 +116,6 @@ def test_cache_growth_and_crop(cuda):
     assert c.get_seq_length() == 100
     c.crop(500)
     assert c.get_seq_length() == 100
-    with pytest.raises(NotImplementedError):
-        c.reorder_cache(torch.zeros(2, dtype=torch.long))
 
 
 @pytest.mark.parametrize("kind", ["mxfp4", "int8"])
@@ -154,3 +152,30 @@ def test_llama_layer_prefill_then_decode(cuda, kind):
         got = to_host_bits(out[1])
         n = min(got.shape[0], kc_ref.shape[0])
         assert O.rel_err(got[:n], kc_ref[:n]) <= TOL
+
+
+def test_reorder_cache_gathers_beams(cuda):
+    """Beam-search reordering: sequence i continues the history of old sequence beam_idx[i]; a cache of CB sequences
+    is first repeated per beam (src/csrc/llm/attn.h:327-403)."""
+    from tpp_pytorch_extension_b200._C._tpp_attn import TppCache
+    rng = np.random.default_rng(5)
+    CB, Nkv, S, H = 2, 2, 40, 64
+    k = O.randn_bf16(rng, (CB, Nkv, S, H))
+    v = O.randn_bf16(rng, (CB, Nkv, S, H))
+    cache = TppCache()
+    kc, vc = cache.update(to_dev_bf16(k, cuda), to_dev_bf16(v, cuda), 0)
+    beams = torch.tensor([1, 0, 3, 3])  # 2 beams per cached sequence: rows (0,0,1,1) after the repeat
+    cache.reorder_cache(beams)
+    lc = cache.layer(0)
+    assert lc.k.shape[1] == 4 and lc.offset == S
+    got_k, got_v = to_host_bits(lc.k), to_host_bits(lc.v)
+    src = np.array([0, 0, 1, 1])[beams.numpy()]
+    for i in range(4):
+        for t in (0, 31, 32, S - 1):
+            assert np.array_equal(got_k[t // 32, i, :, t % 32], k[src[i], :, t])
+            assert np.array_equal(got_v[t // 32, i, :, t % 32], v[src[i], :, t])
+    cache.reorder_cache(torch.tensor([3, 2, 1, 0]))
+    got_k = to_host_bits(cache.layer(0).k)
+    assert np.array_equal(got_k[0, 0, :, 5], k[src[3], :, 5])
+    with pytest.raises(Exception):
+        cache.reorder_cache(torch.tensor([0, 1, 2]))

@@ -92,7 +92,25 @@ class TppCache:
                 lc.offset = max_length
 
     def reorder_cache(self, beam_idx):
-        raise NotImplementedError("beam-search cache reordering (src/csrc/llm/attn.h:327-403) is not built yet")
+        """TppCache::reorder_cache (src/csrc/llm/attn.h:327-403): after the call, sequence i continues the history
+        of the old sequence beam_idx[i]. The reference records the permutations and gathers rows inside attention;
+        here the cache rows are gathered once per call (the batch dimension of [S1, B, Nkv, 32, H] is dim 1), which
+        yields the same keys and values for every later step. A cache of CB sequences meeting B = CB * beams
+        indices is first repeated per beam, as the reference does (attn.h:345-367)."""
+        beam_idx = beam_idx.to(torch.long)
+        B = beam_idx.shape[0]
+        for lc in self.layers:
+            if lc.k is None:
+                continue
+            CB = lc.k.shape[1]
+            if CB != B:
+                if B % CB != 0:
+                    raise _lib.TpxError(f"New batch ({B}) must be multiple of cached batch size ({CB})")
+                lc.k = lc.k.repeat_interleave(B // CB, dim=1)
+                lc.v = lc.v.repeat_interleave(B // CB, dim=1)
+            idx = beam_idx.to(lc.k.device)
+            lc.k = lc.k.index_select(1, idx).contiguous()
+            lc.v = lc.v.index_select(1, idx).contiguous()
 
 
 def attention(q, kc, vc, mask, key_len, causal=True, out_bsnrh=False, dev_len=None):
