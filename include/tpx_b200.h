@@ -90,6 +90,11 @@ int tpx_repack_mxfp4(const uint8_t* codes, const uint8_t* scales, int64_t N, int
                      uint8_t* pk_scales, void* stream);
 int tpx_repack_qint8(const int8_t* q, const float* scales, int64_t N, int64_t K, int64_t block_size,
                      uint8_t* pk_codes, float* pk_scales, void* stream);
+/* The packed int8 weight back as a plain bf16 matrix [N][K] = bf16(q * scale). Used for many-token calls (prefill)
+ * of int8 weights, which run as a dense bf16 GEMM on the unpacked weight; the decode-sized calls stream the packed
+ * tiles. No counterpart in the reference (its int8 path quantises the activations instead, fused_gemm.h:1249). */
+int tpx_unpack_qint8_bf16(const uint8_t* pk_codes, const float* pk_scales, int64_t N, int64_t K, int64_t block_size,
+                          uint16_t* out, void* stream);
 
 /* ---------------------------------------------------------------- quantized linear
  * Replaces GemmCaller / fc_plain with a post-op (src/csrc/fused_gemm.h:1509-1650) and

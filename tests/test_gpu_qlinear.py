@@ -110,6 +110,22 @@ def test_rmsnorm_fused_into_linear(cuda, M):
     assert np.array_equal(y3, y)
 
 
+def test_int8_many_tokens(cuda):
+    """Prefill-sized calls on int8 weights (unpacked to bf16 + dense GEMM) against the oracle, with post-ops and the pair."""
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    rng = np.random.default_rng(123)
+    N, K, M = 256, 512, 200
+    q, wd, _ = make_qweight(rng, N, K, "int8", cuda)
+    q2, wd2, _ = make_qweight(rng, N, K, "int8", cuda)
+    x = O.randn_bf16(rng, (M, K))
+    bias = O.randn_bf16(rng, (N,), 0.01)
+    res = O.randn_bf16(rng, (M, N))
+    y = run_fc(x, q, cuda, bias=to_dev_bf16(bias, cuda), act="silu", res=to_dev_bf16(res, cuda), res_scale=0.5)
+    assert O.rel_err(y, O.qlinear(x, wd, bias=bias, res=res, res_scale=0.5, act=O.ACT_SILU)) <= TOL
+    y2 = to_host_bits(F.fc_gate_up(to_dev_bf16(x, cuda), q, q2))
+    assert O.rel_err(y2, O.gate_up(x, wd, wd2)) <= TOL
+
+
 def test_int8_reference_arithmetic_is_within_tolerance(cuda):
     """The reference's int8 path quantises activations on the fly; ours is weight-only. Both sit within the
     tolerance of the fp32 oracle, and of each other."""

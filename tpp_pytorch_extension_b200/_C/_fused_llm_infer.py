@@ -70,6 +70,8 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
         if (w2.out_features, w2.in_features, w2.kind, w2.block_size) != (N, K, w.kind, w.block_size):
             raise _lib.TpxError("gate/up weights must have the same shape and quantization")
         pc2, ps2 = w2.packed()
+    if w.kind != 1 and M > INT8_DENSE_MIN_M:
+        return _int8_dense(x, y, w, w2, pc, ps, pc2, ps2, bias, act, mul_in, res, res_scale)
     key = (w.kind, min(M, 32), N, K, w.block_size, w2 is not None)
     nb = _SCRATCH_BYTES.get(key)
     if nb is None:
@@ -80,6 +82,41 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
                        float(res_scale), y.data_ptr(), sc.data_ptr(), sc.numel(), _lib.stream())
     if rc:
         _lib.check(rc)
+    return y
+
+
+INT8_DENSE_MIN_M = 64
+
+
+def _int8_dense(x, y, w, w2, pc, ps, pc2, ps2, bias, act, mul_in, res, res_scale):
+    """Many tokens on int8 weights: the streaming kernel takes 32 tokens per pass over the weight, so prefill-sized
+    calls unpack the weight to bf16 once per call (tpx_unpack_qint8_bf16, 3 bytes of traffic per weight) and run a
+    dense bf16 GEMM on it (cuBLAS through torch: a plain library GEMM), with the post-ops applied in fp32 after it."""
+    L = _lib.lib()
+    N, K = w.out_features, w.in_features
+    x2 = x.reshape(-1, K)
+
+    def dense(codes, scales):
+        wb = torch.empty((N, K), dtype=torch.bfloat16, device=x.device)
+        _lib.check(L.tpx_unpack_qint8_bf16(codes.data_ptr(), scales.data_ptr(), N, K, w.block_size, wb.data_ptr(), _lib.stream()))
+        return torch.matmul(x2, wb.t()).float()
+
+    v = dense(pc, ps)
+    if bias is not None and bias.numel() > 0:
+        v = v + bias.float()
+    if act == "gelu":
+        v = torch.nn.functional.gelu(v)
+    elif act == "silu":
+        v = torch.nn.functional.silu(v)
+    elif act == "relu":
+        v = torch.relu(v)
+    if w2 is not None:
+        v = v * dense(pc2, ps2)
+    if mul_in is not None and mul_in.numel() > 0:
+        v = v * mul_in.reshape(-1, N).float()
+    if res is not None and res.numel() > 0:
+        v = v + res.reshape(-1, N).float() * float(res_scale)
+    y.copy_(v.to(torch.bfloat16).view(y.shape))
     return y
 
 

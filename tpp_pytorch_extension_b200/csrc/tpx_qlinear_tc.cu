@@ -312,7 +312,8 @@ struct TcCfg {
   static constexpr int COLS_RAW = D_COLS + STAGES * SF_COLS;
   static constexpr int TMEM_COLS = COLS_RAW <= 32 ? 32 : COLS_RAW <= 64 ? 64 : COLS_RAW <= 128 ? 128 : COLS_RAW <= 256 ? 256 : 512;
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;  // + alignment slack
-  static_assert(A_TILES % 2 == 0, "weight tiles are fetched in pairs");
+  static constexpr int W_BOX = A_TILES >= 2 ? 2 : 1;     // weight tiles per copy request (256 or 128 rows)
+  static_assert(A_TILES % W_BOX == 0, "weight tiles are fetched W_BOX at a time");
   static_assert(STAGES >= 2, "at least two stages");
   static_assert(COLS_RAW <= 512, "tensor memory");
 };
@@ -427,7 +428,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const int wtile = (tn * p.KS + ks) * C::A_TILES;  // first weight tile of the unit
         if (!(p.dbg & 2)) {
 #pragma unroll
-          for (int r = 0; r < C::A_TILES / 2; r++) tc_tma_2d(st + r * 2 * C::A_BYTES, &tmW, 0, (wtile + 2 * r) * 128, bar);
+          for (int r = 0; r < C::A_TILES / C::W_BOX; r++) tc_tma_2d(st + r * C::W_BOX * C::A_BYTES, &tmW, 0, (wtile + C::W_BOX * r) * 128, bar);
         }
         tc_bulk_g2s(st + C::A_TILES * C::A_BYTES + C::X_ROWS * 128, p.sfa + (size_t)wtile * 512, C::A_TILES * 512, bar);
       };
@@ -446,7 +447,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       auto prefetch_w = [&](int tn, int ks) {
         const int wtile = (tn * p.KS + ks) * C::A_TILES;
 #pragma unroll
-        for (int r = 0; r < C::A_TILES / 2; r++) tc_prefetch_2d(&tmW, 0, (wtile + 2 * r) * 128);
+        for (int r = 0; r < C::A_TILES / C::W_BOX; r++) tc_prefetch_2d(&tmW, 0, (wtile + C::W_BOX * r) * 128);
         tc_prefetch_bulk(p.sfa + (size_t)wtile * 512, C::A_TILES * 512);
       };
       // the first stages' weights go out before this grid is allowed to see the split kernel's output
@@ -965,7 +966,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       rc = r == CUDA_SUCCESS ? TPX_OK : TPX_ERR_CUDA;
     } else
-      rc = tc_make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, (uint64_t)pl.TN * pl.KS * (dual ? 2 : 1) * 128, 64, 256);
+      rc = tc_make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, (uint64_t)pl.TN * pl.KS * (dual ? 2 : 1) * 128, 64, (dual ? 2 : 1) * pl.uks >= 2 ? 256 : 128);
   }
   if (rc) return rc;
   rc = tc_make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, terms, (uint64_t)pl.Mpad * pl.KS * 2, 128, (uint32_t)pl.xbox);
