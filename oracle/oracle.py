@@ -389,14 +389,15 @@ def llama_layer(hs, mask, pos, W, cache, layer_idx, n_q, n_kv, head_dim, eps, ep
 
     hs [B,S,D] bf16 patterns; W: dict of dequantised plain fp32 weights q,k,v,o,gate,up,down and
     bf16 norm weights ln1, ln2. `allreduce` is called on the fp32 view of the row-parallel outputs
-    when world > 1 (the residual is pre-scaled by 1/world, :1206,1261,1273)."""
+    when world > 1 (the residual is pre-scaled by 1/world, :1206,1261,1273). Optional bf16 biases bq, bk, bv in W
+    give Qwen2DecoderLayer::_forward (:1440-1510), which differs only in them."""
     B, S, D = hs.shape
     scale = 1.0 / world
     res = hs.reshape(B * S, D)
     x = rmsnorm(res, W["ln1"], eps)
-    q = qlinear(x, W["q"]).reshape(B, S, n_q * head_dim)
-    k = qlinear(x, W["k"]).reshape(B, S, n_kv * head_dim)
-    v = qlinear(x, W["v"]).reshape(B, S, n_kv, head_dim)
+    q = qlinear(x, W["q"], bias=W.get("bq")).reshape(B, S, n_q * head_dim)
+    k = qlinear(x, W["k"], bias=W.get("bk")).reshape(B, S, n_kv * head_dim)
+    v = qlinear(x, W["v"], bias=W.get("bv")).reshape(B, S, n_kv, head_dim)
     q = rope_llama(q, ep, pos, n_q, head_dim)
     k = rope_llama(k, ep, pos, n_kv, head_dim).reshape(B, S, n_kv, head_dim)
     kc, vc = cache.update(k, v, layer_idx)

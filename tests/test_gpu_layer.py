@@ -154,6 +154,42 @@ def test_llama_layer_prefill_then_decode(cuda, kind):
         assert O.rel_err(got[:n], kc_ref[:n]) <= TOL
 
 
+def test_qwen2_layer_has_qkv_bias(cuda):
+    """Qwen2DecoderLayer = the Llama block plus q/k/v biases (src/csrc/llm/fused_llm_infer.cpp:1289-1510)."""
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    from tpp_pytorch_extension_b200._C._tpp_attn import TppCache
+    rng = np.random.default_rng(15)
+    D, Nq, Nkv, H, FF, B, MP = 256, 4, 2, 64, 512, 2, 64
+    eps = 1e-6
+    names = {"q": (Nq * H, D), "k": (Nkv * H, D), "v": (Nkv * H, D), "o": (D, Nq * H), "gate": (FF, D), "up": (FF, D), "down": (D, FF)}
+    qt, W = {}, {}
+    for nm, (n, k) in names.items():
+        qt[nm], W[nm], _ = make_qweight(rng, n, k, "mxfp4", cuda, std=0.05)
+    W["ln1"], W["ln2"] = O.f32_to_bf16(np.ones(D, np.float32)), O.f32_to_bf16(np.ones(D, np.float32))
+    for nm, n in (("bq", Nq * H), ("bk", Nkv * H), ("bv", Nkv * H)):
+        W[nm] = O.randn_bf16(rng, (n,), 0.5)
+    ep = O.rope_table(MP, H, 1e6)
+    layer = F.Qwen2DecoderLayer([to_dev_bf16(W["ln1"], cuda), qt["q"], qt["k"], qt["v"], qt["o"], to_dev_bf16(W["ln2"], cuda),
+                                 qt["gate"], qt["up"], qt["down"], to_dev_bf16(W["bq"], cuda), to_dev_bf16(W["bk"], cuda),
+                                 to_dev_bf16(W["bv"], cuda), torch.from_numpy(ep).to(cuda)], 0, eps, H, MP, H)
+    cache, ocache = TppCache(), O.KVCache()
+    total = 0
+    for S in (20, 1):
+        hs = O.randn_bf16(rng, (B, S, D))
+        pos = np.arange(total, total + S, dtype=np.int64)[None]
+        total += S
+        m01 = np.ones((B, total))
+        am = cache.align_and_invert_mask(torch.from_numpy(m01).to(cuda))
+        out = layer.forward([to_dev_bf16(hs, cuda), am, torch.from_numpy(pos).to(cuda)], cache, True)
+        ref = O.llama_layer(hs, O.align_and_invert_mask(m01), pos, W, ocache, 0, Nq, Nkv, H, eps, ep)
+        assert_no_kernel_error()
+        assert O.rel_err(to_host_bits(out[0]), ref) <= TOL, S
+    # the biases matter: without them the result is far off
+    W0 = {k: v for k, v in W.items() if k not in ("bq", "bk", "bv")}
+    no_bias = O.llama_layer(hs, O.align_and_invert_mask(m01), pos, W0, O.KVCache(), 0, Nq, Nkv, H, eps, ep)
+    assert O.rel_err(no_bias, ref) > TOL
+
+
 def test_reorder_cache_gathers_beams(cuda):
     """Beam-search reordering: sequence i continues the history of old sequence beam_idx[i]; a cache of CB sequences
     is first repeated per beam (src/csrc/llm/attn.h:327-403)."""

@@ -227,6 +227,7 @@ class LlamaDecoderLayer:
         self.Nq = Wq.out_features // self.H
         self.Nkv = Wk.out_features // self.H
         self.Wqkv = _cat_q([Wq, Wk, Wv])
+        self.Bqkv = None  # Qwen2DecoderLayer sets the fused q/k/v bias
         if self.EP.dtype != torch.float32 or tuple(self.EP.shape[:1]) != (2,):
             raise _lib.TpxError("embed_positions must be fp32 [2, max_positions, rotary_dim]")
         self.EP = self.EP.contiguous()
@@ -247,7 +248,7 @@ class LlamaDecoderLayer:
         scale = 1.0 / ws
         L = _lib.lib()
         res = hs.reshape(B * S, D)
-        qkv = fc_plain_norm(res, self.Gi, self.eps, self.Wqkv)
+        qkv = fc_plain_norm(res, self.Gi, self.eps, self.Wqkv, self.Bqkv)
         lc = cache.layer(self.layer_idx)
         if dev_len is None:
             lc.ensure(B, self.Nkv, self.H, S, hs.dtype, hs.device)
@@ -275,3 +276,19 @@ class LlamaDecoderLayer:
         if use_cache:
             return [out, lc.k, lc.v]
         return [out]
+
+
+class Qwen2DecoderLayer(LlamaDecoderLayer):
+    """torch.classes.tpp_llm.Qwen2DecoderLayer (src/csrc/llm/fused_llm_infer.cpp:1289-1510): the Llama block with
+    biases on the q, k and v projections. params: [input_ln_gamma, q, k, v, o, post_attention_ln_gamma, gate, up,
+    down, q_bias, k_bias, v_bias, embed_positions] (:1317-1333)."""
+
+    def __init__(self, params, layer_idx, eps, H, max_positions, rotary_dim):
+        if len(params) != 13:
+            raise _lib.TpxError("Qwen2DecoderLayer expects 13 parameters")
+        bq, bk, bv = params[9:12]
+        super().__init__(list(params[:9]) + [params[12]], layer_idx, eps, H, max_positions, rotary_dim)
+        for b, n in ((bq, self.Nq * self.H), (bk, self.Nkv * self.H), (bv, self.Nkv * self.H)):
+            if b.numel() != n:
+                raise _lib.TpxError("Qwen2DecoderLayer: bias length does not match its projection")
+        self.Bqkv = torch.cat([bq.reshape(-1), bk.reshape(-1), bv.reshape(-1)]).to(self.EP.device, torch.bfloat16).contiguous()

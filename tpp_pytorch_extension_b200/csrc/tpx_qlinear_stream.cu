@@ -259,6 +259,8 @@ __global__ void __launch_bounds__(kThreads) qlinear_stream(StreamParams p) {
   __shared__ float red[kWarps];
   __shared__ __align__(8) unsigned long long bars[kWarps][kStages];
 
+  pdl_trigger();
+  pdl_wait();  // x, the residual and the scratch belong to earlier grids until they have completed
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int ks = blockIdx.y;
@@ -527,9 +529,7 @@ static int launch_one(const StreamParams& p, const Plan& pl, cudaStream_t st) {
     TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_stream<KIND, NT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
     if (dev >= 0 && dev < 16) opted[dev] = true;
   }
-  count_launch();
-  qlinear_stream<KIND, NT, DUAL><<<dim3(pl.grid_x, pl.ksplit), kThreads, pl.smem, st>>>(p);
-  TPX_LAUNCH_OK();
+  TPX_CUDA_OK(launch_pdl(qlinear_stream<KIND, NT, DUAL>, dim3(pl.grid_x, pl.ksplit), dim3(kThreads), (size_t)pl.smem, st, p));
   return TPX_OK;
 }
 
