@@ -63,8 +63,13 @@ def make_layer(shape, weights, layer_idx, ep, weight_dtype, device):
         w = _shard(weights[name].to(device), dim, blk)
         qs[name] = quantize_weight(w, weight_dtype)
     params = [weights["ln1"].to(device, torch.bfloat16), qs["q"], qs["k"], qs["v"], qs["o"],
-              weights["ln2"].to(device, torch.bfloat16), qs["gate"], qs["up"], qs["down"], ep]
-    layer = fused_llm_cpp.LlamaDecoderLayer(params, layer_idx, shape.rms_norm_eps, H, ep.shape[1], H)
+              weights["ln2"].to(device, torch.bfloat16), qs["gate"], qs["up"], qs["down"]]
+    if "bq" in weights:  # Qwen2: biases of the column-parallel q/k/v projections are sharded like their rows
+        bs = [_shard(weights[n].to(device).reshape(-1, 1), 0, blk).reshape(-1).to(torch.bfloat16)
+              for n, blk in (("bq", grp), ("bk", H), ("bv", H))]
+        layer = fused_llm_cpp.Qwen2DecoderLayer(params + bs + [ep], layer_idx, shape.rms_norm_eps, H, ep.shape[1], H)
+    else:
+        layer = fused_llm_cpp.LlamaDecoderLayer(params + [ep], layer_idx, shape.rms_norm_eps, H, ep.shape[1], H)
     # the interchange tensors are no longer needed once the streaming layouts exist
     for w in (layer.Wqkv, layer.Wp, layer.Wd, layer.Wg, layer.Wu):
         w.codes = w.codes.new_empty(0)
@@ -224,13 +229,21 @@ def OptimizeModelForLlama(model, dtype=torch.bfloat16, device="cuda", weight_dty
     ep = rope_table(shape.max_position_embeddings, shape.head_dim, shape.rope_theta, dev)
     layers = []
     for i, l in enumerate(model.model.layers):
-        w = {"q": l.self_attn.q_proj.weight.data, "k": l.self_attn.k_proj.weight.data, "v": l.self_attn.v_proj.weight.data,
+        w = {}
+        if getattr(l.self_attn.q_proj, "bias", None) is not None:  # Qwen2 (fused_qwen2_infer.py of the reference)
+            w.update(bq=l.self_attn.q_proj.bias.data, bk=l.self_attn.k_proj.bias.data, bv=l.self_attn.v_proj.bias.data)
+        w.update({"q": l.self_attn.q_proj.weight.data, "k": l.self_attn.k_proj.weight.data, "v": l.self_attn.v_proj.weight.data,
              "o": l.self_attn.o_proj.weight.data, "gate": l.mlp.gate_proj.weight.data, "up": l.mlp.up_proj.weight.data,
-             "down": l.mlp.down_proj.weight.data, "ln1": l.input_layernorm.weight.data, "ln2": l.post_attention_layernorm.weight.data}
+             "down": l.mlp.down_proj.weight.data, "ln1": l.input_layernorm.weight.data, "ln2": l.post_attention_layernorm.weight.data})
         layers.append(make_layer(shape, w, i, ep, weight_dtype, dev))
     embed = model.model.embed_tokens.weight.data.to(dev, torch.bfloat16)
     lm = _lm_head_shard(model.lm_head.weight.data.to(dev, torch.bfloat16))
     return LlamaRunner(shape, embed, layers, model.model.norm.weight.data.to(dev, torch.bfloat16), lm, ep)
+
+
+def OptimizeModelForQwen2(model, dtype=torch.bfloat16, device="cuda", weight_dtype="mxfp4"):
+    """Reference entry point llm/fused_qwen2_infer.py:OptimizeModelForQwen2: the same runner, layers carry q/k/v biases."""
+    return OptimizeModelForLlama(model, dtype, device, weight_dtype)
 
 
 LLAMA2_7B = LlamaShape(32, 4096, 32, 32, 11008, 32000, rms_norm_eps=1e-5, rope_theta=1e4)
