@@ -424,7 +424,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       auto fetch_w = [&](int s, int tn, int ks) {  // weight tiles and their scale blocks: independent of the split kernel
         const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
         const uint32_t bar = tc_smem_u32(&bar_full[s]);
-        tc_mbar_expect_tx(bar, (p.dbg & 2) ? C::TX - C::A_TILES * C::A_TX : C::TX);
+        tc_mbar_expect_tx(bar, ((p.dbg & 2) ? C::TX - C::A_TILES * C::A_TX : C::TX) - ((p.dbg & 128) ? C::X_ROWS * 128 + UKS * C::SFB_PER * 512 : 0));
         const int wtile = (tn * p.KS + ks) * C::A_TILES;  // first weight tile of the unit
         if (!(p.dbg & 2)) {
 #pragma unroll
@@ -478,7 +478,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           }
           fetch_w(s, tn, ks);
         }
-        fetch_x(s, tm, ks);
+        if (!(p.dbg & 128)) fetch_x(s, tm, ks);
         if (++ks == p.KS) { ks = 0; tile++; }
       }
     }
