@@ -906,12 +906,19 @@ extern "C" int tpx_repack_mxfp4_tc(const uint8_t* codes, const uint8_t* scales, 
   return TPX_OK;
 }
 
-// With TPX_TC_WIDE=1 up to 64 tokens go to the kernel that puts the weights on the wide (N) side of the MMA. Both
-// kernels stream weights at about the same pace (shared-memory bandwidth: the unpacking copy writes 2 bytes per
-// packed byte and the MMA reads them back), so the default stays with the one kernel that serves every M.
-static bool tc_wide(int64_t M) {
+// Kernel choice for up to 64 tokens. The kernel with the weights on the wide (N) side of the MMA spends fewer
+// tensor-pipe cycles per weight byte (one 128x256x32 MMA per 4 KiB instead of two 128x32x32 per 2 KiB each) and wins
+// when every CTA owns whole tiles (the gate/up pair of a decode step: 29.3 against 31.3 us at M = 8, 34.2 against
+// 35.3 us at M = 64); shapes with few tiles are better served by
+// the cluster split-K of the other kernel. TPX_TC_WIDE=1 forces it for every M <= 64, TPX_TC_WIDE=0 disables it.
+static bool tc_wide(int64_t M, int64_t N, int64_t K, bool pair) {
+  if (M > 64) return false;
   const char* e = getenv("TPX_TC_WIDE");
-  return e && atoi(e) != 0 && M <= 64;
+  if (e) return atoi(e) != 0;
+  const long long T = pair ? (N + 127) / 128 : (N + 255) / 256;  // tiles of the wide kernel
+  const int sms = sm_count();
+  (void)K;
+  return (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
 }
 
 static size_t tc_scratch_need(int64_t M, int64_t N, int64_t K, bool pair, bool wide) {
@@ -920,7 +927,7 @@ static size_t tc_scratch_need(int64_t M, int64_t N, int64_t K, bool pair, bool w
 
 extern "C" size_t tpx_qlinear_mxfp4_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int pair) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  return tc_scratch_need(M, N, K, pair != 0, tc_wide(M));
+  return tc_scratch_need(M, N, K, pair != 0, tc_wide(M, N, K, pair != 0));
 }
 
 static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M, int64_t N, int64_t K,
@@ -998,7 +1005,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
 extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M, int64_t N,
                                     int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
                                     float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream) {
-  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, tc_wide(M));
+  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, tc_wide(M, N, K, pair != 0));
 }
 
 extern "C" int tpx_rmsnorm_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, const void* gamma,
@@ -1007,7 +1014,7 @@ extern "C" int tpx_rmsnorm_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sf
                                             size_t scratch_bytes, void* stream) {
   TPX_REQUIRE(gamma, TPX_ERR_ARG, "rmsnorm_qlinear_mxfp4_tc: null gamma");
   TcNorm nm = {gamma, gamma_is_f32, eps};
-  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, tc_wide(M), &nm);
+  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, tc_wide(M, N, K, pair != 0), &nm);
 }
 
 // ---------------------------------------------------------------- variant that allocates nothing
@@ -1043,7 +1050,7 @@ extern "C" int tpx_qlinear_mxfp4_tc_static(const uint8_t* wq, const uint8_t* sfa
   TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear_mxfp4_tc_static: bad shape");
   if (M == 0) return TPX_OK;
   // the kernel whose scratch fits the array: the wide one's partial slots grow with the token count
-  bool wide = tc_wide(M);
+  bool wide = tc_wide(M, N, K, pair != 0);
   if (wide && tc_scratch_need(M, N, K, pair != 0, true) > kStaticScratchBytes) wide = false;
   const size_t need = tc_scratch_need(M, N, K, pair != 0, wide);
   TPX_REQUIRE(need <= kStaticScratchBytes, TPX_ERR_SCRATCH,

@@ -6,7 +6,9 @@
 //   A (128 rows)  = the activation terms of up to 64 tokens (hi and lo E4M3 terms are separate rows),
 //   B (256 rows)  = 256 output features of packed E2M1 weights (a gate tile and its up tile, or two adjacent tiles),
 //   D             = [token term][feature] in tensor memory, 256 fp32 columns.
-// Every MMA then consumes 4 KiB of packed weights in the same time, and the weight stream is bounded by memory.
+// Every MMA then consumes 4 KiB of packed weights in about the time the other orientation needs for 2 KiB (a
+// 128-row MMA costs ~97 cycles however narrow it is, ~128 at N = 256). A pipeline stage holds two k steps (32 KiB
+// of packed weights) for up to 16 tokens, one k step otherwise.
 //
 // Replaces the same reference functions as tpx_qlinear_tc.cu (fc_plain / fc_gate_up of
 // src/csrc/llm/fused_llm_infer.cpp on MXFP4 weights) for M <= 64; layouts of the packed weights are shared.
@@ -17,24 +19,27 @@
 
 namespace tpx {
 
-template <int TOKP>
+template <int TOKP, int UKS>
 struct TcwCfg {
-  static constexpr int X_BYTES = 2 * TOKP * 128;        // both terms of one k step (128 k values of TOKP tokens)
-  static constexpr int B_BYTES = 256 * 128;             // 256 features x 128 k values, unpacked to 16-byte-aligned groups
-  static constexpr int B_TX = 256 * 64;                 // what the copy accounts for (packed bytes)
-  static constexpr int SF_BYTES = 512 + 2 * 512;        // activation scale block, two weight scale blocks
+  static constexpr int X1 = 2 * TOKP * 128;             // both terms of one k step (128 k values of TOKP tokens)
+  static constexpr int B1 = 256 * 128;                  // 256 features x 128 k values, unpacked to 16-byte-aligned groups
+  static constexpr int X_BYTES = UKS * X1;              // a stage holds UKS k steps
+  static constexpr int B_BYTES = UKS * B1;
+  static constexpr int B_TX = 256 * 64;                 // what the copy of one k step accounts for (packed bytes)
+  static constexpr int SF_BYTES = UKS * (512 + 2 * 512);  // per k step: activation scale block, two weight scale blocks
   static constexpr int RAW = X_BYTES + B_BYTES + SF_BYTES;
   static constexpr int STAGE_BYTES = (RAW + 1023) / 1024 * 1024;
   static constexpr int BUDGET = 227 * 1024 - 2048;
   static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
-  static constexpr int SF_COLS = 12;                    // 4 (activations) + 8 (weights) columns per stage
+  static constexpr int SF_COLS = 12 * UKS;              // per k step 4 (activations) + 8 (weights) columns
   static constexpr int D_COLS = 256;
   static constexpr int TMEM_COLS = 512;
   static constexpr int EPI_WARPS = TOKP / 16;           // 32-lane quarters of tensor memory that hold tokens
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
   static_assert(D_COLS + STAGES * SF_COLS <= 512, "tensor memory");
-  static_assert(X_BYTES + B_BYTES >= 128 * 128, "the A descriptor spans 128 rows inside the stage");
+  static_assert((UKS - 1) * X1 + 128 * 128 <= X_BYTES + B_BYTES, "the A descriptor spans 128 rows inside the stage");
+  static_assert(UKS * 2 * TOKP <= 256, "one copy request for the activation rows of a stage");
 };
 
 // Eight consecutive output features of one token: bias, activation, gate multiply, residual, one 16-byte store.
@@ -99,12 +104,13 @@ __device__ __forceinline__ void tcw_finish8(const TcParams& p, int tok, int n, c
   *reinterpret_cast<uint4*>(p.y + o) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// p.TN counts the 256-feature tiles here (a gate/up pair: 128 + 128), p.TM is 1, p.KS the k steps of 128.
-template <int TOKP, bool DUAL>
+// p.TN counts the 256-feature tiles here (a gate/up pair: 128 + 128), p.TM is 1, p.KS the k units (UKS k steps of
+// 128 each) per tile, ksteps the k steps of a tile in the packed weight.
+template <int TOKP, bool DUAL, int UKS>
 __global__ void __launch_bounds__(kTcThreads, 1)
 qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, TcParams p, const uint8_t* wq,
-                   int tiles128) {
-  using C = TcwCfg<TOKP>;
+                   int tiles128, int ksteps) {
+  using C = TcwCfg<TOKP, UKS>;
   extern __shared__ unsigned char tcw_smem_raw[];
   __shared__ __align__(8) unsigned long long bar_full[C::STAGES], bar_empty[C::STAGES];
   __shared__ __align__(8) unsigned long long bar_acc_full, bar_acc_empty;
@@ -147,8 +153,8 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
   // weight tiles (of 128 features) of feature tile t at k step ks: a pair is stored as [t][ks][gate, up], single
   // weights as [tile128][ks], so the two halves of a 256-feature tile are p.KS tiles apart
-  auto wtile_a = [&](int t, int ks) { return DUAL ? (t * p.KS + ks) * 2 : (2 * t * p.KS + ks); };
-  auto wtile_b = [&](int t, int ks) { return DUAL ? (t * p.KS + ks) * 2 + 1 : ((2 * t + 1) * p.KS + ks); };
+  auto wtile_a = [&](int t, int kstep) { return DUAL ? (t * ksteps + kstep) * 2 : (2 * t * ksteps + kstep); };
+  auto wtile_b = [&](int t, int kstep) { return DUAL ? (t * ksteps + kstep) * 2 + 1 : ((2 * t + 1) * ksteps + kstep); };
   auto has_b = [&](int t) { return DUAL || 2 * t + 1 < tiles128; };
 
   if (warp == 0) {
@@ -157,36 +163,39 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       auto fetch_w = [&](int s, int t, int ks) {
         const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
         const uint32_t bar = tc_smem_u32(&bar_full[s]);
-        const uint32_t sb = st + C::X_BYTES, ssf = sb + C::B_BYTES + 512;
+        const uint32_t sb = st + C::X_BYTES, ssf = sb + C::B_BYTES + UKS * 512;
         const bool second = has_b(t);
-        tc_mbar_expect_tx(bar, C::X_BYTES + 512 + (second ? C::B_TX + 1024 : C::B_TX / 2 + 512));
-        const int ta = wtile_a(t, ks), tb = wtile_b(t, ks);
-        if (DUAL) {
-          tc_tma_2d(sb, &tmW, 0, ta * 128, bar);  // 256 rows: gate tile and up tile are adjacent
-          tc_bulk_g2s(ssf, p.sfa + (size_t)ta * 512, 1024, bar);
-        } else {
-          tc_tma_2d(sb, &tmW, 0, ta * 128, bar);
-          tc_bulk_g2s(ssf, p.sfa + (size_t)ta * 512, 512, bar);
-          if (second) {
-            tc_tma_2d(sb + C::B_BYTES / 2, &tmW, 0, tb * 128, bar);
-            tc_bulk_g2s(ssf + 512, p.sfa + (size_t)tb * 512, 512, bar);
+        tc_mbar_expect_tx(bar, C::X_BYTES + UKS * 512 + UKS * (second ? C::B_TX + 1024 : C::B_TX / 2 + 512));
+#pragma unroll
+        for (int kk = 0; kk < UKS; kk++) {
+          const int ta = wtile_a(t, ks * UKS + kk), tb = wtile_b(t, ks * UKS + kk);
+          if (DUAL) {
+            tc_tma_2d(sb + kk * C::B1, &tmW, 0, ta * 128, bar);  // 256 rows: gate tile and up tile are adjacent
+            tc_bulk_g2s(ssf + kk * 1024, p.sfa + (size_t)ta * 512, 1024, bar);
+          } else {
+            tc_tma_2d(sb + kk * C::B1, &tmW, 0, ta * 128, bar);
+            tc_bulk_g2s(ssf + kk * 1024, p.sfa + (size_t)ta * 512, 512, bar);
+            if (second) {
+              tc_tma_2d(sb + kk * C::B1 + C::B1 / 2, &tmW, 0, tb * 128, bar);
+              tc_bulk_g2s(ssf + kk * 1024 + 512, p.sfa + (size_t)tb * 512, 512, bar);
+            }
           }
         }
       };
       auto fetch_x = [&](int s, int ks) {
         const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
         const uint32_t bar = tc_smem_u32(&bar_full[s]);
-        tc_tma_2d(st, &tmX, 0, ks * 2 * TOKP, bar);
-        tc_bulk_g2s(st + C::X_BYTES + C::B_BYTES, p.sfb + (size_t)ks * 512, 512, bar);
+        tc_tma_2d(st, &tmX, 0, ks * UKS * 2 * TOKP, bar);
+        tc_bulk_g2s(st + C::X_BYTES + C::B_BYTES, p.sfb + (size_t)ks * UKS * 512, UKS * 512, bar);
       };
-      // Packed weights further ahead than the stages reach are prefetched into L2 with one request per 8 KiB or
-      // 16 KiB run, so that the bytes in flight from HBM are not limited by shared memory.
+      // Packed weights further ahead than the stages reach are prefetched into L2, so that the bytes in flight from
+      // HBM are not limited by shared memory.
       auto prefetch_w = [&](int t, int ks) {
         if (DUAL) {
-          tc_prefetch_bulk(wq + (size_t)wtile_a(t, ks) * 8192, 16384);
+          tc_prefetch_bulk(wq + (size_t)wtile_a(t, ks * UKS) * 8192, UKS * 16384);  // the k steps of a pair tile are adjacent
         } else {
-          tc_prefetch_bulk(wq + (size_t)wtile_a(t, ks) * 8192, 8192);
-          if (has_b(t)) tc_prefetch_bulk(wq + (size_t)wtile_b(t, ks) * 8192, 8192);
+          tc_prefetch_bulk(wq + (size_t)wtile_a(t, ks * UKS) * 8192, UKS * 8192);
+          if (has_b(t)) tc_prefetch_bulk(wq + (size_t)wtile_b(t, ks * UKS) * 8192, UKS * 8192);
         }
       };
       const int early = nunits < C::STAGES ? nunits : C::STAGES;
@@ -244,17 +253,22 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const uint32_t ssf = sb + C::B_BYTES;
         const uint32_t sf_t = tmem + C::D_COLS + (uint32_t)s * C::SF_COLS;
         const bool part_end = (ks == p.KS - 1) || (it == nunits - 1);
-        if (!(p.dbg & 16)) {
 #pragma unroll
-          for (int q = 0; q < 3; q++) tc_cp_sf(sf_t + q * 4, tc_sf_desc(ssf + q * 512));
-        }
+        for (int kk = 0; kk < UKS; kk++) {
+          // shared memory: [activation blocks of the UKS k steps][weight blocks, two per k step]; tensor memory: per k
+          // step 4 activation columns, then 8 weight columns
+          const uint32_t sfk = sf_t + kk * 12;
+          tc_cp_sf(sfk, tc_sf_desc(ssf + kk * 512));
+          tc_cp_sf(sfk + 4, tc_sf_desc(ssf + UKS * 512 + kk * 1024));
+          tc_cp_sf(sfk + 8, tc_sf_desc(ssf + UKS * 512 + kk * 1024 + 512));
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-          if (p.dbg & 32) break;
-          const uint32_t idesc = idesc0 | ((uint32_t)j << 29) | ((uint32_t)j << 4);
-          const uint64_t adesc = tc_smem_desc(st) + (uint64_t)(2 * j);   // rows past 2*TOKP read the weight area: unused lanes
-          const uint64_t bdesc = tc_smem_desc(sb) + (uint64_t)(2 * j);
-          tc_mma(tmem, adesc, bdesc, idesc, sf_t | ((uint32_t)j << 30), (sf_t + 4) | ((uint32_t)j << 30), (fresh && j == 0) ? 0u : 1u);
+          for (int j = 0; j < 4; j++) {
+            const uint32_t idesc = idesc0 | ((uint32_t)j << 29) | ((uint32_t)j << 4);
+            const uint64_t adesc = tc_smem_desc(st + kk * C::X1) + (uint64_t)(2 * j);  // rows past 2*TOKP: unused lanes
+            const uint64_t bdesc = tc_smem_desc(sb + kk * C::B1) + (uint64_t)(2 * j);
+            tc_mma(tmem, adesc, bdesc, idesc, sfk | ((uint32_t)j << 30), (sfk + 4) | ((uint32_t)j << 30),
+                   (fresh && kk == 0 && j == 0) ? 0u : 1u);
+          }
         }
         tc_commit(tc_smem_u32(&bar_empty[s]));
         if (part_end) tc_commit(tc_smem_u32(&bar_acc_full));
@@ -287,34 +301,44 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const bool whole = (part_first_ks == 0) && (ks == p.KS - 1);
         float* myslot = p.partial + (((size_t)blockIdx.x * 2 + (tile == tile0 ? 0 : 1)) * TOKP + tok) * 256;
         constexpr int CHUNKS = DUAL ? 8 : 16;
-#pragma unroll 2
-        for (int c = 0; c < CHUNKS; c++) {
-          uint32_t a[16], b[16];
-          tc_ld_x16(tmem + lane_base + c * 16, a);
-          if (DUAL) tc_ld_x16(tmem + lane_base + 128 + c * 16, b);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          float v[8], u[8];
+#pragma unroll 1
+        for (int c0 = 0; c0 < CHUNKS; c0 += 4) {  // four 16-column chunks per round trip to tensor memory
+          uint32_t a[4][16], b[4][16];
 #pragma unroll
-          for (int i = 0; i < 16; i++) {
-            const float sa = __uint_as_float(a[i]) + __shfl_xor_sync(0xffffffffu, __uint_as_float(a[i]), 16);
-            if ((i >> 3) == 0) { if (!half) v[i & 7] = sa; } else { if (half) v[i & 7] = sa; }
-            if (DUAL) {
-              const float sb2 = __uint_as_float(b[i]) + __shfl_xor_sync(0xffffffffu, __uint_as_float(b[i]), 16);
-              if ((i >> 3) == 0) { if (!half) u[i & 7] = sb2; } else { if (half) u[i & 7] = sb2; }
-            } else {
-              u[i & 7] = 0.0f;
-            }
+          for (int q = 0; q < 4; q++) {
+            tc_ld_x16(tmem + lane_base + (c0 + q) * 16, a[q]);
+            if (DUAL) tc_ld_x16(tmem + lane_base + 128 + (c0 + q) * 16, b[q]);
           }
-          const int col = c * 16 + half * 8;  // first of this thread's 8 accumulator columns
-          if (whole) {
-            const int n = DUAL ? tile * 128 + col : tile * 256 + col;
-            if (tok < p.M && n < p.N) tcw_finish8<DUAL>(p, tok, n, v, u);
-          } else {
-            __stcg(reinterpret_cast<float4*>(myslot + col), make_float4(v[0], v[1], v[2], v[3]));
-            __stcg(reinterpret_cast<float4*>(myslot + col) + 1, make_float4(v[4], v[5], v[6], v[7]));
-            if (DUAL) {
-              __stcg(reinterpret_cast<float4*>(myslot + 128 + col), make_float4(u[0], u[1], u[2], u[3]));
-              __stcg(reinterpret_cast<float4*>(myslot + 128 + col) + 1, make_float4(u[4], u[5], u[6], u[7]));
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            // lanes l and l ^ 16 hold the hi and lo sums of one token: each keeps 8 of the 16 columns and gets the
+            // other term of those from its partner
+            float v[8], u[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+              const float mine = __uint_as_float(half ? a[q][i + 8] : a[q][i]);
+              const float send = __uint_as_float(half ? a[q][i] : a[q][i + 8]);
+              v[i] = mine + __shfl_xor_sync(0xffffffffu, send, 16);
+              if (DUAL) {
+                const float mine2 = __uint_as_float(half ? b[q][i + 8] : b[q][i]);
+                const float send2 = __uint_as_float(half ? b[q][i] : b[q][i + 8]);
+                u[i] = mine2 + __shfl_xor_sync(0xffffffffu, send2, 16);
+              } else {
+                u[i] = 0.0f;
+              }
+            }
+            const int col = (c0 + q) * 16 + half * 8;  // first of this thread's 8 accumulator columns
+            if (whole) {
+              const int n = DUAL ? tile * 128 + col : tile * 256 + col;
+              if (tok < p.M && n < p.N) tcw_finish8<DUAL>(p, tok, n, v, u);
+            } else {
+              __stcg(reinterpret_cast<float4*>(myslot + col), make_float4(v[0], v[1], v[2], v[3]));
+              __stcg(reinterpret_cast<float4*>(myslot + col) + 1, make_float4(v[4], v[5], v[6], v[7]));
+              if (DUAL) {
+                __stcg(reinterpret_cast<float4*>(myslot + 128 + col), make_float4(u[0], u[1], u[2], u[3]));
+                __stcg(reinterpret_cast<float4*>(myslot + 128 + col) + 1, make_float4(u[4], u[5], u[6], u[7]));
+              }
             }
           }
         }
@@ -393,7 +417,7 @@ __global__ void __launch_bounds__(128) tcw_fixup_kernel(TcParams p, int TOKP, in
 
 // ---------------------------------------------------------------- host side
 struct TcwPlan {
-  int tokp, KS, tiles128, TN, grid, whole;
+  int tokp, uks, KS, KU, tiles128, TN, grid, whole;  // KS k steps, KU = KS / uks pipeline units per tile
   size_t off_terms, off_sfb, off_partial, total;
 };
 
@@ -401,9 +425,11 @@ static TcwPlan tcw_plan(int64_t M, int64_t N, int64_t K, bool pair) {
   TcwPlan pl;
   pl.tokp = M <= 16 ? 16 : M <= 32 ? 32 : 64;
   pl.KS = tc_padded_ks(K, pair);
+  pl.uks = pl.tokp == 16 ? 2 : 1;  // two k steps per stage while three such stages fit in shared memory
+  pl.KU = pl.KS / pl.uks;
   pl.tiles128 = (int)((N + 127) / 128);
   pl.TN = pair ? pl.tiles128 : (pl.tiles128 + 1) / 2;
-  const long long U = (long long)pl.TN * pl.KS, T = pl.TN;
+  const long long U = (long long)pl.TN * pl.KU, T = pl.TN;
   const int sms = sm_count();
   // whole tiles when their count suits the SM count (no fix-up pass), else the (tile, k step) units are cut evenly
   pl.whole = (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
@@ -420,15 +446,15 @@ static TcwPlan tcw_plan(int64_t M, int64_t N, int64_t K, bool pair) {
 
 size_t tcw_scratch_bytes(int64_t M, int64_t N, int64_t K, bool pair) { return tcw_plan(M, N, K, pair).total; }
 
-template <int TOKP, bool DUAL>
-static int tcw_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams& p, const uint8_t* wq, int tiles128, int grid,
-                      cudaStream_t st) {
-  using C = TcwCfg<TOKP>;
+template <int TOKP, bool DUAL, int UKS>
+static int tcw_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams& p, const uint8_t* wq, int tiles128, int ksteps,
+                      int grid, cudaStream_t st) {
+  using C = TcwCfg<TOKP, UKS>;
   static bool opted[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 16 || !opted[dev]) {
-    TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_tcw_kernel<TOKP, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+    TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_tcw_kernel<TOKP, DUAL, UKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     if (dev >= 0 && dev < 16) opted[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -442,7 +468,7 @@ static int tcw_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   count_launch();
-  TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tcw_kernel<TOKP, DUAL>, w, x, p, wq, tiles128));
+  TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tcw_kernel<TOKP, DUAL, UKS>, w, x, p, wq, tiles128, ksteps));
   if (!p.whole_tiles && grid > 1) {
     constexpr int GROUPS = DUAL ? 16 : 32;
     cudaLaunchConfig_t c2 = {};
@@ -472,25 +498,25 @@ int tcw_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x,
   const uint64_t wrows = (uint64_t)(pair ? pl.TN * 2 : pl.tiles128) * pl.KS * 128;
   rc = tc_make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, wrows, 64, pair ? 256 : 128);
   if (rc) return rc;
-  rc = tc_make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, terms, (uint64_t)pl.KS * 2 * pl.tokp, 128, (uint32_t)(2 * pl.tokp));
+  rc = tc_make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, terms, (uint64_t)pl.KS * 2 * pl.tokp, 128, (uint32_t)(pl.uks * 2 * pl.tokp));
   if (rc) return rc;
   TcParams p = base;
   p.sfa = sfa; p.sfa2 = nullptr; p.sfb = sfb;
   p.partial = reinterpret_cast<float*>(sc + pl.off_partial);
   p.counters = reinterpret_cast<unsigned*>(sc);
   p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
-  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KS; p.TN = pl.TN; p.TM = 1; p.whole_tiles = pl.whole;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = 1; p.whole_tiles = pl.whole;
   if (pair) {
     switch (pl.tokp) {
-      case 16: return tcw_launch<16, true>(mw, mx, p, wq, pl.tiles128, pl.grid, st);
-      case 32: return tcw_launch<32, true>(mw, mx, p, wq, pl.tiles128, pl.grid, st);
-      default: return tcw_launch<64, true>(mw, mx, p, wq, pl.tiles128, pl.grid, st);
+      case 16: return tcw_launch<16, true, 2>(mw, mx, p, wq, pl.tiles128, pl.KS, pl.grid, st);
+      case 32: return tcw_launch<32, true, 1>(mw, mx, p, wq, pl.tiles128, pl.KS, pl.grid, st);
+      default: return tcw_launch<64, true, 1>(mw, mx, p, wq, pl.tiles128, pl.KS, pl.grid, st);
     }
   }
   switch (pl.tokp) {
-    case 16: return tcw_launch<16, false>(mw, mx, p, wq, pl.tiles128, pl.grid, st);
-    case 32: return tcw_launch<32, false>(mw, mx, p, wq, pl.tiles128, pl.grid, st);
-    default: return tcw_launch<64, false>(mw, mx, p, wq, pl.tiles128, pl.grid, st);
+    case 16: return tcw_launch<16, false, 2>(mw, mx, p, wq, pl.tiles128, pl.KS, pl.grid, st);
+    case 32: return tcw_launch<32, false, 1>(mw, mx, p, wq, pl.tiles128, pl.KS, pl.grid, st);
+    default: return tcw_launch<64, false, 1>(mw, mx, p, wq, pl.tiles128, pl.KS, pl.grid, st);
   }
 }
 
