@@ -41,6 +41,9 @@ namespace tpx {
 //   sfb   [TM][KU][UKS][ceil(2*TOK/128)][512]   scale blocks over the 2*TOK MMA columns (hi columns, then lo
 //         columns with the same scales): byte (c%32)*16 + ((c%128)/32)*4 + j of block c/128 for column c
 // Padding rows and padding columns get zeros with scale 2^0.
+// rowmap 2 (16 tokens on the M side, four per 32-lane quarter of tensor memory so that four warps share the
+// epilogue): 32 rows per k step in memory, token r at row 8*(r/4) + r%4 (hi) and 4 further (lo); the MMA reads them
+// through a descriptor whose 8-row groups are 256 bytes apart, as its rows 32*(r/4) + r%4 and 16 further.
 // rowmap 1 (tokens on the M side of the MMA, one token tile): a k step holds 2*TOK rows with the hi row of token r
 // at 32*(r/16) + r%16 and its lo row 16 further, so that both terms of a token sit in the same 32-lane quarter of
 // tensor memory; one scale block of 128 rows per k step.
@@ -101,8 +104,18 @@ __global__ void split_activations_kernel(const uint16_t* __restrict__ x, int M, 
   const int tm = tok / TOK, r = tok % TOK, ks = kb / 4, j = kb % 4;
   const int KU = KS / UKS, ku = ks / UKS, kk = ks % UKS;
   const size_t step = ((size_t)tm * KU + ku) * UKS + kk;  // k step in fetch order
-  if (rowmap == 1) {
-    const int rh = 32 * (r / 16) + (r % 16), rl = rh + 16;
+  if (rowmap >= 1) {
+    // rows in memory (rh, rl) and rows as the MMA numbers them (gh, gl: the scale bytes are indexed by those)
+    int rh, rl, gh, gl;
+    if (rowmap == 1) {
+      rh = gh = 32 * (r / 16) + (r % 16);
+      rl = gl = rh + 16;
+    } else {
+      rh = 8 * (r / 4) + (r % 4);
+      rl = rh + 4;
+      gh = 32 * (r / 4) + (r % 4);
+      gl = gh + 16;
+    }
     uint4* dh = reinterpret_cast<uint4*>(terms + (step * 2 * TOK + rh) * 128 + j * 32);
     uint4* dl = reinterpret_cast<uint4*>(terms + (step * 2 * TOK + rl) * 128 + j * 32);
     dh[0] = make_uint4(ph[0], ph[1], ph[2], ph[3]);
@@ -110,8 +123,8 @@ __global__ void split_activations_kernel(const uint16_t* __restrict__ x, int M, 
     dl[0] = make_uint4(pl[0], pl[1], pl[2], pl[3]);
     dl[1] = make_uint4(pl[4], pl[5], pl[6], pl[7]);
     uint8_t* blk = sfb + step * 512;
-    blk[(rh % 32) * 16 + (rh / 32) * 4 + j] = (uint8_t)(e + 127);
-    blk[(rl % 32) * 16 + (rl / 32) * 4 + j] = (uint8_t)(e + 127);
+    blk[(gh % 32) * 16 + (gh / 32) * 4 + j] = (uint8_t)(e + 127);
+    blk[(gl % 32) * 16 + (gl / 32) * 4 + j] = (uint8_t)(e + 127);
     return;
   }
   uint4* dh = reinterpret_cast<uint4*>(terms + ((step * 2 + 0) * TOK + r) * 128 + j * 32);
@@ -229,23 +242,29 @@ __global__ void __launch_bounds__(kNsThreads) rmsnorm_split_kernel(const uint16_
     if (!in) continue;
     const int kb = i >> 2, part = i & 3, ks = kb >> 2, j = kb & 3;
     const size_t step = ((size_t)tm * KU + ks / UKS) * UKS + ks % UKS;
-    int rh, rl;  // rows of the hi and lo term inside the k step, and the scale block they belong to
+    int rh, rl, gh, gl;  // rows of the hi and lo term in memory, and as the MMA numbers them (scale bytes)
     size_t blk_off;
     if (rowmap == 1) {
-      rh = 32 * (r / 16) + (r % 16);
-      rl = rh + 16;
+      rh = gh = 32 * (r / 16) + (r % 16);
+      rl = gl = rh + 16;
+      blk_off = step * 512;
+    } else if (rowmap == 2) {
+      rh = 8 * (r / 4) + (r % 4);
+      rl = rh + 4;
+      gh = 32 * (r / 4) + (r % 4);
+      gl = gh + 16;
       blk_off = step * 512;
     } else {
-      rh = r;
-      rl = TOK + r;
+      rh = gh = r;
+      rl = gl = TOK + r;
       blk_off = step * (size_t)((2 * TOK + 127) / 128) * 512;
     }
     *reinterpret_cast<uint2*>(terms + (step * 2 * TOK + rh) * 128 + j * 32 + part * 8) = make_uint2(ph[0], ph[1]);
     *reinterpret_cast<uint2*>(terms + (step * 2 * TOK + rl) * 128 + j * 32 + part * 8) = make_uint2(pl[0], pl[1]);
     if (part == 0) {
       uint8_t* blk = sfb + blk_off;
-      blk[(rh / 128) * 512 + (rh % 32) * 16 + ((rh % 128) / 32) * 4 + j] = (uint8_t)(e + 127);
-      blk[(rl / 128) * 512 + (rl % 32) * 16 + ((rl % 128) / 32) * 4 + j] = (uint8_t)(e + 127);
+      blk[(gh / 128) * 512 + (gh % 32) * 16 + ((gh % 128) / 32) * 4 + j] = (uint8_t)(e + 127);
+      blk[(gl / 128) * 512 + (gl % 32) * 16 + ((gl % 128) / 32) * 4 + j] = (uint8_t)(e + 127);
     }
   }
 }

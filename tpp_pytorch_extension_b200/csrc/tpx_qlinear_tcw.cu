@@ -35,7 +35,8 @@ struct TcwCfg {
   static constexpr int SF_COLS = 12 * UKS;              // per k step 4 (activations) + 8 (weights) columns
   static constexpr int D_COLS = 256;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int EPI_WARPS = TOKP / 16;           // 32-lane quarters of tensor memory that hold tokens
+  static constexpr int EPI_WARPS = TOKP == 16 ? 4 : TOKP / 16;  // 32-lane quarters of tensor memory that hold tokens
+  static constexpr int TOK_PER_WARP = TOKP == 16 ? 4 : 16;       // 16 tokens are spread four per quarter (row map 2)
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
   static_assert(D_COLS + STAGES * SF_COLS <= 512, "tensor memory");
   static_assert((UKS - 1) * X1 + 128 * 128 <= X_BYTES + B_BYTES, "the A descriptor spans 128 rows inside the stage");
@@ -264,7 +265,9 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 4; j++) {
             const uint32_t idesc = idesc0 | ((uint32_t)j << 29) | ((uint32_t)j << 4);
-            const uint64_t adesc = tc_smem_desc(st + kk * C::X1) + (uint64_t)(2 * j);  // rows past 2*TOKP: unused lanes
+            // rows past the stored ones alias other rows or the weight area: unused lanes. 16 tokens: 8-row groups 256
+            // bytes apart, so that MMA rows 32q + 16*term + t read the stored row 8q + 4*term + t
+            const uint64_t adesc = (TOKP == 16 ? tc_smem_desc_sbo(st + kk * C::X1, 256) : tc_smem_desc(st + kk * C::X1)) + (uint64_t)(2 * j);
             const uint64_t bdesc = tc_smem_desc(sb + kk * C::B1) + (uint64_t)(2 * j);
             tc_mma(tmem, adesc, bdesc, idesc, sfk | ((uint32_t)j << 30), (sfk + 4) | ((uint32_t)j << 30),
                    (fresh && kk == 0 && j == 0) ? 0u : 1u);
@@ -282,7 +285,8 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     // tokens 16*sub .. 16*sub+15: hi terms in lanes 0-15, lo terms in lanes 16-31
     const int sub = warp & 3;
     const uint32_t lane_base = ((uint32_t)(sub * 32)) << 16;
-    const int tok = sub * 16 + (lane & 15);
+    const int tok = sub * C::TOK_PER_WARP + (lane & 15);
+    const bool lane_live = (lane & 15) < C::TOK_PER_WARP;  // lanes beyond hold rows that alias others
     const int half = lane >> 4;  // after the hi+lo sum both halves hold the same values: each finishes 8 of 16 features
     int tile = tile0, ks = ks0;
     int part_first_ks = ks0;
@@ -331,8 +335,8 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             const int col = (c0 + q) * 16 + half * 8;  // first of this thread's 8 accumulator columns
             if (whole) {
               const int n = DUAL ? tile * 128 + col : tile * 256 + col;
-              if (tok < p.M && n < p.N) tcw_finish8<DUAL>(p, tok, n, v, u);
-            } else {
+              if (lane_live && tok < p.M && n < p.N) tcw_finish8<DUAL>(p, tok, n, v, u);
+            } else if (lane_live) {
               __stcg(reinterpret_cast<float4*>(myslot + col), make_float4(v[0], v[1], v[2], v[3]));
               __stcg(reinterpret_cast<float4*>(myslot + col) + 1, make_float4(v[4], v[5], v[6], v[7]));
               if (DUAL) {
@@ -492,7 +496,7 @@ int tcw_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x,
               "qlinear_mxfp4_tc: y, bias, mul_in and res must be 16-byte aligned");
   unsigned char* sc = reinterpret_cast<unsigned char*>(scratch);
   uint8_t *terms = sc + pl.off_terms, *sfb = sc + pl.off_sfb;
-  int rc = tc_launch_split(x, (int)M, (int)K, pl.tokp, pl.KS, pl.tokp, 1, 1, terms, sfb, st, norm);
+  int rc = tc_launch_split(x, (int)M, (int)K, pl.tokp, pl.KS, pl.tokp, 1, pl.tokp == 16 ? 2 : 1, terms, sfb, st, norm);
   if (rc) return rc;
   CUtensorMap mw, mx;
   const uint64_t wrows = (uint64_t)(pair ? pl.TN * 2 : pl.tiles128) * pl.KS * 128;

@@ -149,6 +149,13 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// The same tile read with its 8-row groups `sbo` bytes apart instead of 1024: consecutive groups then overlap in
+// memory (group g starts at row g * sbo / 128). Swizzling acts on address bits, so rows written by a plain swizzled
+// copy are read back consistently.
+__device__ __forceinline__ uint64_t tc_smem_desc_sbo(uint32_t saddr, uint32_t sbo) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
 // host helpers shared by the tensor-core linears
 int tc_make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows);
 int tc_padded_ks(int64_t K, bool pair);
