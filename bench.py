@@ -31,7 +31,7 @@ SWEEP = [1, 8, 64, 512, 4096]
 DECODE_MAX_M = 64
 # dram__bytes_read.sum + dram__bytes_write.sum of one qlinear_tc_kernel gate/up launch, from the ncu captures
 # summarised under profiles/ (bytes); None where no capture exists
-NCU_TRAFFIC = {1: 63.06e6, 8: 63.06e6, 64: 63.60e6}  # M=1 runs the M=8 kernel instantiation on the same weight bytes
+NCU_TRAFFIC = {1: 63.02e6, 8: 63.02e6, 64: 63.32e6}  # M=1 runs the M=8 kernel instantiation on the same weight bytes
 N_COPIES = 6  # distinct packed weight sets: 6 x 93.6 MB = 561 MB >> 126 MB of L2
 
 
