@@ -489,9 +489,9 @@ using namespace tpx;
 
 extern "C" int tpx_rmsnorm(const uint16_t* x, const void* gamma, int gamma_is_f32, float eps, int64_t rows, int64_t D,
                            uint16_t* y, void* stream) {
-  TPX_REQUIRE(x && gamma && y, TPX_ERR_ARG, "rmsnorm: null pointer");
   TPX_REQUIRE(rows >= 0 && D > 0 && D % 8 == 0, TPX_ERR_ARG, "rmsnorm: D must be a positive multiple of 8 (D=%ld)", (long)D);
-  if (rows == 0) return TPX_OK;
+  if (rows == 0) return TPX_OK;  // an empty tensor has no storage: nothing to check, nothing to do
+  TPX_REQUIRE(x && gamma && y, TPX_ERR_ARG, "rmsnorm: null pointer");
   const bool aligned = (((uintptr_t)x | (uintptr_t)y | (uintptr_t)gamma) & 15) == 0;
   if (rows <= 2048 && D <= kNormThreads * kNormVecs * 8 && aligned)
     TPX_CUDA_OK(launch_pdl(rmsnorm_row_kernel, dim3((unsigned)rows), dim3(kNormThreads), 0, (cudaStream_t)stream, x, gamma, gamma_is_f32,
@@ -505,6 +505,7 @@ extern "C" int tpx_rmsnorm(const uint16_t* x, const void* gamma, int gamma_is_f3
 extern "C" int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const int64_t* pos, int64_t B, int64_t S, int64_t Nq,
                                   int64_t Nkv, int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset,
                                   int64_t capacity, const int32_t* dev_len, uint16_t* q_out, uint16_t* kc, uint16_t* vc, void* stream) {
+  if (S == 0 && B > 0) return TPX_OK;  // nothing to rotate or append
   TPX_REQUIRE(qkv && ep && pos && q_out && kc && vc, TPX_ERR_ARG, "rope_kv_update: null pointer");
   TPX_REQUIRE(B > 0 && S >= 0 && Nq > 0 && Nkv > 0 && Nq % Nkv == 0 && H % 2 == 0, TPX_ERR_ARG,
               "rope_kv_update: bad shape");
@@ -569,6 +570,7 @@ extern "C" size_t tpx_attention_scratch_bytes(int64_t B, int64_t Nkv, int64_t Sq
 extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, const uint16_t* am, int64_t B,
                              int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len, int64_t Spad, int causal,
                              int out_bsnrh, const int32_t* dev_len, uint16_t* out, void* scratch, size_t scratch_bytes, void* stream) {
+  if (Sq == 0 && B > 0 && Nkv > 0 && R > 0) return TPX_OK;  // no queries
   TPX_REQUIRE(q && kc && vc && out, TPX_ERR_ARG, "attention: null pointer");
   TPX_REQUIRE(B > 0 && Nkv > 0 && Sq >= 0 && R > 0 && key_len >= Sq, TPX_ERR_ARG, "attention: bad shape");
   TPX_REQUIRE(H == 64 || H == 128, TPX_ERR_UNSUPPORTED, "attention: head dim %ld not supported (64 or 128)", (long)H);
