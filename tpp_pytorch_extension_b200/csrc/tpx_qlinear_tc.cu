@@ -814,7 +814,7 @@ static TcPlan tc_plan(int64_t M, int64_t N, int64_t K, bool pair, bool allow_clu
   // Few tiles: a cluster of c CTAs per tile cuts K between them and reduces through distributed shared memory,
   // which takes the fix-up pass (a second kernel behind a round trip through L2) off the critical path.
   pl.cluster = 1;
-  if (allow_cluster && !pl.whole_tiles && T * 2 <= sms && pl.tok <= 32) {
+  if (allow_cluster && !pl.whole_tiles && T * 2 <= sms) {  // (down projection, M = 128: 39.9 us against 47.5 us with the fix-up pass)
     int c = (int)(sms / T);
     if (c > 8) c = 8;
     if (c > pl.KU) c = pl.KU;
