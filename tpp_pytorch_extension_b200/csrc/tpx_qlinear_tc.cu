@@ -937,7 +937,8 @@ static bool tc_wide(int64_t M, int64_t N, int64_t K, bool pair) {
   const long long T = pair ? (N + 127) / 128 : (N + 255) / 256;  // tiles of the wide kernel
   const int sms = sm_count();
   (void)K;
-  return (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
+  if ((T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms) return true;  // whole tiles
+  return M <= 16 && T * 2 <= sms;  // few tiles: clusters split K in either kernel, the wide one needs fewer MMA cycles
 }
 
 static size_t tc_scratch_need(int64_t M, int64_t N, int64_t K, bool pair, bool wide) {

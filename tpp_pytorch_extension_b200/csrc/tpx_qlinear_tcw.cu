@@ -123,8 +123,13 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const long long U = (long long)p.TN * p.KS;
   const long long G = gridDim.x;
   const long long T = p.TN;
-  const long long u0 = p.whole_tiles ? ((long long)blockIdx.x * T / G) * p.KS : (long long)blockIdx.x * U / G;
-  const long long u1 = p.whole_tiles ? (((long long)blockIdx.x + 1) * T / G) * p.KS : ((long long)blockIdx.x + 1) * U / G;
+  // p.cluster > 1: the CTAs of a cluster share one tile and cut its k units evenly between them
+  const int crank = p.cluster > 1 ? (int)tc_cluster_rank() : 0;
+  const long long ctile = blockIdx.x / p.cluster;
+  const long long u0 = p.cluster > 1 ? ctile * p.KS + (long long)crank * p.KS / p.cluster
+                     : p.whole_tiles ? ((long long)blockIdx.x * T / G) * p.KS : (long long)blockIdx.x * U / G;
+  const long long u1 = p.cluster > 1 ? ctile * p.KS + ((long long)crank + 1) * p.KS / p.cluster
+                     : p.whole_tiles ? (((long long)blockIdx.x + 1) * T / G) * p.KS : ((long long)blockIdx.x + 1) * U / G;
   const int nunits = (int)(u1 - u0);
   const int tile0 = (int)(u0 / p.KS), ks0 = (int)(u0 % p.KS);
 
@@ -336,6 +341,16 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             if (whole) {
               const int n = DUAL ? tile * 128 + col : tile * 256 + col;
               if (lane_live && tok < p.M && n < p.N) tcw_finish8<DUAL>(p, tok, n, v, u);
+            } else if (p.cluster > 1) {  // partial of a cluster member: [token][256 columns] fp32 at the start of its stages
+              if (lane_live) {
+                const uint32_t sp = smem_base + (uint32_t)((tok * 256 + col) * 4);
+                tc_st_shared_f4(sp, make_float4(v[0], v[1], v[2], v[3]));
+                tc_st_shared_f4(sp + 16, make_float4(v[4], v[5], v[6], v[7]));
+                if (DUAL) {
+                  tc_st_shared_f4(sp + 512, make_float4(u[0], u[1], u[2], u[3]));
+                  tc_st_shared_f4(sp + 528, make_float4(u[4], u[5], u[6], u[7]));
+                }
+              }
             } else if (lane_live) {
               __stcg(reinterpret_cast<float4*>(myslot + col), make_float4(v[0], v[1], v[2], v[3]));
               __stcg(reinterpret_cast<float4*>(myslot + col) + 1, make_float4(v[4], v[5], v[6], v[7]));
@@ -360,6 +375,37 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   if (threadIdx.x == 128) tc_stamp(p, 6);
   tc_fence_before();
   __syncthreads();
+  if (p.cluster > 1) {
+    // every member's partial is in its own shared memory; the (token, 8 features) groups of the tile go round the
+    // members, each adds the members' parts in rank order (distributed shared memory reads) and finishes its groups.
+    // Nobody leaves before all have finished reading.
+    tc_cluster_sync();
+    if (warp >= 2) {
+      constexpr int GROUPS = DUAL ? 16 : 32;  // groups of 8 output features per token
+      const int et = (int)threadIdx.x - 64;
+      const int live_tok = p.M < TOKP ? p.M : TOKP;
+      for (int i = crank * 128 + et; i < live_tok * GROUPS; i += 128 * p.cluster) {
+        const int tk = i / GROUPS, col = (i % GROUPS) * 8;
+        const int n = DUAL ? (int)ctile * 128 + col : (int)ctile * 256 + col;
+        if (n >= p.N) continue;
+        float v[8], u[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) v[q] = u[q] = 0.0f;
+        const uint32_t sp = smem_base + (uint32_t)((tk * 256 + col) * 4);
+        for (int m = 0; m < p.cluster; m++) {
+          const uint32_t rp = tc_mapa(sp, (uint32_t)m);
+          const float4 a0 = tc_ld_cluster_f4(rp), a1 = tc_ld_cluster_f4(rp + 16);
+          v[0] += a0.x; v[1] += a0.y; v[2] += a0.z; v[3] += a0.w; v[4] += a1.x; v[5] += a1.y; v[6] += a1.z; v[7] += a1.w;
+          if (DUAL) {
+            const float4 b0 = tc_ld_cluster_f4(rp + 512), b1 = tc_ld_cluster_f4(rp + 528);
+            u[0] += b0.x; u[1] += b0.y; u[2] += b0.z; u[3] += b0.w; u[4] += b1.x; u[5] += b1.y; u[6] += b1.z; u[7] += b1.w;
+          }
+        }
+        tcw_finish8<DUAL>(p, tk, n, v, u);
+      }
+    }
+    tc_cluster_sync();
+  }
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)C::TMEM_COLS) : "memory");
@@ -421,7 +467,7 @@ __global__ void __launch_bounds__(128) tcw_fixup_kernel(TcParams p, int TOKP, in
 
 // ---------------------------------------------------------------- host side
 struct TcwPlan {
-  int tokp, uks, KS, KU, tiles128, TN, grid, whole;  // KS k steps, KU = KS / uks pipeline units per tile
+  int tokp, uks, KS, KU, tiles128, TN, grid, whole, cluster;  // KS k steps, KU = KS / uks pipeline units per tile
   size_t off_terms, off_sfb, off_partial, total;
 };
 
@@ -439,6 +485,15 @@ static TcwPlan tcw_plan(int64_t M, int64_t N, int64_t K, bool pair) {
   pl.whole = (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
   { const char* e = getenv("TPX_TC_WHOLE"); if (e) pl.whole = atoi(e); }
   pl.grid = pl.whole ? (int)(T < sms ? T : sms) : (int)(U < sms ? U : sms);
+  // few tiles: a cluster of CTAs per tile cuts K and reduces over distributed shared memory (no fix-up pass)
+  pl.cluster = 1;
+  if (!pl.whole && T * 2 <= sms) {
+    int c = (int)(sms / T);
+    if (c > 8) c = 8;
+    if (c > pl.KU) c = pl.KU;
+    if (c > 1) pl.cluster = c;
+  }
+  { const char* e = getenv("TPX_TC_CLUSTER"); if (e && atoi(e) == 0) pl.cluster = 1; }
   size_t o = kTcCounterBytes;
   auto bump = [&](size_t bytes) { size_t r = o; o += (bytes + 1023) & ~(size_t)1023; return r; };
   pl.off_terms = bump((size_t)pl.KS * 2 * pl.tokp * 128);
@@ -471,6 +526,46 @@ static int tcw_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (p.cluster > 1) {
+    // one cluster per tile, all of them resident at once, or not at all (then the tiles are cut stream-K fashion)
+    cudaLaunchConfig_t cc = cfg;
+    cc.gridDim = dim3((unsigned)(p.TN * p.cluster));
+    cudaLaunchAttribute a2[2];
+    a2[0] = attr[0];
+    a2[1].id = cudaLaunchAttributeClusterDimension;
+    a2[1].val.clusterDim.x = (unsigned)p.cluster;
+    a2[1].val.clusterDim.y = 1;
+    a2[1].val.clusterDim.z = 1;
+    cc.attrs = a2;
+    cc.numAttrs = 2;
+    // the largest cluster size, from the planned one down, of which one cluster per tile can be resident at once
+    static int fits[16][9] = {};  // 0 unknown, else 1 + the number of clusters of this size that can be resident
+    int c = p.cluster;
+    for (; c >= 2; c--) {
+      int& f = fits[(dev >= 0 && dev < 16) ? dev : 0][c];
+      if (f == 0) {
+        a2[1].val.clusterDim.x = (unsigned)c;
+        cc.gridDim = dim3((unsigned)(p.TN * c));
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, qlinear_tcw_kernel<TOKP, DUAL, UKS>, &cc);
+        if (e != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
+        f = 1 + n;
+      }
+      if (f - 1 >= p.TN) break;
+    }
+    if (c >= 2) {
+      TcParams q = p;
+      q.cluster = c;
+      a2[1].val.clusterDim.x = (unsigned)c;
+      cc.gridDim = dim3((unsigned)(p.TN * c));
+      count_launch();
+      TPX_CUDA_OK(cudaLaunchKernelEx(&cc, qlinear_tcw_kernel<TOKP, DUAL, UKS>, w, x, q, wq, tiles128, ksteps));
+      return TPX_OK;
+    }
+    TcParams q = p;
+    q.cluster = 1;
+    return tcw_launch<TOKP, DUAL, UKS>(w, x, q, wq, tiles128, ksteps, grid, st);
+  }
   count_launch();
   TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tcw_kernel<TOKP, DUAL, UKS>, w, x, p, wq, tiles128, ksteps));
   if (!p.whole_tiles && grid > 1) {
@@ -509,7 +604,7 @@ int tcw_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x,
   p.partial = reinterpret_cast<float*>(sc + pl.off_partial);
   p.counters = reinterpret_cast<unsigned*>(sc);
   p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
-  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = 1; p.whole_tiles = pl.whole;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = 1; p.whole_tiles = pl.whole; p.cluster = pl.cluster;
   if (pair) {
     switch (pl.tokp) {
       case 16: return tcw_launch<16, true, 2>(mw, mx, p, wq, pl.tiles128, pl.KS, pl.grid, st);
