@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-linear hot path on B200.
 
-Workload (BASELINE config 2): MXFP4 weight-only linears of the Llama-3-8B MLP shape,
+Workload (the MXFP4 sweep configuration of the benchmark): MXFP4 weight-only linears of the Llama-3-8B MLP shape,
 W_gate/W_up [14336, 4096] and W_down [4096, 14336], bf16 activations X [M, 4096] for
 M in {1, 8, 64, 512, 4096}. One *step* is one pass of the sweep: for every M, the fused
 gate/up pair with the SiLU*mul epilogue, then the down projection.

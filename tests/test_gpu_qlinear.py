@@ -167,7 +167,7 @@ def test_linearity_full_size(cuda):
 
 
 def test_config1_shape_int8_silu(cuda):
-    """BASELINE config 1: int8 (block 64) [11008 x 4096], M = 32, bias, SiLU; a sampled check against the oracle."""
+    """The int8 single-op configuration of the benchmark: int8 (block 64) [11008 x 4096], M = 32, bias, SiLU; a sampled check against the oracle."""
     rng = np.random.default_rng(0)
     N, K, M = 11008, 4096, 32
     q, wd, _ = make_qweight(rng, N, K, "int8", cuda, block=64)
