@@ -158,6 +158,22 @@ int tpx_qlinear_mxfp4_tc_static(const uint8_t* wq, const uint8_t* sfa, int pair,
                                 int64_t N, int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in,
                                 const uint16_t* res, float res_scale, uint16_t* y, void* stream);
 
+/* ---------------------------------------------------------------- int8 linear on the tcgen05 tensor cores
+ * Up to 64 tokens with the reference's own int8 arithmetic (TppBlockedQInt8LinearW, src/csrc/fused_gemm.h:1075-1341):
+ * the activations are quantised on the fly to int8 with one scale per (token, K block) (:1249), each K block is an
+ * int8 x int8 -> int32 product and y accumulates tmp * s_x * s_w (:1197-1204); the running sum stays in fp32 where
+ * the reference rounds it to bf16 after every block. wq is the plain int8 weight [ceil(N/128)*128][ceil(K/128)*128]
+ * (zero padding) and swT its scales [K/block][ceil(N/128)*128], both built by tpx_repack_qint8_tc from the
+ * interchange tensors of tpx_remap_and_quantize_qint8. Block sizes 64, 128, 256, 512. Post-ops as tpx_qlinear. The
+ * scratch holds the quantised activations; its first 64 KiB as for tpx_qlinear.                                   */
+int tpx_tc_packed_bytes_qint8(int64_t N, int64_t K, int64_t block_size, size_t* wq_bytes, size_t* sw_bytes);
+int tpx_repack_qint8_tc(const int8_t* q, const float* scales, int64_t N, int64_t K, int64_t block_size, int8_t* wq,
+                        float* swT, void* stream);
+size_t tpx_qlinear_qint8_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int64_t block_size);
+int tpx_qlinear_qint8_tc(const int8_t* wq, const float* swT, const uint16_t* x, int64_t M, int64_t N, int64_t K,
+                         int64_t block_size, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
+                         float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream);
+
 /* ---------------------------------------------------------------- decoder-layer pieces
  * RMSNorm: y = x * rsqrt(mean(x^2) + eps) * gamma, fp32 statistics. Replaces llama_rms_norm
  * (src/csrc/llm/fused_llm_infer.cpp:336-363; RMSNormFwdTPP::ref src/csrc/xsmm_functors.h:4628-4654).

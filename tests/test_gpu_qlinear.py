@@ -126,6 +126,31 @@ def test_int8_many_tokens(cuda):
     assert O.rel_err(y2, O.gate_up(x, wd, wd2)) <= TOL
 
 
+@pytest.mark.parametrize("block", [64, 256])
+@pytest.mark.parametrize("M", [1, 7, 16, 33, 64])
+def test_int8_tensor_core_kernel_matches_reference_arithmetic(cuda, monkeypatch, M, block):
+    """The tcgen05 kind::i8 kernel (activations quantised per K block, int32 block products, fp32 scaling) against the
+    oracle's restatement of the reference's int8 arithmetic and against the weight-only fp32 oracle; post-ops, a gate/up
+    pair, ragged N and a K split over a cluster."""
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    monkeypatch.setenv("TPX_INT8_PATH", "tc")
+    rng = np.random.default_rng(300 + M + block)
+    N, K = 208, 1024
+    q, wd, (qq, ss, bs) = make_qweight(rng, N, K, "int8", cuda, block=block)
+    q2, wd2, _ = make_qweight(rng, N, K, "int8", cuda, block=block)
+    x = O.randn_bf16(rng, (M, K))
+    y = run_fc(x, q, cuda)
+    assert O.rel_err(y, O.qlinear_int8_dynact(x, qq, ss, bs)) <= 1.5e-2  # same arithmetic up to the bf16 rounding of the running sum after every block
+    assert O.rel_err(y, O.qlinear(x, wd)) <= TOL
+    bias = O.randn_bf16(rng, (N,), 0.01)
+    res = O.randn_bf16(rng, (M, N))
+    y = run_fc(x, q, cuda, bias=to_dev_bf16(bias, cuda), act="silu", res=to_dev_bf16(res, cuda), res_scale=0.5)
+    assert O.rel_err(y, O.qlinear(x, wd, bias=bias, res=res, res_scale=0.5, act=O.ACT_SILU)) <= TOL
+    y2 = to_host_bits(F.fc_gate_up(to_dev_bf16(x, cuda), q, q2))
+    assert O.rel_err(y2, O.gate_up(x, wd, wd2)) <= TOL
+    assert_no_kernel_error()
+
+
 def test_int8_reference_arithmetic_is_within_tolerance(cuda):
     """The reference's int8 path quantises activations on the fly; ours is weight-only. Both sit within the
     tolerance of the fp32 oracle, and of each other."""

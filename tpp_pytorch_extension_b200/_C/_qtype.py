@@ -109,6 +109,30 @@ class QTensor:
         return self._packed
 
 
+def _packed_i8tc(self):
+    """(wq, swT) of an int8 weight for the tensor-core int8 linear: the plain int8 matrix padded to 128 x 128 tiles and
+    feature-contiguous scales; built once and cached."""
+    if self.kind == W_MXFP4:
+        raise _lib.TpxError("the int8 tensor-core path takes int8 weights")
+    hit = getattr(self, "_i8tc", None)
+    if hit is not None:
+        return hit
+    if self.codes.numel() == 0:
+        raise _lib.TpxError("the interchange tensors of this weight were dropped before it was packed for this use")
+    L = _lib.lib()
+    N, K = self.out_features, self.in_features
+    wb, sb = ctypes.c_size_t(), ctypes.c_size_t()
+    _lib.check(L.tpx_tc_packed_bytes_qint8(N, K, self.block_size, ctypes.byref(wb), ctypes.byref(sb)))
+    dev = self.codes.device
+    wq = torch.empty(wb.value, dtype=torch.int8, device=dev)
+    sw = torch.empty(sb.value // 4, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(L.tpx_repack_qint8_tc(self.codes.data_ptr(), self.scales.data_ptr(), N, K, self.block_size, wq.data_ptr(),
+                                         sw.data_ptr(), _lib.stream()))
+    self._i8tc = (wq, sw)
+    return self._i8tc
+
+
 def _packed_tc(self, other=None):
     """(wq, sfa) in the tensor-core layout (MXFP4 only), built once and cached. With `other` (the up
     projection of a SwiGLU pair, `self` being the gate) the two weights are packed tile by tile side by
@@ -144,6 +168,7 @@ def _packed_tc(self, other=None):
 
 
 QTensor.packed_tc = _packed_tc
+QTensor.packed_i8tc = _packed_i8tc
 
 
 def _prepare(self, drop_interchange=False, pair_with=None):
@@ -157,6 +182,12 @@ def _prepare(self, drop_interchange=False, pair_with=None):
         self.packed()
         if pair_with is not None:
             pair_with.packed()
+        if self.kind != W_MXFP4:  # int8: the decode kernel of the tensor-core family reads its own layout
+            from ._fused_llm_infer import int8_path
+            if int8_path() == "tc":
+                self.packed_i8tc()
+                if pair_with is not None:
+                    pair_with.packed_i8tc()
     if drop_interchange:
         self.codes = self.codes.new_empty(0)
         if pair_with is not None:

@@ -156,6 +156,55 @@ __device__ __forceinline__ uint64_t tc_smem_desc_sbo(uint32_t saddr, uint32_t sb
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// Epilogue of 16 consecutive tokens of one output feature n: bias, activation, gate multiply, residual, bf16 store.
+// Straight-line code over the 16 tokens (loads first, then arithmetic, then stores) so that the tokens' dependent
+// chains overlap; only the loads and stores are predicated on the token being inside M.
+template <bool DUAL>
+__device__ __forceinline__ void tc_finish16(const TcParams& p, int tok0, int n, const float (&v)[16], const float (&v2)[16]) {
+  const int live = p.M - tok0;  // tokens tok0 .. tok0+live-1 exist
+  const size_t o0 = (size_t)tok0 * p.N + n;
+  const float b = p.bias ? bf16_bits_to_f32(p.bias[n]) : 0.0f;
+  float x[16];
+#pragma unroll
+  for (int j = 0; j < 16; j++) x[j] = v[j] + b;
+  switch (p.act) {
+    case TPX_ACT_GELU:
+#pragma unroll
+      for (int j = 0; j < 16; j++) x[j] = 0.5f * x[j] * (1.0f + erff(x[j] * 0.70710678118654752f));
+      break;
+    case TPX_ACT_SILU:
+#pragma unroll
+      for (int j = 0; j < 16; j++) x[j] = __fdividef(x[j], 1.0f + __expf(-x[j]));
+      break;
+    case TPX_ACT_RELU:
+#pragma unroll
+      for (int j = 0; j < 16; j++) x[j] = fmaxf(x[j], 0.0f);
+      break;
+    default: break;
+  }
+  if (DUAL) {
+#pragma unroll
+    for (int j = 0; j < 16; j++) x[j] *= v2[j];
+  }
+  if (p.mul_in) {
+    uint16_t t[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) t[j] = j < live ? p.mul_in[o0 + (size_t)j * p.N] : (uint16_t)0;
+#pragma unroll
+    for (int j = 0; j < 16; j++) x[j] *= bf16_bits_to_f32(t[j]);
+  }
+  if (p.res) {
+    uint16_t t[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) t[j] = j < live ? p.res[o0 + (size_t)j * p.N] : (uint16_t)0;
+#pragma unroll
+    for (int j = 0; j < 16; j++) x[j] += bf16_bits_to_f32(t[j]) * p.res_scale;
+  }
+#pragma unroll
+  for (int j = 0; j < 16; j++)
+    if (j < live) p.y[o0 + (size_t)j * p.N] = f32_to_bf16_bits(x[j]);
+}
+
 // host helpers shared by the tensor-core linears
 int tc_make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows);
 int tc_padded_ks(int64_t K, bool pair);
