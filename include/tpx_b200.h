@@ -165,14 +165,17 @@ int tpx_qlinear_mxfp4_tc_static(const uint8_t* wq, const uint8_t* sfa, int pair,
  * the reference rounds it to bf16 after every block. wq is the plain int8 weight [ceil(N/128)*128][ceil(K/128)*128]
  * (zero padding) and swT its scales [K/block][ceil(N/128)*128], both built by tpx_repack_qint8_tc from the
  * interchange tensors of tpx_remap_and_quantize_qint8. Block sizes 64, 128, 256, 512. Post-ops as tpx_qlinear. The
- * scratch holds the quantised activations; its first 64 KiB as for tpx_qlinear.                                   */
+ * scratch holds the quantised activations; its first 64 KiB as for tpx_qlinear. reuse_act != 0 skips the quantisation
+ * and reads what the previous call on the same scratch left there (same x, same K and block size: the second linear
+ * of a gate/up pair). gamma != NULL applies an RMSNorm (gamma bf16 or fp32, eps) to x before the quantisation, in the
+ * same kernel (rows of up to 8192 values, blocks of up to 256).                                                    */
 int tpx_tc_packed_bytes_qint8(int64_t N, int64_t K, int64_t block_size, size_t* wq_bytes, size_t* sw_bytes);
 int tpx_repack_qint8_tc(const int8_t* q, const float* scales, int64_t N, int64_t K, int64_t block_size, int8_t* wq,
                         float* swT, void* stream);
 size_t tpx_qlinear_qint8_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int64_t block_size);
-int tpx_qlinear_qint8_tc(const int8_t* wq, const float* swT, const uint16_t* x, int64_t M, int64_t N, int64_t K,
-                         int64_t block_size, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
-                         float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream);
+int tpx_qlinear_qint8_tc(const int8_t* wq, const float* swT, const uint16_t* x, const void* gamma, int gamma_is_f32,
+                         float eps, int64_t M, int64_t N, int64_t K, int64_t block_size, int reuse_act, const uint16_t* bias, int act, const uint16_t* mul_in,
+                         const uint16_t* res, float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream);
 
 /* ---------------------------------------------------------------- decoder-layer pieces
  * RMSNorm: y = x * rsqrt(mean(x^2) + eps) * gamma, fp32 statistics. Replaces llama_rms_norm

@@ -18,6 +18,8 @@ def mxfp4_path(request, monkeypatch):
     the tcgen05 kernel with the weights on the wide side (up to 64 tokens), and the mma.sync streaming kernel."""
     monkeypatch.setenv("TPX_MXFP4_PATH", "stream" if request.param == "stream" else "tc")
     monkeypatch.setenv("TPX_TC_WIDE", "1" if request.param == "tc_wide" else "0")
+    # int8 weights: the tcgen05 kind::i8 kernel (reference arithmetic) with the tensor-core families, else the streaming kernel
+    monkeypatch.setenv("TPX_INT8_PATH", "stream" if request.param == "stream" else "tc")
     return request.param
 
 
@@ -31,7 +33,7 @@ def run_fc(x_bits, q, dev, **kw):
 
 @pytest.mark.parametrize("kind", ["mxfp4", "int8"])
 @pytest.mark.parametrize("M", [1, 3, 8, 13, 32, 45])
-def test_fc_plain_matches_oracle(cuda, kind, M):
+def test_fc_plain_matches_oracle(cuda, kind, M, mxfp4_path):
     rng = np.random.default_rng(100 + M)
     N, K = 256, 512
     q, wd, _ = make_qweight(rng, N, K, kind, cuda)
@@ -39,8 +41,10 @@ def test_fc_plain_matches_oracle(cuda, kind, M):
     y = run_fc(x, q, cuda)
     ref = O.qlinear(x, wd)
     assert O.rel_err(y, ref) <= TOL
-    # exact products + fp32 accumulation: the only differences are summation order and one bf16 rounding
-    assert O.rel_err(y, ref) <= 1e-2
+    if kind == "mxfp4" or mxfp4_path == "stream":
+        # exact products + fp32 accumulation: the only differences are summation order and one bf16 rounding
+        # (the int8 tensor-core kernel quantises the activations as the reference does: only the wider bound holds)
+        assert O.rel_err(y, ref) <= 1e-2
 
 
 @pytest.mark.parametrize("kind", ["mxfp4", "int8"])
@@ -148,6 +152,14 @@ def test_int8_tensor_core_kernel_matches_reference_arithmetic(cuda, monkeypatch,
     assert O.rel_err(y, O.qlinear(x, wd, bias=bias, res=res, res_scale=0.5, act=O.ACT_SILU)) <= TOL
     y2 = to_host_bits(F.fc_gate_up(to_dev_bf16(x, cuda), q, q2))
     assert O.rel_err(y2, O.gate_up(x, wd, wd2)) <= TOL
+    # RMSNorm fused into the activation quantisation
+    gamma = O.f32_to_bf16(1 + 0.2 * rng.standard_normal(K).astype(np.float32))
+    xs = O.randn_bf16(rng, (M, K), 3.0)
+    xn = O.rmsnorm(xs, gamma, 1e-5)
+    y3 = to_host_bits(F.fc_plain_norm(to_dev_bf16(xs, cuda), to_dev_bf16(gamma, cuda), 1e-5, q))
+    assert O.rel_err(y3, O.qlinear_int8_dynact(xn, qq, ss, bs)) <= 1.5e-2
+    y4 = to_host_bits(F.fc_gate_up(to_dev_bf16(xs, cuda), q, q2, "silu", norm=(to_dev_bf16(gamma, cuda), 1e-5)))
+    assert O.rel_err(y4, O.gate_up(xn, wd, wd2)) <= TOL
     assert_no_kernel_error()
 
 

@@ -17,28 +17,31 @@ def mxfp4_path():
 
 
 def int8_path():
-    """Kernel family for int8 weights at up to 64 tokens: "tc" = tcgen05 kind::i8 kernel with the reference's
+    """Kernel family for int8 weights at up to 64 tokens: "tc" (default) = tcgen05 kind::i8 kernel with the reference's
     activation-quantised arithmetic, "stream" = the mma.sync weight-only streaming kernel. Read from TPX_INT8_PATH
     on every call."""
     import os
-    return os.environ.get("TPX_INT8_PATH", "stream")
+    return os.environ.get("TPX_INT8_PATH", "tc")
 
 
-def _int8_tc(x, y, w, w2, bias, act, mul_in, res, res_scale):
+def _int8_tc(x, y, w, w2, bias, act, mul_in, res, res_scale, norm=None):
     """Up to 64 tokens on int8 weights through tpx_qlinear_qint8_tc; a gate/up pair runs as two calls, the second
     multiplying by the activated first."""
     L = _lib.lib()
     N, K = w.out_features, w.in_features
     M = x.numel() // K
 
-    def run(wt, out, b, a, m, r, rs):
+    gam, eps = (norm[0], float(norm[1])) if norm is not None else (None, 0.0)
+
+    def run(wt, out, b, a, m, r, rs, reuse=0):
         wq, sw = wt.packed_i8tc()
         key = ("i8tc", M, N, K, wt.block_size)
         nb = _SCRATCH_BYTES.get(key)
         if nb is None:
             nb = _SCRATCH_BYTES[key] = L.tpx_qlinear_qint8_tc_scratch_bytes(M, N, K, wt.block_size)
         sc = _lib.scratch(nb, x.device)
-        rc = L.tpx_qlinear_qint8_tc(wq.data_ptr(), sw.data_ptr(), x.data_ptr(), M, N, K, wt.block_size, _lib.ptr(b), ACT[a], _lib.ptr(m),
+        rc = L.tpx_qlinear_qint8_tc(wq.data_ptr(), sw.data_ptr(), x.data_ptr(), _lib.ptr(gam), int(gam is not None and gam.dtype == torch.float32),
+                                    eps, M, N, K, wt.block_size, reuse, _lib.ptr(b), ACT[a], _lib.ptr(m),
                                     _lib.ptr(r), float(rs), out.data_ptr(), sc.data_ptr(), sc.numel(), _lib.stream())
         if rc:
             _lib.check(rc)
@@ -48,7 +51,7 @@ def _int8_tc(x, y, w, w2, bias, act, mul_in, res, res_scale):
         return y
     h = torch.empty_like(y)
     run(w, h, bias, act, None, None, 1.0)
-    run(w2, y, None, None, h, None, 1.0)
+    run(w2, y, None, None, h, None, 1.0, reuse=1)  # same x: the quantised activations are still in the scratch
     return y
 
 
@@ -98,12 +101,14 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
         if rc:
             _lib.check(rc)
         return y
-    if norm is not None:
-        x = rms_norm(x, norm[0], norm[1])
     if w.kind != 1 and 0 < M <= 64 and int8_path() == "tc" and w.block_size in (64, 128, 256, 512):
         if w2 is not None and (w2.out_features, w2.in_features, w2.kind, w2.block_size) != (N, K, w.kind, w.block_size):
             raise _lib.TpxError("gate/up weights must have the same shape and quantization")
-        return _int8_tc(x, y, w, w2, bias, act, mul_in, res, res_scale)
+        if norm is not None and not (K <= 8192 and w.block_size <= 256):
+            x, norm = rms_norm(x, norm[0], norm[1]), None
+        return _int8_tc(x, y, w, w2, bias, act, mul_in, res, res_scale, norm)
+    if norm is not None:
+        x = rms_norm(x, norm[0], norm[1])
     pc, ps = w.packed()
     pc2 = ps2 = None
     if w2 is not None:

@@ -84,6 +84,99 @@ __global__ void quantize_act_i8_kernel(const uint16_t* __restrict__ x, int M, in
   sx[(size_t)blk * TOKP + tok] = scale;
 }
 
+// The same quantisation with one CTA per token row, vectorised, for blocks of up to 256 values, optionally behind an
+// RMSNorm of the row (y = bf16(x * rsqrt(mean(x^2) + eps) * gamma), llama_rms_norm of the reference, rows of up to
+// 8192 values then): eight consecutive values per thread, the B/8 threads of a block reduce its maximum with shuffles.
+constexpr int kQaThreads = 256;
+__global__ void __launch_bounds__(kQaThreads) quantize_act_i8_row_kernel(const uint16_t* __restrict__ x, const void* __restrict__ gamma,
+                                                                         int gamma_f32, float eps, int M, int K, int Kp, int B, int TOKP,
+                                                                         int8_t* __restrict__ xq, float* __restrict__ sx) {
+  __shared__ float red[kQaThreads / 32];
+  pdl_trigger();
+  pdl_wait();
+  const int tok = blockIdx.x;
+  const int nv = K / 8;
+  const int lanes = B / 8;  // threads per scale block: 8, 16 or 32
+  const bool live = tok < M;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)tok * K);
+  float inv = 1.0f;
+  if (gamma && live) {
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < nv; i += kQaThreads) {
+      const uint4 v = xr[i];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float a = bf16_bits_to_f32((uint16_t)(w[j] & 0xffff)), b = bf16_bits_to_f32((uint16_t)(w[j] >> 16));
+        ss += a * a + b * b;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kQaThreads / 32; w++) tot += red[w];
+    inv = rsqrtf(tot / (float)K + eps);
+  }
+  for (int i0 = 0; i0 < nv; i0 += kQaThreads) {
+    const int i = i0 + threadIdx.x;
+    const bool in = i < nv;
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) f[j] = 0.0f;
+    if (in && live) {
+      const uint4 v = xr[i];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        f[2 * j] = bf16_bits_to_f32((uint16_t)(w[j] & 0xffff));
+        f[2 * j + 1] = bf16_bits_to_f32((uint16_t)(w[j] >> 16));
+      }
+      if (gamma) {
+        float g[8];
+        if (gamma_f32) {
+          const float4 g0 = reinterpret_cast<const float4*>(gamma)[2 * i], g1 = reinterpret_cast<const float4*>(gamma)[2 * i + 1];
+          g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+        } else {
+          const uint4 gv = reinterpret_cast<const uint4*>(gamma)[i];
+          const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            g[2 * j] = bf16_bits_to_f32((uint16_t)(gw[j] & 0xffff));
+            g[2 * j + 1] = bf16_bits_to_f32((uint16_t)(gw[j] >> 16));
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) f[j] = bf16_bits_to_f32(f32_to_bf16_bits(f[j] * inv * g[j]));
+      }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(f[j]));
+    for (int o = 1; o < lanes; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = (float)((double)amax / 127.0);
+    const float iscale = scale != 0.0f ? 1.0f / scale : 0.0f;
+    uint32_t o2[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        float q = nearbyintf(f[4 * h + e] * iscale);
+        q = fminf(fmaxf(q, -127.0f), 127.0f);
+        word |= ((uint32_t)(uint8_t)(int8_t)(int)q) << (8 * e);
+      }
+      o2[h] = word;
+    }
+    if (in) {
+      *reinterpret_cast<uint2*>(xq + (size_t)tok * Kp + (size_t)i * 8) = make_uint2(o2[0], o2[1]);
+      if ((i % lanes) == 0) sx[(size_t)(i / lanes) * TOKP + tok] = live ? scale : 0.0f;
+    }
+  }
+}
+
 // Interchange tensors of remap_and_quantize_qint8 (q [N/16][K/B][B/4][16][4], scales [N/16][K/B][16]) -> plain int8
 // weight [Np][Kp] (zero padding) and feature-contiguous scales [K/B][Np].
 __global__ void repack_qint8_tc_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales, int64_t N, int64_t K, int64_t B,
@@ -107,7 +200,9 @@ struct I8Cfg {
   static constexpr int A_BYTES = 128 * 128;   // 128 features x 128 k values
   static constexpr int B_BYTES = TOK * 128;   // TOK tokens x 128 k values
   static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES + 1023) / 1024 * 1024;
-  static constexpr int NBUF = 8;              // int32 accumulators in flight (one per K block)
+  static constexpr int GROUP = 4;             // K blocks handed to the epilogue per barrier round trip
+  static constexpr int NBUF = 512 / TOK > 16 ? 16 : 512 / TOK;  // int32 accumulators (one per K block) in tensor memory
+  static constexpr int NGRP = NBUF / GROUP;
   static constexpr int TMEM_COLS = NBUF * TOK < 32 ? 32 : NBUF * TOK;
   static constexpr size_t SMEM = (size_t)kI8Stages * STAGE_BYTES + 1024;
   static_assert(NBUF * TOK <= 512, "tensor memory");
@@ -120,7 +215,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   using C = I8Cfg<TOK>;
   extern __shared__ unsigned char i8_smem_raw[];
   __shared__ __align__(8) unsigned long long bar_full[kI8Stages], bar_empty[kI8Stages];
-  __shared__ __align__(8) unsigned long long d_full[C::NBUF], d_free[C::NBUF];
+  __shared__ __align__(8) unsigned long long d_full[C::NGRP], d_free[C::NGRP];
   __shared__ uint32_t tmem_holder;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -139,7 +234,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       tc_mbar_init(tc_smem_u32(&bar_full[s]), 1);
       tc_mbar_init(tc_smem_u32(&bar_empty[s]), 1);
     }
-    for (int b = 0; b < C::NBUF; b++) {
+    for (int b = 0; b < C::NGRP; b++) {
       tc_mbar_init(tc_smem_u32(&d_full[b]), 1);
       tc_mbar_init(tc_smem_u32(&d_free[b]), 4);
     }
@@ -189,8 +284,10 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       // kind::i8: D = S32 (2), A = B = S8 (1), both K-major, N = TOK, M = 128
       const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TOK >> 3) << 17) | ((128u >> 4) << 24);
       int buf = 0, inblk = 0;  // accumulator in use, k32 steps already in the current scale block
-      uint32_t free_phase = 0;  // bit b: parity to wait for on d_free[b]
-      unsigned used = 0;        // bit b: accumulator b has been handed out before
+      uint32_t free_phase = 0;  // bit g: parity to wait for on d_free[g]
+      unsigned used = 0;        // bit g: group g has been handed out before
+      const int nblocks = nsteps * 4 / p.bsteps;
+      int done_blocks = 0;
       for (int it = 0; it < nsteps; it++) {
         const int s = it % kI8Stages;
         if (!tc_wait(tc_smem_u32(&bar_full[s]), (uint32_t)((it / kI8Stages) & 1))) { atomicExch(p.t.err, 4u); break; }
@@ -199,18 +296,23 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         bool dead = false;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-          if (inblk == 0 && ((used >> buf) & 1u)) {  // a recycled accumulator: the epilogue must have read it
-            if (!tc_wait(tc_smem_u32(&d_free[buf]), (free_phase >> buf) & 1u)) { atomicExch(p.t.err, 3u); dead = true; break; }
-            free_phase ^= 1u << buf;
+          const int grp = buf / C::GROUP;
+          if (inblk == 0 && buf % C::GROUP == 0 && ((used >> grp) & 1u)) {  // a recycled group: the epilogue must have read it
+            if (!tc_wait(tc_smem_u32(&d_free[grp]), (free_phase >> grp) & 1u)) { atomicExch(p.t.err, 3u); dead = true; break; }
+            free_phase ^= 1u << grp;
             tc_fence_after();
           }
           i8_mma(tmem + buf * TOK, tc_smem_desc(st) + (uint64_t)(2 * j), tc_smem_desc(st + C::A_BYTES) + (uint64_t)(2 * j), idesc,
                  inblk == 0 ? 0u : 1u);
-          if (++inblk == p.bsteps) {  // block complete: hand the accumulator to the epilogue
-            tc_commit(tc_smem_u32(&d_full[buf]));
-            used |= 1u << buf;
+          if (++inblk == p.bsteps) {  // block complete
             inblk = 0;
+            done_blocks++;
             buf = (buf + 1) % C::NBUF;
+            if (buf % C::GROUP == 0 || done_blocks == nblocks) {  // group complete: hand its accumulators to the epilogue
+              tc_commit(tc_smem_u32(&d_full[grp]));
+              used |= 1u << grp;
+              if (buf % C::GROUP != 0) buf = (buf / C::GROUP + 1) * C::GROUP % C::NBUF;
+            }
           }
         }
         if (dead) break;
@@ -228,36 +330,64 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const int nblocks = nsteps * 4 / p.bsteps;
     const int blk0 = ks0 * 4 / p.bsteps;
     uint32_t full_phase = 0;
-    float sw_next = blk0 < p.nblk ? p.swT[(size_t)blk0 * p.Np + n] : 0.0f;
-    for (int b = 0; b < nblocks; b++) {
-      const int buf = b % C::NBUF;
-      const float sw = sw_next;
-      if (b + 1 < nblocks) sw_next = blk0 + b + 1 < p.nblk ? p.swT[(size_t)(blk0 + b + 1) * p.Np + n] : 0.0f;
-      const bool real = blk0 + b < p.nblk;  // a block of pure k padding holds zeros and has no scales
-      const float4* sxp = reinterpret_cast<const float4*>(p.sx + (size_t)(real ? blk0 + b : 0) * TOK);
-      float sxv[TOK];
+    constexpr bool kPrefetchSx = TOK * C::GROUP <= 128;  // activation scales of a whole group in registers
+    int b = 0, buf = 0;
+    bool dead = false;
+    while (b < nblocks && !dead) {
+      const int grp = buf / C::GROUP;
+      const int cnt = nblocks - b < C::GROUP ? nblocks - b : C::GROUP;
+      // scales of the group's blocks are fetched before the wait (a block of pure k padding has none: zeros)
+      float sw[C::GROUP];
+      float sxg[kPrefetchSx ? C::GROUP : 1][TOK];
 #pragma unroll
-      for (int q = 0; q < TOK / 4; q++) {
-        const float4 v = sxp[q];
-        sxv[4 * q] = v.x; sxv[4 * q + 1] = v.y; sxv[4 * q + 2] = v.z; sxv[4 * q + 3] = v.w;
+      for (int q = 0; q < C::GROUP; q++) {
+        const int blk = blk0 + b + q;
+        const bool real = q < cnt && blk < p.nblk;
+        sw[q] = real ? p.swT[(size_t)blk * p.Np + n] : 0.0f;
+        if (kPrefetchSx) {
+          const float4* sxp = reinterpret_cast<const float4*>(p.sx + (size_t)(real ? blk : 0) * TOK);
+#pragma unroll
+          for (int i = 0; i < TOK / 4; i++) {
+            const float4 v = sxp[i];
+            sxg[q][4 * i] = v.x; sxg[q][4 * i + 1] = v.y; sxg[q][4 * i + 2] = v.z; sxg[q][4 * i + 3] = v.w;
+          }
+        }
       }
-      if (!tc_wait(tc_smem_u32(&d_full[buf]), (full_phase >> buf) & 1u)) {
+      if (!tc_wait(tc_smem_u32(&d_full[grp]), (full_phase >> grp) & 1u)) {
         if (lane == 0) atomicExch(p.t.err, 6u);
+        dead = true;
         break;
       }
-      full_phase ^= 1u << buf;
+      full_phase ^= 1u << grp;
       tc_fence_after();
 #pragma unroll
-      for (int c0 = 0; c0 < TOK; c0 += 16) {
-        uint32_t d[16];
-        tc_ld_x16(tmem + lane_base + buf * TOK + c0, d);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      for (int q = 0; q < C::GROUP; q++) {
+        if (q < cnt) {
+          if (!kPrefetchSx) {
+            const int blk = blk0 + b + q;
+            const float4* sxp = reinterpret_cast<const float4*>(p.sx + (size_t)(blk < p.nblk ? blk : 0) * TOK);
 #pragma unroll
-        for (int i = 0; i < 16; i++) acc[c0 + i] += (float)(int)d[i] * sxv[c0 + i] * sw;
+            for (int i = 0; i < TOK / 4; i++) {
+              const float4 v = sxp[i];
+              sxg[0][4 * i] = v.x; sxg[0][4 * i + 1] = v.y; sxg[0][4 * i + 2] = v.z; sxg[0][4 * i + 3] = v.w;
+            }
+          }
+          const float* sxv = sxg[kPrefetchSx ? q : 0];
+#pragma unroll
+          for (int c0 = 0; c0 < TOK; c0 += 16) {
+            uint32_t d[16];
+            tc_ld_x16(tmem + lane_base + (buf + q) * TOK + c0, d);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 16; i++) acc[c0 + i] += (float)(int)d[i] * sxv[c0 + i] * sw[q];
+          }
+        }
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) tc_mbar_arrive(tc_smem_u32(&d_free[buf]));
+      if (lane == 0) tc_mbar_arrive(tc_smem_u32(&d_free[grp]));
+      b += cnt;
+      buf = (grp + 1) * C::GROUP % C::NBUF;
     }
     if (csize == 1) {
 #pragma unroll
@@ -435,9 +565,9 @@ extern "C" size_t tpx_qlinear_qint8_tc_scratch_bytes(int64_t M, int64_t N, int64
   return i8_plan(M, N, K, block_size).total;
 }
 
-extern "C" int tpx_qlinear_qint8_tc(const int8_t* wq, const float* swT, const uint16_t* x, int64_t M, int64_t N, int64_t K,
-                                    int64_t block_size, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
-                                    float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream) {
+extern "C" int tpx_qlinear_qint8_tc(const int8_t* wq, const float* swT, const uint16_t* x, const void* gamma, int gamma_is_f32, float eps,
+                                    int64_t M, int64_t N, int64_t K, int64_t block_size, int reuse_act, const uint16_t* bias, int act, const uint16_t* mul_in,
+                                    const uint16_t* res, float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream) {
   TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear_qint8_tc: bad shape");
   if (M == 0) return TPX_OK;
   TPX_REQUIRE(M <= 64, TPX_ERR_UNSUPPORTED, "qlinear_qint8_tc: at most 64 tokens per call (M=%ld)", (long)M);
@@ -456,8 +586,13 @@ extern "C" int tpx_qlinear_qint8_tc(const int8_t* wq, const float* swT, const ui
   unsigned char* sc = reinterpret_cast<unsigned char*>(scratch);
   int8_t* xq = reinterpret_cast<int8_t*>(sc + pl.off_xq);
   float* sx = reinterpret_cast<float*>(sc + pl.off_sx);
-  if (pl.Kp != K) TPX_CUDA_OK(cudaMemsetAsync(xq, 0, (size_t)pl.tokp * pl.Kp, st));  // the k padding of the last step reads as zero
-  {
+  if (!reuse_act && pl.Kp != K) TPX_CUDA_OK(cudaMemsetAsync(xq, 0, (size_t)pl.tokp * pl.Kp, st));  // the k padding reads as zero
+  TPX_REQUIRE(!gamma || (K <= 8192 && block_size <= 256 && ((uintptr_t)gamma & 15) == 0), TPX_ERR_UNSUPPORTED,
+              "qlinear_qint8_tc: the fused RMSNorm takes rows of up to 8192 values, blocks of up to 256 and a 16-byte aligned gamma");
+  if (!reuse_act && block_size <= 256) {
+    TPX_CUDA_OK(launch_pdl(quantize_act_i8_row_kernel, dim3((unsigned)pl.tokp), dim3(kQaThreads), 0, st, x, gamma, gamma_is_f32, eps, (int)M,
+                           (int)K, (int)pl.Kp, (int)block_size, pl.tokp, xq, sx));
+  } else if (!reuse_act) {
     const int threads = pl.tokp * (int)(K / block_size);
     TPX_CUDA_OK(launch_pdl(quantize_act_i8_kernel, dim3((unsigned)((threads + 127) / 128)), dim3(128), 0, st, x, (int)M, (int)K, (int)pl.Kp,
                            (int)block_size, pl.tokp, xq, sx));
