@@ -200,7 +200,8 @@ struct I8Cfg {
   static constexpr int A_BYTES = 128 * 128;   // 128 features x 128 k values
   static constexpr int B_BYTES = TOK * 128;   // TOK tokens x 128 k values
   static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES + 1023) / 1024 * 1024;
-  static constexpr int GROUP = 4;             // K blocks handed to the epilogue per barrier round trip
+  static constexpr int GROUP = 4;             // accumulators per group; a group (up to 4 K blocks, 256 k values or one larger block)
+                                              // is handed to the epilogue per barrier round trip
   static constexpr int NBUF = 512 / TOK > 16 ? 16 : 512 / TOK;  // int32 accumulators (one per K block) in tensor memory
   static constexpr int NGRP = NBUF / GROUP;
   static constexpr int TMEM_COLS = NBUF * TOK < 32 ? 32 : NBUF * TOK;
@@ -287,6 +288,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       uint32_t free_phase = 0;  // bit g: parity to wait for on d_free[g]
       unsigned used = 0;        // bit g: group g has been handed out before
       const int nblocks = nsteps * 4 / p.bsteps;
+      const int gsize = p.bsteps >= 8 ? 1 : 8 / p.bsteps;  // blocks per group: 256 k values, or one larger block
       int done_blocks = 0;
       for (int it = 0; it < nsteps; it++) {
         const int s = it % kI8Stages;
@@ -307,16 +309,18 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           if (++inblk == p.bsteps) {  // block complete
             inblk = 0;
             done_blocks++;
-            buf = (buf + 1) % C::NBUF;
-            if (buf % C::GROUP == 0 || done_blocks == nblocks) {  // group complete: hand its accumulators to the epilogue
+            if (buf % C::GROUP + 1 == gsize || done_blocks == nblocks) {
+              // group complete: hand its accumulators to the epilogue. This one commit also tells that the stages the
+              // group read are free again (the epilogue passes that on to the producer), so stages need none of their own.
               tc_commit(tc_smem_u32(&d_full[grp]));
               used |= 1u << grp;
-              if (buf % C::GROUP != 0) buf = (buf / C::GROUP + 1) * C::GROUP % C::NBUF;
+              buf = (grp + 1) * C::GROUP % C::NBUF;
+            } else {
+              buf++;
             }
           }
         }
         if (dead) break;
-        tc_commit(tc_smem_u32(&bar_empty[s]));
       }
     }
     __syncwarp();
@@ -331,11 +335,12 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const int blk0 = ks0 * 4 / p.bsteps;
     uint32_t full_phase = 0;
     constexpr bool kPrefetchSx = TOK * C::GROUP <= 128;  // activation scales of a whole group in registers
+    const int gsize = p.bsteps >= 8 ? 1 : 8 / p.bsteps;
     int b = 0, buf = 0;
     bool dead = false;
     while (b < nblocks && !dead) {
       const int grp = buf / C::GROUP;
-      const int cnt = nblocks - b < C::GROUP ? nblocks - b : C::GROUP;
+      const int cnt = nblocks - b < gsize ? nblocks - b : gsize;
       // scales of the group's blocks are fetched before the wait (a block of pure k padding has none: zeros)
       float sw[C::GROUP];
       float sxg[kPrefetchSx ? C::GROUP : 1][TOK];
@@ -360,6 +365,10 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       }
       full_phase ^= 1u << grp;
       tc_fence_after();
+      if (sub == 0 && lane == 0) {  // the MMAs of this group are complete: the stages they read may be refilled
+        const int it_lo = b * p.bsteps / 4, it_hi = (b + cnt) * p.bsteps / 4;
+        for (int it = it_lo; it < it_hi; it++) tc_mbar_arrive(tc_smem_u32(&bar_empty[it % kI8Stages]));
+      }
 #pragma unroll
       for (int q = 0; q < C::GROUP; q++) {
         if (q < cnt) {
