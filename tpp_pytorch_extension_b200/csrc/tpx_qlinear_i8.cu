@@ -17,7 +17,7 @@
 
 namespace tpx {
 
-constexpr int kI8Stages = 8;
+constexpr int kI8MaxStages = 8;
 
 struct I8Params {
   TcParams t;          // epilogue fields (bias, act, mul_in, res, res_scale, y, M, N, err, cluster)
@@ -200,14 +200,16 @@ struct I8Cfg {
   static constexpr int A_BYTES = 128 * 128;   // 128 features x 128 k values
   static constexpr int B_BYTES = TOK * 128;   // TOK tokens x 128 k values
   static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES + 1023) / 1024 * 1024;
+  static constexpr int STAGES_FIT = (227 * 1024 - 3072) / STAGE_BYTES;   // as many stages as shared memory holds: the bytes in
+  static constexpr int STAGES = STAGES_FIT > kI8MaxStages ? kI8MaxStages : STAGES_FIT;  // flight bound the stream, not the MMAs
   static constexpr int GROUP = 4;             // accumulators per group; a group (up to 4 K blocks, 256 k values or one larger block)
                                               // is handed to the epilogue per barrier round trip
   static constexpr int NBUF = 512 / TOK > 16 ? 16 : 512 / TOK;  // int32 accumulators (one per K block) in tensor memory
   static constexpr int NGRP = NBUF / GROUP;
   static constexpr int TMEM_COLS = NBUF * TOK < 32 ? 32 : NBUF * TOK;
-  static constexpr size_t SMEM = (size_t)kI8Stages * STAGE_BYTES + 1024;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
   static_assert(NBUF * TOK <= 512, "tensor memory");
-  static_assert(128 * TOK * 4 <= kI8Stages * STAGE_BYTES, "the partial tile of a cluster member fits in the stages");
+  static_assert(128 * TOK * 4 <= STAGES * STAGE_BYTES, "the partial tile of a cluster member fits in the stages");
 };
 
 template <int TOK>
@@ -215,7 +217,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, I8Params p) {
   using C = I8Cfg<TOK>;
   extern __shared__ unsigned char i8_smem_raw[];
-  __shared__ __align__(8) unsigned long long bar_full[kI8Stages], bar_empty[kI8Stages];
+  __shared__ __align__(8) unsigned long long bar_full[C::STAGES], bar_empty[C::STAGES];
   __shared__ __align__(8) unsigned long long d_full[C::NGRP], d_free[C::NGRP];
   __shared__ uint32_t tmem_holder;
 
@@ -231,7 +233,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   const int nsteps = ks1 - ks0;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kI8Stages; s++) {
+    for (int s = 0; s < C::STAGES; s++) {
       tc_mbar_init(tc_smem_u32(&bar_full[s]), 1);
       tc_mbar_init(tc_smem_u32(&bar_empty[s]), 1);
     }
@@ -266,13 +268,13 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         tc_mbar_expect_tx(tc_smem_u32(&bar_full[s]), C::A_BYTES + C::B_BYTES);
         tc_tma_2d(st, &tmW, ks * 128, tile * 128, tc_smem_u32(&bar_full[s]));
       };
-      const int early = nsteps < kI8Stages ? nsteps : kI8Stages;
+      const int early = nsteps < C::STAGES ? nsteps : C::STAGES;
       for (int it = 0; it < early; it++) fetch_w(it, ks0 + it);  // weights do not depend on the quantisation kernel
       pdl_wait();
       for (int it = 0; it < nsteps; it++) {
-        const int s = it % kI8Stages;
-        if (it >= kI8Stages) {
-          if (!tc_wait(tc_smem_u32(&bar_empty[s]), (uint32_t)((it / kI8Stages - 1) & 1))) { atomicExch(p.t.err, 2u); break; }
+        const int s = it % C::STAGES;
+        if (it >= C::STAGES) {
+          if (!tc_wait(tc_smem_u32(&bar_empty[s]), (uint32_t)((it / C::STAGES - 1) & 1))) { atomicExch(p.t.err, 2u); break; }
           fetch_w(s, ks0 + it);
         }
         tc_tma_2d(smem_base + (uint32_t)s * C::STAGE_BYTES + C::A_BYTES, &tmX, (ks0 + it) * 128, 0, tc_smem_u32(&bar_full[s]));
@@ -291,8 +293,8 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const int gsize = p.bsteps >= 8 ? 1 : 8 / p.bsteps;  // blocks per group: 256 k values, or one larger block
       int done_blocks = 0;
       for (int it = 0; it < nsteps; it++) {
-        const int s = it % kI8Stages;
-        if (!tc_wait(tc_smem_u32(&bar_full[s]), (uint32_t)((it / kI8Stages) & 1))) { atomicExch(p.t.err, 4u); break; }
+        const int s = it % C::STAGES;
+        if (!tc_wait(tc_smem_u32(&bar_full[s]), (uint32_t)((it / C::STAGES) & 1))) { atomicExch(p.t.err, 4u); break; }
         tc_fence_after();
         const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
         bool dead = false;
@@ -367,7 +369,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       tc_fence_after();
       if (sub == 0 && lane == 0) {  // the MMAs of this group are complete: the stages they read may be refilled
         const int it_lo = b * p.bsteps / 4, it_hi = (b + cnt) * p.bsteps / 4;
-        for (int it = it_lo; it < it_hi; it++) tc_mbar_arrive(tc_smem_u32(&bar_empty[it % kI8Stages]));
+        for (int it = it_lo; it < it_hi; it++) tc_mbar_arrive(tc_smem_u32(&bar_empty[it % C::STAGES]));
       }
 #pragma unroll
       for (int q = 0; q < C::GROUP; q++) {
