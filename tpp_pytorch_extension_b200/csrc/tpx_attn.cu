@@ -276,7 +276,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_mma_kernel(AttnParams p)
   for (int i = 0; i < NT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};  // rows g and g + 8; l is this thread's share
 
-  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(attn_smem) + (MODE == 0 ? 0u : (uint32_t)warp * 2u * STAGE);
+  constexpr int NST = 2;  // stages per KV stream (a third stage per warp measured no faster: a warp's own arithmetic per block bounds decoding)
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(attn_smem) + (MODE == 0 ? 0u : (uint32_t)warp * (uint32_t)NST * STAGE);
   const int gtid = MODE == 0 ? threadIdx.x : lane;
   auto load_block = [&](int blk, int stage) {
     const uint32_t dst = sbase + (uint32_t)stage * STAGE;
@@ -295,16 +296,20 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_mma_kernel(AttnParams p)
   };
 
   const int first = MODE == 0 ? blk0 : blk0 + warp, step = MODE == 0 ? 1 : kAttnWarps;
-  if (first < blk1) load_block(first, 0);
+  // every round commits exactly one copy group (an empty one when the stream has run out), so "all but the NST-1
+  // newest groups are complete" always means "this round's block has landed"
+#pragma unroll
+  for (int s0 = 0; s0 < NST - 1; s0++) {
+    if (first + s0 * step < blk1) load_block(first + s0 * step, s0);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   int it = 0;
   for (int blk = first; blk < blk1; blk += step, it++) {
-    const int stage = it & 1;
-    if (blk + step < blk1) {
-      load_block(blk + step, stage ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
+    const int stage = it % NST;
+    if (blk + (NST - 1) * step < blk1) load_block(blk + (NST - 1) * step, (it + NST - 1) % NST);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    if (NST == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
+    else asm volatile("cp.async.wait_group 2;" ::: "memory");
     group_sync();
     if (blk * 32 < warp_kmax) {
       const uint32_t sk = sbase + (uint32_t)stage * STAGE, sv = sk + TILE;
@@ -543,7 +548,7 @@ static int attn_plan(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t key_
 template <int H, int MODE>
 static int attn_launch(const AttnParams& p, dim3 grid, cudaStream_t st) {
   constexpr int STAGE = 2 * 32 * (H * 2 + 16);
-  constexpr size_t smem = MODE == 0 ? 2 * STAGE : (size_t)kAttnWarps * 2 * STAGE;
+  constexpr size_t smem = MODE == 0 ? 2 * STAGE : (size_t)kAttnWarps * 2 * STAGE;  // two stages per stream, as in the kernel
   static_assert(MODE == 0 || smem >= (size_t)kAttnWarps * kAttnRows * H * sizeof(float), "merge area");
   static bool opted[16] = {};
   int dev = 0;
