@@ -170,7 +170,7 @@ __global__ void rope_kv_kernel(const uint16_t* __restrict__ qkv, const float* __
 // ---------------------------------------------------------------- attention
 // Query rows are consecutive (query position, group member) pairs of one (batch, kv head). Each warp keeps a
 // running (max, sum, fp32 output) for 16 rows over the KV blocks it visits. With more than one KV split a CTA
-// writes an un-normalised partial (max, sum, output) and a second kernel merges the splits (flash-decoding).
+// writes an un-normalised partial (max, sum, output); the split that arrives last merges them (flash-decoding).
 constexpr int kAttnWarps = 4;
 constexpr int kAttnRows = 16;
 
@@ -223,7 +223,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 //   share every KV block, copied once into shared memory (two stages, cp.async).
 // MODE 1 (decoding, at most 16 query rows): all warps work on the same 16 rows and take every fourth KV block of
 //   the CTA's split, each with its own two stages; the warps' (max, sum, output) are merged through shared memory,
-//   and with more than one KV split the CTA writes an un-normalised partial for attn_merge_kernel.
+//   and with more than one KV split the CTA writes an un-normalised partial that the last-arriving split merges.
 // Rows of a KV block are kept 16 bytes apart from a power-of-two pitch so that ldmatrix is conflict-free.
 template <int H, int MODE>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_mma_kernel(AttnParams p) {
@@ -279,15 +279,27 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_mma_kernel(AttnParams p)
   constexpr int NST = 2;  // stages per KV stream (a third stage per warp measured no faster: a warp's own arithmetic per block bounds decoding)
   const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(attn_smem) + (MODE == 0 ? 0u : (uint32_t)warp * (uint32_t)NST * STAGE);
   const int gtid = MODE == 0 ? threadIdx.x : lane;
+  // A copying thread keeps its chunk column and walks down the rows: thread j of the group copies chunk j % CPR of
+  // rows j / CPR, + GROUP / CPR, ...; per copy that is one add on each side.
+  constexpr int CPR = H / 8;            // 16-byte chunks per row
+  constexpr int RSTEP = GROUP / CPR;    // rows between a thread's consecutive copies
+  static_assert(GROUP % CPR == 0 && 32 % RSTEP == 0, "copy pattern");
+  const int cp_r0 = gtid / CPR, cp_c = gtid % CPR;
+  const uint32_t cp_dst0 = sbase + (uint32_t)(cp_r0 * PB + cp_c * 16);
+  const int64_t cp_src0 = (((int64_t)b * p.Nkv + n) * 32 + cp_r0) * H + cp_c * 8;
+  const int64_t blk_stride = (int64_t)p.B * p.Nkv * 32 * H;
+  // mask values can be read two at a time when every row of the mask starts on a 4-byte boundary
+  const bool am_pairs = p.am && (p.Spad & 1) == 0 && (reinterpret_cast<uintptr_t>(p.am) & 3) == 0;
   auto load_block = [&](int blk, int stage) {
-    const uint32_t dst = sbase + (uint32_t)stage * STAGE;
-    const int64_t boff = ((((int64_t)blk * p.B + b) * p.Nkv + n) * 32) * H;
-    constexpr int CPR = H / 8;  // 16-byte chunks per row
-    for (int i = gtid; i < 32 * CPR; i += GROUP) {
-      const int r = i / CPR, c = i % CPR;
-      const bool valid = blk * 32 + r < key_len;  // slots past the cached length may hold anything
-      cp_async_16(dst + r * PB + c * 16, p.kc + boff + r * H + c * 8, valid);
-      cp_async_16(dst + TILE + r * PB + c * 16, p.vc + boff + r * H + c * 8, valid);
+    const uint32_t dst = cp_dst0 + (uint32_t)stage * STAGE;
+    const uint16_t* ks = p.kc + (int64_t)blk * blk_stride + cp_src0;
+    const uint16_t* vs = p.vc + (int64_t)blk * blk_stride + cp_src0;
+    const int live = key_len - blk * 32 - cp_r0;  // rows r0 + k*RSTEP with k*RSTEP < live hold cached tokens
+#pragma unroll
+    for (int k = 0; k < 32 / RSTEP; k++) {
+      const bool valid = k * RSTEP < live;  // slots past the cached length may hold anything: zero-filled
+      cp_async_16(dst + k * RSTEP * PB, ks + k * RSTEP * H, valid);
+      cp_async_16(dst + TILE + k * RSTEP * PB, vs + k * RSTEP * H, valid);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -330,19 +342,40 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_mma_kernel(AttnParams p)
       // ---- scale, masks, running max
       float bm[2] = {-INFINITY, -INFINITY};
       const int sq_a = (row0 + g) / p.R, sq_b = (row0 + g + 8) / p.R;
+      const int kbase = blk * 32 + 2 * t;  // this thread's keys: kbase + 8*nt + {0, 1}
+      // a block wholly inside the cached length, the causal limit of every row of the warp and the mask needs no per-key tests
+      const bool plain = blk * 32 + 31 < key_len && (!p.causal || blk * 32 + 31 <= offset + row0 / p.R) && (!p.am || (blk * 32 + 31 < p.Spad && am_pairs));
+      if (plain) {
 #pragma unroll
-      for (int nt = 0; nt < 4; nt++) {
+        for (int nt = 0; nt < 4; nt++) {
+          float m0 = 0.0f, m1 = 0.0f;
+          if (p.am) {  // two consecutive bf16 mask values in one load (kbase is even)
+            const uint32_t mw = *reinterpret_cast<const uint32_t*>(p.am + (int64_t)b * p.Spad + kbase + 8 * nt);
+            m0 = bf16_bits_to_f32((uint16_t)(mw & 0xffff));
+            m1 = bf16_bits_to_f32((uint16_t)(mw >> 16));
+          }
+          sc[nt][0] = fmaf(sc[nt][0], p.scale, m0);
+          sc[nt][1] = fmaf(sc[nt][1], p.scale, m1);
+          sc[nt][2] = fmaf(sc[nt][2], p.scale, m0);
+          sc[nt][3] = fmaf(sc[nt][3], p.scale, m1);
+          bm[0] = fmaxf(bm[0], fmaxf(sc[nt][0], sc[nt][1]));
+          bm[1] = fmaxf(bm[1], fmaxf(sc[nt][2], sc[nt][3]));
+        }
+      } else {
 #pragma unroll
-        for (int e = 0; e < 2; e++) {
-          const int key = blk * 32 + nt * 8 + 2 * t + e;
-          const float madd = (p.am && key < p.Spad) ? bf16_bits_to_f32(p.am[(int64_t)b * p.Spad + key]) : 0.0f;
-          const bool in = key < key_len;
-          const bool va = in && (!p.causal || key <= offset + sq_a);
-          const bool vb = in && (!p.causal || key <= offset + sq_b);
-          sc[nt][e] = va ? sc[nt][e] * p.scale + madd : -INFINITY;
-          sc[nt][2 + e] = vb ? sc[nt][2 + e] * p.scale + madd : -INFINITY;
-          bm[0] = fmaxf(bm[0], sc[nt][e]);
-          bm[1] = fmaxf(bm[1], sc[nt][2 + e]);
+        for (int nt = 0; nt < 4; nt++) {
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            const int key = kbase + nt * 8 + e;
+            const float madd = (p.am && key < p.Spad) ? bf16_bits_to_f32(p.am[(int64_t)b * p.Spad + key]) : 0.0f;
+            const bool in = key < key_len;
+            const bool va = in && (!p.causal || key <= offset + sq_a);
+            const bool vb = in && (!p.causal || key <= offset + sq_b);
+            sc[nt][e] = va ? fmaf(sc[nt][e], p.scale, madd) : -INFINITY;
+            sc[nt][2 + e] = vb ? fmaf(sc[nt][2 + e], p.scale, madd) : -INFINITY;
+            bm[0] = fmaxf(bm[0], sc[nt][e]);
+            bm[1] = fmaxf(bm[1], sc[nt][2 + e]);
+          }
         }
       }
       float alpha[2];
@@ -526,8 +559,11 @@ extern "C" int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const in
   return TPX_OK;
 }
 
-// More than 16 query rows: 64 rows per CTA, no KV split. Up to 16 rows (decoding): one CTA row tile, the KV range
-// split while the grid is short of two CTAs per SM and every split keeps a block for each warp.
+// More than 16 query rows: 64 rows per CTA, no KV split. Up to 16 rows (decoding): one CTA row tile and the KV range
+// cut into the number of splits that minimises waves x (blocks per warp + fixed cost per CTA). One CTA is resident per
+// SM (its copy stages take most of the shared memory), so a grid a little over a multiple of the SM count pays for a
+// whole extra wave; the fixed cost (first copy's latency, query load, merge) is worth about two blocks, three when
+// partials go through global memory. TPX_ATTN_SPLITS overrides the choice.
 static int attn_plan(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t key_len, int* chunks, int* splits) {
   const int64_t rows = Sq * R;
   if (rows > kAttnRows) {
@@ -536,12 +572,25 @@ static int attn_plan(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t key_
     return 0;
   }
   *chunks = 1;
-  int64_t ctas = B * Nkv;
-  int nblocks = (int)((key_len + 31) / 32);
-  int s = 1;
-  int sms = sm_count();
-  while (ctas * s < 2 * sms && nblocks / (s * 2) >= kAttnWarps && s < 64) s *= 2;
-  *splits = s;
+  const int64_t ctas = B * Nkv;
+  const int nblocks = (int)((key_len + 31) / 32);
+  const int sms = sm_count();
+  static const int forced = [] { const char* e = getenv("TPX_ATTN_SPLITS"); return e ? atoi(e) : 0; }();
+  int best = 1;
+  if (forced > 0) {
+    best = forced < 64 ? forced : 64;
+    while (best > 1 && nblocks / best < 1) best--;
+  } else {
+    double best_cost = 1e30;
+    for (int s = 1; s <= 64; s++) {
+      if (s > 1 && nblocks / s < kAttnWarps) break;  // every warp of every split keeps a block
+      const int64_t waves = (ctas * s + sms - 1) / sms;
+      const int per_warp = ((nblocks + s - 1) / s + kAttnWarps - 1) / kAttnWarps;
+      const double cost = (double)waves * (per_warp + (s > 1 ? 3 : 2));
+      if (cost < best_cost * 0.97) { best_cost = cost; best = s; }  // ties go to fewer splits
+    }
+  }
+  *splits = best;
   return 0;
 }
 
