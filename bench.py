@@ -338,8 +338,8 @@ def run_ours(args):
                         "frac_of_bf16_peak": pre_flops / (pre_ms * 1e-3) / 1e12 / pk["bf16_tflops"] if pre_ms > 0 else None,
                         "peak_src": pk["src"]},
             "roofline": {"bound": "hbm",
-                         "kernel": f"MXFP4 gate/up pair GEMM, M={SWEEP[dom]} (tcgen05 kind::mxf8f6f4; qlinear_tcw_kernel for M <= 64 "
-                                   f"unless TPX_TC_WIDE=0, else qlinear_tc_kernel)"
+                         "kernel": f"MXFP4 gate/up pair GEMM, M={SWEEP[dom]} (tcgen05: qlinear_tc4_kernel, kind::mxf4, for M <= 32; "
+                                   f"qlinear_tcw_kernel, kind::mxf8f6f4, for M <= 64; else qlinear_tc_kernel)"
                                    if F.mxfp4_path() == "tc" else f"qlinear_stream gate/up pair, M={SWEEP[dom]}",
                          "achieved": dom_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": dom_gbs / pk["hbm_gbs"],
                          "peak_src": pk["src"], "traffic": NCU_TRAFFIC.get(SWEEP[dom]),

@@ -12,12 +12,14 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-2
 
 
-@pytest.fixture(autouse=True, params=["tc", "tc_wide", "stream"])
+@pytest.fixture(autouse=True, params=["tc", "tc_wide", "tc_f4", "stream"])
 def mxfp4_path(request, monkeypatch):
     """Every case runs on each MXFP4 kernel family: the tcgen05 kernel with the weights on the 128-row side of the MMA,
-    the tcgen05 kernel with the weights on the wide side (up to 64 tokens), and the mma.sync streaming kernel."""
+    the tcgen05 kernel with the weights on the wide side (up to 64 tokens), the packed-fp4 tcgen05 kernel (up to 32
+    tokens) and the mma.sync streaming kernel."""
     monkeypatch.setenv("TPX_MXFP4_PATH", "stream" if request.param == "stream" else "tc")
     monkeypatch.setenv("TPX_TC_WIDE", "1" if request.param == "tc_wide" else "0")
+    monkeypatch.setenv("TPX_TC_F4", "1" if request.param == "tc_f4" else "0")
     # int8 weights: the tcgen05 kind::i8 kernel (reference arithmetic) with the tensor-core families, else the streaming kernel
     monkeypatch.setenv("TPX_INT8_PATH", "stream" if request.param == "stream" else "tc")
     return request.param

@@ -79,7 +79,7 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
             raise _lib.TpxError("gate/up weights must have the same shape and quantization")
         wq, sfa = w.packed_tc(w2)
         import os
-        key = ("tc", M, N, K, w2 is not None, os.environ.get("TPX_TC_WIDE", "auto"))
+        key = ("tc", M, N, K, w2 is not None, os.environ.get("TPX_TC_WIDE", "auto"), os.environ.get("TPX_TC_F4", "auto"))
         nb = _SCRATCH_BYTES.get(key)
         if nb is None:
             nb = _SCRATCH_BYTES[key] = L.tpx_qlinear_mxfp4_tc_scratch_bytes(M, N, K, int(w2 is not None))

@@ -715,6 +715,21 @@ int tc_make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64
   return TPX_OK;
 }
 
+// 2-D byte tensor of `rows` rows of 64 bytes, box = 64 bytes x box_rows, 64-byte swizzle (packed 4-bit operands).
+int tc_make_map64(CUtensorMap* m, const void* base, uint64_t rows, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  TPX_REQUIRE(fn, TPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[2] = {64, rows};
+  cuuint64_t gstr[1] = {64};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TPX_REQUIRE(r == CUDA_SUCCESS, TPX_ERR_CUDA, "cuTensorMapEncodeTiled (64-byte rows) failed with %d (rows=%llu box_rows=%u)", (int)r,
+              (unsigned long long)rows, box_rows);
+  return TPX_OK;
+}
+
 int tc_padded_ks(int64_t K, bool pair) {
   int ks = (int)((K + 127) / 128);
   int m = pair ? 2 : 4;
@@ -846,6 +861,22 @@ static int tc_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams&
   return TPX_OK;
 }
 
+int tc_launch_fixup(bool dual, const TcParams& p, int TOK, int grid, cudaStream_t st) {
+  cudaLaunchConfig_t c2 = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  c2.gridDim = dim3((unsigned)(p.TN * p.TM), (unsigned)(TOK / 16));
+  c2.blockDim = dim3(128);
+  c2.stream = st;
+  c2.attrs = attr;
+  c2.numAttrs = 1;
+  count_launch();
+  if (dual) TPX_CUDA_OK(cudaLaunchKernelEx(&c2, tc_fixup_kernel<true>, p, TOK, grid));
+  else TPX_CUDA_OK(cudaLaunchKernelEx(&c2, tc_fixup_kernel<false>, p, TOK, grid));
+  return TPX_OK;
+}
+
 }  // namespace tpx
 
 using namespace tpx;
@@ -892,18 +923,34 @@ static bool tc_wide(int64_t M, int64_t N, int64_t K, bool pair) {
   return M <= 16 && T * 2 <= sms;  // few tiles: clusters split K in either kernel, the wide one needs fewer MMA cycles
 }
 
-static size_t tc_scratch_need(int64_t M, int64_t N, int64_t K, bool pair, bool wide) {
-  return wide ? tcw_scratch_bytes(M, N, K, pair) : tc_plan(M, N, K, pair).total;
+// Kernel family for a call: 0 = weights on the 128-row side (all M), 1 = weights on the N side (M <= 64),
+// 2 = packed-fp4 operands (M <= 32). Default where every CTA owns whole tiles (the gate/up pair of a decode step:
+// 26.6 against 31.0 us at M = 8, 30.1 against 33.3 us at M = 32); shapes with few tiles, which cut K inside a cluster,
+// measured no faster (down projection: 25.6 against 25.6 us at M = 8, 29.5 against 27.7 us at M = 32) and stay on
+// family 1. TPX_TC_F4=1 selects it for every M <= 32, TPX_TC_F4=0 never.
+static int tc_kind(int64_t M, int64_t N, int64_t K, bool pair) {
+  if (M <= 32) {
+    const char* e = getenv("TPX_TC_F4");
+    const long long T = (N + 127) / 128 * ((M + (M <= 16 ? 15 : 31)) / (M <= 16 ? 16 : 32));
+    const int sms = sm_count();
+    const bool whole = (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
+    if (e ? atoi(e) != 0 : whole) return 2;
+  }
+  return tc_wide(M, N, K, pair) ? 1 : 0;
+}
+
+static size_t tc_scratch_need(int64_t M, int64_t N, int64_t K, bool pair, int kind) {
+  return kind == 2 ? tc4_scratch_bytes(M, N, K, pair) : kind == 1 ? tcw_scratch_bytes(M, N, K, pair) : tc_plan(M, N, K, pair).total;
 }
 
 extern "C" size_t tpx_qlinear_mxfp4_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int pair) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  return tc_scratch_need(M, N, K, pair != 0, tc_wide(M, N, K, pair != 0));
+  return tc_scratch_need(M, N, K, pair != 0, tc_kind(M, N, K, pair != 0));
 }
 
 static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M, int64_t N, int64_t K,
                   const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y,
-                  void* scratch, size_t scratch_bytes, void* stream, bool wide, const TcNorm* norm = nullptr) {
+                  void* scratch, size_t scratch_bytes, void* stream, int kind, const TcNorm* norm = nullptr) {
   TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear_mxfp4_tc: bad shape");
   if (M == 0) return TPX_OK;
   TPX_REQUIRE(wq && sfa && x && y, TPX_ERR_ARG, "qlinear_mxfp4_tc: null pointer");
@@ -913,7 +960,16 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   TPX_REQUIRE(((uintptr_t)wq & 31) == 0 && ((uintptr_t)sfa & 15) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)scratch & 255) == 0,
               TPX_ERR_ARG, "qlinear_mxfp4_tc: misaligned pointer");
   const bool dual = pair != 0;
-  if (wide) {
+  if (kind == 2) {
+    TcParams b = {};
+    b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act; b.tl = g_tc_timeline;
+    { const char* e = getenv("TPX_TC_DBG"); b.dbg = e ? atoi(e) : 0; }
+    // no L2 prefetch ahead of the stages: this kernel's stages already hold 160-210 KB of packed weights per SM, and
+    // prefetches issued at the start delay the first stage (gate/up, M = 8: 26.5 us without, 29.2 us with 8 units ahead)
+    { const char* e = getenv("TPX_TC_PF"); b.pf = e ? atoi(e) : 0; }
+    return tc4_run(wq, sfa, dual, x, M, N, K, b, scratch, scratch_bytes, (cudaStream_t)stream, norm);
+  }
+  if (kind == 1) {
     TcParams b = {};
     b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act; b.tl = g_tc_timeline;
     { const char* e = getenv("TPX_TC_DBG"); b.dbg = e ? atoi(e) : 0; }
@@ -976,7 +1032,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
 extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M, int64_t N,
                                     int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
                                     float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream) {
-  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, tc_wide(M, N, K, pair != 0));
+  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, tc_kind(M, N, K, pair != 0));
 }
 
 extern "C" int tpx_rmsnorm_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, const void* gamma,
@@ -985,7 +1041,7 @@ extern "C" int tpx_rmsnorm_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sf
                                             size_t scratch_bytes, void* stream) {
   TPX_REQUIRE(gamma, TPX_ERR_ARG, "rmsnorm_qlinear_mxfp4_tc: null gamma");
   TcNorm nm = {gamma, gamma_is_f32, eps};
-  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, tc_wide(M, N, K, pair != 0), &nm);
+  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, tc_kind(M, N, K, pair != 0), &nm);
 }
 
 // ---------------------------------------------------------------- variant that allocates nothing
@@ -1021,8 +1077,8 @@ extern "C" int tpx_qlinear_mxfp4_tc_static(const uint8_t* wq, const uint8_t* sfa
   TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear_mxfp4_tc_static: bad shape");
   if (M == 0) return TPX_OK;
   // the kernel whose scratch fits the array: the wide one's partial slots grow with the token count
-  bool wide = tc_wide(M, N, K, pair != 0);
-  if (wide && tc_scratch_need(M, N, K, pair != 0, true) > kStaticScratchBytes) wide = false;
+  int wide = tc_kind(M, N, K, pair != 0);
+  if (wide && tc_scratch_need(M, N, K, pair != 0, wide) > kStaticScratchBytes) wide = 0;
   const size_t need = tc_scratch_need(M, N, K, pair != 0, wide);
   TPX_REQUIRE(need <= kStaticScratchBytes, TPX_ERR_SCRATCH,
               "qlinear_mxfp4_tc_static: M=%ld N=%ld K=%ld needs %zu bytes of scratch, the built-in array holds %zu; "

@@ -122,6 +122,16 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
       : "memory");
 }
+// Both operands packed E2M1 (two codes per byte in shared memory), K = 64 per instruction, one UE8M0 scale per 32 k:
+// the instruction reads two consecutive scale bytes per row, selected by scale-factor id 0 or 2.
+__device__ __forceinline__ void tc_mma_f4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                          uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+      "  tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p; }" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
 // 32 rows x 16 bytes, rows 16 bytes apart, no swizzle: 8-row core matrices 128 bytes apart.
 __device__ __forceinline__ uint64_t tc_sf_desc(uint32_t saddr) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(128 >> 4) << 32) | (1ull << 46);
@@ -147,6 +157,11 @@ __device__ __forceinline__ void tc_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
 // K-major operand tile, 128-byte rows, 128-byte swizzle: 8-row groups are 1024 bytes apart.
 __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// K-major operand tile of 64-byte rows (128 packed 4-bit codes), 64-byte swizzle: 8-row groups are 512 bytes apart.
+__device__ __forceinline__ uint64_t tc_smem_desc64(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(512 >> 4) << 32) | (1ull << 46) | (4ull << 61);
 }
 
 // The same tile read with its 8-row groups `sbo` bytes apart instead of 1024: consecutive groups then overlap in
@@ -207,6 +222,7 @@ __device__ __forceinline__ void tc_finish16(const TcParams& p, int tok0, int n, 
 
 // host helpers shared by the tensor-core linears
 int tc_make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows);
+int tc_make_map64(CUtensorMap* m, const void* base, uint64_t rows, uint32_t box_rows);
 int tc_padded_ks(int64_t K, bool pair);
 struct TcNorm {  // optional RMSNorm applied to x on its way into the split (null gamma: none)
   const void* gamma;
@@ -215,6 +231,11 @@ struct TcNorm {  // optional RMSNorm applied to x on its way into the split (nul
 };
 int tc_launch_split(const uint16_t* x, int M, int K, int Mpad, int KS, int TOK, int UKS, int rowmap, uint8_t* terms, uint8_t* sfb,
                     cudaStream_t st, const TcNorm* norm = nullptr);
+int tc_launch_fixup(bool dual, const TcParams& p, int TOK, int grid, cudaStream_t st);
+// packed-fp4 variant for up to 32 tokens (activations as four E2M1 terms): tpx_qlinear_tc4.cu
+size_t tc4_scratch_bytes(int64_t M, int64_t N, int64_t K, bool pair);
+int tc4_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x, int64_t M, int64_t N, int64_t K, const TcParams& base,
+            void* scratch, size_t scratch_bytes, cudaStream_t st, const TcNorm* norm = nullptr);
 // decode-shaped variant (tokens on the M side of the MMA): tpx_qlinear_tcw.cu
 size_t tcw_scratch_bytes(int64_t M, int64_t N, int64_t K, bool pair);
 int tcw_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x, int64_t M, int64_t N, int64_t K, const TcParams& base,
