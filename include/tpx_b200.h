@@ -184,6 +184,11 @@ int tpx_qlinear_qint8_tc(const int8_t* wq, const float* swT, const uint16_t* x, 
 int tpx_rmsnorm(const uint16_t* x, const void* gamma, int gamma_is_f32, float eps, int64_t rows, int64_t D,
                 uint16_t* y, void* stream);
 
+/* Greedy sampling: out[r] = index of the largest of x[r][0..n), the first among equals, NaN above every number, as
+ * torch.argmax(-1) of the head's logits returns it (the reference drives HF generate with --greedy,
+ * examples/llm/run_generation.py:337-339). x bf16 [rows][n], out int64 [rows].                          */
+int tpx_argmax_bf16(const uint16_t* x, int64_t rows, int64_t n, int64_t* out, void* stream);
+
 /* RoPE + KV-cache append in one pass. Replaces apply_rotary_pos_emb_llama on q and k
  * (src/csrc/llm/fused_llm_infer.cpp:206-253), the q/k/v views and the q permute of self_mha (:563-584) and
  * TppCache::update -> LayerCache::update (src/csrc/llm/attn.h:197-221, KVLayout_BNSH src/csrc/llm/attn.cpp:389-463).

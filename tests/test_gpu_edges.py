@@ -93,3 +93,21 @@ def test_many_tokens_fused_norm_and_full_cache(cuda):
     assert O.rel_err(to_host_bits(out), ref) <= TOL
     assert TppCache().get_seq_length() == 0
     assert_no_kernel_error()
+
+
+def test_argmax_rows_matches_torch(cuda):
+    """Greedy pick: the first of equal maxima, NaN above every number, ragged row lengths (rows not 16-byte aligned)."""
+    import torch
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    g = torch.Generator(device="cpu").manual_seed(5)
+    for rows, n in [(1, 128256), (16, 128256), (3, 1001), (2, 7), (5, 32000)]:
+        x = torch.randn(rows, n, generator=g).bfloat16()  # bf16 rounding makes equal maxima common
+        x[0, n // 2] = x[0].max()                          # and one certain tie
+        y = F.argmax_rows(x.to(cuda))
+        assert torch.equal(y.cpu(), x.float().argmax(-1))
+    x = torch.randn(2, 4096, generator=g).bfloat16()
+    x[1, 100] = float("nan")
+    x[1, 3000] = float("nan")
+    y = F.argmax_rows(x.to(cuda))
+    assert y[1].item() == 100 and y[0].item() == int(x[0].float().argmax())
+    assert F.argmax_rows(torch.empty(0, 16, dtype=torch.bfloat16, device=cuda)).shape == (0,)

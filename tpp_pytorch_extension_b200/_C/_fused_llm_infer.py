@@ -206,6 +206,19 @@ def rms_norm(x, gamma, eps):
     return y
 
 
+def argmax_rows(x):
+    """Greedy pick over the last dimension of bf16 logits [..., n] -> int64 [...], torch.argmax semantics (first of
+    equal maxima). One launch of a row-per-CTA kernel instead of the library's generic reduction."""
+    _lib.require_cuda(x, "logits")
+    if x.dtype != torch.bfloat16:
+        raise _lib.TpxError("argmax_rows: bf16 logits expected")
+    x = x.contiguous()
+    n = x.shape[-1]
+    out = torch.empty(x.shape[:-1], dtype=torch.int64, device=x.device)
+    _lib.check(_lib.lib().tpx_argmax_bf16(x.data_ptr(), x.numel() // n if n else 0, n, out.data_ptr(), _lib.stream()))
+    return out
+
+
 _pg = None
 
 

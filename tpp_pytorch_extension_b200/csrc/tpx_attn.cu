@@ -521,9 +521,75 @@ __global__ void invert_mask_kernel(const uint16_t* __restrict__ mask, int B, int
   out[idx] = v;
 }
 
+// ---------------------------------------------------------------- greedy sampling
+// Index of the largest value of every row of x[rows][n] (bf16), the first one among equals and NaN above everything, as
+// torch.argmax over the last dimension returns it. One CTA per row: the head's logits of a decode step are a few
+// rows of ~10^5 values, read once with 16-byte loads.
+constexpr int kArgmaxThreads = 1024;
+__device__ __forceinline__ bool argmax_better(float v, long long i, float bv, long long bi) {
+  const bool vn = v != v, bn = bv != bv;
+  if (vn != bn) return vn;
+  if (!vn && v != bv) return v > bv;
+  return i < bi;
+}
+__global__ void __launch_bounds__(kArgmaxThreads) argmax_rows_kernel(const uint16_t* __restrict__ x, long long n, long long* __restrict__ out) {
+  __shared__ float sv[kArgmaxThreads / 32];
+  __shared__ long long si[kArgmaxThreads / 32];
+  pdl_trigger();
+  pdl_wait();
+  const uint16_t* row = x + (size_t)blockIdx.x * n;
+  float bv = -INFINITY;
+  long long bi = 0x7fffffffffffffffLL;
+  // the row starts on an 8-element boundary when both the base and n allow 16-byte loads
+  const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
+  const long long nv = vec ? n / 8 : 0;
+#pragma unroll 4
+  for (long long i = threadIdx.x; i < nv; i += kArgmaxThreads) {
+    const uint4 w = __ldg(reinterpret_cast<const uint4*>(row) + i);
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float a = bf16_bits_to_f32((uint16_t)(ww[j] & 0xffff)), b = bf16_bits_to_f32((uint16_t)(ww[j] >> 16));
+      if (argmax_better(a, i * 8 + 2 * j, bv, bi)) { bv = a; bi = i * 8 + 2 * j; }
+      if (argmax_better(b, i * 8 + 2 * j + 1, bv, bi)) { bv = b; bi = i * 8 + 2 * j + 1; }
+    }
+  }
+  for (long long i = nv * 8 + threadIdx.x; i < n; i += kArgmaxThreads) {
+    const float a = bf16_bits_to_f32(row[i]);
+    if (argmax_better(a, i, bv, bi)) { bv = a; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (argmax_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    bv = sv[threadIdx.x]; bi = si[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (argmax_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = bi;
+  }
+}
+
 }  // namespace tpx
 
 using namespace tpx;
+
+extern "C" int tpx_argmax_bf16(const uint16_t* x, int64_t rows, int64_t n, int64_t* out, void* stream) {
+  TPX_REQUIRE(rows >= 0 && n > 0, TPX_ERR_ARG, "argmax: bad shape");
+  if (rows == 0) return TPX_OK;
+  TPX_REQUIRE(x && out, TPX_ERR_ARG, "argmax: null pointer");
+  TPX_CUDA_OK(launch_pdl(argmax_rows_kernel, dim3((unsigned)rows), dim3(kArgmaxThreads), 0, (cudaStream_t)stream, x, (long long)n,
+                         reinterpret_cast<long long*>(out)));
+  return TPX_OK;
+}
 
 extern "C" int tpx_rmsnorm(const uint16_t* x, const void* gamma, int gamma_is_f32, float eps, int64_t rows, int64_t D,
                            uint16_t* y, void* stream) {

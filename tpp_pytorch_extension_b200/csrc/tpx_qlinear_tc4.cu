@@ -21,10 +21,8 @@ namespace tpx {
 // ---------------------------------------------------------------- activation split into four E2M1 terms
 //   terms [TM][KU][UKS][4 terms][TOK rows][64 bytes]   (one k step of one term = a TOK x 64-byte operand tile,
 //         low nibble = even k)
-//   sfb   [TM][KU][ceil(UKS*4*TOK/128)][512]   scale bytes of the 4*TOK MMA columns (column t*TOK + r for term t of
-//         token r) of the unit's k steps, packed: with c' = kk*4*TOK + c for column c of k step kk, byte
-//         (c'%32)*16 + ((c'%128)/32)*4 + j of block c'/128, j the 32-wide block of the k step. With 16 tokens the
-//         two k steps of a unit share one block (one shared -> tensor memory copy instead of two).
+//   sfb   [TM][KU][UKS][512]   scale bytes of the 4*TOK MMA columns (column t*TOK + r for term t of token r):
+//         byte (c%32)*16 + (c/32)*4 + j for column c and 32-wide block j of the k step
 // One thread owns 8 consecutive elements; the four threads of a 32-wide block share the scale.
 __device__ __forceinline__ void split4_emit(const float (&f)[8], bool store, int tok, int i, int KS, int TOK, int UKS,
                                             uint8_t* __restrict__ terms, uint8_t* __restrict__ sfb) {
@@ -82,13 +80,12 @@ __device__ __forceinline__ void split4_emit(const float (&f)[8], bool store, int
   for (int t = 0; t < 4; t++)
     *reinterpret_cast<uint32_t*>(terms + ((step * 4 + t) * TOK + row) * 64 + chunk * 4) = packed[t];
   if ((chunk & 3) == 0) {
-    const int actb = (UKS * 4 * TOK + 127) / 128;  // activation scale blocks per unit
-    uint8_t* unit = sfb + ((size_t)tm * KU + ks / UKS) * actb * 512;
+    uint8_t* blk = sfb + step * 512;
     const int shift[4] = {0, 2, 5, 8};
 #pragma unroll
     for (int t = 0; t < 4; t++) {
-      const int c = (ks % UKS) * 4 * TOK + t * TOK + row;
-      unit[(c / 128) * 512 + (c % 32) * 16 + ((c % 128) / 32) * 4 + j] = (uint8_t)(e + 127 - shift[t]);
+      const int c = t * TOK + row;
+      blk[(c % 32) * 16 + (c / 32) * 4 + j] = (uint8_t)(e + 127 - shift[t]);
     }
   }
 }
@@ -208,8 +205,9 @@ struct Tc4Cfg {
   static constexpr int X_ROWS = UKS * 4 * TOK;         // rows of 64 bytes of the four terms of the unit
   static constexpr int X_BOX = X_ROWS > 256 ? 256 : X_ROWS;
   static constexpr int NCOL = 4 * TOK;                 // MMA N: term 1 columns, term 2 columns, ...
-  static constexpr int ACT_BLOCKS = (UKS * NCOL + 127) / 128;  // activation scale blocks of the unit (k steps packed)
-  static constexpr int SF_BLOCKS = UKS * NW + ACT_BLOCKS;      // weight blocks first, then the activation blocks
+  // weight blocks first, then one activation block per k step (packing the two k steps' 64 columns of a 16-token unit
+  // into one block saves a copy per unit but measured slower end to end: 2.94 against 2.84 ms/token, Llama-3-8B batch 1)
+  static constexpr int SF_BLOCKS = UKS * (NW + 1);
   static constexpr int RAW = A_TILES * A_BYTES + X_ROWS * 64 + SF_BLOCKS * 512;
   static constexpr int STAGE_BYTES = (RAW + 1023) / 1024 * 1024;
   static constexpr int TX = RAW;
@@ -303,8 +301,7 @@ qlinear_tc4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const int xrow = (tm * p.KS + ks) * C::X_ROWS;
 #pragma unroll
         for (int r = 0; r < C::X_ROWS / C::X_BOX; r++) tc_tma_2d(sb + r * C::X_BOX * 64, &tmX, 0, xrow + r * C::X_BOX, bar);
-        tc_bulk_g2s(sb + C::X_ROWS * 64 + C::A_TILES * 512, p.sfb + ((size_t)tm * p.KS + ks) * C::ACT_BLOCKS * 512,
-                    C::ACT_BLOCKS * 512, bar);
+        tc_bulk_g2s(sb + C::X_ROWS * 64 + C::A_TILES * 512, p.sfb + ((size_t)tm * p.KS + ks) * UKS * 512, UKS * 512, bar);
       };
       auto prefetch_w = [&](int tn, int ks) {  // into L2, ahead of the stages
         const int wtile = (tn * p.KS + ks) * C::A_TILES;
@@ -393,7 +390,7 @@ qlinear_tc4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
               const uint64_t adesc = tc_smem_desc64(st + (kk * C::NW + d) * C::A_BYTES) + (uint64_t)(2 * j);
               const uint32_t acc = (fresh && kk == 0 && j == 0) ? 0u : 1u;
               tc_mma_f4(tmem + d * C::NCOL, adesc, bdesc, idesc, (sf_t + (kk * C::NW + d) * 4) | (sfid << 30),
-                        (sf_t + C::A_TILES * 4 + (kk * C::NCOL) / 32) | (sfid << 30), acc);
+                        (sf_t + (C::A_TILES + kk) * 4) | (sfid << 30), acc);
             }
           }
         }
@@ -578,7 +575,7 @@ static Tc4Plan tc4_plan(int64_t M, int64_t N, int64_t K, bool pair) {
   size_t o = kTcCounterBytes;
   auto bump = [&](size_t bytes) { size_t r = o; o += (bytes + 1023) & ~(size_t)1023; return r; };
   pl.off_terms = bump((size_t)pl.Mpad * pl.KS * 4 * 64);
-  pl.off_sfb = bump((size_t)pl.TM * pl.KU * ((pl.uks * 4 * pl.tok + 127) / 128) * 512);
+  pl.off_sfb = bump((size_t)pl.TM * pl.KS * 512);
   pl.off_partial = bump((size_t)pl.grid * 2 * (pair ? 2 : 1) * pl.tok * 128 * sizeof(float));
   pl.total = o;
   return pl;

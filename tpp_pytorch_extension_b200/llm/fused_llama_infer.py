@@ -130,7 +130,7 @@ class LlamaRunner(torch.nn.Module):
         dev = input_ids.device
         mask = attention_mask if attention_mask is not None else torch.ones_like(input_ids)
         logits, cache = self.forward(input_ids, mask, None, cache)
-        tok = logits[:, -1].argmax(-1, keepdim=True)
+        tok = fused_llm_cpp.argmax_rows(logits[:, -1]).unsqueeze(-1)
         outs = [input_ids, tok.clone()]
         steps = max_new_tokens - 1
         if steps <= 0:
@@ -149,7 +149,7 @@ class LlamaRunner(torch.nn.Module):
             for layer in self.layers:
                 hs = layer.forward([hs, am, pos], cpp, True, dev_len=dev_len)[0]
             lg = self._head(hs)
-            tok.copy_(lg[:, -1].argmax(-1, keepdim=True))
+            tok.copy_(fused_llm_cpp.argmax_rows(lg[:, -1]).unsqueeze(-1))
             pos.add_(1)
             dev_len.add_(1)
 
