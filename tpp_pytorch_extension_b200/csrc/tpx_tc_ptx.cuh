@@ -31,7 +31,8 @@ struct TcParams {
   unsigned long long* tl;  // optional per-CTA timeline (8 globaltimer stamps each), null in normal use
   int cluster;          // CTAs per thread-block cluster that share one output tile along K (1: none)
   int pf;               // units prefetched into L2 ahead of the shared-memory stages
-  int dbg;              // debug knobs for timing experiments: 1 = skip MMAs, 2 = skip weight copies, 128 = skip activation copies
+  int dbg;              // debug knobs for timing experiments (results are then wrong): 1 = skip MMAs, 2 = skip weight copies,
+                        // 128 = skip activation copies; packed-fp4 kernel: 16 = skip scale-factor copies, 32 = MMA thread issues them
 };
 
 __device__ __forceinline__ void tc_stamp(const TcParams& p, int slot) {
