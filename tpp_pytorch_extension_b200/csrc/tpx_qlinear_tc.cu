@@ -1014,7 +1014,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = pl.TM; p.act = act; p.whole_tiles = pl.whole_tiles; p.cluster = pl.cluster; p.tl = g_tc_timeline;
   { const char* e = getenv("TPX_TC_DBG"); p.dbg = e ? atoi(e) : 0; }
-  { const char* e = getenv("TPX_TC_PF"); p.pf = e ? atoi(e) : (M <= 64 ? 0 : 6); }  // decode shapes: see above
+  { const char* e = getenv("TPX_TC_PF"); p.pf = e ? atoi(e) : 0; }  // off, see above (prefill shapes: 842 against 838 TFLOP/s)
   { const char* e = getenv("TPX_TC_CLUSTER"); if (e && atoi(e) == 0) p.cluster = 1; }
   if (dual) {
     switch (pl.tok) {
