@@ -215,3 +215,23 @@ def test_config1_shape_int8_silu(cuda):
     y = run_fc(x, q, cuda, bias=to_dev_bf16(bias, cuda), act="silu")
     ref = O.qlinear(x, wd, bias=bias, act=O.ACT_SILU)
     assert O.rel_err(y, ref) <= TOL
+
+
+@pytest.mark.parametrize("M", [5, 20])
+def test_tiles_cut_between_ctas(cuda, M):
+    """76 output tiles: more than half the SMs (no cluster per tile), fewer than 70 % of them (no whole tiles), so
+    the (tile, k unit) list is cut into equal ranges and partial tiles are completed by the fix-up pass; plain
+    linear and gate/up pair, twice (the arrival counters must come back to zero)."""
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    rng = np.random.default_rng(300 + M)
+    N, K = 9728, 512
+    q, wd, _ = make_qweight(rng, N, K, "mxfp4", cuda)
+    q2, wd2, _ = make_qweight(rng, N, K, "mxfp4", cuda)
+    x = O.randn_bf16(rng, (M, K))
+    ref = O.qlinear(x, wd)
+    ref_pair = O.gate_up(x, wd, wd2)
+    for _ in range(2):
+        assert O.rel_err(run_fc(x, q, cuda), ref) <= 1e-2
+        y = F.fc_gate_up(to_dev_bf16(x, cuda), q, q2)
+        assert_no_kernel_error()
+        assert O.rel_err(to_host_bits(y), ref_pair) <= TOL

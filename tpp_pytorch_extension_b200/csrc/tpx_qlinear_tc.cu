@@ -925,13 +925,16 @@ static bool tc_wide(int64_t M, int64_t N, int64_t K, bool pair) {
 
 // Kernel family for a call: 0 = weights on the 128-row side (all M), 1 = weights on the N side (M <= 64),
 // 2 = packed-fp4 operands (M <= 32). Default where every CTA owns whole tiles (the gate/up pair of a decode step:
-// 26.6 against 31.0 us at M = 8, 30.1 against 33.3 us at M = 32); shapes with few tiles, which cut K inside a cluster,
-// measured no faster (down projection: 25.6 against 25.6 us at M = 8, 29.5 against 27.7 us at M = 32) and stay on
-// family 1. TPX_TC_F4=1 selects it for every M <= 32, TPX_TC_F4=0 never.
+// 20.0 against 24.3 us at M = 8, 23.2 against 26.2 us at M = 32, launches back to back; Llama-3-8B decodes at 2.81
+// against 2.94 ms/token). Not where tiles are cut between CTAs with a fix-up pass: single launches measured faster up
+// to 16 tokens (gate/up pair of 11008 features: 22.2 against 24.3 us at M = 8) but a whole model slower (Llama-2-7B,
+// its q/k/v and gate/up linears on this family: 2.76 against 2.66 ms/token). Not where few tiles cut K inside a
+// cluster either (down projection: 19.4 against 18.7 us at M = 8). TPX_TC_F4=1 selects it for every M <= 32,
+// TPX_TC_F4=0 never.
 static int tc_kind(int64_t M, int64_t N, int64_t K, bool pair) {
   if (M <= 32) {
     const char* e = getenv("TPX_TC_F4");
-    const long long T = (N + 127) / 128 * ((M + (M <= 16 ? 15 : 31)) / (M <= 16 ? 16 : 32));
+    const long long T = (N + 127) / 128;  // one token tile up to 32 tokens
     const int sms = sm_count();
     const bool whole = (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
     if (e ? atoi(e) != 0 : whole) return 2;
