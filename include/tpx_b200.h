@@ -44,9 +44,17 @@ int tpx_version(void);
 const char* tpx_last_error(void);
 /* number of SMs of the current device (used by callers to size scratch) */
 int tpx_sm_count(void);
+/* The kernel-selection switches (TPX_TC_WHOLE, TPX_TC_WIDE, TPX_TC_F4, TPX_TC_CLUSTER, TPX_TC_PF, TPX_ATTN_SPLITS) are
+ * read from the environment once, at first use; this call reads them again. None of them changes a result; they exist
+ * so that tests can run every kernel family. No counterpart in the reference.                                     */
+void tpx_reload_options(void);
 /* Number of kernels of the linear / norm / rope / attention path this library has launched so far in this process
  * (host-side tally, for benchmarks that report their launch count). No counterpart in the reference.          */
 unsigned long long tpx_launch_count(void);
+
+/* out256[b] = the two fp16 values (low half = low nibble) that the GPU's own E2M1 decoder makes of byte b: the element
+ * table of the MXFP4 codes (src/csrc/qtypes.cpp:42-57) as this hardware implements it. 256 words of device memory. */
+int tpx_e2m1_pair_table(uint32_t* out256, void* stream);
 
 /* ---------------------------------------------------------------- quantize / remap
  * Replaces _C._qtype.remap_and_quantize_mxfp4 (src/csrc/qtypes.cpp:783-864, pybind :1086).
@@ -60,12 +68,15 @@ int tpx_remap_and_quantize_mxfp4(const uint16_t* blocked, int64_t K1, int64_t C1
 
 /* Replaces _C._qtype.remap_and_quantize_qint8 (src/csrc/qtypes.cpp:866-932, pybind :1087).
  * block_size plays the role of the QINT8_BLOCK_SIZE environment variable (:28), and is
- * adjusted downwards as the reference does when it does not divide K (:878-889); the block
- * size actually used is returned through *block_size_used.
+ * adjusted as the reference does when it does not divide K (:878-889: the largest power of two
+ * from 4096 down to 64 below the request that divides K, else the blocked tensor's own C2*C3);
+ * the block size actually used, B, is returned through *block_size_used. block_size must be a
+ * positive multiple of 4. scales_capacity is the number of floats `scales` can hold; the call
+ * refuses (TPX_ERR_ARG) when B needs more than that.
  * out: q int8 [K1][C/B][B/4][K2][4], scales fp32 [K1][C/B][1][K2].                         */
 int tpx_remap_and_quantize_qint8(const uint16_t* blocked, int64_t K1, int64_t C1, int64_t C2, int64_t K2,
                                  int64_t C3, int64_t block_size, int8_t* q, float* scales,
-                                 int64_t* block_size_used, void* stream);
+                                 int64_t scales_capacity, int64_t* block_size_used, void* stream);
 
 /* Replaces Tensor.dequantize() on the two quantized carriers
  * (PerBlockMxFPQuantizer::dequantize src/csrc/qtypes.cpp:438-445, PerBlockAffineQuantizer
@@ -149,11 +160,16 @@ int tpx_rmsnorm_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair
 /* The same linear for callers that cannot allocate device memory where they call it (all free memory already
  * handed to a cache pool, a fixed budget inside another framework, a thread that must stay off the allocator's
  * locks). It has no counterpart in the reference. Its scratch is an 8 MiB array built into the library
- * (tpx_qlinear_mxfp4_tc_static_max_bytes); shapes whose scratch need (tpx_qlinear_mxfp4_tc_scratch_bytes) exceeds
- * that are refused with TPX_ERR_SCRATCH. The call allocates nothing. The first call on each device looks up the
+ * (tpx_qlinear_mxfp4_tc_static_max_bytes). Where the kernel family the planner would pick needs more scratch than
+ * that, the call runs the family with the smallest scratch instead; a shape that fits neither is refused with
+ * TPX_ERR_SCRATCH. The call allocates nothing. The first call on each device looks up the
  * array's device address and should therefore come before any stream capture. All calls on one GPU share the
- * array: two of them in flight at once (different streams) corrupt each other; serialise them.                */
+ * array: two of them in flight at once (different streams) corrupt each other; serialise them.
+ * A kernel that gave up on one of its bounded waits leaves a non-zero code in a word of the array; the word stays set
+ * across later calls until tpx_qlinear_mxfp4_tc_static_status copies it to *status_host and clears it (that call
+ * waits for `stream`). 0 = every call since the last read completed normally.                                  */
 size_t tpx_qlinear_mxfp4_tc_static_max_bytes(void);
+int tpx_qlinear_mxfp4_tc_static_status(void* stream, unsigned* status_host);
 int tpx_qlinear_mxfp4_tc_static(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M,
                                 int64_t N, int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in,
                                 const uint16_t* res, float res_scale, uint16_t* y, void* stream);

@@ -1,4 +1,7 @@
 """Helpers shared by the GPU parity tests: numpy bf16 bit patterns <-> torch CUDA tensors."""
+import contextlib
+import os
+
 import numpy as np
 import torch
 
@@ -30,6 +33,23 @@ def make_qweight(rng, N, K, kind, dev, block=64, std=0.02):
 def assert_no_kernel_error():
     """The bounded waits inside the kernels report through a word in the scratch buffer."""
     from tpp_pytorch_extension_b200 import _lib
-    torch.cuda.synchronize()
-    for buf in _lib._scratch.values():
-        assert int(buf[65532:65536].view(torch.int32).item()) == 0, "a kernel gave up on a bounded wait"
+    _lib.assert_no_kernel_error()
+
+
+@contextlib.contextmanager
+def knob_env(**env):
+    """Sets TPX_* kernel-selection switches for the enclosed code. The library and the Python layer read them once, so
+    both are told to read again on the way in and on the way out."""
+    from tpp_pytorch_extension_b200 import _lib
+    old = {k: os.environ.get(k) for k in env}
+    os.environ.update({k: str(v) for k, v in env.items()})
+    _lib.reload_options()
+    try:
+        yield
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+        _lib.reload_options()

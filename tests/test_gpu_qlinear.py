@@ -6,23 +6,23 @@ import pytest
 import torch
 
 from oracle import oracle as O
-from tests.gpu_util import assert_no_kernel_error, make_qweight, to_dev_bf16, to_host_bits
+from tests.gpu_util import assert_no_kernel_error, knob_env, make_qweight, to_dev_bf16, to_host_bits
 
 pytestmark = pytest.mark.gpu
 TOL = 2e-2
 
 
 @pytest.fixture(autouse=True, params=["tc", "tc_wide", "tc_f4", "stream"])
-def mxfp4_path(request, monkeypatch):
+def mxfp4_path(request):
     """Every case runs on each MXFP4 kernel family: the tcgen05 kernel with the weights on the 128-row side of the MMA,
     the tcgen05 kernel with the weights on the wide side (up to 64 tokens), the packed-fp4 tcgen05 kernel (up to 32
     tokens) and the mma.sync streaming kernel."""
-    monkeypatch.setenv("TPX_MXFP4_PATH", "stream" if request.param == "stream" else "tc")
-    monkeypatch.setenv("TPX_TC_WIDE", "1" if request.param == "tc_wide" else "0")
-    monkeypatch.setenv("TPX_TC_F4", "1" if request.param == "tc_f4" else "0")
     # int8 weights: the tcgen05 kind::i8 kernel (reference arithmetic) with the tensor-core families, else the streaming kernel
-    monkeypatch.setenv("TPX_INT8_PATH", "stream" if request.param == "stream" else "tc")
-    return request.param
+    with knob_env(TPX_MXFP4_PATH="stream" if request.param == "stream" else "tc",
+                  TPX_TC_WIDE="1" if request.param == "tc_wide" else "0",
+                  TPX_TC_F4="1" if request.param == "tc_f4" else "0",
+                  TPX_INT8_PATH="stream" if request.param == "stream" else "tc"):
+        yield request.param
 
 
 def run_fc(x_bits, q, dev, **kw):
@@ -134,12 +134,13 @@ def test_int8_many_tokens(cuda):
 
 @pytest.mark.parametrize("block", [64, 256])
 @pytest.mark.parametrize("M", [1, 7, 16, 33, 64])
-def test_int8_tensor_core_kernel_matches_reference_arithmetic(cuda, monkeypatch, M, block):
+def test_int8_tensor_core_kernel_matches_reference_arithmetic(cuda, M, block):
     """The tcgen05 kind::i8 kernel (activations quantised per K block, int32 block products, fp32 scaling) against the
     oracle's restatement of the reference's int8 arithmetic and against the weight-only fp32 oracle; post-ops, a gate/up
     pair, ragged N and a K split over a cluster."""
     from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
-    monkeypatch.setenv("TPX_INT8_PATH", "tc")
+    if F.int8_path() != "tc":
+        pytest.skip("runs with the tensor-core families")
     rng = np.random.default_rng(300 + M + block)
     N, K = 208, 1024
     q, wd, (qq, ss, bs) = make_qweight(rng, N, K, "int8", cuda, block=block)

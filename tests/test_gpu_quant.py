@@ -13,7 +13,7 @@ def test_cvt_table_is_e2m1(cuda):
     """The in-kernel 4-bit expansion: byte -> (low nibble, high nibble) as f16 pairs."""
     from tpp_pytorch_extension_b200 import _lib
     out = torch.zeros(256, dtype=torch.int32, device=cuda)
-    _lib.check(_lib.lib().tpx_debug_cvt_e2m1(out.data_ptr(), _lib.stream()))
+    _lib.check(_lib.lib().tpx_e2m1_pair_table(out.data_ptr(), _lib.stream()))
     got = out.cpu().numpy().view(np.uint32)
     lut = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], dtype=np.float16)
     for b in range(256):

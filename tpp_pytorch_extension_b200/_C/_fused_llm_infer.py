@@ -5,23 +5,30 @@ import torch
 from .. import _lib
 from ._qtype import QTensor
 
+import os
+
 ACT = {None: 0, "none": 0, "gelu": 1, "silu": 2, "relu": 3}
 _SCRATCH_BYTES = {}
+_OPTS = {}  # TPX_* switches, read from the environment once; _lib.reload_options() empties it
+
+
+def _opt(name, default):
+    v = _OPTS.get(name)
+    if v is None:
+        v = _OPTS[name] = os.environ.get(name, default)
+    return v
 
 
 def mxfp4_path():
     """Kernel family for MXFP4 weights: "tc" = tcgen05 tensor-core kernel (default), "stream" = the
-    mma.sync weight-streaming kernel. Read from TPX_MXFP4_PATH on every call so tests can flip it."""
-    import os
-    return os.environ.get("TPX_MXFP4_PATH", "tc")
+    mma.sync weight-streaming kernel (TPX_MXFP4_PATH)."""
+    return _opt("TPX_MXFP4_PATH", "tc")
 
 
 def int8_path():
-    """Kernel family for int8 weights at up to 64 tokens: "tc" (default) = tcgen05 kind::i8 kernel with the reference's
-    activation-quantised arithmetic, "stream" = the mma.sync weight-only streaming kernel. Read from TPX_INT8_PATH
-    on every call."""
-    import os
-    return os.environ.get("TPX_INT8_PATH", "tc")
+    """Kernel family for int8 weights: "tc" (default) = tcgen05 kind::i8 kernel with the reference's
+    activation-quantised arithmetic, "stream" = the mma.sync weight-only streaming kernel (TPX_INT8_PATH)."""
+    return _opt("TPX_INT8_PATH", "tc")
 
 
 def _int8_tc(x, y, w, w2, bias, act, mul_in, res, res_scale, norm=None):
@@ -78,13 +85,12 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
         if w2 is not None and (w2.out_features, w2.in_features, w2.kind) != (N, K, w.kind):
             raise _lib.TpxError("gate/up weights must have the same shape and quantization")
         wq, sfa = w.packed_tc(w2)
-        import os
-        key = ("tc", M, N, K, w2 is not None, os.environ.get("TPX_TC_WIDE", "auto"), os.environ.get("TPX_TC_F4", "auto"))
+        key = ("tc", M, N, K, w2 is not None, _opt("TPX_TC_WIDE", "auto"), _opt("TPX_TC_F4", "auto"))
         nb = _SCRATCH_BYTES.get(key)
         if nb is None:
             nb = _SCRATCH_BYTES[key] = L.tpx_qlinear_mxfp4_tc_scratch_bytes(M, N, K, int(w2 is not None))
         sc = _lib.scratch(nb, x.device)
-        if norm is not None and K <= 8192 and os.environ.get("TPX_FUSED_NORM", "1") != "0":
+        if norm is not None and K <= 8192 and _opt("TPX_FUSED_NORM", "1") != "0":
             gamma, eps = norm
             rc = L.tpx_rmsnorm_qlinear_mxfp4_tc(wq.data_ptr(), sfa.data_ptr(), int(w2 is not None), x.data_ptr(), gamma.data_ptr(),
                                                 int(gamma.dtype == torch.float32), float(eps), M, N, K, _lib.ptr(bias), ACT[act],

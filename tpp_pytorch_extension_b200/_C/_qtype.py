@@ -222,6 +222,22 @@ def remap_and_quantize_mxfp4(t):
     return QTensor(codes, scales, (K1o, C1, C2, 32, C3), kPerBlockMxFP, 32)
 
 
+def qint8_block_size_used(C, own_block, block_size):
+    """The block size remap_and_quantize_qint8 ends up with (src/csrc/qtypes.cpp:878-889): the requested one if it
+    divides the in-features C; else the largest power of two from 4096 down to 64 that is smaller than the request and
+    divides C; else the blocked tensor's own inner block C2*C3."""
+    if block_size < 4 or block_size % 4:
+        raise _lib.TpxError(f"remap_and_quantize_qint8: block size {block_size} must be a positive multiple of 4")
+    if C % block_size == 0:
+        return block_size
+    qbs = 4096
+    while qbs >= 64:
+        if block_size > qbs and C % qbs == 0:
+            return qbs
+        qbs //= 2
+    return own_block
+
+
 def remap_and_quantize_qint8(t, block_size=None):
     """src/csrc/qtypes.cpp:866-932. `block_size` defaults to the QINT8_BLOCK_SIZE environment
     variable (256 if unset), as in the reference (:28)."""
@@ -231,14 +247,15 @@ def remap_and_quantize_qint8(t, block_size=None):
         block_size = int(os.environ.get("QINT8_BLOCK_SIZE", "256"))
     K1, C1, C2, K2, C3 = t.shape
     C = C1 * C2 * C3
+    B = qint8_block_size_used(C, C2 * C3, int(block_size))
     used = ctypes.c_int64(0)
     q = torch.empty(K1 * C * K2, dtype=torch.int8, device=t.device)
-    # scale count depends on the block size actually used; allocate for the smallest (64)
-    scales = torch.empty(K1 * (C // 64) * K2, dtype=torch.float32, device=t.device)
+    scales = torch.empty(K1 * (C // B) * K2, dtype=torch.float32, device=t.device)
     with torch.cuda.device(t.device):
         _lib.check(_lib.lib().tpx_remap_and_quantize_qint8(t.data_ptr(), K1, C1, C2, K2, C3, block_size, q.data_ptr(),
-                                                           scales.data_ptr(), ctypes.byref(used), _lib.stream()))
-    B = used.value
+                                                           scales.data_ptr(), scales.numel(), ctypes.byref(used), _lib.stream()))
+    if used.value != B:
+        raise _lib.TpxError(f"remap_and_quantize_qint8: the library used block size {used.value}, the host computed {B}")
     q = q.view(K1, C // B, B // 4, K2, 4)
     scales = scales[: K1 * (C // B) * K2].view(K1, C // B, 1, K2)
     return QTensor(q, scales, (K1, C // B, B // 4, K2, 4), kPerBlockAffine, B)

@@ -18,9 +18,10 @@ _SIGS = {
     "tpx_version": (c_int, []),
     "tpx_last_error": (ctypes.c_char_p, []),
     "tpx_sm_count": (c_int, []),
-    "tpx_debug_cvt_e2m1": (c_int, [c_vp, c_vp]),
+    "tpx_e2m1_pair_table": (c_int, [c_vp, c_vp]),
+    "tpx_reload_options": (None, []),
     "tpx_remap_and_quantize_mxfp4": (c_int, [c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp]),
-    "tpx_remap_and_quantize_qint8": (c_int, [c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, ctypes.POINTER(c_i64), c_vp]),
+    "tpx_remap_and_quantize_qint8": (c_int, [c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_i64, ctypes.POINTER(c_i64), c_vp]),
     "tpx_dequantize_mxfp4": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp]),
     "tpx_dequantize_qint8": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp]),
     "tpx_packed_bytes": (c_int, [c_int, c_i64, c_i64, c_i64, ctypes.POINTER(c_sz), ctypes.POINTER(c_sz)]),
@@ -41,7 +42,8 @@ _SIGS = {
     "tpx_qlinear_qint8_tc": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_i64, c_i64, c_int, c_vp, c_int, c_vp, c_vp, c_f32,
                                      c_vp, c_vp, c_sz, c_vp]),
     "tpx_launch_count": (ctypes.c_ulonglong, []),
-    "tpx_debug_tc_timeline": (None, [c_vp]),
+    "tpx_debug_tc_timeline": (None, [c_vp]),  # exported only by a -DTPX_DEBUG build
+    "tpx_qlinear_mxfp4_tc_static_status": (c_int, [c_vp, ctypes.POINTER(ctypes.c_uint)]),
     "tpx_qlinear_mxfp4_tc_static_max_bytes": (c_sz, []),
     "tpx_qlinear_mxfp4_tc_static": (c_int, [c_vp, c_vp, c_int, c_vp, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp, c_f32, c_vp, c_vp]),
     "tpx_rmsnorm": (c_int, [c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_vp, c_vp]),
@@ -96,6 +98,25 @@ def require_cuda(t, name):
         raise TpxError(f"{name} must be a CUDA tensor (this library has no CPU path)")
     if not t.is_contiguous():
         raise TpxError(f"{name} must be contiguous")
+
+
+def reload_options():
+    """Re-read the TPX_* kernel-selection switches (the library and the Python side read them once)."""
+    from ._C import _fused_llm_infer
+    _fused_llm_infer._OPTS.clear()
+    if _lib is not None:
+        _lib.tpx_reload_options()
+
+
+def assert_no_kernel_error(sync=True):
+    """Raises if a kernel gave up on one of its bounded waits since the buffers were created: such a kernel leaves a
+    code in the error word of its scratch and finishes early with a wrong result."""
+    if sync:
+        torch.cuda.synchronize()
+    for (dev, _), buf in list(_scratch.items()):
+        code = int(buf[65532:65536].view(torch.int32).item())
+        if code:
+            raise TpxError(f"a linear kernel on device {dev} gave up on a bounded wait (code {code})")
 
 
 _scratch = {}

@@ -2,6 +2,7 @@
 // dispatch of tpx_qlinear onto the kernel families.
 #include "tpx_common.cuh"
 #include <string.h>
+#include <stdlib.h>
 
 namespace tpx {
 
@@ -16,6 +17,30 @@ void set_error(const char* fmt, ...) {
 
 static unsigned long long g_launches = 0;  // relaxed tally; exact when one host thread launches
 void count_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
+
+static Knobs g_knobs;
+static bool g_knobs_read = false;
+
+static void read_knobs() {
+  auto env = [](const char* name, int dflt) { const char* e = getenv(name); return e ? atoi(e) : dflt; };
+  g_knobs.tc_whole = env("TPX_TC_WHOLE", -1);
+  g_knobs.tc_wide = env("TPX_TC_WIDE", -1);
+  g_knobs.tc_f4 = env("TPX_TC_F4", -1);
+  g_knobs.tc_cluster = env("TPX_TC_CLUSTER", 1);
+  g_knobs.tc_pf = env("TPX_TC_PF", 0);
+  g_knobs.attn_splits = env("TPX_ATTN_SPLITS", 0);
+#ifdef TPX_DEBUG
+  g_knobs.dbg = env("TPX_TC_DBG", 0);
+#else
+  g_knobs.dbg = 0;
+#endif
+  g_knobs_read = true;
+}
+
+const Knobs& knobs() {
+  if (!g_knobs_read) read_knobs();
+  return g_knobs;
+}
 
 int sm_count() {
   static int cached[64] = {0};
@@ -35,7 +60,7 @@ int qlinear_stream_launch(int kind, const uint8_t* pk_codes, const void* pk_scal
                           const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res, float res_scale,
                           uint16_t* y, void* scratch, size_t scratch_bytes, cudaStream_t st);
 
-__global__ void debug_cvt_e2m1_kernel(uint32_t* out) {
+__global__ void e2m1_pair_table_kernel(uint32_t* out) {
   uint32_t b = threadIdx.x;
   uint32_t r;
   asm("{ .reg .b8 t; cvt.u8.u32 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(r) : "r"(b));
@@ -49,10 +74,11 @@ using namespace tpx;
 extern "C" int tpx_version(void) { return 100; }
 extern "C" const char* tpx_last_error(void) { return g_err; }
 extern "C" int tpx_sm_count(void) { return sm_count(); }
+extern "C" void tpx_reload_options(void) { read_knobs(); }
 
-extern "C" int tpx_debug_cvt_e2m1(uint32_t* out256, void* stream) {
-  TPX_REQUIRE(out256, TPX_ERR_ARG, "debug_cvt_e2m1: null pointer");
-  debug_cvt_e2m1_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(out256);
+extern "C" int tpx_e2m1_pair_table(uint32_t* out256, void* stream) {
+  TPX_REQUIRE(out256, TPX_ERR_ARG, "e2m1_pair_table: null pointer");
+  e2m1_pair_table_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(out256);
   TPX_LAUNCH_OK();
   return TPX_OK;
 }

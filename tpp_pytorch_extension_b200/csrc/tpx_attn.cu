@@ -641,7 +641,7 @@ static int attn_plan(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t key_
   const int64_t ctas = B * Nkv;
   const int nblocks = (int)((key_len + 31) / 32);
   const int sms = sm_count();
-  static const int forced = [] { const char* e = getenv("TPX_ATTN_SPLITS"); return e ? atoi(e) : 0; }();
+  const int forced = knobs().attn_splits;
   int best = 1;
   if (forced > 0) {
     best = forced < 64 ? forced : 64;

@@ -62,6 +62,15 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 int sm_count();
 void count_launch();  // host-side tally behind tpx_launch_count()
 
+// Kernel-selection switches, read from the environment once (first use) and again on tpx_reload_options():
+// TPX_TC_WHOLE, TPX_TC_WIDE, TPX_TC_F4 (-1 = let the planner decide), TPX_TC_CLUSTER (0 = no cluster split-K),
+// TPX_TC_PF (L2 prefetch distance), TPX_ATTN_SPLITS (0 = cost model). None of them changes a result. `dbg` carries
+// TPX_TC_DBG and is always 0 unless the library was built with -DTPX_DEBUG.
+struct Knobs {
+  int tc_whole, tc_wide, tc_f4, tc_cluster, tc_pf, attn_splits, dbg;
+};
+const Knobs& knobs();
+
 // Programmatic dependent launch. Every kernel of the decoder-layer path starts with pdl_trigger() (the next
 // kernel in the stream may be scheduled and run its prologue while this one works) and calls pdl_wait() before
 // it touches global memory that an earlier kernel may have written or may still read: the wait returns once

@@ -394,9 +394,9 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       auto fetch_w = [&](int s, int tn, int ks) {  // weight tiles and their scale blocks: independent of the split kernel
         const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
         const uint32_t bar = tc_smem_u32(&bar_full[s]);
-        tc_mbar_expect_tx(bar, ((p.dbg & 2) ? C::TX - C::A_TILES * C::A_TX : C::TX) - ((p.dbg & 128) ? C::X_ROWS * 128 + UKS * C::SFB_PER * 512 : 0));
+        tc_mbar_expect_tx(bar, ((TPX_DBG(p) & 2) ? C::TX - C::A_TILES * C::A_TX : C::TX) - ((TPX_DBG(p) & 128) ? C::X_ROWS * 128 + UKS * C::SFB_PER * 512 : 0));
         const int wtile = (tn * p.KS + ks) * C::A_TILES;  // first weight tile of the unit
-        if (!(p.dbg & 2)) {
+        if (!(TPX_DBG(p) & 2)) {
 #pragma unroll
           for (int r = 0; r < C::A_TILES / C::W_BOX; r++) tc_tma_2d(st + r * C::W_BOX * C::A_BYTES, &tmW, 0, (wtile + C::W_BOX * r) * 128, bar);
         }
@@ -448,7 +448,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           }
           fetch_w(s, tn, ks);
         }
-        if (!(p.dbg & 128)) fetch_x(s, tm, ks);
+        if (!(TPX_DBG(p) & 128)) fetch_x(s, tm, ks);
         if (++ks == p.KS) { ks = 0; tile++; }
       }
     }
@@ -480,7 +480,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const uint32_t sb = st + C::A_TILES * C::A_BYTES;
         const uint32_t ssf = sb + C::X_ROWS * 128;
         const bool part_end = (ks == p.KS - 1) || (it == nunits - 1);
-        if (p.dbg & 1) {
+        if (TPX_DBG(p) & 1) {
           tc_mbar_arrive(tc_smem_u32(&bar_empty[s]));
           if (part_end) tc_mbar_arrive(tc_smem_u32(&bar_acc_full));
         } else {
@@ -775,7 +775,7 @@ static TcPlan tc_plan(int64_t M, int64_t N, int64_t K, bool pair, bool allow_clu
   // Cutting tiles between CTAs balances the weight stream exactly but costs a fix-up pass through scratch at
   // loaded-memory latency; with nearly as many tiles as SMs, or many tiles per SM, whole tiles are cheaper.
   pl.whole_tiles = (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
-  { const char* e = getenv("TPX_TC_WHOLE"); if (e) pl.whole_tiles = atoi(e); }
+  if (knobs().tc_whole >= 0) pl.whole_tiles = knobs().tc_whole;
   pl.grid = pl.whole_tiles ? (int)(T < sms ? T : sms) : (int)(U < sms ? U : sms);
   // Few tiles: a cluster of c CTAs per tile cuts K between them and reduces through distributed shared memory,
   // which takes the fix-up pass (a second kernel behind a round trip through L2) off the critical path.
@@ -883,8 +883,11 @@ using namespace tpx;
 
 static unsigned long long* g_tc_timeline = nullptr;
 
-// Debug aid: when set, every CTA of the next tensor-core GEMMs writes 8 globaltimer stamps to `buf`.
+#ifdef TPX_DEBUG
+// Debug aid (only in a -DTPX_DEBUG build): when set, every CTA of the next tensor-core GEMMs writes 8 globaltimer
+// stamps to `buf`.
 extern "C" void tpx_debug_tc_timeline(void* buf) { g_tc_timeline = reinterpret_cast<unsigned long long*>(buf); }
+#endif
 
 extern "C" int tpx_tc_packed_bytes(int64_t N, int64_t K, int pair, size_t* wq_bytes, size_t* sfa_bytes) {
   TPX_REQUIRE(N > 0 && K > 0 && N % 32 == 0 && K % 64 == 0, TPX_ERR_ARG, "tc_packed_bytes: needs N %% 32 == 0 and K %% 64 == 0");
@@ -914,8 +917,7 @@ extern "C" int tpx_repack_mxfp4_tc(const uint8_t* codes, const uint8_t* scales, 
 // the cluster split-K of the other kernel. TPX_TC_WIDE=1 forces it for every M <= 64, TPX_TC_WIDE=0 disables it.
 static bool tc_wide(int64_t M, int64_t N, int64_t K, bool pair) {
   if (M > 64) return false;
-  const char* e = getenv("TPX_TC_WIDE");
-  if (e) return atoi(e) != 0;
+  if (knobs().tc_wide >= 0) return knobs().tc_wide != 0;
   const long long T = pair ? (N + 127) / 128 : (N + 255) / 256;  // tiles of the wide kernel
   const int sms = sm_count();
   (void)K;
@@ -933,11 +935,11 @@ static bool tc_wide(int64_t M, int64_t N, int64_t K, bool pair) {
 // TPX_TC_F4=0 never.
 static int tc_kind(int64_t M, int64_t N, int64_t K, bool pair) {
   if (M <= 32) {
-    const char* e = getenv("TPX_TC_F4");
+    const int forced = knobs().tc_f4;
     const long long T = (N + 127) / 128;  // one token tile up to 32 tokens
     const int sms = sm_count();
     const bool whole = (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
-    if (e ? atoi(e) != 0 : whole) return 2;
+    if (forced >= 0 ? forced != 0 : whole) return 2;
   }
   return tc_wide(M, N, K, pair) ? 1 : 0;
 }
@@ -966,19 +968,19 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   if (kind == 2) {
     TcParams b = {};
     b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act; b.tl = g_tc_timeline;
-    { const char* e = getenv("TPX_TC_DBG"); b.dbg = e ? atoi(e) : 0; }
+    b.dbg = knobs().dbg;
     // no L2 prefetch ahead of the stages: this kernel's stages already hold 160-210 KB of packed weights per SM, and
     // prefetches issued at the start delay the first stage (gate/up, M = 8: 26.5 us without, 29.2 us with 8 units ahead)
-    { const char* e = getenv("TPX_TC_PF"); b.pf = e ? atoi(e) : 0; }
+    b.pf = knobs().tc_pf;
     return tc4_run(wq, sfa, dual, x, M, N, K, b, scratch, scratch_bytes, (cudaStream_t)stream, norm);
   }
   if (kind == 1) {
     TcParams b = {};
     b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act; b.tl = g_tc_timeline;
-    { const char* e = getenv("TPX_TC_DBG"); b.dbg = e ? atoi(e) : 0; }
+    b.dbg = knobs().dbg;
     // L2 prefetch ahead of the stages is off: with launches back to back it delays the first stage more than it helps
     // later ones (gate/up, M = 8: 23.4 us without, 25.3 us with 8 units ahead)
-    { const char* e = getenv("TPX_TC_PF"); b.pf = e ? atoi(e) : 0; }
+    b.pf = knobs().tc_pf;
     return tcw_run(wq, sfa, dual, x, M, N, K, b, scratch, scratch_bytes, (cudaStream_t)stream, norm);
   }
   TcPlan pl = tc_plan(M, N, K, dual);
@@ -994,19 +996,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   CUtensorMap mw, mx;
   // weight: 64-byte rows of 128 codes, 256 rows (two tiles) per request; activation terms: 128-byte rows
   int rc;
-  { const char* e = getenv("TPX_TC_DBG"); if (e && (atoi(e) & 4)) {  // timing experiment: raw byte copy instead of the unpacking copy
-      EncodeTiledFn fn = encode_fn();
-      const bool wide_rows = (atoi(e) & 8) != 0;  // 128-byte rows instead of 64-byte rows, same bytes per request
-      cuuint64_t gdim[2] = {wide_rows ? 128u : 64u, (uint64_t)pl.TN * pl.KS * (dual ? 2 : 1) * (wide_rows ? 64 : 128)};
-      cuuint64_t gstr[1] = {wide_rows ? 128u : 64u};
-      cuuint32_t box[2] = {wide_rows ? 128u : 64u, wide_rows ? 128u : 256u};
-      cuuint32_t estr[2] = {1, 1};
-      CUresult r = fn(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(wq), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-      rc = r == CUDA_SUCCESS ? TPX_OK : TPX_ERR_CUDA;
-    } else
-      rc = tc_make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, (uint64_t)pl.TN * pl.KS * (dual ? 2 : 1) * 128, 64, (dual ? 2 : 1) * pl.uks >= 2 ? 256 : 128);
-  }
+  rc = tc_make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, (uint64_t)pl.TN * pl.KS * (dual ? 2 : 1) * 128, 64, (dual ? 2 : 1) * pl.uks >= 2 ? 256 : 128);
   if (rc) return rc;
   rc = tc_make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, terms, (uint64_t)pl.Mpad * pl.KS * 2, 128, (uint32_t)pl.xbox);
   if (rc) return rc;
@@ -1016,9 +1006,9 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   p.counters = reinterpret_cast<unsigned*>(sc);
   p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = pl.TM; p.act = act; p.whole_tiles = pl.whole_tiles; p.cluster = pl.cluster; p.tl = g_tc_timeline;
-  { const char* e = getenv("TPX_TC_DBG"); p.dbg = e ? atoi(e) : 0; }
-  { const char* e = getenv("TPX_TC_PF"); p.pf = e ? atoi(e) : 0; }  // off, see above (prefill shapes: 842 against 838 TFLOP/s)
-  { const char* e = getenv("TPX_TC_CLUSTER"); if (e && atoi(e) == 0) p.cluster = 1; }
+  p.dbg = knobs().dbg;
+  p.pf = knobs().tc_pf;  // off by default, see above (prefill shapes: 842 against 838 TFLOP/s)
+  if (knobs().tc_cluster == 0) p.cluster = 1;
   if (dual) {
     switch (pl.tok) {
       case 16: return tc_launch<16, true, 2>(mw, mx, p, pl.grid, st);
@@ -1076,12 +1066,28 @@ static int static_scratch_ptr(void** out) {
 
 extern "C" size_t tpx_qlinear_mxfp4_tc_static_max_bytes(void) { return kStaticScratchBytes; }
 
+// The bounded waits inside the kernels report through a word of the scratch; with the built-in array the caller has no
+// pointer to it, so this call copies it out (and clears it). It waits for `stream`: use it at a point where a
+// synchronisation is acceptable (after a step, not between the launches of one).
+extern "C" int tpx_qlinear_mxfp4_tc_static_status(void* stream, unsigned* status_host) {
+  TPX_REQUIRE(status_host, TPX_ERR_ARG, "qlinear_mxfp4_tc_static_status: null pointer");
+  void* sc = nullptr;
+  int rc = static_scratch_ptr(&sc);
+  if (rc) return rc;
+  unsigned char* word = reinterpret_cast<unsigned char*>(sc) + kTcCounterBytes - 4;
+  TPX_CUDA_OK(cudaMemcpyAsync(status_host, word, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  TPX_CUDA_OK(cudaMemsetAsync(word, 0, 4, (cudaStream_t)stream));
+  TPX_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+  return TPX_OK;
+}
+
 extern "C" int tpx_qlinear_mxfp4_tc_static(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M,
                                            int64_t N, int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in,
                                            const uint16_t* res, float res_scale, uint16_t* y, void* stream) {
   TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear_mxfp4_tc_static: bad shape");
   if (M == 0) return TPX_OK;
-  // the kernel whose scratch fits the array: the wide one's partial slots grow with the token count
+  // the planner's kernel family if its scratch fits the array, else the family with the smallest scratch (the
+  // 128-row-side kernel); only when that does not fit either is the shape refused
   int wide = tc_kind(M, N, K, pair != 0);
   if (wide && tc_scratch_need(M, N, K, pair != 0, wide) > kStaticScratchBytes) wide = 0;
   const size_t need = tc_scratch_need(M, N, K, pair != 0, wide);
@@ -1092,7 +1098,8 @@ extern "C" int tpx_qlinear_mxfp4_tc_static(const uint8_t* wq, const uint8_t* sfa
   void* sc = nullptr;
   int rc = static_scratch_ptr(&sc);
   if (rc) return rc;
-  // the array keeps whatever the previous call left: the arrival counters and the error word must start at zero
-  TPX_CUDA_OK(cudaMemsetAsync(sc, 0, kTcCounterBytes, (cudaStream_t)stream));
+  // the array keeps whatever the previous call left: the arrival counters must start at zero. The error word at the
+  // end of the counter block is left alone: it stays set until tpx_qlinear_mxfp4_tc_static_status reads it.
+  TPX_CUDA_OK(cudaMemsetAsync(sc, 0, kTcCounterBytes - 4, (cudaStream_t)stream));
   return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, sc, kStaticScratchBytes, stream, wide);
 }

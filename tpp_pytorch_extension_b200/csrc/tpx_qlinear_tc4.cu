@@ -370,16 +370,16 @@ qlinear_tc4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const uint32_t sb = st + C::A_TILES * C::A_BYTES;
         const uint32_t ssf = sb + C::X_ROWS * 64;
         const bool part_end = (ks == p.KS - 1) || (it == nunits - 1);
-        if (p.dbg & 32) {  // timing experiment: copies issued by this thread, in order with its MMAs
+        if (TPX_DBG(p) & 32) {  // timing experiment: copies issued by this thread, in order with its MMAs
 #pragma unroll
           for (int q = 0; q < C::SF_BLOCKS; q++) tc_cp_sf(sf_t + q * 4, tc_sf_desc(ssf + q * 512));
-        } else if (!(p.dbg & 16)) {
+        } else if (!(TPX_DBG(p) & 16)) {
           if (!tc_wait(tc_smem_u32(&bar_sf[s]), ph)) { atomicExch(p.err, 5u); break; }
           tc_fence_after();
         }
 #pragma unroll
         for (int kk = 0; kk < UKS; kk++) {
-          if (p.dbg & 1) break;
+          if (TPX_DBG(p) & 1) break;
 #pragma unroll
           for (int j = 0; j < 2; j++) {  // k 64*j .. 64*j+63 of the step: 32 bytes along the row, scale bytes 2j and 2j+1
             const uint32_t sfid = (uint32_t)(2 * j);
@@ -405,7 +405,7 @@ qlinear_tc4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     // ------------------------------------------------------------ scale-factor copies (shared -> tensor memory)
     // Issued by their own thread so that they are not queued in order between the MMAs; a stage's tensor-memory
     // columns are free again once its shared memory has been refilled (the refill waits for the stage's MMAs).
-    if (lane == 0 && !(p.dbg & 48)) {
+    if (lane == 0 && !(TPX_DBG(p) & 48)) {
       for (int it = 0; it < nunits; it++) {
         const int s = it % C::STAGES;
         const uint32_t ph = (uint32_t)((it / C::STAGES) & 1);
@@ -562,7 +562,7 @@ static Tc4Plan tc4_plan(int64_t M, int64_t N, int64_t K, bool pair) {
   const long long T = (long long)pl.TN * pl.TM;
   const int sms = sm_count();
   pl.whole_tiles = (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
-  { const char* e = getenv("TPX_TC_WHOLE"); if (e) pl.whole_tiles = atoi(e); }
+  if (knobs().tc_whole >= 0) pl.whole_tiles = knobs().tc_whole;
   pl.grid = pl.whole_tiles ? (int)(T < sms ? T : sms) : (int)(U < sms ? U : sms);
   pl.cluster = 1;
   if (!pl.whole_tiles && T * 2 <= sms) {
@@ -571,7 +571,7 @@ static Tc4Plan tc4_plan(int64_t M, int64_t N, int64_t K, bool pair) {
     if (c > pl.KU) c = pl.KU;
     if (c > 1) pl.cluster = c;
   }
-  { const char* e = getenv("TPX_TC_CLUSTER"); if (e && atoi(e) == 0) pl.cluster = 1; }
+  if (knobs().tc_cluster == 0) pl.cluster = 1;
   size_t o = kTcCounterBytes;
   auto bump = [&](size_t bytes) { size_t r = o; o += (bytes + 1023) & ~(size_t)1023; return r; };
   pl.off_terms = bump((size_t)pl.Mpad * pl.KS * 4 * 64);

@@ -483,7 +483,7 @@ static TcwPlan tcw_plan(int64_t M, int64_t N, int64_t K, bool pair) {
   const int sms = sm_count();
   // whole tiles when their count suits the SM count (no fix-up pass), else the (tile, k step) units are cut evenly
   pl.whole = (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
-  { const char* e = getenv("TPX_TC_WHOLE"); if (e) pl.whole = atoi(e); }
+  if (knobs().tc_whole >= 0) pl.whole = knobs().tc_whole;
   pl.grid = pl.whole ? (int)(T < sms ? T : sms) : (int)(U < sms ? U : sms);
   // few tiles: a cluster of CTAs per tile cuts K and reduces over distributed shared memory (no fix-up pass)
   pl.cluster = 1;
@@ -493,7 +493,7 @@ static TcwPlan tcw_plan(int64_t M, int64_t N, int64_t K, bool pair) {
     if (c > pl.KU) c = pl.KU;
     if (c > 1) pl.cluster = c;
   }
-  { const char* e = getenv("TPX_TC_CLUSTER"); if (e && atoi(e) == 0) pl.cluster = 1; }
+  if (knobs().tc_cluster == 0) pl.cluster = 1;
   size_t o = kTcCounterBytes;
   auto bump = [&](size_t bytes) { size_t r = o; o += (bytes + 1023) & ~(size_t)1023; return r; };
   pl.off_terms = bump((size_t)pl.KS * 2 * pl.tokp * 128);

@@ -258,18 +258,24 @@ extern "C" int tpx_remap_and_quantize_mxfp4(const uint16_t* blocked, int64_t K1,
 
 extern "C" int tpx_remap_and_quantize_qint8(const uint16_t* blocked, int64_t K1, int64_t C1, int64_t C2, int64_t K2,
                                             int64_t C3, int64_t block_size, int8_t* q, float* scales,
-                                            int64_t* block_size_used, void* stream) {
+                                            int64_t scales_capacity, int64_t* block_size_used, void* stream) {
   TPX_REQUIRE(blocked && q && scales, TPX_ERR_ARG, "remap_and_quantize_qint8: null pointer");
   TPX_REQUIRE(C3 == 1 || C3 == 2 || C3 == 4, TPX_ERR_ARG, "remap_and_quantize_qint8: C3 must be 1, 2 or 4");
+  TPX_REQUIRE(K1 > 0 && C1 > 0 && C2 > 0 && K2 > 0, TPX_ERR_ARG, "remap_and_quantize_qint8: empty shape");
+  TPX_REQUIRE(block_size >= 4 && block_size % 4 == 0, TPX_ERR_ARG, "remap_and_quantize_qint8: block size %ld must be a positive multiple of 4",
+              (long)block_size);
   int64_t C = C1 * C2 * C3;
   int64_t B = block_size;
-  if (C % B != 0) {  // src/csrc/qtypes.cpp:881-888
+  if (C % B != 0) {  // src/csrc/qtypes.cpp:881-888; with no candidate the tensor keeps its own inner block C2*C3
+    B = C2 * C3;
     for (int64_t QBS = 4096; QBS >= 64; QBS /= 2)
       if (block_size > QBS && C % QBS == 0) { B = QBS; break; }
   }
   TPX_REQUIRE(B > 0 && C % B == 0 && B % 4 == 0, TPX_ERR_ARG, "Shape not compatible for VNNI4 (C=%ld block=%ld)", (long)C, (long)B);
   if (block_size_used) *block_size_used = B;
   int64_t total = K1 * (C / B) * K2;
+  TPX_REQUIRE(scales_capacity >= total, TPX_ERR_ARG, "remap_and_quantize_qint8: block size %ld needs %ld scales, the buffer holds %ld",
+              (long)B, (long)total, (long)scales_capacity);
   quantize_qint8_kernel<<<blocks_for(total, 128), 128, 0, (cudaStream_t)stream>>>(blocked, K1, C1, C2, K2, C3, B, q, scales);
   TPX_LAUNCH_OK();
   return TPX_OK;

@@ -31,10 +31,14 @@ struct TcParams {
   unsigned long long* tl;  // optional per-CTA timeline (8 globaltimer stamps each), null in normal use
   int cluster;          // CTAs per thread-block cluster that share one output tile along K (1: none)
   int pf;               // units prefetched into L2 ahead of the shared-memory stages
-  int dbg;              // debug knobs for timing experiments (results are then wrong): 1 = skip MMAs, 2 = skip weight copies,
-                        // 128 = skip activation copies; packed-fp4 kernel: 16 = skip scale-factor copies, 32 = MMA thread issues them
+  int dbg;              // timing-experiment knobs, honoured only by a -DTPX_DEBUG build (results are then wrong): 1 = skip MMAs,
+                        // 2 = skip weight copies, 128 = skip activation copies; packed-fp4 kernel: 16 = skip scale-factor
+                        // copies, 32 = MMA thread issues them
 };
 
+// The default build compiles the experiment knobs and the timeline stamps out: TPX_DBG(p) is the constant 0 there.
+#ifdef TPX_DEBUG
+#define TPX_DBG(p) ((p).dbg)
 __device__ __forceinline__ void tc_stamp(const TcParams& p, int slot) {
   if (p.tl) {
     unsigned long long t;
@@ -42,6 +46,10 @@ __device__ __forceinline__ void tc_stamp(const TcParams& p, int slot) {
     p.tl[(size_t)blockIdx.x * 8 + slot] = t;
   }
 }
+#else
+#define TPX_DBG(p) 0
+__device__ __forceinline__ void tc_stamp(const TcParams&, int) {}
+#endif
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

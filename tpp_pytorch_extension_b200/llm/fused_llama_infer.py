@@ -129,7 +129,10 @@ class LlamaRunner(torch.nn.Module):
         B, P = input_ids.shape
         dev = input_ids.device
         mask = attention_mask if attention_mask is not None else torch.ones_like(input_ids)
-        logits, cache = self.forward(input_ids, mask, None, cache)
+        # positions count the kept tokens only, in the prompt as in the decode steps (HF generate: cumsum(mask) - 1),
+        # so that a left-padded sequence rotates its tokens as the unpadded one would
+        prompt_pos = (mask.to(torch.int64).cumsum(-1) - 1).clamp_(min=0).contiguous() if attention_mask is not None else None
+        logits, cache = self.forward(input_ids, mask, prompt_pos, cache)
         tok = fused_llm_cpp.argmax_rows(logits[:, -1]).unsqueeze(-1)
         outs = [input_ids, tok.clone()]
         steps = max_new_tokens - 1
@@ -178,7 +181,10 @@ class LlamaRunner(torch.nn.Module):
         for lc in cpp.layers:
             lc.offset += steps
         self.last_graph = graph
-        return torch.cat(outs, dim=1)
+        out = torch.cat(outs, dim=1)
+        from .. import _lib
+        _lib.assert_no_kernel_error()  # a kernel that gave up on a bounded wait would have produced wrong tokens
+        return out
 
 
 def _lm_head_shard(w):
