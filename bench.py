@@ -123,11 +123,20 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU arm
+def host_threads():
+    """The cores this process may use (launchers set OMP_NUM_THREADS=1 for their ranks; the CPU arm undoes that)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_arm(seconds_target=12.0):
-    """Times the CPU restatement on a bounded sample: the gate/up pair at M = 1 and M = 8 over a slice
-    of 1024 output features (of 14336), all host threads. Returns GB/s of algorithmic bytes."""
+    """Times the CPU restatement on a bounded sample: the gate/up pair at every decode-shaped token count of the sweep
+    (M = 1, 8, 64) over a slice of 1024 output features (of 14336), on all host threads. GB/s of algorithmic bytes."""
     import numpy as np
     from oracle import oracle as O
+    O.lib().orc_set_num_threads(host_threads())
     rng = np.random.default_rng(0)
     Ns = 1024
     wg = O.randn_bf16(rng, (Ns, D_MODEL), 0.02)
@@ -137,7 +146,8 @@ def cpu_arm(seconds_target=12.0):
     threads = O.lib().orc_num_threads()
     total_b, total_t = 0.0, 0.0
     per_m = {}
-    for M in (1, 8):
+    ms = [M for M in SWEEP if M <= DECODE_MAX_M]
+    for M in ms:
         x = O.randn_bf16(rng, (M, D_MODEL))
         O.qlinear_mxfp4_packed(x, cg, sg, cu, su, act=O.ACT_SILU)  # warm-up
         reps, t0 = 0, time.perf_counter()
@@ -145,14 +155,15 @@ def cpu_arm(seconds_target=12.0):
             O.qlinear_mxfp4_packed(x, cg, sg, cu, su, act=O.ACT_SILU)
             reps += 1
             dt = time.perf_counter() - t0
-            if dt > seconds_target / 2 or reps >= 200:
+            if dt > seconds_target / len(ms) or reps >= 200:
                 break
         b = reps * (2 * packed_bytes(Ns, D_MODEL) + M * D_MODEL * 2 + M * Ns * 2)
         per_m[M] = b / dt / 1e9
         total_b += b
         total_t += dt
     return {"value": total_b / total_t / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"gate/up pair, M in (1, 8), {Ns} of {D_FF} output features, K = {D_MODEL}; "
+            "sample": f"gate/up pair, M in {tuple(ms)}, a slice of {Ns} of the {D_FF} output features, K = {D_MODEL}, plain-C port "
+                      f"(not the reference's libxsmm kernels); "
                       f"per-M GB/s {', '.join(f'M={m}: {v:.2f}' for m, v in per_m.items())}"}
 
 
@@ -190,6 +201,36 @@ def workload_config():
 
 
 # --------------------------------------------------------------------------- GPU arm
+def spot_rows(N):
+    """Eight runs of 32 consecutive output features spread over [0, N), first and last rows included."""
+    import torch
+    starts = sorted({int(round(g * (N - 32) / 7 / 32)) * 32 for g in range(8)})
+    return torch.cat([torch.arange(s, s + 32) for s in starts])
+
+
+def parity_spot_check(wset, w_cpu, xs_host, dev):
+    """The timed ops once more at M = 8 on the seed-0 weight set, compared with the CPU oracle on 256 sampled output
+    features (the oracle quantizes those rows itself): max |y - ref| / max |ref|, bound 2e-2."""
+    import numpy as np
+    import torch
+    from oracle import oracle as O
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+
+    def bits(t):
+        return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+    wg, wu, wd = wset
+    x = xs_host[8] if 8 in xs_host else torch.randn(8, D_MODEL, generator=torch.Generator().manual_seed(8)).to(torch.bfloat16)
+    h = F.fc_gate_up(x.to(dev), wg, wu)
+    y = F.fc_plain(h, wd)
+    torch.cuda.synchronize()
+    deq = [O.mxfp4_dequant_plain(*O.remap_and_quantize_mxfp4(bits(w))) for w in w_cpu]
+    e1 = O.rel_err(bits(h)[:, spot_rows(D_FF).numpy()], O.gate_up(bits(x), deq[0], deq[1]))
+    e2 = O.rel_err(bits(y)[:, spot_rows(D_MODEL).numpy()], O.qlinear(bits(h), deq[2]))
+    return {"gate_up_rel_err": e1, "down_rel_err": e2, "bound": 2e-2, "ok": bool(e1 <= 2e-2 and e2 <= 2e-2),
+            "scope": "M = 8, 256 sampled output features of each op, against the CPU oracle"}
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -213,11 +254,14 @@ def run_ours(args):
 
     g = torch.Generator(device="cpu").manual_seed(0)
     sets = []
+    w_cpu = []  # 256 sampled rows of each weight of the first set, for the oracle spot check
     for c in range(N_COPIES):
         ws = []
         for (N, K) in ((D_FF, D_MODEL), (D_FF, D_MODEL), (D_MODEL, D_FF)):
             if c == 0:  # seed-0 CPU weights for the first set, device RNG for the L2-rotation copies
-                w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+                w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+                w_cpu.append(w[spot_rows(N)].clone())
+                w = w.to(dev)
             else:
                 w = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
             ws.append(_qtype.remap_and_quantize_mxfp4(block(w)))
@@ -273,29 +317,44 @@ def run_ours(args):
     hs = {}  # input of the down projection per token count: the gate/up output of the last warm-up step
     for _ in range(max(args.warmup, 3)):
         sweep()
-    # ---- device-resident timing: the K steps are issued shape by shape (K launches of each), events at shape boundaries
-    evs = [[[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(2)] for _ in SWEEP]
+    # ---- device-resident timing: the K steps are issued shape by shape (K launches of each), events at shape boundaries.
+    # The K-step block is repeated (`rounds`) until at least a second of device time has been measured, so that the
+    # clock sampler sees the GPU under load; every figure is the mean over all rounds.
     sampler = ClockSampler(local)
     barrier()
     sampler.start()
-    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    # Hold the stream busy while the host enqueues the first launches, so that the events measure device
-    # time of back-to-back launches and not the host's launch rate (the end-to-end figure below keeps it).
-    torch.cuda._sleep(int(5e6))
-    launches_before = launch_count()
-    t_start.record()
-    for mi, M in enumerate(SWEEP):
-        run_shape(M, True, args.steps, evs[mi][0])
-        run_shape(M, False, args.steps, evs[mi][1])
-    t_end.record()
-    timed_launches = launch_count() - launches_before
+    seg = np.zeros((len(SWEEP), 2))
+    total_ms, rounds, timed_launches = 0.0, 0, 0
+    while True:
+        evs = [[[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(2)] for _ in SWEEP]
+        t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # Hold the stream busy while the host enqueues the first launches, so that the events measure device
+        # time of back-to-back launches and not the host's launch rate (the end-to-end figure below keeps it).
+        torch.cuda._sleep(int(5e6))
+        launches_before = launch_count()
+        t_start.record()
+        for mi, M in enumerate(SWEEP):
+            run_shape(M, True, args.steps, evs[mi][0])
+            run_shape(M, False, args.steps, evs[mi][1])
+        t_end.record()
+        timed_launches += launch_count() - launches_before
+        torch.cuda.synchronize()
+        total_ms += t_start.elapsed_time(t_end)
+        for mi in range(len(SWEEP)):
+            for o in range(2):
+                seg[mi, o] += evs[mi][o][0].elapsed_time(evs[mi][o][1]) / args.steps  # ms per launch
+        rounds += 1
+        flag = torch.tensor([1.0 if (total_ms >= args.min_seconds * 1e3 or rounds >= 500) else 0.0], device=dev)
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)  # every rank runs the same number of rounds
+        if flag.item() > 0:
+            break
     barrier()
     clocks = sampler.stop()
-    total_ms = t_start.elapsed_time(t_end)
-    seg = np.zeros((len(SWEEP), 2))
-    for mi in range(len(SWEEP)):
-        for o in range(2):
-            seg[mi, o] = evs[mi][o][0].elapsed_time(evs[mi][o][1]) / args.steps  # ms per launch
+    seg /= rounds
+    total_ms /= rounds
+    timed_launches //= rounds
+    _lib.assert_no_kernel_error()  # a kernel that gave up on a bounded wait finishes early: such a run is not a measurement
     # ---- end to end: host buffers in, host buffers out, through the public ops
     for _ in range(2):
         sweep(host=True)
@@ -317,6 +376,8 @@ def run_ours(args):
         for mi in range(len(SWEEP)):
             e2e_ms[mi] += e_evs[s][mi][0].elapsed_time(e_evs[s][mi][1])
     e2e_ms /= args.steps
+    _lib.assert_no_kernel_error()
+    parity = parity_spot_check(sets[0], w_cpu, xs_host, dev) if rank == 0 else None
 
     dec = [i for i, M in enumerate(SWEEP) if M <= DECODE_MAX_M]
     pre = [i for i, M in enumerate(SWEEP) if M > DECODE_MAX_M]
@@ -325,8 +386,12 @@ def run_ours(args):
     pre_flops = sum(op_flops(SWEEP[i], True) + op_flops(SWEEP[i], False) for i in pre)
     pre_ms = float(sum(seg[i].sum() for i in pre))
     stats = torch.tensor([total_ms, dec_ms, pre_ms, float(sum(e2e_ms[i] for i in dec))], device=dev, dtype=torch.float64)
+    per_rank = [stats.clone() for _ in range(world)]
     if world > 1:
+        dist.all_gather(per_rank, stats)
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    per_rank_dec_ms = [round(float(t[1]), 5) for t in per_rank]
+    per_rank_e2e_ms = [round(float(t[3]), 5) for t in per_rank]
     total_ms, dec_ms, pre_ms, e2e_dec_ms = [float(v) for v in stats.cpu()]
     pk = peaks()
     value = world * dec_bytes / (dec_ms * 1e-3) / 1e9
@@ -351,6 +416,9 @@ def run_ours(args):
             "config": workload_config(),
             "prefill": {"tflops": world * pre_flops / (pre_ms * 1e-3) / 1e12 if pre_ms > 0 else None, "unit": "TFLOP/s",
                         "frac_of_bf16_peak": pre_flops / (pre_ms * 1e-3) / 1e12 / pk["bf16_tflops"] if pre_ms > 0 else None,
+                        # the prefill kernel issues kind::mxf8f6f4 MMAs, which run at the 8-bit rate (twice the bf16 rate)
+                        "frac_of_issued_kind_peak": pre_flops / (pre_ms * 1e-3) / 1e12 / (2 * pk["bf16_tflops"]) if pre_ms > 0 else None,
+                        "issued_kind_peak": "2 x the bf16 cuBLAS burst figure (no 8-bit GEMM peak is measured on this pool)",
                         "peak_src": pk["src"]},
             "roofline": {"bound": "hbm",
                          "kernel": f"MXFP4 gate/up pair GEMM, M={SWEEP[dom]} (tcgen05: qlinear_tc4_kernel, kind::mxf4, for M <= 32; "
@@ -358,6 +426,7 @@ def run_ours(args):
                                    if F.mxfp4_path() == "tc" else f"qlinear_stream gate/up pair, M={SWEEP[dom]}",
                          "achieved": dom_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": dom_gbs / pk["hbm_gbs"],
                          "peak_src": pk["src"], "traffic": NCU_TRAFFIC.get(SWEEP[dom]),
+                         "traffic_src": "ncu capture summarised under profiles/, not measured in this run",
                          "duration": "CUDA events around K back-to-back launches of the op (activation-split kernel + GEMM kernel each), divided by K"},
             "kernels": kernels,
             "e2e": {"value": e2e_value, "unit": "GB/s",
@@ -365,6 +434,10 @@ def run_ours(args):
                     "d2h_bytes_per_step": sum(M * D_MODEL * 2 for M in SWEEP),
                     "scope": "same decode-shaped launches, pinned host X in and host Y out inside the timed region"},
             "gpu_launches": int(timed_launches),
+            "timed": {"rounds": rounds, "region_s": round(total_ms * rounds * 1e-3, 3),
+                      "note": "the K-step block is repeated until >= min_seconds of device time; figures are means over the rounds"},
+            "per_rank": {"decode_ms": per_rank_dec_ms, "e2e_decode_ms": per_rank_e2e_ms},
+            "kernel_errors": 0, "parity_check": parity,
             "clocks": clocks,
         }
         if world == 1:
@@ -374,31 +447,6 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def read_calibration():
-    """How fast can a plain streaming read of one launch's worth of weight bytes go on this GPU? Times a library
-    reduction (torch.sum over an int32 view) over rotating buffers of the gate/up pair's packed size and of
-    1 GiB, with the same enqueue-ahead event timing as the benchmark. Prints one JSON line."""
-    import torch
-    dev = torch.device("cuda", 0)
-    out = {}
-    for label, nbytes in (("pair_62MB", 2 * packed_bytes(D_FF, D_MODEL)), ("down_31MB", packed_bytes(D_MODEL, D_FF)), ("1GiB", 1 << 30)):
-        n = nbytes // 4
-        bufs = [torch.randint(0, 1 << 30, (n,), dtype=torch.int32, device=dev) for _ in range(10 if nbytes < (1 << 28) else 3)]
-        for b in bufs:
-            b.sum()
-        torch.cuda.synchronize()
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(20)]
-        torch.cuda._sleep(int(5e6))
-        for i, (a, b) in enumerate(evs):
-            a.record()
-            bufs[i % len(bufs)].sum()
-            b.record()
-        torch.cuda.synchronize()
-        ts = sorted(a.elapsed_time(b) for a, b in evs)
-        out[label] = {"us": round(ts[len(ts) // 2] * 1e3, 2), "gbs": round(nbytes / ts[len(ts) // 2] / 1e6, 1)}
-    print(json.dumps({"read_calibration": out, "peak_hbm_gbs": peaks()["hbm_gbs"]}))
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -406,10 +454,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ms", default="", help="comma-separated subset of the token counts to run (for profiler captures)")
-    ap.add_argument("--read-calibration", action="store_true", help="time a plain library read of the same byte counts and exit")
+    ap.add_argument("--min-seconds", type=float, default=1.0, help="repeat the K timed steps until this much device time was measured")
     args = ap.parse_args()
-    if args.read_calibration:
-        return read_calibration()
     if args.ms:
         global SWEEP
         SWEEP = [int(v) for v in args.ms.split(",")]

@@ -24,8 +24,17 @@ def build(force=False):
     so = os.path.join(_HERE, "libtpx_oracle.so")
     src = os.path.join(_HERE, "tpx_oracle.c")
     if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
-        subprocess.check_call(["make", "-C", _HERE, "--no-print-directory"], stdout=subprocess.DEVNULL)
+        subprocess.check_call(["make", "-C", _HERE, "--no-print-directory", "REF=" + reference_root()], stdout=subprocess.DEVNULL)
     return so
+
+
+def reference_root():
+    """Root of the reference's source tree: TPX_REFERENCE_ROOT, else a `reference` directory beside this repository;
+    "" when neither holds the MX header (the prebuilt shim under oracle/_ref is then kept as it is)."""
+    for cand in (os.environ.get("TPX_REFERENCE_ROOT", ""), os.path.join(_HERE, "..", "..", "reference")):
+        if cand and os.path.exists(os.path.join(cand, "src", "csrc", "mxfp_quant.h")):
+            return os.path.abspath(cand)
+    return ""
 
 
 def lib():
@@ -39,6 +48,7 @@ def lib():
         _LIB.orc_mxfp4_dequant_elem.restype = ctypes.c_float
         _LIB.orc_mxfp4_dequant_elem.argtypes = [ctypes.c_uint8, ctypes.c_uint8]
         _LIB.orc_num_threads.restype = ctypes.c_int
+        _LIB.orc_set_num_threads.argtypes = [ctypes.c_int]
     return _LIB
 
 

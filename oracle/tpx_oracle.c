@@ -52,6 +52,15 @@ static inline float bits_f32(uint32_t u) {
   return v.f;
 }
 
+/* Launchers export OMP_NUM_THREADS=1 to the ranks they start; a timed run asks for the host's cores explicitly. */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

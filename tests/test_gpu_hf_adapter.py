@@ -55,11 +55,11 @@ def test_adapter_matches_hugging_face_forward(cuda, family):
         assert type(runner.layers[0]).__name__ == "Qwen2DecoderLayer"
     logits, cache = runner.forward(ids.to(cuda))
     got = logits[:, -1].float().cpu()
-    assert float((got - want).abs().max()) <= 3e-2 * float(want.abs().max())
+    assert float((got - want).abs().max()) <= 2e-2 * float(want.abs().max())
     # one decode step against Hugging Face run on the extended sequence
     nxt = want.argmax(-1, keepdim=True)
     with torch.no_grad():
         want2 = model(torch.cat([ids, nxt], 1)).logits[:, -1].float()
     logits2, _ = runner.forward(nxt.to(cuda), cache=cache)
     got2 = logits2[:, -1].float().cpu()
-    assert float((got2 - want2).abs().max()) <= 3e-2 * float(want2.abs().max())
+    assert float((got2 - want2).abs().max()) <= 2e-2 * float(want2.abs().max())

@@ -71,7 +71,7 @@ def test_tiny_llama_matches_oracle(cuda):
         logits, cache = runner.forward(torch.from_numpy(nxt[:, None]).to(cuda), cache=cache)
         past += 1
         got = logits[:, -1].float().cpu().numpy()
-        assert np.max(np.abs(got - ref_logits)) <= 3e-2 * np.max(np.abs(ref_logits))
+        assert np.max(np.abs(got - ref_logits)) <= 2e-2 * np.max(np.abs(ref_logits))
         nxt = ref_logits.argmax(-1)
         gpu_next = got.argmax(-1)
     # generate: eager and CUDA-graph decoding agree token for token, and with the oracle's first tokens

@@ -120,3 +120,21 @@ def test_repack_roundtrip_mxfp4(cuda):
                 want = 0
                 assert sc[nt, kt, r, b] == 0
             assert got == want, (n, k)
+
+
+@pytest.mark.parametrize("K,block", [(256, 32), (192, 256), (4096, 128)])
+def test_quantize_qint8_block_sizes(cuda, K, block):
+    """Block sizes other than the default: 32 (twice as many scales as blocks of 64), a request that does not divide K
+    (the reference falls back to a smaller power of two, src/csrc/qtypes.cpp:881-888), and a bad one refused."""
+    from tpp_pytorch_extension_b200 import _lib
+    from tpp_pytorch_extension_b200._C import _qtype
+    rng = np.random.default_rng(K + block)
+    w = O.randn_bf16(rng, (32, K), 0.02)
+    wb = O.block_weight(w)
+    q = _qtype.remap_and_quantize_qint8(to_dev_bf16(wb, cuda), block)
+    qq, ss, bs = O.remap_and_quantize_qint8(w, block)
+    assert q.block_size == bs and tuple(q.codes.shape) == qq.shape and tuple(q.scales.shape) == ss.shape
+    assert np.array_equal(q.codes.cpu().numpy(), qq)
+    assert np.array_equal(q.scales.cpu().numpy().view(np.uint32), ss.view(np.uint32))
+    with pytest.raises(_lib.TpxError):
+        _qtype.remap_and_quantize_qint8(to_dev_bf16(wb, cuda), 0)

@@ -79,7 +79,7 @@ def test_tensor_parallel_two_gpus_matches_one():
     l2, e2, g2, captured = results[2]
     l1, l2, e1, e2, g2 = (torch.tensor(v) for v in (l1, l2, e1, e2, g2))
     # bf16 all-reduces round differently from one fp32 accumulation: logits agree to bf16 accuracy
-    assert float((l1 - l2).abs().max()) <= 3e-2 * float(l1.abs().max())
+    assert float((l1 - l2).abs().max()) <= 2e-2 * float(l1.abs().max())
     assert torch.equal(e2, g2), "graph decoding differs from eager decoding under tensor parallelism"
     assert captured, "the decode step was not captured in a CUDA graph under tensor parallelism"
     assert torch.equal(e1[:, :ids.shape[1] + 1], e2[:, :ids.shape[1] + 1]), "first generated token differs"

@@ -3,6 +3,7 @@ and the layout facts the CUDA kernels rely on."""
 import ctypes
 
 import numpy as np
+import pytest
 
 from oracle import oracle as O
 
@@ -187,3 +188,21 @@ def test_empty_and_ragged():
     wd = np.ones((16, 64), np.float32)
     y = O.qlinear(np.zeros((0, 64), np.uint16), wd)
     assert y.shape == (0, 16)
+
+
+def test_qint8_block_size_rule_matches_oracle():
+    """The block size remap_and_quantize_qint8 ends up with (src/csrc/qtypes.cpp:878-889), host-side rule of the package
+    against the oracle's remap on the same shapes: a divisor is kept, otherwise the next power of two below the request,
+    otherwise the blocked tensor's own inner block."""
+    from tpp_pytorch_extension_b200._C._qtype import qint8_block_size_used
+    from tpp_pytorch_extension_b200 import _lib
+    for K, req in [(4096, 256), (4096, 64), (4096, 32), (11008, 256), (192, 256), (320, 128), (14336, 512)]:
+        wb = O.block_weight(np.zeros((16, K), dtype=np.uint16))
+        _, bs = O.remap_qint8(wb, req)
+        assert qint8_block_size_used(K, wb.shape[2] * wb.shape[4], req) == bs, (K, req, bs)
+    assert qint8_block_size_used(4096, 64, 32) == 32
+    assert qint8_block_size_used(192, 64, 256) == 64    # 128 and 64 are tried: 64 divides 192
+    assert qint8_block_size_used(96, 32, 256) == 32     # nothing from 4096 to 64 divides 96: the tensor's own block
+    for bad in (0, -4, 6):
+        with pytest.raises(_lib.TpxError):
+            qint8_block_size_used(4096, 64, bad)

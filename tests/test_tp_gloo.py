@@ -63,7 +63,30 @@ def _worker(rank, world, port, q):
         b0 = lin2.bias.data.clone()
         LC.ShardLinear(lin2, 1, rank, world, 64)
         ok_row = lin2.weight.shape[1] == [64, 128][rank] and torch.allclose(lin2.bias.data, b0 / world)
-        q.put((rank, err, bool(ok_uneven), bool(ok_row), None))
+        # fc_plain with parallel_dim 0 (column-parallel, uneven all-gather of the outputs) and 1 (row-parallel, the
+        # input split by split_sizes, all-reduce): fc_plain_wrap of the reference, src/csrc/llm/fused_llm_infer.cpp:1514-1566.
+        # The single-rank linear underneath is replaced by a CPU one: what is under test is the host logic around it.
+        from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+        F.set_pg(dist.group.WORLD)
+        g = torch.Generator().manual_seed(5)
+        wfull = torch.randn(192, 128, generator=g)
+        bfull = torch.randn(192, generator=g)
+        xin = torch.randn(3, 128, generator=g)
+        real_fc = F.fc_plain
+        F.fc_plain = lambda x, w, b=None, parallel_dim=-1, split_sizes=(): torch.nn.functional.linear(x, w, b)
+        try:
+            split0 = [64, 128]  # 3 blocks of 64 over 2 ranks
+            lo = sum(split0[:rank])
+            y0 = LC.fc_plain_parallel(xin, wfull[lo:lo + split0[rank]], bfull[lo:lo + split0[rank]], 0, split0)
+            ok_gather = torch.allclose(y0, torch.nn.functional.linear(xin, wfull, bfull), atol=1e-5)
+            split1 = [64, 64]
+            w1 = torch.randn(16, 128, generator=g)
+            b1 = torch.randn(16, generator=g)
+            y1 = LC.fc_plain_parallel(xin, w1[:, 64 * rank:64 * rank + 64].contiguous(), b1 / world, 1, split1)
+            ok_reduce = torch.allclose(y1, torch.nn.functional.linear(xin, w1, b1), atol=1e-4)
+        finally:
+            F.fc_plain = real_fc
+        q.put((rank, err, bool(ok_uneven), bool(ok_row and ok_gather and ok_reduce), None))
         dist.destroy_process_group()
     except Exception as e:  # surface the failure in the parent instead of hanging it
         q.put((rank, None, False, False, repr(e)))

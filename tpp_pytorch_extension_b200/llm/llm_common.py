@@ -156,6 +156,13 @@ def fc_plain_parallel(input, weight, bias, parallel_dim, split_sizes):
         fused_llm_cpp.allreduce(y)
         return y
     y = fused_llm_cpp.fc_plain(input, weight, bias)
-    outs = [y.new_empty(y.shape[:-1] + (s,)) for s in split_sizes]
-    dist.all_gather(outs, y)
-    return torch.cat(outs, dim=-1)
+    if len(split_sizes) != get_size():
+        raise ValueError("Length of split vector doesn't match group size")
+    # ranks may own different numbers of output features (ShardLinear cuts in whole blocks); the collective moves
+    # equal-sized pieces, so every rank sends its slice padded to the widest one
+    widest = max(split_sizes)
+    if y.shape[-1] != widest:
+        y = torch.nn.functional.pad(y, (0, widest - y.shape[-1]))
+    outs = [y.new_empty(y.shape) for _ in split_sizes]
+    dist.all_gather(outs, y.contiguous(), group=fused_llm_cpp._pg)
+    return torch.cat([o[..., :s] for o, s in zip(outs, split_sizes)], dim=-1)
