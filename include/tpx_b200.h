@@ -101,12 +101,6 @@ int tpx_repack_mxfp4(const uint8_t* codes, const uint8_t* scales, int64_t N, int
                      uint8_t* pk_scales, void* stream);
 int tpx_repack_qint8(const int8_t* q, const float* scales, int64_t N, int64_t K, int64_t block_size,
                      uint8_t* pk_codes, float* pk_scales, void* stream);
-/* The packed int8 weight back as a plain bf16 matrix [N][K] = bf16(q * scale). Used for many-token calls (prefill)
- * of int8 weights, which run as a dense bf16 GEMM on the unpacked weight; the decode-sized calls stream the packed
- * tiles. No counterpart in the reference (its int8 path quantises the activations instead, fused_gemm.h:1249). */
-int tpx_unpack_qint8_bf16(const uint8_t* pk_codes, const float* pk_scales, int64_t N, int64_t K, int64_t block_size,
-                          uint16_t* out, void* stream);
-
 /* ---------------------------------------------------------------- quantized linear
  * Replaces GemmCaller / fc_plain with a post-op (src/csrc/fused_gemm.h:1509-1650) and
  * torch.ops.tpp_llm.fc_plain (src/csrc/llm/fused_llm_infer.cpp:1514-1566):
@@ -174,8 +168,22 @@ int tpx_qlinear_mxfp4_tc_static(const uint8_t* wq, const uint8_t* sfa, int pair,
                                 int64_t N, int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in,
                                 const uint16_t* res, float res_scale, uint16_t* y, void* stream);
 
+/* ---------------------------------------------------------------- bf16-weight linear on the tcgen05 tensor cores
+ * Replaces fc_plain on an unquantized bf16 weight (TppBlockedLinearW<bf16>, src/csrc/fused_gemm.h:784-1073, reached from
+ * torch.ops.tpp_llm.fc_plain, src/csrc/llm/fused_llm_infer.cpp:1514-1566): on the decoder path this is the lm_head, which
+ * the reference leaves in bf16 unless it is asked to quantize it (examples/llm/run_generation.py:277-282).
+ *     y[M][N] = epilogue(x[M][K] . w[N][K]^T + bias[N]),   epilogue as for tpx_qlinear
+ * w is the plain row-major weight (nn.Linear.weight), not re-laid out; K a multiple of 8; any M and N. fp32
+ * accumulation, one bf16 rounding at the store. The scratch (tpx_linear_bf16_tc_scratch_bytes, 64 KiB, zero before
+ * first use, 256-byte aligned) only carries the error word of the bounded waits at byte 65532.                    */
+size_t tpx_linear_bf16_tc_scratch_bytes(int64_t M, int64_t N, int64_t K);
+int tpx_linear_bf16_tc(const uint16_t* w, const uint16_t* x, int64_t M, int64_t N, int64_t K, const uint16_t* bias, int act,
+                       const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y, void* scratch,
+                       size_t scratch_bytes, void* stream);
+
 /* ---------------------------------------------------------------- int8 linear on the tcgen05 tensor cores
- * Up to 64 tokens with the reference's own int8 arithmetic (TppBlockedQInt8LinearW, src/csrc/fused_gemm.h:1075-1341):
+ * Any number of tokens (tiles of 16, 32, 64 or 128 tokens x 128 features) with the reference's own int8 arithmetic
+ * (TppBlockedQInt8LinearW, src/csrc/fused_gemm.h:1075-1341):
  * the activations are quantised on the fly to int8 with one scale per (token, K block) (:1249), each K block is an
  * int8 x int8 -> int32 product and y accumulates tmp * s_x * s_w (:1197-1204); the running sum stays in fp32 where
  * the reference rounds it to bf16 after every block. wq is the plain int8 weight [ceil(N/128)*128][ceil(K/128)*128]

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-2
 
 
-@pytest.fixture(autouse=True, params=["tc", "tc_wide", "tc_f4", "stream"])
+@pytest.fixture(autouse=True, params=["tc", "tc_wide", "tc_f4", "tc_w4", "stream"])
 def mxfp4_path(request):
     """Every case runs on each MXFP4 kernel family: the tcgen05 kernel with the weights on the 128-row side of the MMA,
     the tcgen05 kernel with the weights on the wide side (up to 64 tokens), the packed-fp4 tcgen05 kernel (up to 32
@@ -21,6 +21,7 @@ def mxfp4_path(request):
     with knob_env(TPX_MXFP4_PATH="stream" if request.param == "stream" else "tc",
                   TPX_TC_WIDE="1" if request.param == "tc_wide" else "0",
                   TPX_TC_F4="1" if request.param == "tc_f4" else "0",
+                  TPX_TC_W4="1" if request.param == "tc_w4" else "0",
                   TPX_INT8_PATH="stream" if request.param == "stream" else "tc"):
         yield request.param
 
@@ -133,7 +134,7 @@ def test_int8_many_tokens(cuda):
 
 
 @pytest.mark.parametrize("block", [64, 256])
-@pytest.mark.parametrize("M", [1, 7, 16, 33, 64])
+@pytest.mark.parametrize("M", [1, 7, 16, 33, 64, 100, 128, 300])
 def test_int8_tensor_core_kernel_matches_reference_arithmetic(cuda, M, block):
     """The tcgen05 kind::i8 kernel (activations quantised per K block, int32 block products, fp32 scaling) against the
     oracle's restatement of the reference's int8 arithmetic and against the weight-only fp32 oracle; post-ops, a gate/up

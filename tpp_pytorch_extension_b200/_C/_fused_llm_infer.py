@@ -32,7 +32,7 @@ def int8_path():
 
 
 def _int8_tc(x, y, w, w2, bias, act, mul_in, res, res_scale, norm=None):
-    """Up to 64 tokens on int8 weights through tpx_qlinear_qint8_tc; a gate/up pair runs as two calls, the second
+    """int8 weights through tpx_qlinear_qint8_tc (any number of tokens); a gate/up pair runs as two calls, the second
     multiplying by the activated first."""
     L = _lib.lib()
     N, K = w.out_features, w.in_features
@@ -62,9 +62,49 @@ def _int8_tc(x, y, w, w2, bias, act, mul_in, res, res_scale, norm=None):
     return y
 
 
+def _bf16_linear(x, w, bias, act, mul_in, res, res_scale):
+    """Unquantized bf16 weight, plain [N, K] (nn.Linear.weight) or blocked 5-D [N/bk, K/bc, bc/2, bk, 2]
+    (BlockedParameter.block(), un-blocked once and cached on the tensor): tpx_linear_bf16_tc."""
+    _lib.require_cuda(x, "input")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise _lib.TpxError("fc_plain: bf16 input and bf16 weight expected")
+    if w.dim() == 5:
+        plain = getattr(w, "_tpx_plain", None)
+        if plain is None:
+            from ..utils.blocked_layout import unblock_weight
+            plain = unblock_weight(w)
+            try:
+                w._tpx_plain = plain
+            except Exception:
+                pass
+        w = plain
+    if w.dim() != 2 or not w.is_contiguous():
+        raise _lib.TpxError("fc_plain: the bf16 weight must be a contiguous [out_features, in_features] matrix")
+    N, K = w.shape
+    if x.shape[-1] != K:
+        raise _lib.TpxError(f"fc_plain: input features {x.shape[-1]} do not match weight in-features {K}")
+    if not x.is_contiguous():
+        x = x.contiguous()
+    M = x.numel() // K
+    y = torch.empty(x.shape[:-1] + (N,), dtype=torch.bfloat16, device=x.device)
+    for name, t in (("bias", bias), ("mul_in", mul_in), ("res", res)):
+        if t is not None and t.numel() > 0:
+            _lib.require_cuda(t, name)
+            if t.dtype != torch.bfloat16:
+                raise _lib.TpxError(f"fc_plain: {name} must be bfloat16")
+    sc = _lib.scratch(1 << 16, x.device)
+    _lib.check(_lib.lib().tpx_linear_bf16_tc(w.data_ptr(), x.data_ptr(), M, N, K, _lib.ptr(bias), ACT[act], _lib.ptr(mul_in),
+                                             _lib.ptr(res), float(res_scale), y.data_ptr(), sc.data_ptr(), sc.numel(), _lib.stream()))
+    return y
+
+
 def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
+    if isinstance(w, torch.Tensor) and w2 is None:
+        if norm is not None:
+            x = rms_norm(x, norm[0], norm[1])
+        return _bf16_linear(x, w, bias, act, mul_in, res, res_scale)
     if not isinstance(w, QTensor):
-        raise _lib.TpxError("fc_plain: weight must be a quantized tensor from remap_and_quantize_*")
+        raise _lib.TpxError("fc_plain: weight must be a quantized tensor from remap_and_quantize_* or a bf16 tensor")
     _lib.require_cuda(x, "input")
     if x.dtype != torch.bfloat16:
         raise _lib.TpxError("fc_plain: input must be bfloat16")
@@ -107,7 +147,7 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
         if rc:
             _lib.check(rc)
         return y
-    if w.kind != 1 and 0 < M <= 64 and int8_path() == "tc" and w.block_size in (64, 128, 256, 512):
+    if w.kind != 1 and M > 0 and int8_path() == "tc" and w.block_size in (64, 128, 256, 512):
         if w2 is not None and (w2.out_features, w2.in_features, w2.kind, w2.block_size) != (N, K, w.kind, w.block_size):
             raise _lib.TpxError("gate/up weights must have the same shape and quantization")
         if norm is not None and not (K <= 8192 and w.block_size <= 256):
@@ -121,8 +161,6 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
         if (w2.out_features, w2.in_features, w2.kind, w2.block_size) != (N, K, w.kind, w.block_size):
             raise _lib.TpxError("gate/up weights must have the same shape and quantization")
         pc2, ps2 = w2.packed()
-    if w.kind != 1 and M > INT8_DENSE_MIN_M:
-        return _int8_dense(x, y, w, w2, pc, ps, pc2, ps2, bias, act, mul_in, res, res_scale)
     key = (w.kind, min(M, 32), N, K, w.block_size, w2 is not None)
     nb = _SCRATCH_BYTES.get(key)
     if nb is None:
@@ -133,41 +171,6 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
                        float(res_scale), y.data_ptr(), sc.data_ptr(), sc.numel(), _lib.stream())
     if rc:
         _lib.check(rc)
-    return y
-
-
-INT8_DENSE_MIN_M = 64
-
-
-def _int8_dense(x, y, w, w2, pc, ps, pc2, ps2, bias, act, mul_in, res, res_scale):
-    """Many tokens on int8 weights: the streaming kernel takes 32 tokens per pass over the weight, so prefill-sized
-    calls unpack the weight to bf16 once per call (tpx_unpack_qint8_bf16, 3 bytes of traffic per weight) and run a
-    dense bf16 GEMM on it (cuBLAS through torch: a plain library GEMM), with the post-ops applied in fp32 after it."""
-    L = _lib.lib()
-    N, K = w.out_features, w.in_features
-    x2 = x.reshape(-1, K)
-
-    def dense(codes, scales):
-        wb = torch.empty((N, K), dtype=torch.bfloat16, device=x.device)
-        _lib.check(L.tpx_unpack_qint8_bf16(codes.data_ptr(), scales.data_ptr(), N, K, w.block_size, wb.data_ptr(), _lib.stream()))
-        return torch.matmul(x2, wb.t()).float()
-
-    v = dense(pc, ps)
-    if bias is not None and bias.numel() > 0:
-        v = v + bias.float()
-    if act == "gelu":
-        v = torch.nn.functional.gelu(v)
-    elif act == "silu":
-        v = torch.nn.functional.silu(v)
-    elif act == "relu":
-        v = torch.relu(v)
-    if w2 is not None:
-        v = v * dense(pc2, ps2)
-    if mul_in is not None and mul_in.numel() > 0:
-        v = v * mul_in.reshape(-1, N).float()
-    if res is not None and res.numel() > 0:
-        v = v + res.reshape(-1, N).float() * float(res_scale)
-    y.copy_(v.to(torch.bfloat16).view(y.shape))
     return y
 
 
@@ -189,6 +192,11 @@ def fc_plain_act(input, weight, bias=None, act=None, mul_in=None, res=None, res_
 def fc_gate_up(input, w_gate, w_up, act="silu", norm=None):
     """act(x.Wg^T) * (x.Wu^T) in one pass over both weights (src/csrc/llm/fused_llm_infer.cpp:1271-1272).
     norm = (gamma, eps): RMSNorm of the input first, fused into the linear where the kernel family supports it."""
+    if isinstance(w_gate, torch.Tensor):  # bf16 weights: two passes, the second multiplying by the activated first
+        if norm is not None:
+            input = rms_norm(input, norm[0], norm[1])
+        g = _bf16_linear(input, w_gate, None, act, None, None, 1.0)
+        return _bf16_linear(input, w_up, None, None, g, None, 1.0)
     return _qlinear(input, w_gate, w_up, None, act, None, None, 1.0, norm)
 
 
@@ -282,22 +290,27 @@ class LlamaDecoderLayer:
                 ws = [w if isinstance(w, _qtype.QTensor) else _qtype.remap_and_quantize_mxfp4(w) for w in ws]
             elif os.environ.get("USE_QINT8", "0") == "1":
                 ws = [w if isinstance(w, _qtype.QTensor) else _qtype.remap_and_quantize_qint8(w) for w in ws]
+            elif all(isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16 for w in ws):
+                # unquantized bf16 weights (the reference's default): plain [N, K] matrices for the bf16 kernel
+                from ..utils.blocked_layout import unblock_weight
+                ws = [unblock_weight(w) if w.dim() == 5 else w.contiguous() for w in ws]
             else:
-                raise _lib.TpxError("LlamaDecoderLayer: unquantized weights are not built on this path; pass "
-                                    "weight_dtype='mxfp4' or 'qint8' (or set USE_MXFP4=1 / USE_QINT8=1)")
+                raise _lib.TpxError("LlamaDecoderLayer: weights must be all quantized tensors or all bf16 tensors")
         Wq, Wk, Wv, self.Wp, self.Wg, self.Wu, self.Wd = ws
         self.layer_idx, self.eps, self.H = int(layer_idx), float(eps), int(H)
         self.max_positions, self.rotary_dim = int(max_positions), int(rotary_dim)
-        self.Nq = Wq.out_features // self.H
-        self.Nkv = Wk.out_features // self.H
-        self.Wqkv = _cat_q([Wq, Wk, Wv])
+        self.bf16 = isinstance(Wq, torch.Tensor)
+        self.Nq = (Wq.shape[0] if self.bf16 else Wq.out_features) // self.H
+        self.Nkv = (Wk.shape[0] if self.bf16 else Wk.out_features) // self.H
+        self.Wqkv = torch.cat([Wq, Wk, Wv], 0).contiguous() if self.bf16 else _cat_q([Wq, Wk, Wv])
         self.Bqkv = None  # Qwen2DecoderLayer sets the fused q/k/v bias
         if self.EP.dtype != torch.float32 or tuple(self.EP.shape[:1]) != (2,):
             raise _lib.TpxError("embed_positions must be fp32 [2, max_positions, rotary_dim]")
         self.EP = self.EP.contiguous()
-        for w in (self.Wqkv, self.Wp, self.Wd):
-            w.prepare()
-        self.Wg.prepare(pair_with=self.Wu)
+        if not self.bf16:
+            for w in (self.Wqkv, self.Wp, self.Wd):
+                w.prepare()
+            self.Wg.prepare(pair_with=self.Wu)
 
     def forward(self, inp, cache, use_cache=True, dev_len=None):
         """inp = [hidden_states [B,S,D] bf16, additive mask [B,Spad], position_ids int64 [1 or B, S]]

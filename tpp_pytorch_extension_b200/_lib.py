@@ -35,12 +35,13 @@ _SIGS = {
                                      c_vp, c_sz, c_vp]),
     "tpx_rmsnorm_qlinear_mxfp4_tc": (c_int, [c_vp, c_vp, c_int, c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp,
                                              c_f32, c_vp, c_vp, c_sz, c_vp]),
-    "tpx_unpack_qint8_bf16": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp]),
     "tpx_tc_packed_bytes_qint8": (c_int, [c_i64, c_i64, c_i64, c_vp, c_vp]),
     "tpx_repack_qint8_tc": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "tpx_qlinear_qint8_tc_scratch_bytes": (c_sz, [c_i64, c_i64, c_i64, c_i64]),
     "tpx_qlinear_qint8_tc": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_i64, c_i64, c_int, c_vp, c_int, c_vp, c_vp, c_f32,
                                      c_vp, c_vp, c_sz, c_vp]),
+    "tpx_linear_bf16_tc_scratch_bytes": (c_sz, [c_i64, c_i64, c_i64]),
+    "tpx_linear_bf16_tc": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp, c_f32, c_vp, c_vp, c_sz, c_vp]),
     "tpx_launch_count": (ctypes.c_ulonglong, []),
     "tpx_debug_tc_timeline": (None, [c_vp]),  # exported only by a -DTPX_DEBUG build
     "tpx_qlinear_mxfp4_tc_static_status": (c_int, [c_vp, ctypes.POINTER(ctypes.c_uint)]),

@@ -1,4 +1,4 @@
-// int8 linear for up to 64 tokens on the tcgen05 tensor cores, with the reference's own arithmetic.
+// int8 linear on the tcgen05 tensor cores, with the reference's own arithmetic, for any number of tokens.
 //
 // Replaces TppBlockedQInt8LinearW (src/csrc/fused_gemm.h:1075-1341): activations are quantised on the fly to int8 with
 // one scale per (token, K block) (quantize_int8sym, :1249), every K block is an int8 x int8 -> int32 product
@@ -11,8 +11,9 @@
 // Difference to the reference, inside the parity tolerance: the running output is kept in fp32, where the reference
 // rounds it to bf16 after every K block.
 //
-// Work split: one output tile (128 features) per CTA; when tiles are few, a thread-block cluster per tile cuts K
-// between its CTAs, which add their parts over distributed shared memory.
+// Work split: one output tile (128 features x TOK tokens, TOK = 16, 32, 64 or, for more than 64 tokens, 128) per CTA;
+// when tiles are few, a thread-block cluster per tile cuts K between its CTAs, which add their parts over distributed
+// shared memory.
 #include "tpx_tc_ptx.cuh"
 
 namespace tpx {
@@ -27,6 +28,8 @@ struct I8Params {
   int bsteps;          // k32 steps per scale block (B / 32)
   int Np;              // features padded to 128
   int nblk;            // scale blocks of the real K (the k padding of the last step has none)
+  int tilesN;          // feature tiles; CTA (or cluster) t works on feature tile t % tilesN, token tile t / tilesN
+  int Mp;              // tokens padded to whole token tiles: row stride of sx
 };
 
 __device__ __forceinline__ void i8_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -202,8 +205,8 @@ struct I8Cfg {
   static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES + 1023) / 1024 * 1024;
   static constexpr int STAGES_FIT = (227 * 1024 - 3072) / STAGE_BYTES;   // as many stages as shared memory holds: the bytes in
   static constexpr int STAGES = STAGES_FIT > kI8MaxStages ? kI8MaxStages : STAGES_FIT;  // flight bound the stream, not the MMAs
-  static constexpr int GROUP = 4;             // accumulators per group; a group (up to 4 K blocks, 256 k values or one larger block)
-                                              // is handed to the epilogue per barrier round trip
+  static constexpr int GROUP = TOK >= 128 ? 2 : 4;  // accumulators per group; a group (up to GROUP K blocks, 256 k values or one
+                                                    // larger block) is handed to the epilogue per barrier round trip
   static constexpr int NBUF = 512 / TOK > 16 ? 16 : 512 / TOK;  // int32 accumulators (one per K block) in tensor memory
   static constexpr int NGRP = NBUF / GROUP;
   static constexpr int TMEM_COLS = NBUF * TOK < 32 ? 32 : NBUF * TOK;
@@ -225,7 +228,8 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   const uint32_t smem_base = (tc_smem_u32(i8_smem_raw) + 1023u) & ~1023u;
   const int csize = p.t.cluster;
   const int crank = csize > 1 ? (int)tc_cluster_rank() : 0;
-  const int tile = blockIdx.x / csize;
+  const int tile = (int)(blockIdx.x / csize) % p.tilesN;  // feature tile
+  const int tm = (int)(blockIdx.x / csize) / p.tilesN;    // token tile
   // K range of this CTA in k steps, aligned to whole scale blocks
   const int align = p.bsteps > 4 ? p.bsteps / 4 : 1;  // k steps per scale block when a block spans several
   const int groups = p.ksteps / align;
@@ -277,7 +281,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           if (!tc_wait(tc_smem_u32(&bar_empty[s]), (uint32_t)((it / C::STAGES - 1) & 1))) { atomicExch(p.t.err, 2u); break; }
           fetch_w(s, ks0 + it);
         }
-        tc_tma_2d(smem_base + (uint32_t)s * C::STAGE_BYTES + C::A_BYTES, &tmX, (ks0 + it) * 128, 0, tc_smem_u32(&bar_full[s]));
+        tc_tma_2d(smem_base + (uint32_t)s * C::STAGE_BYTES + C::A_BYTES, &tmX, (ks0 + it) * 128, tm * TOK, tc_smem_u32(&bar_full[s]));
       }
     }
     __syncwarp();
@@ -290,7 +294,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       uint32_t free_phase = 0;  // bit g: parity to wait for on d_free[g]
       unsigned used = 0;        // bit g: group g has been handed out before
       const int nblocks = nsteps * 4 / p.bsteps;
-      const int gsize = p.bsteps >= 8 ? 1 : 8 / p.bsteps;  // blocks per group: 256 k values, or one larger block
+      const int gsize = p.bsteps >= 8 ? 1 : (8 / p.bsteps < C::GROUP ? 8 / p.bsteps : C::GROUP);  // blocks per group: 256 k values, or one larger block
       int done_blocks = 0;
       for (int it = 0; it < nsteps; it++) {
         const int s = it % C::STAGES;
@@ -337,7 +341,8 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const int blk0 = ks0 * 4 / p.bsteps;
     uint32_t full_phase = 0;
     constexpr bool kPrefetchSx = TOK * C::GROUP <= 128;  // activation scales of a whole group in registers
-    const int gsize = p.bsteps >= 8 ? 1 : 8 / p.bsteps;
+    const int gsize = p.bsteps >= 8 ? 1 : (8 / p.bsteps < C::GROUP ? 8 / p.bsteps : C::GROUP);
+    const float* sx_tile = p.sx + (size_t)tm * TOK;  // this token tile's columns of sx [K/B][Mp]
     int b = 0, buf = 0;
     bool dead = false;
     while (b < nblocks && !dead) {
@@ -345,14 +350,14 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const int cnt = nblocks - b < gsize ? nblocks - b : gsize;
       // scales of the group's blocks are fetched before the wait (a block of pure k padding has none: zeros)
       float sw[C::GROUP];
-      float sxg[kPrefetchSx ? C::GROUP : 1][TOK];
+      float sxg[kPrefetchSx ? C::GROUP : 1][kPrefetchSx ? TOK : 1];
 #pragma unroll
       for (int q = 0; q < C::GROUP; q++) {
         const int blk = blk0 + b + q;
         const bool real = q < cnt && blk < p.nblk;
         sw[q] = real ? p.swT[(size_t)blk * p.Np + n] : 0.0f;
         if (kPrefetchSx) {
-          const float4* sxp = reinterpret_cast<const float4*>(p.sx + (size_t)(real ? blk : 0) * TOK);
+          const float4* sxp = reinterpret_cast<const float4*>(sx_tile + (size_t)(real ? blk : 0) * p.Mp);
 #pragma unroll
           for (int i = 0; i < TOK / 4; i++) {
             const float4 v = sxp[i];
@@ -374,23 +379,23 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 #pragma unroll
       for (int q = 0; q < C::GROUP; q++) {
         if (q < cnt) {
-          if (!kPrefetchSx) {
-            const int blk = blk0 + b + q;
-            const float4* sxp = reinterpret_cast<const float4*>(p.sx + (size_t)(blk < p.nblk ? blk : 0) * TOK);
-#pragma unroll
-            for (int i = 0; i < TOK / 4; i++) {
-              const float4 v = sxp[i];
-              sxg[0][4 * i] = v.x; sxg[0][4 * i + 1] = v.y; sxg[0][4 * i + 2] = v.z; sxg[0][4 * i + 3] = v.w;
-            }
-          }
-          const float* sxv = sxg[kPrefetchSx ? q : 0];
+          const int blk = blk0 + b + q;
+          const float4* sxp = reinterpret_cast<const float4*>(sx_tile + (size_t)(blk < p.nblk ? blk : 0) * p.Mp);
 #pragma unroll
           for (int c0 = 0; c0 < TOK; c0 += 16) {
+            float sxc[16];
+            if (!kPrefetchSx) {  // many tokens: the scales of 16 tokens at a time (they sit in L1 after the first warp's read)
+#pragma unroll
+              for (int i = 0; i < 4; i++) {
+                const float4 v = sxp[c0 / 4 + i];
+                sxc[4 * i] = v.x; sxc[4 * i + 1] = v.y; sxc[4 * i + 2] = v.z; sxc[4 * i + 3] = v.w;
+              }
+            }
             uint32_t d[16];
             tc_ld_x16(tmem + lane_base + (buf + q) * TOK + c0, d);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int i = 0; i < 16; i++) acc[c0 + i] += (float)(int)d[i] * sxv[c0 + i] * sw[q];
+            for (int i = 0; i < 16; i++) acc[c0 + i] += (float)(int)d[i] * (kPrefetchSx ? sxg[q][c0 + i] : sxc[i]) * sw[q];
           }
         }
       }
@@ -406,7 +411,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         float v[16], v2[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) { v[i] = acc[c0 + i]; v2[i] = 0.0f; }
-        if (n < p.t.N && c0 < p.t.M) tc_finish16<false>(p.t, c0, n, v, v2);
+        if (n < p.t.N && tm * TOK + c0 < p.t.M) tc_finish16<false>(p.t, tm * TOK + c0, n, v, v2);
       }
     } else {
       const uint32_t sp = smem_base + (uint32_t)(row * TOK * 4);
@@ -437,7 +442,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             v[4 * q] += t4.x; v[4 * q + 1] += t4.y; v[4 * q + 2] += t4.z; v[4 * q + 3] += t4.w;
           }
         }
-        if (n < p.t.N && c0 < p.t.M) tc_finish16<false>(p.t, c0, n, v, v2);
+        if (n < p.t.N && tm * TOK + c0 < p.t.M) tc_finish16<false>(p.t, tm * TOK + c0, n, v, v2);
       }
     }
     tc_cluster_sync();
@@ -450,18 +455,20 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
 // ---------------------------------------------------------------- host side
 struct I8Plan {
-  int tokp, ksteps, tiles, cluster;
-  int64_t Kp, Np;
+  int tokp, ksteps, tiles, cluster, TM;  // tiles = feature tiles x token tiles
+  int64_t Kp, Np, Mp;
   size_t off_xq, off_sx, total;
 };
 
 static I8Plan i8_plan(int64_t M, int64_t N, int64_t K, int64_t B) {
   I8Plan pl;
-  pl.tokp = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+  pl.tokp = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  pl.TM = (int)((M + pl.tokp - 1) / pl.tokp);
+  pl.Mp = (int64_t)pl.TM * pl.tokp;
   pl.Kp = (K + 127) / 128 * 128;
   pl.Np = (N + 127) / 128 * 128;
   pl.ksteps = (int)(pl.Kp / 128);
-  pl.tiles = (int)(pl.Np / 128);
+  pl.tiles = (int)(pl.Np / 128) * pl.TM;
   const int sms = sm_count();
   const int groups = (int)(B > 128 ? pl.ksteps / (B / 128) : pl.ksteps);  // units a cluster can cut K into
   int c = pl.tiles > 0 ? sms / pl.tiles : 1;
@@ -470,8 +477,8 @@ static I8Plan i8_plan(int64_t M, int64_t N, int64_t K, int64_t B) {
   pl.cluster = c < 1 ? 1 : c;
   size_t o = kTcCounterBytes;
   auto bump = [&](size_t bytes) { size_t r = o; o += (bytes + 1023) & ~(size_t)1023; return r; };
-  pl.off_xq = bump((size_t)pl.tokp * pl.Kp);
-  pl.off_sx = bump((size_t)(K / B) * pl.tokp * sizeof(float));
+  pl.off_xq = bump((size_t)pl.Mp * pl.Kp);
+  pl.off_sx = bump((size_t)(K / B) * pl.Mp * sizeof(float));
   pl.total = o;
   return pl;
 }
@@ -581,7 +588,7 @@ extern "C" int tpx_qlinear_qint8_tc(const int8_t* wq, const float* swT, const ui
                                     const uint16_t* res, float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream) {
   TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear_qint8_tc: bad shape");
   if (M == 0) return TPX_OK;
-  TPX_REQUIRE(M <= 64, TPX_ERR_UNSUPPORTED, "qlinear_qint8_tc: at most 64 tokens per call (M=%ld)", (long)M);
+  TPX_REQUIRE(M <= (1 << 20), TPX_ERR_UNSUPPORTED, "qlinear_qint8_tc: at most 2^20 tokens per call (M=%ld)", (long)M);
   TPX_REQUIRE(wq && swT && x && y, TPX_ERR_ARG, "qlinear_qint8_tc: null pointer");
   TPX_REQUIRE(block_size == 64 || block_size == 128 || block_size == 256 || block_size == 512, TPX_ERR_UNSUPPORTED,
               "qlinear_qint8_tc: block size %ld not supported (64, 128, 256, 512)", (long)block_size);
@@ -597,30 +604,32 @@ extern "C" int tpx_qlinear_qint8_tc(const int8_t* wq, const float* swT, const ui
   unsigned char* sc = reinterpret_cast<unsigned char*>(scratch);
   int8_t* xq = reinterpret_cast<int8_t*>(sc + pl.off_xq);
   float* sx = reinterpret_cast<float*>(sc + pl.off_sx);
-  if (!reuse_act && pl.Kp != K) TPX_CUDA_OK(cudaMemsetAsync(xq, 0, (size_t)pl.tokp * pl.Kp, st));  // the k padding reads as zero
+  if (!reuse_act && pl.Kp != K) TPX_CUDA_OK(cudaMemsetAsync(xq, 0, (size_t)pl.Mp * pl.Kp, st));  // the k padding reads as zero
   TPX_REQUIRE(!gamma || (K <= 8192 && block_size <= 256 && ((uintptr_t)gamma & 15) == 0), TPX_ERR_UNSUPPORTED,
               "qlinear_qint8_tc: the fused RMSNorm takes rows of up to 8192 values, blocks of up to 256 and a 16-byte aligned gamma");
   if (!reuse_act && block_size <= 256) {
-    TPX_CUDA_OK(launch_pdl(quantize_act_i8_row_kernel, dim3((unsigned)pl.tokp), dim3(kQaThreads), 0, st, x, gamma, gamma_is_f32, eps, (int)M,
-                           (int)K, (int)pl.Kp, (int)block_size, pl.tokp, xq, sx));
+    TPX_CUDA_OK(launch_pdl(quantize_act_i8_row_kernel, dim3((unsigned)pl.Mp), dim3(kQaThreads), 0, st, x, gamma, gamma_is_f32, eps, (int)M,
+                           (int)K, (int)pl.Kp, (int)block_size, (int)pl.Mp, xq, sx));
   } else if (!reuse_act) {
-    const int threads = pl.tokp * (int)(K / block_size);
+    const long long threads = (long long)pl.Mp * (K / block_size);
     TPX_CUDA_OK(launch_pdl(quantize_act_i8_kernel, dim3((unsigned)((threads + 127) / 128)), dim3(128), 0, st, x, (int)M, (int)K, (int)pl.Kp,
-                           (int)block_size, pl.tokp, xq, sx));
+                           (int)block_size, (int)pl.Mp, xq, sx));
   }
   CUtensorMap mw, mx;
   int rc = make_map_u8(&mw, wq, (uint64_t)pl.Np, (uint64_t)pl.Kp, 128);
   if (rc) return rc;
-  rc = make_map_u8(&mx, xq, (uint64_t)pl.tokp, (uint64_t)pl.Kp, (uint32_t)pl.tokp);
+  rc = make_map_u8(&mx, xq, (uint64_t)pl.Mp, (uint64_t)pl.Kp, (uint32_t)pl.tokp);
   if (rc) return rc;
   I8Params p = {};
   p.t.bias = bias; p.t.mul_in = mul_in; p.t.res = res; p.t.res_scale = res_scale; p.t.y = y; p.t.act = act;
   p.t.M = (int)M; p.t.N = (int)N; p.t.K = (int)K; p.t.cluster = pl.cluster;
   p.t.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
   p.swT = swT; p.sx = sx; p.ksteps = pl.ksteps; p.bsteps = (int)(block_size / 32); p.Np = (int)pl.Np; p.nblk = (int)(K / block_size);
+  p.tilesN = (int)(pl.Np / 128); p.Mp = (int)pl.Mp;
   switch (pl.tokp) {
     case 16: return i8_launch<16>(mw, mx, p, pl.tiles, st);
     case 32: return i8_launch<32>(mw, mx, p, pl.tiles, st);
-    default: return i8_launch<64>(mw, mx, p, pl.tiles, st);
+    case 64: return i8_launch<64>(mw, mx, p, pl.tiles, st);
+    default: return i8_launch<128>(mw, mx, p, pl.tiles, st);
   }
 }

@@ -933,7 +933,16 @@ static bool tc_wide(int64_t M, int64_t N, int64_t K, bool pair) {
 // its q/k/v and gate/up linears on this family: 2.76 against 2.66 ms/token). Not where few tiles cut K inside a
 // cluster either (down projection: 19.4 against 18.7 us at M = 8). TPX_TC_F4=1 selects it for every M <= 32,
 // TPX_TC_F4=0 never.
+constexpr int kW4AutoMaxTokens = 0;  // token counts up to which family 3 is chosen without being asked for
 static int tc_kind(int64_t M, int64_t N, int64_t K, bool pair) {
+  // 3 = weights on the N side with packed-fp4 operands (tpx_qlinear_tcw4.cu): the default up to 32 tokens wherever its
+  // work split applies (whole tiles or a cluster per tile), unless a test forces another family; TPX_TC_W4=1 selects it
+  // for every shape it serves (up to 64 tokens), TPX_TC_W4=0 never.
+  {
+    const int w4 = knobs().tc_w4;
+    const bool other_forced = knobs().tc_f4 >= 0 || knobs().tc_wide >= 0;
+    if (w4 != 0 && (w4 > 0 || (!other_forced && M <= kW4AutoMaxTokens)) && tcw4_serves(M, N, K, pair)) return 3;
+  }
   if (M <= 32) {
     const int forced = knobs().tc_f4;
     const long long T = (N + 127) / 128;  // one token tile up to 32 tokens
@@ -945,7 +954,8 @@ static int tc_kind(int64_t M, int64_t N, int64_t K, bool pair) {
 }
 
 static size_t tc_scratch_need(int64_t M, int64_t N, int64_t K, bool pair, int kind) {
-  return kind == 2 ? tc4_scratch_bytes(M, N, K, pair) : kind == 1 ? tcw_scratch_bytes(M, N, K, pair) : tc_plan(M, N, K, pair).total;
+  return kind == 3 ? tcw4_scratch_bytes(M, N, K, pair) : kind == 2 ? tc4_scratch_bytes(M, N, K, pair) : kind == 1 ? tcw_scratch_bytes(M, N, K, pair)
+                   : tc_plan(M, N, K, pair).total;
 }
 
 extern "C" size_t tpx_qlinear_mxfp4_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int pair) {
@@ -965,6 +975,11 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   TPX_REQUIRE(((uintptr_t)wq & 31) == 0 && ((uintptr_t)sfa & 15) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)scratch & 255) == 0,
               TPX_ERR_ARG, "qlinear_mxfp4_tc: misaligned pointer");
   const bool dual = pair != 0;
+  if (kind == 3) {
+    TcParams b = {};
+    b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act;
+    return tcw4_run(wq, sfa, dual, x, M, N, K, b, scratch, scratch_bytes, (cudaStream_t)stream, norm);
+  }
   if (kind == 2) {
     TcParams b = {};
     b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act; b.tl = g_tc_timeline;

@@ -300,37 +300,6 @@ extern "C" int tpx_dequantize_qint8(const int8_t* q, const float* scales, int64_
   return TPX_OK;
 }
 
-// Packed int8 tiles (the streaming layout of repack_qint8_kernel) -> plain bf16 weight [N][K] = bf16(q * scale).
-// One thread per packed word (4 consecutive k of one row).
-__global__ void unpack_qint8_bf16_kernel(const uint32_t* __restrict__ pk, const float* __restrict__ pks, int64_t N, int64_t K,
-                                         int64_t B, uint16_t* __restrict__ out) {
-  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t KT = K / 64;
-  if (idx >= (N / 16) * KT * 256) return;
-  const int b = idx & 3, lane = (idx >> 2) & 31, h = (idx >> 7) & 1;
-  const int64_t tile = idx >> 8, kt = tile % KT, nt = tile / KT;
-  const int g = lane >> 2, t = lane & 3;
-  const int64_t n = nt * 16 + g + 8 * h, k = kt * 64 + 16 * b + 4 * t;
-  const float sc = pks[(nt * (K / B) + k / B) * 16 + (g + 8 * h)];
-  const uint32_t w = pk[idx];
-  uint16_t o[4];
-#pragma unroll
-  for (int i = 0; i < 4; i++) o[i] = f32_to_bf16_bits((float)(int8_t)((w >> (8 * i)) & 0xff) * sc);
-  *reinterpret_cast<uint2*>(out + n * K + k) = make_uint2((uint32_t)o[0] | ((uint32_t)o[1] << 16), (uint32_t)o[2] | ((uint32_t)o[3] << 16));
-}
-
-extern "C" int tpx_unpack_qint8_bf16(const uint8_t* pk_codes, const float* pk_scales, int64_t N, int64_t K, int64_t block_size,
-                                     uint16_t* out, void* stream) {
-  TPX_REQUIRE(pk_codes && pk_scales && out, TPX_ERR_ARG, "unpack_qint8_bf16: null pointer");
-  TPX_REQUIRE(N % 16 == 0 && K % 64 == 0 && block_size % 64 == 0 && K % block_size == 0, TPX_ERR_ARG,
-              "unpack_qint8_bf16: needs N %% 16 == 0, K %% 64 == 0 and a block size that is a multiple of 64 dividing K");
-  int64_t total = (N / 16) * (K / 64) * 256;
-  unpack_qint8_bf16_kernel<<<blocks_for(total, 256), 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const uint32_t*>(pk_codes), pk_scales, N,
-                                                                                      K, block_size, out);
-  TPX_LAUNCH_OK();
-  return TPX_OK;
-}
-
 extern "C" int tpx_packed_bytes(int kind, int64_t N, int64_t K, int64_t block_size, size_t* codes_bytes,
                                 size_t* scales_bytes) {
   TPX_REQUIRE(N > 0 && K > 0 && N % 16 == 0, TPX_ERR_ARG, "packed_bytes: N must be a positive multiple of 16");

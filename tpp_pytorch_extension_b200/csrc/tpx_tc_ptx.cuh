@@ -249,4 +249,9 @@ int tc4_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x,
 size_t tcw_scratch_bytes(int64_t M, int64_t N, int64_t K, bool pair);
 int tcw_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x, int64_t M, int64_t N, int64_t K, const TcParams& base,
             void* scratch, size_t scratch_bytes, cudaStream_t st, const TcNorm* norm = nullptr);
+// weights on the N side, packed-fp4 operands, up to 64 tokens (up to 8 without an activation kernel): tpx_qlinear_tcw4.cu
+bool tcw4_serves(int64_t M, int64_t N, int64_t K, bool pair);
+size_t tcw4_scratch_bytes(int64_t M, int64_t N, int64_t K, bool pair);
+int tcw4_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x, int64_t M, int64_t N, int64_t K, const TcParams& base,
+             void* scratch, size_t scratch_bytes, cudaStream_t st, const TcNorm* norm = nullptr);
 }  // namespace tpx

@@ -33,6 +33,7 @@ def main(argv=None):
     ap.add_argument("--num-warmup", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="keep only this many decoder layers (0 = all)")
     ap.add_argument("--no-graph", action="store_true", help="decode eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--quantize-lm-head", action="store_true", help="quantize the lm_head like the decoder linears (bf16 otherwise)")
     a = ap.parse_args(argv)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -48,7 +49,8 @@ def main(argv=None):
         import dataclasses
         shape = dataclasses.replace(shape, num_hidden_layers=a.layers)
     wd = {"bfloat16": "bf16"}.get(a.weight_dtype, a.weight_dtype)
-    model = FL.build_random_llama(shape, wd, "cuda", max_positions=a.input_tokens + a.max_new_tokens + 8)
+    model = FL.build_random_llama(shape, wd, "cuda", max_positions=a.input_tokens + a.max_new_tokens + 8,
+                                  quantize_lm_head=a.quantize_lm_head and wd != "bf16")
     g = torch.Generator(device="cpu").manual_seed(1234)
     ids = torch.randint(0, shape.vocab_size, (a.batch_size, a.input_tokens), generator=g).cuda()
 

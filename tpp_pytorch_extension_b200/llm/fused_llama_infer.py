@@ -72,7 +72,8 @@ def make_layer(shape, weights, layer_idx, ep, weight_dtype, device):
         layer = fused_llm_cpp.LlamaDecoderLayer(params + [ep], layer_idx, shape.rms_norm_eps, H, ep.shape[1], H)
     # the interchange tensors are no longer needed once the streaming layouts exist
     for w in (layer.Wqkv, layer.Wp, layer.Wd, layer.Wg, layer.Wu):
-        w.codes = w.codes.new_empty(0)
+        if hasattr(w, "codes"):
+            w.codes = w.codes.new_empty(0)
     return layer
 
 
@@ -83,7 +84,6 @@ class LlamaRunner(torch.nn.Module):
         # lm_head stays bf16 as in the reference unless it is quantized separately; with tensor parallelism it is
         # row-parallel followed by an all-reduce (fused_llama_infer.py:218-224)
         self.lm_head_w = lm_head_w
-        self.lm_split = [lm_head_w.shape[1]] if get_size() == 1 else None
         self.only_last_logit = True
 
     def _head(self, hs):
@@ -91,13 +91,18 @@ class LlamaRunner(torch.nn.Module):
         if self.only_last_logit:
             hs = hs[:, -1:, :]
         hs = fused_llm_cpp.rms_norm(hs.contiguous(), self.norm_w, self.shape.rms_norm_eps)
+        # lm_head_w is a bf16 matrix (the reference's default) or a quantized tensor (its --quantize-lm-head): both go
+        # through fc_plain, i.e. this library's own tensor-core kernels
         if get_size() > 1:
             offs = shard_offsets(self.shape.hidden_size, get_size(), 64)
             r = get_rank()
-            logits = torch.nn.functional.linear(hs[..., offs[r]:offs[r + 1]], self.lm_head_w)
+            logits = fused_llm_cpp.fc_plain(hs[..., offs[r]:offs[r + 1]].contiguous(), self.lm_head_w)
             fused_llm_cpp.allreduce(logits)
-            return logits
-        return torch.nn.functional.linear(hs, self.lm_head_w)
+        else:
+            logits = fused_llm_cpp.fc_plain(hs, self.lm_head_w)
+        if logits.shape[-1] != self.shape.vocab_size:  # a quantized head padded to whole row groups
+            logits = logits[..., :self.shape.vocab_size]
+        return logits
 
     @torch.no_grad()
     def forward(self, input_ids, attention_mask=None, position_ids=None, cache=None):
@@ -195,7 +200,19 @@ def _lm_head_shard(w):
     return w[:, offs[r]:offs[r + 1]].contiguous()
 
 
-def build_random_llama(shape, weight_dtype="mxfp4", device="cuda", seed=0, std=0.02, max_positions=None):
+def _lm_head(w, quantize, weight_dtype):
+    """This rank's lm_head: bf16 as it is, or quantized like the decoder linears (examples/llm/run_generation.py:277-282)."""
+    w = _lm_head_shard(w)
+    if not quantize:
+        return w
+    if w.shape[0] % 32:  # vocabularies that are not a whole number of MXFP4 row groups get zero rows
+        w = torch.nn.functional.pad(w, (0, 0, 0, 32 - w.shape[0] % 32))
+    q = quantize_weight(w, weight_dtype)
+    q.prepare(drop_interchange=True)
+    return q
+
+
+def build_random_llama(shape, weight_dtype="mxfp4", device="cuda", seed=0, std=0.02, max_positions=None, quantize_lm_head=False):
     """Random N(0, std) linears and embeddings, unit norm weights, quantized layer by layer on the device.
     Every tensor-parallel rank draws the same full weights (same seed) and keeps its shard."""
     llm_common.set_pg()
@@ -216,11 +233,11 @@ def build_random_llama(shape, weight_dtype="mxfp4", device="cuda", seed=0, std=0
              "up": rnd(FF, D), "down": rnd(D, FF), "ln1": torch.ones(D), "ln2": torch.ones(D)}
         layers.append(make_layer(shape, w, i, ep, weight_dtype, dev))
         del w
-    lm = _lm_head_shard(rnd(shape.vocab_size, D))
+    lm = _lm_head(rnd(shape.vocab_size, D), quantize_lm_head, weight_dtype)
     return LlamaRunner(shape, embed, layers, torch.ones(D, device=dev, dtype=torch.bfloat16), lm, ep)
 
 
-def OptimizeModelForLlama(model, dtype=torch.bfloat16, device="cuda", weight_dtype="mxfp4"):
+def OptimizeModelForLlama(model, dtype=torch.bfloat16, device="cuda", weight_dtype="mxfp4", quantize_lm_head=False):
     """Reference entry point (fused_llama_infer.py:176-233) for a Hugging Face LlamaForCausalLM."""
     if dtype != torch.bfloat16:
         raise ValueError("the CUDA path computes in bfloat16")
@@ -243,13 +260,13 @@ def OptimizeModelForLlama(model, dtype=torch.bfloat16, device="cuda", weight_dty
              "down": l.mlp.down_proj.weight.data, "ln1": l.input_layernorm.weight.data, "ln2": l.post_attention_layernorm.weight.data})
         layers.append(make_layer(shape, w, i, ep, weight_dtype, dev))
     embed = model.model.embed_tokens.weight.data.to(dev, torch.bfloat16)
-    lm = _lm_head_shard(model.lm_head.weight.data.to(dev, torch.bfloat16))
+    lm = _lm_head(model.lm_head.weight.data.to(dev, torch.bfloat16), quantize_lm_head, weight_dtype)
     return LlamaRunner(shape, embed, layers, model.model.norm.weight.data.to(dev, torch.bfloat16), lm, ep)
 
 
-def OptimizeModelForQwen2(model, dtype=torch.bfloat16, device="cuda", weight_dtype="mxfp4"):
+def OptimizeModelForQwen2(model, dtype=torch.bfloat16, device="cuda", weight_dtype="mxfp4", quantize_lm_head=False):
     """Reference entry point llm/fused_qwen2_infer.py:OptimizeModelForQwen2: the same runner, layers carry q/k/v biases."""
-    return OptimizeModelForLlama(model, dtype, device, weight_dtype)
+    return OptimizeModelForLlama(model, dtype, device, weight_dtype, quantize_lm_head)
 
 
 LLAMA2_7B = LlamaShape(32, 4096, 32, 32, 11008, 32000, rms_norm_eps=1e-5, rope_theta=1e4)
