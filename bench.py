@@ -231,6 +231,121 @@ def parity_spot_check(wset, w_cpu, xs_host, dev):
             "scope": "M = 8, 256 sampled output features of each op, against the CPU oracle"}
 
 
+def model_bytes_per_step(shape, batch, context, world, lm_head_bf16=True):
+    """Algorithmic bytes ONE GPU reads per decode step: its shard of the MXFP4 decoder weights (0.53125 B per weight),
+    of the bf16 lm_head and of the KV cache (keys and values of `context` tokens per sequence)."""
+    D, H = shape.hidden_size, shape.head_dim
+    per_layer = (shape.num_attention_heads + 2 * shape.num_key_value_heads) * H * D + D * shape.num_attention_heads * H \
+        + 3 * shape.intermediate_size * D
+    w = shape.num_hidden_layers * per_layer * 0.53125
+    lm = shape.vocab_size * D * (2 if lm_head_bf16 else 0.53125)
+    kv = shape.num_hidden_layers * 2 * context * batch * shape.num_key_value_heads * H * 2
+    return (w + lm + kv) / world
+
+
+def model_decode_leg(name, shape, batch, context, steps, dev, world, rank, real_prefill):
+    """Greedy decode of `steps` tokens per sequence on a random-weight MXFP4 model of the named shape, tensor parallel
+    over the `world` ranks (all-reduce after o_proj, down_proj and lm_head), the step replayed as a CUDA graph. The
+    context is either prefilled for real (timed) or stands in as a random KV cache of the same shape."""
+    import torch
+    import torch.distributed as dist
+    from tpp_pytorch_extension_b200.llm import fused_llama_infer as FL
+    t0 = time.perf_counter()
+    torch.cuda.empty_cache()
+    runner = FL.build_random_llama(shape, "mxfp4", dev, max_positions=context + steps + 16)
+    torch.cuda.synchronize()
+    build_s = time.perf_counter() - t0
+    g = torch.Generator(device="cpu").manual_seed(1234)
+    out = {"model": name, "layers": shape.num_hidden_layers, "batch": batch, "context": context, "tensor_parallel": world,
+           "build_s": round(build_s, 1)}
+    mask = torch.ones((batch, context), dtype=torch.int64, device=dev)
+    if real_prefill:
+        ids = torch.randint(0, shape.vocab_size, (batch, context), generator=g).to(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        runner.forward(ids[:, :64])  # warm-up of the prefill kernels on a short prompt
+        torch.cuda.synchronize()
+        a.record()
+        logits, cache = runner.forward(ids, mask)
+        b.record()
+        torch.cuda.synchronize()
+        pre_ms = a.elapsed_time(b)
+        out["prefill_ms"] = round(pre_ms, 2)
+        out["prefill_tok_s"] = round(batch * context / (pre_ms * 1e-3), 1)
+        tok = logits[:, -1].argmax(-1, keepdim=True)
+        out["context_source"] = "prefilled in this run (timed)"
+    else:
+        cache = runner.synthetic_cache(batch, context, steps + 16)
+        tok = torch.randint(0, shape.vocab_size, (batch, 1), generator=g).to(dev)
+        out["context_source"] = "random KV cache of the prefilled shape (a decode step's cost does not depend on the values)"
+    timing = {}
+    runner.decode(tok, cache, mask, steps + 1, use_graph=True, timing=timing)
+    torch.cuda.synchronize()
+    ms = timing["events"][0].elapsed_time(timing["events"][1]) / max(1, timing["steps"])
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    bps = model_bytes_per_step(shape, batch, context + steps // 2, world)
+    pk = peaks()
+    out.update({"ms_per_step": round(ms, 4), "decode_tok_s": round(batch / (ms * 1e-3), 1), "timed_steps": timing["steps"],
+                "graph": runner.last_graph is not None,
+                "bytes_per_step_per_gpu": int(bps), "hbm_gbs_per_gpu": round(bps / (ms * 1e-3) / 1e9, 1),
+                "hbm_frac_of_peak": round(bps / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)})
+    if world > 1:  # the all-reduces of one step, timed alone (they cannot carry events inside the replayed graph)
+        D = shape.hidden_size
+        bufs = [torch.zeros((batch, D), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        lg = torch.zeros((batch, shape.vocab_size), dtype=torch.bfloat16, device=dev)
+        n = 2 * shape.num_hidden_layers
+        for _ in range(3):
+            dist.all_reduce(bufs[0])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(n):
+            dist.all_reduce(bufs[i & 1])
+        dist.all_reduce(lg)
+        b.record()
+        torch.cuda.synchronize()
+        ar = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
+        dist.all_reduce(ar, op=dist.ReduceOp.MAX)
+        out["allreduce"] = {"calls_per_step": n + 1, "payload_bytes": batch * D * 2, "ms_back_to_back": round(float(ar.item()), 4),
+                            "share_of_step": round(float(ar.item()) / ms, 3),
+                            "note": "NCCL all-reduces of one step issued back to back outside the graph; inside the step they sit between dependent kernels"}
+    del runner, cache
+    torch.cuda.empty_cache()
+    return out
+
+
+def tp_consistency_check(dev, world):
+    """Two layers of the tensor-parallel configuration's shape, same seeded weights: logits of the sharded model (this
+    run's ranks) against the unsharded model built on the same GPU. max |a - b| / max |b|."""
+    import dataclasses
+    import torch
+    from tpp_pytorch_extension_b200.llm import fused_llama_infer as FL
+    from tpp_pytorch_extension_b200.llm import llm_common as LC
+    shape = dataclasses.replace(FL.LLAMA2_70B, num_hidden_layers=2)
+    ids = torch.randint(0, shape.vocab_size, (4, 96), generator=torch.Generator().manual_seed(7)).to(dev)
+    sharded = FL.build_random_llama(shape, "mxfp4", dev, max_positions=256)
+    l_tp, _ = sharded.forward(ids)
+    del sharded
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    LC.tensor_parallel_enabled = False
+    pg = F._pg
+    try:
+        single = FL.build_random_llama(shape, "mxfp4", dev, max_positions=256)
+        F.set_pg(None)  # the layers ask the op module for the group size
+        l_1, _ = single.forward(ids)
+        del single
+    finally:
+        LC.tensor_parallel_enabled = True
+        F.set_pg(pg)
+    a, b = l_tp[:, -1].float(), l_1[:, -1].float()
+    err = float((a - b).abs().max() / b.abs().max())
+    torch.cuda.empty_cache()
+    return {"layers": 2, "tokens": "4 x 96", "max_rel_diff_vs_unsharded": err, "same_argmax": bool((a.argmax(-1) == b.argmax(-1)).all()),
+            "ranks": world}
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -442,6 +557,23 @@ def run_ours(args):
         }
         if world == 1:
             line["cpu_baseline"] = cpu_arm()
+    # ---- model-level decode legs (outside the timed region of the headline metric)
+    del sets
+    torch.cuda.empty_cache()
+    legs = {}
+    want = [v for v in args.legs.split(",") if v]
+    from tpp_pytorch_extension_b200.llm import fused_llama_infer as FL
+    import dataclasses
+    if "cfg4" in want and world == 1:
+        legs["config4_llama3_8b_mxfp4"] = model_decode_leg("Llama-3-8B shape, MXFP4", FL.LLAMA3_8B, 16, 2048, args.model_steps, dev, 1, 0, True)
+    if "cfg5" in want:
+        shape = FL.LLAMA2_70B if not args.cfg5_layers else dataclasses.replace(FL.LLAMA2_70B, num_hidden_layers=args.cfg5_layers)
+        if world > 1:
+            legs["config5_tp_consistency"] = tp_consistency_check(dev, world)
+        legs["config5_llama2_70b_mxfp4_tp"] = model_decode_leg("Llama-2-70B shape, MXFP4, tensor parallel", shape, 64, 4096, args.model_steps, dev,
+                                                               world, rank, False)
+    if rank == 0:
+        line["decode_models"] = legs
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -454,6 +586,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ms", default="", help="comma-separated subset of the token counts to run (for profiler captures)")
+    ap.add_argument("--legs", default="cfg4,cfg5", help="model-level decode legs to run after the op sweep: cfg4 (Llama-3-8B shape, one GPU), "
+                    "cfg5 (Llama-2-70B shape, tensor parallel over --gpus ranks); empty for none")
+    ap.add_argument("--model-steps", type=int, default=24, help="decode steps timed in each model-level leg")
+    ap.add_argument("--cfg5-layers", type=int, default=0, help="decoder layers of the 70B-shape leg (0 = all 80)")
     ap.add_argument("--min-seconds", type=float, default=1.0, help="repeat the K timed steps until this much device time was measured")
     args = ap.parse_args()
     if args.ms:

@@ -42,8 +42,10 @@ def test_argument_errors_are_reported(cuda):
         F.fc_plain(torch.zeros(3, 128, dtype=torch.float16, device=cuda), q)
     with pytest.raises(_lib.TpxError):  # host tensor
         F.fc_plain(torch.zeros(3, 128, dtype=torch.bfloat16), q)
-    with pytest.raises(_lib.TpxError):  # a plain tensor is not a quantized weight
-        F.fc_plain(torch.zeros(3, 128, dtype=torch.bfloat16, device=cuda), torch.zeros(64, 128, dtype=torch.bfloat16, device=cuda))
+    with pytest.raises(_lib.TpxError):  # a plain weight must be bf16 (then it runs on the bf16 kernel)
+        F.fc_plain(torch.zeros(3, 128, dtype=torch.bfloat16, device=cuda), torch.zeros(64, 128, dtype=torch.float32, device=cuda))
+    y = F.fc_plain(torch.zeros(3, 128, dtype=torch.bfloat16, device=cuda), torch.zeros(64, 128, dtype=torch.bfloat16, device=cuda))
+    assert y.shape == (3, 64) and y.abs().max().item() == 0.0
     q_other, _, _ = make_qweight(rng, 32, 128, "mxfp4", cuda)
     with pytest.raises(_lib.TpxError):  # gate/up of different shapes
         F.fc_gate_up(torch.zeros(3, 128, dtype=torch.bfloat16, device=cuda), q, q_other)

@@ -3,6 +3,7 @@
 import torch
 
 from .. import _lib
+from .. import _timers
 from ._qtype import QTensor
 
 import os
@@ -325,7 +326,17 @@ class LlamaDecoderLayer:
         scale = 1.0 / ws
         L = _lib.lib()
         res = hs.reshape(B * S, D)
-        qkv = fc_plain_norm(res, self.Gi, self.eps, self.Wqkv, self.Bqkv)
+        T = B * S
+        sc = _timers.scope
+
+        def wbytes(w):  # bytes a linear has to read for its weight (packed codes + scales, or bf16)
+            return w.numel() * 2 if isinstance(w, torch.Tensor) else (w.numel() * 17 // 32 if w.kind == 1 else w.numel() + 4 * w.numel() // w.block_size)
+
+        def nk(w):
+            return tuple(w.shape) if isinstance(w, torch.Tensor) else (w.out_features, w.in_features)
+
+        with sc("fqkv_gemm", 2 * T * nk(self.Wqkv)[0] * D, wbytes(self.Wqkv) + 2 * T * (D + nk(self.Wqkv)[0])):
+            qkv = fc_plain_norm(res, self.Gi, self.eps, self.Wqkv, self.Bqkv)
         lc = cache.layer(self.layer_idx)
         if dev_len is None:
             lc.ensure(B, self.Nkv, self.H, S, hs.dtype, hs.device)
@@ -333,22 +344,30 @@ class LlamaDecoderLayer:
         q = torch.empty((B, self.Nkv, S, R, self.H), dtype=hs.dtype, device=hs.device)
         if pos.dtype != torch.int64 or not pos.is_contiguous():
             pos = pos.to(torch.int64).contiguous()
-        _lib.check(L.tpx_rope_kv_update(qkv.data_ptr(), self.EP.data_ptr(), pos.data_ptr(), B, S, self.Nq, self.Nkv, self.H,
-                                        self.EP.shape[1], self.EP.shape[2], pos.shape[0], lc.offset, lc.capacity(),
-                                        _lib.ptr(dev_len), q.data_ptr(), lc.k.data_ptr(), lc.v.data_ptr(), _lib.stream()))
+        with sc("rotary", 0, 4 * T * (self.Nq + 2 * self.Nkv) * self.H):
+            _lib.check(L.tpx_rope_kv_update(qkv.data_ptr(), self.EP.data_ptr(), pos.data_ptr(), B, S, self.Nq, self.Nkv, self.H,
+                                            self.EP.shape[1], self.EP.shape[2], pos.shape[0], lc.offset, lc.capacity(),
+                                            _lib.ptr(dev_len), q.data_ptr(), lc.k.data_ptr(), lc.v.data_ptr(), _lib.stream()))
         if dev_len is None:
             lc.offset += S
             key_len = lc.offset
         else:
             key_len = lc.capacity()  # planning maximum; the kernels read the real length from dev_len
-        ctx = attention(q, lc.k, lc.v, am, key_len, causal=True, out_bsnrh=True, dev_len=dev_len).view(B * S, self.Nq * self.H)
-        so = fc_plain_act(ctx, self.Wp, res=res, res_scale=scale)
+        with sc("mha", 4 * T * self.Nq * self.H * key_len // (2 if S > 1 else 1), 4 * B * self.Nkv * self.H * key_len + 4 * T * self.Nq * self.H):
+            ctx = attention(q, lc.k, lc.v, am, key_len, causal=True, out_bsnrh=True, dev_len=dev_len).view(B * S, self.Nq * self.H)
+        with sc("proj_gemm", 2 * T * D * nk(self.Wp)[1], wbytes(self.Wp) + 2 * T * (2 * D + nk(self.Wp)[1])):
+            so = fc_plain_act(ctx, self.Wp, res=res, res_scale=scale)
         if ws > 1:
-            allreduce(so)
-        inter = fc_gate_up(so, self.Wg, self.Wu, "silu", norm=(self.Gpa, self.eps))
-        out = fc_plain_act(inter, self.Wd, res=so, res_scale=scale)
+            with sc("allred", 0, 2 * T * D):
+                allreduce(so)
+        FF = nk(self.Wg)[0]
+        with sc("i_gemm", 4 * T * FF * D, wbytes(self.Wg) + wbytes(self.Wu) + 2 * T * (D + FF)):
+            inter = fc_gate_up(so, self.Wg, self.Wu, "silu", norm=(self.Gpa, self.eps))
+        with sc("o_gemm", 2 * T * FF * D, wbytes(self.Wd) + 2 * T * (2 * D + FF)):
+            out = fc_plain_act(inter, self.Wd, res=so, res_scale=scale)
         if ws > 1:
-            allreduce(out)
+            with sc("allred", 0, 2 * T * D):
+                allreduce(out)
         out = out.view(B, S, D)
         if use_cache:
             return [out, lc.k, lc.v]

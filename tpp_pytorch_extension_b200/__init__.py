@@ -4,10 +4,7 @@ reference's Python names. The compute lives in the in-tree CUDA library (include
 from . import _lib  # noqa: F401
 
 
-def print_debug_timers(tid=0, detailed=True):
-    """The reference prints its per-scope CPU timers here (src/csrc/init.cpp:81-153); on the GPU, timing is taken
-    with CUDA events by the caller (bench.py), so this is an explicit no-op kept for API compatibility."""
+from ._timers import print_debug_timers, reset_debug_timers  # noqa: E402,F401
+from . import _torch_namespaces  # noqa: E402
 
-
-def reset_debug_timers():
-    """See print_debug_timers."""
+_torch_namespaces.install()

@@ -27,6 +27,7 @@ static void read_knobs() {
   g_knobs.tc_wide = env("TPX_TC_WIDE", -1);
   g_knobs.tc_f4 = env("TPX_TC_F4", -1);
   g_knobs.tc_w4 = env("TPX_TC_W4", -1);
+  g_knobs.tc4_occ = env("TPX_TC4_OCC", 1);
   g_knobs.tc_cluster = env("TPX_TC_CLUSTER", 1);
   g_knobs.tc_pf = env("TPX_TC_PF", 0);
   g_knobs.attn_splits = env("TPX_ATTN_SPLITS", 0);

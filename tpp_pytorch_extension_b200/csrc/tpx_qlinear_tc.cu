@@ -977,7 +977,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   const bool dual = pair != 0;
   if (kind == 3) {
     TcParams b = {};
-    b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act;
+    b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act; b.tl = g_tc_timeline;
     return tcw4_run(wq, sfa, dual, x, M, N, K, b, scratch, scratch_bytes, (cudaStream_t)stream, norm);
   }
   if (kind == 2) {

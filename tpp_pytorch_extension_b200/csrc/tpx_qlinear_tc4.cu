@@ -196,7 +196,10 @@ static int tc4_launch_split(const uint16_t* x, int M, int K, int Mpad, int KS, i
 
 // ---------------------------------------------------------------- the GEMM kernel
 // TOK tokens per tile (16 or 32), DUAL = gate/up pair, UKS = k steps (of 128) per pipeline unit.
-template <int TOK, bool DUAL, int UKS>
+// OCC = CTAs meant to share an SM: with 2, a CTA keeps to half of the shared memory and at most 256 columns of tensor
+// memory, so that the CTAs of the NEXT launch become resident (programmatic dependent launch) while this one still
+// streams: their prologue and their first weight stages then overlap this launch's stream instead of following it.
+template <int TOK, bool DUAL, int UKS, int OCC = 1>
 struct Tc4Cfg {
   static constexpr int NW = DUAL ? 2 : 1;
   static constexpr int A_BYTES = 128 * 64;             // a packed 128 x 128 tile, in shared memory as in HBM
@@ -211,7 +214,7 @@ struct Tc4Cfg {
   static constexpr int RAW = A_TILES * A_BYTES + X_ROWS * 64 + SF_BLOCKS * 512;
   static constexpr int STAGE_BYTES = (RAW + 1023) / 1024 * 1024;
   static constexpr int TX = RAW;
-  static constexpr int BUDGET = 227 * 1024 - 2048;
+  static constexpr int BUDGET = OCC == 2 ? 112 * 1024 - 1024 : 227 * 1024 - 2048;
   static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SF_COLS = SF_BLOCKS * 4;        // tensor-memory columns of one stage's scale factors
@@ -225,15 +228,16 @@ struct Tc4Cfg {
   static_assert(X_ROWS % X_BOX == 0, "activation rows are fetched in whole boxes");
   static_assert(STAGES >= 2, "at least two stages");
   static_assert(COLS_RAW <= 512, "tensor memory");
+  static_assert(OCC == 1 || COLS_RAW <= 256, "two CTAs per SM share the 512 columns");
   static_assert(STAGES * STAGE_BYTES >= NW * 128 * TOK * 4, "the stages hold a cluster member's partial tile");
 };
 
 constexpr int kTc4Threads = 224;  // + warp 6: scale-factor copies, issued apart from the MMAs
 
-template <int TOK, bool DUAL, int UKS>
-__global__ void __launch_bounds__(kTc4Threads, 1)
+template <int TOK, bool DUAL, int UKS, int OCC = 1>
+__global__ void __launch_bounds__(kTc4Threads, OCC)
 qlinear_tc4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, TcParams p) {
-  using C = Tc4Cfg<TOK, DUAL, UKS>;
+  using C = Tc4Cfg<TOK, DUAL, UKS, OCC>;
   extern __shared__ unsigned char tc4_smem_raw[];
   __shared__ __align__(8) unsigned long long bar_full[C::STAGES], bar_empty[C::STAGES], bar_sf[C::STAGES];
   __shared__ __align__(8) unsigned long long bar_acc_full, bar_acc_empty;
@@ -540,7 +544,7 @@ qlinear_tc4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
 // ---------------------------------------------------------------- host side
 struct Tc4Plan {
-  int tok, uks;
+  int tok, uks, occ;
   int TN, TM, KS, KU, Mpad, grid, xbox, whole_tiles, cluster;
   size_t off_terms, off_sfb, off_partial, total;
 };
@@ -550,7 +554,8 @@ struct Tc4Plan {
 static Tc4Plan tc4_plan(int64_t M, int64_t N, int64_t K, bool pair) {
   Tc4Plan pl;
   pl.tok = M <= 16 ? 16 : 32;
-  pl.uks = 2;
+  pl.occ = (knobs().tc4_occ == 2 && (pl.tok == 16 || !pair)) ? 2 : 1;
+  pl.uks = (pl.occ == 2 && pair) ? 1 : 2;
   pl.KS = tc_padded_ks(K, pair);
   pl.KU = pl.KS / pl.uks;
   pl.TN = (int)((N + 127) / 128);
@@ -581,14 +586,14 @@ static Tc4Plan tc4_plan(int64_t M, int64_t N, int64_t K, bool pair) {
   return pl;
 }
 
-template <int TOK, bool DUAL, int UKS>
+template <int TOK, bool DUAL, int UKS, int OCC = 1>
 static int tc4_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams& p, int grid, cudaStream_t st) {
-  using C = Tc4Cfg<TOK, DUAL, UKS>;
+  using C = Tc4Cfg<TOK, DUAL, UKS, OCC>;
   static bool opted[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 16 || !opted[dev]) {
-    TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_tc4_kernel<TOK, DUAL, UKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+    TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_tc4_kernel<TOK, DUAL, UKS, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     if (dev >= 0 && dev < 16) opted[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -616,7 +621,7 @@ static int tc4_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams
       int& f = fits[(dev >= 0 && dev < 16) ? dev : 0][c];
       if (f == 0) {
         int n = 0;
-        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, qlinear_tc4_kernel<TOK, DUAL, UKS>, &cc);
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, qlinear_tc4_kernel<TOK, DUAL, UKS, OCC>, &cc);
         if (e != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
         f = 1 + n;
       }
@@ -624,16 +629,16 @@ static int tc4_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams
         TcParams q = p;
         q.cluster = c;
         count_launch();
-        TPX_CUDA_OK(cudaLaunchKernelEx(&cc, qlinear_tc4_kernel<TOK, DUAL, UKS>, w, x, q));
+        TPX_CUDA_OK(cudaLaunchKernelEx(&cc, qlinear_tc4_kernel<TOK, DUAL, UKS, OCC>, w, x, q));
         return TPX_OK;
       }
     }
     TcParams q = p;
     q.cluster = 1;
-    return tc4_launch<TOK, DUAL, UKS>(w, x, q, grid, st);
+    return tc4_launch<TOK, DUAL, UKS, OCC>(w, x, q, grid, st);
   }
   count_launch();
-  TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tc4_kernel<TOK, DUAL, UKS>, w, x, p));
+  TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tc4_kernel<TOK, DUAL, UKS, OCC>, w, x, p));
   if (!p.whole_tiles && grid > 1) return tc_launch_fixup(DUAL, p, TOK, grid, st);  // tiles cut between CTAs
   return TPX_OK;
 }
@@ -663,6 +668,11 @@ int tc4_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x,
   p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = pl.TM;
   p.whole_tiles = pl.whole_tiles; p.cluster = pl.cluster;
+  if (pl.occ == 2) {
+    if (pair) return tc4_launch<16, true, 1, 2>(mw, mx, p, pl.grid, st);
+    if (pl.tok == 16) return tc4_launch<16, false, 2, 2>(mw, mx, p, pl.grid, st);
+    return tc4_launch<32, false, 2, 2>(mw, mx, p, pl.grid, st);
+  }
   if (pair) {
     if (pl.tok == 16) return tc4_launch<16, true, 2>(mw, mx, p, pl.grid, st);
     return tc4_launch<32, true, 2>(mw, mx, p, pl.grid, st);

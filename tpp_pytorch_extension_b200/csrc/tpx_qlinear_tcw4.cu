@@ -8,17 +8,20 @@
 // 128-row MMA costs ~100 cycles however few columns it has, and every 512-byte scale-factor copy costs about as much.
 // So each instruction should consume as many weight bytes as possible:
 //   B (256 rows) = 256 output features of packed E2M1 weights, as they lie in HBM: one MMA (K = 64) reads 8 KiB of them
-//   A (128 rows) = the activation terms: a bf16 value is four E2M1 terms with block scales 2^e, 2^(e-2), 2^(e-5), 2^(e-8)
-//                  (exact to 2^-10.5 of the 32-wide block maximum, as in tpx_qlinear_tc4.cu); the four terms of a token
-//                  are four ROWS of A inside one 32-lane quarter of tensor memory, so the epilogue adds them with two
-//                  warp shuffles
+//   A (128 rows) = the activation terms: a bf16 value x of a 32-wide block becomes the integer n = round(x / 2^s)
+//                  (2^s chosen so that the block maximum lands in (877, 1755]: exact to 2^-11..2^-10 of the block maximum),
+//                  and n + 2340 is written in base 8: n = sum_i (d_i - 4) * 8^i, digits d_i - 4 in [-4, 3], all of them
+//                  E2M1 values; term i carries the block scale 2^(s + 3i). Integer arithmetic only, no conversion
+//                  instructions. The four terms of a token are four ROWS of A inside one 32-lane quarter of tensor
+//                  memory, so the epilogue adds them with two warp shuffles
 //   D            = [token term][feature], 256 fp32 columns of tensor memory
 // Token-count classes (TOKP):
 //    8: up to 8 tokens, two per quarter. The activation terms of the CTA's whole K range are built by the CTA itself
 //       (its four epilogue warps, idle until the end otherwise) straight into shared memory, optionally behind the RMSNorm
-//       of the reference's decoder block (llama_rms_norm, src/csrc/llm/fused_llm_infer.cpp:336-363), and their scale
-//       factors are copied to tensor memory once: no activation kernel runs before the GEMM, no activation bytes travel
-//       through the pipeline stages, and one scale copy per k step is saved.
+//       of the reference's decoder block (llama_rms_norm, src/csrc/llm/fused_llm_infer.cpp:336-363): no activation kernel
+//       runs before the GEMM and no activation bytes travel through the pipeline stages. Where every CTA needs the whole
+//       K range (whole tiles), the CTAs of a thread-block cluster share the work: each builds the terms of some k steps and
+//       stores them into every member's shared memory (distributed shared memory).
 //   32: up to 32 tokens, eight per quarter; terms come from split4w_kernel through TMA, per stage.
 //   64: up to 64 tokens, sixteen per quarter; two A tiles (terms 0,1 and terms 2,3) accumulate into the same D.
 // Work split: whole 256-feature tiles per CTA when the tile count suits the SM count, else one thread-block cluster per
@@ -28,6 +31,7 @@
 namespace tpx {
 
 constexpr int kW4MaxStages = 8;
+constexpr int kW4ConvThreads = 384;  // TOKP 8: threads that build the activation terms (the four epilogue warps and eight more)
 
 template <int TOKP>
 struct W4Cfg {
@@ -41,10 +45,10 @@ struct W4Cfg {
   static constexpr int SFA1 = ATILES * 512;
   static constexpr int STAGE_RAW = UKS * (B1 + 1024 + (RES ? 0 : A1 + SFA1));
   static constexpr int STAGE_BYTES = (STAGE_RAW + 1023) / 1024 * 1024;
-  static constexpr int SFC = 8 + (RES ? 0 : 4 * ATILES);    // tensor-memory columns of one k step's scale factors in the ring
-  static constexpr int RING_COL0 = RES ? 384 : 256;         // D: [0, 256); resident activation scales: [256, 384)
-  static constexpr int MAX_RES_KSTEPS = 32;                 // 4 columns each
-  static_assert(RING_COL0 + kW4MaxStages * UKS * SFC <= 512 || !RES, "tensor memory");
+  static constexpr int SFC = 8 + 4 * ATILES;                // tensor-memory columns of one k step's scale factors in the ring
+  static constexpr int RING_COL0 = 256;                     // D: [0, 256)
+  static constexpr int MAX_RES_KSTEPS = 32;                 // 2.5 KiB of shared memory each
+  static_assert(RING_COL0 + kW4MaxStages * UKS * SFC <= 512, "tensor memory");
 };
 
 struct W4Params {
@@ -55,6 +59,7 @@ struct W4Params {
   float eps;
   int tiles128, ksteps;  // 128-feature tiles and k steps of the packed weight
   int stages;            // pipeline stages that fit beside the resident terms
+  int share;             // TOKP 8, whole tiles: CTAs per cluster that build the terms together (1: every CTA for itself)
 };
 
 // K-major operand of 64-byte rows, 64-byte swizzle, 8-row groups `sbo` bytes apart (512: plain; 128: groups overlap and
@@ -63,53 +68,112 @@ __device__ __forceinline__ uint64_t w4_desc64(uint32_t saddr, uint32_t sbo) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46) | (4ull << 61);
 }
 
-// Eight values (already divided into the block's range by the caller's scale choice) -> four words of eight E2M1 codes,
-// term after term; the residual after each term is exact in fp32.
-__device__ __forceinline__ void w4_terms(float (&r)[8], uint32_t (&packed)[4]) {
-#pragma unroll
-  for (int t = 0; t < 4; t++) {
-    uint32_t w, h0, h1, h2, h3;
-    asm("{ .reg .b8 b0, b1, b2, b3;\n"
-        "  cvt.rn.satfinite.e2m1x2.f32 b0, %6, %5;\n"
-        "  cvt.rn.satfinite.e2m1x2.f32 b1, %8, %7;\n"
-        "  cvt.rn.satfinite.e2m1x2.f32 b2, %10, %9;\n"
-        "  cvt.rn.satfinite.e2m1x2.f32 b3, %12, %11;\n"
-        "  mov.b32 %0, {b0, b1, b2, b3};\n"
-        "  cvt.rn.f16x2.e2m1x2 %1, b0;\n"
-        "  cvt.rn.f16x2.e2m1x2 %2, b1;\n"
-        "  cvt.rn.f16x2.e2m1x2 %3, b2;\n"
-        "  cvt.rn.f16x2.e2m1x2 %4, b3; }"
-        : "=r"(w), "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3)
-        : "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]));
-    packed[t] = w;
-    if (t < 3) {
-      const uint32_t h[4] = {h0, h1, h2, h3};
-      const float up = t == 0 ? 4.0f : 8.0f;
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const float2 q = __half22float2(*reinterpret_cast<const __half2*>(&h[j]));
-        r[2 * j] = (r[2 * j] - q.x) * up;
-        r[2 * j + 1] = (r[2 * j + 1] - q.y) * up;
-      }
-    }
-  }
-}
-
-// Block scale of a 32-wide block from its maximum: 2^e with the maximum in (3, 6]. The four lanes of a block call this
-// together (their eight-value maxima are combined with shuffles).
+// Block scale exponent s of a 32-wide block from its maximum: max / 2^s in (877, 1755]. The four lanes of a block call
+// this together (their eight-value maxima are combined with shuffles).
 __device__ __forceinline__ int w4_block_exp(const float (&f)[8]) {
   float amax = 0.0f;
 #pragma unroll
   for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(f[j]));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  int e = -119;
+  int sx = -120;
   if (amax > 0.0f && amax < INFINITY) {
-    e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 - 2;
-    e = max(-119, min(125, e));
-    if (amax * __uint_as_float((uint32_t)(127 - e) << 23) > 6.0f) e++;
+    sx = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 - 9;  // amax / 2^s in [512, 1024)
+    sx = max(-119, min(110, sx));
+    if (amax * __uint_as_float((uint32_t)(127 - (sx - 1)) << 23) <= 1755.0f) sx--;
   }
-  return e;
+  return sx;
+}
+
+// Eight values of a block with scale exponent s -> four words of eight E2M1 codes (value j in nibble j): word i holds
+// digit i of n + 2340 in base 8, n = round(x / 2^s) clamped to [-2340, 1755], as the E2M1 code of (digit - 4).
+__device__ __forceinline__ void w4_digits(const float (&f)[8], int sx, uint32_t (&packed)[4]) {
+  const float inv = __uint_as_float((uint32_t)(127 - sx) << 23);
+#pragma unroll
+  for (int i = 0; i < 4; i++) packed[i] = 0u;
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const float t = fminf(fmaxf(f[j] * inv, -2340.0f), 1755.0f);
+    // round to nearest even through the mantissa of t + 1.5 * 2^23
+    const uint32_t m = (__float_as_uint(t + 12582912.0f) & 0x7fffffu) - 0x400000u + 2340u;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint32_t d = (m >> (3 * i)) & 7u;
+      packed[i] |= ((0x5420ACDEu >> (4u * d)) & 15u) << (4 * j);  // codes of -4, -3, -2, -1, 0, 1, 2, 3
+    }
+  }
+}
+
+// Table behind the in-kernel activation split: entry m (= n + 2340, 0..4095) holds the E2M1 codes of the four base-8
+// digits of m, each minus 4, one code per byte (term i in byte i). Filled once per device by w4_lut_init_kernel; the
+// GEMM copies it into shared memory while it waits for its input.
+static __device__ __align__(16) uint32_t g_w4_lut[4096];
+
+__global__ void w4_lut_init_kernel() {
+  const uint32_t m = blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= 4096) return;
+  uint32_t e = 0;
+#pragma unroll
+  for (int i = 0; i < 4; i++) e |= ((0x5420ACDEu >> (4u * ((m >> (3 * i)) & 7u))) & 15u) << (8 * i);
+  g_w4_lut[m] = e;
+}
+
+// Eight values of a block with scale exponent s -> the same four words as w4_digits, through the table in shared memory.
+__device__ __forceinline__ void w4_digits_lut(const float (&f)[8], int sx, const uint32_t* __restrict__ lut, uint32_t (&packed)[4]) {
+  const float inv = __uint_as_float((uint32_t)(127 - sx) << 23);
+  uint32_t E[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const float t = fminf(fmaxf(f[j] * inv, -2340.0f), 1755.0f);
+    const uint32_t m = (__float_as_uint(t + 12582912.0f) & 0x7fffffu) - 0x400000u + 2340u;
+    E[j] = lut[m];
+  }
+  // byte i of P_a: the codes of term i for values 2a (low nibble) and 2a + 1; then a 4 x 4 byte transpose
+  const uint32_t P0 = E[0] | (E[1] << 4), P1 = E[2] | (E[3] << 4), P2 = E[4] | (E[5] << 4), P3 = E[6] | (E[7] << 4);
+  const uint32_t A = __byte_perm(P0, P1, 0x5140), B = __byte_perm(P2, P3, 0x5140);
+  const uint32_t Cc = __byte_perm(P0, P1, 0x7362), D = __byte_perm(P2, P3, 0x7362);
+  packed[0] = __byte_perm(A, B, 0x5410);
+  packed[1] = __byte_perm(A, B, 0x7632);
+  packed[2] = __byte_perm(Cc, D, 0x5410);
+  packed[3] = __byte_perm(Cc, D, 0x7632);
+}
+
+// Bounded wait that also sees what other CTAs of the cluster stored before they arrived on the barrier.
+__device__ __forceinline__ bool w4_wait_cluster(uint32_t bar, uint32_t parity) {
+  for (unsigned spins = 0; spins < kTcSpinLimit; spins++) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    if (ok) return true;
+    __nanosleep(200);  // a long wait beside working warps: leave them the issue slots and the memory pipeline
+  }
+  return false;
+}
+// Bounded wait for long waits beside working warps (the producer waiting for a free stage): polls with pauses.
+__device__ __forceinline__ bool w4_wait_relaxed(uint32_t bar, uint32_t parity) {
+  for (unsigned spins = 0; spins < kTcSpinLimit; spins++) {
+    if (tc_mbar_try_wait(bar, parity)) return true;
+    __nanosleep(100);
+  }
+  return false;
+}
+__device__ __forceinline__ void w4_st_cluster_b32(uint32_t caddr, uint32_t v) {
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(caddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void w4_st_cluster_b8(uint32_t caddr, uint32_t v) {
+  asm volatile("st.shared::cluster.b8 [%0], %1;" ::"r"(caddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void w4_arrive_cluster(uint32_t cbar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cbar) : "memory");
+}
+
+// 16-byte global load that stays where it is written: a batch of these is issued before anything consumes them.
+__device__ __forceinline__ uint4 w4_ld16(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr) : "memory");
+  return v;
 }
 
 __device__ __forceinline__ void w4_unpack8(const uint4& v, float (&f)[8]) {
@@ -127,22 +191,18 @@ __device__ __forceinline__ void w4_unpack8(const uint4& v, float (&f)[8]) {
 // Scale byte of MMA row R, 32-wide block j of the k step: (R%32)*16 + (R/32)*4 + j. One thread per 8 elements.
 __device__ __forceinline__ void w4_emit(float (&f)[8], bool store, int tok, int i, int TOKP, uint8_t* __restrict__ terms,
                                         uint8_t* __restrict__ sfa) {
-  const int e = w4_block_exp(f);
-  const float down = __uint_as_float((uint32_t)(127 - e) << 23);
-#pragma unroll
-  for (int j = 0; j < 8; j++) f[j] *= down;
+  const int sx = w4_block_exp(f);
   uint32_t packed[4];
-  w4_terms(f, packed);
+  w4_digits(f, sx, packed);
   if (!store) return;
   const int ks = i >> 4, chunk = i & 15, j = chunk >> 2;
   const int at = TOKP == 64 ? 2 : 1;
-  const int shift[4] = {0, 2, 5, 8};
 #pragma unroll
   for (int t = 0; t < 4; t++) {
     const int tile = TOKP == 64 ? t >> 1 : 0;
     const int R = TOKP == 64 ? 32 * (tok >> 4) + 16 * (t & 1) + (tok & 15) : 32 * (tok >> 3) + 8 * t + (tok & 7);
     *reinterpret_cast<uint32_t*>(terms + ((size_t)(ks * at + tile) * 128 + R) * 64 + chunk * 4) = packed[t];
-    if ((chunk & 3) == 0) sfa[(size_t)(ks * at + tile) * 512 + (R % 32) * 16 + (R / 32) * 4 + j] = (uint8_t)(e + 127 - shift[t]);
+    if ((chunk & 3) == 0) sfa[(size_t)(ks * at + tile) * 512 + (R % 32) * 16 + (R / 32) * 4 + j] = (uint8_t)(127 + sx + 3 * t);
   }
 }
 
@@ -267,20 +327,21 @@ __device__ __forceinline__ void w4_finish(const TcParams& p, int tok, int n, con
 
 // ---------------------------------------------------------------- the GEMM kernel
 template <int TOKP, bool DUAL>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(TOKP == 8 ? 64 + kW4ConvThreads : kTcThreads, 1)
 qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, W4Params pp) {
   using C = W4Cfg<TOKP>;
   constexpr int UKS = C::UKS;
   const TcParams& p = pp.t;
   extern __shared__ unsigned char w4_smem_raw[];
   __shared__ __align__(8) unsigned long long bar_full[kW4MaxStages], bar_empty[kW4MaxStages];
-  __shared__ __align__(8) unsigned long long bar_acc_full, bar_acc_empty, bar_a_ready;
+  __shared__ __align__(8) unsigned long long bar_acc_full, bar_acc_empty, bar_a_ready, bar_lut;
   __shared__ uint32_t tmem_holder;
   __shared__ float inv_rms[8];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem_base = (tc_smem_u32(w4_smem_raw) + 1023u) & ~1023u;
   const int STAGES = pp.stages;
+  if (threadIdx.x == 0) tc_stamp(p, 0);
 
   const long long G = gridDim.x;
   const long long T = p.TN;
@@ -296,7 +357,8 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   const int res_n = (p.cluster > 1 ? nunits : p.KS) * UKS;
   const uint32_t res_a = smem_base;                                    // [res_n][32 rows][64 B]
   const uint32_t res_sf = smem_base + (uint32_t)res_n * C::RES_A1;     // [res_n][512]
-  const uint32_t stage0 = C::RES ? ((res_sf + (uint32_t)res_n * 512 + 1023u) & ~1023u) : smem_base;
+  const uint32_t lut_s = (res_sf + (uint32_t)res_n * 512 + 15u) & ~15u;  // [4096] words: the split table
+  const uint32_t stage0 = C::RES ? ((lut_s + 16384u + 1023u) & ~1023u) : smem_base;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kW4MaxStages; s++) {
@@ -305,7 +367,8 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     }
     tc_mbar_init(tc_smem_u32(&bar_acc_full), 1);
     tc_mbar_init(tc_smem_u32(&bar_acc_empty), 4);
-    tc_mbar_init(tc_smem_u32(&bar_a_ready), 128);
+    tc_mbar_init(tc_smem_u32(&bar_a_ready), (uint32_t)kW4ConvThreads * (uint32_t)(pp.share > 1 ? pp.share : 1));
+    tc_mbar_init(tc_smem_u32(&bar_lut), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -317,6 +380,8 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_holder;
+  if (C::RES && pp.share > 1) tc_cluster_sync();  // every member's barriers exist before anyone arrives on them from afar
+  if (threadIdx.x == 0) tc_stamp(p, 1);
   pdl_trigger();
 
   // weight tiles (of 128 features) of feature tile t at k step ks: a pair is stored as [t][ks][gate, up], single
@@ -359,6 +424,10 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         tc_tma_2d(st, &tmX, 0, ks * UKS * C::ATILES * 128, bar);
         tc_bulk_g2s(st + OFF_SFA, p.sfb + (size_t)ks * UKS * C::SFA1, UKS * C::SFA1, bar);
       };
+      if (C::RES) {  // the split table: constant, fetched ahead of everything else
+        tc_mbar_expect_tx(tc_smem_u32(&bar_lut), 16384);
+        tc_bulk_g2s(lut_s, g_w4_lut, 16384, tc_smem_u32(&bar_lut));
+      }
       const int early = nunits < STAGES ? nunits : STAGES;
       int ptile = tile0, pks = ks0;
       for (int pit = 0; pit < early; pit++) {  // weights do not depend on earlier grids: out before the dependency wait
@@ -370,7 +439,7 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       for (int it = 0; it < nunits; it++) {
         const int s = it % STAGES;
         if (it >= STAGES) {
-          if (!tc_wait(tc_smem_u32(&bar_empty[s]), (uint32_t)((it / STAGES - 1) & 1))) { atomicExch(p.err, 2u); break; }
+          if (!w4_wait_relaxed(tc_smem_u32(&bar_empty[s]), (uint32_t)((it / STAGES - 1) & 1))) { atomicExch(p.err, 2u); break; }
           fetch_w(s, tile, ks);
         }
         if (!C::RES) fetch_x(s, ks);
@@ -384,12 +453,11 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       // kind::mxf4: A = B = E2M1 (1), both K-major, N = 256, UE8M0 scales, M = 128, K = 64
       const uint32_t idesc0 = (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
       bool ok = true;
-      if (C::RES) {  // the epilogue warps have built the terms; their scale factors go to tensor memory once
-        ok = tc_wait(tc_smem_u32(&bar_a_ready), 0);
+      if (C::RES) {  // the epilogue warps (of this CTA, or of all members of its cluster) have built the terms
+        ok = w4_wait_cluster(tc_smem_u32(&bar_a_ready), 0);
         if (!ok) atomicExch(p.err, 5u);
+        asm volatile("fence.proxy.async;" ::: "memory");  // written with ordinary stores, read by the tensor core
         tc_fence_after();
-        if (ok)
-          for (int k = 0; k < res_n; k++) tc_cp_sf(tmem + 256 + k * 4, tc_sf_desc(res_sf + k * 512));
       }
       int ks = ks0;
       uint32_t acc_phase = 0;
@@ -402,6 +470,8 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           acc_phase ^= 1;
         }
         if (!tc_wait(tc_smem_u32(&bar_full[s]), ph)) { atomicExch(p.err, 4u); break; }
+        if (it == 0) tc_stamp(p, 2);
+        if (it == nunits - 1) tc_stamp(p, 3);
         tc_fence_after();
         const uint32_t st = stage0 + (uint32_t)s * C::STAGE_BYTES;
         const uint32_t ring = tmem + C::RING_COL0 + (uint32_t)s * UKS * C::SFC;
@@ -411,11 +481,13 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           const uint32_t sfw = ring + kk * C::SFC;  // 8 weight columns, then 4 per A tile
           tc_cp_sf(sfw, tc_sf_desc(st + OFF_SFW + kk * 1024));
           tc_cp_sf(sfw + 4, tc_sf_desc(st + OFF_SFW + kk * 1024 + 512));
-          if (!C::RES) {
+          const int kl = (ks - ks0 * (p.cluster > 1 ? 1 : 0)) * UKS + kk;  // index of this k step among the resident ones
+          if (C::RES) {
+            tc_cp_sf(sfw + 8, tc_sf_desc(res_sf + (uint32_t)kl * 512));
+          } else {
 #pragma unroll
             for (int a = 0; a < C::ATILES; a++) tc_cp_sf(sfw + 8 + 4 * a, tc_sf_desc(st + OFF_SFA + (kk * C::ATILES + a) * 512));
           }
-          const int kl = (ks - ks0 * (p.cluster > 1 ? 1 : 0)) * UKS + kk;  // index of this k step among the resident ones
 #pragma unroll
           for (int j = 0; j < 2; j++) {  // k 64*j .. 64*j+63 of the step: 32 bytes along the rows, scale bytes 2j and 2j+1
             const uint32_t sfid = (uint32_t)(2 * j);
@@ -425,7 +497,7 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             for (int a = 0; a < C::ATILES; a++) {
               const uint64_t adesc = (C::RES ? w4_desc64(res_a + (uint32_t)kl * C::RES_A1, 128)
                                              : w4_desc64(st + (kk * C::ATILES + a) * 128 * 64, 512)) + (uint64_t)(2 * j);
-              const uint32_t sfa_t = C::RES ? tmem + 256 + (uint32_t)kl * 4 : sfw + 8 + 4 * a;
+              const uint32_t sfa_t = sfw + 8 + 4 * a;
               tc_mma_f4(tmem, adesc, bdesc, idesc, sfa_t | (sfid << 30), sfw | (sfid << 30), (fresh && kk == 0 && j == 0 && a == 0) ? 0u : 1u);
             }
           }
@@ -438,13 +510,17 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ warps 2..5: (TOKP 8) build the terms, then the epilogue
+    // ------------------------------------------------------------ warps 2..: (TOKP 8) build the terms; warps 2..5: the epilogue
     const int sub = warp & 3;  // tensor-memory lanes 32*sub .. 32*sub+31 belong to this warp
-    const int et = (int)threadIdx.x - 64;
     pdl_wait();  // x, residual and multiplier inputs belong to earlier grids
+    if (threadIdx.x == 64) tc_stamp(p, 7);
     if (C::RES) {
+      // The split is a chain of dependent integer operations: one warp per scheduler would run it at a fraction of the
+      // issue rate, so the kernel carries extra warps that do nothing else (kW4ConvThreads in all, with the epilogue warps).
+      constexpr int NCV = kW4ConvThreads;
+      const int ct = (int)threadIdx.x - 64;
       if (pp.gamma) {  // RMSNorm statistics over the whole rows (this CTA may only multiply a slice of K)
-        for (int tok = warp - 2; tok < p.M; tok += 4) {
+        for (int tok = warp - 2; tok < p.M; tok += NCV / 32) {
           const uint4* xr = reinterpret_cast<const uint4*>(pp.x + (size_t)tok * p.K);
           float ss = 0.0f;
           for (int i = lane; i < p.K / 8; i += 32) {
@@ -457,32 +533,45 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
           if (lane == 0) inv_rms[tok] = rsqrtf(ss / (float)p.K + pp.eps);
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(NCV) : "memory");
       }
-      const int nch = res_n * 16;      // 8-element chunks per token in this CTA's K range
-      const int total = p.M * nch;     // a multiple of 16: the four chunks of a 32-wide block sit in four neighbouring lanes
-      const int kbase = res_k0 * 128;
+      // Work items are (token, 8-element chunk) pairs; the four chunks of a 32-wide block sit in four neighbouring lanes.
+      // With `share` members building together, member r takes the resident k steps r, r + share, ... and stores each
+      // result into every member's shared memory.
+      const int nshare = pp.share > 1 ? pp.share : 1;
+      const int myrank = nshare > 1 ? (int)tc_cluster_rank() : 0;
+      const int myks = (res_n - myrank + nshare - 1) / nshare;   // k steps this CTA builds
+      const int nch = myks * 16;
+      const int total = p.M * nch;
+      constexpr int U = 4;  // items per thread and round: loads first, then the arithmetic of all, then the stores
+      const uint32_t* lut = reinterpret_cast<const uint32_t*>(w4_smem_raw + (lut_s - tc_smem_u32(w4_smem_raw)));
+      if (!tc_wait(tc_smem_u32(&bar_lut), 0) && lane == 0) atomicExch(p.err, 8u);
 #pragma unroll 1
-      for (int base = 0; base < total; base += 512) {
-        uint4 raw[4];
+      for (int base = 0; base < total; base += NCV * U) {
+        uint4 raw[U];
+        int tokv[U], cv[U];
 #pragma unroll
-        for (int u = 0; u < 4; u++) {  // four loads in flight per thread
-          const int idx = base + u * 128 + et;
-          raw[u] = make_uint4(0, 0, 0, 0);
-          if (idx < total) {
-            const int tok = idx / nch, k = kbase + (idx % nch) * 8;
-            if (k < p.K) raw[u] = *reinterpret_cast<const uint4*>(pp.x + (size_t)tok * p.K + k);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-          const int idx = base + u * 128 + et;
+        for (int u = 0; u < U; u++) {
+          const int idx = base + u * NCV + ct;
           const bool in = idx < total;
-          const int tok = in ? idx / nch : 0, ch = in ? idx % nch : 0;
+          tokv[u] = in ? idx / nch : -1;
+          cv[u] = in ? idx % nch : 0;
+          raw[u] = make_uint4(0, 0, 0, 0);
+          const int k = (res_k0 + myrank + (cv[u] >> 4) * nshare) * 128 + (cv[u] & 15) * 8;
+          if (in && k < p.K) raw[u] = w4_ld16(pp.x + (size_t)tokv[u] * p.K + k);
+        }
+        uint32_t packed[U][4];
+        int sxv[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+          const bool in = tokv[u] >= 0;
           float f[8];
           w4_unpack8(raw[u], f);
+#ifdef TPX_DEBUG
+          if (threadIdx.x == 64 && base == 0 && u == 0 && p.tl) { if (f[0] == 12345.678f) inv_rms[7] = 1.0f; tc_stamp(p, 1); }
+#endif
           if (pp.gamma) {  // the normalised value rounded to bf16, as the separate kernel would store it
-            const int k = kbase + ch * 8;
+            const int k = (res_k0 + myrank + (cv[u] >> 4) * nshare) * 128 + (cv[u] & 15) * 8;
             float g[8];
 #pragma unroll
             for (int j = 0; j < 8; j++) g[j] = 0.0f;
@@ -495,36 +584,44 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 w4_unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(pp.gamma) + k), g);
               }
             }
-            const float inv = in ? inv_rms[tok] : 0.0f;
+            const float inv = in ? inv_rms[tokv[u]] : 0.0f;
 #pragma unroll
             for (int j = 0; j < 8; j++) f[j] = bf16_bits_to_f32(f32_to_bf16_bits(f[j] * inv * g[j]));
           }
-          const int e = w4_block_exp(f);
-          const float down = __uint_as_float((uint32_t)(127 - e) << 23);
+          sxv[u] = w4_block_exp(f);
+          w4_digits_lut(f, sxv[u], lut, packed[u]);
+        }
 #pragma unroll
-          for (int j = 0; j < 8; j++) f[j] *= down;
-          uint32_t packed[4];
-          w4_terms(f, packed);
-          if (in) {
-            const int kl = ch >> 4, c16 = ch & 15, q = tok >> 1, i2 = tok & 1;
-            const int shift[4] = {0, 2, 5, 8};
+        for (int u = 0; u < U; u++) {
+          if (tokv[u] < 0) continue;
+          const int kl = myrank + (cv[u] >> 4) * nshare, c16 = cv[u] & 15;
+          const int q = tokv[u] >> 1, i2 = tokv[u] & 1;
 #pragma unroll
-            for (int t = 0; t < 4; t++) {
-              const int row = 8 * q + 2 * t + i2;  // stored row; the MMA reads it as its row 32q + 8t + i2
-              const uint32_t off = (uint32_t)kl * C::RES_A1 + (uint32_t)row * 64 + ((uint32_t)((c16 >> 2) ^ ((row >> 1) & 3)) << 4) + (uint32_t)(c16 & 3) * 4;
-              asm volatile("st.shared.b32 [%0], %1;" ::"r"(res_a + off), "r"(packed[t]) : "memory");
-              if ((c16 & 3) == 0) {
-                const uint32_t sfo = (uint32_t)kl * 512 + (uint32_t)(8 * t + i2) * 16 + (uint32_t)q * 4 + (uint32_t)(c16 >> 2);
-                asm volatile("st.shared.b8 [%0], %1;" ::"r"(res_sf + sfo), "r"((uint32_t)(e + 127 - shift[t])) : "memory");
+          for (int t = 0; t < 4; t++) {
+            const int row = 8 * q + 2 * t + i2;  // stored row; the MMA reads it as its row 32q + 8t + i2
+            const uint32_t off = (uint32_t)kl * C::RES_A1 + (uint32_t)row * 64 + ((uint32_t)((c16 >> 2) ^ ((row >> 1) & 3)) << 4) + (uint32_t)(c16 & 3) * 4;
+            const uint32_t sfo = (uint32_t)kl * 512 + (uint32_t)(8 * t + i2) * 16 + (uint32_t)q * 4 + (uint32_t)(c16 >> 2);
+            if (nshare == 1) {
+              asm volatile("st.shared.b32 [%0], %1;" ::"r"(res_a + off), "r"(packed[u][t]) : "memory");
+              if ((c16 & 3) == 0) asm volatile("st.shared.b8 [%0], %1;" ::"r"(res_sf + sfo), "r"((uint32_t)(127 + sxv[u] + 3 * t)) : "memory");
+            } else {
+              for (int m = 0; m < nshare; m++) {
+                w4_st_cluster_b32(tc_mapa(res_a + off, (uint32_t)m), packed[u][t]);
+                if ((c16 & 3) == 0) w4_st_cluster_b8(tc_mapa(res_sf + sfo, (uint32_t)m), (uint32_t)(127 + sxv[u] + 3 * t));
               }
             }
           }
         }
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads these bytes through the async proxy
-      tc_mbar_arrive(tc_smem_u32(&bar_a_ready));
+      asm volatile("fence.proxy.async;" ::: "memory");  // the tensor core reads these bytes through the async proxy
+      if (nshare == 1) {
+        tc_mbar_arrive(tc_smem_u32(&bar_a_ready));
+      } else {
+        for (int m = 0; m < nshare; m++) w4_arrive_cluster(tc_mapa(tc_smem_u32(&bar_a_ready), (uint32_t)m));
+      }
+      if (threadIdx.x == 64) tc_stamp(p, 4);
     }
-
+    if (warp < 6) {  // ---------------------------------------------- epilogue
     const uint32_t lane_base = ((uint32_t)(sub * 32)) << 16;
     constexpr bool TWO = TOKP != 64;  // two shuffle rounds (four term lanes per token) or one (two)
     const int tok = TWO ? sub * C::LIVE + (lane & 7) : sub * 16 + (lane & 15);
@@ -542,6 +639,7 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         }
         acc_phase ^= 1;
         tc_fence_after();
+        if (threadIdx.x == 64 && it == nunits - 1) tc_stamp(p, 5);
         constexpr int CHUNKS = DUAL ? 8 : 16;
 #pragma unroll 1
         for (int c0 = 0; c0 < CHUNKS; c0 += 2) {  // two 16-column chunks per round trip to tensor memory
@@ -611,7 +709,9 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       }
       if (++ks == p.KS) { ks = 0; tile++; }
     }
+    }  // warps 2..5
   }
+  if (threadIdx.x == 64) tc_stamp(p, 6);
   tc_fence_before();
   __syncthreads();
   if (p.cluster > 1) {
@@ -619,7 +719,7 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     // members, each adds the members' parts in rank order (distributed shared memory reads) and finishes its groups.
     // Nobody leaves before all have finished reading.
     tc_cluster_sync();
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
       constexpr int GROUPS = DUAL ? 16 : 32;  // groups of 8 output features per token
       const int et = (int)threadIdx.x - 64;
       const int live_tok = p.M < TOKP ? p.M : TOKP;
@@ -689,7 +789,7 @@ static void w4_size(W4Plan& pl, int cluster) {
   const int stage = pl.tokp == 8 ? W4Cfg<8>::STAGE_BYTES : pl.tokp == 32 ? W4Cfg<32>::STAGE_BYTES : W4Cfg<64>::STAGE_BYTES;
   pl.cluster = cluster;
   pl.res_n = (cluster > 1 ? (pl.KU + cluster - 1) / cluster : pl.KU) * uks;
-  const int res = pl.tokp == 8 ? (pl.res_n * 2560 + 1023) / 1024 * 1024 : 0;
+  const int res = pl.tokp == 8 ? (pl.res_n * 2560 + 16384 + 16 + 1023) / 1024 * 1024 : 0;
   int st = (budget - res) / stage;
   if (st > kW4MaxStages) st = kW4MaxStages;
   pl.stages = st;
@@ -730,11 +830,11 @@ static int w4_launch(const CUtensorMap& w, const CUtensorMap& x, W4Params pp, W4
   cudaGetDevice(&dev);
   const int di = (dev >= 0 && dev < 16) ? dev : 0;
   if (opted[di] < (int)pl.smem) {
-    TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_tcw4_kernel<TOKP, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    opted[di] = 227 * 1024;
+    TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_tcw4_kernel<TOKP, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024));
+    opted[di] = 227 * 1024 - 1024;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kTcThreads);
+  cfg.blockDim = dim3(TOKP == 8 ? 64 + kW4ConvThreads : kTcThreads);
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -768,10 +868,31 @@ static int w4_launch(const CUtensorMap& w, const CUtensorMap& x, W4Params pp, W4
   }
   pp.t.cluster = c > 1 ? c : 1;
   pp.stages = pl.stages;
-  attr[1].val.clusterDim.x = (unsigned)pp.t.cluster;
+  pp.share = 1;
+  int cdim = pp.t.cluster;
+  if (TOKP == 8 && c <= 1 && pp.t.M >= 2) {
+    // whole tiles: every CTA needs the terms of the whole K range; the members of a cluster build them together
+    static int share_ok[16][9] = {};  // 0 unknown, 1 no, 2 yes
+    for (int sh = 8; sh >= 2; sh--) {
+      if (pl.grid % sh) continue;
+      int& f = share_ok[di][sh];
+      if (f == 0) {
+        attr[1].val.clusterDim.x = (unsigned)sh;
+        cfg.gridDim = dim3((unsigned)pl.grid);
+        cfg.dynamicSmemBytes = 227 * 1024 - 1024;
+        cfg.numAttrs = 2;
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, qlinear_tcw4_kernel<TOKP, DUAL>, &cfg);
+        if (e != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
+        f = n >= 1 ? 2 : 1;
+      }
+      if (f == 2) { pp.share = sh; cdim = sh; break; }
+    }
+  }
+  attr[1].val.clusterDim.x = (unsigned)cdim;
   cfg.gridDim = dim3((unsigned)(c > 1 ? pl.TN * c : pl.grid));
   cfg.dynamicSmemBytes = pl.smem;
-  cfg.numAttrs = c > 1 ? 2 : 1;
+  cfg.numAttrs = cdim > 1 ? 2 : 1;
   count_launch();
   TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tcw4_kernel<TOKP, DUAL>, w, x, pp));
   return TPX_OK;
@@ -802,6 +923,16 @@ int tcw4_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x
     }
   } else if (has_norm) {
     TPX_REQUIRE((((uintptr_t)x | (uintptr_t)norm->gamma) & 15) == 0, TPX_ERR_ARG, "fused RMSNorm: x and gamma must be 16-byte aligned");
+  }
+  if (pl.tokp == 8) {  // the split table of this device, once
+    static bool lut_done[64] = {};
+    int dev = 0;
+    TPX_CUDA_OK(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !lut_done[dev]) {
+      w4_lut_init_kernel<<<16, 256, 0, st>>>();
+      TPX_LAUNCH_OK();
+      lut_done[dev] = true;
+    }
   }
   CUtensorMap mw, mx;
   const uint64_t wrows = (uint64_t)(pair ? pl.TN * 2 : pl.tiles128) * pl.KS * 128;

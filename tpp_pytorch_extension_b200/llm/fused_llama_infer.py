@@ -130,17 +130,26 @@ class LlamaRunner(torch.nn.Module):
         graph and replayed: the lengths the kernels need live in device memory, the cache is sized up front, and the
         host only replays. Returns [B, prompt + max_new_tokens] token ids."""
         cache = TppCache()
-        cpp = cache.get_cpp()
-        B, P = input_ids.shape
-        dev = input_ids.device
         mask = attention_mask if attention_mask is not None else torch.ones_like(input_ids)
         # positions count the kept tokens only, in the prompt as in the decode steps (HF generate: cumsum(mask) - 1),
         # so that a left-padded sequence rotates its tokens as the unpadded one would
         prompt_pos = (mask.to(torch.int64).cumsum(-1) - 1).clamp_(min=0).contiguous() if attention_mask is not None else None
         logits, cache = self.forward(input_ids, mask, prompt_pos, cache)
         tok = fused_llm_cpp.argmax_rows(logits[:, -1]).unsqueeze(-1)
-        outs = [input_ids, tok.clone()]
-        steps = max_new_tokens - 1
+        new = self.decode(tok, cache, mask, max_new_tokens - 1, use_graph=use_graph)
+        return torch.cat([input_ids, new], dim=1)
+
+    @torch.no_grad()
+    def decode(self, tok, cache, mask, steps, use_graph=True, timing=None):
+        """`steps` greedy decode steps from a cache that already holds the context: tok [B, 1] is the first new token
+        (not yet in the cache), mask [B, context] the keep-mask of the cached tokens. Returns [B, 1 + steps] tokens.
+        timing: optional dict; receives 'events' = (start, end) CUDA events around the replayed steps and 'steps'."""
+        cpp = cache.get_cpp()
+        B = tok.shape[0]
+        dev = tok.device
+        P = cpp.get_seq_length()
+        tok = tok.clone()
+        outs = [tok.clone()]
         if steps <= 0:
             return torch.cat(outs, dim=1)
         # room for every token to come, so that no cache tensor moves during decoding
@@ -176,6 +185,10 @@ class LlamaRunner(torch.nn.Module):
                 warnings.warn(f"CUDA graph capture of the decode step failed ({e!r}); decoding eagerly")
                 graph = None
                 torch.cuda.synchronize()
+        if timing is not None:
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            timing["events"], timing["steps"] = ev, steps - done
+            ev[0].record()
         while done < steps:
             if graph is not None:
                 graph.replay()
@@ -183,6 +196,8 @@ class LlamaRunner(torch.nn.Module):
                 step()
             outs.append(tok.clone())
             done += 1
+        if timing is not None:
+            timing["events"][1].record()
         for lc in cpp.layers:
             lc.offset += steps
         self.last_graph = graph
@@ -190,6 +205,22 @@ class LlamaRunner(torch.nn.Module):
         from .. import _lib
         _lib.assert_no_kernel_error()  # a kernel that gave up on a bounded wait would have produced wrong tokens
         return out
+
+    def synthetic_cache(self, batch, context, room, seed=1):
+        """A cache that looks as if `context` tokens per sequence had been prefilled: random keys and values of the
+        right shapes (what a decode step costs does not depend on their values). For benchmarks of the decode step on
+        long contexts, where running the prefill itself would take most of the run."""
+        cache = TppCache()
+        cpp = cache.get_cpp()
+        g = torch.Generator(device=self.embed.device).manual_seed(seed)
+        for i, layer in enumerate(self.layers):
+            lc = cpp.layer(i)
+            s1 = (context + room + 31) // 32
+            shape = (s1, batch, layer.Nkv, 32, layer.H)
+            lc.k = torch.randn(shape, generator=g, device=self.embed.device, dtype=torch.bfloat16)
+            lc.v = torch.randn(shape, generator=g, device=self.embed.device, dtype=torch.bfloat16)
+            lc.offset = context
+        return cache
 
 
 def _lm_head_shard(w):
