@@ -245,6 +245,26 @@ int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, con
                   int64_t Sq, int64_t R, int64_t H, int64_t key_len, int64_t Spad, int causal, int out_bsnrh,
                   const int32_t* dev_len, uint16_t* out, void* scratch, size_t scratch_bytes, void* stream);
 
+/* Paged form of the two calls above. The cache of one layer is a sequence of 32-token pages, each a separate
+ * [B][Nkv][32][H] slab (what one index of the reference's leading cache dimension holds, src/csrc/llm/attn.h:144-153);
+ * k_pages / v_pages are DEVICE arrays of the pages' device addresses, entry i for tokens 32i .. 32i+31. A cache grows by
+ * appending pages, where the reference allocates a larger tensor and copies (src/csrc/llm/attn.h:162-178); nothing
+ * already cached moves. Everything else as tpx_rope_kv_update / tpx_attention (`capacity` = 32 x the number of pages).
+ * Prompts on a paged cache run on the mma.sync attention kernel (the TMA kernel needs one contiguous tensor).      */
+int tpx_rope_kv_update_paged(const uint16_t* qkv, const float* ep, const int64_t* pos, int64_t B, int64_t S, int64_t Nq,
+                             int64_t Nkv, int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset, int64_t capacity,
+                             const int32_t* dev_len, uint16_t* q_out, const uint64_t* k_pages, const uint64_t* v_pages, void* stream);
+int tpx_attention_paged(const uint16_t* q, const uint64_t* k_pages, const uint64_t* v_pages, const uint16_t* am, int64_t B, int64_t Nkv,
+                        int64_t Sq, int64_t R, int64_t H, int64_t key_len, int64_t Spad, int causal, int out_bsnrh,
+                        const int32_t* dev_len, uint16_t* out, void* scratch, size_t scratch_bytes, void* stream);
+
+/* The prefill kernel behind tpx_attention (64 query rows or more per (batch, kv head): tcgen05 tensor cores, K/V tiles by
+ * TMA; cache slots past key_len must hold finite values, as a zero-initialised or cropped cache does) has no scratch to
+ * report through: a bounded wait that gave up leaves a code in a word inside the library. This call copies that word
+ * to *status_host and clears it (it waits for `stream`). 0 = every call since the last read completed normally.
+ * No counterpart in the reference.                                                                              */
+int tpx_attention_tc_status(void* stream, unsigned* status_host);
+
 /* TppCache::align_and_invert_mask (src/csrc/llm/attn.h:310-322): [B][S] bf16 0/1 mask -> [B][Spad] additive
  * mask (1 -> 0, 0 -> min_bits, padding -> min_bits), Spad a multiple of 32.                                  */
 int tpx_align_and_invert_mask(const uint16_t* mask, int64_t B, int64_t S, int64_t Spad, uint16_t min_bits,

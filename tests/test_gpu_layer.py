@@ -71,9 +71,19 @@ def test_rope_rejects_overflow(cuda):
     assert rc == 1 and b"capacity" in _lib.lib().tpx_last_error()
 
 
+@pytest.mark.parametrize("prefill_kernel", ["tcgen05", "mma_sync"])
 @pytest.mark.parametrize("B,Nkv,R,H,ctx,Sq", [(1, 2, 4, 128, 100, 1), (2, 1, 8, 128, 1500, 1), (1, 8, 1, 64, 64, 64),
-                                              (2, 2, 4, 128, 300, 37), (16, 8, 4, 128, 2048, 1), (1, 1, 2, 128, 4100, 3)])
-def test_attention_matches_oracle(cuda, B, Nkv, R, H, ctx, Sq):
+                                              (2, 2, 4, 128, 300, 37), (16, 8, 4, 128, 2048, 1), (1, 1, 2, 128, 4100, 3),
+                                              (2, 2, 1, 64, 333, 333), (1, 1, 4, 128, 700, 260), (1, 2, 4, 128, 2048, 2048)])
+def test_attention_matches_oracle(cuda, B, Nkv, R, H, ctx, Sq, prefill_kernel):
+    """Decoding (one query), short and long prompts, prompts on top of a cached context, causal 2048 x 2048; prompts of
+    64 rows or more run on the tcgen05 kernel or, with TPX_ATTN_TC=0, on the mma.sync kernel."""
+    from tests.gpu_util import knob_env
+    with knob_env(TPX_ATTN_TC="1" if prefill_kernel == "tcgen05" else "0"):
+        _attention_case(cuda, B, Nkv, R, H, ctx, Sq)
+
+
+def _attention_case(cuda, B, Nkv, R, H, ctx, Sq):
     from tpp_pytorch_extension_b200._C._tpp_attn import TppCache, attention
     rng = np.random.default_rng(ctx + Sq)
     key_len = ctx
@@ -99,6 +109,7 @@ def test_attention_matches_oracle(cuda, B, Nkv, R, H, ctx, Sq):
     out2 = attention(to_dev_bf16(q, cuda), to_dev_bf16(kc, cuda), to_dev_bf16(vc, cuda), am, key_len, out_bsnrh=True)
     want = np.ascontiguousarray(ref.transpose(0, 2, 1, 3, 4)).reshape(B, Sq, -1)
     assert O.rel_err(to_host_bits(out2), want) <= TOL
+    assert_no_kernel_error()
 
 
 def test_cache_growth_and_crop(cuda):
@@ -116,6 +127,54 @@ def test_cache_growth_and_crop(cuda):
     assert c.get_seq_length() == 100
     c.crop(500)
     assert c.get_seq_length() == 100
+    # growth appended pages: the first run of pages is still the tensor the first update returned (nothing was copied)
+    lc = c.layers[0]
+    assert len(lc.arenas) == 2 and lc.arenas[0][0].data_ptr() == c.layers[0].arenas[0][0].data_ptr()
+    assert lc.k_ptrs.numel() == lc.pages() and int(lc.k_ptrs[0].item()) == lc.arenas[0][0].data_ptr()
+    assert int(lc.k_ptrs[lc.arenas[0][0].shape[0]].item()) == lc.arenas[1][0].data_ptr()
+
+
+def test_paged_cache_layer_matches_oracle(cuda, monkeypatch):
+    """A decoder layer decoding across page-run boundaries: with no spare capacity (KV_CACHE_INC_SIZE = 0) the cache
+    grows by one run of pages every 32 tokens, the kernels follow the page tables (tpx_rope_kv_update_paged,
+    tpx_attention_paged), earlier pages never move, and every step matches the oracle; then a prompt chunk on top of the
+    paged cache (the mma.sync prefill path) and the gathered cache tensor."""
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    from tpp_pytorch_extension_b200._C import _tpp_attn as A
+    monkeypatch.setattr(A, "KV_CACHE_INC_SIZE", 0)
+    rng = np.random.default_rng(77)
+    D, Nq, Nkv, H, FF, B, MP = 256, 4, 2, 64, 512, 2, 256
+    eps = 1e-5
+    names = {"q": (Nq * H, D), "k": (Nkv * H, D), "v": (Nkv * H, D), "o": (D, Nq * H), "gate": (FF, D), "up": (FF, D), "down": (D, FF)}
+    qt, W = {}, {}
+    for nm, (n, k) in names.items():
+        qt[nm], W[nm], _ = make_qweight(rng, n, k, "mxfp4", cuda, std=0.05)
+    W["ln1"], W["ln2"] = O.f32_to_bf16(np.ones(D, np.float32)), O.f32_to_bf16(np.ones(D, np.float32))
+    ep = O.rope_table(MP, H, 1e4)
+    layer = F.LlamaDecoderLayer([to_dev_bf16(W["ln1"], cuda), qt["q"], qt["k"], qt["v"], qt["o"], to_dev_bf16(W["ln2"], cuda),
+                                 qt["gate"], qt["up"], qt["down"], torch.from_numpy(ep).to(cuda)], 0, eps, H, MP, H)
+    cache, ocache = A.TppCache(), O.KVCache()
+    total = 0
+    first_ptr = None
+    for S in (37,) + (1,) * 30 + (70, 1):
+        hs = O.randn_bf16(rng, (B, S, D))
+        pos = np.arange(total, total + S, dtype=np.int64)[None]
+        total += S
+        m01 = np.ones((B, total))
+        am = cache.align_and_invert_mask(torch.from_numpy(m01).to(cuda))
+        out = layer.forward([to_dev_bf16(hs, cuda), am, torch.from_numpy(pos).to(cuda)], cache, True)
+        ref = O.llama_layer(hs, O.align_and_invert_mask(m01), pos, W, ocache, 0, Nq, Nkv, H, eps, ep)
+        assert O.rel_err(to_host_bits(out[0]), ref) <= TOL, (S, total)
+        lc = cache.layers[0]
+        if first_ptr is None:
+            first_ptr = lc.arenas[0][0].data_ptr()
+        assert lc.arenas[0][0].data_ptr() == first_ptr and cache.get_seq_length() == total
+    assert len(cache.layers[0].arenas) >= 3
+    kc_ref = ocache.layers[0]["k"]
+    got = to_host_bits(cache.get(0)[0])
+    n = min(got.shape[0], kc_ref.shape[0], (total + 31) // 32)
+    assert O.rel_err(got[:n], kc_ref[:n]) <= TOL
+    assert_no_kernel_error()
 
 
 @pytest.mark.parametrize("kind", ["mxfp4", "int8"])

@@ -344,17 +344,25 @@ class LlamaDecoderLayer:
         q = torch.empty((B, self.Nkv, S, R, self.H), dtype=hs.dtype, device=hs.device)
         if pos.dtype != torch.int64 or not pos.is_contiguous():
             pos = pos.to(torch.int64).contiguous()
+        paged = not lc.contiguous()  # several arenas: the kernels follow the page tables
+        kc, vc = (None, None) if paged else lc.arenas[0]
         with sc("rotary", 0, 4 * T * (self.Nq + 2 * self.Nkv) * self.H):
-            _lib.check(L.tpx_rope_kv_update(qkv.data_ptr(), self.EP.data_ptr(), pos.data_ptr(), B, S, self.Nq, self.Nkv, self.H,
-                                            self.EP.shape[1], self.EP.shape[2], pos.shape[0], lc.offset, lc.capacity(),
-                                            _lib.ptr(dev_len), q.data_ptr(), lc.k.data_ptr(), lc.v.data_ptr(), _lib.stream()))
+            if paged:
+                _lib.check(L.tpx_rope_kv_update_paged(qkv.data_ptr(), self.EP.data_ptr(), pos.data_ptr(), B, S, self.Nq, self.Nkv, self.H,
+                                                      self.EP.shape[1], self.EP.shape[2], pos.shape[0], lc.offset, lc.capacity(),
+                                                      _lib.ptr(dev_len), q.data_ptr(), lc.k_ptrs.data_ptr(), lc.v_ptrs.data_ptr(), _lib.stream()))
+            else:
+                _lib.check(L.tpx_rope_kv_update(qkv.data_ptr(), self.EP.data_ptr(), pos.data_ptr(), B, S, self.Nq, self.Nkv, self.H,
+                                                self.EP.shape[1], self.EP.shape[2], pos.shape[0], lc.offset, lc.capacity(),
+                                                _lib.ptr(dev_len), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), _lib.stream()))
         if dev_len is None:
             lc.offset += S
             key_len = lc.offset
         else:
             key_len = lc.capacity()  # planning maximum; the kernels read the real length from dev_len
         with sc("mha", 4 * T * self.Nq * self.H * key_len // (2 if S > 1 else 1), 4 * B * self.Nkv * self.H * key_len + 4 * T * self.Nq * self.H):
-            ctx = attention(q, lc.k, lc.v, am, key_len, causal=True, out_bsnrh=True, dev_len=dev_len).view(B * S, self.Nq * self.H)
+            ctx = attention(q, kc, vc, am, key_len, causal=True, out_bsnrh=True, dev_len=dev_len,
+                            pages=(lc.k_ptrs, lc.v_ptrs) if paged else None).view(B * S, self.Nq * self.H)
         with sc("proj_gemm", 2 * T * D * nk(self.Wp)[1], wbytes(self.Wp) + 2 * T * (2 * D + nk(self.Wp)[1])):
             so = fc_plain_act(ctx, self.Wp, res=res, res_scale=scale)
         if ws > 1:
@@ -369,8 +377,10 @@ class LlamaDecoderLayer:
             with sc("allred", 0, 2 * T * D):
                 allreduce(out)
         out = out.view(B, S, D)
-        if use_cache:
-            return [out, lc.k, lc.v]
+        if use_cache:  # the cache tensors while they are one arena, else the list of arenas (TppCache.get gathers them)
+            if paged:
+                return [out, [a[0] for a in lc.arenas], [a[1] for a in lc.arenas]]
+            return [out, kc, vc]
         return [out]
 
 

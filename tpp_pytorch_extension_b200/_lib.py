@@ -50,8 +50,11 @@ _SIGS = {
     "tpx_rmsnorm": (c_int, [c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_vp, c_vp]),
     "tpx_argmax_bf16": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp]),
     "tpx_rope_kv_update": (c_int, [c_vp, c_vp, c_vp] + [c_i64] * 10 + [c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "tpx_rope_kv_update_paged": (c_int, [c_vp, c_vp, c_vp] + [c_i64] * 10 + [c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "tpx_attention_paged": (c_int, [c_vp, c_vp, c_vp, c_vp] + [c_i64] * 7 + [c_int, c_int, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "tpx_attention_scratch_bytes": (c_sz, [c_i64] * 6),
     "tpx_attention": (c_int, [c_vp, c_vp, c_vp, c_vp] + [c_i64] * 7 + [c_int, c_int, c_vp, c_vp, c_vp, c_sz, c_vp]),
+    "tpx_attention_tc_status": (c_int, [c_vp, ctypes.POINTER(ctypes.c_uint)]),
     "tpx_align_and_invert_mask": (c_int, [c_vp, c_i64, c_i64, c_i64, ctypes.c_uint16, c_vp, c_vp]),
     "tpx_qlinear": (c_int, [c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp,
                             c_f32, c_vp, c_vp, c_sz, c_vp]),
@@ -118,6 +121,11 @@ def assert_no_kernel_error(sync=True):
         code = int(buf[65532:65536].view(torch.int32).item())
         if code:
             raise TpxError(f"a linear kernel on device {dev} gave up on a bounded wait (code {code})")
+    if _lib is not None and torch.cuda.is_available():
+        st = ctypes.c_uint(0)
+        check(_lib.tpx_attention_tc_status(stream(), ctypes.byref(st)))
+        if st.value:
+            raise TpxError(f"the prefill attention kernel gave up on a bounded wait (code {st.value})")
 
 
 _scratch = {}

@@ -31,6 +31,7 @@ static void read_knobs() {
   g_knobs.tc_cluster = env("TPX_TC_CLUSTER", 1);
   g_knobs.tc_pf = env("TPX_TC_PF", 0);
   g_knobs.attn_splits = env("TPX_ATTN_SPLITS", 0);
+  g_knobs.attn_tc = env("TPX_ATTN_TC", 1);
 #ifdef TPX_DEBUG
   g_knobs.dbg = env("TPX_TC_DBG", 0);
 #else

@@ -8,7 +8,7 @@
 //
 // The KV cache keeps the reference's layout [S1][B][Nkv][32][H] (token t at block t/32, slot t%32): a block of
 // 32 tokens of one (batch, kv head) is 32*H contiguous elements, which is what the attention kernel streams.
-#include "tpx_common.cuh"
+#include "tpx_attn.cuh"
 
 namespace tpx {
 
@@ -129,7 +129,8 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_row_kernel(const uint16_
 // One thread per (token, head, pair of rotary lanes).
 __global__ void rope_kv_kernel(const uint16_t* __restrict__ qkv, const float* __restrict__ ep, const int64_t* __restrict__ pos,
                                int B, int S, int Nq, int Nkv, int H, int MP, int HR, int Bpos, int64_t offset_arg,
-                               const int* __restrict__ dev_len, int64_t capacity, uint16_t* __restrict__ q_out, uint16_t* __restrict__ kc, uint16_t* __restrict__ vc) {
+                               const int* __restrict__ dev_len, int64_t capacity, uint16_t* __restrict__ q_out, uint16_t* __restrict__ kc, uint16_t* __restrict__ vc,
+                               const uint64_t* __restrict__ kpages, const uint64_t* __restrict__ vpages) {
   pdl_trigger();
   pdl_wait();
   const int heads = Nq + 2 * Nkv;
@@ -161,7 +162,11 @@ __global__ void rope_kv_kernel(const uint16_t* __restrict__ qkv, const float* __
     const int n = is_k ? hd - Nq : hd - Nq - Nkv;
     const int64_t t = offset + s;
     if (t >= capacity) return;  // never write beyond the cache (the host checks this when it knows the offset)
-    dst = (is_k ? kc : vc) + ((((t / 32) * B + b) * Nkv + n) * 32 + (t % 32)) * H;
+    if (kpages) {  // paged cache: block t / 32 lives wherever its page was allocated
+      dst = reinterpret_cast<uint16_t*>((is_k ? kpages : vpages)[t / 32]) + (((int64_t)b * Nkv + n) * 32 + (t % 32)) * H;
+    } else {
+      dst = (is_k ? kc : vc) + ((((t / 32) * B + b) * Nkv + n) * 32 + (t % 32)) * H;
+    }
   }
   dst[h2] = o0;
   dst[h2 + half] = o1;
@@ -171,30 +176,6 @@ __global__ void rope_kv_kernel(const uint16_t* __restrict__ qkv, const float* __
 // Query rows are consecutive (query position, group member) pairs of one (batch, kv head). Each warp keeps a
 // running (max, sum, fp32 output) for 16 rows over the KV blocks it visits. With more than one KV split a CTA
 // writes an un-normalised partial (max, sum, output); the split that arrives last merges them (flash-decoding).
-constexpr int kAttnWarps = 4;
-constexpr int kAttnRows = 16;
-
-struct AttnParams {
-  const uint16_t* q;    // [B][Nkv][Sq][R][H]
-  const uint16_t* kc;   // [S1][B][Nkv][32][H]
-  const uint16_t* vc;
-  const uint16_t* am;   // [B][Spad] additive mask or null
-  uint16_t* out;        // same shape as q
-  float* part;          // [B*Nkv][chunks][splits][16][H + 2]
-  unsigned* counters;   // [B*Nkv][chunks] arrivals of the KV splits; zero between calls
-  int B, Nkv, Sq, R, H;
-  int key_len, Spad, causal;
-  int chunks, splits;
-  const int* dev_len;   // when set: keys cached before this call; key_len = *dev_len + Sq (key_len above is then the planning maximum)
-  int out_bsnrh;        // 0: out laid out like q; 1: out[B][Sq][Nkv][R][H] (rows of the following linear)
-  float scale;
-};
-
-__device__ __forceinline__ int64_t attn_out_index(const AttnParams& p, int bn, int row, int H) {
-  if (!p.out_bsnrh) return ((int64_t)bn * p.Sq * p.R + row) * H;
-  const int b = bn / p.Nkv, n = bn % p.Nkv, sq = row / p.R, r = row % p.R;
-  return ((((int64_t)b * p.Sq + sq) * p.Nkv + n) * p.R + r) * H;
-}
 
 // ---- tensor-core attention (mma.sync m16n8k16, bf16 in, fp32 accumulate), flash-attention style
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -292,8 +273,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_mma_kernel(AttnParams p)
   const bool am_pairs = p.am && (p.Spad & 1) == 0 && (reinterpret_cast<uintptr_t>(p.am) & 3) == 0;
   auto load_block = [&](int blk, int stage) {
     const uint32_t dst = cp_dst0 + (uint32_t)stage * STAGE;
-    const uint16_t* ks = p.kc + (int64_t)blk * blk_stride + cp_src0;
-    const uint16_t* vs = p.vc + (int64_t)blk * blk_stride + cp_src0;
+    const uint16_t* ks = (p.kpages ? reinterpret_cast<const uint16_t*>(p.kpages[blk]) : p.kc + (int64_t)blk * blk_stride) + cp_src0;
+    const uint16_t* vs = (p.vpages ? reinterpret_cast<const uint16_t*>(p.vpages[blk]) : p.vc + (int64_t)blk * blk_stride) + cp_src0;
     const int live = key_len - blk * 32 - cp_r0;  // rows r0 + k*RSTEP with k*RSTEP < live hold cached tokens
 #pragma unroll
     for (int k = 0; k < 32 / RSTEP; k++) {
@@ -606,11 +587,12 @@ extern "C" int tpx_rmsnorm(const uint16_t* x, const void* gamma, int gamma_is_f3
   return TPX_OK;
 }
 
-extern "C" int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const int64_t* pos, int64_t B, int64_t S, int64_t Nq,
-                                  int64_t Nkv, int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset,
-                                  int64_t capacity, const int32_t* dev_len, uint16_t* q_out, uint16_t* kc, uint16_t* vc, void* stream) {
+static int rope_kv_update_impl(const uint16_t* qkv, const float* ep, const int64_t* pos, int64_t B, int64_t S, int64_t Nq,
+                               int64_t Nkv, int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset,
+                               int64_t capacity, const int32_t* dev_len, uint16_t* q_out, uint16_t* kc, uint16_t* vc,
+                               const uint64_t* kpages, const uint64_t* vpages, void* stream) {
   if (S == 0 && B > 0) return TPX_OK;  // nothing to rotate or append
-  TPX_REQUIRE(qkv && ep && pos && q_out && kc && vc, TPX_ERR_ARG, "rope_kv_update: null pointer");
+  TPX_REQUIRE(qkv && ep && pos && q_out && ((kc && vc) || (kpages && vpages)), TPX_ERR_ARG, "rope_kv_update: null pointer");
   TPX_REQUIRE(B > 0 && S >= 0 && Nq > 0 && Nkv > 0 && Nq % Nkv == 0 && H % 2 == 0, TPX_ERR_ARG,
               "rope_kv_update: bad shape");
   TPX_REQUIRE(HR == H, TPX_ERR_UNSUPPORTED, "rope_kv_update: rotary width %ld != head dim %ld (partial rotary is not built)", (long)HR, (long)H);
@@ -621,8 +603,21 @@ extern "C" int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const in
   if (S == 0) return TPX_OK;
   int64_t total = B * S * (Nq + 2 * Nkv) * (H / 2);
   TPX_CUDA_OK(launch_pdl(rope_kv_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, qkv, ep, pos, (int)B,
-                         (int)S, (int)Nq, (int)Nkv, (int)H, (int)MP, (int)HR, (int)Bpos, offset, dev_len, capacity, q_out, kc, vc));
+                         (int)S, (int)Nq, (int)Nkv, (int)H, (int)MP, (int)HR, (int)Bpos, offset, dev_len, capacity, q_out, kc, vc, kpages, vpages));
   return TPX_OK;
+}
+
+extern "C" int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const int64_t* pos, int64_t B, int64_t S, int64_t Nq,
+                                  int64_t Nkv, int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset,
+                                  int64_t capacity, const int32_t* dev_len, uint16_t* q_out, uint16_t* kc, uint16_t* vc, void* stream) {
+  return rope_kv_update_impl(qkv, ep, pos, B, S, Nq, Nkv, H, MP, HR, Bpos, offset, capacity, dev_len, q_out, kc, vc, nullptr, nullptr, stream);
+}
+
+extern "C" int tpx_rope_kv_update_paged(const uint16_t* qkv, const float* ep, const int64_t* pos, int64_t B, int64_t S, int64_t Nq,
+                                        int64_t Nkv, int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset,
+                                        int64_t capacity, const int32_t* dev_len, uint16_t* q_out, const uint64_t* k_pages,
+                                        const uint64_t* v_pages, void* stream) {
+  return rope_kv_update_impl(qkv, ep, pos, B, S, Nq, Nkv, H, MP, HR, Bpos, offset, capacity, dev_len, q_out, nullptr, nullptr, k_pages, v_pages, stream);
 }
 
 // More than 16 query rows: 64 rows per CTA, no KV split. Up to 16 rows (decoding): one CTA row tile and the KV range
@@ -687,17 +682,17 @@ extern "C" size_t tpx_attention_scratch_bytes(int64_t B, int64_t Nkv, int64_t Sq
   return attn_counter_bytes(B, Nkv, chunks) + (size_t)B * Nkv * chunks * splits * kAttnRows * (H + 2) * sizeof(float);
 }
 
-extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, const uint16_t* am, int64_t B,
-                             int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len, int64_t Spad, int causal,
-                             int out_bsnrh, const int32_t* dev_len, uint16_t* out, void* scratch, size_t scratch_bytes, void* stream) {
+static int attention_impl(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, const uint64_t* kpages, const uint64_t* vpages,
+                          const uint16_t* am, int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len, int64_t Spad, int causal,
+                          int out_bsnrh, const int32_t* dev_len, uint16_t* out, void* scratch, size_t scratch_bytes, void* stream) {
   if (Sq == 0 && B > 0 && Nkv > 0 && R > 0) return TPX_OK;  // no queries
-  TPX_REQUIRE(q && kc && vc && out, TPX_ERR_ARG, "attention: null pointer");
+  TPX_REQUIRE(q && ((kc && vc) || (kpages && vpages)) && out, TPX_ERR_ARG, "attention: null pointer");
   TPX_REQUIRE(B > 0 && Nkv > 0 && Sq >= 0 && R > 0 && key_len >= Sq, TPX_ERR_ARG, "attention: bad shape");
   TPX_REQUIRE(H == 64 || H == 128, TPX_ERR_UNSUPPORTED, "attention: head dim %ld not supported (64 or 128)", (long)H);
   TPX_REQUIRE(!am || Spad >= key_len, TPX_ERR_ARG, "attention: mask of %ld keys is shorter than the cache (%ld)", (long)Spad, (long)key_len);
   if (Sq == 0) return TPX_OK;
   AttnParams p;
-  p.q = q; p.kc = kc; p.vc = vc; p.am = am; p.out = out; p.part = nullptr; p.counters = nullptr;
+  p.q = q; p.kc = kc; p.vc = vc; p.kpages = kpages; p.vpages = vpages; p.am = am; p.out = out; p.part = nullptr; p.counters = nullptr;
   p.B = (int)B; p.Nkv = (int)Nkv; p.Sq = (int)Sq; p.R = (int)R; p.H = (int)H;
   p.key_len = (int)key_len; p.Spad = (int)Spad; p.causal = causal; p.out_bsnrh = out_bsnrh; p.dev_len = dev_len;
   attn_plan(B, Nkv, Sq, R, key_len, &p.chunks, &p.splits);
@@ -709,6 +704,7 @@ extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16
     p.counters = reinterpret_cast<unsigned*>(scratch);
     p.part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(scratch) + attn_counter_bytes(B, Nkv, p.chunks));
   }
+  if (!kpages && attn_tc_serves(Sq * R, H)) return attn_tc_launch(p, (cudaStream_t)stream);  // prefill on a contiguous cache: tcgen05 + TMA kernel
   dim3 grid((unsigned)(B * Nkv), (unsigned)p.chunks, (unsigned)p.splits);
   TPX_REQUIRE(p.chunks <= 65535, TPX_ERR_UNSUPPORTED, "attention: too many query rows in one call");
   cudaStream_t st = (cudaStream_t)stream;
@@ -718,6 +714,19 @@ extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16
   else rc = decode ? attn_launch<64, 1>(p, grid, st) : attn_launch<64, 0>(p, grid, st);
   if (rc) return rc;
   return TPX_OK;
+}
+
+extern "C" int tpx_attention(const uint16_t* q, const uint16_t* kc, const uint16_t* vc, const uint16_t* am, int64_t B,
+                             int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len, int64_t Spad, int causal,
+                             int out_bsnrh, const int32_t* dev_len, uint16_t* out, void* scratch, size_t scratch_bytes, void* stream) {
+  return attention_impl(q, kc, vc, nullptr, nullptr, am, B, Nkv, Sq, R, H, key_len, Spad, causal, out_bsnrh, dev_len, out, scratch, scratch_bytes, stream);
+}
+
+extern "C" int tpx_attention_paged(const uint16_t* q, const uint64_t* k_pages, const uint64_t* v_pages, const uint16_t* am, int64_t B,
+                                   int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len, int64_t Spad, int causal,
+                                   int out_bsnrh, const int32_t* dev_len, uint16_t* out, void* scratch, size_t scratch_bytes, void* stream) {
+  return attention_impl(q, nullptr, nullptr, k_pages, v_pages, am, B, Nkv, Sq, R, H, key_len, Spad, causal, out_bsnrh, dev_len, out, scratch,
+                        scratch_bytes, stream);
 }
 
 extern "C" int tpx_align_and_invert_mask(const uint16_t* mask, int64_t B, int64_t S, int64_t Spad, uint16_t min_bits,

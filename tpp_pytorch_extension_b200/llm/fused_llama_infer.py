@@ -153,8 +153,9 @@ class LlamaRunner(torch.nn.Module):
         if steps <= 0:
             return torch.cat(outs, dim=1)
         # room for every token to come, so that no cache tensor moves during decoding
-        for lc in cpp.layers:
-            lc.ensure(B, lc.k.shape[2], lc.k.shape[4], steps, lc.k.dtype, dev)
+        for lc in cpp.layers:  # appends pages; nothing cached moves
+            _, nkv, hd = lc.dims()
+            lc.ensure(B, nkv, hd, steps, lc.arenas[0][0].dtype, dev)
         cap = cpp.layers[0].capacity()
         keep = torch.cat([mask.to(torch.bfloat16), torch.ones((B, cap - P), dtype=torch.bfloat16, device=dev)], dim=1)
         am = cpp.align_and_invert_mask(keep)  # positions not yet written are excluded by the length, not by the mask
@@ -217,9 +218,8 @@ class LlamaRunner(torch.nn.Module):
             lc = cpp.layer(i)
             s1 = (context + room + 31) // 32
             shape = (s1, batch, layer.Nkv, 32, layer.H)
-            lc.k = torch.randn(shape, generator=g, device=self.embed.device, dtype=torch.bfloat16)
-            lc.v = torch.randn(shape, generator=g, device=self.embed.device, dtype=torch.bfloat16)
-            lc.offset = context
+            lc.adopt(torch.randn(shape, generator=g, device=self.embed.device, dtype=torch.bfloat16),
+                     torch.randn(shape, generator=g, device=self.embed.device, dtype=torch.bfloat16), context)
         return cache
 
 
