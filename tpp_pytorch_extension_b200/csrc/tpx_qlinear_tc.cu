@@ -332,13 +332,18 @@ struct TcCfg {
   static constexpr int TMEM_COLS = COLS_RAW <= 32 ? 32 : COLS_RAW <= 64 ? 64 : COLS_RAW <= 128 ? 128 : COLS_RAW <= 256 ? 256 : 512;
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;  // + alignment slack
   static constexpr int W_BOX = A_TILES >= 2 ? 2 : 1;     // weight tiles per copy request (256 or 128 rows)
+  // The epilogue is a chain of dependent scalar instructions per output value; one warp per 32-row quarter of tensor
+  // memory runs it at a fraction of the issue rate, and the tile's MMAs wait for it. With 32 tokens or more every quarter
+  // has two warps, each taking half of the 16-token chunks.
+  static constexpr int EPI_SPLIT = TOK >= 32 ? 2 : 1;
+  static constexpr int THREADS = 64 + 128 * EPI_SPLIT;
   static_assert(A_TILES % W_BOX == 0, "weight tiles are fetched W_BOX at a time");
   static_assert(STAGES >= 2, "at least two stages");
   static_assert(COLS_RAW <= 512, "tensor memory");
 };
 
 template <int TOK, bool DUAL, int UKS>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(TcCfg<TOK, DUAL, UKS>::THREADS, 1)
 qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, TcParams p) {
   using C = TcCfg<TOK, DUAL, UKS>;
   extern __shared__ unsigned char tc_smem_raw[];
@@ -370,7 +375,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       tc_mbar_init(tc_smem_u32(&bar_empty[s]), 1);
     }
     tc_mbar_init(tc_smem_u32(&bar_acc_full), 1);
-    tc_mbar_init(tc_smem_u32(&bar_acc_empty), 4);
+    tc_mbar_init(tc_smem_u32(&bar_acc_empty), 4 * C::EPI_SPLIT);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -536,8 +541,10 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const bool whole = (part_first_ks == 0) && (ks == p.KS - 1);
         // partial tiles live as [slot][weight][128 rows][TOK] fp32: a thread owns one row, TOK consecutive floats
         float* myslot = p.partial + (((size_t)blockIdx.x * 2 + (tile == tile0 ? 0 : 1)) * C::NW) * TOK * 128 + (size_t)row * TOK;
+        constexpr int TPW = TOK / C::EPI_SPLIT;  // tokens of this warp: [cpart * TPW, +TPW)
+        const int cpart = (warp - 2) >> 2;
 #pragma unroll 1
-        for (int c0 = 0; c0 < TOK; c0 += 16) {
+        for (int c0 = cpart * TPW; c0 < (cpart + 1) * TPW; c0 += 16) {
           float r0[16], r1[16];
           {  // hi columns + lo columns
             uint32_t a0[16], t0[16], a1[16], t1[16];
@@ -593,7 +600,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     // the members' parts in rank order (distributed shared memory reads) and runs the epilogue on them. Nobody
     // leaves before all have finished reading.
     tc_cluster_sync();
-    if (warp >= 2) {  // 16-token chunks of the tile go round the members
+    if (warp >= 2 && warp < 6) {  // 16-token chunks of the tile go round the members
       const int sub = warp & 3;
       const int row = sub * 32 + lane;
       const int tn = (int)(ctile / p.TM), tm = (int)(ctile % p.TM);
@@ -808,7 +815,7 @@ static int tc_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams&
   // programmatic dependent launch: the prologue and the first weight fetches overlap the split kernel
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(kTcThreads);
+  cfg.blockDim = dim3(C::THREADS);
   cfg.dynamicSmemBytes = C::SMEM;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];

@@ -36,6 +36,11 @@ struct TcwCfg {
   static constexpr int D_COLS = 256;
   static constexpr int TMEM_COLS = 512;
   static constexpr int EPI_WARPS = TOKP == 16 ? 4 : TOKP / 16;  // 32-lane quarters of tensor memory that hold tokens
+  // The epilogue is a chain of dependent scalar instructions per (token, column): one warp per quarter ran it at a
+  // fraction of the issue rate (5 us of a 27 us gate/up launch at 64 tokens). Every quarter therefore has EPI_SPLIT
+  // warps, each taking a contiguous share of the 16-column chunks.
+  static constexpr int EPI_SPLIT = 4;
+  static constexpr int THREADS = 64 + 128 * EPI_SPLIT;
   static constexpr int TOK_PER_WARP = TOKP == 16 ? 4 : 16;       // 16 tokens are spread four per quarter (row map 2)
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
   static_assert(D_COLS + STAGES * SF_COLS <= 512, "tensor memory");
@@ -108,7 +113,7 @@ __device__ __forceinline__ void tcw_finish8(const TcParams& p, int tok, int n, c
 // p.TN counts the 256-feature tiles here (a gate/up pair: 128 + 128), p.TM is 1, p.KS the k units (UKS k steps of
 // 128 each) per tile, ksteps the k steps of a tile in the packed weight.
 template <int TOKP, bool DUAL, int UKS>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(TcwCfg<TOKP, UKS>::THREADS, 1)
 qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, TcParams p, const uint8_t* wq,
                    int tiles128, int ksteps) {
   using C = TcwCfg<TOKP, UKS>;
@@ -140,7 +145,7 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       tc_mbar_init(tc_smem_u32(&bar_empty[s]), 1);
     }
     tc_mbar_init(tc_smem_u32(&bar_acc_full), 1);
-    tc_mbar_init(tc_smem_u32(&bar_acc_empty), C::EPI_WARPS);
+    tc_mbar_init(tc_smem_u32(&bar_acc_empty), C::EPI_WARPS * C::EPI_SPLIT);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -310,17 +315,19 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const bool whole = (part_first_ks == 0) && (ks == p.KS - 1);
         float* myslot = p.partial + (((size_t)blockIdx.x * 2 + (tile == tile0 ? 0 : 1)) * TOKP + tok) * 256;
         constexpr int CHUNKS = DUAL ? 8 : 16;
+        constexpr int CPW = CHUNKS / C::EPI_SPLIT;  // chunks of this warp: [cpart * CPW, +CPW)
+        const int cpart = (warp - 2) >> 2;
 #pragma unroll 1
-        for (int c0 = 0; c0 < CHUNKS; c0 += 4) {  // four 16-column chunks per round trip to tensor memory
-          uint32_t a[4][16], b[4][16];
+        for (int c0 = cpart * CPW; c0 < (cpart + 1) * CPW; c0 += 2) {  // two 16-column chunks per round trip to tensor memory
+          uint32_t a[2][16], b[2][16];
 #pragma unroll
-          for (int q = 0; q < 4; q++) {
+          for (int q = 0; q < 2; q++) {
             tc_ld_x16(tmem + lane_base + (c0 + q) * 16, a[q]);
             if (DUAL) tc_ld_x16(tmem + lane_base + 128 + (c0 + q) * 16, b[q]);
           }
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int q = 0; q < 4; q++) {
+          for (int q = 0; q < 2; q++) {
             // lanes l and l ^ 16 hold the hi and lo sums of one token: each keeps 8 of the 16 columns and gets the
             // other term of those from its partner
             float v[8], u[8];
@@ -382,9 +389,10 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     tc_cluster_sync();
     if (warp >= 2) {
       constexpr int GROUPS = DUAL ? 16 : 32;  // groups of 8 output features per token
+      constexpr int NT = C::THREADS - 64;
       const int et = (int)threadIdx.x - 64;
       const int live_tok = p.M < TOKP ? p.M : TOKP;
-      for (int i = crank * 128 + et; i < live_tok * GROUPS; i += 128 * p.cluster) {
+      for (int i = crank * NT + et; i < live_tok * GROUPS; i += NT * p.cluster) {
         const int tk = i / GROUPS, col = (i % GROUPS) * 8;
         const int n = DUAL ? (int)ctile * 128 + col : (int)ctile * 256 + col;
         if (n >= p.N) continue;
@@ -518,7 +526,7 @@ static int tcw_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(kTcThreads);
+  cfg.blockDim = dim3(C::THREADS);
   cfg.dynamicSmemBytes = C::SMEM;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
