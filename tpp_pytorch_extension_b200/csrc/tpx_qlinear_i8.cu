@@ -208,6 +208,12 @@ struct I8Cfg {
   static constexpr int GROUP = TOK >= 128 ? 2 : 4;  // accumulators per group; a group (up to GROUP K blocks, 256 k values or one
                                                     // larger block) is handed to the epilogue per barrier round trip
   static constexpr int NBUF = 512 / TOK > 16 ? 16 : 512 / TOK;  // int32 accumulators (one per K block) in tensor memory
+  // Draining a K block (tensor memory -> int32 -> * s_x * s_w -> fp32 sum) is a chain of dependent scalar instructions;
+  // with one warp per 32-row quarter it, not the MMAs, bounds the kernel as soon as there are many tokens. Every quarter
+  // has EPI_SPLIT warps, each owning TW = TOK / EPI_SPLIT tokens (columns) of the tile.
+  static constexpr int EPI_SPLIT = TOK >= 64 ? 4 : TOK / 16;
+  static constexpr int TW = TOK / EPI_SPLIT;
+  static constexpr int THREADS = 64 + 128 * EPI_SPLIT;
   static constexpr int NGRP = NBUF / GROUP;
   static constexpr int TMEM_COLS = NBUF * TOK < 32 ? 32 : NBUF * TOK;
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
@@ -216,7 +222,7 @@ struct I8Cfg {
 };
 
 template <int TOK>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(I8Cfg<TOK>::THREADS, 1)
 qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, I8Params p) {
   using C = I8Cfg<TOK>;
   extern __shared__ unsigned char i8_smem_raw[];
@@ -243,7 +249,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
     for (int b = 0; b < C::NGRP; b++) {
       tc_mbar_init(tc_smem_u32(&d_full[b]), 1);
-      tc_mbar_init(tc_smem_u32(&d_free[b]), 4);
+      tc_mbar_init(tc_smem_u32(&d_free[b]), 4 * C::EPI_SPLIT);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -260,9 +266,10 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   const uint32_t tmem = tmem_holder;
   pdl_trigger();
 
-  float acc[TOK];
+  constexpr int TW = C::TW;
+  float acc[TW];  // this thread's tokens of its feature row
 #pragma unroll
-  for (int i = 0; i < TOK; i++) acc[i] = 0.0f;
+  for (int i = 0; i < TW; i++) acc[i] = 0.0f;
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -340,9 +347,10 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const int nblocks = nsteps * 4 / p.bsteps;
     const int blk0 = ks0 * 4 / p.bsteps;
     uint32_t full_phase = 0;
-    constexpr bool kPrefetchSx = TOK * C::GROUP <= 128;  // activation scales of a whole group in registers
+    constexpr bool kPrefetchSx = TW * C::GROUP <= 128;  // activation scales of a whole group in registers
+    const int cpart = (warp - 2) >> 2;                   // this warp's tokens: [cpart * TW, +TW) of the tile
     const int gsize = p.bsteps >= 8 ? 1 : (8 / p.bsteps < C::GROUP ? 8 / p.bsteps : C::GROUP);
-    const float* sx_tile = p.sx + (size_t)tm * TOK;  // this token tile's columns of sx [K/B][Mp]
+    const float* sx_tile = p.sx + (size_t)tm * TOK + (size_t)cpart * TW;  // this warp's columns of sx [K/B][Mp]
     int b = 0, buf = 0;
     bool dead = false;
     while (b < nblocks && !dead) {
@@ -350,7 +358,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const int cnt = nblocks - b < gsize ? nblocks - b : gsize;
       // scales of the group's blocks are fetched before the wait (a block of pure k padding has none: zeros)
       float sw[C::GROUP];
-      float sxg[kPrefetchSx ? C::GROUP : 1][kPrefetchSx ? TOK : 1];
+      float sxg[kPrefetchSx ? C::GROUP : 1][kPrefetchSx ? TW : 1];
 #pragma unroll
       for (int q = 0; q < C::GROUP; q++) {
         const int blk = blk0 + b + q;
@@ -359,7 +367,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         if (kPrefetchSx) {
           const float4* sxp = reinterpret_cast<const float4*>(sx_tile + (size_t)(real ? blk : 0) * p.Mp);
 #pragma unroll
-          for (int i = 0; i < TOK / 4; i++) {
+          for (int i = 0; i < TW / 4; i++) {
             const float4 v = sxp[i];
             sxg[q][4 * i] = v.x; sxg[q][4 * i + 1] = v.y; sxg[q][4 * i + 2] = v.z; sxg[q][4 * i + 3] = v.w;
           }
@@ -372,7 +380,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       }
       full_phase ^= 1u << grp;
       tc_fence_after();
-      if (sub == 0 && lane == 0) {  // the MMAs of this group are complete: the stages they read may be refilled
+      if (sub == 0 && lane == 0 && cpart == 0) {  // the MMAs of this group are complete: the stages they read may be refilled
         const int it_lo = b * p.bsteps / 4, it_hi = (b + cnt) * p.bsteps / 4;
         for (int it = it_lo; it < it_hi; it++) tc_mbar_arrive(tc_smem_u32(&bar_empty[it % C::STAGES]));
       }
@@ -382,7 +390,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           const int blk = blk0 + b + q;
           const float4* sxp = reinterpret_cast<const float4*>(sx_tile + (size_t)(blk < p.nblk ? blk : 0) * p.Mp);
 #pragma unroll
-          for (int c0 = 0; c0 < TOK; c0 += 16) {
+          for (int c0 = 0; c0 < TW; c0 += 16) {
             float sxc[16];
             if (!kPrefetchSx) {  // many tokens: the scales of 16 tokens at a time (they sit in L1 after the first warp's read)
 #pragma unroll
@@ -392,7 +400,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
               }
             }
             uint32_t d[16];
-            tc_ld_x16(tmem + lane_base + (buf + q) * TOK + c0, d);
+            tc_ld_x16(tmem + lane_base + (buf + q) * TOK + cpart * TW + c0, d);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
             for (int i = 0; i < 16; i++) acc[c0 + i] += (float)(int)d[i] * (kPrefetchSx ? sxg[q][c0 + i] : sxc[i]) * sw[q];
@@ -407,16 +415,17 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
     if (csize == 1) {
 #pragma unroll
-      for (int c0 = 0; c0 < TOK; c0 += 16) {
+      for (int c0 = 0; c0 < TW; c0 += 16) {
         float v[16], v2[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) { v[i] = acc[c0 + i]; v2[i] = 0.0f; }
-        if (n < p.t.N && tm * TOK + c0 < p.t.M) tc_finish16<false>(p.t, tm * TOK + c0, n, v, v2);
+        const int tok0 = tm * TOK + cpart * TW + c0;
+        if (n < p.t.N && tok0 < p.t.M) tc_finish16<false>(p.t, tok0, n, v, v2);
       }
     } else {
-      const uint32_t sp = smem_base + (uint32_t)(row * TOK * 4);
+      const uint32_t sp = smem_base + (uint32_t)((row * TOK + cpart * TW) * 4);
 #pragma unroll
-      for (int c0 = 0; c0 < TOK; c0 += 4) tc_st_shared_f4(sp + c0 * 4, make_float4(acc[c0], acc[c0 + 1], acc[c0 + 2], acc[c0 + 3]));
+      for (int c0 = 0; c0 < TW; c0 += 4) tc_st_shared_f4(sp + c0 * 4, make_float4(acc[c0], acc[c0 + 1], acc[c0 + 2], acc[c0 + 3]));
     }
   }
   tc_fence_before();
@@ -425,7 +434,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     // every member's partial tile is in its own shared memory; 16-token chunks go round the members, each adds the
     // parts in rank order over distributed shared memory and finishes its chunks. Nobody leaves before all have read.
     tc_cluster_sync();
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
       const int row = (warp & 3) * 32 + lane;
       const int n = tile * 128 + row;
 #pragma unroll 1
@@ -494,7 +503,7 @@ static int i8_launch(const CUtensorMap& w, const CUtensorMap& x, I8Params p, int
     if (dev >= 0 && dev < 16) opted[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kTcThreads);
+  cfg.blockDim = dim3(C::THREADS);
   cfg.dynamicSmemBytes = C::SMEM;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
