@@ -231,19 +231,19 @@ def parity_spot_check(wset, w_cpu, xs_host, dev):
             "scope": "M = 8, 256 sampled output features of each op, against the CPU oracle"}
 
 
-def model_bytes_per_step(shape, batch, context, world, lm_head_bf16=True):
+def model_bytes_per_step(shape, batch, context, world, lm_head_bf16=True, wbytes=0.53125):
     """Algorithmic bytes ONE GPU reads per decode step: its shard of the MXFP4 decoder weights (0.53125 B per weight),
     of the bf16 lm_head and of the KV cache (keys and values of `context` tokens per sequence)."""
     D, H = shape.hidden_size, shape.head_dim
     per_layer = (shape.num_attention_heads + 2 * shape.num_key_value_heads) * H * D + D * shape.num_attention_heads * H \
         + 3 * shape.intermediate_size * D
-    w = shape.num_hidden_layers * per_layer * 0.53125
+    w = shape.num_hidden_layers * per_layer * wbytes  # MXFP4: 4-bit code + 1/32 scale byte; int8, blocks of 64: 1 + 4/64
     lm = shape.vocab_size * D * (2 if lm_head_bf16 else 0.53125)
     kv = shape.num_hidden_layers * 2 * context * batch * shape.num_key_value_heads * H * 2
     return (w + lm + kv) / world
 
 
-def model_decode_leg(name, shape, batch, context, steps, dev, world, rank, real_prefill):
+def model_decode_leg(name, shape, batch, context, steps, dev, world, rank, real_prefill, weight_dtype="mxfp4"):
     """Greedy decode of `steps` tokens per sequence on a random-weight MXFP4 model of the named shape, tensor parallel
     over the `world` ranks (all-reduce after o_proj, down_proj and lm_head), the step replayed as a CUDA graph. The
     context is either prefilled for real (timed) or stands in as a random KV cache of the same shape."""
@@ -252,7 +252,9 @@ def model_decode_leg(name, shape, batch, context, steps, dev, world, rank, real_
     from tpp_pytorch_extension_b200.llm import fused_llama_infer as FL
     t0 = time.perf_counter()
     torch.cuda.empty_cache()
-    runner = FL.build_random_llama(shape, "mxfp4", dev, max_positions=context + steps + 16)
+    if weight_dtype == "qint8":
+        os.environ["QINT8_BLOCK_SIZE"] = "64"  # the configuration's K-block size (the reference's switch of the same name)
+    runner = FL.build_random_llama(shape, weight_dtype, dev, max_positions=context + steps + 16)
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t0
     g = torch.Generator(device="cpu").manual_seed(1234)
@@ -285,7 +287,7 @@ def model_decode_leg(name, shape, batch, context, steps, dev, world, rank, real_
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    bps = model_bytes_per_step(shape, batch, context + steps // 2, world)
+    bps = model_bytes_per_step(shape, batch, context + steps // 2, world, wbytes=0.53125 if weight_dtype == "mxfp4" else 1.0625)
     pk = peaks()
     out.update({"ms_per_step": round(ms, 4), "decode_tok_s": round(batch / (ms * 1e-3), 1), "timed_steps": timing["steps"],
                 "graph": runner.last_graph is not None,
@@ -564,6 +566,9 @@ def run_ours(args):
     want = [v for v in args.legs.split(",") if v]
     from tpp_pytorch_extension_b200.llm import fused_llama_infer as FL
     import dataclasses
+    if "cfg3" in want and world == 1:
+        legs["config3_llama2_7b_int8"] = model_decode_leg("Llama-2-7B shape, int8 (K blocks of 64)", FL.LLAMA2_7B, 1, 1024, 128, dev, 1, 0, True,
+                                                          weight_dtype="qint8")
     if "cfg4" in want and world == 1:
         legs["config4_llama3_8b_mxfp4"] = model_decode_leg("Llama-3-8B shape, MXFP4", FL.LLAMA3_8B, 16, 2048, args.model_steps, dev, 1, 0, True)
     if "cfg5" in want:
@@ -586,7 +591,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ms", default="", help="comma-separated subset of the token counts to run (for profiler captures)")
-    ap.add_argument("--legs", default="cfg4,cfg5", help="model-level decode legs to run after the op sweep: cfg4 (Llama-3-8B shape, one GPU), "
+    ap.add_argument("--legs", default="cfg3,cfg4,cfg5", help="model-level decode legs to run after the op sweep: cfg3 (Llama-2-7B shape, int8, one GPU), cfg4 (Llama-3-8B shape, one GPU), "
                     "cfg5 (Llama-2-70B shape, tensor parallel over --gpus ranks); empty for none")
     ap.add_argument("--model-steps", type=int, default=24, help="decode steps timed in each model-level leg")
     ap.add_argument("--cfg5-layers", type=int, default=0, help="decoder layers of the 70B-shape leg (0 = all 80)")

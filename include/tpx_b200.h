@@ -265,6 +265,21 @@ int tpx_attention_paged(const uint16_t* q, const uint64_t* k_pages, const uint64
  * No counterpart in the reference.                                                                              */
 int tpx_attention_tc_status(void* stream, unsigned* status_host);
 
+/* ---------------------------------------------------------------- tensor-parallel all-reduce over peer memory
+ * Replaces tpp_llm.allreduce (src/csrc/llm/fused_llm_infer.cpp:101-119) for the small bf16 tensors a decoder layer
+ * reduces after its row-parallel linears (:1263-1277); the reference's own latency-oriented path is its shared-memory
+ * all-reduce (src/csrc/shm_coll.cpp). In-place SUM of data[n] (n a multiple of 8, at most buf_elems / 2) over `world`
+ * ranks (2..8) of one NVLink domain, fp32 accumulation in rank order (every rank gets the same bits), one kernel per
+ * rank and call. The caller provides, per rank r, an exchange buffer of buf_elems bf16 (buf_ptrs_host[r]) and a flag
+ * array of tpx_allreduce_flag_bytes() bytes (flag_ptrs_host[r]), all of them addressable from every rank (peer or
+ * symmetric memory) and zero before first use; `state` is 16 bytes of this rank's own device memory, zero before first
+ * use: word 0 counts the calls, word 2 receives 1 + the rank of a peer that did not arrive within the bounded wait
+ * (the kernel then finishes with a wrong sum instead of hanging). buf_ptrs_host / flag_ptrs_host are HOST arrays of
+ * `world` device addresses. Every rank must make the same sequence of calls with the same n.                      */
+size_t tpx_allreduce_flag_bytes(void);
+int tpx_allreduce_bf16(uint16_t* data, int64_t n, int rank, int world, const uint64_t* buf_ptrs_host,
+                       const uint64_t* flag_ptrs_host, void* state, int64_t buf_elems, void* stream);
+
 /* TppCache::align_and_invert_mask (src/csrc/llm/attn.h:310-322): [B][S] bf16 0/1 mask -> [B][Spad] additive
  * mask (1 -> 0, 0 -> min_bits, padding -> min_bits), Spad a multiple of 32.                                  */
 int tpx_align_and_invert_mask(const uint16_t* mask, int64_t B, int64_t S, int64_t Spad, uint16_t min_bits,

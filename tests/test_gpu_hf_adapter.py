@@ -63,3 +63,39 @@ def test_adapter_matches_hugging_face_forward(cuda, family):
     logits2, _ = runner.forward(nxt.to(cuda), cache=cache)
     got2 = logits2[:, -1].float().cpu()
     assert float((got2 - want2).abs().max()) <= 2e-2 * float(want2.abs().max())
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 2, 128), (8, 1, 128), (4, 4, 64)])
+def test_adapter_gqa_ratios_and_left_padding(cuda, heads, kv_heads, head_dim):
+    """Group sizes 4 and 8 at head dimension 128 (the Llama-3 and Llama-2-70B attention shapes) and plain multi-head
+    attention, with one left-padded sequence in the batch: prompt logits and greedily generated tokens against Hugging
+    Face's own forward / generate on the same weights (positions count the kept tokens only, in both phases)."""
+    from tpp_pytorch_extension_b200.llm import fused_llama_infer as FL
+    torch.manual_seed(1)
+    cfg = transformers.LlamaConfig(hidden_size=heads * head_dim, intermediate_size=512, num_hidden_layers=2, num_attention_heads=heads,
+                                   num_key_value_heads=kv_heads, head_dim=head_dim, vocab_size=512, max_position_embeddings=128,
+                                   rms_norm_eps=1e-5, tie_word_embeddings=False, pad_token_id=0)
+    model = transformers.LlamaForCausalLM(cfg).float().eval()
+    for layer in model.model.layers:
+        for lin in (layer.self_attn.q_proj, layer.self_attn.k_proj, layer.self_attn.v_proj, layer.self_attn.o_proj,
+                    layer.mlp.gate_proj, layer.mlp.up_proj, layer.mlp.down_proj):
+            lin.weight.data.normal_(0, 0.04)
+    _round_linears_to_mxfp4(model)
+    B, P, NEW = 3, 21, 5
+    ids = torch.randint(1, cfg.vocab_size, (B, P))
+    mask = torch.ones(B, P, dtype=torch.long)
+    mask[1, :6] = 0  # sequence 1 is left-padded by six tokens
+    ids[1, :6] = 0
+    with torch.no_grad():
+        pos = (mask.cumsum(-1) - 1).clamp(min=0)
+        want = model(ids, attention_mask=mask, position_ids=pos).logits[:, -1].float()
+        ref_tokens = model.generate(ids, attention_mask=mask, max_new_tokens=NEW, do_sample=False)
+    runner = FL.OptimizeModelForLlama(model, torch.bfloat16, cuda, "mxfp4")
+    logits, _ = runner.forward(ids.to(cuda), mask.to(cuda), pos.to(cuda))
+    got = logits[:, -1].float().cpu()
+    assert float((got - want).abs().max()) <= 2e-2 * float(want.abs().max())
+    out = runner.generate(ids.to(cuda), NEW, attention_mask=mask.to(cuda)).cpu()
+    assert out.shape == ref_tokens.shape
+    # greedy tokens agree wherever Hugging Face's own margin between the two best logits is not a rounding matter
+    agree = (out[:, P:] == ref_tokens[:, P:]).float().mean().item()
+    assert torch.equal(out[:, P], ref_tokens[:, P]) and agree >= 0.8, (agree, out[:, P:], ref_tokens[:, P:])

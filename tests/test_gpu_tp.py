@@ -22,6 +22,68 @@ def _free_port():
     return p
 
 
+def _check_peer_allreduce(rank, world, dev):
+    """The library's own all-reduce over peer memory against NCCL's on the same data: several sizes, many calls in a row
+    (the exchange buffers alternate), a CUDA-graph replay, and the bounded wait: a call that no peer joins ends with
+    an error code instead of hanging. Returns a dict for the parent (None when peer memory cannot be set up here)."""
+    import torch.distributed as dist
+    from tpp_pytorch_extension_b200 import _peer_allreduce as PA
+    PA.AUTO_MAX_BYTES = 4 << 20  # every size below goes through the kernel
+    peer = PA.get(dist.group.WORLD)
+    if peer is None:
+        return {"available": False}
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    worst = 0.0
+    for n in (8, 4096, 64 * 8192, 1 << 20, 24 * 1000 * 8):
+        for rep in range(5):
+            x = torch.randn(n, generator=g, device=dev).bfloat16()
+            want = x.float().clone()
+            dist.all_reduce(want)  # fp32 sum of the bf16 inputs, as the kernel accumulates
+            got = x.clone()
+            peer(got)
+            worst = max(worst, float((got.float() - want.bfloat16().float()).abs().max()))
+    same = torch.tensor([worst], device=dev)
+    # every rank holds bit-identical results
+    y = torch.randn(4096, generator=torch.Generator(device=dev).manual_seed(7 + rank), device=dev).bfloat16()
+    peer(y)
+    gathered = [torch.empty_like(y) for _ in range(world)]
+    dist.all_gather(gathered, y)
+    identical = all(torch.equal(gathered[0], t) for t in gathered)
+    # recorded in a CUDA graph and replayed: the call counter lives on the device
+    z = torch.ones(8192, device=dev).bfloat16()
+    peer(z)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        peer(z)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    zval = float(z.float()[0])  # 1 -> w (the eager call) -> w^4 (three replays; capturing does not run the kernel)
+    del graph
+    return {"available": True, "worst_abs_diff": float(same.item()), "identical": identical, "graph_value": zval,
+            "clean_before": peer.error_code() == 0}
+
+
+def _check_lone_call(rank, dev, report):
+    """A call nobody joins: rank 0 alone; its wait runs out (about a second) and leaves the code of the missing peer in
+    the state block instead of hanging the GPU. The ranks' call counters are apart afterwards: the buffers are dropped."""
+    import torch.distributed as dist
+    from tpp_pytorch_extension_b200 import _peer_allreduce as PA
+    peer = PA.get(dist.group.WORLD)
+    if peer is None:
+        return
+    report["clean_after_model"] = peer.error_code() == 0
+    dist.barrier()
+    if rank == 0:
+        w = torch.ones(64, device=dev).bfloat16()
+        peer(w)
+        report["lone_call_code"] = peer.error_code()
+    dist.barrier()
+    PA.release()
+    PA._failed.add(id(dist.group.WORLD))
+
+
 def _run(rank, world, port, ids, q):
     try:
         import torch.distributed as dist
@@ -31,16 +93,21 @@ def _run(rank, world, port, ids, q):
             os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
             dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
         dev = torch.device("cuda", rank)
+        peer_report = None
+        if world > 1:
+            peer_report = _check_peer_allreduce(rank, world, dev)
         model = FL.build_random_llama(FL.LlamaShape(**SHAPE), "mxfp4", dev, seed=3, std=0.05)
         ids = ids.to(dev)
         logits, _ = model.forward(ids)
         eager = model.generate(ids, 6, use_graph=False)
         graph = model.generate(ids, 6, use_graph=True)
         torch.cuda.synchronize()
+        if world > 1 and peer_report and peer_report.get("available"):
+            _check_lone_call(rank, dev, peer_report)
         if rank == 0:
             # plain Python lists: nothing the parent would have to fetch from this process after it has exited
             q.put(("ok", logits[:, -1].float().cpu().tolist(), eager.cpu().tolist(), graph.cpu().tolist(),
-                   model.last_graph is not None))
+                   model.last_graph is not None, peer_report))
         if world > 1:
             import gc
             got_graph = model.last_graph is not None
@@ -48,6 +115,8 @@ def _run(rank, world, port, ids, q):
             gc.collect()
             torch.cuda.synchronize()
             dist.barrier()
+            from tpp_pytorch_extension_b200 import _peer_allreduce
+            _peer_allreduce.release()
             dist.destroy_process_group()
     except Exception as e:  # surface the failure in the parent
         import traceback
@@ -75,8 +144,14 @@ def test_tensor_parallel_two_gpus_matches_one():
         assert res[0] == "ok", res[1]
         assert all(p.exitcode == 0 for p in procs)
         results[world] = res[1:]
-    l1, e1, g1, _ = results[1]
-    l2, e2, g2, captured = results[2]
+    l1, e1, g1, _, _ = results[1]
+    l2, e2, g2, captured, peer = results[2]
+    print("peer all-reduce report:", peer)
+    if peer and peer.get("available"):
+        assert peer["worst_abs_diff"] == 0.0, peer  # fp32 accumulation in rank order, one rounding: NCCL's fp32 sum rounded to bf16
+        assert peer["identical"] and peer["clean_before"] and peer["clean_after_model"], peer
+        assert peer["graph_value"] == float(2 ** 4), peer
+        assert peer["lone_call_code"] == 2, peer  # rank 0 waited for rank 1 in vain: code = 1 + the missing rank
     l1, l2, e1, e2, g2 = (torch.tensor(v) for v in (l1, l2, e1, e2, g2))
     # bf16 all-reduces round differently from one fp32 accumulation: logits agree to bf16 accuracy
     assert float((l1 - l2).abs().max()) <= 2e-2 * float(l1.abs().max())

@@ -250,10 +250,16 @@ def get_pg_size():
 
 def allreduce(t):
     """tpp_llm.allreduce (src/csrc/llm/fused_llm_infer.cpp:101-119): in-place SUM over the tensor-parallel ranks
-    (NCCL over NVLink here; the reference uses its shared-memory all-reduce or the c10d backend)."""
+    (small bf16 tensors: this library's own kernel over peer memory, csrc/tpx_allreduce.cu; anything else: NCCL. The
+    reference likewise has a shared-memory all-reduce beside the c10d backend)."""
     import torch.distributed as dist
     if _pg is None or not dist.is_initialized():
         raise _lib.TpxError("Missing process group when using model parallel, use set_pg()")
+    if t.is_cuda:
+        from .. import _peer_allreduce
+        peer = _peer_allreduce.get(_pg)
+        if peer is not None and peer.serves(t):
+            return peer(t)
     dist.all_reduce(t, group=_pg)
     return t
 

@@ -42,6 +42,8 @@ _SIGS = {
                                      c_vp, c_vp, c_sz, c_vp]),
     "tpx_linear_bf16_tc_scratch_bytes": (c_sz, [c_i64, c_i64, c_i64]),
     "tpx_linear_bf16_tc": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp, c_f32, c_vp, c_vp, c_sz, c_vp]),
+    "tpx_allreduce_flag_bytes": (c_sz, []),
+    "tpx_allreduce_bf16": (c_int, [c_vp, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_i64, c_vp]),
     "tpx_launch_count": (ctypes.c_ulonglong, []),
     "tpx_debug_tc_timeline": (None, [c_vp]),  # exported only by a -DTPX_DEBUG build
     "tpx_qlinear_mxfp4_tc_static_status": (c_int, [c_vp, ctypes.POINTER(ctypes.c_uint)]),
@@ -121,6 +123,11 @@ def assert_no_kernel_error(sync=True):
         code = int(buf[65532:65536].view(torch.int32).item())
         if code:
             raise TpxError(f"a linear kernel on device {dev} gave up on a bounded wait (code {code})")
+    from . import _peer_allreduce
+    for inst in list(_peer_allreduce._instances.values()):
+        code = inst.error_code()
+        if code:
+            raise TpxError(f"the peer-memory all-reduce gave up waiting for rank {code - 1}")
     if _lib is not None and torch.cuda.is_available():
         st = ctypes.c_uint(0)
         check(_lib.tpx_attention_tc_status(stream(), ctypes.byref(st)))
