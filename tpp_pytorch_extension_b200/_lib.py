@@ -110,6 +110,7 @@ def reload_options():
     """Re-read the TPX_* kernel-selection switches (the library and the Python side read them once)."""
     from ._C import _fused_llm_infer
     _fused_llm_infer._OPTS.clear()
+    _fused_llm_infer._SCRATCH_BYTES.clear()  # sizes depend on the kernel family the switches select
     if _lib is not None:
         _lib.tpx_reload_options()
 

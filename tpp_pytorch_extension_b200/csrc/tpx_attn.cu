@@ -172,6 +172,71 @@ __global__ void rope_kv_kernel(const uint16_t* __restrict__ qkv, const float* __
   dst[h2 + half] = o1;
 }
 
+// The same with one thread per (token, head, eight pairs of rotary lanes): 16-byte loads and stores. For head sizes
+// that are a multiple of 16 and 16-byte aligned tensors; the arithmetic is the scalar kernel's, lane for lane.
+__global__ void rope_kv_v8_kernel(const uint16_t* __restrict__ qkv, const float* __restrict__ ep, const int64_t* __restrict__ pos,
+                                  int B, int S, int Nq, int Nkv, int H, int MP, int HR, int Bpos, int64_t offset_arg,
+                                  const int* __restrict__ dev_len, int64_t capacity, uint16_t* __restrict__ q_out, uint16_t* __restrict__ kc,
+                                  uint16_t* __restrict__ vc, const uint64_t* __restrict__ kpages, const uint64_t* __restrict__ vpages) {
+  pdl_trigger();
+  pdl_wait();
+  const int heads = Nq + 2 * Nkv;
+  const int half = H / 2, groups = half / 8;
+  const int64_t offset = dev_len ? (int64_t)*dev_len : offset_arg;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)B * S * heads * groups) return;
+  const int h2 = (int)(idx % groups) * 8;
+  const int hd = (int)((idx / groups) % heads);
+  const int s = (int)((idx / ((int64_t)groups * heads)) % S);
+  const int b = (int)(idx / ((int64_t)groups * heads * S));
+  const uint16_t* src = qkv + ((int64_t)(b * S + s) * heads + hd) * H;
+  uint4 lo = *reinterpret_cast<const uint4*>(src + h2), hi = *reinterpret_cast<const uint4*>(src + h2 + half);
+  if (hd < Nq + Nkv) {
+    const int64_t p = pos[(int64_t)(Bpos == 1 ? 0 : b) * S + s];
+    if (p < MP) {
+      const float* cs = ep + (0 * (int64_t)MP + p) * HR + h2;
+      const float* sp = ep + (1 * (int64_t)MP + p) * HR + h2;
+      const float4 c0 = *reinterpret_cast<const float4*>(cs), c1 = *reinterpret_cast<const float4*>(cs + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+      const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+      uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w}, hw[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        uint32_t nl = 0, nh = 0;
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          const float x0 = bf16_bits_to_f32((uint16_t)(lw[j] >> (16 * e))), x1 = bf16_bits_to_f32((uint16_t)(hw[j] >> (16 * e)));
+          const float c = cv[2 * j + e], sn = sv[2 * j + e];
+          nl |= (uint32_t)f32_to_bf16_bits(x0 * c - x1 * sn) << (16 * e);
+          nh |= (uint32_t)f32_to_bf16_bits(x1 * c + x0 * sn) << (16 * e);
+        }
+        lw[j] = nl;
+        hw[j] = nh;
+      }
+      lo = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+      hi = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+    }
+  }
+  uint16_t* dst;
+  if (hd < Nq) {
+    const int R = Nq / Nkv, n = hd / R, r = hd % R;
+    dst = q_out + ((((int64_t)b * Nkv + n) * S + s) * R + r) * H;
+  } else {
+    const bool is_k = hd < Nq + Nkv;
+    const int n = is_k ? hd - Nq : hd - Nq - Nkv;
+    const int64_t t = offset + s;
+    if (t >= capacity) return;
+    if (kpages) {
+      dst = reinterpret_cast<uint16_t*>((is_k ? kpages : vpages)[t / 32]) + (((int64_t)b * Nkv + n) * 32 + (t % 32)) * H;
+    } else {
+      dst = (is_k ? kc : vc) + ((((t / 32) * B + b) * Nkv + n) * 32 + (t % 32)) * H;
+    }
+  }
+  *reinterpret_cast<uint4*>(dst + h2) = lo;
+  *reinterpret_cast<uint4*>(dst + h2 + half) = hi;
+}
+
 // ---------------------------------------------------------------- attention
 // Query rows are consecutive (query position, group member) pairs of one (batch, kv head). Each warp keeps a
 // running (max, sum, fp32 output) for 16 rows over the KV blocks it visits. With more than one KV split a CTA
@@ -601,6 +666,13 @@ static int rope_kv_update_impl(const uint16_t* qkv, const float* ep, const int64
     TPX_REQUIRE(offset >= 0 && offset + S <= capacity, TPX_ERR_ARG, "rope_kv_update: cache capacity %ld is short of %ld tokens",
                 (long)capacity, (long)(offset + S));
   if (S == 0) return TPX_OK;
+  const bool aligned = (((uintptr_t)qkv | (uintptr_t)ep | (uintptr_t)q_out | (uintptr_t)kc | (uintptr_t)vc) & 15) == 0;
+  if (H % 16 == 0 && aligned) {  // pages are whole [B][Nkv][32][H] slabs of an aligned allocation
+    int64_t total8 = B * S * (Nq + 2 * Nkv) * (H / 16);
+    TPX_CUDA_OK(launch_pdl(rope_kv_v8_kernel, dim3((unsigned)((total8 + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, qkv, ep, pos, (int)B,
+                           (int)S, (int)Nq, (int)Nkv, (int)H, (int)MP, (int)HR, (int)Bpos, offset, dev_len, capacity, q_out, kc, vc, kpages, vpages));
+    return TPX_OK;
+  }
   int64_t total = B * S * (Nq + 2 * Nkv) * (H / 2);
   TPX_CUDA_OK(launch_pdl(rope_kv_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, qkv, ep, pos, (int)B,
                          (int)S, (int)Nq, (int)Nkv, (int)H, (int)MP, (int)HR, (int)Bpos, offset, dev_len, capacity, q_out, kc, vc, kpages, vpages));

@@ -254,4 +254,9 @@ bool tcw4_serves(int64_t M, int64_t N, int64_t K, bool pair);
 size_t tcw4_scratch_bytes(int64_t M, int64_t N, int64_t K, bool pair);
 int tcw4_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x, int64_t M, int64_t N, int64_t K, const TcParams& base,
              void* scratch, size_t scratch_bytes, cudaStream_t st, const TcNorm* norm = nullptr);
+// many tokens, whole tiles of 128 x 128, three accumulators (the epilogue overlaps the next tile): tpx_qlinear_tcp.cu
+bool tcp_serves(int64_t M, int64_t N, int64_t K, bool pair);
+size_t tcp_scratch_bytes(int64_t M, int64_t N, int64_t K, bool pair);
+int tcp_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x, int64_t M, int64_t N, int64_t K, const TcParams& base,
+            void* scratch, size_t scratch_bytes, cudaStream_t st, const TcNorm* norm = nullptr);
 }  // namespace tpx
