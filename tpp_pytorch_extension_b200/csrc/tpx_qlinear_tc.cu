@@ -707,8 +707,38 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// A tensor map is a pure function of its arguments, and a decoder calls the same few dozen (weight, shape) pairs
+// over and over: encoded maps are kept in a small per-thread, direct-mapped table keyed by those arguments.
+struct MapKey {
+  const void* base;
+  uint64_t rows, row_bytes;
+  uint32_t box_rows;
+  int dt, kind;  // kind 0: 128-element rows, 128-byte swizzle; 1: 64-byte rows, 64-byte swizzle
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows && dt == o.dt && kind == o.kind;
+  }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kMapSlots = 256;
+static MapSlot* map_slot(const MapKey& k) {
+  static thread_local MapSlot table[kMapSlots] = {};
+  uint64_t h = (uint64_t)(uintptr_t)k.base * 0x9E3779B97F4A7C15ull ^ (k.rows * 0xC2B2AE3D27D4EB4Full) ^ ((uint64_t)k.box_rows << 7) ^ ((uint64_t)k.dt << 3) ^
+               (uint64_t)k.kind ^ (k.row_bytes << 17);
+  return &table[(h >> 32) % kMapSlots];
+}
+
 // 2-D tensor of `rows` rows of 128 elements (row_bytes apart), box = 128 elements x box_rows, 128-byte swizzle.
 int tc_make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+  const MapKey key = {base, rows, row_bytes, box_rows, (int)dt, 0};
+  MapSlot* slot = map_slot(key);
+  if (slot->used && slot->key == key) {
+    *m = slot->map;
+    return TPX_OK;
+  }
   EncodeTiledFn fn = encode_fn();
   TPX_REQUIRE(fn, TPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t gdim[2] = {128, rows};
@@ -719,11 +749,18 @@ int tc_make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TPX_REQUIRE(r == CUDA_SUCCESS, TPX_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (rows=%llu row_bytes=%llu box_rows=%u)", (int)r,
               (unsigned long long)rows, (unsigned long long)row_bytes, box_rows);
+  slot->key = key; slot->map = *m; slot->used = true;
   return TPX_OK;
 }
 
 // 2-D byte tensor of `rows` rows of 64 bytes, box = 64 bytes x box_rows, 64-byte swizzle (packed 4-bit operands).
 int tc_make_map64(CUtensorMap* m, const void* base, uint64_t rows, uint32_t box_rows) {
+  const MapKey key = {base, rows, 64, box_rows, (int)CU_TENSOR_MAP_DATA_TYPE_UINT8, 1};
+  MapSlot* slot = map_slot(key);
+  if (slot->used && slot->key == key) {
+    *m = slot->map;
+    return TPX_OK;
+  }
   EncodeTiledFn fn = encode_fn();
   TPX_REQUIRE(fn, TPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t gdim[2] = {64, rows};
@@ -734,6 +771,7 @@ int tc_make_map64(CUtensorMap* m, const void* base, uint64_t rows, uint32_t box_
                   CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TPX_REQUIRE(r == CUDA_SUCCESS, TPX_ERR_CUDA, "cuTensorMapEncodeTiled (64-byte rows) failed with %d (rows=%llu box_rows=%u)", (int)r,
               (unsigned long long)rows, box_rows);
+  slot->key = key; slot->map = *m; slot->used = true;
   return TPX_OK;
 }
 
