@@ -874,17 +874,29 @@ static int tc_launch(const CUtensorMap& w, const CUtensorMap& x, const TcParams&
     a2[1].val.clusterDim.z = 1;
     cc.attrs = a2;
     cc.numAttrs = 2;
+    // the largest cluster size, from the planned one down, of which one cluster per tile can be resident at once
+    // (48 clusters of 3 do not fit 148 SMs in GPCs of 16 to 18, 48 of 2 do)
     static int fits[16][9] = {};  // 0 unknown, else 1 + the number of clusters of this size that can be resident
-    int& f = fits[(dev >= 0 && dev < 16) ? dev : 0][p.cluster];
-    if (f == 0) {
-      int n = 0;
-      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, qlinear_tc_kernel<TOK, DUAL, UKS>, &cc);
-      if (e != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
-      f = 1 + n;
+    int c = p.cluster;
+    for (; c >= 2; c--) {
+      int& f = fits[(dev >= 0 && dev < 16) ? dev : 0][c];
+      if (f == 0) {
+        a2[1].val.clusterDim.x = (unsigned)c;
+        cc.gridDim = dim3((unsigned)(tiles * c));
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, qlinear_tc_kernel<TOK, DUAL, UKS>, &cc);
+        if (e != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
+        f = 1 + n;
+      }
+      if (f - 1 >= tiles) break;
     }
-    if (f - 1 >= tiles) {
+    if (c >= 2) {
+      TcParams q = p;
+      q.cluster = c;
+      a2[1].val.clusterDim.x = (unsigned)c;
+      cc.gridDim = dim3((unsigned)(tiles * c));
       count_launch();
-  TPX_CUDA_OK(cudaLaunchKernelEx(&cc, qlinear_tc_kernel<TOK, DUAL, UKS>, w, x, p));
+      TPX_CUDA_OK(cudaLaunchKernelEx(&cc, qlinear_tc_kernel<TOK, DUAL, UKS>, w, x, q));
       return TPX_OK;
     }
     TcParams q = p;
@@ -956,18 +968,31 @@ extern "C" int tpx_repack_mxfp4_tc(const uint8_t* codes, const uint8_t* scales, 
 }
 
 // Kernel choice for up to 64 tokens. The kernel with the weights on the wide (N) side of the MMA spends fewer
-// tensor-pipe cycles per weight byte (one 128x256x32 MMA per 4 KiB instead of two 128x32x32 per 2 KiB each) and wins
-// when every CTA owns whole tiles (the gate/up pair of a decode step: 29.3 against 31.3 us at M = 8, 34.2 against
-// 35.3 us at M = 64); shapes with few tiles are better served by
-// the cluster split-K of the other kernel. TPX_TC_WIDE=1 forces it for every M <= 64, TPX_TC_WIDE=0 disables it.
+// tensor-pipe cycles per weight byte (one 128x256x32 MMA per 4 KiB instead of two 128x32x32 per 2 KiB each); the rule
+// below follows a sweep of both kernels over the linear shapes of Llama-3-8B, Llama-2-7B and Llama-2-70B (2 and 8
+// tensor-parallel ranks) at 1 to 64 tokens, launches back to back. TPX_TC_WIDE=1 forces the wide kernel for every
+// M <= 64, TPX_TC_WIDE=0 disables it.
 static bool tc_wide(int64_t M, int64_t N, int64_t K, bool pair) {
   if (M > 64) return false;
   if (knobs().tc_wide >= 0) return knobs().tc_wide != 0;
-  const long long T = pair ? (N + 127) / 128 : (N + 255) / 256;  // tiles of the wide kernel
-  const int sms = sm_count();
   (void)K;
-  if ((T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms) return true;  // whole tiles
-  return M <= 16 && T * 2 <= sms;  // few tiles: clusters split K in either kernel, the wide one needs fewer MMA cycles
+  const int sms = sm_count();
+  auto whole = [&](long long T) { return (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms; };
+  const long long T0 = (N + 127) / 128;                        // tiles of the 128-row kernel (a pair: pair tiles)
+  const long long T1 = pair ? (N + 127) / 128 : (N + 255) / 256;  // tiles of the wide kernel
+  if (whole(T1)) return true;  // every CTA owns whole tiles
+  // A pair has the same tiles in both kernels; the wide one measured faster or equal at every token count (Llama-2-7B
+  // gate/up, 86 tiles, 64 tokens: 28.5 against 41.2 us; 28 tiles of K = 8192: 24.8 against 28.8 us).
+  if (pair) return true;
+  if (whole(T0)) return false;
+  // The 128-row kernel would cut tiles between CTAs and add a fix-up pass; the wide kernel has half as many tiles and
+  // can usually split K inside clusters (q/k/v of 12288 features, 64 tokens: 20.2 against 27.2 us).
+  if (T0 * 2 > sms) return true;
+  // Both split K inside clusters. Up to 16 tokens the wide kernel: launched back to back the 128-row kernel measured
+  // faster at 16 tokens (4096 x 14336: 17.6 against 19.5 us) but a whole Llama-3-8B decode step at batch 16 slower (4.13
+  // against 3.96 ms), so the choice follows the model-level measurement. Beyond 16 tokens the 128-row kernel has the
+  // shorter epilogue (4096 x 4096 at 64 tokens: 16.4 against 19.2 us).
+  return M <= 16;
 }
 
 // Kernel family for a call: 0 = weights on the 128-row side (all M), 1 = weights on the N side (M <= 64),
