@@ -33,9 +33,9 @@ if ROOT not in sys.path:
 D_MODEL, D_FF = 4096, 14336
 SWEEP = [1, 8, 64, 512, 4096]
 DECODE_MAX_M = 64
-# dram__bytes_read.sum + dram__bytes_write.sum of one qlinear_tc_kernel gate/up launch, from the ncu captures
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch of the tensor-core kernels, from the ncu captures
 # summarised under profiles/ (bytes); None where no capture exists
-NCU_TRAFFIC = {1: 63.02e6, 8: 63.02e6, 64: 63.32e6}  # M=1 runs the M=8 kernel instantiation on the same weight bytes
+NCU_TRAFFIC = {1: 63.02e6, 8: 63.02e6, 64: 63.82e6}  # M=1 runs the M=8 kernel instantiation on the same weight bytes
 N_COPIES = 6  # distinct packed weight sets: 6 x 93.6 MB = 561 MB >> 126 MB of L2
 
 
@@ -539,7 +539,7 @@ def run_ours(args):
                         "peak_src": pk["src"]},
             "roofline": {"bound": "hbm",
                          "kernel": f"MXFP4 gate/up pair GEMM, M={SWEEP[dom]} (tcgen05: qlinear_tc4_kernel, kind::mxf4, for M <= 32; "
-                                   f"qlinear_tcw_kernel, kind::mxf8f6f4, for M <= 64; else qlinear_tc_kernel)"
+                                   f"qlinear_tcw_kernel, kind::mxf8f6f4, for M <= 64; qlinear_tcp_kernel beyond)"
                                    if F.mxfp4_path() == "tc" else f"qlinear_stream gate/up pair, M={SWEEP[dom]}",
                          "achieved": dom_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": dom_gbs / pk["hbm_gbs"],
                          "peak_src": pk["src"], "traffic": NCU_TRAFFIC.get(SWEEP[dom]),
