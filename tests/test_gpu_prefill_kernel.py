@@ -1,5 +1,6 @@
-"""The many-token MXFP4 kernel (whole 128 x 128 tiles, three accumulators in tensor memory, epilogue overlapped with the
-next tile) against the oracle, forced by TPX_TC_P=1 for shapes the library would otherwise give to the general kernel:
+"""The many-token MXFP4 kernels against the oracle: the CTA-pair kernel (tcgen05.mma.cta_group::2, TPX_TC_P2=1) and the
+one-CTA kernel (whole 128 x 128 tiles, three accumulators in tensor memory, TPX_TC_P=1 with TPX_TC_P2=0), forced for
+shapes the library would otherwise give to the general kernel:
 token counts that are not multiples of the tile, feature counts that end inside a tile, K with a tail, one and two k
 steps per pipeline stage, every epilogue, the gate/up pair and the fused RMSNorm.
 Tolerance: max |y - ref| / max |ref| <= 2e-2."""
@@ -13,9 +14,10 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-2
 
 
-@pytest.fixture(autouse=True, params=[2, 1], ids=["uks2", "uks1"])
+@pytest.fixture(autouse=True, params=[(1, 2), (1, 1), (0, 2), (0, 1)], ids=["pair-uks2", "pair-uks1", "one-uks2", "one-uks1"])
 def forced(request, cuda):
-    with knob_env(TPX_MXFP4_PATH="tc", TPX_TC_P=1, TPX_TC_P_UKS=request.param):
+    p2, uks = request.param
+    with knob_env(TPX_MXFP4_PATH="tc", TPX_TC_P=1, TPX_TC_P2=p2, TPX_TC_P_UKS=uks):
         yield
 
 
@@ -79,7 +81,7 @@ def test_many_tiles_per_cta_match_the_general_kernel(cuda):
     xd = to_dev_bf16(O.randn_bf16(rng, (M, K)), cuda)
     res = to_dev_bf16(O.randn_bf16(rng, (M, N)), cuda)
     y = F.fc_plain_act(xd, q, None, None, None, res, 1.0).float()
-    with knob_env(TPX_TC_P=0):
+    with knob_env(TPX_TC_P=0, TPX_TC_P2=0):
         y0 = F.fc_plain_act(xd, q, None, None, None, res, 1.0).float()
     assert ((y - y0).abs().max() / y0.abs().max()).item() <= 1e-2
     assert_no_kernel_error()

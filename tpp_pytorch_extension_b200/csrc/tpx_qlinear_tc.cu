@@ -1020,12 +1020,13 @@ static int tc_kind(int64_t M, int64_t N, int64_t K, bool pair) {
     const bool whole = (T * 10 >= (long long)sms * 7 && T <= sms) || T >= 8LL * sms;
     if (forced >= 0 ? forced != 0 : whole) return 2;
   }
+  if (tcp2_serves(M, N, K, pair)) return 5;  // many tokens on CTA pairs
   if (tcp_serves(M, N, K, pair)) return 4;  // many tokens in whole tiles: the kernel with overlapped epilogue
   return tc_wide(M, N, K, pair) ? 1 : 0;
 }
 
 static size_t tc_scratch_need(int64_t M, int64_t N, int64_t K, bool pair, int kind) {
-  return kind == 4 ? tcp_scratch_bytes(M, N, K, pair) : kind == 3 ? tcw4_scratch_bytes(M, N, K, pair) : kind == 2 ? tc4_scratch_bytes(M, N, K, pair) : kind == 1 ? tcw_scratch_bytes(M, N, K, pair)
+  return kind == 5 ? tcp2_scratch_bytes(M, N, K, pair) : kind == 4 ? tcp_scratch_bytes(M, N, K, pair) : kind == 3 ? tcw4_scratch_bytes(M, N, K, pair) : kind == 2 ? tc4_scratch_bytes(M, N, K, pair) : kind == 1 ? tcw_scratch_bytes(M, N, K, pair)
                    : tc_plan(M, N, K, pair).total;
 }
 
@@ -1046,6 +1047,12 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   TPX_REQUIRE(((uintptr_t)wq & 31) == 0 && ((uintptr_t)sfa & 15) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)scratch & 255) == 0,
               TPX_ERR_ARG, "qlinear_mxfp4_tc: misaligned pointer");
   const bool dual = pair != 0;
+  if (kind == 5) {
+    TcParams b = {};
+    b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act; b.tl = g_tc_timeline;
+    b.dbg = knobs().dbg;
+    return tcp2_run(wq, sfa, dual, x, M, N, K, b, scratch, scratch_bytes, (cudaStream_t)stream, norm);
+  }
   if (kind == 4) {
     TcParams b = {};
     b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act; b.tl = g_tc_timeline;

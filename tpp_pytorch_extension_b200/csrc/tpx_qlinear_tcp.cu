@@ -356,12 +356,12 @@ static TcpPlan tcp_plan(int64_t M, int64_t N, int64_t K, bool pair) {
 // where fewer than a quarter of the SMs get a tile and K is long (128 tokens, 4096 x 14336: 70 against 40 us with the
 // cluster split of K). TPX_TC_P=0 never, TPX_TC_P=1 for every M > 64.
 bool tcp_serves(int64_t M, int64_t N, int64_t K, bool pair) {
-  (void)K; (void)pair;
+  (void)pair;
   const int k = knobs().tc_p;
   if (k == 0 || M <= 64) return false;
   if (k > 0) return true;
   const long long T = ((N + 127) / 128) * ((M + 127) / 128);
-  return T * 4 >= sm_count();
+  return T * 2 >= sm_count() || (T * 4 >= sm_count() && K <= 4096);
 }
 
 size_t tcp_scratch_bytes(int64_t M, int64_t N, int64_t K, bool pair) { return tcp_plan(M, N, K, pair).total; }

@@ -259,4 +259,9 @@ bool tcp_serves(int64_t M, int64_t N, int64_t K, bool pair);
 size_t tcp_scratch_bytes(int64_t M, int64_t N, int64_t K, bool pair);
 int tcp_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x, int64_t M, int64_t N, int64_t K, const TcParams& base,
             void* scratch, size_t scratch_bytes, cudaStream_t st, const TcNorm* norm = nullptr);
+// the same on CTA pairs (tcgen05.mma.cta_group::2, each CTA holds half of the activation operand): tpx_qlinear_tcp2.cu
+bool tcp2_serves(int64_t M, int64_t N, int64_t K, bool pair);
+size_t tcp2_scratch_bytes(int64_t M, int64_t N, int64_t K, bool pair);
+int tcp2_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x, int64_t M, int64_t N, int64_t K, const TcParams& base,
+             void* scratch, size_t scratch_bytes, cudaStream_t st, const TcNorm* norm = nullptr);
 }  // namespace tpx
