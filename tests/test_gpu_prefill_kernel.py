@@ -14,10 +14,12 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-2
 
 
-@pytest.fixture(autouse=True, params=[(1, 2), (1, 1), (0, 2), (0, 1)], ids=["pair-uks2", "pair-uks1", "one-uks2", "one-uks1"])
+@pytest.fixture(autouse=True, params=[(1, 2, 1), (1, 1, 1), (1, 2, 0), (0, 2, 1), (0, 1, 1)],
+                ids=["pair-uks2", "pair-uks1", "pair-blockscales", "one-uks2", "one-uks1"])
 def forced(request, cuda):
-    p2, uks = request.param
-    with knob_env(TPX_MXFP4_PATH="tc", TPX_TC_P=1, TPX_TC_P2=p2, TPX_TC_P_UKS=uks):
+    """pair: CTA-pair kernel, with one activation scale per token (default) or per 32 values (TPX_TC_P_ROWS=0)."""
+    p2, uks, rows = request.param
+    with knob_env(TPX_MXFP4_PATH="tc", TPX_TC_P=1, TPX_TC_P2=p2, TPX_TC_P_UKS=uks, TPX_TC_P_ROWS=rows):
         yield
 
 
@@ -52,6 +54,41 @@ def test_gate_up_pair(cuda, M, N, K):
     for _ in range(2):
         y = to_host_bits(F.fc_gate_up(to_dev_bf16(x, cuda), qg, qu))
         assert O.rel_err(y, O.gate_up(x, wg, wu)) <= TOL
+    assert_no_kernel_error()
+
+
+def test_rows_longer_than_the_per_token_split_serves(cuda):
+    """K = 16512: the per-token split keeps a row in registers up to 16384 elements; beyond, block scales are used."""
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    rng = np.random.default_rng(3)
+    M, N, K = 70, 256, 16512
+    q, wd, _ = make_qweight(rng, N, K, "mxfp4", cuda)
+    q.prepare()
+    x = O.randn_bf16(rng, (M, K))
+    y = to_host_bits(F.fc_plain(to_dev_bf16(x, cuda), q))
+    assert O.rel_err(y, O.qlinear(x, wd)) <= TOL
+    assert_no_kernel_error()
+
+
+def test_outlier_channels_keep_their_precision(cuda):
+    """A few activation channels 1000 times larger than the rest (as LLM activations have), with one scale per token: the
+    bound holds with the outliers, and for the same rows without them."""
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    rng = np.random.default_rng(4)
+    M, N, K = 130, 256, 1024
+    q, wd, _ = make_qweight(rng, N, K, "mxfp4", cuda)
+    q.prepare()
+    xf = O.bf16_to_f32(O.randn_bf16(rng, (M, K)))
+    xf[:, [5, 300, 777]] *= 1000.0
+    x = O.f32_to_bf16(xf)
+    y = to_host_bits(F.fc_plain(to_dev_bf16(x, cuda), q))
+    ref = O.qlinear(x, wd)
+    assert O.rel_err(y, ref) <= TOL
+    x2f = xf.copy()
+    x2f[:, [5, 300, 777]] = 0.0
+    x2 = O.f32_to_bf16(x2f)
+    y2 = to_host_bits(F.fc_plain(to_dev_bf16(x2, cuda), q))
+    assert O.rel_err(y2, O.qlinear(x2, wd)) <= TOL
     assert_no_kernel_error()
 
 

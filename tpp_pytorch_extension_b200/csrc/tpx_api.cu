@@ -32,6 +32,7 @@ static void read_knobs() {
   g_knobs.tc_pf = env("TPX_TC_PF", 0);
   g_knobs.tc_p = env("TPX_TC_P", -1);
   g_knobs.tc_p2 = env("TPX_TC_P2", -1);
+  g_knobs.tc_p_rows = env("TPX_TC_P_ROWS", 1);
   g_knobs.tc_p_uks = env("TPX_TC_P_UKS", 2);
   g_knobs.attn_splits = env("TPX_ATTN_SPLITS", 0);
   g_knobs.attn_tc = env("TPX_ATTN_TC", 1);

@@ -67,7 +67,7 @@ void count_launch();  // host-side tally behind tpx_launch_count()
 // TPX_TC_PF (L2 prefetch distance), TPX_ATTN_SPLITS (0 = cost model), TPX_ATTN_TC (0 = prefill attention on the mma.sync kernel). None of them changes a result. `dbg` carries
 // TPX_TC_DBG and is always 0 unless the library was built with -DTPX_DEBUG.
 struct Knobs {
-  int tc_whole, tc_wide, tc_f4, tc_w4, tc4_occ, tc_cluster, tc_pf, tc_p, tc_p2, tc_p_uks, attn_splits, attn_tc, dbg;
+  int tc_whole, tc_wide, tc_f4, tc_w4, tc4_occ, tc_cluster, tc_pf, tc_p, tc_p2, tc_p_uks, tc_p_rows, attn_splits, attn_tc, dbg;
 };
 const Knobs& knobs();
 

@@ -20,30 +20,35 @@
 //     first CTA's barrier, remote for the second CTA), then run bias / activation / gate / residual and the stores while
 //     the next tile's MMAs proceed. A gate/up pair is two consecutive accumulations; the gate values wait in registers.
 // Layouts of the packed weights, scale blocks and activation terms are those of tpx_qlinear_tc.cu (token tile 128).
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
 #include "tpx_tc_ptx.cuh"
 
 namespace tpx {
 
-template <int UKS>
+// ROWS: one activation scale per token (rowscale_split_kernel): no activation scale blocks in the stages.
+template <int UKS, bool ROWS>
 struct Tcp2Cfg {
   static constexpr int A_BYTES = 128 * 128;             // an unpacked 128 x 128 fp4 tile in shared memory
   static constexpr int A_TX = 128 * 64;                 // what its copy accounts for (packed bytes)
   static constexpr int B_BYTES = 128 * 128;             // this CTA's half of B for one k step: 128 rows of one term
-  static constexpr int SF_BYTES = 512 + 1024;           // per k step: own weight block, both activation blocks
+  static constexpr int SF_BYTES = ROWS ? 512 : 512 + 1024;  // per k step: own weight block (+ both activation blocks)
   static constexpr int RAW = UKS * (A_BYTES + B_BYTES + SF_BYTES);
   static constexpr int STAGE_BYTES = (RAW + 1023) / 1024 * 1024;
   static constexpr int TX_CTA = UKS * (A_TX + B_BYTES + SF_BYTES);  // bytes one CTA's copies deliver per stage
   static constexpr int BUDGET = 227 * 1024 - 2048;
   static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int SF_COLS = UKS * 12;              // per k step 4 (weights) + 8 (activations) columns
+  static constexpr int SF_COLS = UKS * (ROWS ? 4 : 12);  // per k step 4 (weights) + 8 (activations) columns
   static constexpr int D_COLS = 256;
+  static constexpr int CONST_COLS = ROWS ? 8 : 0;       // activation scale factors 1.0 for all 256 columns, written once
   static constexpr int TMEM_COLS = 512;
   static constexpr int EPI_SPLIT = 4;                   // warps per 32-lane quarter of tensor memory, 32 tokens each
   static constexpr int THREADS = 96 + 128 * EPI_SPLIT;  // weight producer, MMA issuer, activation producer, epilogue warps
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
   static_assert(STAGES >= 2, "at least two stages");
-  static_assert(D_COLS + STAGES * SF_COLS <= 512, "tensor memory");
+  static_assert(D_COLS + CONST_COLS + STAGES * SF_COLS <= 512, "tensor memory");
 };
 
 __device__ __forceinline__ void t2_tma_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t cluster_bar) {
@@ -86,10 +91,20 @@ __device__ __forceinline__ bool t2_wait_cluster(uint32_t bar, uint32_t parity) {
 // 16 consecutive tokens of output feature n from the accumulator values x (gate/up pair: u holds the up values):
 // bias, activation, gate multiply, residual, bf16 stores; residual / gate inputs arrive packed two per register.
 template <bool DUAL>
-__device__ __forceinline__ void t2_finish16(const TcParams& p, int tok0, int n, float (&x)[16], const float (&u)[16],
-                                            const uint32_t (&resp)[8], const uint32_t (&mulp)[8]) {
+__device__ __forceinline__ void t2_finish16(const TcParams& p, int tok0, int n, float (&x)[16], float (&u)[16],
+                                            const uint32_t (&resp)[8], const uint32_t (&mulp)[8], const float* __restrict__ tok_scale) {
   const int live = p.M - tok0;
   const size_t o0 = (size_t)tok0 * p.N + n;
+  if (tok_scale) {  // the activations were split as x / 2^e per token: give the 2^e back (the array is padded to whole tiles)
+    const float4* sp = reinterpret_cast<const float4*>(tok_scale + tok0);
+    const float4 s0 = __ldg(sp), s1 = __ldg(sp + 1), s2 = __ldg(sp + 2), s3 = __ldg(sp + 3);
+    const float sc[16] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w, s2.x, s2.y, s2.z, s2.w, s3.x, s3.y, s3.z, s3.w};
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      x[j] *= sc[j];
+      if (DUAL) u[j] *= sc[j];
+    }
+  }
   if (p.bias) {
     const float b = bf16_bits_to_f32(p.bias[n]);
 #pragma unroll
@@ -137,13 +152,126 @@ __device__ __forceinline__ void t2_preload16(const uint16_t* __restrict__ src, i
   for (int j = 0; j < 8; j++) pk[j] = (uint32_t)t[2 * j] | ((uint32_t)t[2 * j + 1] << 16);
 }
 
+// Activation split with ONE power-of-two scale per token instead of one per 32 values: x / 2^e as a hi and a lo E4M3
+// term, 2^e in `tok_scale` for the epilogue. The activation scale factors of the block-scaled MMA are then the constant
+// 1.0, written to tensor memory once per kernel instead of copied per k step (two of the three scale-factor copies of a
+// k step, each of which holds the tensor pipe for about 100 cycles). The row maximum lands in [128, 256) of E4M3's
+// range (largest finite value 448, smallest subnormal 2^-9): values down to 2^-17 of the row maximum keep a non-zero hi
+// term, so the two terms carry 8 significant bits wherever the value matters to a dot product with the row.
+// One CTA per token row, the row in registers (VECS x 256 threads x 8 elements); optional RMSNorm first
+// (llama_rms_norm, src/csrc/llm/fused_llm_infer.cpp:336-363, rounded to bf16 as the reference stores it).
+// Term layout as split_activations_kernel with 128-token tiles: [tm][k step][hi 128 rows | lo 128 rows][128 B].
+constexpr int kRsThreads = 256;
+template <int VECS>
+__global__ void __launch_bounds__(kRsThreads) rowscale_split_kernel(const uint16_t* __restrict__ x, const void* __restrict__ gamma, int gamma_f32,
+                                                                    float eps, int M, int K, int KS, uint8_t* __restrict__ terms,
+                                                                    float* __restrict__ tok_scale) {
+  __shared__ float red[kRsThreads / 32];
+  pdl_trigger();
+  pdl_wait();
+  const int tok = blockIdx.x;
+  const bool live_row = tok < M;
+  const int nv = K / 8, nvp = KS * 16;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)tok * K);
+  float f[VECS][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int q = 0; q < VECS; q++) {
+    const int i = threadIdx.x + q * kRsThreads;
+    const bool have = live_row && i < nv;
+    const uint4 v = have ? xr[i] : make_uint4(0, 0, 0, 0);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      f[q][2 * j] = bf16_bits_to_f32((uint16_t)(w[j] & 0xffff));
+      f[q][2 * j + 1] = bf16_bits_to_f32((uint16_t)(w[j] >> 16));
+      ss += f[q][2 * j] * f[q][2 * j] + f[q][2 * j + 1] * f[q][2 * j + 1];
+    }
+  }
+  if (gamma) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kRsThreads / 32; w++) tot += red[w];
+    __syncthreads();
+    const float inv = rsqrtf(tot / (float)K + eps);
+#pragma unroll
+    for (int q = 0; q < VECS; q++) {
+      const int i = threadIdx.x + q * kRsThreads;
+      if (!(live_row && i < nv)) continue;
+      float g[8];
+      if (gamma_f32) {
+        const float4 g0 = reinterpret_cast<const float4*>(gamma)[2 * i], g1 = reinterpret_cast<const float4*>(gamma)[2 * i + 1];
+        g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+      } else {
+        const uint4 gv = reinterpret_cast<const uint4*>(gamma)[i];
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          g[2 * j] = bf16_bits_to_f32((uint16_t)(gw[j] & 0xffff));
+          g[2 * j + 1] = bf16_bits_to_f32((uint16_t)(gw[j] >> 16));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; j++) f[q][j] = bf16_bits_to_f32(f32_to_bf16_bits(f[q][j] * inv * g[j]));
+    }
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int q = 0; q < VECS; q++) {
+#pragma unroll
+    for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(f[q][j]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < kRsThreads / 32; w++) amax = fmaxf(amax, red[w]);
+  int e = 0;
+  if (amax > 0.0f && amax < INFINITY) e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 - 7;
+  e = max(-126, min(127, e));
+  const float down = __uint_as_float((uint32_t)(127 - e) << 23);
+  if (threadIdx.x == 0) tok_scale[tok] = __uint_as_float((uint32_t)(127 + e) << 23);
+  const int tm = tok / 128, r = tok % 128;
+#pragma unroll
+  for (int q = 0; q < VECS; q++) {
+    const int i = threadIdx.x + q * kRsThreads;  // vector index: 16 vectors per k step of 128
+    if (i >= nvp) continue;
+    uint32_t ph[2], pl[2];
+#pragma unroll
+    for (int h2 = 0; h2 < 2; h2++) {
+      uint32_t h4 = 0, l4 = 0;
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        const float a = f[q][4 * h2 + 2 * j] * down, b = f[q][4 * h2 + 2 * j + 1] * down;
+        __nv_fp8x2_storage_t hs = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+        __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(hs, __NV_E4M3);
+        const float ra = a - __half2float(__ushort_as_half(hr.x)), rb = b - __half2float(__ushort_as_half(hr.y));
+        __nv_fp8x2_storage_t ls = __nv_cvt_float2_to_fp8x2(make_float2(ra, rb), __NV_SATFINITE, __NV_E4M3);
+        h4 |= (uint32_t)hs << (16 * j);
+        l4 |= (uint32_t)ls << (16 * j);
+      }
+      ph[h2] = h4;
+      pl[h2] = l4;
+    }
+    const int ks = i >> 4, c = i & 15;  // k step and 8-byte column inside its 128-byte row
+    const size_t step = (size_t)tm * KS + ks;
+    *reinterpret_cast<uint2*>(terms + (step * 256 + r) * 128 + c * 8) = make_uint2(ph[0], ph[1]);
+    *reinterpret_cast<uint2*>(terms + (step * 256 + 128 + r) * 128 + c * 8) = make_uint2(pl[0], pl[1]);
+  }
+}
+
 // UKS k steps of 128 per pipeline stage; DUAL: gate/up pair. Launched as clusters of two CTAs; p.KS counts stages per
 // accumulation; pairs of feature tiles x token tiles are cut evenly between the clusters.
-template <int UKS, bool DUAL>
-__global__ void __launch_bounds__(Tcp2Cfg<UKS>::THREADS, 1)
+template <int UKS, bool DUAL, bool ROWS>
+__global__ void __launch_bounds__(Tcp2Cfg<UKS, ROWS>::THREADS, 1)
 qlinear_tcp2_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                     const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB, TcParams p) {
-  using C = Tcp2Cfg<UKS>;
+  using C = Tcp2Cfg<UKS, ROWS>;
   constexpr int NWT = DUAL ? 2 : 1;  // accumulations per output tile
   extern __shared__ unsigned char tcp2_smem_raw[];
   __shared__ __align__(8) unsigned long long bar_full[C::STAGES], bar_empty[C::STAGES];
@@ -181,10 +309,20 @@ qlinear_tcp2_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
-  tc_cluster_sync();  // the partner's barriers and tensor memory exist before anything is sent to them
   tc_fence_after();
   const uint32_t tmem = tmem_holder;
-  const uint32_t sf_col0 = C::D_COLS;
+  if (ROWS && warp >= 3 && warp < 7) {  // one warp per 32-lane quarter: UE8M0 127 = 1.0 in every byte of the 8 columns
+    const uint32_t t = tmem + (((uint32_t)((warp & 3) * 32)) << 16) + C::D_COLS;
+    const uint4 ones = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+    tc_st_x4(t, ones);
+    tc_st_x4(t + 4, ones);
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_cluster_sync();  // the partner's barriers and tensor memory exist before anything is sent to them
+  tc_fence_after();
+  const uint32_t sf_col0 = C::D_COLS + C::CONST_COLS;
   if (threadIdx.x == 0) tc_stamp(p, 1);
   pdl_trigger();
 
@@ -251,7 +389,7 @@ qlinear_tcp2_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         const int xrow = (tm * KU + ku) * (UKS * 256) + crank * 128;
 #pragma unroll
         for (int kk = 0; kk < UKS; kk++) t2_tma_2d(sb + kk * C::B_BYTES, &tmX, 0, xrow + kk * 256, lbar);
-        t2_tma_2d(st + UKS * (C::A_BYTES + C::B_BYTES) + UKS * 512, &tmSFB, 0, (tm * KU + ku) * UKS * 2, lbar);
+        if (!ROWS) t2_tma_2d(st + UKS * (C::A_BYTES + C::B_BYTES) + UKS * 512, &tmSFB, 0, (tm * KU + ku) * UKS * 2, lbar);
       }
     }
     __syncwarp();
@@ -290,8 +428,10 @@ qlinear_tcp2_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll
           for (int kk = 0; kk < UKS; kk++) {
             t2_cp_sf(sf_t + kk * 4, tc_sf_desc(ssf + kk * 512));
-            t2_cp_sf(sf_t + UKS * 4 + kk * 8, tc_sf_desc(ssf + UKS * 512 + kk * 1024));
-            t2_cp_sf(sf_t + UKS * 4 + kk * 8 + 4, tc_sf_desc(ssf + UKS * 512 + kk * 1024 + 512));
+            if (!ROWS) {
+              t2_cp_sf(sf_t + UKS * 4 + kk * 8, tc_sf_desc(ssf + UKS * 512 + kk * 1024));
+              t2_cp_sf(sf_t + UKS * 4 + kk * 8 + 4, tc_sf_desc(ssf + UKS * 512 + kk * 1024 + 512));
+            }
           }
 #pragma unroll
           for (int kk = 0; kk < UKS; kk++) {
@@ -302,7 +442,7 @@ qlinear_tcp2_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
               const uint64_t bdesc = tc_smem_desc(sb + kk * C::B_BYTES) + (uint64_t)(2 * j);
               const uint32_t acc = (ku == 0 && kk == 0 && j == 0) ? 0u : 1u;
               t2_mma(tmem, adesc, bdesc, idesc, (sf_t + kk * 4) | ((uint32_t)j << 30),
-                     (sf_t + UKS * 4 + kk * 8) | ((uint32_t)j << 30), acc);
+                     (ROWS ? tmem + C::D_COLS : sf_t + UKS * 4 + kk * 8) | ((uint32_t)j << 30), acc);
             }
           }
           t2_commit_both(tc_smem_u32(&bar_empty[s]));
@@ -382,7 +522,7 @@ qlinear_tcp2_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           x[j] = g[c * 16 + j];
           uf[j] = DUAL ? u[c * 16 + j] : 0.0f;
         }
-        if (live && tokb + c * 16 < p.M) t2_finish16<DUAL>(p, tokb + c * 16, n, x, uf, resp[c], mulp[c]);
+        if (live && tokb + c * 16 < p.M) t2_finish16<DUAL>(p, tokb + c * 16, n, x, uf, resp[c], mulp[c], ROWS ? p.partial : nullptr);
       }
     }
   }
@@ -422,8 +562,8 @@ static int tcp2_make_sf_map(CUtensorMap* m, const void* base, uint64_t rows, uin
 }
 
 struct Tcp2Plan {
-  int TN, TM, KS, Mpad, uks;
-  size_t off_terms, off_sfb, total;
+  int TN, TM, KS, Mpad, uks, rows;  // rows: one activation scale per token (rows of up to 16384 elements)
+  size_t off_terms, off_sfb, off_tscale, total;
 };
 
 static Tcp2Plan tcp2_plan(int64_t M, int64_t N, int64_t K, bool pair) {
@@ -437,6 +577,8 @@ static Tcp2Plan tcp2_plan(int64_t M, int64_t N, int64_t K, bool pair) {
   auto bump = [&](size_t bytes) { size_t r = o; o += (bytes + 1023) & ~(size_t)1023; return r; };
   pl.off_terms = bump((size_t)pl.Mpad * pl.KS * 128 * 2);
   pl.off_sfb = bump((size_t)pl.TM * pl.KS * 2 * 512);
+  pl.off_tscale = bump((size_t)pl.Mpad * sizeof(float));
+  pl.rows = (knobs().tc_p_rows != 0 && pl.KS * 16 <= kRsThreads * 8) ? 1 : 0;
   pl.total = o;
   return pl;
 }
@@ -456,17 +598,17 @@ bool tcp2_serves(int64_t M, int64_t N, int64_t K, bool pair) {
 
 size_t tcp2_scratch_bytes(int64_t M, int64_t N, int64_t K, bool pair) { return tcp2_plan(M, N, K, pair).total; }
 
-template <int UKS, bool DUAL>
+template <int UKS, bool DUAL, bool ROWS>
 static int tcp2_launch(const CUtensorMap& w, const CUtensorMap& x, const CUtensorMap& sfa, const CUtensorMap& sfb, const TcParams& p,
                        long long pairs, cudaStream_t st) {
-  using C = Tcp2Cfg<UKS>;
+  using C = Tcp2Cfg<UKS, ROWS>;
   static bool opted[16] = {};
   static int resident[16] = {};  // clusters of two that fit the device at once
   int dev = 0;
   cudaGetDevice(&dev);
   const int di = (dev >= 0 && dev < 16) ? dev : 0;
   if (!opted[di]) {
-    TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_tcp2_kernel<UKS, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+    TPX_CUDA_OK(cudaFuncSetAttribute(qlinear_tcp2_kernel<UKS, DUAL, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     opted[di] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -485,7 +627,7 @@ static int tcp2_launch(const CUtensorMap& w, const CUtensorMap& x, const CUtenso
   if (resident[di] == 0) {
     cfg.gridDim = dim3((unsigned)(2 * (sm_count() / 2)));
     int n = 0;
-    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, qlinear_tcp2_kernel<UKS, DUAL>, &cfg);
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, qlinear_tcp2_kernel<UKS, DUAL, ROWS>, &cfg);
     if (e != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
     resident[di] = n > 0 ? n : -1;
   }
@@ -494,7 +636,7 @@ static int tcp2_launch(const CUtensorMap& w, const CUtensorMap& x, const CUtenso
   if (clusters > sm_count() / 2) clusters = sm_count() / 2;
   cfg.gridDim = dim3((unsigned)(2 * clusters));
   count_launch();
-  TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tcp2_kernel<UKS, DUAL>, w, x, sfa, sfb, p));
+  TPX_CUDA_OK(cudaLaunchKernelEx(&cfg, qlinear_tcp2_kernel<UKS, DUAL, ROWS>, w, x, sfa, sfb, p));
   return TPX_OK;
 }
 
@@ -505,7 +647,20 @@ int tcp2_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x
               scratch_bytes);
   unsigned char* sc = reinterpret_cast<unsigned char*>(scratch);
   uint8_t *terms = sc + pl.off_terms, *sfb = sc + pl.off_sfb;
-  {
+  float* tscale = reinterpret_cast<float*>(sc + pl.off_tscale);
+  if (pl.rows) {
+    TPX_REQUIRE(((uintptr_t)x & 15) == 0 && (!norm || !norm->gamma || ((uintptr_t)norm->gamma & 15) == 0), TPX_ERR_ARG,
+                "qlinear_mxfp4_tc: x and gamma must be 16-byte aligned");
+    const void* gamma = norm ? norm->gamma : nullptr;
+    const int gf = norm ? norm->gamma_f32 : 0;
+    const float eps = norm ? norm->eps : 0.0f;
+    if (pl.KS * 16 <= kRsThreads * 4)
+      TPX_CUDA_OK(launch_pdl(rowscale_split_kernel<4>, dim3((unsigned)pl.Mpad), dim3(kRsThreads), 0, st, x, gamma, gf, eps, (int)M, (int)K, pl.KS,
+                             terms, tscale));
+    else
+      TPX_CUDA_OK(launch_pdl(rowscale_split_kernel<8>, dim3((unsigned)pl.Mpad), dim3(kRsThreads), 0, st, x, gamma, gf, eps, (int)M, (int)K, pl.KS,
+                             terms, tscale));
+  } else {
     int rc0 = tc_launch_split(x, (int)M, (int)K, pl.Mpad, pl.KS, 128, pl.uks, 0, terms, sfb, st, norm);
     if (rc0) return rc0;
   }
@@ -522,14 +677,18 @@ int tcp2_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x
   if (rc) return rc;
   TcParams p = base;
   p.sfa = sfa; p.sfa2 = nullptr; p.sfb = sfb;
-  p.partial = nullptr;
+  p.partial = pl.rows ? tscale : nullptr;  // this kernel has no partial tiles: the field carries the per-token scales
   p.counters = reinterpret_cast<unsigned*>(sc);
   p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KS / pl.uks; p.TN = pl.TN; p.TM = pl.TM;
   p.whole_tiles = 1; p.cluster = 2;
   const long long pairs = (long long)((pl.TN + 1) / 2) * pl.TM;
-  if (pl.uks == 2) return pair ? tcp2_launch<2, true>(mw, mx, msfa, msfb, p, pairs, st) : tcp2_launch<2, false>(mw, mx, msfa, msfb, p, pairs, st);
-  return pair ? tcp2_launch<1, true>(mw, mx, msfa, msfb, p, pairs, st) : tcp2_launch<1, false>(mw, mx, msfa, msfb, p, pairs, st);
+  if (pl.rows) {
+    if (pl.uks == 2) return pair ? tcp2_launch<2, true, true>(mw, mx, msfa, msfb, p, pairs, st) : tcp2_launch<2, false, true>(mw, mx, msfa, msfb, p, pairs, st);
+    return pair ? tcp2_launch<1, true, true>(mw, mx, msfa, msfb, p, pairs, st) : tcp2_launch<1, false, true>(mw, mx, msfa, msfb, p, pairs, st);
+  }
+  if (pl.uks == 2) return pair ? tcp2_launch<2, true, false>(mw, mx, msfa, msfb, p, pairs, st) : tcp2_launch<2, false, false>(mw, mx, msfa, msfb, p, pairs, st);
+  return pair ? tcp2_launch<1, true, false>(mw, mx, msfa, msfb, p, pairs, st) : tcp2_launch<1, false, false>(mw, mx, msfa, msfb, p, pairs, st);
 }
 
 }  // namespace tpx
