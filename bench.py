@@ -539,7 +539,7 @@ def run_ours(args):
                         "peak_src": pk["src"]},
             "roofline": {"bound": "hbm",
                          "kernel": f"MXFP4 gate/up pair GEMM, M={SWEEP[dom]} (tcgen05: qlinear_tc4_kernel, kind::mxf4, for M <= 32; "
-                                   f"qlinear_tcw_kernel, kind::mxf8f6f4, for M <= 64; qlinear_tcp_kernel beyond)"
+                                   f"qlinear_tcw_kernel, kind::mxf8f6f4, for M <= 64; qlinear_tcp2_kernel, cta_group::2, beyond)"
                                    if F.mxfp4_path() == "tc" else f"qlinear_stream gate/up pair, M={SWEEP[dom]}",
                          "achieved": dom_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": dom_gbs / pk["hbm_gbs"],
                          "peak_src": pk["src"], "traffic": NCU_TRAFFIC.get(SWEEP[dom]),

@@ -161,12 +161,14 @@ __device__ __forceinline__ void t2_preload16(const uint16_t* __restrict__ src, i
 // One CTA per token row, the row in registers (VECS x 256 threads x 8 elements); optional RMSNorm first
 // (llama_rms_norm, src/csrc/llm/fused_llm_infer.cpp:336-363, rounded to bf16 as the reference stores it).
 // Term layout as split_activations_kernel with 128-token tiles: [tm][k step][hi 128 rows | lo 128 rows][128 B].
+// Rows of up to 4096 elements run with 128 threads (more CTAs, hence more loads in flight, per SM: about 4 us less for
+// 4096 x 4096), longer ones with 256.
 constexpr int kRsThreads = 256;
-template <int VECS>
-__global__ void __launch_bounds__(kRsThreads) rowscale_split_kernel(const uint16_t* __restrict__ x, const void* __restrict__ gamma, int gamma_f32,
+template <int VECS, int THREADS>
+__global__ void __launch_bounds__(THREADS) rowscale_split_kernel(const uint16_t* __restrict__ x, const void* __restrict__ gamma, int gamma_f32,
                                                                     float eps, int M, int K, int KS, uint8_t* __restrict__ terms,
                                                                     float* __restrict__ tok_scale) {
-  __shared__ float red[kRsThreads / 32];
+  __shared__ float red[THREADS / 32];
   pdl_trigger();
   pdl_wait();
   const int tok = blockIdx.x;
@@ -177,7 +179,7 @@ __global__ void __launch_bounds__(kRsThreads) rowscale_split_kernel(const uint16
   float ss = 0.0f;
 #pragma unroll
   for (int q = 0; q < VECS; q++) {
-    const int i = threadIdx.x + q * kRsThreads;
+    const int i = threadIdx.x + q * THREADS;
     const bool have = live_row && i < nv;
     const uint4 v = have ? xr[i] : make_uint4(0, 0, 0, 0);
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -195,12 +197,12 @@ __global__ void __launch_bounds__(kRsThreads) rowscale_split_kernel(const uint16
     __syncthreads();
     float tot = 0.0f;
 #pragma unroll
-    for (int w = 0; w < kRsThreads / 32; w++) tot += red[w];
+    for (int w = 0; w < THREADS / 32; w++) tot += red[w];
     __syncthreads();
     const float inv = rsqrtf(tot / (float)K + eps);
 #pragma unroll
     for (int q = 0; q < VECS; q++) {
-      const int i = threadIdx.x + q * kRsThreads;
+      const int i = threadIdx.x + q * THREADS;
       if (!(live_row && i < nv)) continue;
       float g[8];
       if (gamma_f32) {
@@ -230,7 +232,7 @@ __global__ void __launch_bounds__(kRsThreads) rowscale_split_kernel(const uint16
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
   __syncthreads();
 #pragma unroll
-  for (int w = 0; w < kRsThreads / 32; w++) amax = fmaxf(amax, red[w]);
+  for (int w = 0; w < THREADS / 32; w++) amax = fmaxf(amax, red[w]);
   int e = 0;
   if (amax > 0.0f && amax < INFINITY) e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 - 7;
   e = max(-126, min(127, e));
@@ -239,7 +241,7 @@ __global__ void __launch_bounds__(kRsThreads) rowscale_split_kernel(const uint16
   const int tm = tok / 128, r = tok % 128;
 #pragma unroll
   for (int q = 0; q < VECS; q++) {
-    const int i = threadIdx.x + q * kRsThreads;  // vector index: 16 vectors per k step of 128
+    const int i = threadIdx.x + q * THREADS;  // vector index: 16 vectors per k step of 128
     if (i >= nvp) continue;
     uint32_t ph[2], pl[2];
 #pragma unroll
@@ -654,12 +656,15 @@ int tcp2_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x
     const void* gamma = norm ? norm->gamma : nullptr;
     const int gf = norm ? norm->gamma_f32 : 0;
     const float eps = norm ? norm->eps : 0.0f;
-    if (pl.KS * 16 <= kRsThreads * 4)
-      TPX_CUDA_OK(launch_pdl(rowscale_split_kernel<4>, dim3((unsigned)pl.Mpad), dim3(kRsThreads), 0, st, x, gamma, gf, eps, (int)M, (int)K, pl.KS,
+    if (pl.KS * 16 <= 128 * 4)
+      TPX_CUDA_OK(launch_pdl(rowscale_split_kernel<4, 128>, dim3((unsigned)pl.Mpad), dim3(128), 0, st, x, gamma, gf, eps, (int)M, (int)K, pl.KS,
                              terms, tscale));
+    else if (pl.KS * 16 <= kRsThreads * 4)
+      TPX_CUDA_OK(launch_pdl(rowscale_split_kernel<4, kRsThreads>, dim3((unsigned)pl.Mpad), dim3(kRsThreads), 0, st, x, gamma, gf, eps, (int)M,
+                             (int)K, pl.KS, terms, tscale));
     else
-      TPX_CUDA_OK(launch_pdl(rowscale_split_kernel<8>, dim3((unsigned)pl.Mpad), dim3(kRsThreads), 0, st, x, gamma, gf, eps, (int)M, (int)K, pl.KS,
-                             terms, tscale));
+      TPX_CUDA_OK(launch_pdl(rowscale_split_kernel<8, kRsThreads>, dim3((unsigned)pl.Mpad), dim3(kRsThreads), 0, st, x, gamma, gf, eps, (int)M,
+                             (int)K, pl.KS, terms, tscale));
   } else {
     int rc0 = tc_launch_split(x, (int)M, (int)K, pl.Mpad, pl.KS, 128, pl.uks, 0, terms, sfb, st, norm);
     if (rc0) return rc0;
