@@ -208,6 +208,12 @@ int tpx_qlinear_qint8_tc(const int8_t* wq, const float* swT, const uint16_t* x, 
 int tpx_rmsnorm(const uint16_t* x, const void* gamma, int gamma_is_f32, float eps, int64_t rows, int64_t D,
                 uint16_t* y, void* stream);
 
+/* LayerNorm: y = (x - mean) * rsqrt(var + eps) * gamma + beta, fp32 statistics, variance around the mean. Replaces
+ * lyr_norm (src/csrc/llm/fused_llm_infer.cpp:256-306; LayerNormFwdTPP src/csrc/xsmm_functors.h:4720), the norm of the
+ * OPT and GPT-J decoder blocks. gamma and beta are both bf16 or, with params_are_f32 != 0, both fp32.           */
+int tpx_layernorm(const uint16_t* x, const void* gamma, const void* beta, int params_are_f32, float eps, int64_t rows,
+                  int64_t D, uint16_t* y, void* stream);
+
 /* Greedy sampling: out[r] = index of the largest of x[r][0..n), the first among equals, NaN above every number, as
  * torch.argmax(-1) of the head's logits returns it (the reference drives HF generate with --greedy,
  * examples/llm/run_generation.py:337-339). x bf16 [rows][n], out int64 [rows].                          */

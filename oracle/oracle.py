@@ -312,6 +312,17 @@ def rmsnorm(x_bf16, g_bf16, eps):
     return y
 
 
+def layernorm(x_bf16, g_bf16, b_bf16, eps):
+    """lyr_norm (src/csrc/llm/fused_llm_infer.cpp:256-306, LayerNormFwdTPP): fp32 mean and variance around the mean,
+    y = (x - mean) * rsqrt(var + eps) * gamma + beta, rounded to bf16."""
+    x = bf16_to_f32(_c(x_bf16, np.uint16)).astype(np.float32)
+    g = bf16_to_f32(_c(g_bf16, np.uint16)).astype(np.float32)
+    b = bf16_to_f32(_c(b_bf16, np.uint16)).astype(np.float32)
+    mean = x.mean(-1, keepdims=True, dtype=np.float32)
+    var = ((x - mean) ** 2).mean(-1, keepdims=True, dtype=np.float32)
+    return f32_to_bf16(((x - mean) / np.sqrt(var + np.float32(eps))) * g + b)
+
+
 def rope_table(max_pos, head_dim, theta):
     """cat(cos, sin).view(2, MP, head_dim) fp32 as built in OptimizeModelForLlama
     (src/tpp_pytorch_extension/llm/fused_llama_infer.py:186-204); HF's default rotary embedding:
@@ -424,6 +435,37 @@ def llama_layer(hs, mask, pos, W, cache, layer_idx, n_q, n_kv, head_dim, eps, ep
     out = qlinear(inter, W["down"], res=so, res_scale=scale)
     if world > 1:
         out = allreduce(out)
+    return out.reshape(B, S, D)
+
+
+def opt_layer(hs, mask, W, cache, layer_idx, n_heads, head_dim, eps1, eps2, do_layer_norm_before=True, world=1, allreduce=None):
+    """OPTDecoderLayer::_forward (src/csrc/llm/fused_llm_infer.cpp:978-1068): LayerNorm before (or after) each half,
+    q/k/v with biases, attention without rotary embedding, out_proj + residual, fc1 + ReLU, fc2 + residual.
+    W: plain fp32 weights q,k,v,o,fc1,fc2, bf16 biases bq,bk,bv,bo,b1,b2 and LayerNorm parameters g1,b_ln1,g2,b_ln2."""
+    B, S, D = hs.shape
+    scale = 1.0 / world
+    res = hs.reshape(B * S, D)
+    x = layernorm(res, W["g1"], W["b_ln1"], eps1) if do_layer_norm_before else res
+    q = qlinear(x, W["q"], bias=W["bq"]).reshape(B, S, n_heads, head_dim)
+    k = qlinear(x, W["k"], bias=W["bk"]).reshape(B, S, n_heads, head_dim)
+    v = qlinear(x, W["v"], bias=W["bv"]).reshape(B, S, n_heads, head_dim)
+    kc, vc = cache.update(k, v, layer_idx)
+    key_len = cache.get_seq_length(layer_idx)
+    q5 = np.ascontiguousarray(q.reshape(B, S, n_heads, 1, head_dim).transpose(0, 2, 1, 3, 4))
+    ctx = attention(q5, kc, vc, mask, key_len, causal=True)
+    ctx = np.ascontiguousarray(ctx.transpose(0, 2, 1, 3, 4)).reshape(B * S, n_heads * head_dim)
+    so = qlinear(ctx, W["o"], bias=W["bo"], res=res, res_scale=scale)
+    if world > 1:
+        so = allreduce(so)
+    if not do_layer_norm_before:
+        so = layernorm(so, W["g1"], W["b_ln1"], eps1)
+    x = layernorm(so, W["g2"], W["b_ln2"], eps2) if do_layer_norm_before else so
+    inter = qlinear(x, W["fc1"], bias=W["b1"], act=ACT_RELU)
+    out = qlinear(inter, W["fc2"], bias=W["b2"], res=so, res_scale=scale)
+    if world > 1:
+        out = allreduce(out)
+    if not do_layer_norm_before:
+        out = layernorm(out, W["g2"], W["b_ln2"], eps2)
     return out.reshape(B, S, D)
 
 

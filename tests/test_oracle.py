@@ -206,3 +206,15 @@ def test_qint8_block_size_rule_matches_oracle():
     for bad in (0, -4, 6):
         with pytest.raises(_lib.TpxError):
             qint8_block_size_used(4096, 64, bad)
+
+
+def test_layernorm_restatement_matches_torch():
+    """lyr_norm restated in numpy against torch.nn.functional.layer_norm in fp32 (one bf16 rounding apart)."""
+    import torch
+    rng = np.random.default_rng(5)
+    x = O.f32_to_bf16(O.bf16_to_f32(O.randn_bf16(rng, (6, 320))) * 2.0 - 0.7)
+    g, b = O.randn_bf16(rng, (320,), 0.5), O.randn_bf16(rng, (320,), 0.3)
+    y = O.bf16_to_f32(O.layernorm(x, g, b, 1e-5))
+    want = torch.nn.functional.layer_norm(torch.from_numpy(O.bf16_to_f32(x)), (320,), torch.from_numpy(O.bf16_to_f32(g)),
+                                          torch.from_numpy(O.bf16_to_f32(b)), 1e-5).numpy()
+    assert np.abs(y - want).max() <= 2.0 ** -7 * np.abs(want).max()

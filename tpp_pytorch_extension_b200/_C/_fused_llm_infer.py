@@ -209,6 +209,22 @@ def fc_plain_norm(input, gamma, eps, weight, bias=None):
 
 
 # --------------------------------------------------------------------------- decoder-layer pieces
+def layer_norm(x, gamma, beta, eps):
+    """lyr_norm (src/csrc/llm/fused_llm_infer.cpp:256-306): LayerNorm over the last dimension, bf16 in and out, gamma and
+    beta both bf16 or both fp32."""
+    _lib.require_cuda(x, "input")
+    if x.dtype != torch.bfloat16:
+        raise _lib.TpxError("lyr_norm: input must be bfloat16")
+    if gamma.dtype != beta.dtype or gamma.dtype not in (torch.bfloat16, torch.float32):
+        raise _lib.TpxError("lyr_norm: unsupported gamma dtype")
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    D = x.shape[-1]
+    _lib.check(_lib.lib().tpx_layernorm(x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), int(gamma.dtype == torch.float32), float(eps),
+                                        x.numel() // D if D else 0, D, y.data_ptr(), _lib.stream()))
+    return y
+
+
 def rms_norm(x, gamma, eps):
     """llama_rms_norm (src/csrc/llm/fused_llm_infer.cpp:336-363)."""
     _lib.require_cuda(x, "input")
@@ -404,3 +420,105 @@ class Qwen2DecoderLayer(LlamaDecoderLayer):
             if b.numel() != n:
                 raise _lib.TpxError("Qwen2DecoderLayer: bias length does not match its projection")
         self.Bqkv = torch.cat([bq.reshape(-1), bk.reshape(-1), bv.reshape(-1)]).to(self.EP.device, torch.bfloat16).contiguous()
+
+
+class OPTDecoderLayer:
+    """torch.classes.tpp_llm.OPTDecoderLayer (src/csrc/llm/fused_llm_infer.cpp:850-1069).
+
+    params, in the reference's order (:877-898): [ln1_gamma, ln1_beta, ln2_gamma, ln2_beta, q, q_bias, k, k_bias, v,
+    v_bias, out_proj, out_bias, fc1, fc1_bias, fc2, fc2_bias]; the linear weights are quantized tensors (or blocked bf16
+    with USE_MXFP4 / USE_QINT8 set, or all plain bf16). No rotary embedding: positions enter through the model's
+    learned position embedding before the first layer."""
+
+    def __init__(self, params, layer_idx, eps1, eps2, H, do_layer_norm_before):
+        import os
+        from . import _qtype
+        if len(params) != 16:
+            raise _lib.TpxError("OPTDecoderLayer expects 16 parameters")
+        (self.G1, self.B1, self.G2, self.B2, Wq, Bq, Wk, Bk, Wv, Bv, Wp, self.Bp, Wi, self.Bi, Wo, self.Bo) = params
+        ws = [Wq, Wk, Wv, Wp, Wi, Wo]
+        if not all(isinstance(w, _qtype.QTensor) for w in ws):
+            if os.environ.get("USE_MXFP4", "0") == "1":
+                ws = [w if isinstance(w, _qtype.QTensor) else _qtype.remap_and_quantize_mxfp4(w) for w in ws]
+            elif os.environ.get("USE_QINT8", "0") == "1":
+                ws = [w if isinstance(w, _qtype.QTensor) else _qtype.remap_and_quantize_qint8(w) for w in ws]
+            elif all(isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16 for w in ws):
+                from ..utils.blocked_layout import unblock_weight
+                ws = [unblock_weight(w) if w.dim() == 5 else w.contiguous() for w in ws]
+            else:
+                raise _lib.TpxError("OPTDecoderLayer: weights must be all quantized tensors or all bf16 tensors")
+        Wq, Wk, Wv, self.Wp, self.Wi, self.Wo = ws
+        self.layer_idx, self.eps1, self.eps2, self.H = int(layer_idx), float(eps1), float(eps2), int(H)
+        self.do_layer_norm_before = bool(do_layer_norm_before)
+        self.bf16 = isinstance(Wq, torch.Tensor)
+        self.Nq = self.Nkv = (Wq.shape[0] if self.bf16 else Wq.out_features) // self.H
+        self.Wqkv = torch.cat([Wq, Wk, Wv], 0).contiguous() if self.bf16 else _cat_q([Wq, Wk, Wv])
+        dev = self.G1.device
+        self.Bqkv = torch.cat([Bq.reshape(-1), Bk.reshape(-1), Bv.reshape(-1)]).to(dev, torch.bfloat16).contiguous()
+        self.Bp, self.Bi, self.Bo = (b.to(dev, torch.bfloat16).contiguous() for b in (self.Bp, self.Bi, self.Bo))
+        # the rotary kernel also appends k and v to the cache and lays q out for attention; with an empty table
+        # (max_positions 0) it rotates nothing
+        self._no_rope = torch.zeros((2, 1, self.H), dtype=torch.float32, device=dev)
+        if not self.bf16:
+            for w in (self.Wqkv, self.Wp, self.Wi, self.Wo):
+                w.prepare()
+
+    def forward(self, inp, cache, use_cache=True, dev_len=None):
+        """inp = [hidden_states [B,S,D] bf16, additive mask [B,Spad]] (OPTDecoderLayer::_forward, :978-1068); a third
+        element (position ids), if present, is ignored."""
+        from ._tpp_attn import attention
+        hs, am = inp[0], inp[1]
+        _lib.require_cuda(hs, "hidden_states")
+        B, S, D = hs.shape
+        ws = get_pg_size()
+        scale = 1.0 / ws
+        L = _lib.lib()
+        res = hs.reshape(B * S, D)
+        sc = _timers.scope
+        x = layer_norm(res, self.G1, self.B1, self.eps1) if self.do_layer_norm_before else res
+        with sc("qkv_gemm", 0, 0):
+            qkv = fc_plain(x, self.Wqkv, self.Bqkv)
+        lc = cache.layer(self.layer_idx)
+        if dev_len is None:
+            lc.ensure(B, self.Nkv, self.H, S, hs.dtype, hs.device)
+        q = torch.empty((B, self.Nkv, S, 1, self.H), dtype=hs.dtype, device=hs.device)
+        pos = torch.zeros((1, S), dtype=torch.int64, device=hs.device)
+        paged = not lc.contiguous()
+        kc, vc = (None, None) if paged else lc.arenas[0]
+        if paged:
+            _lib.check(L.tpx_rope_kv_update_paged(qkv.data_ptr(), self._no_rope.data_ptr(), pos.data_ptr(), B, S, self.Nq, self.Nkv, self.H,
+                                                  0, self.H, 1, lc.offset, lc.capacity(), _lib.ptr(dev_len), q.data_ptr(),
+                                                  lc.k_ptrs.data_ptr(), lc.v_ptrs.data_ptr(), _lib.stream()))
+        else:
+            _lib.check(L.tpx_rope_kv_update(qkv.data_ptr(), self._no_rope.data_ptr(), pos.data_ptr(), B, S, self.Nq, self.Nkv, self.H,
+                                            0, self.H, 1, lc.offset, lc.capacity(), _lib.ptr(dev_len), q.data_ptr(), kc.data_ptr(),
+                                            vc.data_ptr(), _lib.stream()))
+        if dev_len is None:
+            lc.offset += S
+            key_len = lc.offset
+        else:
+            key_len = lc.capacity()
+        with sc("mha", 0, 0):
+            ctx = attention(q, kc, vc, am, key_len, causal=True, out_bsnrh=True, dev_len=dev_len,
+                            pages=(lc.k_ptrs, lc.v_ptrs) if paged else None).view(B * S, self.Nq * self.H)
+        with sc("proj_gemm", 0, 0):
+            so = fc_plain_act(ctx, self.Wp, self.Bp, res=res, res_scale=scale)
+        if ws > 1:
+            allreduce(so)
+        if not self.do_layer_norm_before:
+            so = layer_norm(so, self.G1, self.B1, self.eps1)
+        x = layer_norm(so, self.G2, self.B2, self.eps2) if self.do_layer_norm_before else so
+        with sc("i_gemm", 0, 0):
+            inter = fc_plain_act(x, self.Wi, self.Bi, "relu")
+        with sc("o_gemm", 0, 0):
+            out = fc_plain_act(inter, self.Wo, self.Bo, res=so, res_scale=scale)
+        if ws > 1:
+            allreduce(out)
+        if not self.do_layer_norm_before:
+            out = layer_norm(out, self.G2, self.B2, self.eps2)
+        out = out.view(B, S, D)
+        if use_cache:
+            if paged:
+                return [out, [a[0] for a in lc.arenas], [a[1] for a in lc.arenas]]
+            return [out, kc, vc]
+        return [out]

@@ -50,6 +50,7 @@ _SIGS = {
     "tpx_qlinear_mxfp4_tc_static_max_bytes": (c_sz, []),
     "tpx_qlinear_mxfp4_tc_static": (c_int, [c_vp, c_vp, c_int, c_vp, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp, c_f32, c_vp, c_vp]),
     "tpx_rmsnorm": (c_int, [c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_vp, c_vp]),
+    "tpx_layernorm": (c_int, [c_vp, c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_vp, c_vp]),
     "tpx_argmax_bf16": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp]),
     "tpx_rope_kv_update": (c_int, [c_vp, c_vp, c_vp] + [c_i64] * 10 + [c_vp, c_vp, c_vp, c_vp, c_vp]),
     "tpx_rope_kv_update_paged": (c_int, [c_vp, c_vp, c_vp] + [c_i64] * 10 + [c_vp, c_vp, c_vp, c_vp, c_vp]),

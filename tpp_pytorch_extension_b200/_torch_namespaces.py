@@ -7,6 +7,7 @@ written against the reference runs unchanged:
     torch.classes.tpp_llm.TppCache()
     torch.classes.tpp_llm.LlamaDecoderLayer(params, layer_idx, eps, head_dim, max_positions, rotary_dim).forward(inputs, cache, use_cache)
     torch.classes.tpp_llm.Qwen2DecoderLayer(...)
+    torch.classes.tpp_llm.OPTDecoderLayer(params, layer_idx, eps1, eps2, head_dim, do_layer_norm_before)
 
 The quantized weight carrier of this package is a Python object (the reference's custom quantizer tensors cannot exist
 on a CUDA device without its C++ classes), which an operator schema cannot name; the entries are therefore attached to
@@ -22,5 +23,6 @@ def install():
     for name, fn in (("fc_plain", F.fc_plain), ("set_pg", F.set_pg), ("allreduce", F.allreduce)):
         setattr(ops, name, fn)
     classes = torch.classes.tpp_llm
-    for name, cls in (("TppCache", A.TppCache), ("LlamaDecoderLayer", F.LlamaDecoderLayer), ("Qwen2DecoderLayer", F.Qwen2DecoderLayer)):
+    for name, cls in (("TppCache", A.TppCache), ("LlamaDecoderLayer", F.LlamaDecoderLayer), ("Qwen2DecoderLayer", F.Qwen2DecoderLayer),
+                      ("OPTDecoderLayer", F.OPTDecoderLayer)):
         setattr(classes, name, cls)

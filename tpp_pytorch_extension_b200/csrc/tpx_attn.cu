@@ -57,6 +57,61 @@ __global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const void* __res
   }
 }
 
+// ---------------------------------------------------------------- LayerNorm: one warp per row
+// y = (x - mean) * rsqrt(var + eps) * gamma + beta with fp32 statistics (lyr_norm / LayerNormFwdTPP,
+// src/csrc/llm/fused_llm_infer.cpp:256-306): the norm of the OPT and GPT-J blocks. The variance is taken around the
+// mean in a second pass over the row (it comes from L1), not as E[x^2] - mean^2.
+__device__ __forceinline__ float ln_param(const void* p, int f32, int i) {
+  return f32 ? reinterpret_cast<const float*>(p)[i] : bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(p)[i]);
+}
+__global__ void layernorm_kernel(const uint16_t* __restrict__ x, const void* __restrict__ gamma, const void* __restrict__ beta,
+                                 int params_f32, float eps, int64_t rows, int D, uint16_t* __restrict__ y) {
+  pdl_trigger();
+  pdl_wait();
+  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+  float s = 0.0f;
+  for (int i = lane; i < D / 8; i += 32) {
+    const uint4 v = xr[i];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) s += bf16_bits_to_f32((uint16_t)(w[j] & 0xffff)) + bf16_bits_to_f32((uint16_t)(w[j] >> 16));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  const float mean = s / (float)D;
+  float ss = 0.0f;
+  for (int i = lane; i < D / 8; i += 32) {
+    const uint4 v = xr[i];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float a = bf16_bits_to_f32((uint16_t)(w[j] & 0xffff)) - mean, b = bf16_bits_to_f32((uint16_t)(w[j] >> 16)) - mean;
+      ss += a * a + b * b;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float inv = rsqrtf(ss / (float)D + eps);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * D);
+  for (int i = lane; i < D / 8; i += 32) {
+    const uint4 v = xr[i];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float a = (bf16_bits_to_f32((uint16_t)(w[j] & 0xffff)) - mean) * inv * ln_param(gamma, params_f32, i * 8 + 2 * j) +
+                      ln_param(beta, params_f32, i * 8 + 2 * j);
+      const float b = (bf16_bits_to_f32((uint16_t)(w[j] >> 16)) - mean) * inv * ln_param(gamma, params_f32, i * 8 + 2 * j + 1) +
+                      ln_param(beta, params_f32, i * 8 + 2 * j + 1);
+      o[j] = (uint32_t)f32_to_bf16_bits(a) | ((uint32_t)f32_to_bf16_bits(b) << 16);
+    }
+    yr[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 // Few rows (decoding): one CTA of 256 threads per row, the row kept in registers between the two passes.
 constexpr int kNormThreads = 256;
 constexpr int kNormVecs = 4;  // uint4 vectors per thread held in registers: rows up to 256 * 4 * 8 = 8192 elements
@@ -649,6 +704,17 @@ extern "C" int tpx_rmsnorm(const uint16_t* x, const void* gamma, int gamma_is_f3
   else
     TPX_CUDA_OK(launch_pdl(rmsnorm_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, (cudaStream_t)stream, x, gamma, gamma_is_f32, eps,
                            rows, (int)D, y));
+  return TPX_OK;
+}
+
+extern "C" int tpx_layernorm(const uint16_t* x, const void* gamma, const void* beta, int params_are_f32, float eps, int64_t rows,
+                             int64_t D, uint16_t* y, void* stream) {
+  TPX_REQUIRE(rows >= 0 && D > 0 && D % 8 == 0, TPX_ERR_ARG, "layernorm: D must be a positive multiple of 8 (D=%ld)", (long)D);
+  if (rows == 0) return TPX_OK;
+  TPX_REQUIRE(x && gamma && beta && y, TPX_ERR_ARG, "layernorm: null pointer");
+  TPX_REQUIRE((((uintptr_t)x | (uintptr_t)y) & 15) == 0, TPX_ERR_ARG, "layernorm: x and y must be 16-byte aligned");
+  TPX_CUDA_OK(launch_pdl(layernorm_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, (cudaStream_t)stream, x, gamma, beta,
+                         params_are_f32, eps, rows, (int)D, y));
   return TPX_OK;
 }
 

@@ -19,7 +19,10 @@ import torch
 from tpp_pytorch_extension_b200.llm import fused_llama_infer as FL
 from tpp_pytorch_extension_b200._C import _fused_llm_infer as fused_llm_cpp
 
-MODELS = {"llama2-7b": FL.LLAMA2_7B, "llama3-8b": FL.LLAMA3_8B, "llama2-70b": FL.LLAMA2_70B}
+from tpp_pytorch_extension_b200.llm import fused_opt_infer as FO
+
+MODELS = {"llama2-7b": FL.LLAMA2_7B, "llama3-8b": FL.LLAMA3_8B, "llama2-70b": FL.LLAMA2_70B,
+          "opt-6.7b": FO.OPTShape(32, 4096, 32, 16384, 50272), "opt-30b": FO.OPTShape(48, 7168, 56, 28672, 50272)}
 
 
 def main(argv=None):
@@ -49,8 +52,11 @@ def main(argv=None):
         import dataclasses
         shape = dataclasses.replace(shape, num_hidden_layers=a.layers)
     wd = {"bfloat16": "bf16"}.get(a.weight_dtype, a.weight_dtype)
-    model = FL.build_random_llama(shape, wd, "cuda", max_positions=a.input_tokens + a.max_new_tokens + 8,
-                                  quantize_lm_head=a.quantize_lm_head and wd != "bf16")
+    if isinstance(shape, FO.OPTShape):
+        model = FO.build_random_opt(shape, wd, "cuda")
+    else:
+        model = FL.build_random_llama(shape, wd, "cuda", max_positions=a.input_tokens + a.max_new_tokens + 8,
+                                      quantize_lm_head=a.quantize_lm_head and wd != "bf16")
     g = torch.Generator(device="cpu").manual_seed(1234)
     ids = torch.randint(0, shape.vocab_size, (a.batch_size, a.input_tokens), generator=g).cuda()
 

@@ -86,11 +86,18 @@ class LlamaRunner(torch.nn.Module):
         self.lm_head_w = lm_head_w
         self.only_last_logit = True
 
+    def _embed(self, ids, positions):
+        """Token embedding; model families with learned position embeddings add them here."""
+        return torch.nn.functional.embedding(ids, self.embed)
+
+    def _final_norm(self, hs):
+        return fused_llm_cpp.rms_norm(hs.contiguous(), self.norm_w, self.shape.rms_norm_eps)
+
     def _head(self, hs):
         """Final norm + lm_head on the last position (logits slicing of the reference, fused_llama_infer.py:385-390)."""
         if self.only_last_logit:
             hs = hs[:, -1:, :]
-        hs = fused_llm_cpp.rms_norm(hs.contiguous(), self.norm_w, self.shape.rms_norm_eps)
+        hs = self._final_norm(hs)
         # lm_head_w is a bf16 matrix (the reference's default) or a quantized tensor (its --quantize-lm-head): both go
         # through fc_plain, i.e. this library's own tensor-core kernels
         if get_size() > 1:
@@ -110,10 +117,10 @@ class LlamaRunner(torch.nn.Module):
         if cache is None:
             cache = TppCache()
         B, S = input_ids.shape
-        hs = torch.nn.functional.embedding(input_ids, self.embed)
         past = cache.get_seq_length()
         if position_ids is None:
             position_ids = torch.arange(past, past + S, device=input_ids.device).unsqueeze(0)
+        hs = self._embed(input_ids, position_ids)
         if attention_mask is None:
             attention_mask = torch.ones((B, past + S), device=input_ids.device, dtype=hs.dtype)
         am = cache.align_and_invert_mask(attention_mask, hs)
@@ -163,7 +170,7 @@ class LlamaRunner(torch.nn.Module):
         pos = mask.sum(-1, keepdim=True).to(torch.int64).contiguous()  # next position per sequence (left padding aware)
 
         def step():
-            hs = torch.nn.functional.embedding(tok, self.embed)
+            hs = self._embed(tok, pos)
             for layer in self.layers:
                 hs = layer.forward([hs, am, pos], cpp, True, dev_len=dev_len)[0]
             lg = self._head(hs)
