@@ -171,6 +171,44 @@ QTensor.packed_tc = _packed_tc
 QTensor.packed_i8tc = _packed_i8tc
 
 
+def _state(self):
+    """Everything needed to use this weight again without quantizing or repacking: the quantizer's attributes, the
+    interchange tensors (possibly already dropped) and every kernel layout built so far, on the CPU. What
+    BlockedParameter's state-dict hooks do for blocked weights in the reference
+    (src/tpp_pytorch_extension/utils/blocked_layout.py:309-364), for quantized and packed ones."""
+    cpu = lambda t: None if t is None else t.detach().cpu()
+    pair = getattr(self, "_pair_tc", None)
+    i8 = getattr(self, "_i8tc", None)
+    return {"shape": self.shape, "qscheme": self._qscheme, "block_size": self.block_size, "axis": self.axis, "is_vnni": self.is_vnni,
+            "codes": cpu(self.codes), "scales": cpu(self.scales),
+            "packed": None if self._packed is None else tuple(cpu(t) for t in self._packed),
+            "packed_tc": None if self._packed_tc is None else tuple(cpu(t) for t in self._packed_tc),
+            "pair_tc": None if pair is None else tuple(cpu(t) for t in pair[1]),
+            "i8tc": None if i8 is None else tuple(cpu(t) for t in i8)}
+
+
+def _from_state(st, device, pair_with=None):
+    """Inverse of QTensor.state(). `pair_with`: the up-projection object this gate weight was packed with (the pair
+    layout is looked up by that object's identity)."""
+    dev = lambda t: None if t is None else t.to(device)
+    q = QTensor(dev(st["codes"]), dev(st["scales"]), st["shape"], st["qscheme"], st["block_size"], st["axis"], st["is_vnni"])
+    if st["packed"] is not None:
+        q._packed = tuple(dev(t) for t in st["packed"])
+    if st["packed_tc"] is not None:
+        q._packed_tc = tuple(dev(t) for t in st["packed_tc"])
+    if st["i8tc"] is not None:
+        q._i8tc = tuple(dev(t) for t in st["i8tc"])
+    if st["pair_tc"] is not None:
+        if pair_with is None:
+            raise _lib.TpxError("this weight was packed as the gate of a gate/up pair: pass the up projection")
+        q._pair_tc = (pair_with, tuple(dev(t) for t in st["pair_tc"]))
+    return q
+
+
+QTensor.state = _state
+QTensor.from_state = staticmethod(_from_state)
+
+
 def _prepare(self, drop_interchange=False, pair_with=None):
     """Build the device layout of the kernel family in use now (`pair_with`: this weight is the gate of a
     gate/up pair and is only used that way); optionally free the interchange copy (dequantize() and the

@@ -37,6 +37,8 @@ def main(argv=None):
     ap.add_argument("--layers", type=int, default=0, help="keep only this many decoder layers (0 = all)")
     ap.add_argument("--no-graph", action="store_true", help="decode eagerly instead of replaying a CUDA graph")
     ap.add_argument("--quantize-lm-head", action="store_true", help="quantize the lm_head like the decoder linears (bf16 otherwise)")
+    ap.add_argument("--save-sharded-model", action="store_true", help="write this rank's quantized, packed shard to ./sharded_model/r<rank>_<size>/model.pt")
+    ap.add_argument("--load-sharded-model", action="store_true", help="read the shard written by --save-sharded-model instead of building the model")
     a = ap.parse_args(argv)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -52,11 +54,16 @@ def main(argv=None):
         import dataclasses
         shape = dataclasses.replace(shape, num_hidden_layers=a.layers)
     wd = {"bfloat16": "bf16"}.get(a.weight_dtype, a.weight_dtype)
-    if isinstance(shape, FO.OPTShape):
+    from tpp_pytorch_extension_b200.llm import llm_common
+    if a.load_sharded_model:
+        model = llm_common.load_sharded_model()
+    elif isinstance(shape, FO.OPTShape):
         model = FO.build_random_opt(shape, wd, "cuda")
     else:
         model = FL.build_random_llama(shape, wd, "cuda", max_positions=a.input_tokens + a.max_new_tokens + 8,
                                       quantize_lm_head=a.quantize_lm_head and wd != "bf16")
+    if a.save_sharded_model:
+        llm_common.save_sharded_model(model)
     g = torch.Generator(device="cpu").manual_seed(1234)
     ids = torch.randint(0, shape.vocab_size, (a.batch_size, a.input_tokens), generator=g).cuda()
 

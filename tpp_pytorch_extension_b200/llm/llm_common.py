@@ -168,3 +168,101 @@ def fc_plain_parallel(input, weight, bias, parallel_dim, split_sizes):
     outs = [y.new_empty(y.shape) for _ in split_sizes]
     dist.all_gather(outs, y.contiguous(), group=fused_llm_cpp._pg)
     return torch.cat([o[..., :s] for o, s in zip(outs, split_sizes)], dim=-1)
+
+
+# --------------------------------------------------------------------------- packed checkpoints
+def _pack_value(v):
+    if isinstance(v, qtype.QTensor):
+        return {"__qtensor__": v.state()}
+    if isinstance(v, torch.Tensor):
+        return v.detach().cpu()
+    if isinstance(v, (list, tuple)):
+        return type(v)(_pack_value(x) for x in v)
+    return v
+
+
+def _layer_state(layer, shared_ep):
+    # the rotary table is one tensor shared by all layers and the runner: stored once, with the runner
+    return {"class": type(layer).__name__,
+            "attrs": {k: ("__runner_ep__" if (k == "EP" and shared_ep) else _pack_value(v)) for k, v in vars(layer).items()}}
+
+
+def _layer_from_state(st, device):
+    cls = getattr(fused_llm_cpp, st["class"])
+    layer = cls.__new__(cls)
+    pending = {}
+    for k, v in st["attrs"].items():
+        if isinstance(v, dict) and "__qtensor__" in v:
+            pending[k] = v["__qtensor__"]
+        elif isinstance(v, torch.Tensor):
+            setattr(layer, k, v.to(device))
+        else:
+            setattr(layer, k, v)
+    # a gate weight packed together with its up projection finds that layout by the up projection's identity
+    for k in sorted(pending, key=lambda n: pending[n]["pair_tc"] is not None):
+        pair = getattr(layer, "Wu", None) if pending[k]["pair_tc"] is not None else None
+        setattr(layer, k, qtype.QTensor.from_state(pending[k], device, pair))
+    return layer
+
+
+def runner_state(runner):
+    """Everything a runner holds (this rank's shard), with the weights in their quantized AND kernel layouts: loading it
+    needs no quantization and no repacking."""
+    import dataclasses
+    st = {"runner": type(runner).__name__, "shape": dataclasses.asdict(runner.shape), "shape_class": type(runner.shape).__name__,
+          "rank": get_rank(), "size": get_size(), "layers": [_layer_state(l, getattr(runner, "ep", None) is not None) for l in runner.layers], "extra": {}}
+    for k, v in vars(runner).items():
+        if k in ("layers", "shape", "last_graph") or k.startswith("_"):
+            continue
+        if isinstance(v, (torch.Tensor, qtype.QTensor, tuple, list, bool, int, float, type(None))):
+            st["extra"][k] = _pack_value(v)
+    return st
+
+
+def runner_from_state(st, device="cuda"):
+    from . import fused_llama_infer as FL
+    from . import fused_opt_infer as FO
+    if (st["rank"], st["size"]) != (get_rank(), get_size()):
+        raise ValueError(f"this checkpoint holds shard {st['rank']} of {st['size']}, the process is rank {get_rank()} of {get_size()}")
+    set_pg()
+    dev = torch.device(device)
+    shape_cls = {"LlamaShape": FL.LlamaShape, "OPTShape": FO.OPTShape}[st["shape_class"]]
+    cls = {"LlamaRunner": FL.LlamaRunner, "OPTRunner": FO.OPTRunner}[st["runner"]]
+    runner = cls.__new__(cls)
+    torch.nn.Module.__init__(runner)
+    runner.shape = shape_cls(**st["shape"])
+    runner.layers = [_layer_from_state(l, dev) for l in st["layers"]]
+
+    def unpack(v):
+        if isinstance(v, dict) and "__qtensor__" in v:
+            return qtype.QTensor.from_state(v["__qtensor__"], dev)
+        if isinstance(v, torch.Tensor):
+            return v.to(dev)
+        if isinstance(v, (list, tuple)):
+            return type(v)(unpack(x) for x in v)
+        return v
+
+    for k, v in st["extra"].items():
+        setattr(runner, k, unpack(v))
+    for layer in runner.layers:
+        if isinstance(getattr(layer, "EP", None), str):
+            layer.EP = runner.ep
+    return runner
+
+
+def sharded_model_file(root="./sharded_model"):
+    """The reference's per-rank file (examples/llm/run_generation.py:267-275)."""
+    import os
+    return os.path.join(root, f"r{get_rank()}_{get_size()}", "model.pt")
+
+
+def save_sharded_model(runner, root="./sharded_model"):
+    import os
+    path = sharded_model_file(root)
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    torch.save(runner_state(runner), path)
+    return path
+
+
+def load_sharded_model(root="./sharded_model", device="cuda"):
+    return runner_from_state(torch.load(sharded_model_file(root), weights_only=False), device)
