@@ -214,6 +214,45 @@ class LlamaRunner(torch.nn.Module):
         _lib.assert_no_kernel_error()  # a kernel that gave up on a bounded wait would have produced wrong tokens
         return out
 
+    @torch.no_grad()
+    def beam_search(self, input_ids, max_new_tokens, num_beams=4, attention_mask=None):
+        """Beam search for a fixed number of new tokens (the reference's default driver runs Hugging Face generate with
+        num_beams=4, examples/llm/run_generation.py:337-339; its own part is the cache reordering, which this uses).
+
+        Scores are sums of log-softmax over the bf16 logits in fp32; every step keeps the num_beams best continuations
+        per sequence and reorders the KV cache rows to follow their parents (TppCache.reorder_cache: after the prompt
+        the cache of B sequences is first repeated per beam). No end-of-sequence handling and no length penalty: all
+        hypotheses have the same length. Returns ([B, num_beams, prompt + max_new_tokens] token ids, best first,
+        [B, num_beams] scores)."""
+        B, P = input_ids.shape
+        dev = input_ids.device
+        nb = int(num_beams)
+        cache = TppCache()
+        mask = attention_mask if attention_mask is not None else torch.ones_like(input_ids)
+        prompt_pos = (mask.to(torch.int64).cumsum(-1) - 1).clamp_(min=0).contiguous() if attention_mask is not None else None
+        logits, cache = self.forward(input_ids, mask, prompt_pos, cache)
+        logp = torch.log_softmax(logits[:, -1].float(), dim=-1)             # [B, V]
+        V = logp.shape[-1]
+        scores, tok = logp.topk(nb, dim=-1)                                  # [B, nb]: the first step expands one beam
+        seqs = torch.cat([input_ids.unsqueeze(1).expand(B, nb, P), tok.unsqueeze(-1)], dim=-1)
+        # sequence b's beams are rows b*nb .. b*nb+nb-1 from here on; the first reorder meets a cache of B rows, repeats
+        # each row nb times (indices then address the expanded batch) and every beam continues its own copy
+        parent_rows = torch.arange(B * nb, device=dev)
+        mask = mask.repeat_interleave(nb, dim=0)
+        pos = mask.sum(-1, keepdim=True).to(torch.int64)
+        for _ in range(max_new_tokens - 1):
+            cache.reorder_cache(parent_rows)
+            mask = torch.cat([mask, torch.ones((B * nb, 1), dtype=mask.dtype, device=dev)], dim=1)
+            logits, cache = self.forward(tok.reshape(B * nb, 1), mask, pos, cache)
+            pos = pos + 1
+            logp = torch.log_softmax(logits[:, -1].float(), dim=-1).view(B, nb, V)
+            cand = (scores.unsqueeze(-1) + logp).view(B, nb * V)
+            scores, idx = cand.topk(nb, dim=-1)
+            parent, tok = idx // V, idx % V                                   # [B, nb]
+            seqs = torch.cat([seqs.gather(1, parent.unsqueeze(-1).expand(-1, -1, seqs.shape[-1])), tok.unsqueeze(-1)], dim=-1)
+            parent_rows = (parent + torch.arange(B, device=dev).unsqueeze(-1) * nb).reshape(-1)
+        return seqs, scores
+
     def synthetic_cache(self, batch, context, room, seed=1):
         """A cache that looks as if `context` tokens per sequence had been prefilled: random keys and values of the
         right shapes (what a decode step costs does not depend on their values). For benchmarks of the decode step on
