@@ -314,8 +314,10 @@ def build_random_llama(shape, weight_dtype="mxfp4", device="cuda", seed=0, std=0
     return LlamaRunner(shape, embed, layers, torch.ones(D, device=dev, dtype=torch.bfloat16), lm, ep)
 
 
-def OptimizeModelForLlama(model, dtype=torch.bfloat16, device="cuda", weight_dtype="mxfp4", quantize_lm_head=False):
-    """Reference entry point (fused_llama_infer.py:176-233) for a Hugging Face LlamaForCausalLM."""
+def OptimizeModelForLlama(model, dtype=torch.bfloat16, device="cuda", weight_dtype="mxfp4", quantize_lm_head=False, patch_model=False):
+    """Reference entry point (fused_llama_infer.py:176-233) for a Hugging Face LlamaForCausalLM. Returns the runner;
+    with patch_model=True the Hugging Face object is also patched in place, as the reference does, so that
+    model(...) and model.generate(...) run on the fused layers (llm_common.patch_hf_model)."""
     if dtype != torch.bfloat16:
         raise ValueError("the CUDA path computes in bfloat16")
     llm_common.set_pg()
@@ -338,12 +340,15 @@ def OptimizeModelForLlama(model, dtype=torch.bfloat16, device="cuda", weight_dty
         layers.append(make_layer(shape, w, i, ep, weight_dtype, dev))
     embed = model.model.embed_tokens.weight.data.to(dev, torch.bfloat16)
     lm = _lm_head(model.lm_head.weight.data.to(dev, torch.bfloat16), quantize_lm_head, weight_dtype)
-    return LlamaRunner(shape, embed, layers, model.model.norm.weight.data.to(dev, torch.bfloat16), lm, ep)
+    runner = LlamaRunner(shape, embed, layers, model.model.norm.weight.data.to(dev, torch.bfloat16), lm, ep)
+    if patch_model:
+        llm_common.patch_hf_model(model, runner)
+    return runner
 
 
-def OptimizeModelForQwen2(model, dtype=torch.bfloat16, device="cuda", weight_dtype="mxfp4", quantize_lm_head=False):
+def OptimizeModelForQwen2(model, dtype=torch.bfloat16, device="cuda", weight_dtype="mxfp4", quantize_lm_head=False, patch_model=False):
     """Reference entry point llm/fused_qwen2_infer.py:OptimizeModelForQwen2: the same runner, layers carry q/k/v biases."""
-    return OptimizeModelForLlama(model, dtype, device, weight_dtype, quantize_lm_head)
+    return OptimizeModelForLlama(model, dtype, device, weight_dtype, quantize_lm_head, patch_model)
 
 
 LLAMA2_7B = LlamaShape(32, 4096, 32, 32, 11008, 32000, rms_norm_eps=1e-5, rope_theta=1e4)

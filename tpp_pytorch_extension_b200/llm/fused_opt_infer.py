@@ -104,7 +104,7 @@ def build_random_opt(shape, weight_dtype="mxfp4", device="cuda", seed=0, std=0.0
     return OPTRunner(shape, embed, pos_embed, layers, final_ln, _lm_head(embed, False, weight_dtype))
 
 
-def OptimizeModelForOPT(model, dtype=torch.bfloat16, device="cuda", weight_dtype="mxfp4", quantize_lm_head=False):
+def OptimizeModelForOPT(model, dtype=torch.bfloat16, device="cuda", weight_dtype="mxfp4", quantize_lm_head=False, patch_model=False):
     """Reference entry point llm/fused_opt_infer.py:OptimizeModelForOPT for a Hugging Face OPTForCausalLM."""
     if dtype != torch.bfloat16:
         raise ValueError("the CUDA path computes in bfloat16")
@@ -133,4 +133,7 @@ def OptimizeModelForOPT(model, dtype=torch.bfloat16, device="cuda", weight_dtype
     final_ln = (bf(fl.weight), bf(fl.bias)) if fl is not None else None
     embed = bf(dec.embed_tokens.weight)
     lm = _lm_head(bf(model.lm_head.weight), quantize_lm_head, weight_dtype)
-    return OPTRunner(shape, embed, bf(dec.embed_positions.weight), layers, final_ln, lm)
+    runner = OPTRunner(shape, embed, bf(dec.embed_positions.weight), layers, final_ln, lm)
+    if patch_model:
+        llm_common.patch_hf_model(model, runner)
+    return runner

@@ -266,3 +266,46 @@ def save_sharded_model(runner, root="./sharded_model"):
 
 def load_sharded_model(root="./sharded_model", device="cuda"):
     return runner_from_state(torch.load(sharded_model_file(root), weights_only=False), device)
+
+
+# --------------------------------------------------------------------------- Hugging Face model patched in place
+def patch_hf_model(model, runner):
+    """Make a Hugging Face causal-LM object run on the fused layers, as the reference's OptimizeModelFor* leave it
+    (their patched LlamaModel.forward / LlamaForCausalLM.forward, llm/fused_llama_infer.py:236-408): `model(...)` and
+    `model.generate(...)` (greedy, sampling, beam search: the cache object answers get_seq_length, reorder_cache and
+    crop) then go through `runner`. The decoder layers of the Hugging Face object are dropped (their weights live, quantized,
+    in the runner) and what remains moves to the runner's device so that generate() creates its tensors there. An empty
+    cache that generate() supplies is replaced by a TppCache, a non-empty foreign cache is refused, as in the reference
+    (:262-270)."""
+    import types
+    from transformers.modeling_outputs import CausalLMOutputWithPast
+    dev = runner.embed.device
+    inner = getattr(model, "model", None)
+    holder = getattr(inner, "decoder", inner)  # OPT keeps its layers one level further down
+    if holder is not None and hasattr(holder, "layers"):
+        holder.layers = torch.nn.ModuleList()
+    model.to(device=dev, dtype=torch.bfloat16)
+
+    def forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None, use_cache=None,
+                logits_to_keep=0, **unused):
+        if input_ids is None:
+            raise ValueError("the fused path takes input_ids (inputs_embeds is not supported)")
+        cache = past_key_values
+        if not isinstance(cache, TppCache):
+            if cache is None or cache.get_seq_length() == 0:
+                cache = TppCache()
+            else:
+                raise ValueError("past_key_values must be of TppCache type")
+        keep_last = isinstance(logits_to_keep, int) and logits_to_keep == 1
+        old = runner.only_last_logit
+        runner.only_last_logit = keep_last
+        try:
+            logits, cache = runner.forward(input_ids.to(dev), None if attention_mask is None else attention_mask.to(dev),
+                                           None if position_ids is None else position_ids.to(dev), cache)
+        finally:
+            runner.only_last_logit = old
+        return CausalLMOutputWithPast(logits=logits, past_key_values=cache)
+
+    model.forward = types.MethodType(forward, model)
+    model.tpp_runner = runner
+    return model
