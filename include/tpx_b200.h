@@ -196,6 +196,11 @@ int tpx_linear_bf16_tc(const uint16_t* w, const uint16_t* x, int64_t M, int64_t 
 int tpx_tc_packed_bytes_qint8(int64_t N, int64_t K, int64_t block_size, size_t* wq_bytes, size_t* sw_bytes);
 int tpx_repack_qint8_tc(const int8_t* q, const float* scales, int64_t N, int64_t K, int64_t block_size, int8_t* wq,
                         float* swT, void* stream);
+/* The packed int8 weight of tpx_repack_qint8_tc as a plain bf16 matrix w[N][K] = bf16(q * s): what the host feeds
+ * tpx_linear_bf16_tc for more than 128 tokens, where the per-block drain of the int8 kernel costs more than its MMAs
+ * (weight-only arithmetic with bf16 activations: the reference's QINT8_EMU mode, src/csrc/qtypes.cpp:27, :928-930).     */
+int tpx_unpack_qint8_tc_bf16(const int8_t* wq, const float* swT, int64_t N, int64_t K, int64_t block_size, uint16_t* w_bf16,
+                             void* stream);
 size_t tpx_qlinear_qint8_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int64_t block_size);
 int tpx_qlinear_qint8_tc(const int8_t* wq, const float* swT, const uint16_t* x, const void* gamma, int gamma_is_f32,
                          float eps, int64_t M, int64_t N, int64_t K, int64_t block_size, int reuse_act, const uint16_t* bias, int act, const uint16_t* mul_in,

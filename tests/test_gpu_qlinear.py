@@ -142,28 +142,58 @@ def test_int8_tensor_core_kernel_matches_reference_arithmetic(cuda, M, block):
     from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
     if F.int8_path() != "tc":
         pytest.skip("runs with the tensor-core families")
-    rng = np.random.default_rng(300 + M + block)
-    N, K = 208, 1024
-    q, wd, (qq, ss, bs) = make_qweight(rng, N, K, "int8", cuda, block=block)
-    q2, wd2, _ = make_qweight(rng, N, K, "int8", cuda, block=block)
+    with knob_env(TPX_INT8_DENSE=0):
+        rng = np.random.default_rng(300 + M + block)
+        N, K = 208, 1024
+        q, wd, (qq, ss, bs) = make_qweight(rng, N, K, "int8", cuda, block=block)
+        q2, wd2, _ = make_qweight(rng, N, K, "int8", cuda, block=block)
+        x = O.randn_bf16(rng, (M, K))
+        y = run_fc(x, q, cuda)
+        assert O.rel_err(y, O.qlinear_int8_dynact(x, qq, ss, bs)) <= 1.5e-2  # same arithmetic up to the bf16 rounding of the running sum after every block
+        assert O.rel_err(y, O.qlinear(x, wd)) <= TOL
+        bias = O.randn_bf16(rng, (N,), 0.01)
+        res = O.randn_bf16(rng, (M, N))
+        y = run_fc(x, q, cuda, bias=to_dev_bf16(bias, cuda), act="silu", res=to_dev_bf16(res, cuda), res_scale=0.5)
+        assert O.rel_err(y, O.qlinear(x, wd, bias=bias, res=res, res_scale=0.5, act=O.ACT_SILU)) <= TOL
+        y2 = to_host_bits(F.fc_gate_up(to_dev_bf16(x, cuda), q, q2))
+        assert O.rel_err(y2, O.gate_up(x, wd, wd2)) <= TOL
+        # RMSNorm fused into the activation quantisation
+        gamma = O.f32_to_bf16(1 + 0.2 * rng.standard_normal(K).astype(np.float32))
+        xs = O.randn_bf16(rng, (M, K), 3.0)
+        xn = O.rmsnorm(xs, gamma, 1e-5)
+        y3 = to_host_bits(F.fc_plain_norm(to_dev_bf16(xs, cuda), to_dev_bf16(gamma, cuda), 1e-5, q))
+        assert O.rel_err(y3, O.qlinear_int8_dynact(xn, qq, ss, bs)) <= 1.5e-2
+        y4 = to_host_bits(F.fc_gate_up(to_dev_bf16(xs, cuda), q, q2, "silu", norm=(to_dev_bf16(gamma, cuda), 1e-5)))
+        assert O.rel_err(y4, O.gate_up(xn, wd, wd2)) <= TOL
+        assert_no_kernel_error()
+
+
+@pytest.mark.parametrize("dense", [0, 1])
+def test_int8_many_tokens_both_routes(cuda, dense):
+    """More than 128 tokens: the int8 tensor-core kernel over several token tiles (TPX_INT8_DENSE=0) and the default
+    route (weight unpacked to bf16 per call, bf16 tensor-core kernel, weight-only arithmetic), plain, with post-ops, as
+    a gate/up pair and behind an RMSNorm."""
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    if F.int8_path() != "tc":
+        pytest.skip("runs with the tensor-core families")
+    rng = np.random.default_rng(77)
+    M, N, K = 300, 208, 1024
+    q, wd, (qq, ss, bs) = make_qweight(rng, N, K, "int8", cuda, block=64)
+    q2, wd2, _ = make_qweight(rng, N, K, "int8", cuda, block=64)
     x = O.randn_bf16(rng, (M, K))
-    y = run_fc(x, q, cuda)
-    assert O.rel_err(y, O.qlinear_int8_dynact(x, qq, ss, bs)) <= 1.5e-2  # same arithmetic up to the bf16 rounding of the running sum after every block
-    assert O.rel_err(y, O.qlinear(x, wd)) <= TOL
-    bias = O.randn_bf16(rng, (N,), 0.01)
-    res = O.randn_bf16(rng, (M, N))
-    y = run_fc(x, q, cuda, bias=to_dev_bf16(bias, cuda), act="silu", res=to_dev_bf16(res, cuda), res_scale=0.5)
-    assert O.rel_err(y, O.qlinear(x, wd, bias=bias, res=res, res_scale=0.5, act=O.ACT_SILU)) <= TOL
-    y2 = to_host_bits(F.fc_gate_up(to_dev_bf16(x, cuda), q, q2))
-    assert O.rel_err(y2, O.gate_up(x, wd, wd2)) <= TOL
-    # RMSNorm fused into the activation quantisation
+    bias, res = O.randn_bf16(rng, (N,), 0.01), O.randn_bf16(rng, (M, N))
     gamma = O.f32_to_bf16(1 + 0.2 * rng.standard_normal(K).astype(np.float32))
-    xs = O.randn_bf16(rng, (M, K), 3.0)
-    xn = O.rmsnorm(xs, gamma, 1e-5)
-    y3 = to_host_bits(F.fc_plain_norm(to_dev_bf16(xs, cuda), to_dev_bf16(gamma, cuda), 1e-5, q))
-    assert O.rel_err(y3, O.qlinear_int8_dynact(xn, qq, ss, bs)) <= 1.5e-2
-    y4 = to_host_bits(F.fc_gate_up(to_dev_bf16(xs, cuda), q, q2, "silu", norm=(to_dev_bf16(gamma, cuda), 1e-5)))
-    assert O.rel_err(y4, O.gate_up(xn, wd, wd2)) <= TOL
+    with knob_env(TPX_INT8_DENSE=dense):
+        y = run_fc(x, q, cuda)
+        assert O.rel_err(y, O.qlinear(x, wd)) <= (TOL if dense == 0 else 1e-2)
+        if dense == 0:  # the reference's arithmetic (its bf16 running sum alone moves it about 1e-2 from the exact product)
+            assert O.rel_err(y, O.qlinear_int8_dynact(x, qq, ss, bs)) <= 1.5e-2
+        y = run_fc(x, q, cuda, bias=to_dev_bf16(bias, cuda), act="gelu", res=to_dev_bf16(res, cuda), res_scale=0.5)
+        assert O.rel_err(y, O.qlinear(x, wd, bias=bias, res=res, res_scale=0.5, act=O.ACT_GELU)) <= TOL
+        y2 = to_host_bits(F.fc_gate_up(to_dev_bf16(x, cuda), q, q2))
+        assert O.rel_err(y2, O.gate_up(x, wd, wd2)) <= TOL
+        y3 = to_host_bits(F.fc_plain_norm(to_dev_bf16(x, cuda), to_dev_bf16(gamma, cuda), 1e-5, q))
+        assert O.rel_err(y3, O.qlinear(O.rmsnorm(x, gamma, 1e-5), wd)) <= TOL
     assert_no_kernel_error()
 
 

@@ -32,12 +32,33 @@ def int8_path():
     return _opt("TPX_INT8_PATH", "tc")
 
 
+INT8_DENSE_MIN_TOKENS = 128  # above this the int8 weight is unpacked to bf16 per call (256 tokens: 68 against 160 us)
+
+
 def _int8_tc(x, y, w, w2, bias, act, mul_in, res, res_scale, norm=None):
-    """int8 weights through tpx_qlinear_qint8_tc (any number of tokens); a gate/up pair runs as two calls, the second
-    multiplying by the activated first."""
+    """int8 weights: up to 128 tokens through tpx_qlinear_qint8_tc (the reference's activation-quantised arithmetic); a
+    gate/up pair runs as two calls, the second multiplying by the activated first. More tokens: weight-only arithmetic
+    on the bf16 tensor-core kernel (TPX_INT8_DENSE=0 keeps the int8 kernel for every token count)."""
     L = _lib.lib()
     N, K = w.out_features, w.in_features
     M = x.numel() // K
+
+    if M > INT8_DENSE_MIN_TOKENS and _opt("TPX_INT8_DENSE", "1") != "0":
+        # many tokens: the weight unpacked to bf16 for this call, then the bf16 tensor-core kernel (weight-only
+        # arithmetic; see tpx_unpack_qint8_tc_bf16)
+        if norm is not None:
+            x = rms_norm(x, norm[0], norm[1])
+
+        def dense(wt):
+            wq, sw = wt.packed_i8tc()
+            buf = _lib.dense_scratch(N * K * 2, x.device)[: N * K * 2].view(torch.bfloat16).view(N, K)
+            _lib.check(L.tpx_unpack_qint8_tc_bf16(wq.data_ptr(), sw.data_ptr(), N, K, wt.block_size, buf.data_ptr(), _lib.stream()))
+            return buf
+
+        if w2 is None:
+            return _bf16_linear(x, dense(w), bias, act, mul_in, res, res_scale)
+        h = _bf16_linear(x, dense(w), bias, act, None, None, 1.0)
+        return _bf16_linear(x, dense(w2), None, None, h, None, 1.0)
 
     gam, eps = (norm[0], float(norm[1])) if norm is not None else (None, 0.0)
 

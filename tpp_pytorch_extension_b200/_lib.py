@@ -37,6 +37,7 @@ _SIGS = {
                                              c_f32, c_vp, c_vp, c_sz, c_vp]),
     "tpx_tc_packed_bytes_qint8": (c_int, [c_i64, c_i64, c_i64, c_vp, c_vp]),
     "tpx_repack_qint8_tc": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "tpx_unpack_qint8_tc_bf16": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp]),
     "tpx_qlinear_qint8_tc_scratch_bytes": (c_sz, [c_i64, c_i64, c_i64, c_i64]),
     "tpx_qlinear_qint8_tc": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_i64, c_i64, c_int, c_vp, c_int, c_vp, c_vp, c_f32,
                                      c_vp, c_vp, c_sz, c_vp]),
@@ -147,6 +148,19 @@ def scratch(nbytes, device):
     if buf is None or buf.numel() < nbytes:
         buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _scratch[key] = buf
+    return buf
+
+
+_dense = {}
+
+
+def dense_scratch(nbytes, device):
+    """Transient buffer for a weight unpacked to bf16 for one call (int8 weights with many tokens); no initial state."""
+    key = (device.index, stream())
+    buf = _dense.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _dense[key] = buf
     return buf
 
 

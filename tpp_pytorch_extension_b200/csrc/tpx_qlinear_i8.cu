@@ -642,3 +642,47 @@ extern "C" int tpx_qlinear_qint8_tc(const int8_t* wq, const float* swT, const ui
     default: return i8_launch<128>(mw, mx, p, pl.tiles, st);
   }
 }
+
+
+// ---------------------------------------------------------------- int8 weight -> bf16 matrix (many tokens)
+// With many tokens the per-K-block drain of the int8 kernel (one pass over the accumulator per 64 to 512 k) costs more
+// than the MMAs it serves (253 TOP/s at block 64), while the bf16 tensor-core kernel runs the same shapes at 1000-1170
+// TFLOP/s: for more than 128 tokens the host unpacks the weight to bf16 (w = q * s, rounded once) into a transient
+// buffer and runs tpx_linear_bf16_tc on it, i.e. weight-only arithmetic with bf16 activations (the reference's QINT8_EMU
+// mode, src/csrc/qtypes.cpp:27, :928-930). One thread per 16 consecutive k of one output row.
+namespace tpx {
+__global__ void unpack_qint8_bf16_kernel(const int8_t* __restrict__ wq, const float* __restrict__ swT, long long N, long long K, long long Kp,
+                                         long long Np, int block, uint16_t* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long per_row = K / 16;
+  if (idx >= N * per_row) return;
+  const long long n = idx / per_row, k = (idx % per_row) * 16;
+  const uint4 q = *reinterpret_cast<const uint4*>(wq + n * Kp + k);
+  const float s = swT[(k / block) * Np + n];  // block sizes are multiples of 16: one scale for the sixteen values
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const int a = (int)(int8_t)((w[j >> 1] >> (16 * (j & 1))) & 0xff), b = (int)(int8_t)((w[j >> 1] >> (16 * (j & 1) + 8)) & 0xff);
+    o[j] = (uint32_t)f32_to_bf16_bits((float)a * s) | ((uint32_t)f32_to_bf16_bits((float)b * s) << 16);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(out + n * K + k);
+  dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+  dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+}  // namespace tpx
+
+extern "C" int tpx_unpack_qint8_tc_bf16(const int8_t* wq, const float* swT, int64_t N, int64_t K, int64_t block_size, uint16_t* w_bf16,
+                                        void* stream) {
+  TPX_REQUIRE(wq && swT && w_bf16, TPX_ERR_ARG, "unpack_qint8_tc_bf16: null pointer");
+  TPX_REQUIRE(N > 0 && K > 0 && K % 16 == 0 && block_size >= 16 && block_size % 16 == 0 && K % block_size == 0, TPX_ERR_ARG,
+              "unpack_qint8_tc_bf16: bad shape (N=%ld K=%ld block=%ld)", (long)N, (long)K, (long)block_size);
+  TPX_REQUIRE((((uintptr_t)wq | (uintptr_t)w_bf16) & 15) == 0, TPX_ERR_ARG, "unpack_qint8_tc_bf16: misaligned pointer");
+  const long long Kp = (K + 127) / 128 * 128, Np = (N + 127) / 128 * 128;
+  const long long total = N * (K / 16);
+  TPX_CUDA_OK(tpx::launch_pdl(tpx::unpack_qint8_bf16_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, wq, swT,
+                              (long long)N, (long long)K, Kp, Np, (int)block_size, w_bf16));
+  return TPX_OK;
+}
