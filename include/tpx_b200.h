@@ -276,6 +276,42 @@ int tpx_attention_paged(const uint16_t* q, const uint64_t* k_pages, const uint64
  * No counterpart in the reference.                                                                              */
 int tpx_attention_tc_status(void* stream, unsigned* status_host);
 
+/* ---------------------------------------------------------------- a decoder layer in two calls
+ * LlamaDecoderLayer::_forward / Qwen2DecoderLayer::_forward (src/csrc/llm/fused_llm_infer.cpp:1195-1286, :1440-1510) on
+ * MXFP4 weights, as two sequences of the entry points above issued from C: tpx_llama_layer_attention = RMSNorm + fused
+ * q/k/v (+ bias), rotary embedding + cache append, attention, o_proj + residual -> io->so; tpx_llama_layer_mlp = RMSNorm +
+ * gate/up with SiLU * up, down_proj + residual -> io->out. The reference all-reduces after each half under tensor
+ * parallelism (:1263-1277): the caller does so between and after the calls. TpxLlamaLayer holds what is fixed per layer
+ * (packed weights from tpx_repack_mxfp4_tc, the gate/up pair packed together), TpxLlamaLayerIO what changes per call;
+ * every buffer is the caller's: qkv [T][(Nq+2Nkv)H], q [B][Nkv][S][Nq/Nkv][H], ctx [T][Nq*H], so/out [T][D],
+ * inter [T][FF] with T = B*S; scratch sized for the largest of the four linears (tpx_qlinear_mxfp4_tc_scratch_bytes),
+ * attn_scratch by tpx_attention_scratch_bytes; the cache as kc/vc or, when k_pages != NULL, as page tables.       */
+typedef struct {
+  int64_t D, Nq, Nkv, H, FF, MP, HR;
+  float eps, res_scale;
+  int gamma_is_f32;
+  const void *gamma1, *gamma2;
+  const uint16_t* bias_qkv; /* NULL: none */
+  const float* ep;          /* [2][MP][HR] */
+  const uint8_t *wqkv, *sfa_qkv, *wo, *sfa_o, *wgu, *sfa_gu, *wd, *sfa_d;
+} TpxLlamaLayer;
+typedef struct {
+  int64_t B, S, Bpos, Spad, offset, capacity;
+  const uint16_t* x;
+  const int64_t* pos;
+  const uint16_t* mask;     /* additive [B][Spad] or NULL */
+  const int32_t* dev_len;   /* NULL, or the cached length on the device (CUDA-graph decoding) */
+  uint16_t *kc, *vc;
+  const uint64_t *k_pages, *v_pages;
+  uint16_t *qkv, *q, *ctx, *so, *inter, *out;
+  void* scratch;
+  size_t scratch_bytes;
+  void* attn_scratch;
+  size_t attn_scratch_bytes;
+} TpxLlamaLayerIO;
+int tpx_llama_layer_attention(const TpxLlamaLayer* layer, const TpxLlamaLayerIO* io, void* stream);
+int tpx_llama_layer_mlp(const TpxLlamaLayer* layer, const TpxLlamaLayerIO* io, void* stream);
+
 /* ---------------------------------------------------------------- tensor-parallel all-reduce over peer memory
  * Replaces tpp_llm.allreduce (src/csrc/llm/fused_llm_infer.cpp:101-119) for the small bf16 tensors a decoder layer
  * reduces after its row-parallel linears (:1263-1277); the reference's own latency-oriented path is its shared-memory

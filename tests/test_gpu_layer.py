@@ -213,6 +213,46 @@ def test_llama_layer_prefill_then_decode(cuda, kind):
         assert O.rel_err(got[:n], kc_ref[:n]) <= TOL
 
 
+def test_layer_as_two_c_calls_equals_the_kernel_by_kernel_path(cuda):
+    """LlamaDecoderLayer.forward issues the layer as two C calls (tpx_llama_layer_attention / tpx_llama_layer_mlp) where it
+    can; with TPX_LAYER_C=0 it launches kernel by kernel from Python. Same kernels, same order: bit-identical outputs and
+    caches, through a prompt, decode steps and a cache that grows by pages."""
+    from tests.gpu_util import knob_env
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    from tpp_pytorch_extension_b200._C._tpp_attn import TppCache
+    rng = np.random.default_rng(25)
+    D, Nq, Nkv, H, FF, B, MP = 256, 4, 2, 64, 512, 2, 512
+    names = {"q": (Nq * H, D), "k": (Nkv * H, D), "v": (Nkv * H, D), "o": (D, Nq * H), "gate": (FF, D), "up": (FF, D), "down": (D, FF)}
+    qt = {nm: make_qweight(rng, n, k, "mxfp4", cuda, std=0.05)[0] for nm, (n, k) in names.items()}
+    g1 = to_dev_bf16(O.f32_to_bf16(1 + 0.1 * rng.standard_normal(D).astype(np.float32)), cuda)
+    g2 = to_dev_bf16(O.f32_to_bf16(1 + 0.1 * rng.standard_normal(D).astype(np.float32)), cuda)
+    bias = [to_dev_bf16(O.randn_bf16(rng, (n,), 0.1), cuda) for n in (Nq * H, Nkv * H, Nkv * H)]
+    ep = torch.from_numpy(O.rope_table(MP, H, 1e4)).to(cuda)
+    layer = F.Qwen2DecoderLayer([g1, qt["q"], qt["k"], qt["v"], qt["o"], g2, qt["gate"], qt["up"], qt["down"]] + bias + [ep], 0, 1e-5, H, MP, H)
+    assert layer._c_level_ok()
+    steps = [(70, None)] + [(1, None)] * 3 + [(200, None), (1, None)]  # the 200-token chunk makes the cache grow: paged from then on
+    inputs, total = [], 0
+    for S, _ in steps:
+        hs = to_dev_bf16(O.randn_bf16(rng, (B, S, D)), cuda)
+        pos = torch.arange(total, total + S, device=cuda).unsqueeze(0)
+        total += S
+        inputs.append((hs, pos, total))
+    outs = {}
+    for mode in (1, 0):
+        with knob_env(TPX_LAYER_C=mode):
+            cache = TppCache()
+            got = []
+            for hs, pos, tot in inputs:
+                am = cache.align_and_invert_mask(torch.ones((B, tot), device=cuda))
+                got.append(layer.forward([hs, am, pos], cache, True)[0].clone())
+            outs[mode] = (got, cache.layers[0].k.clone(), cache.layers[0].v.clone(), cache.layers[0].contiguous())
+    assert not outs[1][3]  # the cache did become paged
+    for a, b in zip(outs[1][0], outs[0][0]):
+        assert torch.equal(a, b)
+    assert torch.equal(outs[1][1], outs[0][1]) and torch.equal(outs[1][2], outs[0][2])
+    assert_no_kernel_error()
+
+
 def test_qwen2_layer_has_qkv_bias(cuda):
     """Qwen2DecoderLayer = the Llama block plus q/k/v biases (src/csrc/llm/fused_llm_infer.cpp:1289-1510)."""
     from tpp_pytorch_extension_b200._C import _fused_llm_infer as F

@@ -1,5 +1,7 @@
 """Mirror of the reference's `_C._fused_llm_infer` submodule / `torch.ops.tpp_llm`
 (src/csrc/llm/fused_llm_infer.cpp:1568-1611) for the quantized-linear part of the path."""
+import ctypes
+
 import torch
 
 from .. import _lib
@@ -364,6 +366,8 @@ class LlamaDecoderLayer:
         from ._tpp_attn import attention
         hs, am, pos = inp[0], inp[1], inp[2]
         _lib.require_cuda(hs, "hidden_states")
+        if self._c_level_ok():
+            return self._forward_c(hs, am, pos, cache, use_cache, dev_len)
         B, S, D = hs.shape
         ws = get_pg_size()
         scale = 1.0 / ws
@@ -421,6 +425,98 @@ class LlamaDecoderLayer:
                 allreduce(out)
         out = out.view(B, S, D)
         if use_cache:  # the cache tensors while they are one arena, else the list of arenas (TppCache.get gathers them)
+            if paged:
+                return [out, [a[0] for a in lc.arenas], [a[1] for a in lc.arenas]]
+            return [out, kc, vc]
+        return [out]
+
+
+    # ----- the same forward as two C calls (tpx_llama_layer_attention / tpx_llama_layer_mlp): one foreign call per half
+    # of the layer instead of one per kernel
+    def _c_level_ok(self):
+        if self.bf16 or _timers.enabled() or _opt("TPX_LAYER_C", "1") == "0" or mxfp4_path() != "tc" or _opt("TPX_FUSED_NORM", "1") == "0":
+            return False
+        return all(w.kind == 1 for w in (self.Wqkv, self.Wp, self.Wg, self.Wu, self.Wd)) and self.Wqkv.in_features <= 8192
+
+    def _c_struct(self):
+        st = getattr(self, "_cstruct", None)
+        if st is None:
+            L = _lib.LlamaLayerStruct()
+            L.D, L.Nq, L.Nkv, L.H = self.Wqkv.in_features, self.Nq, self.Nkv, self.H
+            L.FF, L.MP, L.HR = self.Wg.out_features, self.EP.shape[1], self.EP.shape[2]
+            L.eps, L.gamma_is_f32 = self.eps, int(self.Gi.dtype == torch.float32)
+            if self.Gi.dtype != self.Gpa.dtype:
+                raise _lib.TpxError("LlamaDecoderLayer: the two norm weights must share a dtype")
+            keep = [self.Wqkv.packed_tc(), self.Wp.packed_tc(), self.Wg.packed_tc(self.Wu), self.Wd.packed_tc()]
+            (L.wqkv, L.sfa_qkv), (L.wo, L.sfa_o), (L.wgu, L.sfa_gu), (L.wd, L.sfa_d) = [(a.data_ptr(), b.data_ptr()) for a, b in keep]
+            L.gamma1, L.gamma2, L.ep = self.Gi.data_ptr(), self.Gpa.data_ptr(), self.EP.data_ptr()
+            L.bias_qkv = self.Bqkv.data_ptr() if self.Bqkv is not None else None
+            st = self._cstruct = (L, keep)
+        st[0].res_scale = 1.0 / get_pg_size()
+        return st[0]
+
+    def _forward_c(self, hs, am, pos, cache, use_cache, dev_len):
+        B, S, D = hs.shape
+        T = B * S
+        L = self._c_struct()
+        lib = _lib.lib()
+        dev = hs.device
+        if not hs.is_contiguous():
+            hs = hs.contiguous()
+        lc = cache.layer(self.layer_idx)
+        if dev_len is None:
+            lc.ensure(B, self.Nkv, self.H, S, hs.dtype, dev)
+        if pos.dtype != torch.int64 or not pos.is_contiguous():
+            pos = pos.to(torch.int64).contiguous()
+        H, Nq, Nkv, FF = self.H, self.Nq, self.Nkv, L.FF
+        nqkv = (Nq + 2 * Nkv) * H
+        # temporaries of one layer live in one cached workspace (layers run one after the other on the stream)
+        sizes = [T * nqkv, T * Nq * H, T * Nq * H, T * D, T * FF]
+        ws = _lib.layer_workspace(sum(sizes) * 2 + 5 * 256, dev)
+        views, o = [], 0
+        for n in sizes:
+            views.append(ws[o:o + n * 2])
+            o += (n * 2 + 255) // 256 * 256
+        key = ("layer_c", T, D, nqkv, FF, Nq * H)
+        nb = _SCRATCH_BYTES.get(key)
+        if nb is None:
+            f = lib.tpx_qlinear_mxfp4_tc_scratch_bytes
+            nb = _SCRATCH_BYTES[key] = max(f(T, nqkv, D, 0), f(T, D, Nq * H, 0), f(T, FF, D, 1), f(T, D, FF, 0))
+        sc = _lib.scratch(nb, dev)
+        key_len = lc.capacity() if dev_len is not None else lc.offset + S
+        na = lib.tpx_attention_scratch_bytes(B, Nkv, S, Nq // Nkv, H, key_len)
+        asc = _lib.aux_scratch(na, dev) if na else None
+        out = torch.empty((B, S, D), dtype=hs.dtype, device=dev)
+        io = _lib.LlamaLayerIOStruct()
+        io.B, io.S, io.Bpos, io.Spad = B, S, pos.shape[0], (am.shape[1] if am is not None else 0)
+        io.offset, io.capacity = lc.offset, lc.capacity()
+        io.x, io.pos, io.mask, io.dev_len = hs.data_ptr(), pos.data_ptr(), _lib.ptr(am), _lib.ptr(dev_len)
+        paged = not lc.contiguous()
+        if paged:
+            io.k_pages, io.v_pages = lc.k_ptrs.data_ptr(), lc.v_ptrs.data_ptr()
+            kc = vc = None
+        else:
+            kc, vc = lc.arenas[0]
+            io.kc, io.vc = kc.data_ptr(), vc.data_ptr()
+        io.qkv, io.q, io.ctx, io.so, io.inter = [v.data_ptr() for v in views]
+        io.out = out.data_ptr()
+        io.scratch, io.scratch_bytes = sc.data_ptr(), sc.numel()
+        io.attn_scratch, io.attn_scratch_bytes = _lib.ptr(asc), (asc.numel() if asc is not None else 0)
+        st = _lib.stream()
+        world = get_pg_size()
+        rc = lib.tpx_llama_layer_attention(ctypes.byref(L), ctypes.byref(io), st)
+        if rc:
+            _lib.check(rc)
+        if dev_len is None:
+            lc.offset += S
+        if world > 1:
+            allreduce(views[3].view(torch.bfloat16).view(T, D))
+        rc = lib.tpx_llama_layer_mlp(ctypes.byref(L), ctypes.byref(io), st)
+        if rc:
+            _lib.check(rc)
+        if world > 1:
+            allreduce(out)
+        if use_cache:
             if paged:
                 return [out, [a[0] for a in lc.arenas], [a[1] for a in lc.arenas]]
             return [out, kc, vc]

@@ -52,6 +52,8 @@ _SIGS = {
     "tpx_qlinear_mxfp4_tc_static": (c_int, [c_vp, c_vp, c_int, c_vp, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp, c_f32, c_vp, c_vp]),
     "tpx_rmsnorm": (c_int, [c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_vp, c_vp]),
     "tpx_layernorm": (c_int, [c_vp, c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_vp, c_vp]),
+    "tpx_llama_layer_attention": (c_int, [c_vp, c_vp, c_vp]),
+    "tpx_llama_layer_mlp": (c_int, [c_vp, c_vp, c_vp]),
     "tpx_argmax_bf16": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp]),
     "tpx_rope_kv_update": (c_int, [c_vp, c_vp, c_vp] + [c_i64] * 10 + [c_vp, c_vp, c_vp, c_vp, c_vp]),
     "tpx_rope_kv_update_paged": (c_int, [c_vp, c_vp, c_vp] + [c_i64] * 10 + [c_vp, c_vp, c_vp, c_vp, c_vp]),
@@ -83,6 +85,22 @@ def lib():
                 fn.restype, fn.argtypes = res, args
         _lib = L
     return _lib
+
+
+class LlamaLayerStruct(ctypes.Structure):
+    """TpxLlamaLayer of include/tpx_b200.h."""
+    _fields_ = [(n, ctypes.c_int64) for n in ("D", "Nq", "Nkv", "H", "FF", "MP", "HR")] + \
+               [("eps", ctypes.c_float), ("res_scale", ctypes.c_float), ("gamma_is_f32", ctypes.c_int)] + \
+               [(n, ctypes.c_void_p) for n in ("gamma1", "gamma2", "bias_qkv", "ep", "wqkv", "sfa_qkv", "wo", "sfa_o", "wgu", "sfa_gu",
+                                                 "wd", "sfa_d")]
+
+
+class LlamaLayerIOStruct(ctypes.Structure):
+    """TpxLlamaLayerIO of include/tpx_b200.h."""
+    _fields_ = [(n, ctypes.c_int64) for n in ("B", "S", "Bpos", "Spad", "offset", "capacity")] + \
+               [(n, ctypes.c_void_p) for n in ("x", "pos", "mask", "dev_len", "kc", "vc", "k_pages", "v_pages", "qkv", "q", "ctx", "so",
+                                                 "inter", "out", "scratch")] + \
+               [("scratch_bytes", ctypes.c_size_t), ("attn_scratch", ctypes.c_void_p), ("attn_scratch_bytes", ctypes.c_size_t)]
 
 
 def check(rc):
@@ -161,6 +179,19 @@ def dense_scratch(nbytes, device):
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
         _dense[key] = buf
+    return buf
+
+
+_layer_ws = {}
+
+
+def layer_workspace(nbytes, device):
+    """Temporaries of one decoder layer (q/k/v, rotated q, attention output, the two MLP inputs): reused by every layer."""
+    key = (device.index, stream())
+    buf = _layer_ws.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _layer_ws[key] = buf
     return buf
 
 

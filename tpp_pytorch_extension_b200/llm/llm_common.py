@@ -184,7 +184,8 @@ def _pack_value(v):
 def _layer_state(layer, shared_ep):
     # the rotary table is one tensor shared by all layers and the runner: stored once, with the runner
     return {"class": type(layer).__name__,
-            "attrs": {k: ("__runner_ep__" if (k == "EP" and shared_ep) else _pack_value(v)) for k, v in vars(layer).items()}}
+            "attrs": {k: ("__runner_ep__" if (k == "EP" and shared_ep) else _pack_value(v)) for k, v in vars(layer).items()
+                      if k != "_cstruct"}}  # the C-level call's argument block holds device addresses: rebuilt on first use
 
 
 def _layer_from_state(st, device):
