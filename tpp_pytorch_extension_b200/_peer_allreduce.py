@@ -14,9 +14,10 @@ from . import _lib
 
 MAX_ELEMS = 1 << 20            # what the exchange buffer holds per call: 2 MiB of bf16
 _BUF_ELEMS = 2 * MAX_ELEMS     # two halves, alternating by call
-# Largest tensor sent through the peer kernel by default. The kernel is a latency play: between two GPUs it was measured
-# level with NCCL at 1 MiB per call (161 calls of a Llama-2-70B decode step at batch 64: 26.9 against 25.0 ms per step),
-# so tensors above this size stay with the library collective. TPX_ALLREDUCE_MAX_BYTES overrides.
+# Largest tensor sent through the peer kernel by default. Issued back to back between two GPUs the kernel beats NCCL at
+# every size (8 KiB: 11 against 21 us, 1 MiB: 21 against 28 us), but inside a Llama-2-70B decode step at batch 64 (161 calls
+# of 1 MiB between dependent kernels) the step was slower with it (25.6 against 24.9 ms; fewer CTAs made it worse), so
+# tensors above this size stay with the library collective. TPX_ALLREDUCE_MAX_BYTES overrides.
 AUTO_MAX_BYTES = int(os.environ.get("TPX_ALLREDUCE_MAX_BYTES", str(256 * 1024)))
 
 
