@@ -713,7 +713,7 @@ struct MapKey {
   const void* base;
   uint64_t rows, row_bytes;
   uint32_t box_rows;
-  int dt, kind;  // kind 0: 128-element rows, 128-byte swizzle; 1: 64-byte rows, 64-byte swizzle
+  int dt, kind;  // kind 0: 128-element rows, 128-byte swizzle; 1: 64-byte rows, 64-byte swizzle; 2: 512-byte rows, no swizzle
   bool operator==(const MapKey& o) const {
     return base == o.base && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows && dt == o.dt && kind == o.kind;
   }
@@ -770,6 +770,28 @@ int tc_make_map64(CUtensorMap* m, const void* base, uint64_t rows, uint32_t box_
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TPX_REQUIRE(r == CUDA_SUCCESS, TPX_ERR_CUDA, "cuTensorMapEncodeTiled (64-byte rows) failed with %d (rows=%llu box_rows=%u)", (int)r,
+              (unsigned long long)rows, box_rows);
+  slot->key = key; slot->map = *m; slot->used = true;
+  return TPX_OK;
+}
+
+// 2-D tensor of 512-byte scale blocks (128 32-bit words per row), no swizzle: rows land back to back in shared memory.
+int tc_make_map_sf(CUtensorMap* m, const void* base, uint64_t rows, uint32_t box_rows) {
+  const MapKey key = {base, rows, 512, box_rows, (int)CU_TENSOR_MAP_DATA_TYPE_UINT32, 2};
+  MapSlot* slot = map_slot(key);
+  if (slot->used && slot->key == key) {
+    *m = slot->map;
+    return TPX_OK;
+  }
+  EncodeTiledFn fn = encode_fn();
+  TPX_REQUIRE(fn, TPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[2] = {128, rows};
+  cuuint64_t gstr[1] = {512};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TPX_REQUIRE(r == CUDA_SUCCESS, TPX_ERR_CUDA, "cuTensorMapEncodeTiled (scale blocks) failed with %d (rows=%llu box_rows=%u)", (int)r,
               (unsigned long long)rows, box_rows);
   slot->key = key; slot->map = *m; slot->used = true;
   return TPX_OK;

@@ -44,61 +44,6 @@ struct TcpCfg {
   static_assert(NBUF * D_COLS + STAGES * SF_COLS <= 512, "tensor memory");
 };
 
-// 16 consecutive tokens of output feature n: bias, activation, gate multiply, residual, bf16 stores. The residual and
-// gate-input values arrive packed two tokens per register (loaded earlier).
-template <bool DUAL>
-__device__ __forceinline__ void tcp_finish16(const TcParams& p, int tok0, int n, float (&x)[16], const float (&u)[16],
-                                             const uint32_t (&resp)[8], const uint32_t (&mulp)[8]) {
-  const int live = p.M - tok0;
-  const size_t o0 = (size_t)tok0 * p.N + n;
-  if (p.bias) {
-    const float b = bf16_bits_to_f32(p.bias[n]);
-#pragma unroll
-    for (int j = 0; j < 16; j++) x[j] += b;
-  }
-  switch (p.act) {
-    case TPX_ACT_GELU:
-#pragma unroll
-      for (int j = 0; j < 16; j++) x[j] = 0.5f * x[j] * (1.0f + erff(x[j] * 0.70710678118654752f));
-      break;
-    case TPX_ACT_SILU:
-#pragma unroll
-      for (int j = 0; j < 16; j++) x[j] = __fdividef(x[j], 1.0f + __expf(-x[j]));
-      break;
-    case TPX_ACT_RELU:
-#pragma unroll
-      for (int j = 0; j < 16; j++) x[j] = fmaxf(x[j], 0.0f);
-      break;
-    default: break;
-  }
-  if (DUAL) {
-#pragma unroll
-    for (int j = 0; j < 16; j++) x[j] *= u[j];
-  }
-  if (p.mul_in) {
-#pragma unroll
-    for (int j = 0; j < 16; j++) x[j] *= bf16_bits_to_f32((uint16_t)(mulp[j >> 1] >> (16 * (j & 1))));
-  }
-  if (p.res) {
-#pragma unroll
-    for (int j = 0; j < 16; j++) x[j] += bf16_bits_to_f32((uint16_t)(resp[j >> 1] >> (16 * (j & 1)))) * p.res_scale;
-  }
-#pragma unroll
-  for (int j = 0; j < 16; j++)
-    if (j < live) p.y[o0 + (size_t)j * p.N] = f32_to_bf16_bits(x[j]);
-}
-
-// 16 tokens of one feature from a strided bf16 matrix [M][N], packed two per register; zero beyond M.
-__device__ __forceinline__ void tcp_preload16(const uint16_t* __restrict__ src, int M, int N, int tok0, int n, uint32_t (&pk)[8]) {
-  const int live = M - tok0;
-  const uint16_t* s = src + (size_t)tok0 * N + n;
-  uint16_t t[16];
-#pragma unroll
-  for (int j = 0; j < 16; j++) t[j] = j < live ? __ldg(s + (size_t)j * N) : (uint16_t)0;
-#pragma unroll
-  for (int j = 0; j < 8; j++) pk[j] = (uint32_t)t[2 * j] | ((uint32_t)t[2 * j + 1] << 16);
-}
-
 // UKS k steps of 128 per pipeline stage; DUAL: gate/up pair (weights interleaved per k step: gate tile, up tile).
 // p.KS counts stages per accumulation; p.TN x p.TM tiles of 128 features x 128 tokens, cut evenly between the CTAs.
 template <int UKS, bool DUAL>
@@ -281,8 +226,8 @@ qlinear_tcp_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       if (live) {  // in flight while the tile's MMAs run
 #pragma unroll
         for (int c = 0; c < 2; c++) {
-          if (p.res) tcp_preload16(p.res, p.M, p.N, tokb + c * 16, n, resp[c]);
-          if (p.mul_in) tcp_preload16(p.mul_in, p.M, p.N, tokb + c * 16, n, mulp[c]);
+          if (p.res) tc_preload16(p.res, p.M, p.N, tokb + c * 16, n, resp[c]);
+          if (p.mul_in) tc_preload16(p.mul_in, p.M, p.N, tokb + c * 16, n, mulp[c]);
         }
       }
       const int a0 = ti * NWT;
@@ -308,7 +253,7 @@ qlinear_tcp_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           x[j] = __uint_as_float(g[j]);
           uf[j] = DUAL ? __uint_as_float(u[j]) : 0.0f;
         }
-        if (live && tm * 128 + c0 < p.M) tcp_finish16<DUAL>(p, tm * 128 + c0, n, x, uf, resp[c], mulp[c]);
+        if (live && tm * 128 + c0 < p.M) tc_finish16_pre<DUAL>(p, tm * 128 + c0, n, x, uf, resp[c], mulp[c], nullptr);
       }
       tc_fence_before();
       __syncwarp();

@@ -88,70 +88,6 @@ __device__ __forceinline__ bool t2_wait_cluster(uint32_t bar, uint32_t parity) {
   return false;
 }
 
-// 16 consecutive tokens of output feature n from the accumulator values x (gate/up pair: u holds the up values):
-// bias, activation, gate multiply, residual, bf16 stores; residual / gate inputs arrive packed two per register.
-template <bool DUAL>
-__device__ __forceinline__ void t2_finish16(const TcParams& p, int tok0, int n, float (&x)[16], float (&u)[16],
-                                            const uint32_t (&resp)[8], const uint32_t (&mulp)[8], const float* __restrict__ tok_scale) {
-  const int live = p.M - tok0;
-  const size_t o0 = (size_t)tok0 * p.N + n;
-  if (tok_scale) {  // the activations were split as x / 2^e per token: give the 2^e back (the array is padded to whole tiles)
-    const float4* sp = reinterpret_cast<const float4*>(tok_scale + tok0);
-    const float4 s0 = __ldg(sp), s1 = __ldg(sp + 1), s2 = __ldg(sp + 2), s3 = __ldg(sp + 3);
-    const float sc[16] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w, s2.x, s2.y, s2.z, s2.w, s3.x, s3.y, s3.z, s3.w};
-#pragma unroll
-    for (int j = 0; j < 16; j++) {
-      x[j] *= sc[j];
-      if (DUAL) u[j] *= sc[j];
-    }
-  }
-  if (p.bias) {
-    const float b = bf16_bits_to_f32(p.bias[n]);
-#pragma unroll
-    for (int j = 0; j < 16; j++) x[j] += b;
-  }
-  switch (p.act) {
-    case TPX_ACT_GELU:
-#pragma unroll
-      for (int j = 0; j < 16; j++) x[j] = 0.5f * x[j] * (1.0f + erff(x[j] * 0.70710678118654752f));
-      break;
-    case TPX_ACT_SILU:
-#pragma unroll
-      for (int j = 0; j < 16; j++) x[j] = __fdividef(x[j], 1.0f + __expf(-x[j]));
-      break;
-    case TPX_ACT_RELU:
-#pragma unroll
-      for (int j = 0; j < 16; j++) x[j] = fmaxf(x[j], 0.0f);
-      break;
-    default: break;
-  }
-  if (DUAL) {
-#pragma unroll
-    for (int j = 0; j < 16; j++) x[j] *= u[j];
-  }
-  if (p.mul_in) {
-#pragma unroll
-    for (int j = 0; j < 16; j++) x[j] *= bf16_bits_to_f32((uint16_t)(mulp[j >> 1] >> (16 * (j & 1))));
-  }
-  if (p.res) {
-#pragma unroll
-    for (int j = 0; j < 16; j++) x[j] += bf16_bits_to_f32((uint16_t)(resp[j >> 1] >> (16 * (j & 1)))) * p.res_scale;
-  }
-#pragma unroll
-  for (int j = 0; j < 16; j++)
-    if (j < live) p.y[o0 + (size_t)j * p.N] = f32_to_bf16_bits(x[j]);
-}
-
-__device__ __forceinline__ void t2_preload16(const uint16_t* __restrict__ src, int M, int N, int tok0, int n, uint32_t (&pk)[8]) {
-  const int live = M - tok0;
-  const uint16_t* s = src + (size_t)tok0 * N + n;
-  uint16_t t[16];
-#pragma unroll
-  for (int j = 0; j < 16; j++) t[j] = j < live ? __ldg(s + (size_t)j * N) : (uint16_t)0;
-#pragma unroll
-  for (int j = 0; j < 8; j++) pk[j] = (uint32_t)t[2 * j] | ((uint32_t)t[2 * j + 1] << 16);
-}
-
 // Activation split with ONE power-of-two scale per token instead of one per 32 values: x / 2^e as a hi and a lo E4M3
 // term, 2^e in `tok_scale` for the epilogue. The activation scale factors of the block-scaled MMA are then the constant
 // 1.0, written to tensor memory once per kernel instead of copied per k step (two of the three scale-factor copies of a
@@ -492,8 +428,8 @@ qlinear_tcp2_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       if (live) {  // in flight while the tile's MMAs run
 #pragma unroll
         for (int c = 0; c < 2; c++) {
-          if (p.res) t2_preload16(p.res, p.M, p.N, tokb + c * 16, n, resp[c]);
-          if (p.mul_in) t2_preload16(p.mul_in, p.M, p.N, tokb + c * 16, n, mulp[c]);
+          if (p.res) tc_preload16(p.res, p.M, p.N, tokb + c * 16, n, resp[c]);
+          if (p.mul_in) tc_preload16(p.mul_in, p.M, p.N, tokb + c * 16, n, mulp[c]);
         }
       }
       float g[32], u[32];
@@ -524,7 +460,7 @@ qlinear_tcp2_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           x[j] = g[c * 16 + j];
           uf[j] = DUAL ? u[c * 16 + j] : 0.0f;
         }
-        if (live && tokb + c * 16 < p.M) t2_finish16<DUAL>(p, tokb + c * 16, n, x, uf, resp[c], mulp[c], ROWS ? p.partial : nullptr);
+        if (live && tokb + c * 16 < p.M) tc_finish16_pre<DUAL>(p, tokb + c * 16, n, x, uf, resp[c], mulp[c], ROWS ? p.partial : nullptr);
       }
     }
   }
@@ -539,30 +475,6 @@ qlinear_tcp2_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 }
 
 // ---------------------------------------------------------------- host side
-// 2-D tensor of 512-byte scale blocks (128 32-bit words per row), no swizzle: rows land back to back in shared memory.
-static int tcp2_make_sf_map(CUtensorMap* m, const void* base, uint64_t rows, uint32_t box_rows) {
-  typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qr;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  }
-  TPX_REQUIRE(fn, TPX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t gdim[2] = {128, rows};
-  cuuint64_t gstr[1] = {512};
-  cuuint32_t box[2] = {128, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  TPX_REQUIRE(r == CUDA_SUCCESS, TPX_ERR_CUDA, "cuTensorMapEncodeTiled (scale blocks) failed with %d (rows=%llu box_rows=%u)", (int)r,
-              (unsigned long long)rows, box_rows);
-  return TPX_OK;
-}
-
 struct Tcp2Plan {
   int TN, TM, KS, Mpad, uks, rows;  // rows: one activation scale per token (rows of up to 16384 elements)
   size_t off_terms, off_sfb, off_tscale, total;
@@ -676,9 +588,9 @@ int tcp2_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x
   if (rc) return rc;
   rc = tc_make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, terms, (uint64_t)pl.Mpad * pl.KS * 2, 128, 128);
   if (rc) return rc;
-  rc = tcp2_make_sf_map(&msfa, sfa, (uint64_t)pl.TN * pl.KS * nwt, pair ? 1u : (uint32_t)pl.uks);
+  rc = tc_make_map_sf(&msfa, sfa, (uint64_t)pl.TN * pl.KS * nwt, pair ? 1u : (uint32_t)pl.uks);
   if (rc) return rc;
-  rc = tcp2_make_sf_map(&msfb, sfb, (uint64_t)pl.TM * pl.KS * 2, 2u * (uint32_t)pl.uks);
+  rc = tc_make_map_sf(&msfb, sfb, (uint64_t)pl.TM * pl.KS * 2, 2u * (uint32_t)pl.uks);
   if (rc) return rc;
   TcParams p = base;
   p.sfa = sfa; p.sfa2 = nullptr; p.sfb = sfb;

@@ -229,9 +229,75 @@ __device__ __forceinline__ void tc_finish16(const TcParams& p, int tok0, int n, 
     if (j < live) p.y[o0 + (size_t)j * p.N] = f32_to_bf16_bits(x[j]);
 }
 
+// Epilogue of the many-token kernels: 16 consecutive tokens of output feature n from the accumulator values x (gate/up
+// pair: u holds the up values), with the residual / gate-input values loaded beforehand (tc_preload16, while the MMAs ran):
+// bias, activation, gate multiply, residual, bf16 stores; residual / gate inputs arrive packed two per register.
+template <bool DUAL>
+__device__ __forceinline__ void tc_finish16_pre(const TcParams& p, int tok0, int n, float (&x)[16], float (&u)[16],
+                                            const uint32_t (&resp)[8], const uint32_t (&mulp)[8], const float* __restrict__ tok_scale) {
+  const int live = p.M - tok0;
+  const size_t o0 = (size_t)tok0 * p.N + n;
+  if (tok_scale) {  // the activations were split as x / 2^e per token: give the 2^e back (the array is padded to whole tiles)
+    const float4* sp = reinterpret_cast<const float4*>(tok_scale + tok0);
+    const float4 s0 = __ldg(sp), s1 = __ldg(sp + 1), s2 = __ldg(sp + 2), s3 = __ldg(sp + 3);
+    const float sc[16] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w, s2.x, s2.y, s2.z, s2.w, s3.x, s3.y, s3.z, s3.w};
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      x[j] *= sc[j];
+      if (DUAL) u[j] *= sc[j];
+    }
+  }
+  if (p.bias) {
+    const float b = bf16_bits_to_f32(p.bias[n]);
+#pragma unroll
+    for (int j = 0; j < 16; j++) x[j] += b;
+  }
+  switch (p.act) {
+    case TPX_ACT_GELU:
+#pragma unroll
+      for (int j = 0; j < 16; j++) x[j] = 0.5f * x[j] * (1.0f + erff(x[j] * 0.70710678118654752f));
+      break;
+    case TPX_ACT_SILU:
+#pragma unroll
+      for (int j = 0; j < 16; j++) x[j] = __fdividef(x[j], 1.0f + __expf(-x[j]));
+      break;
+    case TPX_ACT_RELU:
+#pragma unroll
+      for (int j = 0; j < 16; j++) x[j] = fmaxf(x[j], 0.0f);
+      break;
+    default: break;
+  }
+  if (DUAL) {
+#pragma unroll
+    for (int j = 0; j < 16; j++) x[j] *= u[j];
+  }
+  if (p.mul_in) {
+#pragma unroll
+    for (int j = 0; j < 16; j++) x[j] *= bf16_bits_to_f32((uint16_t)(mulp[j >> 1] >> (16 * (j & 1))));
+  }
+  if (p.res) {
+#pragma unroll
+    for (int j = 0; j < 16; j++) x[j] += bf16_bits_to_f32((uint16_t)(resp[j >> 1] >> (16 * (j & 1)))) * p.res_scale;
+  }
+#pragma unroll
+  for (int j = 0; j < 16; j++)
+    if (j < live) p.y[o0 + (size_t)j * p.N] = f32_to_bf16_bits(x[j]);
+}
+
+__device__ __forceinline__ void tc_preload16(const uint16_t* __restrict__ src, int M, int N, int tok0, int n, uint32_t (&pk)[8]) {
+  const int live = M - tok0;
+  const uint16_t* s = src + (size_t)tok0 * N + n;
+  uint16_t t[16];
+#pragma unroll
+  for (int j = 0; j < 16; j++) t[j] = j < live ? __ldg(s + (size_t)j * N) : (uint16_t)0;
+#pragma unroll
+  for (int j = 0; j < 8; j++) pk[j] = (uint32_t)t[2 * j] | ((uint32_t)t[2 * j + 1] << 16);
+}
+
 // host helpers shared by the tensor-core linears
 int tc_make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows);
 int tc_make_map64(CUtensorMap* m, const void* base, uint64_t rows, uint32_t box_rows);
+int tc_make_map_sf(CUtensorMap* m, const void* base, uint64_t rows, uint32_t box_rows);
 int tc_padded_ks(int64_t K, bool pair);
 struct TcNorm {  // optional RMSNorm applied to x on its way into the split (null gamma: none)
   const void* gamma;
