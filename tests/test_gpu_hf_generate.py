@@ -59,3 +59,31 @@ def test_generate_of_the_patched_model(cuda):
     mine, _ = runner.beam_search(ids.to(cuda), NEW, num_beams=3)
     # Hugging Face normalises by length only between finished hypotheses; with a fixed length its best beam is ours
     assert (beams == mine[:, 0].cpu()).all(dim=1).float().mean().item() >= 2 / 3
+
+
+def test_assisted_generation_through_the_patched_models(cuda):
+    """Speculative (assisted) decoding as the reference's examples/llm/run_spec_decode_llama_70b.py drives it: Hugging
+    Face's generate with an assistant model, both objects patched in place; the rollback of rejected draft tokens goes
+    through TppCache.crop. With greedy acceptance the result is the target's own greedy continuation."""
+    from tpp_pytorch_extension_b200.llm import fused_llama_infer as FL
+    cfg, target = _tiny_llama()
+    torch.manual_seed(6)
+    dcfg = transformers.LlamaConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=1, num_attention_heads=4,
+                                    num_key_value_heads=2, vocab_size=cfg.vocab_size, max_position_embeddings=128,
+                                    rms_norm_eps=1e-5, tie_word_embeddings=False, pad_token_id=0)
+    draft = transformers.LlamaForCausalLM(dcfg).float().eval()
+    FL.OptimizeModelForLlama(target, torch.bfloat16, cuda, "mxfp4", patch_model=True)
+    FL.OptimizeModelForLlama(draft, torch.bfloat16, cuda, "mxfp4", patch_model=True)
+    ids = torch.randint(1, cfg.vocab_size, (1, 12), generator=torch.Generator().manual_seed(4)).to(cuda)
+    NEW = 10
+    with torch.no_grad():
+        plain = target.generate(ids, max_new_tokens=NEW, do_sample=False)
+        cache_len_probe = target(ids).past_key_values.get_seq_length()
+        assisted = target.generate(ids, max_new_tokens=NEW, do_sample=False, assistant_model=draft)
+    assert cache_len_probe == ids.shape[1]
+    assert assisted.shape == plain.shape
+    # identical unless a verification batch (several tokens at once) rounds a near-tie the other way: then the sequences
+    # part at that position and only the common prefix is comparable
+    same = (assisted == plain)[0]
+    first_diff = int((~same).float().argmax()) if not bool(same.all()) else plain.shape[1]
+    assert first_diff >= ids.shape[1] + NEW // 2, (assisted, plain)

@@ -13,6 +13,10 @@ tensor_parallel_enabled = True
 class TppCache:
     """llm_common.TppCache (llm_common.py:80-181): the object the model forward carries."""
 
+    # what transformers' generate() asks of a cache object it did not create itself
+    is_compileable = False
+    is_sliding = [False]
+
     def __init__(self, **kwargs):
         self.tpp_cache = _CppCache()
 
@@ -27,6 +31,9 @@ class TppCache:
 
     def get_max_length(self):
         return None
+
+    def get_max_cache_shape(self, layer_idx=0):
+        return -1  # grows on demand
 
     def crop(self, max_length):
         seq_len = self.get_seq_length()
