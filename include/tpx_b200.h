@@ -239,6 +239,14 @@ int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const int64_t* pos,
                        int64_t Nkv, int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset, int64_t capacity,
                        const int32_t* dev_len, uint16_t* q_out, uint16_t* kc, uint16_t* vc, void* stream);
 
+/* The same for GPT-J (apply_rotary_pos_emb_gptj, src/csrc/llm/fused_llm_infer.cpp:150-204): the first HR values of every q
+ * and k head rotate in adjacent pairs (2i, 2i+1) with ep [MP][HR] fp32 (HR/2 sines, then HR/2 cosines), the rest of the head
+ * passes through; q permute and cache append as tpx_rope_kv_update. The cache is given as tensors (kc, vc) or, when
+ * k_pages != NULL, as page tables.                                                                                */
+int tpx_rope_kv_update_gptj(const uint16_t* qkv, const float* ep, const int64_t* pos, int64_t B, int64_t S, int64_t Nq, int64_t Nkv,
+                            int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset, int64_t capacity, const int32_t* dev_len,
+                            uint16_t* q_out, uint16_t* kc, uint16_t* vc, const uint64_t* k_pages, const uint64_t* v_pages, void* stream);
+
 /* Attention over the blocked cache. Replaces attn<T> (src/csrc/llm/attn.cpp:780-955):
  *   out = softmax(q.k^T / sqrt(H) + am[b][key], causal: key <= key_len - Sq + query) . v
  * q/out [B][Nkv][Sq][R][H] (GQA group folded into the row dimension, attn.cpp:793-795), am additive bf16 mask

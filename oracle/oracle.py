@@ -469,6 +469,53 @@ def opt_layer(hs, mask, W, cache, layer_idx, n_heads, head_dim, eps1, eps2, do_l
     return out.reshape(B, S, D)
 
 
+def rope_gptj(x_bf16, emb_pos, pos, n_heads, head_dim):
+    """apply_rotary_pos_emb_gptj (src/csrc/llm/fused_llm_infer.cpp:150-204) on [B,S,N*H]: the first HR values of every head
+    rotate in adjacent pairs (2i, 2i+1); emb_pos fp32 [MP, HR] holds HR/2 sines, then HR/2 cosines; positions beyond the
+    table leave the row untouched. Products are rounded separately (no fused multiply-add), the result to bf16."""
+    x = bf16_to_f32(_c(x_bf16, np.uint16)).astype(np.float32)
+    B, S = x.shape[0], x.shape[1]
+    MP, HR = emb_pos.shape
+    x = x.reshape(B, S, n_heads, head_dim).copy()
+    pos = np.asarray(pos, np.int64)
+    for b in range(B):
+        for s in range(S):
+            p = int(pos[0 if pos.shape[0] == 1 else b, s])
+            if p >= MP:
+                continue
+            sn, cs = emb_pos[p, :HR // 2].astype(np.float32), emb_pos[p, HR // 2:].astype(np.float32)
+            x0, x1 = x[b, s, :, 0:HR:2].copy(), x[b, s, :, 1:HR:2].copy()
+            x[b, s, :, 0:HR:2] = x0 * cs - x1 * sn
+            x[b, s, :, 1:HR:2] = x1 * cs + x0 * sn
+    return f32_to_bf16(x.reshape(B, S, n_heads * head_dim))
+
+
+def gptj_layer(hs, mask, pos, W, cache, layer_idx, n_heads, head_dim, eps, emb_pos, world=1, allreduce=None):
+    """GPTJBlock::_forward (src/csrc/llm/fused_llm_infer.cpp:735-848): one LayerNorm feeds attention (q, k, v without
+    bias, GPT-J rotary, out_proj) and the MLP (fc_in + GELU, fc_out) side by side; out = fc_out(...) + attention output
+    + residual / world (Add2ScalePostOp). W: plain fp32 weights q,k,v,o,fc_in,fc_out, bf16 b_in, b_out, g, b_ln."""
+    B, S, D = hs.shape
+    scale = 1.0 / world
+    res = hs.reshape(B * S, D)
+    x = layernorm(res, W["g"], W["b_ln"], eps)
+    q = qlinear(x, W["q"]).reshape(B, S, n_heads * head_dim)
+    k = qlinear(x, W["k"]).reshape(B, S, n_heads * head_dim)
+    v = qlinear(x, W["v"]).reshape(B, S, n_heads, head_dim)
+    q = rope_gptj(q, emb_pos, pos, n_heads, head_dim)
+    k = rope_gptj(k, emb_pos, pos, n_heads, head_dim).reshape(B, S, n_heads, head_dim)
+    kc, vc = cache.update(k, v, layer_idx)
+    key_len = cache.get_seq_length(layer_idx)
+    q5 = np.ascontiguousarray(q.reshape(B, S, n_heads, 1, head_dim).transpose(0, 2, 1, 3, 4))
+    ctx = attention(q5, kc, vc, mask, key_len, causal=True)
+    ctx = np.ascontiguousarray(ctx.transpose(0, 2, 1, 3, 4)).reshape(B * S, n_heads * head_dim)
+    so = qlinear(ctx, W["o"], res=res, res_scale=scale)
+    inter = qlinear(x, W["fc_in"], bias=W["b_in"], act=ACT_GELU)
+    out = qlinear(inter, W["fc_out"], bias=W["b_out"], res=so, res_scale=1.0)
+    if world > 1:
+        out = allreduce(out)
+    return out.reshape(B, S, D)
+
+
 def rel_err(y_bf16, ref_bf16):
     """max |y - ref| / max |ref|: the normalised max error the parity tests bound by 2e-2."""
     a, b = bf16_to_f32(y_bf16).astype(np.float64), bf16_to_f32(ref_bf16).astype(np.float64)

@@ -14,11 +14,14 @@ def _tiny(family, weight_dtype, cuda):
     from tpp_pytorch_extension_b200.llm import fused_opt_infer as FO
     if family == "opt":
         return FO.build_random_opt(FO.OPTShape(2, 256, 4, 512, 320, 128), weight_dtype, cuda, std=0.05)
+    if family == "gptj":
+        from tpp_pytorch_extension_b200.llm import fused_gptj_infer as FG
+        return FG.build_random_gptj(FG.GPTJShape(2, 256, 4, 512, 320, 32, 128), weight_dtype, cuda, std=0.05)
     shape = FL.LlamaShape(2, 256, 4, 2, 512, 320, max_position_embeddings=128)
     return FL.build_random_llama(shape, weight_dtype, cuda, std=0.05, quantize_lm_head=(weight_dtype == "mxfp4"))
 
 
-@pytest.mark.parametrize("family,weight_dtype", [("llama", "mxfp4"), ("llama", "qint8"), ("llama", "bf16"), ("opt", "mxfp4")])
+@pytest.mark.parametrize("family,weight_dtype", [("llama", "mxfp4"), ("llama", "qint8"), ("llama", "bf16"), ("opt", "mxfp4"), ("gptj", "mxfp4")])
 def test_saved_shard_generates_the_same_tokens(cuda, tmp_path, monkeypatch, family, weight_dtype):
     from tpp_pytorch_extension_b200._C import _qtype
     from tpp_pytorch_extension_b200.llm import llm_common

@@ -639,3 +639,86 @@ class OPTDecoderLayer:
                 return [out, [a[0] for a in lc.arenas], [a[1] for a in lc.arenas]]
             return [out, kc, vc]
         return [out]
+
+
+class GPTJBlock:
+    """torch.classes.tpp_llm.GPTJBlock (src/csrc/llm/fused_llm_infer.cpp:607-848).
+
+    params, in the reference's order (:636-652): [ln_gamma, ln_beta, q, k, v, out_proj, fc_in, fc_in_bias, fc_out,
+    fc_out_bias, embed_positions]; embed_positions is fp32 [max_positions, rotary_dim] (sines, then cosines). One
+    LayerNorm feeds the attention and the MLP, which run side by side; the block's output is
+    fc_out(gelu(fc_in(x))) + out_proj(attention) + residual / world, followed by ONE all-reduce."""
+
+    def __init__(self, params, layer_idx, eps, H, max_positions, rotary_dim):
+        import os
+        from . import _qtype
+        if len(params) != 11:
+            raise _lib.TpxError("GPTJBlock expects 11 parameters")
+        self.G, self.B, Wq, Wk, Wv, Wp, Wi, Bi, Wo, Bo, self.EP = params
+        ws = [Wq, Wk, Wv, Wp, Wi, Wo]
+        if not all(isinstance(w, _qtype.QTensor) for w in ws):
+            if os.environ.get("USE_MXFP4", "0") == "1":
+                ws = [w if isinstance(w, _qtype.QTensor) else _qtype.remap_and_quantize_mxfp4(w) for w in ws]
+            elif os.environ.get("USE_QINT8", "0") == "1":
+                ws = [w if isinstance(w, _qtype.QTensor) else _qtype.remap_and_quantize_qint8(w) for w in ws]
+            elif all(isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16 for w in ws):
+                from ..utils.blocked_layout import unblock_weight
+                ws = [unblock_weight(w) if w.dim() == 5 else w.contiguous() for w in ws]
+            else:
+                raise _lib.TpxError("GPTJBlock: weights must be all quantized tensors or all bf16 tensors")
+        Wq, Wk, Wv, self.Wp, self.Wi, self.Wo = ws
+        self.layer_idx, self.eps, self.H = int(layer_idx), float(eps), int(H)
+        self.max_positions, self.rotary_dim = int(max_positions), int(rotary_dim)
+        self.bf16 = isinstance(Wq, torch.Tensor)
+        self.Nq = self.Nkv = (Wq.shape[0] if self.bf16 else Wq.out_features) // self.H
+        self.Wqkv = torch.cat([Wq, Wk, Wv], 0).contiguous() if self.bf16 else _cat_q([Wq, Wk, Wv])
+        dev = self.G.device
+        self.Bi, self.Bo = Bi.to(dev, torch.bfloat16).contiguous(), Bo.to(dev, torch.bfloat16).contiguous()
+        if self.EP.dtype != torch.float32 or self.EP.dim() != 2 or self.EP.shape[1] != self.rotary_dim:
+            raise _lib.TpxError("embed_positions must be fp32 [max_positions, rotary_dim]")
+        self.EP = self.EP.contiguous()
+        if not self.bf16:
+            for w in (self.Wqkv, self.Wp, self.Wi, self.Wo):
+                w.prepare()
+
+    def forward(self, inp, cache, use_cache=True, dev_len=None):
+        """inp = [hidden_states [B,S,D] bf16, additive mask [B,Spad], position_ids int64 [1 or B, S]]."""
+        from ._tpp_attn import attention
+        hs, am, pos = inp[0], inp[1], inp[2]
+        _lib.require_cuda(hs, "hidden_states")
+        B, S, D = hs.shape
+        ws = get_pg_size()
+        L = _lib.lib()
+        res = hs.reshape(B * S, D)
+        x = layer_norm(res, self.G, self.B, self.eps)
+        qkv = fc_plain(x, self.Wqkv)
+        inter = fc_plain_act(x, self.Wi, self.Bi, "gelu")
+        lc = cache.layer(self.layer_idx)
+        if dev_len is None:
+            lc.ensure(B, self.Nkv, self.H, S, hs.dtype, hs.device)
+        q = torch.empty((B, self.Nkv, S, 1, self.H), dtype=hs.dtype, device=hs.device)
+        if pos.dtype != torch.int64 or not pos.is_contiguous():
+            pos = pos.to(torch.int64).contiguous()
+        paged = not lc.contiguous()
+        kc, vc = (None, None) if paged else lc.arenas[0]
+        _lib.check(L.tpx_rope_kv_update_gptj(qkv.data_ptr(), self.EP.data_ptr(), pos.data_ptr(), B, S, self.Nq, self.Nkv, self.H,
+                                             self.EP.shape[0], self.rotary_dim, pos.shape[0], lc.offset, lc.capacity(), _lib.ptr(dev_len),
+                                             q.data_ptr(), _lib.ptr(kc), _lib.ptr(vc),
+                                             lc.k_ptrs.data_ptr() if paged else None, lc.v_ptrs.data_ptr() if paged else None, _lib.stream()))
+        if dev_len is None:
+            lc.offset += S
+            key_len = lc.offset
+        else:
+            key_len = lc.capacity()
+        ctx = attention(q, kc, vc, am, key_len, causal=True, out_bsnrh=True, dev_len=dev_len,
+                        pages=(lc.k_ptrs, lc.v_ptrs) if paged else None).view(B * S, self.Nq * self.H)
+        so = fc_plain_act(ctx, self.Wp, res=res, res_scale=1.0 / ws)   # out_proj + residual / world
+        out = fc_plain_act(inter, self.Wo, self.Bo, res=so, res_scale=1.0)  # fc_out + bias + (attention + residual)
+        if ws > 1:
+            allreduce(out)
+        out = out.view(B, S, D)
+        if use_cache:
+            if paged:
+                return [out, [a[0] for a in lc.arenas], [a[1] for a in lc.arenas]]
+            return [out, kc, vc]
+        return [out]

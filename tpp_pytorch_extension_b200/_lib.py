@@ -54,6 +54,7 @@ _SIGS = {
     "tpx_layernorm": (c_int, [c_vp, c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_vp, c_vp]),
     "tpx_llama_layer_attention": (c_int, [c_vp, c_vp, c_vp]),
     "tpx_llama_layer_mlp": (c_int, [c_vp, c_vp, c_vp]),
+    "tpx_rope_kv_update_gptj": (c_int, [c_vp, c_vp, c_vp] + [c_i64] * 10 + [c_vp] * 6 + [c_vp]),
     "tpx_argmax_bf16": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp]),
     "tpx_rope_kv_update": (c_int, [c_vp, c_vp, c_vp] + [c_i64] * 10 + [c_vp, c_vp, c_vp, c_vp, c_vp]),
     "tpx_rope_kv_update_paged": (c_int, [c_vp, c_vp, c_vp] + [c_i64] * 10 + [c_vp, c_vp, c_vp, c_vp, c_vp]),

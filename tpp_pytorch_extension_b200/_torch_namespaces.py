@@ -8,6 +8,7 @@ written against the reference runs unchanged:
     torch.classes.tpp_llm.LlamaDecoderLayer(params, layer_idx, eps, head_dim, max_positions, rotary_dim).forward(inputs, cache, use_cache)
     torch.classes.tpp_llm.Qwen2DecoderLayer(...)
     torch.classes.tpp_llm.OPTDecoderLayer(params, layer_idx, eps1, eps2, head_dim, do_layer_norm_before)
+    torch.classes.tpp_llm.GPTJBlock(params, layer_idx, eps, head_dim, max_positions, rotary_dim)
 
 The quantized weight carrier of this package is a Python object (the reference's custom quantizer tensors cannot exist
 on a CUDA device without its C++ classes), which an operator schema cannot name; the entries are therefore attached to
@@ -24,5 +25,5 @@ def install():
         setattr(ops, name, fn)
     classes = torch.classes.tpp_llm
     for name, cls in (("TppCache", A.TppCache), ("LlamaDecoderLayer", F.LlamaDecoderLayer), ("Qwen2DecoderLayer", F.Qwen2DecoderLayer),
-                      ("OPTDecoderLayer", F.OPTDecoderLayer)):
+                      ("OPTDecoderLayer", F.OPTDecoderLayer), ("GPTJBlock", F.GPTJBlock)):
         setattr(classes, name, cls)

@@ -292,6 +292,55 @@ __global__ void rope_kv_v8_kernel(const uint16_t* __restrict__ qkv, const float*
   *reinterpret_cast<uint4*>(dst + h2 + half) = hi;
 }
 
+// GPT-J's rotary embedding (apply_rotary_pos_emb_gptj, src/csrc/llm/fused_llm_infer.cpp:150-204) with the same q permute
+// and cache append: the first HR values of a head rotate in ADJACENT pairs (2i, 2i+1), the table is [MP][HR] with the
+// HR/2 sines first, then the cosines; the rest of the head passes through. One thread per (token, head, adjacent pair).
+__global__ void rope_kv_gptj_kernel(const uint16_t* __restrict__ qkv, const float* __restrict__ ep, const int64_t* __restrict__ pos,
+                                    int B, int S, int Nq, int Nkv, int H, int MP, int HR, int Bpos, int64_t offset_arg,
+                                    const int* __restrict__ dev_len, int64_t capacity, uint16_t* __restrict__ q_out, uint16_t* __restrict__ kc,
+                                    uint16_t* __restrict__ vc, const uint64_t* __restrict__ kpages, const uint64_t* __restrict__ vpages) {
+  pdl_trigger();
+  pdl_wait();
+  const int heads = Nq + 2 * Nkv;
+  const int half = H / 2;
+  const int64_t offset = dev_len ? (int64_t)*dev_len : offset_arg;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)B * S * heads * half) return;
+  const int h2 = (int)(idx % half);
+  const int hd = (int)((idx / half) % heads);
+  const int s = (int)((idx / ((int64_t)half * heads)) % S);
+  const int b = (int)(idx / ((int64_t)half * heads * S));
+  const uint16_t* src = qkv + ((int64_t)(b * S + s) * heads + hd) * H;
+  const uint32_t in = *reinterpret_cast<const uint32_t*>(src + 2 * h2);
+  uint16_t o0 = (uint16_t)(in & 0xffff), o1 = (uint16_t)(in >> 16);
+  if (hd < Nq + Nkv && 2 * h2 < HR) {
+    const int64_t p = pos[(int64_t)(Bpos == 1 ? 0 : b) * S + s];
+    if (p < MP) {
+      const float x0 = bf16_bits_to_f32(o0), x1 = bf16_bits_to_f32(o1);
+      const float sn = ep[p * HR + h2], c = ep[p * HR + HR / 2 + h2];
+      // every product rounded on its own (no fused multiply-add): the same value on every compiler and in the oracle
+      o0 = f32_to_bf16_bits(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn)));
+      o1 = f32_to_bf16_bits(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, sn)));
+    }
+  }
+  uint16_t* dst;
+  if (hd < Nq) {
+    const int R = Nq / Nkv, n = hd / R, r = hd % R;
+    dst = q_out + ((((int64_t)b * Nkv + n) * S + s) * R + r) * H;
+  } else {
+    const bool is_k = hd < Nq + Nkv;
+    const int n = is_k ? hd - Nq : hd - Nq - Nkv;
+    const int64_t t = offset + s;
+    if (t >= capacity) return;
+    if (kpages) {
+      dst = reinterpret_cast<uint16_t*>((is_k ? kpages : vpages)[t / 32]) + (((int64_t)b * Nkv + n) * 32 + (t % 32)) * H;
+    } else {
+      dst = (is_k ? kc : vc) + ((((t / 32) * B + b) * Nkv + n) * 32 + (t % 32)) * H;
+    }
+  }
+  *reinterpret_cast<uint32_t*>(dst + 2 * h2) = (uint32_t)o0 | ((uint32_t)o1 << 16);
+}
+
 // ---------------------------------------------------------------- attention
 // Query rows are consecutive (query position, group member) pairs of one (batch, kv head). Each warp keeps a
 // running (max, sum, fp32 output) for 16 rows over the KV blocks it visits. With more than one KV split a CTA
@@ -745,6 +794,26 @@ static int rope_kv_update_impl(const uint16_t* qkv, const float* ep, const int64
   return TPX_OK;
 }
 
+extern "C" int tpx_rope_kv_update_gptj(const uint16_t* qkv, const float* ep, const int64_t* pos, int64_t B, int64_t S, int64_t Nq,
+                                       int64_t Nkv, int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset, int64_t capacity,
+                                       const int32_t* dev_len, uint16_t* q_out, uint16_t* kc, uint16_t* vc, const uint64_t* k_pages,
+                                       const uint64_t* v_pages, void* stream) {
+  if (S == 0 && B > 0) return TPX_OK;
+  TPX_REQUIRE(qkv && ep && pos && q_out && ((kc && vc) || (k_pages && v_pages)), TPX_ERR_ARG, "rope_kv_update_gptj: null pointer");
+  TPX_REQUIRE(B > 0 && S >= 0 && Nq > 0 && Nkv > 0 && Nq % Nkv == 0 && H % 2 == 0 && HR % 2 == 0 && HR >= 0 && HR <= H, TPX_ERR_ARG,
+              "rope_kv_update_gptj: bad shape");
+  TPX_REQUIRE(Bpos == 1 || Bpos == B, TPX_ERR_ARG, "position_ids shape not compatible");
+  if (!dev_len)
+    TPX_REQUIRE(offset >= 0 && offset + S <= capacity, TPX_ERR_ARG, "rope_kv_update_gptj: cache capacity %ld is short of %ld tokens",
+                (long)capacity, (long)(offset + S));
+  if (S == 0) return TPX_OK;
+  const int64_t total = B * S * (Nq + 2 * Nkv) * (H / 2);
+  TPX_CUDA_OK(launch_pdl(rope_kv_gptj_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, qkv, ep, pos, (int)B,
+                         (int)S, (int)Nq, (int)Nkv, (int)H, (int)MP, (int)HR, (int)Bpos, offset, dev_len, capacity, q_out, kc, vc, k_pages,
+                         v_pages));
+  return TPX_OK;
+}
+
 extern "C" int tpx_rope_kv_update(const uint16_t* qkv, const float* ep, const int64_t* pos, int64_t B, int64_t S, int64_t Nq,
                                   int64_t Nkv, int64_t H, int64_t MP, int64_t HR, int64_t Bpos, int64_t offset,
                                   int64_t capacity, const int32_t* dev_len, uint16_t* q_out, uint16_t* kc, uint16_t* vc, void* stream) {
@@ -763,9 +832,9 @@ extern "C" int tpx_rope_kv_update_paged(const uint16_t* qkv, const float* ep, co
 // SM (its copy stages take most of the shared memory), so a grid a little over a multiple of the SM count pays for a
 // whole extra wave; the fixed cost (first copy's latency, query load, merge) is worth about two blocks, three when
 // partials go through global memory. TPX_ATTN_SPLITS overrides the choice.
-static int attn_plan(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t key_len, int* chunks, int* splits) {
+static int attn_plan(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len, int* chunks, int* splits) {
   const int64_t rows = Sq * R;
-  if (rows > kAttnRows) {
+  if (rows > kAttnRows || H > 128) {  // head size 256 (GPT-J): the four warps of a CTA share one KV stream at every row count
     *chunks = (int)((rows + 63) / 64);
     *splits = 1;
     return 0;
@@ -815,7 +884,7 @@ static size_t attn_counter_bytes(int64_t B, int64_t Nkv, int chunks) {
 
 extern "C" size_t tpx_attention_scratch_bytes(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t H, int64_t key_len) {
   int chunks, splits;
-  attn_plan(B, Nkv, Sq, R, key_len, &chunks, &splits);
+  attn_plan(B, Nkv, Sq, R, H, key_len, &chunks, &splits);
   if (splits == 1) return 0;
   return attn_counter_bytes(B, Nkv, chunks) + (size_t)B * Nkv * chunks * splits * kAttnRows * (H + 2) * sizeof(float);
 }
@@ -826,14 +895,14 @@ static int attention_impl(const uint16_t* q, const uint16_t* kc, const uint16_t*
   if (Sq == 0 && B > 0 && Nkv > 0 && R > 0) return TPX_OK;  // no queries
   TPX_REQUIRE(q && ((kc && vc) || (kpages && vpages)) && out, TPX_ERR_ARG, "attention: null pointer");
   TPX_REQUIRE(B > 0 && Nkv > 0 && Sq >= 0 && R > 0 && key_len >= Sq, TPX_ERR_ARG, "attention: bad shape");
-  TPX_REQUIRE(H == 64 || H == 128, TPX_ERR_UNSUPPORTED, "attention: head dim %ld not supported (64 or 128)", (long)H);
+  TPX_REQUIRE(H == 64 || H == 128 || H == 256, TPX_ERR_UNSUPPORTED, "attention: head dim %ld not supported (64, 128 or 256)", (long)H);
   TPX_REQUIRE(!am || Spad >= key_len, TPX_ERR_ARG, "attention: mask of %ld keys is shorter than the cache (%ld)", (long)Spad, (long)key_len);
   if (Sq == 0) return TPX_OK;
   AttnParams p;
   p.q = q; p.kc = kc; p.vc = vc; p.kpages = kpages; p.vpages = vpages; p.am = am; p.out = out; p.part = nullptr; p.counters = nullptr;
   p.B = (int)B; p.Nkv = (int)Nkv; p.Sq = (int)Sq; p.R = (int)R; p.H = (int)H;
   p.key_len = (int)key_len; p.Spad = (int)Spad; p.causal = causal; p.out_bsnrh = out_bsnrh; p.dev_len = dev_len;
-  attn_plan(B, Nkv, Sq, R, key_len, &p.chunks, &p.splits);
+  attn_plan(B, Nkv, Sq, R, H, key_len, &p.chunks, &p.splits);
   p.scale = 1.0f / sqrtf((float)H);
   if (p.splits > 1) {
     size_t need = tpx_attention_scratch_bytes(B, Nkv, Sq, R, H, key_len);
@@ -848,7 +917,8 @@ static int attention_impl(const uint16_t* q, const uint16_t* kc, const uint16_t*
   cudaStream_t st = (cudaStream_t)stream;
   const bool decode = Sq * R <= kAttnRows;
   int rc;
-  if (H == 128) rc = decode ? attn_launch<128, 1>(p, grid, st) : attn_launch<128, 0>(p, grid, st);
+  if (H == 256) rc = attn_launch<256, 0>(p, grid, st);  // 66 KB of KV stages per stream: one stream per CTA
+  else if (H == 128) rc = decode ? attn_launch<128, 1>(p, grid, st) : attn_launch<128, 0>(p, grid, st);
   else rc = decode ? attn_launch<64, 1>(p, grid, st) : attn_launch<64, 0>(p, grid, st);
   if (rc) return rc;
   return TPX_OK;

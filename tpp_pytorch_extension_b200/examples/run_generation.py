@@ -19,10 +19,12 @@ import torch
 from tpp_pytorch_extension_b200.llm import fused_llama_infer as FL
 from tpp_pytorch_extension_b200._C import _fused_llm_infer as fused_llm_cpp
 
+from tpp_pytorch_extension_b200.llm import fused_gptj_infer as FG
 from tpp_pytorch_extension_b200.llm import fused_opt_infer as FO
 
 MODELS = {"llama2-7b": FL.LLAMA2_7B, "llama3-8b": FL.LLAMA3_8B, "llama2-70b": FL.LLAMA2_70B,
-          "opt-6.7b": FO.OPTShape(32, 4096, 32, 16384, 50272), "opt-30b": FO.OPTShape(48, 7168, 56, 28672, 50272)}
+          "opt-6.7b": FO.OPTShape(32, 4096, 32, 16384, 50272), "opt-30b": FO.OPTShape(48, 7168, 56, 28672, 50272),
+          "gptj-6b": FG.GPTJShape(28, 4096, 16, 16384, 50400, 64)}
 
 
 def main(argv=None):
@@ -59,6 +61,8 @@ def main(argv=None):
         model = llm_common.load_sharded_model()
     elif isinstance(shape, FO.OPTShape):
         model = FO.build_random_opt(shape, wd, "cuda")
+    elif isinstance(shape, FG.GPTJShape):
+        model = FG.build_random_gptj(shape, wd, "cuda")
     else:
         model = FL.build_random_llama(shape, wd, "cuda", max_positions=a.input_tokens + a.max_new_tokens + 8,
                                       quantize_lm_head=a.quantize_lm_head and wd != "bf16")

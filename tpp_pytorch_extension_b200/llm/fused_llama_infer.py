@@ -103,10 +103,10 @@ class LlamaRunner(torch.nn.Module):
         if get_size() > 1:
             offs = shard_offsets(self.shape.hidden_size, get_size(), 64)
             r = get_rank()
-            logits = fused_llm_cpp.fc_plain(hs[..., offs[r]:offs[r + 1]].contiguous(), self.lm_head_w)
+            logits = fused_llm_cpp.fc_plain(hs[..., offs[r]:offs[r + 1]].contiguous(), self.lm_head_w, getattr(self, "lm_head_b", None))
             fused_llm_cpp.allreduce(logits)
         else:
-            logits = fused_llm_cpp.fc_plain(hs, self.lm_head_w)
+            logits = fused_llm_cpp.fc_plain(hs, self.lm_head_w, getattr(self, "lm_head_b", None))
         if logits.shape[-1] != self.shape.vocab_size:  # a quantized head padded to whole row groups
             logits = logits[..., :self.shape.vocab_size]
         return logits

@@ -229,13 +229,14 @@ def runner_state(runner):
 
 def runner_from_state(st, device="cuda"):
     from . import fused_llama_infer as FL
+    from . import fused_gptj_infer as FG
     from . import fused_opt_infer as FO
     if (st["rank"], st["size"]) != (get_rank(), get_size()):
         raise ValueError(f"this checkpoint holds shard {st['rank']} of {st['size']}, the process is rank {get_rank()} of {get_size()}")
     set_pg()
     dev = torch.device(device)
-    shape_cls = {"LlamaShape": FL.LlamaShape, "OPTShape": FO.OPTShape}[st["shape_class"]]
-    cls = {"LlamaRunner": FL.LlamaRunner, "OPTRunner": FO.OPTRunner}[st["runner"]]
+    shape_cls = {"LlamaShape": FL.LlamaShape, "OPTShape": FO.OPTShape, "GPTJShape": FG.GPTJShape}[st["shape_class"]]
+    cls = {"LlamaRunner": FL.LlamaRunner, "OPTRunner": FO.OPTRunner, "GPTJRunner": FG.GPTJRunner}[st["runner"]]
     runner = cls.__new__(cls)
     torch.nn.Module.__init__(runner)
     runner.shape = shape_cls(**st["shape"])
