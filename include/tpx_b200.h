@@ -284,6 +284,25 @@ int tpx_attention_paged(const uint16_t* q, const uint64_t* k_pages, const uint64
  * No counterpart in the reference.                                                                              */
 int tpx_attention_tc_status(void* stream, unsigned* status_host);
 
+/* ---------------------------------------------------------------- 8-bit floating-point weights
+ * The reference stores a linear's weight as bfloat8 (E5M2) or hfloat8 (E4M3) when asked to (--weight-dtype bfloat8 /
+ * hfloat8: src/tpp_pytorch_extension/llm/llm_common.py:519-522 casts the blocked weight) and multiplies through
+ * TppBlockedLinearW<Tin, bfloat8 / hfloat8, Tout> (src/csrc/fused_gemm.h:1558-1565): bf16 activations, the weight
+ * converted up, fp32 accumulation, the same post-ops. Here the bytes go to the tensor cores as they are
+ * (tcgen05.mma kind::mxf8f6f4 with the weight as an E4M3 / E5M2 operand and unit block scales) against the two-term
+ * E4M3 split of the activations that the MXFP4 path uses. tpx_repack_fp8_tc tiles a plain [N][K] byte matrix (w2 != NULL:
+ * a gate/up pair) into wq [TN][KS][(2)][128 rows][128 bytes] + sfa (constant scale blocks), sizes from
+ * tpx_fp8_tc_packed_bytes; tpx_qlinear_fp8_tc has the contract of tpx_qlinear_mxfp4_tc plus the weight format and an
+ * optional RMSNorm of x (gamma NULL: none). N % 32 == 0, K % 64 == 0.                                              */
+enum { TPX_FP8_E4M3 = 1, TPX_FP8_E5M2 = 2 };
+int tpx_fp8_tc_packed_bytes(int64_t N, int64_t K, int pair, size_t* wq_bytes, size_t* sfa_bytes);
+int tpx_repack_fp8_tc(const uint8_t* w, const uint8_t* w2, int64_t N, int64_t K, uint8_t* wq, uint8_t* sfa, void* stream);
+size_t tpx_qlinear_fp8_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int pair);
+int tpx_qlinear_fp8_tc(const uint8_t* wq, const uint8_t* sfa, int fmt, int pair, const uint16_t* x, const void* gamma,
+                       int gamma_is_f32, float eps, int64_t M, int64_t N, int64_t K, const uint16_t* bias, int act,
+                       const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y, void* scratch,
+                       size_t scratch_bytes, void* stream);
+
 /* ---------------------------------------------------------------- a decoder layer in two calls
  * LlamaDecoderLayer::_forward / Qwen2DecoderLayer::_forward (src/csrc/llm/fused_llm_infer.cpp:1195-1286, :1440-1510) on
  * MXFP4 weights, as two sequences of the entry points above issued from C: tpx_llama_layer_attention = RMSNorm + fused

@@ -249,6 +249,69 @@ def int8_plain(q, scales):
     return qp, sp
 
 
+# --------------------------------------------------------------------------- 8-bit floating-point weights
+# The reference keeps a weight as bfloat8 / hfloat8 by a plain cast of the blocked bf16 tensor
+# (src/tpp_pytorch_extension/llm/llm_common.py:519-522) and converts it up inside TppBlockedLinearW<Tin, bfloat8 | hfloat8>
+# (src/csrc/fused_gemm.h:1558-1565). Those dtypes exist only in the reference's own PyTorch build; the formats are the
+# published ones: bfloat8 = E5M2 (bias 15, infinities), hfloat8 = E4M3 (bias 7, largest finite value 448, no infinity).
+# Round to nearest even; out-of-range values become infinity (E5M2) or NaN (E4M3). Pinned against the float8 casts of
+# stock PyTorch on the CPU (tests/test_oracle.py).
+FP8_E4M3, FP8_E5M2 = 1, 2
+_FP8_PARAMS = {FP8_E4M3: (4, 3, 7, 448.0), FP8_E5M2: (5, 2, 15, 57344.0)}
+
+
+def fp8_to_f32_table(fmt):
+    ebits, mbits, bias, _ = _FP8_PARAMS[fmt]
+    out = np.zeros(256, dtype=np.float32)
+    for c in range(256):
+        sign = -1.0 if c & 0x80 else 1.0
+        e = (c >> mbits) & ((1 << ebits) - 1)
+        m = c & ((1 << mbits) - 1)
+        if fmt == FP8_E5M2 and e == 31:
+            v = np.inf if m == 0 else np.nan
+        elif fmt == FP8_E4M3 and e == 15 and m == 7:
+            v = np.nan
+        elif e == 0:
+            v = m * 2.0 ** (1 - bias - mbits)
+        else:
+            v = (1.0 + m / (1 << mbits)) * 2.0 ** (e - bias)
+        out[c] = sign * v
+    return out
+
+
+def f32_to_fp8(x, fmt):
+    """fp32 array -> uint8 codes of the format, round to nearest even."""
+    ebits, mbits, bias, vmax = _FP8_PARAMS[fmt]
+    x = np.asarray(x, dtype=np.float32)
+    with np.errstate(invalid="ignore", over="ignore"):
+        return _f32_to_fp8(x, fmt, ebits, mbits, bias, vmax)
+
+
+def _f32_to_fp8(x, fmt, ebits, mbits, bias, vmax):
+    finite = np.isfinite(x)
+    a = np.abs(np.where(finite, x, 0.0)).astype(np.float64)
+    sign = (np.signbit(x)).astype(np.uint8) << 7
+    _, ex = np.frexp(a)                       # a = f * 2^ex, f in [0.5, 1)
+    e = np.maximum(ex - 1, 1 - bias)          # exponent of the binade, clamped to the subnormal one
+    step = np.ldexp(1.0, e - mbits)
+    q = np.rint(a / step)                     # numpy rounds half to even; a / step is exact (power-of-two divisor)
+    over = q * step > vmax
+    e2 = np.where(q >= (2 << mbits), e + 1, e)  # the rounding carried into the next binade
+    q2 = np.where(q >= (2 << mbits), q / 2, q)
+    normal = q2 >= (1 << mbits)
+    code = np.where(normal, ((e2 + bias).astype(np.int64) << mbits) | (q2.astype(np.int64) - (1 << mbits)), q2.astype(np.int64))
+    if fmt == FP8_E5M2:
+        code = np.where(over | np.isinf(x), 0x7c, code)
+        code = np.where(np.isnan(x), 0x7f, code)
+    else:
+        code = np.where(over | ~finite, 0x7f, code)
+    return (code.astype(np.uint8) | sign).astype(np.uint8)
+
+
+def fp8_dequant(codes, fmt):
+    return fp8_to_f32_table(fmt)[np.asarray(codes, dtype=np.uint8)]
+
+
 # --------------------------------------------------------------------------- linear
 def qlinear(x_bf16, wd, bias=None, mul_in=None, res=None, res_scale=1.0, act=ACT_NONE, ref_rounding=False):
     x = _c(x_bf16, np.uint16)

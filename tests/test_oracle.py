@@ -218,3 +218,23 @@ def test_layernorm_restatement_matches_torch():
     want = torch.nn.functional.layer_norm(torch.from_numpy(O.bf16_to_f32(x)), (320,), torch.from_numpy(O.bf16_to_f32(g)),
                                           torch.from_numpy(O.bf16_to_f32(b)), 1e-5).numpy()
     assert np.abs(y - want).max() <= 2.0 ** -7 * np.abs(want).max()
+
+
+def test_fp8_casts_match_stock_torch_on_every_bf16_value():
+    """bfloat8 (E5M2) / hfloat8 (E4M3) weights: the restated round-to-nearest-even cast against torch's float8 casts on
+    all 65536 bf16 bit patterns (subnormals, ties, overflow) and the 256-entry decode table against torch's upcast."""
+    import torch
+    x = O.bf16_to_f32(np.arange(65536, dtype=np.uint16))
+    finite = np.isfinite(x)
+    for fmt, dt in ((O.FP8_E4M3, torch.float8_e4m3fn), (O.FP8_E5M2, torch.float8_e5m2)):
+        t = torch.from_numpy(x.copy()).to(dt)
+        want = t.view(torch.uint8).numpy()
+        got = O.f32_to_fp8(x, fmt)
+        back = t.float().numpy()
+        nan = np.isnan(back)
+        assert np.array_equal(got[finite & ~nan], want[finite & ~nan])
+        assert np.all(np.isnan(O.fp8_dequant(got[finite & nan], fmt)))  # out of range for E4M3: NaN on both sides
+        table = O.fp8_to_f32_table(fmt)
+        codes = np.arange(256, dtype=np.uint8)
+        ref = torch.from_numpy(codes).view(dt).float().numpy()
+        assert np.array_equal(table[~np.isnan(ref)], ref[~np.isnan(ref)]) and np.all(np.isnan(table[np.isnan(ref)]))

@@ -122,7 +122,26 @@ def _bf16_linear(x, w, bias, act, mul_in, res, res_scale):
     return y
 
 
+_FP8 = (torch.float8_e4m3fn, torch.float8_e5m2)
+
+
+def _wrap_fp8(w):
+    """A plain [N, K] tensor of an 8-bit floating-point dtype -> its Fp8Weight (kept on the tensor)."""
+    if isinstance(w, torch.Tensor) and w.dtype in _FP8:
+        hit = getattr(w, "_tpx_fp8", None)
+        if hit is None:
+            from ._qtype import Fp8Weight
+            hit = Fp8Weight(w)
+            try:
+                w._tpx_fp8 = hit
+            except Exception:
+                pass
+        return hit
+    return w
+
+
 def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
+    w, w2 = _wrap_fp8(w), _wrap_fp8(w2)
     if isinstance(w, torch.Tensor) and w2 is None:
         if norm is not None:
             x = rms_norm(x, norm[0], norm[1])
@@ -145,6 +164,27 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
             _lib.require_cuda(t, name)
             if t.dtype != torch.bfloat16:
                 raise _lib.TpxError(f"fc_plain: {name} must be bfloat16")
+    if w.kind == 3:  # 8-bit floating-point weight (bfloat8 / hfloat8): the 128-row tensor-core kernel reads the bytes as they are
+        wq, sfa = w.packed_tc(w2)
+        key = ("fp8", M, N, K, w2 is not None)
+        nb = _SCRATCH_BYTES.get(key)
+        if nb is None:
+            nb = _SCRATCH_BYTES[key] = L.tpx_qlinear_fp8_tc_scratch_bytes(M, N, K, int(w2 is not None))
+        sc = _lib.scratch(nb, x.device)
+        gamma = eps = None
+        if norm is not None and K <= 8192 and _opt("TPX_FUSED_NORM", "1") != "0":
+            gamma, eps = norm
+        elif norm is not None:
+            x = rms_norm(x, norm[0], norm[1])
+        if not x.is_contiguous():
+            x = x.contiguous()
+        rc = L.tpx_qlinear_fp8_tc(wq.data_ptr(), sfa.data_ptr(), w.fmt, int(w2 is not None), x.data_ptr(), _lib.ptr(gamma),
+                                  int(gamma is not None and gamma.dtype == torch.float32), float(eps or 0.0), M, N, K, _lib.ptr(bias),
+                                  ACT[act], _lib.ptr(mul_in), _lib.ptr(res), float(res_scale), y.data_ptr(), sc.data_ptr(), sc.numel(),
+                                  _lib.stream())
+        if rc:
+            _lib.check(rc)
+        return y
     if w.kind == 1 and mxfp4_path() == "tc":
         if w2 is not None and (w2.out_features, w2.in_features, w2.kind) != (N, K, w.kind):
             raise _lib.TpxError("gate/up weights must have the same shape and quantization")
@@ -216,7 +256,7 @@ def fc_plain_act(input, weight, bias=None, act=None, mul_in=None, res=None, res_
 def fc_gate_up(input, w_gate, w_up, act="silu", norm=None):
     """act(x.Wg^T) * (x.Wu^T) in one pass over both weights (src/csrc/llm/fused_llm_infer.cpp:1271-1272).
     norm = (gamma, eps): RMSNorm of the input first, fused into the linear where the kernel family supports it."""
-    if isinstance(w_gate, torch.Tensor):  # bf16 weights: two passes, the second multiplying by the activated first
+    if isinstance(w_gate, torch.Tensor) and w_gate.dtype not in _FP8:  # bf16 weights: two passes, the second multiplying by the activated first
         if norm is not None:
             input = rms_norm(input, norm[0], norm[1])
         g = _bf16_linear(input, w_gate, None, act, None, None, 1.0)
@@ -308,6 +348,11 @@ def _cat_q(ws):
     src/csrc/llm/fused_llm_infer.cpp:422-505): blocks are per output row, so stacking the storage is exact."""
     from ._qtype import QTensor
     w0 = ws[0]
+    if w0.kind == 3:
+        from ._qtype import Fp8Weight
+        if any(w.kind != 3 or w.fmt != w0.fmt or w.shape[1] != w0.shape[1] for w in ws):
+            raise _lib.TpxError("fused q/k/v: weights must share format and in-features")
+        return Fp8Weight(torch.cat([w.codes for w in ws], 0).view(w0.dtype))
     for w in ws[1:]:
         if (w.kind, w.block_size, w.shape[1:]) != (w0.kind, w0.block_size, w0.shape[1:]):
             raise _lib.TpxError("fused q/k/v: weights must share quantization and in-features")
@@ -377,7 +422,7 @@ class LlamaDecoderLayer:
         sc = _timers.scope
 
         def wbytes(w):  # bytes a linear has to read for its weight (packed codes + scales, or bf16)
-            return w.numel() * 2 if isinstance(w, torch.Tensor) else (w.numel() * 17 // 32 if w.kind == 1 else w.numel() + 4 * w.numel() // w.block_size)
+            return w.numel() * 2 if isinstance(w, torch.Tensor) else (w.numel() * 17 // 32 if w.kind == 1 else w.numel() if w.kind == 3 else w.numel() + 4 * w.numel() // w.block_size)
 
         def nk(w):
             return tuple(w.shape) if isinstance(w, torch.Tensor) else (w.out_features, w.in_features)

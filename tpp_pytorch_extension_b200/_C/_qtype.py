@@ -12,7 +12,7 @@ import torch
 
 from .. import _lib
 
-W_MXFP4, W_INT8 = 1, 2
+W_MXFP4, W_INT8, W_FP8 = 1, 2, 3
 kPerBlockMxFP = "per_block_mxfp"      # at::kPerBlockMxFP, src/csrc/qtypes.h:12
 kPerBlockAffine = "per_block_affine"  # at::kPerBlockAffine, src/csrc/qtypes.h:11
 
@@ -191,7 +191,12 @@ def _from_state(st, device, pair_with=None):
     """Inverse of QTensor.state(). `pair_with`: the up-projection object this gate weight was packed with (the pair
     layout is looked up by that object's identity)."""
     dev = lambda t: None if t is None else t.to(device)
-    q = QTensor(dev(st["codes"]), dev(st["scales"]), st["shape"], st["qscheme"], st["block_size"], st["axis"], st["is_vnni"])
+    if st.get("fp8"):
+        q = Fp8Weight.__new__(Fp8Weight)
+        QTensor.__init__(q, dev(st["codes"]), dev(st["scales"]), st["shape"], st["qscheme"], 0, st["axis"], st["is_vnni"])
+        q.fmt = st["fp8"]
+    else:
+        q = QTensor(dev(st["codes"]), dev(st["scales"]), st["shape"], st["qscheme"], st["block_size"], st["axis"], st["is_vnni"])
     if st["packed"] is not None:
         q._packed = tuple(dev(t) for t in st["packed"])
     if st["packed_tc"] is not None:
@@ -207,6 +212,106 @@ def _from_state(st, device, pair_with=None):
 
 QTensor.state = _state
 QTensor.from_state = staticmethod(_from_state)
+
+
+FP8_E4M3, FP8_E5M2 = 1, 2  # TPX_FP8_E4M3 / TPX_FP8_E5M2 of the C interface
+FP8_DTYPES = {"hfloat8": torch.float8_e4m3fn, "bfloat8": torch.float8_e5m2,
+              "float8_e4m3fn": torch.float8_e4m3fn, "float8_e5m2": torch.float8_e5m2}
+
+
+class Fp8Weight(QTensor):
+    """A linear weight held as 8-bit floating point, plain [N, K]: what `weight.data.to(bfloat8 | hfloat8)` leaves behind
+    in the reference (src/tpp_pytorch_extension/llm/llm_common.py:519-522; the dtypes come from the reference's own
+    PyTorch build). bfloat8 is E5M2 (torch.float8_e5m2), hfloat8 is E4M3 (torch.float8_e4m3fn); the cast rounds to
+    nearest even and there are no scales. `codes` holds the bytes; the tensor-core layout is built by packed_tc()."""
+    is_quantized = False
+
+    def __init__(self, data):
+        if data.dtype not in (torch.float8_e4m3fn, torch.float8_e5m2) or data.dim() != 2:
+            raise _lib.TpxError("Fp8Weight: a [N, K] tensor of torch.float8_e4m3fn or torch.float8_e5m2 expected")
+        N, K = data.shape
+        if N % 32 or K % 64:
+            raise _lib.TpxError("8-bit floating-point weights need out-features % 32 == 0 and in-features % 64 == 0")
+        self.fmt = FP8_E4M3 if data.dtype == torch.float8_e4m3fn else FP8_E5M2
+        codes = data.contiguous().view(torch.uint8)
+        super().__init__(codes, codes.new_empty(0), (N, K), "fp8_e4m3" if self.fmt == FP8_E4M3 else "fp8_e5m2", 0, axis=1, is_vnni=False)
+
+    kind = W_FP8
+
+    @property
+    def dtype(self):
+        return torch.float8_e4m3fn if self.fmt == FP8_E4M3 else torch.float8_e5m2
+
+    @property
+    def out_features(self):
+        return self.shape[0]
+
+    @property
+    def in_features(self):
+        return self.shape[1]
+
+    def dequantize(self):
+        return self.codes.view(self.dtype).float()
+
+    def packed(self, drop_interchange=False):
+        raise _lib.TpxError("8-bit floating-point weights run on the tensor-core path only")
+
+    def packed_i8tc(self):
+        raise _lib.TpxError("the int8 tensor-core path takes int8 weights")
+
+    def packed_tc(self, other=None):
+        """(wq, sfa) of tpx_repack_fp8_tc, built once and cached; `other`: the up projection of a gate/up pair."""
+        if other is None:
+            if self._packed_tc is not None:
+                return self._packed_tc
+        else:
+            hit = getattr(self, "_pair_tc", None)
+            if hit is not None and hit[0] is other:
+                return hit[1]
+            if not isinstance(other, Fp8Weight) or other.fmt != self.fmt or other.shape != self.shape:
+                raise _lib.TpxError("gate/up weights must have the same shape and format")
+        if self.codes.numel() == 0 or (other is not None and other.codes.numel() == 0):
+            raise _lib.TpxError("the bytes of this weight were dropped before it was packed for this use")
+        L = _lib.lib()
+        N, K = self.shape
+        wb, sb = ctypes.c_size_t(), ctypes.c_size_t()
+        _lib.check(L.tpx_fp8_tc_packed_bytes(N, K, int(other is not None), ctypes.byref(wb), ctypes.byref(sb)))
+        dev = self.codes.device
+        wq = torch.empty(wb.value, dtype=torch.uint8, device=dev)
+        sfa = torch.empty(sb.value, dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(L.tpx_repack_fp8_tc(self.codes.data_ptr(), other.codes.data_ptr() if other is not None else None, N, K,
+                                           wq.data_ptr(), sfa.data_ptr(), _lib.stream()))
+        if other is None:
+            self._packed_tc = (wq, sfa)
+        else:
+            self._pair_tc = (other, (wq, sfa))
+        return (wq, sfa)
+
+    def prepare(self, drop_interchange=False, pair_with=None):
+        self.packed_tc(pair_with)
+        if drop_interchange:
+            self.codes = self.codes.new_empty(0)
+            if pair_with is not None:
+                pair_with.codes = pair_with.codes.new_empty(0)
+        return self
+
+    def state(self):
+        st = _state(self)
+        st["fp8"] = self.fmt
+        return st
+
+
+def to_fp8_weight(w, weight_dtype):
+    """[N, K] weight (any floating dtype, or already 8-bit) -> Fp8Weight in the named format ("bfloat8" | "hfloat8" or a
+    torch float8 dtype). The values pass through bf16 first, as the reference's do (the layer dtype)."""
+    dt = FP8_DTYPES.get(weight_dtype, weight_dtype) if isinstance(weight_dtype, str) else weight_dtype
+    if dt not in (torch.float8_e4m3fn, torch.float8_e5m2):
+        raise _lib.TpxError(f"unknown 8-bit floating-point format {weight_dtype}")
+    _lib.require_cuda(w, "weight")
+    if w.dtype != dt:
+        w = w.to(torch.bfloat16).to(dt)
+    return Fp8Weight(w)
 
 
 def _prepare(self, drop_interchange=False, pair_with=None):

@@ -52,6 +52,11 @@ _SIGS = {
     "tpx_qlinear_mxfp4_tc_static": (c_int, [c_vp, c_vp, c_int, c_vp, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp, c_f32, c_vp, c_vp]),
     "tpx_rmsnorm": (c_int, [c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_vp, c_vp]),
     "tpx_layernorm": (c_int, [c_vp, c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_vp, c_vp]),
+    "tpx_fp8_tc_packed_bytes": (c_int, [c_i64, c_i64, c_int, ctypes.POINTER(c_sz), ctypes.POINTER(c_sz)]),
+    "tpx_repack_fp8_tc": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "tpx_qlinear_fp8_tc_scratch_bytes": (c_sz, [c_i64, c_i64, c_i64, c_int]),
+    "tpx_qlinear_fp8_tc": (c_int, [c_vp, c_vp, c_int, c_int, c_vp, c_vp, c_int, c_f32, c_i64, c_i64, c_i64, c_vp, c_int, c_vp, c_vp, c_f32,
+                                   c_vp, c_vp, c_sz, c_vp]),
     "tpx_llama_layer_attention": (c_int, [c_vp, c_vp, c_vp]),
     "tpx_llama_layer_mlp": (c_int, [c_vp, c_vp, c_vp]),
     "tpx_rope_kv_update_gptj": (c_int, [c_vp, c_vp, c_vp] + [c_i64] * 10 + [c_vp] * 6 + [c_vp]),

@@ -306,6 +306,28 @@ __global__ void repack_mxfp4_tc_kernel(const uint8_t* __restrict__ codes, const 
   }
 }
 
+// 8-bit floating-point weights (E4M3 or E5M2 bytes, plain [N][K]) -> the same tiling with 128-byte rows:
+//   one weight : wq [TN][KS][128 rows][128 bytes]     gate/up : wq [TN][KS][2][128 rows][128 bytes]
+// and scale blocks of the constant 1.0 (these formats carry no scales). One thread per 16 bytes of wq.
+__global__ void repack_fp8_tc_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ w2, int64_t N, int64_t K, int64_t KS,
+                                     uint8_t* __restrict__ wq, uint8_t* __restrict__ sfa) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t TN = (N + 127) / 128;
+  const int NW = w2 ? 2 : 1;
+  if (idx < TN * KS * NW * 1024) {
+    int64_t tile = idx / 1024;  // (tn*KS + ks)*NW + d
+    int d = (int)(tile % NW);
+    int64_t tk = tile / NW;
+    int r = (int)((idx % 1024) / 8), c = (int)(idx % 8);
+    int64_t n = (tk / KS) * 128 + r, k = (tk % KS) * 128 + 16 * c;
+    const uint8_t* src = d ? w2 : w;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (n < N && k < K) v = *reinterpret_cast<const uint4*>(src + n * K + k);  // K is a multiple of 16
+    reinterpret_cast<uint4*>(wq)[idx] = v;
+  }
+  if (idx < TN * KS * NW * 32) reinterpret_cast<uint4*>(sfa)[idx] = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+}
+
 // ---------------------------------------------------------------- the GEMM kernel
 // TOK tokens per tile, DUAL = gate/up pair, UKS = k steps (of 128) per pipeline unit.
 template <int TOK, bool DUAL, int UKS>
@@ -399,7 +421,9 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       auto fetch_w = [&](int s, int tn, int ks) {  // weight tiles and their scale blocks: independent of the split kernel
         const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
         const uint32_t bar = tc_smem_u32(&bar_full[s]);
-        tc_mbar_expect_tx(bar, ((TPX_DBG(p) & 2) ? C::TX - C::A_TILES * C::A_TX : C::TX) - ((TPX_DBG(p) & 128) ? C::X_ROWS * 128 + UKS * C::SFB_PER * 512 : 0));
+        // 8-bit weights arrive byte for byte; packed 4-bit ones are accounted with their packed size
+        const int w_tx = C::A_TILES * (p.wfmt ? C::A_BYTES : C::A_TX);
+        tc_mbar_expect_tx(bar, ((TPX_DBG(p) & 2) ? C::TX - C::A_TILES * C::A_TX : C::TX - C::A_TILES * C::A_TX + w_tx) - ((TPX_DBG(p) & 128) ? C::X_ROWS * 128 + UKS * C::SFB_PER * 512 : 0));
         const int wtile = (tn * p.KS + ks) * C::A_TILES;  // first weight tile of the unit
         if (!(TPX_DBG(p) & 2)) {
 #pragma unroll
@@ -462,7 +486,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       // instruction descriptor: A = E2M1 (5), B = E4M3 (0), both K-major, N = TOK, UE8M0 scales, M = 128
-      const uint32_t idesc0 = (5u << 7) | (0u << 10) | ((uint32_t)(C::NCOL >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
+      const uint32_t idesc0 = ((p.wfmt == 0 ? 5u : p.wfmt == 1 ? 0u : 1u) << 7) | (0u << 10) | ((uint32_t)(C::NCOL >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
       int ks = ks0;
       uint32_t acc_phase = 0;
       bool fresh = true;  // next MMA starts a new accumulation
@@ -1059,8 +1083,9 @@ extern "C" size_t tpx_qlinear_mxfp4_tc_scratch_bytes(int64_t M, int64_t N, int64
 
 static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M, int64_t N, int64_t K,
                   const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y,
-                  void* scratch, size_t scratch_bytes, void* stream, int kind, const TcNorm* norm = nullptr) {
+                  void* scratch, size_t scratch_bytes, void* stream, int kind, const TcNorm* norm = nullptr, int wfmt = 0) {
   TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear_mxfp4_tc: bad shape");
+  TPX_REQUIRE(wfmt == 0 || kind == 0, TPX_ERR_ARG, "qlinear_tc: 8-bit weights run on the 128-row kernel only");
   if (M == 0) return TPX_OK;
   TPX_REQUIRE(wq && sfa && x && y, TPX_ERR_ARG, "qlinear_mxfp4_tc: null pointer");
   TPX_REQUIRE(!(pair && mul_in), TPX_ERR_ARG, "qlinear_mxfp4_tc: gate/up pair and mul_in are exclusive");
@@ -1117,7 +1142,8 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   CUtensorMap mw, mx;
   // weight: 64-byte rows of 128 codes, 256 rows (two tiles) per request; activation terms: 128-byte rows
   int rc;
-  rc = tc_make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, (uint64_t)pl.TN * pl.KS * (dual ? 2 : 1) * 128, 64, (dual ? 2 : 1) * pl.uks >= 2 ? 256 : 128);
+  rc = tc_make_map(&mw, wfmt ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, (uint64_t)pl.TN * pl.KS * (dual ? 2 : 1) * 128,
+                   wfmt ? 128 : 64, (dual ? 2 : 1) * pl.uks >= 2 ? 256 : 128);
   if (rc) return rc;
   rc = tc_make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, terms, (uint64_t)pl.Mpad * pl.KS * 2, 128, (uint32_t)pl.xbox);
   if (rc) return rc;
@@ -1128,6 +1154,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = pl.TM; p.act = act; p.whole_tiles = pl.whole_tiles; p.cluster = pl.cluster; p.tl = g_tc_timeline;
   p.dbg = knobs().dbg;
+  p.wfmt = wfmt;
   p.pf = knobs().tc_pf;  // off by default, see above (prefill shapes: 842 against 838 TFLOP/s)
   if (knobs().tc_cluster == 0) p.cluster = 1;
   if (dual) {
@@ -1149,6 +1176,41 @@ extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int p
                                     int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,
                                     float res_scale, uint16_t* y, void* scratch, size_t scratch_bytes, void* stream) {
   return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, tc_kind(M, N, K, pair != 0));
+}
+
+// ---------------------------------------------------------------- 8-bit floating-point weights (E4M3 / E5M2, no scales)
+extern "C" int tpx_fp8_tc_packed_bytes(int64_t N, int64_t K, int pair, size_t* wq_bytes, size_t* sfa_bytes) {
+  TPX_REQUIRE(N > 0 && K > 0 && N % 32 == 0 && K % 64 == 0, TPX_ERR_ARG, "fp8_tc_packed_bytes: needs N %% 32 == 0 and K %% 64 == 0");
+  size_t tiles = (size_t)((N + 127) / 128) * tc_padded_ks(K, pair != 0) * (pair ? 2 : 1);
+  if (wq_bytes) *wq_bytes = tiles * 16384;
+  if (sfa_bytes) *sfa_bytes = tiles * 512;
+  return TPX_OK;
+}
+
+extern "C" int tpx_repack_fp8_tc(const uint8_t* w, const uint8_t* w2, int64_t N, int64_t K, uint8_t* wq, uint8_t* sfa, void* stream) {
+  TPX_REQUIRE(w && wq && sfa, TPX_ERR_ARG, "repack_fp8_tc: null pointer");
+  TPX_REQUIRE(N % 32 == 0 && K % 64 == 0, TPX_ERR_ARG, "repack_fp8_tc: needs N %% 32 == 0 and K %% 64 == 0");
+  TPX_REQUIRE((((uintptr_t)w | (uintptr_t)w2 | (uintptr_t)wq | (uintptr_t)sfa) & 15) == 0, TPX_ERR_ARG, "repack_fp8_tc: misaligned pointer");
+  const bool pair = w2 != nullptr;
+  int64_t KS = tc_padded_ks(K, pair);
+  int64_t total = ((N + 127) / 128) * KS * (pair ? 2 : 1) * 1024;
+  repack_fp8_tc_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(w, w2, N, K, KS, wq, sfa);
+  TPX_LAUNCH_OK();
+  return TPX_OK;
+}
+
+extern "C" size_t tpx_qlinear_fp8_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int pair) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  return tc_scratch_need(M, N, K, pair != 0, 0);
+}
+
+extern "C" int tpx_qlinear_fp8_tc(const uint8_t* wq, const uint8_t* sfa, int fmt, int pair, const uint16_t* x, const void* gamma,
+                                  int gamma_is_f32, float eps, int64_t M, int64_t N, int64_t K, const uint16_t* bias, int act,
+                                  const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y, void* scratch,
+                                  size_t scratch_bytes, void* stream) {
+  TPX_REQUIRE(fmt == TPX_FP8_E4M3 || fmt == TPX_FP8_E5M2, TPX_ERR_ARG, "qlinear_fp8_tc: unknown weight format %d", fmt);
+  TcNorm nm = {gamma, gamma_is_f32, eps};
+  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, 0, gamma ? &nm : nullptr, fmt);
 }
 
 extern "C" int tpx_rmsnorm_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, const void* gamma,

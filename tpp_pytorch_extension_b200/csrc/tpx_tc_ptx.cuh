@@ -31,6 +31,7 @@ struct TcParams {
   unsigned long long* tl;  // optional per-CTA timeline (8 globaltimer stamps each), null in normal use
   int cluster;          // CTAs per thread-block cluster that share one output tile along K (1: none)
   int pf;               // units prefetched into L2 ahead of the shared-memory stages
+  int wfmt;             // weight operand of the 128-row kernel: 0 = packed E2M1 (unpacked by the copy), 1 = E4M3 bytes, 2 = E5M2 bytes
   int dbg;              // timing-experiment knobs, honoured only by a -DTPX_DEBUG build (results are then wrong): 1 = skip MMAs,
                         // 2 = skip weight copies, 128 = skip activation copies; packed-fp4 kernel: 16 = skip scale-factor
                         // copies, 32 = MMA thread issues them

@@ -106,7 +106,10 @@ def ShardLinear(m, dim, rank, size, block_size=1):
 
 def quantize_weight(w, weight_dtype, bk=16, bc=64):
     """What FixLinear does to one nn.Linear weight (llm_common.py:437-510): block as [N/bk, K/bc, bc/2, bk, 2]
-    in bf16, then remap_and_quantize_* by weight_dtype ("mxfp4" | "qint8")."""
+    in bf16, then remap_and_quantize_* by weight_dtype ("mxfp4" | "qint8"); "bfloat8" / "hfloat8" cast the bf16 weight to
+    E5M2 / E4M3 (the reference's `.to(weight_dtype)`, llm_common.py:519-522)."""
+    if weight_dtype in qtype.FP8_DTYPES or weight_dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        return qtype.to_fp8_weight(w, weight_dtype)
     wb = block_weight(w.to(torch.bfloat16), bk, bc)
     if weight_dtype == "mxfp4":
         return qtype.remap_and_quantize_mxfp4(wb)
