@@ -335,6 +335,8 @@ typedef struct {
   size_t scratch_bytes;
   void* attn_scratch;
   size_t attn_scratch_bytes;
+  void* handoff;            /* NULL, or a zero-initialised buffer (1024-byte aligned) of handoff_bytes that only these calls */
+  size_t handoff_bytes;     /* write: at most 64 tokens pass from gate/up to down through it (2 * 64 * FF + FF * 4 bytes suffice) */
 } TpxLlamaLayerIO;
 int tpx_llama_layer_attention(const TpxLlamaLayer* layer, const TpxLlamaLayerIO* io, void* stream);
 int tpx_llama_layer_mlp(const TpxLlamaLayer* layer, const TpxLlamaLayerIO* io, void* stream);

@@ -312,6 +312,39 @@ def fp8_dequant(codes, fmt):
     return fp8_to_f32_table(fmt)[np.asarray(codes, dtype=np.uint8)]
 
 
+# --------------------------------------------------------------------------- ternary ("qint2") weights
+def remap_and_quantize_qint2(w_bf16, block_size=256):
+    """remap_and_quantize_qint2_intlv (src/csrc/qtypes.cpp:1004-1073) on a plain bf16 weight [N, K] (bits), N a multiple
+    of 32 (the reference's K2 = 8, K3 = 4 case): per (row, block) scale = max |w| in fp32 (at least 1e-8), code =
+    round-half-even(w / scale) clamped to [-1, 1] with -1 stored as 2; four row groups of eight rows share a byte.
+    Returns (packed uint8 [N/32, K/B, B/4, 8, 4], scales fp32 [N/32, K/B, 32, 1], B). Parity unpinned: the reference holds
+    no vectors for this quantizer and cannot be built here; the restatement follows its tensor operations one by one."""
+    w = bf16_to_f32(np.asarray(w_bf16, dtype=np.uint16))
+    N, K = w.shape
+    assert N % 32 == 0 and K % 4 == 0
+    B = block_size
+    if K % B:
+        B = next((q for q in (4096, 2048, 1024, 512, 256, 128, 64) if block_size > q and K % q == 0), 64)
+    K1, C1 = N // 32, K // B
+    wb = w.reshape(K1, 32, C1, B).transpose(0, 2, 1, 3)                      # [K1, C1, 32, B]
+    scales = np.maximum(np.abs(wb).max(-1, keepdims=True).astype(np.float32), np.float32(1e-8))
+    q = np.clip(np.rint((wb / scales).astype(np.float32)), -1.0, 1.0).astype(np.int8)
+    codes = np.where(q < 0, 2, q).astype(np.uint8)
+    c = codes.reshape(K1, C1, 4, 8, B // 4, 4).transpose(2, 0, 1, 4, 3, 5)   # [K3, K1, C1, C2, K2, C3]
+    packed = c[0] | (c[1] << 2) | (c[2] << 4) | (c[3] << 6)
+    return np.ascontiguousarray(packed), np.ascontiguousarray(scales), B
+
+
+def qint2_dequant_plain(packed, scales, block_size):
+    """fp32 [N, K] from the carrier of remap_and_quantize_qint2."""
+    K1, C1, C2, K2, C3 = packed.shape
+    parts = np.stack([(packed >> (2 * k3)) & 3 for k3 in range(4)], 0).astype(np.int8)  # [K3, K1, C1, C2, K2, C3]
+    q = np.where(parts == 2, -1, parts).astype(np.float32)
+    q = q.transpose(1, 0, 4, 2, 3, 5).reshape(K1, 32, C1, C2 * C3)                       # [K1, (K3 K2), C1, B]
+    w = q * scales.reshape(K1, C1, 32).transpose(0, 2, 1)[..., None]
+    return np.ascontiguousarray(w.reshape(K1 * 32, C1 * block_size).astype(np.float32))
+
+
 # --------------------------------------------------------------------------- linear
 def qlinear(x_bf16, wd, bias=None, mul_in=None, res=None, res_scale=1.0, act=ACT_NONE, ref_rounding=False):
     x = _c(x_bf16, np.uint16)

@@ -253,6 +253,43 @@ def test_layer_as_two_c_calls_equals_the_kernel_by_kernel_path(cuda):
     assert_no_kernel_error()
 
 
+def test_gate_up_hands_its_output_to_down_as_activation_terms(cuda):
+    """With at most 64 tokens (by default: 33 to 64) tpx_llama_layer_mlp lets the gate/up kernel's epilogue write the activation terms the down
+    projection reads (no split kernel in between) when both kernels chosen for the shapes can: an MLP of the Llama-3-8B
+    width (112 whole gate/up tiles). Same arithmetic on the same bf16 values: outputs bit-identical to TPX_HANDOFF=0, with
+    one launch fewer per layer call; covers both producers (packed-fp4 kernel up to 32 tokens, wide kernel beyond) and
+    both consumers (wide kernel up to 16 tokens, 128-row kernel beyond)."""
+    from tests.gpu_util import knob_env
+    from tpp_pytorch_extension_b200 import _lib
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    from tpp_pytorch_extension_b200._C._tpp_attn import TppCache
+    rng = np.random.default_rng(31)
+    D, Nq, Nkv, H, FF, MP = 512, 4, 2, 64, 14336, 64
+    names = {"q": (Nq * H, D), "k": (Nkv * H, D), "v": (Nkv * H, D), "o": (D, Nq * H), "gate": (FF, D), "up": (FF, D), "down": (D, FF)}
+    qt = {nm: make_qweight(rng, n, k, "mxfp4", cuda, std=0.05)[0] for nm, (n, k) in names.items()}
+    g1 = to_dev_bf16(O.f32_to_bf16(1 + 0.1 * rng.standard_normal(D).astype(np.float32)), cuda)
+    g2 = to_dev_bf16(O.f32_to_bf16(1 + 0.1 * rng.standard_normal(D).astype(np.float32)), cuda)
+    ep = torch.from_numpy(O.rope_table(MP, H, 1e4)).to(cuda)
+    layer = F.LlamaDecoderLayer([g1, qt["q"], qt["k"], qt["v"], qt["o"], g2, qt["gate"], qt["up"], qt["down"], ep], 0, 1e-5, H, MP, H)
+    assert layer._c_level_ok()
+    for B in (1, 3, 16, 17, 32, 33, 64, 5):  # 5 after 64: rows of the buffer beyond the live tokens hold older terms
+        hs = to_dev_bf16(O.randn_bf16(rng, (B, 1, D)), cuda)
+        pos = torch.zeros((1, 1), dtype=torch.int64, device=cuda)
+        res = {}
+        for mode in ("1", "0"):
+            with knob_env(TPX_HANDOFF=mode, TPX_HANDOFF_MIN_TOKENS=1):  # by default only 33 to 64 tokens are handed over
+                cache = TppCache()
+                am = cache.align_and_invert_mask(torch.ones((B, 1), device=cuda))
+                layer.forward([hs, am, pos], cache, True)  # warm: buffers, maps
+                cache = TppCache()
+                c0 = _lib.lib().tpx_launch_count()
+                out = layer.forward([hs, am, pos], cache, True)[0].clone()
+                res[mode] = (out, _lib.lib().tpx_launch_count() - c0)
+        assert torch.equal(res["1"][0], res["0"][0]), B
+        assert res["1"][1] == res["0"][1] - 1, (B, res["1"][1], res["0"][1])
+    assert_no_kernel_error()
+
+
 def test_qwen2_layer_has_qkv_bias(cuda):
     """Qwen2DecoderLayer = the Llama block plus q/k/v biases (src/csrc/llm/fused_llm_infer.cpp:1289-1510)."""
     from tpp_pytorch_extension_b200._C import _fused_llm_infer as F

@@ -353,6 +353,12 @@ def _cat_q(ws):
         if any(w.kind != 3 or w.fmt != w0.fmt or w.shape[1] != w0.shape[1] for w in ws):
             raise _lib.TpxError("fused q/k/v: weights must share format and in-features")
         return Fp8Weight(torch.cat([w.codes for w in ws], 0).view(w0.dtype))
+    from ._qtype import QInt2Tensor
+    if isinstance(w0, QInt2Tensor):
+        if any(not isinstance(w, QInt2Tensor) or (w.block_size, w.shape[1:]) != (w0.block_size, w0.shape[1:]) for w in ws):
+            raise _lib.TpxError("fused q/k/v: weights must share quantization and in-features")
+        codes = torch.cat([w.codes for w in ws], 0)
+        return QInt2Tensor(codes, torch.cat([w.scales for w in ws], 0), (codes.shape[0],) + tuple(w0.shape[1:]), w0.block_size)
     for w in ws[1:]:
         if (w.kind, w.block_size, w.shape[1:]) != (w0.kind, w0.block_size, w0.shape[1:]):
             raise _lib.TpxError("fused q/k/v: weights must share quantization and in-features")
@@ -547,6 +553,9 @@ class LlamaDecoderLayer:
         io.out = out.data_ptr()
         io.scratch, io.scratch_bytes = sc.data_ptr(), sc.numel()
         io.attn_scratch, io.attn_scratch_bytes = _lib.ptr(asc), (asc.numel() if asc is not None else 0)
+        if T <= 64 and _opt("TPX_HANDOFF", "1") != "0":  # gate/up hands its output to down as activation terms
+            hb = _lib.handoff_buffer(2 * 64 * FF + 4 * FF + 2048, dev)
+            io.handoff, io.handoff_bytes = hb.data_ptr(), hb.numel()
         st = _lib.stream()
         world = get_pg_size()
         rc = lib.tpx_llama_layer_attention(ctypes.byref(L), ctypes.byref(io), st)

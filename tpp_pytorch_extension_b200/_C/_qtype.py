@@ -404,6 +404,119 @@ def remap_and_quantize_qint8(t, block_size=None):
     return QTensor(q, scales, (K1, C // B, B // 4, K2, 4), kPerBlockAffine, B)
 
 
+class QInt2Tensor(QTensor):
+    """Carrier of remap_and_quantize_qint2_intlv (src/csrc/qtypes.cpp:1004-1073): ternary codes (0, +1, and 2 for -1), four
+    to a byte, with one fp32 scale per output row and block of in-features. `codes` is uint8 [K1, C1, C2, K2, 4]: the
+    byte at (k1, c1, c2, k2, c3) holds, in bit pairs 2*k3, the codes of rows 32*k1 + 8*k3 + k2 (K2 = 8, four row groups
+    interleaved) at column c1*B + 4*c2 + c3; `scales` is fp32 [K1, C1, 32, 1]; the logical shape is [K1, C1, C2, 32, 4].
+    The reference multiplies such weights through the same int8 GEMM class as qint8 (TppBlockedQInt8LinearW,
+    src/csrc/fused_gemm.h:1531-1535): here the codes are expanded once to the int8 carrier (values -1, 0, +1, same scales and
+    block size) and run on the int8 kernels, so the weight streams at one byte per element."""
+
+    def __init__(self, codes, scales, shape, block_size):
+        super().__init__(codes, scales, shape, kPerBlockAffine, block_size)
+        self._twin = None
+
+    @property
+    def dtype(self):
+        return torch.quint2x4
+
+    def plain_codes(self):
+        """int8 [N, K] with values -1, 0, +1."""
+        K1, C1, C2, R, C3 = self.shape
+        K2 = R // 4
+        c = self.codes.view(K1, C1, C2, K2, C3)
+        parts = [((c >> (2 * k3)) & 3) for k3 in range(4)]          # each [K1, C1, C2, K2, C3]
+        q = torch.stack(parts, 3).to(torch.int8)                     # [K1, C1, C2, K3, K2, C3]
+        q = torch.where(q == 2, torch.full_like(q, -1), q)
+        return q.permute(0, 3, 4, 1, 2, 5).reshape(K1 * R, C1 * C2 * C3).contiguous()
+
+    def plain_scales(self):
+        """fp32 [N, K / block_size]."""
+        K1, C1, C2, R, C3 = self.shape
+        return self.scales.view(K1, C1, R).permute(0, 2, 1).reshape(K1 * R, C1).contiguous()
+
+    def dequantize(self):
+        """fp32 [N, K] (plain, not blocked)."""
+        B = self.block_size
+        return (self.plain_codes().float().view(self.out_features, -1, B) * self.plain_scales().unsqueeze(-1)).view(self.out_features, -1)
+
+    def as_int8(self):
+        """The same weight in the int8 carrier of remap_and_quantize_qint8 (16 rows per group), built once."""
+        if self._twin is None:
+            if self.codes.numel() == 0:
+                raise _lib.TpxError("the interchange tensors of this weight were dropped before it was expanded")
+            N, K, B = self.out_features, self.in_features, self.block_size
+            q = self.plain_codes().view(N // 16, 16, K // B, B // 4, 4).permute(0, 2, 3, 1, 4).contiguous()
+            sc = self.plain_scales().view(N // 16, 16, K // B).permute(0, 2, 1).contiguous().view(N // 16, K // B, 1, 16)
+            self._twin = QTensor(q, sc, (N // 16, K // B, B // 4, 16, 4), kPerBlockAffine, B)
+        return self._twin
+
+    def packed(self, drop_interchange=False):
+        return self.as_int8().packed(drop_interchange)
+
+    def packed_i8tc(self):
+        return self.as_int8().packed_i8tc()
+
+    def packed_tc(self, other=None):
+        raise _lib.TpxError("the MXFP4 tensor-core path takes MXFP4 weights")
+
+    def prepare(self, drop_interchange=False, pair_with=None):
+        self.as_int8().prepare(drop_interchange, pair_with.as_int8() if pair_with is not None else None)
+        if drop_interchange:
+            self.codes = self.codes.new_empty(0)
+            if pair_with is not None:
+                pair_with.codes = pair_with.codes.new_empty(0)
+        return self
+
+    def state(self):
+        raise _lib.TpxError("packed checkpoints of qint2 weights are not supported")
+
+
+def qint2_block_size_used(C, own_block, block_size):
+    """Block size remap_and_quantize_qint2_intlv ends up with (src/csrc/qtypes.cpp:1033-1044): the requested one if it
+    divides the in-features; else the largest power of two from 4096 down to 64 below the request that does; else the
+    blocked tensor's own inner block."""
+    if C % block_size == 0:
+        return block_size
+    qbs = 4096
+    while qbs >= 64:
+        if block_size > qbs and C % qbs == 0:
+            return qbs
+        qbs //= 2
+    return own_block
+
+
+def remap_and_quantize_qint2_intlv(t, block_size=None):
+    """src/csrc/qtypes.cpp:1004-1073 for a blocked bf16 weight [K1, C1, C2, K2, 2] on a CUDA device whose out-features
+    are a multiple of 32 (the K2 = 8, K3 = 4 case of the reference). `block_size` defaults to QINT2_BLOCK_SIZE (256).
+    The same sequence of tensor operations as the reference: per (row, block) scale = max |w| (at least 1e-8), code =
+    round(w / scale) clamped to [-1, 1], -1 stored as 2, four row groups interleaved into one byte."""
+    import os
+    t = _as_blocked_bf16(t)
+    if block_size is None:
+        block_size = int(os.environ.get("QINT2_BLOCK_SIZE", "256"))
+    k1, c1, c2, k2, c3 = t.shape
+    N = k1 * k2
+    if N % 32:
+        raise _lib.TpxError("remap_and_quantize_qint2_intlv: out-features must be a multiple of 32")
+    w = t.permute(0, 3, 1, 2, 4).contiguous().view(N, -1)
+    C = w.shape[1]
+    if C % 4:
+        raise _lib.TpxError("remap_and_quantize_qint2_intlv: in-features must be a multiple of 4")
+    B = qint2_block_size_used(C, c2 * c3, int(block_size))
+    if B not in (64, 128, 256, 512):
+        raise _lib.TpxError(f"remap_and_quantize_qint2_intlv: block size {B} is not served by the int8 kernels (64, 128, 256, 512)")
+    K1, K2, K3, C1, C2, C3 = N // 32, 8, 4, C // B, B // 4, 4
+    wb = w.view(K1, K2 * K3, C1, B).permute(0, 2, 1, 3).contiguous()         # [K1, C1, 32, B]
+    scales = wb.abs().amax(-1, keepdim=True).to(torch.float32).clamp_min_(1.0e-8)
+    q = torch.round(wb / scales).clamp_(-1.0, 1.0).to(torch.int8)
+    q = torch.where(q < 0, torch.full_like(q, 2), q).to(torch.uint8)
+    q = q.view(K1, C1, K3, K2, C2, C3).permute(2, 0, 1, 4, 3, 5).contiguous()  # [K3, K1, C1, C2, K2, C3]
+    packed = q[0] | (q[1] << 2) | (q[2] << 4) | (q[3] << 6)
+    return QInt2Tensor(packed.contiguous(), scales.contiguous(), (K1, C1, C2, K2 * K3, C3), B)
+
+
 def q_per_block_scales(q):
     return q.scales
 

@@ -106,7 +106,8 @@ class LlamaLayerIOStruct(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int64) for n in ("B", "S", "Bpos", "Spad", "offset", "capacity")] + \
                [(n, ctypes.c_void_p) for n in ("x", "pos", "mask", "dev_len", "kc", "vc", "k_pages", "v_pages", "qkv", "q", "ctx", "so",
                                                  "inter", "out", "scratch")] + \
-               [("scratch_bytes", ctypes.c_size_t), ("attn_scratch", ctypes.c_void_p), ("attn_scratch_bytes", ctypes.c_size_t)]
+               [("scratch_bytes", ctypes.c_size_t), ("attn_scratch", ctypes.c_void_p), ("attn_scratch_bytes", ctypes.c_size_t),
+                ("handoff", ctypes.c_void_p), ("handoff_bytes", ctypes.c_size_t)]
 
 
 def check(rc):
@@ -199,6 +200,21 @@ def layer_workspace(nbytes, device):
         buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
         _layer_ws[key] = buf
     return buf
+
+
+_handoff = {}
+
+
+def handoff_buffer(nbytes, device):
+    """The buffer through which the gate/up kernel hands its output to the down projection as activation terms (decode
+    shapes): zero-initialised, written by those kernels only."""
+    key = (device.index, stream())
+    buf = _handoff.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(nbytes + 1024, dtype=torch.uint8, device=device)
+        _handoff[key] = buf
+    off = (-buf.data_ptr()) % 1024
+    return buf[off:off + nbytes]
 
 
 _aux = {}

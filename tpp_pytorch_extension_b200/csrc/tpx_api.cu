@@ -30,6 +30,7 @@ static void read_knobs() {
   g_knobs.tc4_occ = env("TPX_TC4_OCC", 1);
   g_knobs.tc_cluster = env("TPX_TC_CLUSTER", 1);
   g_knobs.tc_pf = env("TPX_TC_PF", 0);
+  g_knobs.handoff_min = env("TPX_HANDOFF_MIN_TOKENS", 33);
   g_knobs.tc_p = env("TPX_TC_P", -1);
   g_knobs.tc_p2 = env("TPX_TC_P2", -1);
   g_knobs.tc_p_rows = env("TPX_TC_P_ROWS", 1);

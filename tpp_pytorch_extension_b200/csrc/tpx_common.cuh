@@ -64,10 +64,10 @@ void count_launch();  // host-side tally behind tpx_launch_count()
 
 // Kernel-selection switches, read from the environment once (first use) and again on tpx_reload_options():
 // TPX_TC_WHOLE, TPX_TC_WIDE, TPX_TC_F4, TPX_TC_W4 (-1 = let the planner decide), TPX_TC_CLUSTER (0 = no cluster split-K),
-// TPX_TC_PF (L2 prefetch distance), TPX_ATTN_SPLITS (0 = cost model), TPX_ATTN_TC (0 = prefill attention on the mma.sync kernel). None of them changes a result. `dbg` carries
+// TPX_TC_PF (L2 prefetch distance), TPX_HANDOFF_MIN_TOKENS (fewest tokens at which gate/up hands its output to down as terms), TPX_ATTN_SPLITS (0 = cost model), TPX_ATTN_TC (0 = prefill attention on the mma.sync kernel). None of them changes a result. `dbg` carries
 // TPX_TC_DBG and is always 0 unless the library was built with -DTPX_DEBUG.
 struct Knobs {
-  int tc_whole, tc_wide, tc_f4, tc_w4, tc4_occ, tc_cluster, tc_pf, tc_p, tc_p2, tc_p_uks, tc_p_rows, attn_splits, attn_tc, dbg;
+  int tc_whole, tc_wide, tc_f4, tc_w4, tc4_occ, tc_cluster, tc_pf, handoff_min, tc_p, tc_p2, tc_p_uks, tc_p_rows, attn_splits, attn_tc, dbg;
 };
 const Knobs& knobs();
 

@@ -1081,6 +1081,16 @@ extern "C" size_t tpx_qlinear_mxfp4_tc_scratch_bytes(int64_t M, int64_t N, int64
   return tc_scratch_need(M, N, K, pair != 0, tc_kind(M, N, K, pair != 0));
 }
 
+// ---- hand-over between two decode-shaped linears (see TcEmit)
+static thread_local TcEmit g_emit_next = {}, g_pre_next = {};
+static thread_local bool g_emitted = false;
+namespace tpx {
+void tc_set_emit(const TcEmit& E) { g_emit_next = E; }
+void tc_set_pre(const TcEmit& E) { g_pre_next = E; }
+bool tc_emitted() { return g_emitted; }
+void tc_note_emitted(bool v) { g_emitted = v; }
+}  // namespace tpx
+
 static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M, int64_t N, int64_t K,
                   const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y,
                   void* scratch, size_t scratch_bytes, void* stream, int kind, const TcNorm* norm = nullptr, int wfmt = 0) {
@@ -1094,6 +1104,17 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   TPX_REQUIRE(((uintptr_t)wq & 31) == 0 && ((uintptr_t)sfa & 15) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)scratch & 255) == 0,
               TPX_ERR_ARG, "qlinear_mxfp4_tc: misaligned pointer");
   const bool dual = pair != 0;
+  // a hand-over announced for this call (consumed whatever happens)
+  const TcEmit emit = g_emit_next, pre = g_pre_next;
+  g_emit_next = {};
+  g_pre_next = {};
+  g_emitted = false;
+  TcNorm with_pre = {};
+  if (pre.terms) {
+    TPX_REQUIRE((kind == 0 || kind == 1) && !(norm && norm->gamma) && !wfmt && !dual, TPX_ERR_ARG, "qlinear_mxfp4_tc: this launch cannot take handed-over terms");
+    with_pre.pre = &pre;
+    norm = &with_pre;
+  }
   if (kind == 5) {
     TcParams b = {};
     b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act; b.tl = g_tc_timeline;
@@ -1118,6 +1139,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
     // no L2 prefetch ahead of the stages: this kernel's stages already hold 160-210 KB of packed weights per SM, and
     // prefetches issued at the start delay the first stage (gate/up, M = 8: 26.5 us without, 29.2 us with 8 units ahead)
     b.pf = knobs().tc_pf;
+    b.emit = emit;
     return tc4_run(wq, sfa, dual, x, M, N, K, b, scratch, scratch_bytes, (cudaStream_t)stream, norm);
   }
   if (kind == 1) {
@@ -1127,6 +1149,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
     // L2 prefetch ahead of the stages is off: with launches back to back it delays the first stage more than it helps
     // later ones (gate/up, M = 8: 23.4 us without, 25.3 us with 8 units ahead)
     b.pf = knobs().tc_pf;
+    b.emit = emit;
     return tcw_run(wq, sfa, dual, x, M, N, K, b, scratch, scratch_bytes, (cudaStream_t)stream, norm);
   }
   TcPlan pl = tc_plan(M, N, K, dual);
@@ -1135,7 +1158,13 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   cudaStream_t st = (cudaStream_t)stream;
   unsigned char* sc = reinterpret_cast<unsigned char*>(scratch);
   uint8_t *terms = sc + pl.off_terms, *sfb = sc + pl.off_sfb;
-  {
+  if (norm && norm->pre) {  // the previous linear's epilogue wrote the terms
+    const TcEmit& e = *norm->pre;
+    TPX_REQUIRE(e.TOK == pl.tok && e.UKS == pl.uks && e.KS == pl.KS && e.rowmap == 0, TPX_ERR_ARG,
+                "qlinear_mxfp4_tc: handed-over activation terms do not fit this launch");
+    terms = e.terms;
+    sfb = e.sfb;
+  } else {
     int rc0 = tc_launch_split(x, (int)M, (int)K, pl.Mpad, pl.KS, pl.tok, pl.uks, 0, terms, sfb, st, norm);
     if (rc0) return rc0;
   }
@@ -1155,6 +1184,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = pl.TM; p.act = act; p.whole_tiles = pl.whole_tiles; p.cluster = pl.cluster; p.tl = g_tc_timeline;
   p.dbg = knobs().dbg;
   p.wfmt = wfmt;
+  p.emit = {};
   p.pf = knobs().tc_pf;  // off by default, see above (prefill shapes: 842 against 838 TFLOP/s)
   if (knobs().tc_cluster == 0) p.cluster = 1;
   if (dual) {
@@ -1171,6 +1201,33 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
     default: return tc_launch<128, false, 2>(mw, mx, p, pl.grid, st);
   }
 }
+
+namespace tpx {
+int tc_handoff_plan(int64_t M, int64_t N, int64_t K, void* buf, size_t bytes, TcEmit* E) {
+  *E = {};
+  if (!buf || M < 1 || M > 64 || K % 128) return TPX_OK;
+  const int kind = tc_kind(M, N, K, false);
+  TcEmit e = {};
+  size_t tb = 0, sb = 0;
+  if (kind == 1) {
+    if (!tcw_handoff_layout(M, N, K, &e, &tb, &sb)) return TPX_OK;
+  } else if (kind == 0) {
+    const TcPlan pl = tc_plan(M, N, K, false);
+    if ((int64_t)pl.KS * 128 != K) return TPX_OK;
+    e.TOK = pl.tok; e.UKS = pl.uks; e.KS = pl.KS; e.rowmap = 0;
+    tb = (size_t)pl.Mpad * pl.KS * 256;
+    sb = (size_t)pl.TM * pl.KS * ((2 * pl.tok + 127) / 128) * 512;
+  } else {
+    return TPX_OK;
+  }
+  tb = (tb + 1023) & ~(size_t)1023;
+  if (tb + sb > bytes || ((uintptr_t)buf & 1023)) return TPX_OK;
+  e.terms = reinterpret_cast<uint8_t*>(buf);
+  e.sfb = e.terms + tb;
+  *E = e;
+  return TPX_OK;
+}
+}  // namespace tpx
 
 extern "C" int tpx_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, int64_t M, int64_t N,
                                     int64_t K, const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res,

@@ -468,7 +468,11 @@ qlinear_tc4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             }
           }
           if (whole) {
-            if (n < p.N && tok0 + c0 < p.M) tc_finish16<DUAL>(p, tok0 + c0, n, r0, r1);
+            if (n < p.N && tok0 + c0 < p.M) {  // uniform over the warp (N is a multiple of 32)
+              float st[16];
+              tc_finish16<DUAL>(p, tok0 + c0, n, r0, r1, p.emit.terms ? st : nullptr);
+              if (p.emit.terms) tc_emit16_lanes(p.emit, tok0 + c0, p.M - tok0 - c0, n, st);
+            }
           } else if (p.cluster > 1) {  // partial of a cluster member: [weight][128 rows][TOK] fp32 at the start of its stages
             const uint32_t sp = smem_base + (uint32_t)((row * TOK + c0) * 4);
 #pragma unroll
@@ -668,6 +672,8 @@ int tc4_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x,
   p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = pl.TM;
   p.whole_tiles = pl.whole_tiles; p.cluster = pl.cluster;
+  if (!pl.whole_tiles) p.emit.terms = nullptr;  // only the whole-tile epilogue hands its output over
+  tc_note_emitted(p.emit.terms != nullptr);
   if (pl.occ == 2) {
     if (pair) return tc4_launch<16, true, 1, 2>(mw, mx, p, pl.grid, st);
     if (pl.tok == 16) return tc4_launch<16, false, 2, 2>(mw, mx, p, pl.grid, st);

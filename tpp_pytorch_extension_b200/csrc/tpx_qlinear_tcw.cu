@@ -50,7 +50,8 @@ struct TcwCfg {
 
 // Eight consecutive output features of one token: bias, activation, gate multiply, residual, one 16-byte store.
 template <bool DUAL>
-__device__ __forceinline__ void tcw_finish8(const TcParams& p, int tok, int n, const float (&v)[8], const float (&u)[8]) {
+__device__ __forceinline__ void tcw_finish8(const TcParams& p, int tok, int n, const float (&v)[8], const float (&u)[8],
+                                            float* stored = nullptr) {
   const size_t o = (size_t)tok * p.N + n;
   float x[8];
 #pragma unroll
@@ -108,6 +109,45 @@ __device__ __forceinline__ void tcw_finish8(const TcParams& p, int tok, int n, c
 #pragma unroll
   for (int i = 0; i < 4; i++) w[i] = (uint32_t)f32_to_bf16_bits(x[2 * i]) | ((uint32_t)f32_to_bf16_bits(x[2 * i + 1]) << 16);
   *reinterpret_cast<uint4*>(p.y + o) = make_uint4(w[0], w[1], w[2], w[3]);
+  if (stored) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      stored[2 * i] = bf16_bits_to_f32((uint16_t)(w[i] & 0xffff));
+      stored[2 * i + 1] = bf16_bits_to_f32((uint16_t)(w[i] >> 16));
+    }
+  }
+}
+
+// Hand-over of a finished 32-feature block to the next linear (TcEmit): lanes l and l ^ 16 hold one token's features
+// [n0, n0 + 32) as st[q][i] = feature n0 + 16 q + 8 half + i. Called by every lane of the warp; `live` lanes store.
+__device__ __forceinline__ void tcw_emit32(const TcEmit& E, int tok, int n0, int half, bool live, const float (&st)[2][8]) {
+  float am = 0.0f;
+#pragma unroll
+  for (int q = 0; q < 2; q++)
+#pragma unroll
+    for (int i = 0; i < 8; i++) am = fmaxf(am, fabsf(st[q][i]));
+  am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 16));
+  const int e = tc_emit_exp(__float_as_uint(am));
+  const float down = __uint_as_float((uint32_t)(127 - e) << 23);
+  if (!live) return;
+  const TcEmitAddr a = tc_emit_addr(E, tok, n0 >> 5);
+#pragma unroll
+  for (int q = 0; q < 2; q++) {
+    uint32_t h[2] = {0, 0}, l[2] = {0, 0};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      uint32_t hi, lo;
+      tc_emit_cvt2(st[q][2 * i], st[q][2 * i + 1], down, hi, lo);
+      h[i >> 1] |= hi << (16 * (i & 1));
+      l[i >> 1] |= lo << (16 * (i & 1));
+    }
+    *reinterpret_cast<uint2*>(a.hi + q * 16 + half * 8) = make_uint2(h[0], h[1]);
+    *reinterpret_cast<uint2*>(a.lo + q * 16 + half * 8) = make_uint2(l[0], l[1]);
+  }
+  if (half == 0) {
+    *a.sh = (uint8_t)(e + 127);
+    *a.sl = (uint8_t)(e + 127);
+  }
 }
 
 // p.TN counts the 256-feature tiles here (a gate/up pair: 128 + 128), p.TM is 1, p.KS the k units (UKS k steps of
@@ -326,6 +366,11 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             if (DUAL) tc_ld_x16(tmem + lane_base + 128 + (c0 + q) * 16, b[q]);
           }
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          float st[2][8];  // the stored values of this round, for the hand-over to the next linear
+#pragma unroll
+          for (int q = 0; q < 2; q++)
+#pragma unroll
+            for (int i = 0; i < 8; i++) st[q][i] = 0.0f;
 #pragma unroll
           for (int q = 0; q < 2; q++) {
             // lanes l and l ^ 16 hold the hi and lo sums of one token: each keeps 8 of the 16 columns and gets the
@@ -347,7 +392,7 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             const int col = (c0 + q) * 16 + half * 8;  // first of this thread's 8 accumulator columns
             if (whole) {
               const int n = DUAL ? tile * 128 + col : tile * 256 + col;
-              if (lane_live && tok < p.M && n < p.N) tcw_finish8<DUAL>(p, tok, n, v, u);
+              if (lane_live && tok < p.M && n < p.N) tcw_finish8<DUAL>(p, tok, n, v, u, p.emit.terms ? st[q] : nullptr);
             } else if (p.cluster > 1) {  // partial of a cluster member: [token][256 columns] fp32 at the start of its stages
               if (lane_live) {
                 const uint32_t sp = smem_base + (uint32_t)((tok * 256 + col) * 4);
@@ -366,6 +411,10 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                 __stcg(reinterpret_cast<float4*>(myslot + 128 + col) + 1, make_float4(u[4], u[5], u[6], u[7]));
               }
             }
+          }
+          if (whole && p.emit.terms) {  // uniform over the warp
+            const int n0 = (DUAL ? tile * 128 : tile * 256) + c0 * 16;
+            tcw_emit32(p.emit, tok, n0, half, lane_live && tok < p.M && n0 < p.N, st);
           }
         }
         tc_fence_before();
@@ -599,8 +648,17 @@ int tcw_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x,
               "qlinear_mxfp4_tc: y, bias, mul_in and res must be 16-byte aligned");
   unsigned char* sc = reinterpret_cast<unsigned char*>(scratch);
   uint8_t *terms = sc + pl.off_terms, *sfb = sc + pl.off_sfb;
-  int rc = tc_launch_split(x, (int)M, (int)K, pl.tokp, pl.KS, pl.tokp, 1, pl.tokp == 16 ? 2 : 1, terms, sfb, st, norm);
-  if (rc) return rc;
+  int rc;
+  if (norm && norm->pre) {  // the previous linear's epilogue wrote the terms
+    const TcEmit& e = *norm->pre;
+    TPX_REQUIRE(!norm->gamma && e.TOK == pl.tokp && e.UKS == 1 && e.KS == pl.KS && e.rowmap == (pl.tokp == 16 ? 2 : 1), TPX_ERR_ARG,
+                "qlinear_mxfp4_tc: handed-over activation terms do not fit this launch");
+    terms = e.terms;
+    sfb = e.sfb;
+  } else {
+    rc = tc_launch_split(x, (int)M, (int)K, pl.tokp, pl.KS, pl.tokp, 1, pl.tokp == 16 ? 2 : 1, terms, sfb, st, norm);
+    if (rc) return rc;
+  }
   CUtensorMap mw, mx;
   const uint64_t wrows = (uint64_t)(pair ? pl.TN * 2 : pl.tiles128) * pl.KS * 128;
   rc = tc_make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, wrows, 64, pair ? 256 : 128);
@@ -613,6 +671,8 @@ int tcw_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x,
   p.counters = reinterpret_cast<unsigned*>(sc);
   p.err = reinterpret_cast<unsigned*>(sc + kTcCounterBytes - 4);
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KS = pl.KU; p.TN = pl.TN; p.TM = 1; p.whole_tiles = pl.whole; p.cluster = pl.cluster;
+  if (!pl.whole) p.emit.terms = nullptr;  // only the whole-tile epilogue hands its output over
+  tc_note_emitted(p.emit.terms != nullptr);
   if (pair) {
     switch (pl.tokp) {
       case 16: return tcw_launch<16, true, 2>(mw, mx, p, wq, pl.tiles128, pl.KS, pl.grid, st);
@@ -625,6 +685,17 @@ int tcw_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x,
     case 32: return tcw_launch<32, false, 1>(mw, mx, p, wq, pl.tiles128, pl.KS, pl.grid, st);
     default: return tcw_launch<64, false, 1>(mw, mx, p, wq, pl.tiles128, pl.KS, pl.grid, st);
   }
+}
+
+// Split layout of this kernel as the consumer of a hand-over (one weight, K a whole number of 128-wide k steps).
+bool tcw_handoff_layout(int64_t M, int64_t N, int64_t K, TcEmit* E, size_t* terms_bytes, size_t* sfb_bytes) {
+  if (M < 1 || M > 64 || K % 128) return false;
+  const TcwPlan pl = tcw_plan(M, N, K, false);
+  if ((int64_t)pl.KS * 128 != K) return false;
+  E->TOK = pl.tokp; E->UKS = 1; E->KS = pl.KS; E->rowmap = pl.tokp == 16 ? 2 : 1;
+  *terms_bytes = (size_t)pl.KS * 2 * pl.tokp * 128;
+  *sfb_bytes = (size_t)pl.KS * 512;
+  return true;
 }
 
 }  // namespace tpx

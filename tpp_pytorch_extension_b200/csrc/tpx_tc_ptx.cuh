@@ -1,6 +1,8 @@
 // Inline PTX wrappers and shared parameter block of the tensor-core (tcgen05 + TMA) linear kernels.
 #pragma once
 #include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <stdlib.h>
 
 #include "tpx_common.cuh"
@@ -10,6 +12,15 @@ namespace tpx {
 constexpr unsigned kTcSpinLimit = 1u << 22;
 constexpr int kTcThreads = 192;
 constexpr size_t kTcCounterBytes = 64 * 1024;  // arrival counters (one per output tile) + error word at the end
+
+// Where the epilogue of one linear puts its output as the activation terms of the linear that consumes it (the layout
+// split_activations_kernel would produce from the bf16 output): the consumer then starts without a split kernel of its
+// own. TOK, UKS, KS and rowmap are the consumer's split parameters. terms == nullptr: nothing is emitted.
+struct TcEmit {
+  uint8_t* terms;
+  uint8_t* sfb;
+  int TOK, UKS, KS, rowmap;
+};
 
 struct TcParams {
   const uint8_t* sfa;   // [ceil(N/128)][KS][512] scale-factor blocks of W
@@ -31,6 +42,7 @@ struct TcParams {
   unsigned long long* tl;  // optional per-CTA timeline (8 globaltimer stamps each), null in normal use
   int cluster;          // CTAs per thread-block cluster that share one output tile along K (1: none)
   int pf;               // units prefetched into L2 ahead of the shared-memory stages
+  TcEmit emit;          // optional hand-over of the output to the next linear (decode-shaped gate/up launches)
   int wfmt;             // weight operand of the 128-row kernel: 0 = packed E2M1 (unpacked by the copy), 1 = E4M3 bytes, 2 = E5M2 bytes
   int dbg;              // timing-experiment knobs, honoured only by a -DTPX_DEBUG build (results are then wrong): 1 = skip MMAs,
                         // 2 = skip weight copies, 128 = skip activation copies; packed-fp4 kernel: 16 = skip scale-factor
@@ -182,10 +194,84 @@ __device__ __forceinline__ uint64_t tc_smem_desc_sbo(uint32_t saddr, uint32_t sb
 }
 
 // Epilogue of 16 consecutive tokens of one output feature n: bias, activation, gate multiply, residual, bf16 store.
+// ---- hand-over of an output to the next linear as activation terms (TcEmit)
+// Address of the first byte of 32-block kb of token tok in the hi and the lo term, and of its two scale bytes.
+struct TcEmitAddr {
+  uint8_t *hi, *lo, *sh, *sl;
+};
+__device__ __forceinline__ TcEmitAddr tc_emit_addr(const TcEmit& E, int tok, int kb) {
+  const int tm = tok / E.TOK, r = tok % E.TOK, ks = kb >> 2, j = kb & 3;
+  const size_t step = (size_t)tm * E.KS + ks;
+  int rh, rl, gh, gl;
+  size_t blk_off;
+  if (E.rowmap == 1) {
+    rh = gh = 32 * (r / 16) + (r % 16);
+    rl = gl = rh + 16;
+    blk_off = step * 512;
+  } else if (E.rowmap == 2) {
+    rh = 8 * (r / 4) + (r % 4);
+    rl = rh + 4;
+    gh = 32 * (r / 4) + (r % 4);
+    gl = gh + 16;
+    blk_off = step * 512;
+  } else {
+    rh = gh = r;
+    rl = gl = E.TOK + r;
+    blk_off = step * (size_t)((2 * E.TOK + 127) / 128) * 512;
+  }
+  TcEmitAddr a;
+  a.hi = E.terms + (step * 2 * E.TOK + rh) * 128 + j * 32;
+  a.lo = E.terms + (step * 2 * E.TOK + rl) * 128 + j * 32;
+  uint8_t* blk = E.sfb + blk_off;
+  a.sh = blk + (gh / 128) * 512 + (gh % 32) * 16 + ((gh % 128) / 32) * 4 + j;
+  a.sl = blk + (gl / 128) * 512 + (gl % 32) * 16 + ((gl % 128) / 32) * 4 + j;
+  return a;
+}
+// Block exponent of the split (block maximum to [128, 256): E4M3 holds up to 448) from the maximum's bit pattern.
+__device__ __forceinline__ int tc_emit_exp(uint32_t amax_bits) {
+  int e = 0;
+  if (amax_bits > 0u && amax_bits < 0x7f800000u) e = (int)((amax_bits >> 23) & 0xff) - 127 - 7;
+  return max(-127, min(127, e));
+}
+// Two values -> their hi and lo E4M3 bytes (low byte = first value), scaled by `down` = 2^-e.
+__device__ __forceinline__ void tc_emit_cvt2(float a, float b, float down, uint32_t& hi, uint32_t& lo) {
+  a *= down;
+  b *= down;
+  __nv_fp8x2_storage_t hs = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(hs, __NV_E4M3);
+  float ra = a - __half2float(__ushort_as_half(hr.x)), rb = b - __half2float(__ushort_as_half(hr.y));
+  __nv_fp8x2_storage_t ls = __nv_cvt_float2_to_fp8x2(make_float2(ra, rb), __NV_SATFINITE, __NV_E4M3);
+  hi = (uint32_t)hs;
+  lo = (uint32_t)ls;
+}
+// A warp whose lane l holds output feature n0 + l (n0 a multiple of 32) of 16 consecutive tokens: one 32-block per
+// token. xr: the outputs as stored (rounded to bf16). Called by all 32 lanes.
+__device__ __forceinline__ void tc_emit16_lanes(const TcEmit& E, int tok0, int live, int n, const float (&xr)[16]) {
+  const int lane = n & 31, kb = n >> 5;
+#pragma unroll
+  for (int j = 0; j < 16; j++) {
+    if (j < live) {
+      const uint32_t amax = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(xr[j])));
+      const int e = tc_emit_exp(amax);
+      const float down = __uint_as_float((uint32_t)(127 - e) << 23);
+      uint32_t hi, lo;
+      tc_emit_cvt2(xr[j], 0.0f, down, hi, lo);
+      const TcEmitAddr a = tc_emit_addr(E, tok0 + j, kb);
+      a.hi[lane] = (uint8_t)hi;
+      a.lo[lane] = (uint8_t)lo;
+      if (lane == 0) {
+        *a.sh = (uint8_t)(e + 127);
+        *a.sl = (uint8_t)(e + 127);
+      }
+    }
+  }
+}
+
 // Straight-line code over the 16 tokens (loads first, then arithmetic, then stores) so that the tokens' dependent
 // chains overlap; only the loads and stores are predicated on the token being inside M.
 template <bool DUAL>
-__device__ __forceinline__ void tc_finish16(const TcParams& p, int tok0, int n, const float (&v)[16], const float (&v2)[16]) {
+__device__ __forceinline__ void tc_finish16(const TcParams& p, int tok0, int n, const float (&v)[16], const float (&v2)[16],
+                                            float* stored = nullptr) {
   const int live = p.M - tok0;  // tokens tok0 .. tok0+live-1 exist
   const size_t o0 = (size_t)tok0 * p.N + n;
   const float b = p.bias ? bf16_bits_to_f32(p.bias[n]) : 0.0f;
@@ -226,8 +312,11 @@ __device__ __forceinline__ void tc_finish16(const TcParams& p, int tok0, int n, 
     for (int j = 0; j < 16; j++) x[j] += bf16_bits_to_f32(t[j]) * p.res_scale;
   }
 #pragma unroll
-  for (int j = 0; j < 16; j++)
-    if (j < live) p.y[o0 + (size_t)j * p.N] = f32_to_bf16_bits(x[j]);
+  for (int j = 0; j < 16; j++) {
+    const uint16_t bits = f32_to_bf16_bits(x[j]);
+    if (j < live) p.y[o0 + (size_t)j * p.N] = bits;
+    if (stored) stored[j] = bf16_bits_to_f32(bits);
+  }
 }
 
 // Epilogue of the many-token kernels: 16 consecutive tokens of output feature n from the accumulator values x (gate/up
@@ -304,7 +393,19 @@ struct TcNorm {  // optional RMSNorm applied to x on its way into the split (nul
   const void* gamma;
   int gamma_f32;
   float eps;
+  const TcEmit* pre = nullptr;  // the activation terms are already there (the previous linear's epilogue wrote them): no split
 };
+// Hand-over between two decode-shaped linears (at most 64 tokens), used by the layer calls. tc_handoff_plan fills E
+// with the split layout of the consumer y[M][N] = x[M][K] (one weight) inside buf, or leaves E->terms null when
+// that consumer's kernel takes another layout or K is padded. tc_set_emit: the next tpx_*_qlinear_mxfp4_tc call of this
+// host thread also writes its output as those terms if its kernel can (tc_emitted() tells); tc_set_pre: the next call
+// reads its activation from them instead of splitting x.
+int tc_handoff_plan(int64_t M, int64_t N, int64_t K, void* buf, size_t bytes, TcEmit* E);
+void tc_set_emit(const TcEmit& E);
+void tc_set_pre(const TcEmit& E);
+bool tc_emitted();
+void tc_note_emitted(bool v);
+bool tcw_handoff_layout(int64_t M, int64_t N, int64_t K, TcEmit* E, size_t* terms_bytes, size_t* sfb_bytes);
 int tc_launch_split(const uint16_t* x, int M, int K, int Mpad, int KS, int TOK, int UKS, int rowmap, uint8_t* terms, uint8_t* sfb,
                     cudaStream_t st, const TcNorm* norm = nullptr);
 int tc_launch_fixup(bool dual, const TcParams& p, int TOK, int grid, cudaStream_t st);

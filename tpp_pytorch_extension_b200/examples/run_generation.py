@@ -30,7 +30,7 @@ MODELS = {"llama2-7b": FL.LLAMA2_7B, "llama3-8b": FL.LLAMA3_8B, "llama2-70b": FL
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="llama3-8b", choices=sorted(MODELS))
-    ap.add_argument("--weight-dtype", default="mxfp4", choices=["mxfp4", "qint8", "bfloat16", "bfloat8", "hfloat8"])
+    ap.add_argument("--weight-dtype", default="mxfp4", choices=["mxfp4", "qint8", "qint2", "bfloat16", "bfloat8", "hfloat8"])
     ap.add_argument("--batch-size", type=int, default=1)
     ap.add_argument("--input-tokens", type=int, default=1024)
     ap.add_argument("--max-new-tokens", type=int, default=128)

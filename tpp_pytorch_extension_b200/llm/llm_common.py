@@ -115,6 +115,8 @@ def quantize_weight(w, weight_dtype, bk=16, bc=64):
         return qtype.remap_and_quantize_mxfp4(wb)
     if weight_dtype == "qint8":
         return qtype.remap_and_quantize_qint8(wb)
+    if weight_dtype == "qint2":
+        return qtype.remap_and_quantize_qint2_intlv(wb)
     if weight_dtype in ("bf16", "bfloat16", torch.bfloat16):
         return w.to(torch.bfloat16).contiguous()  # unquantized: the bf16 kernel reads the plain matrix
     raise ValueError(f"Unknown weight_dtype {weight_dtype}")
