@@ -81,3 +81,38 @@ def test_tiny_llama_matches_oracle(cuda):
     assert torch.equal(out_e, out_g)
     assert runner.last_graph is not None, "the decode step was not captured in a CUDA graph"
     assert_no_kernel_error()
+
+
+def test_generate_reuses_cache_and_recorded_step(cuda):
+    """generate() keeps its KV cache and the CUDA graph of the decode step for the next call of the same batch size that
+    fits the cache: prompts of other lengths and other padding then replay the same graph (the lengths live in device
+    memory). Tokens must equal those of a runner that records anew on every call; a larger batch or a longer request
+    starts a new session."""
+    from tpp_pytorch_extension_b200.llm import fused_llama_infer as FL
+    shape = FL.LlamaShape(2, 256, 4, 2, 512, 512, max_position_embeddings=256)
+    runner = FL.build_random_llama(shape, "mxfp4", cuda, seed=5, std=0.05)
+    g = torch.Generator(device="cpu").manual_seed(7)
+    prompts = [torch.randint(1, shape.vocab_size, (3, n), generator=g).to(cuda) for n in (40, 23, 57, 40)]
+    masks = [None, None, torch.ones(3, 57, dtype=torch.long, device=cuda), None]
+    masks[2][1, :9] = 0  # one left-padded sequence
+    runner.reuse_decode_graph = False
+    want = [runner.generate(p, 12, attention_mask=m) for p, m in zip(prompts, masks)]
+    runner.reuse_decode_graph = True
+    graphs = []
+    for p, m, w in zip(prompts, masks, want):
+        got = runner.generate(p, 12, attention_mask=m)
+        graphs.append(runner.last_graph)
+        assert torch.equal(got, w)
+    # the first call sized the cache for 52 tokens (+ the reference's 128 of slack): every later request fits
+    assert graphs[0] is not None and all(gr is graphs[0] for gr in graphs[1:])
+    # a request beyond the cache, and another batch size, record anew
+    long = runner.generate(prompts[0], 200)
+    assert runner.last_graph is not graphs[0] and long.shape == (3, 240)
+    runner.reuse_decode_graph = False
+    assert torch.equal(long, runner.generate(prompts[0], 200))
+    runner.reuse_decode_graph = True
+    two = runner.generate(prompts[1][:2], 12)
+    runner.reuse_decode_graph = False
+    assert torch.equal(two, runner.generate(prompts[1][:2], 12))
+    runner.release_session()
+    assert_no_kernel_error()

@@ -1095,7 +1095,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
                   const uint16_t* bias, int act, const uint16_t* mul_in, const uint16_t* res, float res_scale, uint16_t* y,
                   void* scratch, size_t scratch_bytes, void* stream, int kind, const TcNorm* norm = nullptr, int wfmt = 0) {
   TPX_REQUIRE(M >= 0 && N > 0 && K > 0, TPX_ERR_ARG, "qlinear_mxfp4_tc: bad shape");
-  TPX_REQUIRE(wfmt == 0 || kind == 0, TPX_ERR_ARG, "qlinear_tc: 8-bit weights run on the 128-row kernel only");
+  TPX_REQUIRE(wfmt == 0 || kind == 0 || kind == 1 || kind == 5, TPX_ERR_ARG, "qlinear_tc: 8-bit weights run on the kernels with 8-bit operand containers only");
   if (M == 0) return TPX_OK;
   TPX_REQUIRE(wq && sfa && x && y, TPX_ERR_ARG, "qlinear_mxfp4_tc: null pointer");
   TPX_REQUIRE(!(pair && mul_in), TPX_ERR_ARG, "qlinear_mxfp4_tc: gate/up pair and mul_in are exclusive");
@@ -1111,7 +1111,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
   g_emitted = false;
   TcNorm with_pre = {};
   if (pre.terms) {
-    TPX_REQUIRE((kind == 0 || kind == 1) && !(norm && norm->gamma) && !wfmt && !dual, TPX_ERR_ARG, "qlinear_mxfp4_tc: this launch cannot take handed-over terms");
+    TPX_REQUIRE((kind == 0 || kind == 1) && !(norm && norm->gamma) && !dual, TPX_ERR_ARG, "qlinear_mxfp4_tc: this launch cannot take handed-over terms");
     with_pre.pre = &pre;
     norm = &with_pre;
   }
@@ -1119,6 +1119,7 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
     TcParams b = {};
     b.bias = bias; b.mul_in = mul_in; b.res = res; b.res_scale = res_scale; b.y = y; b.act = act; b.tl = g_tc_timeline;
     b.dbg = knobs().dbg;
+    b.wfmt = wfmt;
     return tcp2_run(wq, sfa, dual, x, M, N, K, b, scratch, scratch_bytes, (cudaStream_t)stream, norm);
   }
   if (kind == 4) {
@@ -1148,8 +1149,9 @@ static int tc_run(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_
     b.dbg = knobs().dbg;
     // L2 prefetch ahead of the stages is off: with launches back to back it delays the first stage more than it helps
     // later ones (gate/up, M = 8: 23.4 us without, 25.3 us with 8 units ahead)
-    b.pf = knobs().tc_pf;
+    b.pf = wfmt ? 0 : knobs().tc_pf;
     b.emit = emit;
+    b.wfmt = wfmt;
     return tcw_run(wq, sfa, dual, x, M, N, K, b, scratch, scratch_bytes, (cudaStream_t)stream, norm);
   }
   TcPlan pl = tc_plan(M, N, K, dual);
@@ -1256,9 +1258,18 @@ extern "C" int tpx_repack_fp8_tc(const uint8_t* w, const uint8_t* w2, int64_t N,
   return TPX_OK;
 }
 
+// Kernel for 8-bit weights: the choice made for MXFP4 at this shape, among the kernels whose weight operand sits in
+// 8-bit containers (the packed-fp4 kernels become the wide kernel, the one-CTA many-token kernel the 128-row one).
+static int fp8_kind(int64_t M, int64_t N, int64_t K, bool pair) {
+  const int k = tc_kind(M, N, K, pair);
+  if (k == 2 || k == 3) return 1;
+  if (k == 4) return 0;
+  return k;
+}
+
 extern "C" size_t tpx_qlinear_fp8_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int pair) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  return tc_scratch_need(M, N, K, pair != 0, 0);
+  return tc_scratch_need(M, N, K, pair != 0, fp8_kind(M, N, K, pair != 0));
 }
 
 extern "C" int tpx_qlinear_fp8_tc(const uint8_t* wq, const uint8_t* sfa, int fmt, int pair, const uint16_t* x, const void* gamma,
@@ -1267,7 +1278,8 @@ extern "C" int tpx_qlinear_fp8_tc(const uint8_t* wq, const uint8_t* sfa, int fmt
                                   size_t scratch_bytes, void* stream) {
   TPX_REQUIRE(fmt == TPX_FP8_E4M3 || fmt == TPX_FP8_E5M2, TPX_ERR_ARG, "qlinear_fp8_tc: unknown weight format %d", fmt);
   TcNorm nm = {gamma, gamma_is_f32, eps};
-  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, 0, gamma ? &nm : nullptr, fmt);
+  return tc_run(wq, sfa, pair, x, M, N, K, bias, act, mul_in, res, res_scale, y, scratch, scratch_bytes, stream, fp8_kind(M, N, K, pair != 0),
+                gamma ? &nm : nullptr, fmt);
 }
 
 extern "C" int tpx_rmsnorm_qlinear_mxfp4_tc(const uint8_t* wq, const uint8_t* sfa, int pair, const uint16_t* x, const void* gamma,

@@ -290,7 +290,7 @@ qlinear_tcp2_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         }
         const uint32_t st = smem_base + (uint32_t)s * C::STAGE_BYTES;
         const uint32_t lbar = tc_mapa(tc_smem_u32(&bar_full[s]), 0u);  // the first CTA's barrier
-        if (crank == 0) tc_mbar_expect_tx(tc_smem_u32(&bar_full[s]), 2u * C::TX_CTA);
+        if (crank == 0) tc_mbar_expect_tx(tc_smem_u32(&bar_full[s]), 2u * (C::TX_CTA + (p.wfmt ? UKS * (128 * 128 - C::A_TX) : 0)));
         const uint32_t ssf = st + UKS * (C::A_BYTES + C::B_BYTES);
         const int ks0 = tn * KSS + ku * UKS;
         if (DUAL) {
@@ -335,7 +335,7 @@ qlinear_tcp2_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     // ------------------------------------------------------------ MMA issuer (first CTA only)
     if (lane == 0 && crank == 0) {
       // instruction descriptor: A = E2M1 (5), B = E4M3 (0), both K-major, N = 256, UE8M0 scales, M = 256 over the pair
-      const uint32_t idesc0 = (5u << 7) | (0u << 10) | ((uint32_t)(256 >> 3) << 17) | (1u << 23) | ((256u >> 4) << 24);
+      const uint32_t idesc0 = ((p.wfmt == 0 ? 5u : p.wfmt == 1 ? 0u : 1u) << 7) | (0u << 10) | ((uint32_t)(256 >> 3) << 17) | (1u << 23) | ((256u >> 4) << 24);
       for (int it = 0; it < nunits; it++) {
         const int s = it % C::STAGES;
         const uint32_t ph = (uint32_t)((it / C::STAGES) & 1);
@@ -583,8 +583,8 @@ int tcp2_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x
   }
   const int nwt = pair ? 2 : 1;
   CUtensorMap mw, mx, msfa, msfb;
-  int rc = tc_make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, (uint64_t)pl.TN * pl.KS * nwt * 128, 64,
-                       pair ? 128u : (uint32_t)pl.uks * 128u);
+  int rc = tc_make_map(&mw, base.wfmt ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq,
+                       (uint64_t)pl.TN * pl.KS * nwt * 128, base.wfmt ? 128 : 64, pair ? 128u : (uint32_t)pl.uks * 128u);
   if (rc) return rc;
   rc = tc_make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, terms, (uint64_t)pl.Mpad * pl.KS * 2, 128, 128);
   if (rc) return rc;

@@ -216,7 +216,8 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const uint32_t bar = tc_smem_u32(&bar_full[s]);
         const uint32_t sb = st + C::X_BYTES, ssf = sb + C::B_BYTES + UKS * 512;
         const bool second = has_b(t);
-        tc_mbar_expect_tx(bar, C::X_BYTES + UKS * 512 + UKS * (second ? C::B_TX + 1024 : C::B_TX / 2 + 512));
+        const int b_tx = p.wfmt ? 2 * C::B_TX : C::B_TX;  // 8-bit weights arrive byte for byte, packed 4-bit ones at half the footprint
+        tc_mbar_expect_tx(bar, C::X_BYTES + UKS * 512 + UKS * (second ? b_tx + 1024 : b_tx / 2 + 512));
 #pragma unroll
         for (int kk = 0; kk < UKS; kk++) {
           const int ta = wtile_a(t, ks * UKS + kk), tb = wtile_b(t, ks * UKS + kk);
@@ -284,7 +285,7 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       // A = E4M3 (0), B = E2M1 (5), both K-major, N = 256, UE8M0 scales, M = 128
-      const uint32_t idesc0 = (0u << 7) | (5u << 10) | ((256u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
+      const uint32_t idesc0 = (0u << 7) | ((p.wfmt == 0 ? 5u : p.wfmt == 1 ? 0u : 1u) << 10) | ((256u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
       int ks = ks0;
       uint32_t acc_phase = 0;
       bool fresh = true;
@@ -661,7 +662,8 @@ int tcw_run(const uint8_t* wq, const uint8_t* sfa, bool pair, const uint16_t* x,
   }
   CUtensorMap mw, mx;
   const uint64_t wrows = (uint64_t)(pair ? pl.TN * 2 : pl.tiles128) * pl.KS * 128;
-  rc = tc_make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, wrows, 64, pair ? 256 : 128);
+  rc = tc_make_map(&mw, base.wfmt ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, wq, wrows, base.wfmt ? 128 : 64,
+                   pair ? 256 : 128);
   if (rc) return rc;
   rc = tc_make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, terms, (uint64_t)pl.KS * 2 * pl.tokp, 128, (uint32_t)(pl.uks * 2 * pl.tokp));
   if (rc) return rc;

@@ -77,7 +77,29 @@ def make_layer(shape, weights, layer_idx, ep, weight_dtype, device):
     return layer
 
 
+class _DecodeSession:
+    """What one recorded decode step needs to be replayed by a later generate() call of the same batch size: the KV
+    cache (sized once for the longest request so far), the tensors the recorded kernels read their inputs from, and the
+    CUDA graph. Recording a step of a 32-layer model costs tens of milliseconds, as much as a dozen decoded tokens."""
+
+    def __init__(self, cache, batch, need):
+        self.cache, self.batch, self.need = cache, batch, need
+        self.graph = self.tok = self.pos = self.dev_len = self.am = None
+        self.capacity, self.arenas = 0, None
+
+    def cache_fits(self, batch, need):
+        layers = self.cache.get_cpp().layers
+        return self.batch == batch and layers and all(lc.contiguous() and lc.capacity() >= need for lc in layers)
+
+    def graph_fits(self, cpp, cap):
+        return (self.graph is not None and self.capacity == cap
+                and self.arenas == [id(a[0]) for lc in cpp.layers for a in lc.arenas])
+
+
 class LlamaRunner(torch.nn.Module):
+    _session = None             # cache + recorded decode step kept by generate() for its next call (_DecodeSession)
+    reuse_decode_graph = True   # False: every generate() call builds its cache and records its decode step anew
+
     def __init__(self, shape, embed, layers, norm_w, lm_head_w, ep):
         super().__init__()
         self.shape, self.embed, self.layers, self.norm_w, self.ep = shape, embed, layers, norm_w, ep
@@ -136,21 +158,43 @@ class LlamaRunner(torch.nn.Module):
         With use_graph the decode step (embedding, all layers, head, argmax, length bump) is recorded once in a CUDA
         graph and replayed: the lengths the kernels need live in device memory, the cache is sized up front, and the
         host only replays. Returns [B, prompt + max_new_tokens] token ids."""
-        cache = TppCache()
+        B, P = input_ids.shape
+        sess = None
+        if use_graph and max_new_tokens - 1 >= 3 and self.reuse_decode_graph:
+            # the cache and the recorded step of the previous call serve again when the batch is the same and the
+            # request fits the cache; else a new cache is sized for this request in one piece
+            need = P + max_new_tokens
+            sess = self._session
+            if sess is None or not sess.cache_fits(B, need):
+                sess = self._session = None  # frees the old cache before the new one is allocated
+                sess = self._session = _DecodeSession(TppCache(), B, need)
+                cpp = sess.cache.get_cpp()
+                for i, layer in enumerate(self.layers):
+                    cpp.layer(i).ensure(B, layer.Nkv, layer.H, need, torch.bfloat16, input_ids.device)
+            else:
+                for lc in sess.cache.get_cpp().layers:
+                    lc.offset = 0
+        cache = sess.cache if sess is not None else TppCache()
         mask = attention_mask if attention_mask is not None else torch.ones_like(input_ids)
         # positions count the kept tokens only, in the prompt as in the decode steps (HF generate: cumsum(mask) - 1),
         # so that a left-padded sequence rotates its tokens as the unpadded one would
         prompt_pos = (mask.to(torch.int64).cumsum(-1) - 1).clamp_(min=0).contiguous() if attention_mask is not None else None
         logits, cache = self.forward(input_ids, mask, prompt_pos, cache)
         tok = fused_llm_cpp.argmax_rows(logits[:, -1]).unsqueeze(-1)
-        new = self.decode(tok, cache, mask, max_new_tokens - 1, use_graph=use_graph)
+        new = self.decode(tok, cache, mask, max_new_tokens - 1, use_graph=use_graph, session=sess)
         return torch.cat([input_ids, new], dim=1)
 
+    def release_session(self):
+        """Drop the cache and the recorded decode step kept for the next generate() call."""
+        self._session = None
+
     @torch.no_grad()
-    def decode(self, tok, cache, mask, steps, use_graph=True, timing=None):
+    def decode(self, tok, cache, mask, steps, use_graph=True, timing=None, session=None):
         """`steps` greedy decode steps from a cache that already holds the context: tok [B, 1] is the first new token
         (not yet in the cache), mask [B, context] the keep-mask of the cached tokens. Returns [B, 1 + steps] tokens.
-        timing: optional dict; receives 'events' = (start, end) CUDA events around the replayed steps and 'steps'."""
+        timing: optional dict; receives 'events' = (start, end) CUDA events around the replayed steps and 'steps'.
+        session: a _DecodeSession whose recorded step is replayed if it was recorded for this cache and capacity, and
+        which otherwise receives the step recorded now."""
         cpp = cache.get_cpp()
         B = tok.shape[0]
         dev = tok.device
@@ -180,7 +224,14 @@ class LlamaRunner(torch.nn.Module):
 
         done = 0
         graph = None
-        if use_graph and steps >= 3:
+        if use_graph and steps >= 3 and session is not None and session.graph_fits(cpp, cap):
+            # the recorded kernels read these tensors: refill them in place and replay
+            session.tok.copy_(tok)
+            session.pos.copy_(pos)
+            session.dev_len.copy_(dev_len)
+            session.am.copy_(am)
+            tok, graph = session.tok, session.graph
+        elif use_graph and steps >= 3:
             step()  # eager once: sizes scratch buffers and opts kernels in to their shared-memory sizes
             outs.append(tok.clone())
             done = 1
@@ -209,6 +260,10 @@ class LlamaRunner(torch.nn.Module):
         for lc in cpp.layers:
             lc.offset += steps
         self.last_graph = graph
+        if session is not None and graph is not None and session.graph is not graph:
+            session.graph, session.tok, session.pos, session.dev_len, session.am = graph, tok, pos, dev_len, am
+            session.capacity = cap
+            session.arenas = [id(a[0]) for lc in cpp.layers for a in lc.arenas]
         out = torch.cat(outs, dim=1)
         from .. import _lib
         _lib.assert_no_kernel_error()  # a kernel that gave up on a bounded wait would have produced wrong tokens
