@@ -401,15 +401,13 @@ def run_ours(args):
         for mi, M in enumerate(SWEEP):
             wg, wu, wd = sets[counter[0] % N_COPIES]
             counter[0] += 1
-            x = xs_host[M].to(dev, non_blocking=True) if host else xs[M]
+            x = xs_host[M] if host else xs[M]
             c0 = launch_count()
             h = F.fc_gate_up(x, wg, wu)
             c1 = launch_count()
-            y = F.fc_plain(h, wd)
+            y = F.fc_plain(h, wd, out=ys_host[M] if host else None)
             per_op_launches[(M, "gate_up")], per_op_launches[(M, "down")] = c1 - c0, launch_count() - c1
             hs[M] = h
-            if host:
-                ys_host[M].copy_(y, non_blocking=True)
 
     def run_shape(M, pair, n, ev):
         """n launches of one shape back to back, weights rotating over the copies, one event pair around them: the
@@ -494,23 +492,33 @@ def run_ours(args):
     for _ in range(2):
         sweep(host=True)
     barrier()
-    e_evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in SWEEP] for _ in range(args.steps)]
-    e2e_ms = np.zeros(len(SWEEP))
-    for s in range(args.steps):
-        for mi, M in enumerate(SWEEP):
-            wg, wu, wd = sets[counter[0] % N_COPIES]
-            counter[0] += 1
-            a, b = e_evs[s][mi]
-            a.record()
-            x = xs_host[M].to(dev, non_blocking=True)
-            y = F.fc_plain(F.fc_gate_up(x, wg, wu), wd)
-            ys_host[M].copy_(y, non_blocking=True)
-            b.record()
-    barrier()
-    for s in range(args.steps):
-        for mi in range(len(SWEEP)):
-            e2e_ms[mi] += e_evs[s][mi][0].elapsed_time(e_evs[s][mi][1])
-    e2e_ms /= args.steps
+    # K steps over the decode shapes (the ones `value` is computed from), one event pair around all of them: the host
+    # issues every launch inside the timed region (no kernel holds the stream back for it), so the figure is the
+    # smaller of what the host path and the device sustain; repeated like the device-timed block.
+    cur = torch.cuda.current_stream()
+    e2e_total, e2e_rounds = 0.0, 0
+    while True:
+        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ea.record(cur)
+        for s in range(args.steps):
+            for mi in dec:
+                M = SWEEP[mi]
+                wg, wu, wd = sets[counter[0] % N_COPIES]
+                counter[0] += 1
+                # the public ops take the pinned host buffers themselves: the activation-split kernel reads X across
+                # the bus, the down projection's epilogue writes Y to host memory (no separate copies in the stream)
+                F.fc_plain(F.fc_gate_up(xs_host[M], wg, wu), wd, out=ys_host[M])
+        eb.record(cur)
+        barrier()
+        e2e_total += ea.elapsed_time(eb) / args.steps
+        e2e_rounds += 1
+        flag = torch.tensor([1.0 if (e2e_total * args.steps >= args.min_seconds * 250.0 or e2e_rounds >= 500) else 0.0], device=dev)
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if flag.item() > 0 or not dec:
+            break
+    e2e_step_ms = e2e_total / e2e_rounds
     _lib.assert_no_kernel_error()
     parity = parity_spot_check(sets[0], w_cpu, xs_host, dev) if rank == 0 else None
 
@@ -518,7 +526,7 @@ def run_ours(args):
     dec_ms = float(sum(seg[i].sum() for i in dec))
     pre_flops = sum(op_flops(SWEEP[i], True) + op_flops(SWEEP[i], False) for i in pre)
     pre_ms = float(sum(seg[i].sum() for i in pre))
-    stats = torch.tensor([total_ms, dec_ms, pre_ms, float(sum(e2e_ms[i] for i in dec))], device=dev, dtype=torch.float64)
+    stats = torch.tensor([total_ms, dec_ms, pre_ms, e2e_step_ms], device=dev, dtype=torch.float64)
     per_rank = [stats.clone() for _ in range(world)]
     if world > 1:
         dist.all_gather(per_rank, stats)
@@ -563,9 +571,11 @@ def run_ours(args):
                          "duration": "CUDA events around K back-to-back launches of the op (activation-split kernel + GEMM kernel each), divided by K"},
             "kernels": kernels,
             "e2e": {"value": e2e_value, "unit": "GB/s",
-                    "h2d_bytes_per_step": sum(M * D_MODEL * 2 for M in SWEEP),
-                    "d2h_bytes_per_step": sum(M * D_MODEL * 2 for M in SWEEP),
-                    "scope": "same decode-shaped launches, pinned host X in and host Y out inside the timed region"},
+                    "h2d_bytes_per_step": sum(SWEEP[i] * D_MODEL * 2 for i in dec),
+                    "d2h_bytes_per_step": sum(SWEEP[i] * D_MODEL * 2 for i in dec), "rounds": e2e_rounds,
+                    "scope": "the decode-shaped launches (M <= 64) through the public ops with pinned HOST X in and pinned host Y out: the "
+                             "kernels read X from and write Y to host memory directly (every byte crosses the bus inside the timed "
+                             "region); K steps inside one event pair, the host issuing every launch inside it"},
             "gpu_launches": int(timed_launches),
             "timed": {"rounds": rounds, "prefill_rounds": pre_rounds,
                       "note": "decode-shaped and many-token launches are timed in separate blocks of K steps, each repeated until its "

@@ -267,3 +267,30 @@ def test_tiles_cut_between_ctas(cuda, M):
         y = F.fc_gate_up(to_dev_bf16(x, cuda), q, q2)
         assert_no_kernel_error()
         assert O.rel_err(to_host_bits(y), ref_pair) <= TOL
+
+
+@pytest.mark.parametrize("M", [1, 8, 64, 200])
+def test_pinned_host_input_and_output(cuda, M, mxfp4_path):
+    """The MXFP4 tensor-core ops accept pinned host memory for the input and for out=: the kernels read and write it
+    across the bus. Same kernels on the same values: bit-identical to the device-resident call."""
+    from tpp_pytorch_extension_b200 import _lib
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    rng = np.random.default_rng(900 + M)
+    N, K = 256, 512
+    qg, _, _ = make_qweight(rng, N, K, "mxfp4", cuda)
+    qu, _, _ = make_qweight(rng, N, K, "mxfp4", cuda)
+    qd, _, _ = make_qweight(rng, K, N, "mxfp4", cuda)
+    x_host = torch.from_numpy(O.randn_bf16(rng, (M, K)).view(np.int16)).view(torch.bfloat16).pin_memory()
+    y_host = torch.zeros((M, K), dtype=torch.bfloat16).pin_memory()
+    if mxfp4_path == "stream":
+        with pytest.raises(_lib.TpxError):
+            F.fc_gate_up(x_host, qg, qu)
+        return
+    want = F.fc_plain(F.fc_gate_up(x_host.to(cuda), qg, qu), qd)
+    got = F.fc_plain(F.fc_gate_up(x_host, qg, qu), qd, out=y_host)
+    assert got is y_host
+    torch.cuda.synchronize()
+    assert torch.equal(y_host, want.cpu())
+    assert_no_kernel_error()
+    with pytest.raises(_lib.TpxError):  # pageable host memory is refused
+        F.fc_gate_up(x_host.clone(), qg, qu)

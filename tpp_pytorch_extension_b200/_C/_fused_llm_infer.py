@@ -70,7 +70,7 @@ def _int8_tc(x, y, w, w2, bias, act, mul_in, res, res_scale, norm=None):
         nb = _SCRATCH_BYTES.get(key)
         if nb is None:
             nb = _SCRATCH_BYTES[key] = L.tpx_qlinear_qint8_tc_scratch_bytes(M, N, K, wt.block_size)
-        sc = _lib.scratch(nb, x.device)
+        sc = _lib.scratch(nb, dev)
         rc = L.tpx_qlinear_qint8_tc(wq.data_ptr(), sw.data_ptr(), x.data_ptr(), _lib.ptr(gam), int(gam is not None and gam.dtype == torch.float32),
                                     eps, M, N, K, wt.block_size, reuse, _lib.ptr(b), ACT[a], _lib.ptr(m),
                                     _lib.ptr(r), float(rs), out.data_ptr(), sc.data_ptr(), sc.numel(), _lib.stream())
@@ -140,24 +140,42 @@ def _wrap_fp8(w):
     return w
 
 
-def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
+def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None, out=None):
     w, w2 = _wrap_fp8(w), _wrap_fp8(w2)
     if isinstance(w, torch.Tensor) and w2 is None:
+        if out is not None:
+            raise _lib.TpxError("fc_plain: out= is served for quantized weights only")
         if norm is not None:
             x = rms_norm(x, norm[0], norm[1])
         return _bf16_linear(x, w, bias, act, mul_in, res, res_scale)
     if not isinstance(w, QTensor):
         raise _lib.TpxError("fc_plain: weight must be a quantized tensor from remap_and_quantize_* or a bf16 tensor")
-    _lib.require_cuda(x, "input")
+    # Host buffers: a PINNED host tensor may stand in for the input and for out= on the MXFP4 tensor-core path. Pinned
+    # memory is addressable from the device, so the activation-split kernel reads x across the bus and the epilogue
+    # writes y there: no separate copies, which on decode-sized tensors cost more stream time than the linear itself.
+    host_in = not x.is_cuda
+    if host_in:
+        if not (x.is_pinned() and x.is_contiguous() and w.kind == 1 and mxfp4_path() == "tc" and norm is None):
+            raise _lib.TpxError("input must be a CUDA tensor (a pinned, contiguous host tensor is accepted by the MXFP4 tensor-core path)")
+        dev = torch.device("cuda", _lib.current_device())
+    else:
+        _lib.require_cuda(x, "input")
+        dev = x.device
     if x.dtype != torch.bfloat16:
         raise _lib.TpxError("fc_plain: input must be bfloat16")
     N, K = w.out_features, w.in_features
     if x.shape[-1] != K:
         raise _lib.TpxError(f"fc_plain: input features {x.shape[-1]} do not match weight in-features {K}")
     M = x.numel() // K
-    y = torch.empty(x.shape[:-1] + (N,), dtype=torch.bfloat16, device=x.device)
+    if out is not None:
+        if (tuple(out.shape) != tuple(x.shape[:-1]) + (N,) or out.dtype != torch.bfloat16 or not out.is_contiguous()
+                or not (out.is_cuda or (out.is_pinned() and w.kind == 1 and mxfp4_path() == "tc"))):
+            raise _lib.TpxError("fc_plain: out= must be a contiguous bfloat16 tensor of the result's shape on the device (or pinned host memory, MXFP4 tensor-core path)")
+        y = out
+    else:
+        y = torch.empty(x.shape[:-1] + (N,), dtype=torch.bfloat16, device=dev)
     L = _lib.lib()
-    if x.device.index != torch.cuda.current_device():
+    if dev.index != _lib.current_device():
         raise _lib.TpxError("fc_plain: input lives on a device other than the current one")
     for name, t in (("bias", bias), ("mul_in", mul_in), ("res", res)):
         if t is not None and t.numel() > 0:
@@ -170,7 +188,7 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
         nb = _SCRATCH_BYTES.get(key)
         if nb is None:
             nb = _SCRATCH_BYTES[key] = L.tpx_qlinear_fp8_tc_scratch_bytes(M, N, K, int(w2 is not None))
-        sc = _lib.scratch(nb, x.device)
+        sc = _lib.scratch(nb, dev)
         gamma = eps = None
         if norm is not None and K <= 8192 and _opt("TPX_FUSED_NORM", "1") != "0":
             gamma, eps = norm
@@ -193,7 +211,7 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
         nb = _SCRATCH_BYTES.get(key)
         if nb is None:
             nb = _SCRATCH_BYTES[key] = L.tpx_qlinear_mxfp4_tc_scratch_bytes(M, N, K, int(w2 is not None))
-        sc = _lib.scratch(nb, x.device)
+        sc = _lib.scratch(nb, dev)
         if norm is not None and K <= 8192 and _opt("TPX_FUSED_NORM", "1") != "0":
             gamma, eps = norm
             rc = L.tpx_rmsnorm_qlinear_mxfp4_tc(wq.data_ptr(), sfa.data_ptr(), int(w2 is not None), x.data_ptr(), gamma.data_ptr(),
@@ -229,7 +247,7 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
     nb = _SCRATCH_BYTES.get(key)
     if nb is None:
         nb = _SCRATCH_BYTES[key] = L.tpx_qlinear_scratch_bytes(w.kind, M, N, K, w.block_size, int(w2 is not None))
-    sc = _lib.scratch(nb, x.device)
+    sc = _lib.scratch(nb, dev)
     rc = L.tpx_qlinear(w.kind, pc.data_ptr(), ps.data_ptr(), _lib.ptr(pc2), _lib.ptr(ps2), w.block_size,
                        x.data_ptr(), M, N, K, _lib.ptr(bias), ACT[act], _lib.ptr(mul_in), _lib.ptr(res),
                        float(res_scale), y.data_ptr(), sc.data_ptr(), sc.numel(), _lib.stream())
@@ -238,12 +256,13 @@ def _qlinear(x, w, w2, bias, act, mul_in, res, res_scale, norm=None):
     return y
 
 
-def fc_plain(input, weight, bias=None, parallel_dim=-1, split_sizes=()):
-    """torch.ops.tpp_llm.fc_plain (src/csrc/llm/fused_llm_infer.cpp:1514-1566), single-rank form."""
+def fc_plain(input, weight, bias=None, parallel_dim=-1, split_sizes=(), out=None):
+    """torch.ops.tpp_llm.fc_plain (src/csrc/llm/fused_llm_infer.cpp:1514-1566), single-rank form. Extension: out= (a
+    device tensor or, for MXFP4 weights, pinned host memory) receives the result; the input may be pinned host memory."""
     if parallel_dim != -1:
         from ..llm import llm_common
         return llm_common.fc_plain_parallel(input, weight, bias, parallel_dim, list(split_sizes))
-    return _qlinear(input, weight, None, bias, None, None, None, 1.0)
+    return _qlinear(input, weight, None, bias, None, None, None, 1.0, out=out)
 
 
 def fc_plain_act(input, weight, bias=None, act=None, mul_in=None, res=None, res_scale=1.0):
