@@ -133,7 +133,8 @@ int tpx_qlinear(int kind, const uint8_t* pk_codes, const void* pk_scales, const 
  * (codes2/scales2 NULL = one weight). With pair != 0 the linear computes y = act(x.Wg^T) * (x.Wu^T).
  * Activations are split on the device into two E4M3 terms with a shared power-of-two block scale
  * (exact for bf16 inputs within 2^-10 of their block maximum). The scratch buffer holds those terms and the
- * partial tiles; its first 64 KiB must be zero before first use, as for tpx_qlinear.                       */
+ * partial tiles; its first 64 KiB must be zero before first use, as for tpx_qlinear. x and y may also be
+ * pinned (page-locked, device-addressable) host memory: the kernels then read x and write y across the bus.   */
 int tpx_tc_packed_bytes(int64_t N, int64_t K, int pair, size_t* wq_bytes, size_t* sfa_bytes);
 int tpx_repack_mxfp4_tc(const uint8_t* codes, const uint8_t* scales, const uint8_t* codes2, const uint8_t* scales2,
                         int64_t N, int64_t K, uint8_t* wq, uint8_t* sfa, void* stream);
