@@ -70,7 +70,7 @@ def _int8_tc(x, y, w, w2, bias, act, mul_in, res, res_scale, norm=None):
         nb = _SCRATCH_BYTES.get(key)
         if nb is None:
             nb = _SCRATCH_BYTES[key] = L.tpx_qlinear_qint8_tc_scratch_bytes(M, N, K, wt.block_size)
-        sc = _lib.scratch(nb, dev)
+        sc = _lib.scratch(nb, x.device)
         rc = L.tpx_qlinear_qint8_tc(wq.data_ptr(), sw.data_ptr(), x.data_ptr(), _lib.ptr(gam), int(gam is not None and gam.dtype == torch.float32),
                                     eps, M, N, K, wt.block_size, reuse, _lib.ptr(b), ACT[a], _lib.ptr(m),
                                     _lib.ptr(r), float(rs), out.data_ptr(), sc.data_ptr(), sc.numel(), _lib.stream())

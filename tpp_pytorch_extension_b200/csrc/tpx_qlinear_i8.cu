@@ -443,14 +443,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 #pragma unroll
         for (int i = 0; i < 16; i++) v[i] = v2[i] = 0.0f;
         const uint32_t sp = smem_base + (uint32_t)((row * TOK + c0) * 4);
-        for (int m = 0; m < csize; m++) {
-          const uint32_t rp = tc_mapa(sp, (uint32_t)m);
-#pragma unroll
-          for (int q = 0; q < 4; q++) {
-            const float4 t4 = tc_ld_cluster_f4(rp + q * 16);
-            v[4 * q] += t4.x; v[4 * q + 1] += t4.y; v[4 * q + 2] += t4.z; v[4 * q + 3] += t4.w;
-          }
-        }
+        tc_cluster_sum<4, 2>(sp, csize, v);
         if (n < p.t.N && tm * TOK + c0 < p.t.M) tc_finish16<false>(p.t, tm * TOK + c0, n, v, v2);
       }
     }

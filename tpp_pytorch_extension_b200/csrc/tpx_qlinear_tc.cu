@@ -635,20 +635,8 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 #pragma unroll
         for (int j = 0; j < 16; j++) v[j] = v2[j] = 0.0f;
         const uint32_t sp = smem_base + (uint32_t)((row * TOK + c0) * 4);
-        for (int m = 0; m < p.cluster; m++) {
-          const uint32_t rp = tc_mapa(sp, (uint32_t)m);
-          float4 t[4], t2[4];
-#pragma unroll
-          for (int q = 0; q < 4; q++) {
-            t[q] = tc_ld_cluster_f4(rp + q * 16);
-            if (DUAL) t2[q] = tc_ld_cluster_f4(rp + 128 * TOK * 4 + q * 16);
-          }
-#pragma unroll
-          for (int q = 0; q < 4; q++) {
-            v[4 * q] += t[q].x; v[4 * q + 1] += t[q].y; v[4 * q + 2] += t[q].z; v[4 * q + 3] += t[q].w;
-            if (DUAL) { v2[4 * q] += t2[q].x; v2[4 * q + 1] += t2[q].y; v2[4 * q + 2] += t2[q].z; v2[4 * q + 3] += t2[q].w; }
-          }
-        }
+        tc_cluster_sum<4, 4>(sp, p.cluster, v);
+        if (DUAL) tc_cluster_sum<4, 4>(sp + 128 * TOK * 4, p.cluster, v2);
         if (n < p.N && tok0 + c0 < p.M) tc_finish16<DUAL>(p, tok0 + c0, n, v, v2);
       }
     }

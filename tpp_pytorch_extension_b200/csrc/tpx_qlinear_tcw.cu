@@ -437,12 +437,16 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     // members, each adds the members' parts in rank order (distributed shared memory reads) and finishes its groups.
     // Nobody leaves before all have finished reading.
     tc_cluster_sync();
+    if (threadIdx.x == 128) tc_stamp(p, 4);
     if (warp >= 2) {
       constexpr int GROUPS = DUAL ? 16 : 32;  // groups of 8 output features per token
       constexpr int NT = C::THREADS - 64;
       const int et = (int)threadIdx.x - 64;
       const int live_tok = p.M < TOKP ? p.M : TOKP;
-      for (int i = crank * NT + et; i < live_tok * GROUPS; i += NT * p.cluster) {
+      // items go round the members a warp's worth at a time, so that every member's shared memory port and store
+      // path carry an equal share (handed out a CTA's worth at a time, 16 tokens left everything to the first member:
+      // 128 KB through one SM's port, 4.3 us)
+      for (int i = (((et >> 5) * p.cluster + crank) << 5) + (et & 31); i < live_tok * GROUPS; i += NT * p.cluster) {
         const int tk = i / GROUPS, col = (i % GROUPS) * 8;
         const int n = DUAL ? (int)ctile * 128 + col : (int)ctile * 256 + col;
         if (n >= p.N) continue;
@@ -450,20 +454,14 @@ qlinear_tcw_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 #pragma unroll
         for (int q = 0; q < 8; q++) v[q] = u[q] = 0.0f;
         const uint32_t sp = smem_base + (uint32_t)((tk * 256 + col) * 4);
-        for (int m = 0; m < p.cluster; m++) {
-          const uint32_t rp = tc_mapa(sp, (uint32_t)m);
-          const float4 a0 = tc_ld_cluster_f4(rp), a1 = tc_ld_cluster_f4(rp + 16);
-          v[0] += a0.x; v[1] += a0.y; v[2] += a0.z; v[3] += a0.w; v[4] += a1.x; v[5] += a1.y; v[6] += a1.z; v[7] += a1.w;
-          if (DUAL) {
-            const float4 b0 = tc_ld_cluster_f4(rp + 512), b1 = tc_ld_cluster_f4(rp + 528);
-            u[0] += b0.x; u[1] += b0.y; u[2] += b0.z; u[3] += b0.w; u[4] += b1.x; u[5] += b1.y; u[6] += b1.z; u[7] += b1.w;
-          }
-        }
+        tc_cluster_sum<2, 4>(sp, p.cluster, v);
+        if (DUAL) tc_cluster_sum<2, 4>(sp + 512, p.cluster, u);
         tcw_finish8<DUAL>(p, tk, n, v, u);
       }
     }
     tc_cluster_sync();
   }
+  if (threadIdx.x == 128) tc_stamp(p, 7);
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)C::TMEM_COLS) : "memory");

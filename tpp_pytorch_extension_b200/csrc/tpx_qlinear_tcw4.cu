@@ -731,15 +731,8 @@ qlinear_tcw4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll
         for (int q = 0; q < 8; q++) v[q] = u[q] = 0.0f;
         const uint32_t sp = smem_base + (uint32_t)((tk * 256 + col) * 4);
-        for (int m = 0; m < p.cluster; m++) {
-          const uint32_t rp = tc_mapa(sp, (uint32_t)m);
-          const float4 a0 = tc_ld_cluster_f4(rp), a1 = tc_ld_cluster_f4(rp + 16);
-          v[0] += a0.x; v[1] += a0.y; v[2] += a0.z; v[3] += a0.w; v[4] += a1.x; v[5] += a1.y; v[6] += a1.z; v[7] += a1.w;
-          if (DUAL) {
-            const float4 b0 = tc_ld_cluster_f4(rp + 512), b1 = tc_ld_cluster_f4(rp + 528);
-            u[0] += b0.x; u[1] += b0.y; u[2] += b0.z; u[3] += b0.w; u[4] += b1.x; u[5] += b1.y; u[6] += b1.z; u[7] += b1.w;
-          }
-        }
+        tc_cluster_sum<2, 4>(sp, p.cluster, v);
+        if (DUAL) tc_cluster_sum<2, 4>(sp + 512, p.cluster, u);
         w4_finish<DUAL, 8>(p, tk, n, v, u);
       }
     }
