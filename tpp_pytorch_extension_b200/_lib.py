@@ -9,7 +9,7 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_SO = os.path.join(_HERE, "libtpx_b200.so")
+_SO = os.environ.get("TPX_LIBRARY") or os.path.join(_HERE, "libtpx_b200.so")  # TPX_LIBRARY: another build of the library (experiments)
 _lib = None
 
 c_i64, c_int, c_f32, c_vp, c_sz = ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
