@@ -280,8 +280,11 @@ def model_decode_leg(name, shape, batch, context, steps, dev, world, rank, real_
         tok = torch.randint(0, shape.vocab_size, (batch, 1), generator=g).to(dev)
         out["context_source"] = "random KV cache of the prefilled shape (a decode step's cost does not depend on the values)"
     timing = {}
+    sampler = ClockSampler(dev.index)  # the leg's own clock record: a decode right behind a long prefill starts power-capped
+    sampler.start()
     runner.decode(tok, cache, mask, steps + 1, use_graph=True, timing=timing)
     torch.cuda.synchronize()
+    out["clocks"] = sampler.stop()
     ms = timing["events"][0].elapsed_time(timing["events"][1]) / max(1, timing["steps"])
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
@@ -621,7 +624,7 @@ def main():
     ap.add_argument("--ms", default="", help="comma-separated subset of the token counts to run (for profiler captures)")
     ap.add_argument("--legs", default="cfg3,cfg4,cfg5", help="model-level decode legs to run after the op sweep: cfg3 (Llama-2-7B shape, int8, one GPU), cfg4 (Llama-3-8B shape, one GPU), "
                     "cfg5 (Llama-2-70B shape, tensor parallel over --gpus ranks); empty for none")
-    ap.add_argument("--model-steps", type=int, default=24, help="decode steps timed in each model-level leg")
+    ap.add_argument("--model-steps", type=int, default=48, help="decode steps timed in each model-level leg")
     ap.add_argument("--cfg5-layers", type=int, default=0, help="decoder layers of the 70B-shape leg (0 = all 80)")
     ap.add_argument("--min-seconds", type=float, default=1.0, help="repeat the K timed steps until this much device time was measured")
     args = ap.parse_args()
