@@ -6,6 +6,12 @@ legs. The product package never imports it.
 bf16 tensors are carried as numpy uint16 arrays holding the bf16 bit patterns, so that every
 rounding is explicit. Layout functions restate, step by step, the tensor views/permutes of the
 reference (file:line cited per function, paths relative to the reference root).
+
+Pinned against the reference: the MXFP4 element / scale / block quantizer and the dequantization table (its own
+test vectors and, where the shim builds, its compiled conversion functions). Pinned against stock PyTorch: the 8-bit
+floating-point casts, LayerNorm. Parity unpinned (restatements with no reference vector or runnable reference code
+to hold them to): the int8 and the ternary quantizers, the blocked layouts (checked by address arithmetic), and the
+GEMM / attention / layer math (cross-checked against Hugging Face's forward in the GPU tests instead).
 """
 import ctypes
 import os
