@@ -376,15 +376,16 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 //   and with more than one KV split the CTA writes an un-normalised partial that the last-arriving split merges.
 // Rows of a KV block are kept 16 bytes apart from a power-of-two pitch so that ldmatrix is conflict-free.
 template <int H, int MODE>
-__global__ void __launch_bounds__(kAttnWarps * 32) attn_mma_kernel(AttnParams p) {
+__global__ void __launch_bounds__((MODE == 0 ? kAttnWarps : kDecWarps) * 32) attn_mma_kernel(AttnParams p) {
+  constexpr int WARPS = MODE == 0 ? kAttnWarps : kDecWarps;
   constexpr int PB = H * 2 + 16;        // bytes per key row in shared memory
   constexpr int TILE = 32 * PB;         // one block of keys or of values
   constexpr int STAGE = 2 * TILE;       // keys, then values
   constexpr int NT = H / 8;             // output n-tiles
   constexpr int KK = H / 16;            // k steps of Q.K^T
-  constexpr int GROUP = MODE == 0 ? kAttnWarps * 32 : 32;  // threads that share a KV stream
+  constexpr int GROUP = MODE == 0 ? WARPS * 32 : 32;  // threads that share a KV stream
   extern __shared__ __align__(16) unsigned char attn_smem[];
-  __shared__ float red_m[kAttnWarps][kAttnRows], red_l[kAttnWarps][kAttnRows];
+  __shared__ float red_m[WARPS][kAttnRows], red_l[WARPS][kAttnRows];
 
   pdl_trigger();
   pdl_wait();
@@ -457,7 +458,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_mma_kernel(AttnParams p)
     if (MODE == 0) __syncthreads(); else __syncwarp();
   };
 
-  const int first = MODE == 0 ? blk0 : blk0 + warp, step = MODE == 0 ? 1 : kAttnWarps;
+  const int first = MODE == 0 ? blk0 : blk0 + warp, step = MODE == 0 ? 1 : WARPS;
   // every round commits exactly one copy group (an empty one when the stream has run out), so "all but the NST-1
   // newest groups are complete" always means "this round's block has landed"
 #pragma unroll
@@ -613,10 +614,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_mma_kernel(AttnParams p)
     const int r = i / H, h = i % H;
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kAttnWarps; w++) mm = fmaxf(mm, red_m[w][r]);
+    for (int w = 0; w < WARPS; w++) mm = fmaxf(mm, red_m[w][r]);
     float ll = 0.0f, oo = 0.0f;
 #pragma unroll
-    for (int w = 0; w < kAttnWarps; w++) {
+    for (int w = 0; w < WARPS; w++) {
       const float f = (red_m[w][r] == -INFINITY) ? 0.0f : __expf(red_m[w][r] - mm);
       ll += red_l[w][r] * f;
       oo += red_o[((size_t)w * kAttnRows + r) * H + h] * f;
@@ -851,9 +852,9 @@ static int attn_plan(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t H, i
   } else {
     double best_cost = 1e30;
     for (int s = 1; s <= 64; s++) {
-      if (s > 1 && nblocks / s < kAttnWarps) break;  // every warp of every split keeps a block
+      if (s > 1 && nblocks / s < kDecWarps) break;  // every warp of every split keeps a block
       const int64_t waves = (ctas * s + sms - 1) / sms;
-      const int per_warp = ((nblocks + s - 1) / s + kAttnWarps - 1) / kAttnWarps;
+      const int per_warp = ((nblocks + s - 1) / s + kDecWarps - 1) / kDecWarps;
       const double cost = (double)waves * (per_warp + (s > 1 ? 3 : 2));
       if (cost < best_cost * 0.97) { best_cost = cost; best = s; }  // ties go to fewer splits
     }
@@ -865,8 +866,10 @@ static int attn_plan(int64_t B, int64_t Nkv, int64_t Sq, int64_t R, int64_t H, i
 template <int H, int MODE>
 static int attn_launch(const AttnParams& p, dim3 grid, cudaStream_t st) {
   constexpr int STAGE = 2 * 32 * (H * 2 + 16);
-  constexpr size_t smem = MODE == 0 ? 2 * STAGE : (size_t)kAttnWarps * 2 * STAGE;  // two stages per stream, as in the kernel
-  static_assert(MODE == 0 || smem >= (size_t)kAttnWarps * kAttnRows * H * sizeof(float), "merge area");
+  constexpr int WARPS = MODE == 0 ? kAttnWarps : kDecWarps;
+  constexpr size_t smem = MODE == 0 ? 2 * STAGE : (size_t)WARPS * 2 * STAGE;  // two stages per stream, as in the kernel
+  static_assert(MODE == 0 || smem >= (size_t)WARPS * kAttnRows * H * sizeof(float), "merge area");
+  static_assert(smem <= 227 * 1024, "shared memory");
   static bool opted[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -874,7 +877,7 @@ static int attn_launch(const AttnParams& p, dim3 grid, cudaStream_t st) {
     TPX_CUDA_OK(cudaFuncSetAttribute(attn_mma_kernel<H, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (dev >= 0 && dev < 16) opted[dev] = true;
   }
-  TPX_CUDA_OK(launch_pdl(attn_mma_kernel<H, MODE>, grid, dim3(kAttnWarps * 32), smem, st, p));
+  TPX_CUDA_OK(launch_pdl(attn_mma_kernel<H, MODE>, grid, dim3(WARPS * 32), smem, st, p));
   return TPX_OK;
 }
 
