@@ -371,7 +371,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 // MODE 0 (prefill): a CTA owns 64 consecutive query rows (16 per warp) of one (batch, kv head); its four warps
 //   share every KV block, copied once into shared memory (two stages, cp.async).
-// MODE 1 (decoding, at most 16 query rows): all warps work on the same 16 rows and take every fourth KV block of
+// MODE 1 (decoding, at most 16 query rows): all kDecWarps warps work on the same 16 rows and take every kDecWarps-th KV block of
 //   the CTA's split, each with its own two stages; the warps' (max, sum, output) are merged through shared memory,
 //   and with more than one KV split the CTA writes an un-normalised partial that the last-arriving split merges.
 // Rows of a KV block are kept 16 bytes apart from a power-of-two pitch so that ldmatrix is conflict-free.
@@ -594,7 +594,7 @@ __global__ void __launch_bounds__((MODE == 0 ? kAttnWarps : kDecWarps) * 32) att
     return;
   }
 
-  // MODE 1: merge the four warps through shared memory (the KV stages are free now)
+  // MODE 1: merge the warps through shared memory (the KV stages are free now)
   __syncthreads();
   float* red_o = reinterpret_cast<float*>(attn_smem);  // [warp][16][H]
   if (t == 0) {
