@@ -115,3 +115,19 @@ def test_llama_on_fp8_weights_matches_hugging_face(cuda, name, dt):
     out = runner.generate(ids.to(cuda), 6)
     assert out.shape == (2, 29)
     assert_no_kernel_error()
+
+
+def test_fp8_weight_state_round_trip(cuda):
+    """Fp8Weight.state() / QTensor.from_state (what the packed checkpoints store): the restored weight carries the format,
+    the bytes and the kernel layout, and the linear on it gives the same bits."""
+    from tpp_pytorch_extension_b200._C import _fused_llm_infer as F
+    from tpp_pytorch_extension_b200._C import _qtype
+    rng = np.random.default_rng(12)
+    q, _ = make_weight(rng, 128, 256, "bfloat8", O.FP8_E5M2, cuda)
+    x = to_dev_bf16(O.randn_bf16(rng, (5, 256)), cuda)
+    want = F.fc_plain(x, q)
+    back = _qtype.QTensor.from_state(q.state(), cuda)
+    assert type(back).__name__ == "Fp8Weight" and back.fmt == q.fmt and back.shape == q.shape
+    assert torch.equal(back.codes, q.codes) and torch.equal(back.packed_tc()[0], q.packed_tc()[0])
+    assert torch.equal(F.fc_plain(x, back), want)
+    assert_no_kernel_error()
